@@ -1,0 +1,176 @@
+/*
+ * sharpnet_b200 -- C ABI of the B200 (sm_100a) replacement for the fp32 matrix-multiply path of
+ * SharpNet: Tensor.Dot, Tensor.BatchMatrixMultiplication and the Dense (Linear) layer forward /
+ * backward with its bias and activation companions.
+ *
+ * Conventions shared by every entry point
+ *   - every matrix is fp32, row-major and dense: the leading dimension equals the logical width,
+ *     exactly as SharpNet's tensors are (Prod/Data/BlasServices.cs:17-19);
+ *   - device pointers are owned by the caller, need only 4-byte alignment, and are never kept
+ *     after the call returns.  The output never aliases an input; inputs may alias each other;
+ *   - work is queued on the handle's stream (the legacy default stream unless snb200_set_stream
+ *     was called) and the call returns without synchronising, like the cuBLAS/cuDNN calls it
+ *     replaces (Prod/GPU/GpuTensor.cs:1196-1227);
+ *   - the return value is 0 on success, otherwise one of the SNB200_STATUS_* codes, which reuse
+ *     the numbering of cublasStatus_t (Prod/GPU/CublasWrapper.cs:8-20) so the caller's
+ *     GPUWrapper.CheckStatus (Prod/GPU/GPUWrapper.cs:662-668) keeps printing meaningful names;
+ *   - a handle is used by one host thread at a time; different handles are independent
+ *     (one managed thread per device, Prod/GPU/GPUWrapper.cs:782-788,824-832);
+ *   - there is no CPU fallback: without a CUDA device snb200_create fails.
+ */
+#ifndef SHARPNET_B200_H
+#define SHARPNET_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct snb200_context* snb200_handle_t;
+
+enum {
+  SNB200_STATUS_SUCCESS = 0,
+  SNB200_STATUS_NOT_INITIALIZED = 1,
+  SNB200_STATUS_ALLOC_FAILED = 3,
+  SNB200_STATUS_INVALID_VALUE = 7,
+  SNB200_STATUS_ARCH_MISMATCH = 8,
+  SNB200_STATUS_EXECUTION_FAILED = 13,
+  SNB200_STATUS_INTERNAL_ERROR = 14,
+  SNB200_STATUS_NOT_SUPPORTED = 15
+};
+
+/* Arithmetic used by the tensor-core kernels.  SharpNet never sets a cuBLAS math mode
+ * (classic fp32 SGEMM), so the default keeps fp32-level accuracy. */
+enum {
+  SNB200_MATH_3XTF32 = 0,    /* tcgen05 TF32 tensor cores, split fp32 = hi + lo, three products; default */
+  SNB200_MATH_TF32 = 1,      /* single TF32 product: opt-in fast mode, ~1e-3 relative accuracy           */
+  SNB200_MATH_FP32_SIMT = 2  /* fp32 FMA on the CUDA cores for every shape                               */
+};
+
+/* Activation selector: the values of cudnnActivationMode_t (Prod/GPU/CudnnWrapper.cs:267-281). */
+enum {
+  SNB200_ACT_SIGMOID = 0,
+  SNB200_ACT_RELU = 1,
+  SNB200_ACT_TANH = 2,
+  SNB200_ACT_IDENTITY = 5,
+  SNB200_ACT_SWISH = 6
+};
+
+/* Storage of the Dense weight matrix.
+ * OUT_IN: W is [out_features, in_features], y = x * W^T   (Prod/Layers/Linear.cs:26-33,130).
+ * IN_OUT: W is [in_features, out_features], y = x * W     (the Keras layout the golden network
+ *         tests were produced with, Tests/NonReg/TestNetworkPropagation.cs:34,95). */
+enum { SNB200_W_OUT_IN = 0, SNB200_W_IN_OUT = 1 };
+
+/* ---- handle ---------------------------------------------------------------------------------
+ * Replaces the per-device cuBLAS/cuDNN handles GPUWrapper creates and destroys
+ * (Prod/GPU/GPUWrapper.cs:99-146,737-777; cublasCreate_v2/cublasDestroy_v2
+ * Prod/GPU/CublasWrapper.cs:35-60).  The handle owns a small workspace (partial sums of the
+ * column reductions, an error word); it never owns caller tensors. */
+int snb200_create(snb200_handle_t* handle, int device_id);
+int snb200_destroy(snb200_handle_t handle);
+/* cudaStream_t passed as void*; NULL selects the legacy default stream (what SharpNet uses for
+ * all cuBLAS/cuDNN work: it never calls cublasSetStream). */
+int snb200_set_stream(snb200_handle_t handle, void* cuda_stream);
+int snb200_set_math_mode(snb200_handle_t handle, int math_mode);
+int snb200_get_math_mode(snb200_handle_t handle, int* math_mode);
+/* Text of the last error recorded on this handle (never NULL; empty when none). */
+const char* snb200_last_error_string(snb200_handle_t handle);
+/* Waits for the handle's stream and returns EXECUTION_FAILED if a kernel reported a
+ * device-side pipeline time-out since the last check. */
+int snb200_check_device_status(snb200_handle_t handle);
+/* Number of kernels this handle has launched so far, and the name of the kernel family chosen
+ * by the last compute call ("umma_3xtf32", "umma_tf32", "simt", "skinny", ...). */
+int snb200_get_launch_count(snb200_handle_t handle, long long* count);
+int snb200_get_last_kernel(snb200_handle_t handle, char* buf, int buf_len);
+int snb200_get_version(void);
+/* Kernel-selection overrides for experiments and tests (no counterpart in SharpNet).
+ * key 0: path (0 automatic, 1 tensor cores whenever the operands allow TMA, 2 SIMT fp32);
+ * key 1: tile width of the tensor-core kernel (0 automatic, else 32, 64, 128 or 256);
+ * key 2: 3xTF32 writes the rounded hi plane back to shared memory (1, default) or lets the
+ *        tensor core truncate the raw fp32 words itself (0). */
+int snb200_set_tuning(snb200_handle_t handle, int key, int value);
+
+/* ---- Tensor.Dot -----------------------------------------------------------------------------
+ * C = alpha * op(A) * op(B) + beta * C.
+ * Replaces cublasSgemm_v2 as called by GPUTensor.Dot (Prod/GPU/GpuTensor.cs:1196-1227,
+ * Prod/GPU/CublasWrapper.cs:105-122) and takes the argument list of BlasServices.DotMkl
+ * (Prod/Data/BlasServices.cs:10-21): A is stored [aH x aW], B is stored [bH x bW],
+ * M = transA ? aW : aH, N = transB ? bH : bW, K = transA ? aH : aW, and C is [M x N].
+ * INVALID_VALUE when the inner dimensions disagree or a dimension is negative. */
+int snb200_gemm(snb200_handle_t handle, int transA, int transB, int aH, int aW, int bH, int bW, float alpha,
+                const float* A, const float* B, float beta, float* C);
+
+/* ---- Tensor.BatchMatrixMultiplication -------------------------------------------------------
+ * C[i] = alpha * op(A[i]) * op(B[i]) + beta * C[i] for i in [0, batchCount).
+ * Replaces cublasSgemmStridedBatched as called by GPUTensor.BatchMatrixMultiplication
+ * (Prod/GPU/GpuTensor.cs:1163-1194); strides are element counts between consecutive matrices
+ * (MultDim0 of the 3-D tensors). */
+int snb200_batched_gemm(snb200_handle_t handle, int transA, int transB, int aH, int aW, long long strideA, int bH,
+                        int bW, long long strideB, long long strideC, int batchCount, float alpha, const float* A,
+                        const float* B, float beta, float* C);
+
+/* ---- Dense forward --------------------------------------------------------------------------
+ * y = act(x * op(W) + bias), x [M x K], y [M x N], bias [N] or NULL, in ONE kernel.
+ * Replaces Linear.DenseForwardPropagation (Prod/Layers/Linear.cs:125-132: Dot, then
+ * BroadcastAddVectorToOutput -> cudnnAddTensor, Prod/GPU/GpuTensor.cs:633-644) followed by
+ * ActivationLayer.ForwardPropagation (Prod/Layers/ActivationLayer.cs:32-38 ->
+ * cudnnActivationForward, Prod/GPU/GpuTensor.cs:438-442).
+ * z, when not NULL, receives the pre-activation x*op(W)+bias, which ActivationLayer keeps for the
+ * Swish gradient (Prod/Layers/ActivationLayer.cs:73). */
+int snb200_dense_fwd(snb200_handle_t handle, int w_layout, int M, int K, int N, const float* x, const float* W,
+                     const float* bias, int act, float* z, float* y);
+
+/* ---- Dense backward -------------------------------------------------------------------------
+ * dz = act'(.) * dy ; dW = dW_multiplier * (dz, x) product in the layout of W ; db = column sums
+ * of dz ; dx = dz * op(W)^T.
+ * Replaces ActivationLayer.BackwardPropagation (Prod/Layers/ActivationLayer.cs:39-69 ->
+ * cudnnActivationBackward, Prod/GPU/GpuTensor.cs:484-488) followed by
+ * Linear.DenseBackwardPropagation (Prod/Layers/Linear.cs:142-191: Dot for dW with
+ * multiplier = 1/batch or 1, Compute_BiasGradient_from_dy -> cudnnConvolutionBackwardBias
+ * Prod/GPU/GpuTensor.cs:686-701, Dot for dx).
+ * y is the activation output (needed unless act is IDENTITY), z the pre-activation (needed for
+ * SWISH only).  dz_scratch is a caller-provided [M x N] buffer (the ActivationLayer's dx in
+ * SharpNet); it may be NULL when act is IDENTITY.  dx may be NULL (previous layer is the input,
+ * Linear.cs:184-187); db may be NULL (layer without bias). */
+int snb200_dense_bwd(snb200_handle_t handle, int w_layout, int M, int K, int N, const float* x, const float* W,
+                     const float* dy, int act, const float* y, const float* z, float dW_multiplier,
+                     float* dz_scratch, float* dx, float* dW, float* db);
+
+/* ---- Dense companions, callable on their own ------------------------------------------------ */
+/* y[m,n] += bias[n].  Tensor.BroadcastAddVectorToOutput (Prod/Data/Tensor.cs:495,
+ * Prod/GPU/GpuTensor.cs:633-644, Prod/CPU/CpuTensor.cs:1468-1487). */
+int snb200_bias_add(snb200_handle_t handle, int M, int N, const float* bias, float* y);
+/* db[n] = sum_m dy[m,n].  Tensor.Compute_BiasGradient_from_dy (Prod/Data/Tensor.cs:710,
+ * Prod/GPU/GpuTensor.cs:686-701, Prod/CPU/CpuTensor.cs:1736-1740,3343-3362). */
+int snb200_bias_grad(snb200_handle_t handle, int M, int N, const float* dy, float* db);
+/* y = act(x) element-wise.  Tensor.ActivationForward (Prod/Data/Tensor.cs:618,
+ * Prod/GPU/GpuTensor.cs:397-443, Prod/CPU/CpuTensorActivationFunctions.cs:152-244). */
+int snb200_activation_fwd(snb200_handle_t handle, int act, long long count, const float* x, float* y);
+/* dx = act'(x, y) * dy element-wise.  Tensor.ActivationBackward (Prod/Data/Tensor.cs:628,
+ * Prod/GPU/GpuTensor.cs:445-490).  x is read for SWISH only and may be NULL otherwise. */
+int snb200_activation_bwd(snb200_handle_t handle, int act, long long count, const float* dy, const float* x,
+                          const float* y, float* dx);
+/* y += alpha * x.  Tensor.Update_Adding_Alpha_X (Prod/Data/Tensor.cs:555,
+ * Prod/GPU/GpuTensor.cs:1359-1362); used for weight decay on dW (Prod/Layers/Linear.cs:176). */
+int snb200_axpy(snb200_handle_t handle, long long count, float alpha, const float* x, float* y);
+
+/* ---- data-parallel gradient sum -------------------------------------------------------------
+ * Sum of the per-replica dW/db buffers, left on every replica.  Replaces the
+ * copy-to-master-and-add loop of Network.AddGradientFromSlaveNetwork
+ * (Prod/Networks/NetworkMultiGPUSupport.cs:161-173: cudaMemcpyPeerAsync + cudnnAddTensor) by one
+ * NCCL all-reduce over NVLink.  NCCL is loaded at run time (libnccl.so.2); without it these
+ * calls return NOT_SUPPORTED and nothing else in the library is affected.
+ *   one process per GPU:  rank 0 calls snb200_comm_get_unique_id, ships the 128 bytes to the
+ *                         other ranks, every rank calls snb200_comm_init_rank;
+ *   one thread per GPU :  snb200_comm_init_all on the array of handles (SharpNet's threading
+ *                         model, Prod/Networks/Network.cs:71-83). */
+int snb200_comm_get_unique_id(void* id_128_bytes);
+int snb200_comm_init_rank(snb200_handle_t handle, int n_ranks, int rank, const void* id_128_bytes);
+int snb200_comm_init_all(snb200_handle_t* handles, int n);
+int snb200_allreduce_sum(snb200_handle_t handle, float* buf, long long count);
+int snb200_comm_destroy(snb200_handle_t handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHARPNET_B200_H */

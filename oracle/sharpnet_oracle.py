@@ -1,0 +1,311 @@
+"""CPU oracle for the Tensor.Dot / Dense path of SharpNet.
+
+THIS IS TEST INFRASTRUCTURE, NOT PRODUCT CODE.  It restates on the CPU what SharpNet's CPU
+backend computes for the path, so that the CUDA kernels can be checked against it.  Only the test
+suite, the smoke check and the ``cpu_baseline`` / ``--impl reference`` legs of the benchmark may
+import it; nothing under ``sharpnet_b200/`` does.
+
+Where the arithmetic lives.  SharpNet's CPU path hands every matrix product to Intel MKL
+(``cblas_sgemm`` in ``mkl_rt``; no version is pinned: Prod/Data/BlasServices.cs:44-45 imports it
+by bare name).  MKL's source is not part of the reference; the stand-in here is the oneAPI MKL
+2024.2 that PyTorch links statically (``torch.addmm`` on CPU fp32 tensors calls its ``sgemm``).
+Everything around the product -- dimension rules, the batched loop, the Dense call sequence,
+bias add, bias gradient, activations and their gradients -- follows the reference's own C# code,
+cited per function.  The float64 functions are the ground truth error is measured against.
+
+Parity is pinned on the reference's own vectors: the exact ``Dot`` cases of
+Tests/GPU/TestGpuTensor.cs:50-120 and the network goldens of
+Tests/NonReg/TestNetworkPropagation.cs:80-132 and Tests/NonReg/ParallelRunWithPyTorch.cs:102-214
+(committed under tests/golden/ and checked by tests/test_oracle_golden.py).
+"""
+import math
+
+import numpy as np
+import torch
+
+# cudnnActivationMode_t values (Prod/GPU/CudnnWrapper.cs:267-281)
+ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
+W_OUT_IN, W_IN_OUT = 0, 1
+
+
+# --------------------------------------------------------------------------------------------
+# Tensor.Dot
+# --------------------------------------------------------------------------------------------
+def gemm_dims(aH, aW, transposeA, bH, bW, transposeB):
+    """M, N, K, lda, ldb, ldc as BlasServices.DotMkl derives them (Prod/Data/BlasServices.cs:14-19)."""
+    M = aW if transposeA else aH
+    N = bH if transposeB else bW
+    K = aH if transposeA else aW
+    return M, N, K, aW, bW, N
+
+
+def dot_mkl(A, aH, aW, transposeA, B, bH, bW, transposeB, C, alpha, beta):
+    """C = alpha * op(A) * op(B) + beta * C in fp32 through MKL sgemm, row-major, in place.
+
+    Mirrors BlasServices.DotMkl (Prod/Data/BlasServices.cs:10-21) as called by CpuTensor.Dot
+    (Prod/CPU/CpuTensor.cs:2991-3002).  A, B, C are flat float32 numpy arrays (C is updated and
+    returned reshaped to [M, N])."""
+    M, N, K, _, _, _ = gemm_dims(aH, aW, transposeA, bH, bW, transposeB)
+    kB = bW if transposeB else bH
+    if K != kB:
+        raise ValueError("inner dimensions differ")
+    a = torch.from_numpy(np.ascontiguousarray(A, dtype=np.float32).reshape(aH, aW))
+    b = torch.from_numpy(np.ascontiguousarray(B, dtype=np.float32).reshape(bH, bW))
+    c = torch.from_numpy(C.reshape(M, N))  # shares memory with C
+    opa = a.t() if transposeA else a
+    opb = b.t() if transposeB else b
+    if K == 0:
+        c.mul_(beta) if beta != 0 else c.zero_()
+    else:
+        torch.addmm(c, opa, opb, beta=float(beta), alpha=float(alpha), out=c)
+    return C.reshape(M, N)
+
+
+def dot_f64(A, aH, aW, transposeA, B, bH, bW, transposeB, C, alpha, beta):
+    """Same contract in float64 (ground truth); returns a new [M, N] float64 array."""
+    M, N, K, _, _, _ = gemm_dims(aH, aW, transposeA, bH, bW, transposeB)
+    a = np.asarray(A, dtype=np.float64).reshape(aH, aW)
+    b = np.asarray(B, dtype=np.float64).reshape(bH, bW)
+    opa = a.T if transposeA else a
+    opb = b.T if transposeB else b
+    out = float(alpha) * (opa @ opb)
+    if beta != 0:
+        out = out + float(beta) * np.asarray(C, dtype=np.float64).reshape(M, N)
+    return out
+
+
+def batch_matrix_multiplication(a_3D, transposeA, b_3D, transposeB, c_3D, alpha, beta, f64=False):
+    """c[i] = alpha * op(a[i]) * op(b[i]) + beta * c[i], one Dot per matrix in a serial loop, which
+    is how CpuTensor.BatchMatrixMultiplication does it (Prod/CPU/CpuTensor.cs:3004-3025)."""
+    nb = a_3D.shape[0]
+    assert b_3D.shape[0] == nb and c_3D.shape[0] == nb
+    out = np.empty(c_3D.shape, dtype=np.float64) if f64 else c_3D
+    for i in range(nb):
+        if f64:
+            out[i] = dot_f64(a_3D[i].ravel(), a_3D.shape[1], a_3D.shape[2], transposeA, b_3D[i].ravel(),
+                             b_3D.shape[1], b_3D.shape[2], transposeB, c_3D[i].ravel(), alpha, beta)
+        else:
+            dot_mkl(a_3D[i].ravel(), a_3D.shape[1], a_3D.shape[2], transposeA, b_3D[i].ravel(), b_3D.shape[1],
+                    b_3D.shape[2], transposeB, c_3D[i].reshape(-1), alpha, beta)
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# Dense companions
+# --------------------------------------------------------------------------------------------
+def broadcast_add_vector_to_output(bias, y):
+    """y[n, col] += bias[col], fp32 (Prod/CPU/CpuTensor.cs:1468-1487).  In place."""
+    y2 = y.reshape(y.shape[0], -1)
+    y2 += np.asarray(bias, dtype=np.float32).reshape(1, -1)
+    return y
+
+
+def compute_bias_gradient_from_dy(dy):
+    """db[col] = sum over rows of dy, accumulated row after row in fp32 exactly as
+    CpuTensor.ComputeSumByColumn does (Prod/CPU/CpuTensor.cs:3343-3362)."""
+    dy2 = np.asarray(dy, dtype=np.float32).reshape(dy.shape[0], -1)
+    acc = np.zeros(dy2.shape[1], dtype=np.float32)
+    for r in range(dy2.shape[0]):
+        acc += dy2[r]
+    return acc
+
+
+def update_adding_alpha_x(y, alpha, x):
+    """y += alpha * x via saxpy (Prod/CPU/CpuTensor.cs:1032-1038).  In place."""
+    y += np.float32(alpha) * np.asarray(x, dtype=np.float32)
+    return y
+
+
+def activation_forward(act, x):
+    """Element-wise activations with the precision SharpNet's CPU code uses
+    (Prod/CPU/CpuTensorActivationFunctions.cs): Swish and Sigmoid go through double
+    (:152-156, Prod/Utils.cs:888-891), Tanh is MathF.Tanh (:184-189), Relu is max(0, x) (:198-201)."""
+    x = np.asarray(x, dtype=np.float32)
+    if act == ACT_RELU:
+        return np.maximum(x, np.float32(0))
+    if act == ACT_SWISH:
+        xd = x.astype(np.float64)
+        return (xd / (1.0 + np.exp(-xd))).astype(np.float32)
+    if act == ACT_SIGMOID:
+        xd = x.astype(np.float64)
+        return (1.0 / (1.0 + np.exp(-xd))).astype(np.float32)
+    if act == ACT_TANH:
+        return np.tanh(x).astype(np.float32)
+    if act == ACT_IDENTITY:
+        return x.copy()
+    raise ValueError(f"activation {act} is not on the path")
+
+
+def activation_backward(act, dy, x, y):
+    """dx from dy, the activation input x and output y, all in fp32
+    (Prod/CPU/CpuTensorActivationFunctions.cs:158-167 Swish, :190-194 Tanh, :202-206 Relu,
+    :240-244 Sigmoid)."""
+    dy = np.asarray(dy, dtype=np.float32)
+    one = np.float32(1)
+    if act == ACT_RELU:
+        return np.where(y > 0, dy, np.float32(0)).astype(np.float32)
+    if act == ACT_SWISH:
+        x = np.asarray(x, dtype=np.float32)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            s = np.where(np.abs(x) < np.float32(0.0001), np.float32(0.5), y / x).astype(np.float32)
+        return (dy * (s + x * s * (one - s))).astype(np.float32)
+    if act == ACT_TANH:
+        return (dy * (one - y * y)).astype(np.float32)
+    if act == ACT_SIGMOID:
+        return (dy * y * (one - y)).astype(np.float32)
+    if act == ACT_IDENTITY:
+        return dy.copy()
+    raise ValueError(f"activation {act} is not on the path")
+
+
+# --------------------------------------------------------------------------------------------
+# Dense layer
+# --------------------------------------------------------------------------------------------
+def dense_forward(x, W, bias, act=ACT_IDENTITY, w_layout=W_OUT_IN, f64=False):
+    """Returns (z, y): z = x * op(W) + bias, y = act(z).
+
+    OUT_IN follows Linear.DenseForwardPropagation (Prod/Layers/Linear.cs:125-132: Dot(x, false,
+    W, true, 1, 0) then BroadcastAddVectorToOutput) and ActivationLayer.ForwardPropagation
+    (Prod/Layers/ActivationLayer.cs:32-38).  IN_OUT is the same product with W stored
+    [in, out] (the layout of the Keras goldens, Tests/NonReg/TestNetworkPropagation.cs:34,95)."""
+    M, K = x.shape
+    N = W.shape[0] if w_layout == W_OUT_IN else W.shape[1]
+    tB = w_layout == W_OUT_IN
+    if f64:
+        z = dot_f64(x.ravel(), M, K, False, W.ravel(), W.shape[0], W.shape[1], tB, np.zeros(M * N), 1.0, 0.0)
+        if bias is not None:
+            z = z + np.asarray(bias, dtype=np.float64).reshape(1, -1)
+        return z, _act_f64(act, z)
+    z = np.zeros((M, N), dtype=np.float32)
+    dot_mkl(x.ravel(), M, K, False, W.ravel(), W.shape[0], W.shape[1], tB, z.reshape(-1), 1.0, 0.0)
+    if bias is not None:
+        broadcast_add_vector_to_output(bias, z)
+    return z, activation_forward(act, z)
+
+
+def dense_backward(x, W, dy, act=ACT_IDENTITY, y=None, z=None, multiplier=1.0, w_layout=W_OUT_IN, need_dx=True,
+                   f64=False):
+    """Returns (dz, dW, db, dx).
+
+    dz = ActivationBackward(dy, z, y) (Prod/Layers/ActivationLayer.cs:39-69), then
+    Linear.DenseBackwardPropagation (Prod/Layers/Linear.cs:142-191): dW = multiplier * dz^T * x
+    (:158), db = column sums of dz (:160-165), dx = dz * W (:190), skipped when the previous layer
+    is the input (:184-187).  IN_OUT stores dW as [in, out] = x^T * dz and uses dx = dz * W^T."""
+    M, K = x.shape
+    N = dy.shape[1]
+    if f64:
+        dz = _act_bwd_f64(act, dy, z, y)
+        xd, Wd = x.astype(np.float64), W.astype(np.float64)
+        if w_layout == W_OUT_IN:
+            dW = multiplier * (dz.T @ xd)
+            dx = dz @ Wd if need_dx else None
+        else:
+            dW = multiplier * (xd.T @ dz)
+            dx = dz @ Wd.T if need_dx else None
+        return dz, dW, dz.sum(axis=0), dx
+    dz = activation_backward(act, dy, z, y)
+    if w_layout == W_OUT_IN:
+        dW = np.zeros((N, K), dtype=np.float32)
+        dot_mkl(dz.ravel(), M, N, True, x.ravel(), M, K, False, dW.reshape(-1), multiplier, 0.0)
+    else:
+        dW = np.zeros((K, N), dtype=np.float32)
+        dot_mkl(x.ravel(), M, K, True, dz.ravel(), M, N, False, dW.reshape(-1), multiplier, 0.0)
+    db = compute_bias_gradient_from_dy(dz)
+    dx = None
+    if need_dx:
+        dx = np.zeros((M, K), dtype=np.float32)
+        if w_layout == W_OUT_IN:
+            dot_mkl(dz.ravel(), M, N, False, W.ravel(), N, K, False, dx.reshape(-1), 1.0, 0.0)
+        else:
+            dot_mkl(dz.ravel(), M, N, False, W.ravel(), K, N, True, dx.reshape(-1), 1.0, 0.0)
+    return dz, dW, db, dx
+
+
+def _act_f64(act, z):
+    if act == ACT_RELU:
+        return np.maximum(z, 0.0)
+    if act == ACT_SWISH:
+        return z / (1.0 + np.exp(-z))
+    if act == ACT_SIGMOID:
+        return 1.0 / (1.0 + np.exp(-z))
+    if act == ACT_TANH:
+        return np.tanh(z)
+    return z.copy()
+
+
+def _act_bwd_f64(act, dy, z, y):
+    dy = np.asarray(dy, dtype=np.float64)
+    if act == ACT_RELU:
+        return np.where(np.asarray(y) > 0, dy, 0.0)
+    if act == ACT_SWISH:
+        zd = np.asarray(z, dtype=np.float64)
+        s = 1.0 / (1.0 + np.exp(-zd))
+        return dy * (s + zd * s * (1.0 - s))
+    if act == ACT_TANH:
+        yd = np.asarray(y, dtype=np.float64)
+        return dy * (1.0 - yd * yd)
+    if act == ACT_SIGMOID:
+        yd = np.asarray(y, dtype=np.float64)
+        return dy * yd * (1.0 - yd)
+    return dy.copy()
+
+
+# --------------------------------------------------------------------------------------------
+# Losses used by the reference's golden network tests (checker side only)
+# --------------------------------------------------------------------------------------------
+def binary_crossentropy(y_true, y_pred):
+    """Mean over rows of the mean over columns of -(t*log(p) + (1-t)*log(1-p))
+    (BinaryCrossentropyLossBuffer, Prod/GPU/Kernels/SinglePrecision.cu:773-791)."""
+    p = np.asarray(y_pred, dtype=np.float64)
+    t = np.asarray(y_true, dtype=np.float64)
+    return float(np.mean(-(t * np.log(p) + (1.0 - t) * np.log(1.0 - p))))
+
+
+def mse(y_true, y_pred):
+    """Mean squared error over all elements (MseLossBuffer, SinglePrecision.cu:991-1006)."""
+    d = np.asarray(y_pred, dtype=np.float64) - np.asarray(y_true, dtype=np.float64)
+    return float(np.mean(d * d))
+
+
+# --------------------------------------------------------------------------------------------
+# Deterministic inputs
+# --------------------------------------------------------------------------------------------
+def numpy_array_for_tests(*shape):
+    """data[i] = (float)(2*(i+1)/count * ((i % 2) - 0.5))
+    (Tests/NonReg/TestNetworkPropagation.cs:167-176)."""
+    count = int(np.prod(shape))
+    i = np.arange(count, dtype=np.float64)
+    return ((2.0 * (i + 1)) / count * ((i % 2) - 0.5)).astype(np.float32).reshape(shape)
+
+
+def y_numpy_array_for_tests(rows, cols):
+    """One-hot rows with the 1 in column row % cols (Tests/NonReg/TestNetworkPropagation.cs:178-186)."""
+    out = np.zeros((rows, cols), dtype=np.float32)
+    for r in range(rows):
+        out[r, r % cols] = 1
+    return out
+
+
+def uniform(shape, lo, hi, seed):
+    """U[lo, hi) float32 from a seeded generator (stands in for Utils.UniformDistribution,
+    Prod/Utils.cs:411-417; .NET's Random stream itself is not reproducible without .NET)."""
+    return np.random.default_rng(seed).uniform(lo, hi, size=shape).astype(np.float32)
+
+
+def normal(shape, mean, std, seed):
+    """N(mean, std) float32 (stands in for Utils.NormalDistribution, Prod/Utils.cs:425-431)."""
+    return np.random.default_rng(seed).normal(mean, std, size=shape).astype(np.float32)
+
+
+def glorot_uniform(shape, seed):
+    """U[-limit, limit), limit = sqrt(6 / (Shape[0] + MultDim0)) (Prod/Data/Tensor.cs:1480-1486)."""
+    fan = shape[0] + int(np.prod(shape[1:]))
+    limit = math.sqrt(6.0 / fan)
+    return uniform(shape, -limit, limit, seed)
+
+
+def scaled_error(got, ref, K, a_max, b_max):
+    """max |got - ref| / (sqrt(K) * a_max * b_max): the error measure the accuracy gates use
+    (<= 1e-5 in 3xTF32 mode, <= 2e-3 in TF32 mode)."""
+    d = np.max(np.abs(np.asarray(got, dtype=np.float64) - np.asarray(ref, dtype=np.float64)))
+    return float(d / (math.sqrt(max(K, 1)) * a_max * b_max))

@@ -1,0 +1,90 @@
+"""ctypes binding of libsharpnet_b200.so: one Python function per entry point of
+include/sharpnet_b200.h, with the same argument order.  This is the Python twin of the C#
+P/Invoke class a SharpNet maintainer adds (one ``[DllImport("sharpnet_b200")]`` per function).
+
+There is no fallback: if the library has not been built, importing it raises.
+"""
+import ctypes
+import os
+
+from .build import LIB_PATH
+
+STATUS_NAMES = {
+    0: "SUCCESS", 1: "NOT_INITIALIZED", 3: "ALLOC_FAILED", 7: "INVALID_VALUE", 8: "ARCH_MISMATCH",
+    13: "EXECUTION_FAILED", 14: "INTERNAL_ERROR", 15: "NOT_SUPPORTED",
+}
+MATH_3XTF32, MATH_TF32, MATH_FP32_SIMT = 0, 1, 2
+ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
+W_OUT_IN, W_IN_OUT = 0, 1
+TUNE_FORCE_PATH, TUNE_FORCE_BN, TUNE_REWRITE_HI = 0, 1, 2
+
+_c = ctypes
+_H = _c.c_void_p
+_F = _c.c_float
+_I = _c.c_int
+_L = _c.c_longlong
+_P = _c.c_void_p
+
+# name -> (restype, argtypes); every symbol include/sharpnet_b200.h declares.
+SIGNATURES = {
+    "snb200_create": (_I, [_c.POINTER(_H), _I]),
+    "snb200_destroy": (_I, [_H]),
+    "snb200_set_stream": (_I, [_H, _P]),
+    "snb200_set_math_mode": (_I, [_H, _I]),
+    "snb200_get_math_mode": (_I, [_H, _c.POINTER(_I)]),
+    "snb200_set_tuning": (_I, [_H, _I, _I]),
+    "snb200_last_error_string": (_c.c_char_p, [_H]),
+    "snb200_check_device_status": (_I, [_H]),
+    "snb200_get_launch_count": (_I, [_H, _c.POINTER(_L)]),
+    "snb200_get_last_kernel": (_I, [_H, _c.c_char_p, _I]),
+    "snb200_get_version": (_I, []),
+    "snb200_gemm": (_I, [_H, _I, _I, _I, _I, _I, _I, _F, _P, _P, _F, _P]),
+    "snb200_batched_gemm": (_I, [_H, _I, _I, _I, _I, _L, _I, _I, _L, _L, _I, _F, _P, _P, _F, _P]),
+    "snb200_dense_fwd": (_I, [_H, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P]),
+    "snb200_dense_bwd": (_I, [_H, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P]),
+    "snb200_bias_add": (_I, [_H, _I, _I, _P, _P]),
+    "snb200_bias_grad": (_I, [_H, _I, _I, _P, _P]),
+    "snb200_activation_fwd": (_I, [_H, _I, _L, _P, _P]),
+    "snb200_activation_bwd": (_I, [_H, _I, _L, _P, _P, _P, _P]),
+    "snb200_axpy": (_I, [_H, _L, _F, _P, _P]),
+    "snb200_comm_get_unique_id": (_I, [_P]),
+    "snb200_comm_init_rank": (_I, [_H, _I, _I, _P]),
+    "snb200_comm_init_all": (_I, [_c.POINTER(_H), _I]),
+    "snb200_allreduce_sum": (_I, [_H, _P, _L]),
+    "snb200_comm_destroy": (_I, [_H]),
+}
+
+_lib = None
+
+
+def load():
+    """Loads the shared library (once) and declares the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m sharpnet_b200.build` "
+            "(there is no CPU or PyTorch fallback for this library)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class SharpNetB200Error(Exception):
+    """Raised when an entry point returns a non-zero status, like GPUWrapper.CheckStatus
+    (Prod/GPU/GPUWrapper.cs:662-668) throws on a cuBLAS status."""
+
+    def __init__(self, status, message):
+        self.status = status
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+
+
+def check(handle, status):
+    if status != 0:
+        msg = load().snb200_last_error_string(handle)
+        raise SharpNetB200Error(status, msg.decode() if msg else "")

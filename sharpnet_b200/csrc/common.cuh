@@ -1,0 +1,67 @@
+// Types shared by the SIMT and tcgen05 GEMM kernels: the problem description and the fused
+// epilogue  v = alpha*acc + beta*C + bias ; z = v ; C = act(v).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace snb {
+
+// Values of cudnnActivationMode_t (Prod/GPU/CudnnWrapper.cs:267-281).
+enum Act : int { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_IDENTITY = 5, ACT_SWISH = 6 };
+
+// One (possibly strided-batched) GEMM  C[b] = epi(alpha * op(A[b]) * op(B[b]) + beta * C[b]).
+// All matrices are dense row-major fp32.
+struct GemmProblem {
+  int M, N, K;            // logical dims of op(A) [M x K], op(B) [K x N], C [M x N]
+  int transA, transB;     // A stored [K x M] when transA, B stored [N x K] when transB
+  int lda, ldb, ldc;      // row pitch (elements) of the stored matrices
+  int batch;
+  long long strideA, strideB, strideC;  // elements between consecutive matrices
+  const float* A;
+  const float* B;
+  float* C;
+  float alpha, beta;
+  const float* bias;      // [N] or nullptr: added to every row
+  float* Z;               // optional copy of the value before the activation (pitch ldc, stride strideC)
+  int act;                // Act
+};
+
+__device__ __forceinline__ float act_forward(int act, float v) {
+  // Formulas of Prod/CPU/CpuTensorActivationFunctions.cs:152-244 and Prod/Utils.cs:888-891.
+  switch (act) {
+    case ACT_RELU: return fmaxf(v, 0.0f);
+    case ACT_SWISH: return v / (1.0f + expf(-v));
+    case ACT_TANH: return tanhf(v);
+    case ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+    default: return v;
+  }
+}
+
+// Gradient with respect to the pre-activation, from the upstream gradient dy, the activation
+// output y and (SWISH only) the pre-activation x.
+__device__ __forceinline__ float act_backward(int act, float dy, float x, float y) {
+  switch (act) {
+    case ACT_RELU: return y > 0.0f ? dy : 0.0f;                       // CpuTensorActivationFunctions.cs:202-206
+    case ACT_SWISH: {                                                  // :158-167
+      float s = (fabsf(x) < 0.0001f) ? 0.5f : y / x;
+      return dy * (s + x * s * (1.0f - s));
+    }
+    case ACT_TANH: return dy * (1.0f - y * y);                        // :190-194
+    case ACT_SIGMOID: return dy * y * (1.0f - y);                     // :240-244
+    default: return dy;
+  }
+}
+
+struct Epilogue {
+  float alpha, beta;
+  const float* bias;
+  float* Z;
+  int act;
+  __device__ __forceinline__ float apply(float acc, float c_old, float bias_v) const {
+    float v = alpha * acc;
+    if (beta != 0.0f) v = fmaf(beta, c_old, v);
+    return v + bias_v;
+  }
+};
+
+}  // namespace snb

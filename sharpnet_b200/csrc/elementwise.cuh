@@ -1,0 +1,123 @@
+// Bandwidth-bound companions of the Dense layer: bias broadcast, column sums (bias gradient),
+// activations and their gradients, axpy, and the fused "activation gradient + bias gradient"
+// pass of the Dense backward.  All are grid-stride / slab kernels sized from the SM count.
+#pragma once
+#include "common.cuh"
+
+namespace snb {
+
+// y[m, n] += bias[n]                               (Prod/CPU/CpuTensor.cs:1468-1487)
+__global__ void bias_add_kernel(long long total, int N, const float* __restrict__ bias, float* __restrict__ y) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride)
+    y[i] += __ldg(bias + (i % N));
+}
+__global__ void bias_add_vec4_kernel(long long total4, int N4, const float4* __restrict__ bias,
+                                     float4* __restrict__ y) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total4; i += stride) {
+    float4 v = y[i];
+    const float4 b = __ldg(bias + (i % N4));
+    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    y[i] = v;
+  }
+}
+
+__global__ void activation_fwd_kernel(int act, long long n, const float* __restrict__ x, float* __restrict__ y) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
+    y[i] = act_forward(act, x[i]);
+}
+__global__ void activation_bwd_kernel(int act, long long n, const float* __restrict__ dy, const float* __restrict__ x,
+                                      const float* __restrict__ y, float* __restrict__ dx) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+    const float xv = (act == ACT_SWISH) ? x[i] : 0.0f;
+    const float yv = (act == ACT_IDENTITY) ? 0.0f : y[i];
+    dx[i] = act_backward(act, dy[i], xv, yv);
+  }
+}
+// y += alpha * x                                    (Prod/CPU/CpuTensor.cs:1032-1038)
+__global__ void axpy_kernel(long long n, float alpha, const float* __restrict__ x, float* __restrict__ y) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
+    y[i] = fmaf(alpha, x[i], y[i]);
+}
+
+// Column sums of g[M x N] over a slab of rows, optionally fused with the activation gradient:
+//   g = dy                        (FUSE_ACT = false:  db = sum_m dy,  CpuTensor.cs:3343-3362)
+//   g = act'(z, y) * dy -> dz     (FUSE_ACT = true:   ActivationBackward + bias gradient in one pass)
+// Block = 256 threads = 8 warps; a warp covers 32*VEC consecutive columns, the 8 warps stride over
+// the rows of the slab.  The slab's sums go to partial[slab, N] (or straight to db when there is
+// one slab); colsum_finish_kernel adds the slabs in a fixed order, so results are deterministic.
+template <int VEC, bool FUSE_ACT>
+__global__ void __launch_bounds__(256)
+colsum_slab_kernel(int M, int N, int rows_per_slab, int act, const float* __restrict__ dy,
+                   const float* __restrict__ y, const float* __restrict__ z, float* __restrict__ dz,
+                   float* __restrict__ out) {
+  __shared__ float red[8][32 * VEC];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = (blockIdx.x * 32 + lane) * VEC;
+  const int r0 = blockIdx.y * rows_per_slab;
+  const int r1 = min(M, r0 + rows_per_slab);
+  float s[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) s[v] = 0.0f;
+  if (col < N) {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      const size_t off = static_cast<size_t>(r) * N + col;
+      float g[VEC], yv[VEC], zv[VEC];
+      if (VEC == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(dy + off);
+        g[0] = t.x; g[1] = t.y; g[2] = t.z; g[3] = t.w;
+      } else {
+        g[0] = dy[off];
+      }
+      if (FUSE_ACT) {
+        if (VEC == 4) {
+          const float4 t = *reinterpret_cast<const float4*>(y + off);
+          yv[0] = t.x; yv[1] = t.y; yv[2] = t.z; yv[3] = t.w;
+          if (act == ACT_SWISH) {
+            const float4 u = *reinterpret_cast<const float4*>(z + off);
+            zv[0] = u.x; zv[1] = u.y; zv[2] = u.z; zv[3] = u.w;
+          }
+        } else {
+          yv[0] = y[off];
+          if (act == ACT_SWISH) zv[0] = z[off];
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) g[v] = act_backward(act, g[v], act == ACT_SWISH ? zv[v] : 0.0f, yv[v]);
+        if (VEC == 4) {
+          *reinterpret_cast<float4*>(dz + off) = make_float4(g[0], g[1], g[2], g[3]);
+        } else {
+          dz[off] = g[0];
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) s[v] += g[v];
+    }
+  }
+  if (out == nullptr) return;   // caller only wanted dz
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) red[warp][lane * VEC + v] = s[v];
+  __syncthreads();
+  if (warp == 0 && col < N) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float t = 0.0f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += red[w][lane * VEC + v];
+      out[static_cast<size_t>(blockIdx.y) * N + col + v] = t;
+    }
+  }
+}
+
+__global__ void colsum_finish_kernel(int N, int slabs, const float* __restrict__ partial, float* __restrict__ db) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= N) return;
+  float t = 0.0f;
+  for (int s = 0; s < slabs; ++s) t += partial[static_cast<size_t>(s) * N + col];
+  db[col] = t;
+}
+
+}  // namespace snb

@@ -1,0 +1,343 @@
+// tcgen05 / TMEM GEMM for sm_100a, fp32 in and out.
+//
+//   C[b] = epi(alpha * op(A[b]) * op(B[b]) + beta * C[b])
+//
+// One persistent CTA per SM walks over 128 x BN output tiles.  Warp roles:
+//   warp 0        TMA producer: fp32 tiles of A and B -> shared memory ring (swizzled)
+//   warp 1        owns TMEM; one lane issues tcgen05.mma (kind::tf32) into a TMEM accumulator
+//   warps 2..5    epilogue: TMEM -> registers -> alpha/beta/bias/activation -> global memory
+//   warps 6..13   (3xTF32 only) split every fp32 operand tile into hi + lo TF32 planes
+// The accumulator is double buffered in TMEM, so the epilogue of tile i overlaps the main loop
+// of tile i+1.
+//
+// Transposes never move data: an operand whose contraction dimension is contiguous in memory is
+// loaded as a K-major tile, the other kind as an MN-major tile, and the tcgen05 descriptors name
+// the layout.  Both are fetched by plain (non-multicast) TMA.
+//
+// 3xTF32: a = a_hi + a_lo with a_hi = tf32(a), a_lo = tf32(a - a_hi); the product is
+// a_lo*b_hi + a_hi*b_lo + a_hi*b_hi accumulated in fp32, which recovers fp32-level accuracy
+// from TF32 tensor cores.  In TF32 mode the raw fp32 tiles feed the tensor core directly.
+#pragma once
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace snb {
+
+constexpr int kUmmaBM = 128;
+constexpr int kUmmaK = 8;  // K extent of one kind::tf32 instruction
+
+template <int BN_, int BK_, bool SPLIT_>
+struct UmmaTile {
+  static constexpr int BM = kUmmaBM;
+  static constexpr int BN = BN_;
+  static constexpr int BK = BK_;
+  static constexpr bool SPLIT = SPLIT_;
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;               // what TMA delivers per stage
+  static constexpr int STAGE_BYTES = RAW_BYTES * (SPLIT ? 2 : 1);   // + the lo planes
+  static constexpr int SMEM_BUDGET = 196 * 1024;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;    // + slack to align the ring to 1 KB
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; power of two
+  static constexpr int N_SPLIT_THREADS = SPLIT ? 256 : 0;
+  static constexpr int THREADS = 192 + N_SPLIT_THREADS;
+  // K-major tiles: one row = BK fp32.  128-byte swizzle for BK = 32, 64-byte for BK = 16.
+  static constexpr int KMAJ_ROW_BYTES = BK * 4;
+  static constexpr int KMAJ_SBO = 8 * KMAJ_ROW_BYTES;
+  static constexpr int KMAJ_LAYOUT = (BK == 32) ? 2 : 4;
+  // MN-major tiles: chunks of 32 fp32 (128 B) along M/N, BK rows each, 128-byte swizzle.
+  static constexpr int MNMAJ_CHUNK_BYTES = BK * 128;
+  static_assert(BK == 32 || BK == 16, "BK must be 16 or 32");
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
+  static_assert(STAGES >= 2, "need at least two stages");
+};
+
+struct UmmaParams {
+  int M, N, K, batch;
+  int tiles_m, tiles_n, k_blocks;
+  int a_mn, b_mn;  // 1 = operand tile is MN-major (A stored [K x M] / B stored [K x N])
+  int ldc;
+  long long strideC;
+  float* C;
+  float* Z;
+  const float* bias;
+  float alpha, beta;
+  int act;
+  int rewrite_hi;   // 3xTF32: store the rounded hi plane back over the raw tile
+  int vec_ok;       // C (and Z) rows are 16-byte aligned
+  int* error_word;  // set to 1 when a pipeline wait timed out
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
+  // Walk tiles in bands of 8 tile-rows so that CTAs running at the same time share A and B
+  // tiles through L2.
+  const int per_batch = tiles_m * tiles_n;
+  b = t / per_batch;
+  int r = t - b * per_batch;
+  const int band = 8 * tiles_n;
+  const int g = r / band;
+  const int first_m = g * 8;
+  const int rows = min(tiles_m - first_m, 8);
+  r -= g * band;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+__device__ __forceinline__ uint32_t to_tf32_rna(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+
+template <class T>
+__global__ void __launch_bounds__(T::THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const UmmaParams p) {
+  constexpr int BM = T::BM, BN = T::BN, BK = T::BK, STAGES = T::STAGES;
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ uint64_t full_bar[STAGES];    // TMA bytes landed
+  __shared__ uint64_t split_bar[STAGES];   // hi/lo planes written (3xTF32)
+  __shared__ uint64_t empty_bar[STAGES];   // MMAs that read the stage retired
+  __shared__ uint64_t acc_full_bar[2];     // accumulator complete in TMEM
+  __shared__ uint64_t acc_empty_bar[2];    // accumulator drained by the epilogue
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint8_t* ring = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&split_bar[s], T::SPLIT ? T::N_SPLIT_THREADS : 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full_bar[b], 1);
+      mbar_init(&acc_empty_bar[b], 128);
+    }
+    abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_holder, T::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_holder;
+  volatile int* abortp = &abort_flag;
+
+  const int total_tiles = p.batch * p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int b, tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) { ok = false; break; }
+          uint8_t* a_dst = ring + s * T::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + T::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], T::RAW_BYTES);
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_3d(a_dst, &tmA, &full_bar[s], k0, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 32; ++j)
+              tma_load_3d(a_dst + j * T::MNMAJ_CHUNK_BYTES, &tmA, &full_bar[s], m0 + 32 * j, k0, b);
+          }
+          if (!p.b_mn) {
+            tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j)
+              tma_load_3d(b_dst + j * T::MNMAJ_CHUNK_BYTES, &tmB, &full_bar[s], n0 + 32 * j, k0, b);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_tf32(BM, BN, p.a_mn, p.b_mn);
+      const uint32_t a_step = p.a_mn ? 1024u : 32u;   // bytes per K = 8 slice
+      const uint32_t b_step = p.b_mn ? 1024u : 32u;
+      const uint32_t a_lbo = p.a_mn ? T::MNMAJ_CHUNK_BYTES : 16u;
+      const uint32_t b_lbo = p.b_mn ? T::MNMAJ_CHUNK_BYTES : 16u;
+      const uint32_t a_sbo = p.a_mn ? 1024u : T::KMAJ_SBO;
+      const uint32_t b_sbo = p.b_mn ? 1024u : T::KMAJ_SBO;
+      const uint32_t a_lay = p.a_mn ? 2u : T::KMAJ_LAYOUT;
+      const uint32_t b_lay = p.b_mn ? 2u : T::KMAJ_LAYOUT;
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t acc_ph = 0;  // bit b = phase of accumulator b
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        if (!mbar_wait(&acc_empty_bar[buf], ((acc_ph >> buf) & 1u) ^ 1u, abortp)) { ok = false; break; }
+        acc_ph ^= 1u << buf;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          uint64_t* ready = T::SPLIT ? &split_bar[s] : &full_bar[s];
+          if (!mbar_wait(ready, ph, abortp)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_hi = smem_u32(ring + s * T::STAGE_BYTES);
+          const uint32_t b_hi = a_hi + T::A_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < BK / kUmmaK; ++ks) {
+            const uint64_t da_hi = make_smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lay);
+            const uint64_t db_hi = make_smem_desc(b_hi + ks * b_step, b_lbo, b_sbo, b_lay);
+            const uint32_t first = (kb == 0 && ks == 0) ? 0u : 1u;
+            if (T::SPLIT) {
+              const uint64_t da_lo = make_smem_desc(a_hi + T::RAW_BYTES + ks * a_step, a_lbo, a_sbo, a_lay);
+              const uint64_t db_lo = make_smem_desc(b_hi + T::RAW_BYTES + ks * b_step, b_lbo, b_sbo, b_lay);
+              umma_tf32_ss(d_tmem, da_lo, db_hi, idesc, first);
+              umma_tf32_ss(d_tmem, da_hi, db_lo, idesc, 1u);
+              umma_tf32_ss(d_tmem, da_hi, db_hi, idesc, 1u);
+            } else {
+              umma_tf32_ss(d_tmem, da_hi, db_hi, idesc, first);
+            }
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&acc_full_bar[buf]);
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t acc_ph = 0;  // bit b = phase of accumulator b
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      int b, tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
+      const int buf = it & 1;
+      if (!mbar_wait(&acc_full_bar[buf], (acc_ph >> buf) & 1u, abortp)) { ok = false; break; }
+      acc_ph ^= 1u << buf;
+      tc_fence_after_sync();
+      const int row = tm * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      const size_t row_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
+      float* crow = p.C + row_off;
+      float* zrow = p.Z ? p.Z + row_off : nullptr;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        float v[32];
+        tmem_ld_32x32(t_addr + c * 32, v);
+        tmem_ld_wait();
+        if (row < p.M) {
+          if (p.vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 o;
+              o.x = p.alpha * v[4 * j + 0];
+              o.y = p.alpha * v[4 * j + 1];
+              o.z = p.alpha * v[4 * j + 2];
+              o.w = p.alpha * v[4 * j + 3];
+              if (p.beta != 0.0f) {
+                const float4 cin = *reinterpret_cast<const float4*>(crow + col0 + 4 * j);
+                o.x = fmaf(p.beta, cin.x, o.x);
+                o.y = fmaf(p.beta, cin.y, o.y);
+                o.z = fmaf(p.beta, cin.z, o.z);
+                o.w = fmaf(p.beta, cin.w, o.w);
+              }
+              if (p.bias) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + 4 * j));
+                o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+              }
+              if (zrow) *reinterpret_cast<float4*>(zrow + col0 + 4 * j) = o;
+              if (p.act != ACT_IDENTITY) {
+                o.x = act_forward(p.act, o.x);
+                o.y = act_forward(p.act, o.y);
+                o.z = act_forward(p.act, o.z);
+                o.w = act_forward(p.act, o.w);
+              }
+              *reinterpret_cast<float4*>(crow + col0 + 4 * j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col < p.N) {
+                float o = p.alpha * v[j];
+                if (p.beta != 0.0f) o = fmaf(p.beta, crow[col], o);
+                if (p.bias) o += __ldg(p.bias + col);
+                if (zrow) zrow[col] = o;
+                crow[col] = act_forward(p.act, o);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty_bar[buf]);
+    }
+  } else if (T::SPLIT) {
+    // ------------------------------------------------------------------ hi / lo split
+    const int tid = threadIdx.x - 192;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait(&full_bar[s], ph, abortp)) { ok = false; break; }
+        uint8_t* raw = ring + s * T::STAGE_BYTES;
+#pragma unroll
+        for (int i = tid; i < T::RAW_BYTES / 16; i += T::N_SPLIT_THREADS) {
+          float4 x = *reinterpret_cast<const float4*>(raw + i * 16);
+          uint4 hi, lo;
+          if (p.rewrite_hi) {
+            hi.x = to_tf32_rna(x.x); hi.y = to_tf32_rna(x.y); hi.z = to_tf32_rna(x.z); hi.w = to_tf32_rna(x.w);
+          } else {
+            // The tensor core reads only the top 19 bits of each word: the raw tile is the hi plane.
+            hi.x = __float_as_uint(x.x) & 0xffffe000u; hi.y = __float_as_uint(x.y) & 0xffffe000u;
+            hi.z = __float_as_uint(x.z) & 0xffffe000u; hi.w = __float_as_uint(x.w) & 0xffffe000u;
+          }
+          lo.x = to_tf32_rna(x.x - __uint_as_float(hi.x));
+          lo.y = to_tf32_rna(x.y - __uint_as_float(hi.y));
+          lo.z = to_tf32_rna(x.z - __uint_as_float(hi.z));
+          lo.w = to_tf32_rna(x.w - __uint_as_float(hi.w));
+          if (p.rewrite_hi) *reinterpret_cast<uint4*>(raw + i * 16) = hi;
+          *reinterpret_cast<uint4*>(raw + T::RAW_BYTES + i * 16) = lo;
+        }
+        fence_proxy_async_smem();   // make the generic-proxy stores visible to tcgen05.mma
+        mbar_arrive(&split_bar[s]);
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && abort_flag) atomicExch(p.error_word, 1);
+}
+
+}  // namespace snb

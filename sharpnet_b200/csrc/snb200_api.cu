@@ -1,0 +1,640 @@
+// Host side of libsharpnet_b200: handle, argument validation, kernel selection and launch.
+// Nothing in this file computes on the host; without a CUDA device every entry point fails.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../../include/sharpnet_b200.h"
+#include "elementwise.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_umma.cuh"
+
+using namespace snb;
+
+// ------------------------------------------------------------------------------------ handle
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_COUNT = 8 };
+
+struct snb200_context {
+  int device;
+  int sm_count;
+  cudaStream_t stream;
+  int math_mode;
+  int tune[TUNE_COUNT];
+  float* workspace;            // partial sums of the column reductions
+  size_t workspace_floats;
+  int* error_word;             // device word set by a kernel whose pipeline wait timed out
+  long long launches;
+  char last_kernel[64];
+  char last_error[256];
+  void* nccl_comm;
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode_tiled = nullptr;
+
+static int fail(snb200_handle_t h, int status, const char* fmt, ...) {
+  if (h) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(h->last_error, sizeof(h->last_error), fmt, ap);
+    va_end(ap);
+  }
+  return status;
+}
+static int cuda_fail(snb200_handle_t h, cudaError_t e, const char* what) {
+  return fail(h, SNB200_STATUS_EXECUTION_FAILED, "%s: %s", what, cudaGetErrorString(e));
+}
+#define SNB_CUDA(h, call)                                        \
+  do {                                                           \
+    cudaError_t e__ = (call);                                    \
+    if (e__ != cudaSuccess) return cuda_fail((h), e__, #call);   \
+  } while (0)
+
+static int enter(snb200_handle_t h) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  cudaError_t e = cudaSetDevice(h->device);
+  if (e != cudaSuccess) return cuda_fail(h, e, "cudaSetDevice");
+  return 0;
+}
+static void note_kernel(snb200_handle_t h, const char* name, int launches) {
+  snprintf(h->last_kernel, sizeof(h->last_kernel), "%s", name);
+  h->launches += launches;
+}
+static int check_launch(snb200_handle_t h, const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(h, e, what);
+  return 0;
+}
+
+extern "C" int snb200_get_version(void) { return 100; }
+
+extern "C" int snb200_create(snb200_handle_t* handle, int device_id) {
+  if (!handle) return SNB200_STATUS_INVALID_VALUE;
+  *handle = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) return SNB200_STATUS_NOT_INITIALIZED;
+  if (device_id < 0 || device_id >= n) return SNB200_STATUS_INVALID_VALUE;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device_id) != cudaSuccess) return SNB200_STATUS_NOT_INITIALIZED;
+  if (prop.major != 10) return SNB200_STATUS_ARCH_MISMATCH;  // kernels are built for sm_100a only
+  if (cudaSetDevice(device_id) != cudaSuccess) return SNB200_STATUS_NOT_INITIALIZED;
+  if (!g_encode_tiled) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
+        q != cudaDriverEntryPointSuccess)
+      return SNB200_STATUS_NOT_INITIALIZED;
+    g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  snb200_context* h = static_cast<snb200_context*>(calloc(1, sizeof(snb200_context)));
+  if (!h) return SNB200_STATUS_ALLOC_FAILED;
+  h->device = device_id;
+  h->sm_count = prop.multiProcessorCount;
+  h->stream = 0;
+  h->math_mode = SNB200_MATH_3XTF32;
+  h->tune[TUNE_REWRITE_HI] = 1;
+  const char* env = getenv("SNB200_MATH_MODE");
+  if (env && env[0] >= '0' && env[0] <= '2' && env[1] == 0) h->math_mode = env[0] - '0';
+  h->workspace_floats = 1u << 20;
+  if (cudaMalloc(&h->workspace, h->workspace_floats * sizeof(float)) != cudaSuccess ||
+      cudaMalloc(&h->error_word, sizeof(int)) != cudaSuccess ||
+      cudaMemset(h->error_word, 0, sizeof(int)) != cudaSuccess) {
+    cudaFree(h->workspace);
+    cudaFree(h->error_word);
+    free(h);
+    return SNB200_STATUS_ALLOC_FAILED;
+  }
+  *handle = h;
+  return 0;
+}
+
+extern "C" int snb200_destroy(snb200_handle_t h) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  cudaSetDevice(h->device);
+  if (h->nccl_comm) snb200_comm_destroy(h);
+  cudaFree(h->workspace);
+  cudaFree(h->error_word);
+  free(h);
+  return 0;
+}
+
+extern "C" int snb200_set_stream(snb200_handle_t h, void* s) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  h->stream = static_cast<cudaStream_t>(s);
+  return 0;
+}
+extern "C" int snb200_set_math_mode(snb200_handle_t h, int m) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  if (m < 0 || m > 2) return fail(h, SNB200_STATUS_INVALID_VALUE, "math mode %d is not one of 0, 1, 2", m);
+  h->math_mode = m;
+  return 0;
+}
+extern "C" int snb200_get_math_mode(snb200_handle_t h, int* m) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  if (!m) return SNB200_STATUS_INVALID_VALUE;
+  *m = h->math_mode;
+  return 0;
+}
+extern "C" int snb200_set_tuning(snb200_handle_t h, int key, int value) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  if (key < 0 || key >= TUNE_COUNT) return fail(h, SNB200_STATUS_INVALID_VALUE, "unknown tuning key %d", key);
+  h->tune[key] = value;
+  return 0;
+}
+extern "C" const char* snb200_last_error_string(snb200_handle_t h) { return h ? h->last_error : "null handle"; }
+extern "C" int snb200_get_launch_count(snb200_handle_t h, long long* c) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  if (!c) return SNB200_STATUS_INVALID_VALUE;
+  *c = h->launches;
+  return 0;
+}
+extern "C" int snb200_get_last_kernel(snb200_handle_t h, char* buf, int len) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  if (!buf || len <= 0) return SNB200_STATUS_INVALID_VALUE;
+  snprintf(buf, len, "%s", h->last_kernel);
+  return 0;
+}
+extern "C" int snb200_check_device_status(snb200_handle_t h) {
+  int st = enter(h);
+  if (st) return st;
+  SNB_CUDA(h, cudaStreamSynchronize(h->stream));
+  int w = 0;
+  SNB_CUDA(h, cudaMemcpy(&w, h->error_word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (w) {
+    cudaMemset(h->error_word, 0, sizeof(int));
+    return fail(h, SNB200_STATUS_EXECUTION_FAILED, "a tensor-core pipeline wait timed out on the device");
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------ GEMM
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static bool encode_3d(CUtensorMap* m, const float* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
+                      uint64_t pitch2, uint32_t b0, uint32_t b1, CUtensorMapSwizzle sw) {
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {pitch1 * sizeof(float), pitch2 * sizeof(float)};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// The TMA path needs 16-byte aligned bases and pitches that are multiples of 16 bytes.
+static bool tma_eligible(const GemmProblem& g) {
+  if (!aligned16(g.A) || !aligned16(g.B)) return false;
+  if ((g.lda & 3) || (g.ldb & 3)) return false;
+  if (g.batch > 1 && ((g.strideA & 3) || (g.strideB & 3))) return false;
+  if (g.K < 1) return false;
+  return true;
+}
+
+template <class T>
+static int launch_umma_t(snb200_handle_t h, const GemmProblem& g) {
+  static bool configured[64] = {};
+  CUtensorMap tmA, tmB;
+  const uint64_t a_rows = g.transA ? g.K : g.M, b_rows = g.transB ? g.N : g.K;
+  const uint64_t pitchA2 = g.batch > 1 ? static_cast<uint64_t>(g.strideA) : a_rows * g.lda;
+  const uint64_t pitchB2 = g.batch > 1 ? static_cast<uint64_t>(g.strideB) : b_rows * g.ldb;
+  const CUtensorMapSwizzle kmaj_sw = (T::BK == 32) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  bool ok;
+  if (!g.transA)  // stored [M x K]: K-major tile, box = BK x 128 rows
+    ok = encode_3d(&tmA, g.A, g.K, g.M, g.batch, g.lda, pitchA2, T::BK, T::BM, kmaj_sw);
+  else            // stored [K x M]: MN-major tile, box = 32 m x BK rows
+    ok = encode_3d(&tmA, g.A, g.M, g.K, g.batch, g.lda, pitchA2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (g.transB)   // stored [N x K]: K-major tile
+    ok = ok && encode_3d(&tmB, g.B, g.K, g.N, g.batch, g.ldb, pitchB2, T::BK, T::BN, kmaj_sw);
+  else            // stored [K x N]: MN-major tile
+    ok = ok && encode_3d(&tmB, g.B, g.N, g.K, g.batch, g.ldb, pitchB2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return fail(h, SNB200_STATUS_INTERNAL_ERROR, "cuTensorMapEncodeTiled rejected the operand layout");
+
+  UmmaParams p;
+  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.batch;
+  p.tiles_m = (g.M + T::BM - 1) / T::BM;
+  p.tiles_n = (g.N + T::BN - 1) / T::BN;
+  p.k_blocks = (g.K + T::BK - 1) / T::BK;
+  p.a_mn = g.transA ? 1 : 0;
+  p.b_mn = g.transB ? 0 : 1;
+  p.ldc = g.ldc; p.strideC = g.strideC;
+  p.C = g.C; p.Z = g.Z; p.bias = g.bias;
+  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act;
+  p.rewrite_hi = h->tune[TUNE_REWRITE_HI];
+  p.vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (g.batch == 1 || g.strideC % 4 == 0) &&
+             (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias));
+  p.error_word = h->error_word;
+
+  if (!configured[h->device]) {
+    SNB_CUDA(h, cudaFuncSetAttribute(umma_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    configured[h->device] = true;
+  }
+  const long long tiles = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
+  const int grid = static_cast<int>(tiles < h->sm_count ? tiles : h->sm_count);
+  umma_gemm_kernel<T><<<grid, T::THREADS, T::SMEM_BYTES, h->stream>>>(tmA, tmB, p);
+  return check_launch(h, "umma_gemm_kernel launch");
+}
+
+static int launch_umma(snb200_handle_t h, const GemmProblem& g, bool split, int bn) {
+  char name[64];
+  snprintf(name, sizeof(name), "umma_%s_128x%d", split ? "3xtf32" : "tf32", bn);
+  note_kernel(h, name, 1);
+  if (split) {
+    switch (bn) {
+      case 256: return launch_umma_t<UmmaTile<256, 16, true>>(h, g);
+      case 128: return launch_umma_t<UmmaTile<128, 16, true>>(h, g);
+      case 64: return launch_umma_t<UmmaTile<64, 16, true>>(h, g);
+      default: return launch_umma_t<UmmaTile<32, 16, true>>(h, g);
+    }
+  }
+  switch (bn) {
+    case 256: return launch_umma_t<UmmaTile<256, 32, false>>(h, g);
+    case 128: return launch_umma_t<UmmaTile<128, 32, false>>(h, g);
+    case 64: return launch_umma_t<UmmaTile<64, 32, false>>(h, g);
+    default: return launch_umma_t<UmmaTile<32, 32, false>>(h, g);
+  }
+}
+
+static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
+  SimtParams p;
+  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.batch;
+  p.sAm = g.transA ? 1 : g.lda;
+  p.sAk = g.transA ? g.lda : 1;
+  p.sBk = g.transB ? 1 : g.ldb;
+  p.sBn = g.transB ? g.ldb : 1;
+  p.strideA = g.strideA; p.strideB = g.strideB; p.strideC = g.strideC;
+  p.ldc = g.ldc;
+  p.A = g.A; p.B = g.B; p.C = g.C; p.Z = g.Z; p.bias = g.bias;
+  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act;
+  p.tiles_m = (g.M + kSimtBM - 1) / kSimtBM;
+  p.tiles_n = (g.N + kSimtBN - 1) / kSimtBN;
+  const long long blocks = static_cast<long long>(p.tiles_m) * p.tiles_n * g.batch;
+  if (blocks > 0x7fffffffLL) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "too many tiles for one launch");
+  note_kernel(h, "simt_fp32_64x64", 1);
+  simt_gemm_kernel<<<static_cast<unsigned>(blocks), kSimtThreads, 0, h->stream>>>(p);
+  return check_launch(h, "simt_gemm_kernel launch");
+}
+
+// Picks the tile width whose wave count wastes the fewest SM-cycles.
+static int choose_bn(const snb200_context* h, const GemmProblem& g) {
+  const int cand[4] = {256, 128, 64, 32};
+  int best = 256;
+  double best_cost = 1e300;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = cand[i];
+    const long long tiles = static_cast<long long>(g.batch) * ((g.M + 127) / 128) * ((g.N + bn - 1) / bn);
+    const long long waves = (tiles + h->sm_count - 1) / h->sm_count;
+    const double cost = static_cast<double>(waves) * ((bn < 64 ? 64 : bn) + 32);
+    if (cost < best_cost * 0.999) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+static int run_gemm(snb200_handle_t h, const GemmProblem& g) {
+  if (g.M == 0 || g.N == 0 || g.batch == 0) return 0;
+  const int force = h->tune[TUNE_FORCE_PATH];  // 0 auto, 1 tensor cores whenever eligible, 2 SIMT
+  bool use_umma = h->math_mode != SNB200_MATH_FP32_SIMT && force != 2 && tma_eligible(g);
+  if (use_umma && force != 1) {
+    // Tiny problems do not amortise a 128-row tensor-core tile.
+    const double macs = static_cast<double>(g.M) * g.N * g.K * g.batch;
+    if (macs < 64.0 * 64 * 64 || g.M < 16 || g.N < 8) use_umma = false;
+  }
+  if (!use_umma) return launch_simt(h, g);
+  int bn = h->tune[TUNE_FORCE_BN];
+  if (bn != 256 && bn != 128 && bn != 64 && bn != 32) bn = choose_bn(h, g);
+  return launch_umma(h, g, h->math_mode == SNB200_MATH_3XTF32, bn);
+}
+
+static int check_ptrs(snb200_handle_t h, const void* a, const void* b, const void* c) {
+  if (!a || !b || !c) return fail(h, SNB200_STATUS_INVALID_VALUE, "null matrix pointer");
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 3u)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "matrix pointers must be 4-byte aligned");
+  return 0;
+}
+
+extern "C" int snb200_batched_gemm(snb200_handle_t h, int transA, int transB, int aH, int aW, long long strideA,
+                                   int bH, int bW, long long strideB, long long strideC, int batchCount,
+                                   float alpha, const float* A, const float* B, float beta, float* C) {
+  int st = enter(h);
+  if (st) return st;
+  if (aH < 0 || aW < 0 || bH < 0 || bW < 0 || batchCount < 0)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  GemmProblem g;
+  memset(&g, 0, sizeof(g));
+  // Dimension rules of BlasServices.DotMkl (Prod/Data/BlasServices.cs:14-19).
+  g.M = transA ? aW : aH;
+  g.N = transB ? bH : bW;
+  g.K = transA ? aH : aW;
+  const int kB = transB ? bW : bH;
+  if (g.K != kB)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "inner dimensions differ: op(A) is %dx%d, op(B) is %dx%d", g.M, g.K,
+                kB, g.N);
+  g.transA = transA ? 1 : 0; g.transB = transB ? 1 : 0;
+  g.lda = aW; g.ldb = bW; g.ldc = g.N;
+  g.batch = batchCount;
+  g.strideA = strideA; g.strideB = strideB; g.strideC = strideC;
+  if (batchCount > 1 && (strideA < 0 || strideB < 0 || strideC < static_cast<long long>(g.M) * g.N))
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "batch strides must be non-negative and C matrices must not overlap");
+  if (g.M == 0 || g.N == 0 || batchCount == 0) return 0;
+  st = check_ptrs(h, A, B, C);
+  if (st) return st;
+  g.A = A; g.B = B; g.C = C;
+  g.alpha = alpha; g.beta = beta;
+  g.act = ACT_IDENTITY;
+  return run_gemm(h, g);
+}
+
+extern "C" int snb200_gemm(snb200_handle_t h, int transA, int transB, int aH, int aW, int bH, int bW, float alpha,
+                           const float* A, const float* B, float beta, float* C) {
+  return snb200_batched_gemm(h, transA, transB, aH, aW, 0, bH, bW, 0, 0, 1, alpha, A, B, beta, C);
+}
+
+// ------------------------------------------------------------------------------------ Dense
+static bool act_supported(int act) {
+  return act == ACT_SIGMOID || act == ACT_RELU || act == ACT_TANH || act == ACT_IDENTITY || act == ACT_SWISH;
+}
+
+extern "C" int snb200_dense_fwd(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
+                                const float* bias, int act, float* z, float* y) {
+  int st = enter(h);
+  if (st) return st;
+  if (M < 0 || K < 0 || N < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (w_layout != SNB200_W_OUT_IN && w_layout != SNB200_W_IN_OUT)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "unknown weight layout %d", w_layout);
+  if (!act_supported(act)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "activation %d is not fused", act);
+  if (M == 0 || N == 0) return 0;
+  st = check_ptrs(h, x, W, y);
+  if (st) return st;
+  GemmProblem g;
+  memset(&g, 0, sizeof(g));
+  g.M = M; g.N = N; g.K = K;
+  g.transA = 0; g.lda = K;
+  if (w_layout == SNB200_W_OUT_IN) { g.transB = 1; g.ldb = K; }   // y = x * W^T, W [N x K]
+  else                             { g.transB = 0; g.ldb = N; }   // y = x * W,   W [K x N]
+  g.ldc = N; g.batch = 1;
+  g.A = x; g.B = W; g.C = y;
+  g.alpha = 1.0f; g.beta = 0.0f;
+  g.bias = bias; g.Z = z; g.act = act;
+  return run_gemm(h, g);
+}
+
+template <bool FUSE>
+static int launch_colsum(snb200_handle_t h, int M, int N, int act, const float* dy, const float* y, const float* z,
+                         float* dz, float* db) {
+  const bool vec = (N % 4 == 0) && aligned16(dy) && (!FUSE || (aligned16(y) && aligned16(dz) && (!z || aligned16(z))));
+  const int cols_per_block = vec ? 128 : 32;
+  const int col_blocks = (N + cols_per_block - 1) / cols_per_block;
+  int slabs = (4 * h->sm_count + col_blocks - 1) / col_blocks;
+  const int max_slabs_rows = (M + 7) / 8;
+  if (slabs > max_slabs_rows) slabs = max_slabs_rows;
+  const long long ws_slabs = static_cast<long long>(h->workspace_floats / (N > 0 ? N : 1));
+  if (slabs > ws_slabs) slabs = static_cast<int>(ws_slabs);
+  if (slabs < 1) slabs = 1;
+  if (slabs > 65535) slabs = 65535;
+  const int rows_per_slab = (M + slabs - 1) / slabs;
+  slabs = (M + rows_per_slab - 1) / rows_per_slab;
+  if (slabs > 1 && static_cast<size_t>(slabs) * N > h->workspace_floats)
+    return fail(h, SNB200_STATUS_NOT_SUPPORTED, "row width %d exceeds the reduction workspace", N);
+  float* out = db ? (slabs == 1 ? db : h->workspace) : nullptr;
+  dim3 grid(col_blocks, slabs);
+  if (vec)
+    colsum_slab_kernel<4, FUSE><<<grid, 256, 0, h->stream>>>(M, N, rows_per_slab, act, dy, y, z, dz, out);
+  else
+    colsum_slab_kernel<1, FUSE><<<grid, 256, 0, h->stream>>>(M, N, rows_per_slab, act, dy, y, z, dz, out);
+  int launches = 1;
+  if (db && slabs > 1) {
+    colsum_finish_kernel<<<(N + 255) / 256, 256, 0, h->stream>>>(N, slabs, h->workspace, db);
+    ++launches;
+  }
+  note_kernel(h, FUSE ? "dz_db_colsum" : "colsum", launches);
+  return check_launch(h, "colsum launch");
+}
+
+extern "C" int snb200_dense_bwd(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
+                                const float* dy, int act, const float* y, const float* z, float dW_multiplier,
+                                float* dz_scratch, float* dx, float* dW, float* db) {
+  int st = enter(h);
+  if (st) return st;
+  if (M < 0 || K < 0 || N < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (w_layout != SNB200_W_OUT_IN && w_layout != SNB200_W_IN_OUT)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "unknown weight layout %d", w_layout);
+  if (!act_supported(act)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "activation %d is not fused", act);
+  st = check_ptrs(h, x, W, dy);
+  if (st) return st;
+  if (!dW) return fail(h, SNB200_STATUS_INVALID_VALUE, "dW is null");
+  const float* dz = dy;
+  long long launches0 = h->launches;
+  if (act != ACT_IDENTITY) {
+    if (!y) return fail(h, SNB200_STATUS_INVALID_VALUE, "activation output y is required for this activation");
+    if (act == ACT_SWISH && !z) return fail(h, SNB200_STATUS_INVALID_VALUE, "pre-activation z is required for SWISH");
+    if (!dz_scratch) return fail(h, SNB200_STATUS_INVALID_VALUE, "dz_scratch is required for this activation");
+    if (M > 0 && N > 0) {
+      st = launch_colsum<true>(h, M, N, act, dy, y, z, dz_scratch, db);   // dz and db in one pass over dy
+      if (st) return st;
+    }
+    dz = dz_scratch;
+  } else if (db && M > 0 && N > 0) {
+    st = launch_colsum<false>(h, M, N, act, dy, nullptr, nullptr, nullptr, db);
+    if (st) return st;
+  }
+  GemmProblem g;
+  memset(&g, 0, sizeof(g));
+  g.batch = 1; g.act = ACT_IDENTITY; g.beta = 0.0f;
+  // dW, in the layout of W.
+  if (w_layout == SNB200_W_OUT_IN) {   // dW [N x K] = mult * dz^T * x          (Linear.cs:158)
+    g.M = N; g.N = K; g.K = M;
+    g.transA = 1; g.A = dz; g.lda = N;
+    g.transB = 0; g.B = x; g.ldb = K;
+  } else {                             // dW [K x N] = mult * x^T * dz
+    g.M = K; g.N = N; g.K = M;
+    g.transA = 1; g.A = x; g.lda = K;
+    g.transB = 0; g.B = dz; g.ldb = N;
+  }
+  g.C = dW; g.ldc = g.N; g.alpha = dW_multiplier;
+  st = run_gemm(h, g);
+  if (st) return st;
+  if (dx) {
+    g.M = M; g.N = K; g.K = N;
+    g.transA = 0; g.A = dz; g.lda = N;
+    if (w_layout == SNB200_W_OUT_IN) { g.transB = 0; g.B = W; g.ldb = K; }   // dx = dz * W      (Linear.cs:190)
+    else                             { g.transB = 1; g.B = W; g.ldb = N; }   // dx = dz * W^T
+    g.C = dx; g.ldc = K; g.alpha = 1.0f;
+    st = run_gemm(h, g);
+    if (st) return st;
+  }
+  (void)launches0;
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------ companions
+static int ew_grid(const snb200_context* h, long long n, int block) {
+  long long want = (n + block - 1) / block;
+  const long long cap = static_cast<long long>(h->sm_count) * 8;
+  if (want > cap) want = cap;
+  return static_cast<int>(want < 1 ? 1 : want);
+}
+
+extern "C" int snb200_bias_add(snb200_handle_t h, int M, int N, const float* bias, float* y) {
+  int st = enter(h);
+  if (st) return st;
+  if (M < 0 || N < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (M == 0 || N == 0) return 0;
+  if (!bias || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  const long long total = static_cast<long long>(M) * N;
+  if (N % 4 == 0 && aligned16(bias) && aligned16(y))
+    bias_add_vec4_kernel<<<ew_grid(h, total / 4, 256), 256, 0, h->stream>>>(
+        total / 4, N / 4, reinterpret_cast<const float4*>(bias), reinterpret_cast<float4*>(y));
+  else
+    bias_add_kernel<<<ew_grid(h, total, 256), 256, 0, h->stream>>>(total, N, bias, y);
+  note_kernel(h, "bias_add", 1);
+  return check_launch(h, "bias_add launch");
+}
+
+extern "C" int snb200_bias_grad(snb200_handle_t h, int M, int N, const float* dy, float* db) {
+  int st = enter(h);
+  if (st) return st;
+  if (M < 0 || N < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (N == 0) return 0;
+  if (!db || (M > 0 && !dy)) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  if (M == 0) {
+    SNB_CUDA(h, cudaMemsetAsync(db, 0, sizeof(float) * N, h->stream));
+    return 0;
+  }
+  return launch_colsum<false>(h, M, N, ACT_IDENTITY, dy, nullptr, nullptr, nullptr, db);
+}
+
+extern "C" int snb200_activation_fwd(snb200_handle_t h, int act, long long count, const float* x, float* y) {
+  int st = enter(h);
+  if (st) return st;
+  if (count < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative count");
+  if (!act_supported(act)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "activation %d is not implemented", act);
+  if (count == 0) return 0;
+  if (!x || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  activation_fwd_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(act, count, x, y);
+  note_kernel(h, "activation_fwd", 1);
+  return check_launch(h, "activation_fwd launch");
+}
+
+extern "C" int snb200_activation_bwd(snb200_handle_t h, int act, long long count, const float* dy, const float* x,
+                                     const float* y, float* dx) {
+  int st = enter(h);
+  if (st) return st;
+  if (count < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative count");
+  if (!act_supported(act)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "activation %d is not implemented", act);
+  if (count == 0) return 0;
+  if (!dy || !dx || (act != ACT_IDENTITY && !y) || (act == ACT_SWISH && !x))
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  activation_bwd_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(act, count, dy, x, y, dx);
+  note_kernel(h, "activation_bwd", 1);
+  return check_launch(h, "activation_bwd launch");
+}
+
+extern "C" int snb200_axpy(snb200_handle_t h, long long count, float alpha, const float* x, float* y) {
+  int st = enter(h);
+  if (st) return st;
+  if (count < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative count");
+  if (count == 0) return 0;
+  if (!x || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  axpy_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, alpha, x, y);
+  note_kernel(h, "axpy", 1);
+  return check_launch(h, "axpy launch");
+}
+
+// ------------------------------------------------------------------------------------ NCCL (loaded at run time)
+struct NcclId { char bytes[128]; };
+typedef int (*nccl_get_id_t)(NcclId*);
+typedef int (*nccl_init_rank_t)(void**, int, NcclId, int);
+typedef int (*nccl_init_all_t)(void**, int, const int*);
+typedef int (*nccl_allreduce_t)(const void*, void*, size_t, int, int, void*, cudaStream_t);
+typedef int (*nccl_destroy_t)(void*);
+typedef const char* (*nccl_errstr_t)(int);
+static struct {
+  void* lib;
+  nccl_get_id_t get_id;
+  nccl_init_rank_t init_rank;
+  nccl_init_all_t init_all;
+  nccl_allreduce_t allreduce;
+  nccl_destroy_t destroy;
+  nccl_errstr_t errstr;
+} g_nccl;
+
+static bool load_nccl() {
+  if (g_nccl.lib) return true;
+  const char* names[3] = {getenv("SNB200_NCCL_LIBRARY"), "libnccl.so.2", "libnccl.so"};
+  void* lib = nullptr;
+  for (int i = 0; i < 3 && !lib; ++i)
+    if (names[i] && names[i][0]) lib = dlopen(names[i], RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) return false;
+  g_nccl.get_id = reinterpret_cast<nccl_get_id_t>(dlsym(lib, "ncclGetUniqueId"));
+  g_nccl.init_rank = reinterpret_cast<nccl_init_rank_t>(dlsym(lib, "ncclCommInitRank"));
+  g_nccl.init_all = reinterpret_cast<nccl_init_all_t>(dlsym(lib, "ncclCommInitAll"));
+  g_nccl.allreduce = reinterpret_cast<nccl_allreduce_t>(dlsym(lib, "ncclAllReduce"));
+  g_nccl.destroy = reinterpret_cast<nccl_destroy_t>(dlsym(lib, "ncclCommDestroy"));
+  g_nccl.errstr = reinterpret_cast<nccl_errstr_t>(dlsym(lib, "ncclGetErrorString"));
+  if (!g_nccl.get_id || !g_nccl.init_rank || !g_nccl.init_all || !g_nccl.allreduce || !g_nccl.destroy) {
+    dlclose(lib);
+    return false;
+  }
+  g_nccl.lib = lib;
+  return true;
+}
+static int nccl_fail(snb200_handle_t h, int r, const char* what) {
+  return fail(h, SNB200_STATUS_EXECUTION_FAILED, "%s: %s", what, g_nccl.errstr ? g_nccl.errstr(r) : "NCCL error");
+}
+
+extern "C" int snb200_comm_get_unique_id(void* id) {
+  if (!id) return SNB200_STATUS_INVALID_VALUE;
+  if (!load_nccl()) return SNB200_STATUS_NOT_SUPPORTED;
+  return g_nccl.get_id(static_cast<NcclId*>(id)) == 0 ? 0 : SNB200_STATUS_EXECUTION_FAILED;
+}
+extern "C" int snb200_comm_init_rank(snb200_handle_t h, int n_ranks, int rank, const void* id) {
+  int st = enter(h);
+  if (st) return st;
+  if (!id || n_ranks < 1 || rank < 0 || rank >= n_ranks) return fail(h, SNB200_STATUS_INVALID_VALUE, "bad rank %d of %d", rank, n_ranks);
+  if (h->nccl_comm) return fail(h, SNB200_STATUS_INVALID_VALUE, "communicator already initialised");
+  if (!load_nccl()) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "libnccl.so.2 could not be loaded");
+  NcclId nid;
+  memcpy(&nid, id, sizeof(nid));
+  int r = g_nccl.init_rank(&h->nccl_comm, n_ranks, nid, rank);
+  if (r) { h->nccl_comm = nullptr; return nccl_fail(h, r, "ncclCommInitRank"); }
+  return 0;
+}
+extern "C" int snb200_comm_init_all(snb200_handle_t* handles, int n) {
+  if (!handles || n < 1 || n > 64) return SNB200_STATUS_INVALID_VALUE;
+  if (!load_nccl()) return SNB200_STATUS_NOT_SUPPORTED;
+  void* comms[64];
+  int devs[64];
+  for (int i = 0; i < n; ++i) {
+    if (!handles[i]) return SNB200_STATUS_NOT_INITIALIZED;
+    if (handles[i]->nccl_comm) return fail(handles[i], SNB200_STATUS_INVALID_VALUE, "communicator already initialised");
+    devs[i] = handles[i]->device;
+  }
+  int r = g_nccl.init_all(comms, n, devs);
+  if (r) return nccl_fail(handles[0], r, "ncclCommInitAll");
+  for (int i = 0; i < n; ++i) handles[i]->nccl_comm = comms[i];
+  return 0;
+}
+extern "C" int snb200_allreduce_sum(snb200_handle_t h, float* buf, long long count) {
+  int st = enter(h);
+  if (st) return st;
+  if (count < 0 || (count > 0 && !buf)) return fail(h, SNB200_STATUS_INVALID_VALUE, "bad buffer");
+  if (!h->nccl_comm) return fail(h, SNB200_STATUS_NOT_INITIALIZED, "no communicator on this handle");
+  if (count == 0) return 0;
+  int r = g_nccl.allreduce(buf, buf, static_cast<size_t>(count), /*ncclFloat32*/ 7, /*ncclSum*/ 0, h->nccl_comm, h->stream);
+  if (r) return nccl_fail(h, r, "ncclAllReduce");
+  return 0;
+}
+extern "C" int snb200_comm_destroy(snb200_handle_t h) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  if (!h->nccl_comm) return 0;
+  cudaSetDevice(h->device);
+  int r = g_nccl.destroy(h->nccl_comm);
+  h->nccl_comm = nullptr;
+  return r ? nccl_fail(h, r, "ncclCommDestroy") : 0;
+}

@@ -1,0 +1,111 @@
+"""Extracts the known-answer vectors that SharpNet's own tests hold for the Dot / Dense path and
+writes them to ``reference_vectors.json`` next to this script.
+
+Run it where a checkout of the reference is available:
+    python tests/golden/make_golden.py /path/to/SharpNet
+Nothing at test or run time reads the reference: the JSON file is committed.
+
+Sources (paths inside the reference):
+  Tests/GPU/TestGpuTensor.cs:50-120              exact Dot cases (tolerance 1e-9)
+  Tests/NonReg/TestNetworkPropagation.cs:24-34   inputs X_1_1_4_4, X_2_1_4_4 and weights W_N_1_4_4
+  Tests/NonReg/TestNetworkPropagation.cs:80-132  Linear + Sigmoid predictions before training ([in,out] weights)
+  Tests/NonReg/ParallelRunWithPyTorch.cs:102-138 Linear(5->3, last-dim flatten)+ReLU+Flatten+Linear(36->3), Mse
+  Tests/NonReg/ParallelRunWithPyTorch.cs:179-214 Linear(16->3)+ReLU+Linear(3->3)+Sigmoid, BCE ([out,in] weights)
+"""
+import json
+import os
+import re
+import sys
+
+
+def _between(text, start_marker, end_marker):
+    i = text.index(start_marker)
+    j = text.index(end_marker, i)
+    return text[i:j]
+
+
+def _numbers(s):
+    return [float(v) for v in re.findall(r"-?\d+\.?\d*(?:[eE]-?\d+)?", s)]
+
+
+def _const(text, name):
+    m = re.search(name + r'\s*=\s*@?"(.*?)";', text)
+    body = m.group(1)
+    body = body.replace("numpy.array(", "").replace(", numpy.float)", "")
+    return _numbers(body)
+
+
+def _nth_numpy_literal(block, n):
+    lits = re.findall(r'FromNumpyArray\("(\[\[.*?\]\])"\)', block)
+    return _numbers(lits[n])
+
+
+def main(ref):
+    out = {}
+    # ---- exact Dot cases: (aShape, a, bShape, b, expectedShape, expected) -------------------
+    gpu = open(os.path.join(ref, "Tests/GPU/TestGpuTensor.cs"), encoding="utf-8-sig").read()
+    block = _between(gpu, "public void TestDot()", "// [10x1x28x28]")
+    cases = []
+    # Walk the block statement by statement instead of trusting regex order.
+    stmts = [s.strip() for s in block.split(";")]
+    cur = {}
+    last_data = None
+    for s in stmts:
+        m = re.search(r"float\[\]\s+(\w+)\s*=\s*new\s*\[\]\s*\{(.*?)\}", s, re.S)
+        if m:
+            last_data = [float(v.strip().rstrip("f")) for v in m.group(2).split(",") if v.strip()]
+            cur[m.group(1)] = last_data
+            continue
+        m = re.search(r"(\w+)\s*=\s*new GPUTensor<float>\(new\s*\[\]\s*\{(.*?)\},\s*(\w+),", s, re.S)
+        if m:
+            name, shape, data = m.group(1), [int(v) for v in m.group(2).split(",")], m.group(3)
+            cur[("t", name.split()[-1])] = (shape, cur.get(data))
+            continue
+        m = re.search(r"expected\s*=\s*new CpuTensor<float>\(new\s*\[\]\s*\{(.*?)\},\s*new\s*\[\]\s*\{(.*?)\}\)", s, re.S)
+        if m:
+            eshape = [int(v) for v in m.group(1).split(",")]
+            edata = [float(v.strip().rstrip("f")) for v in m.group(2).split(",") if v.strip()]
+            a_shape, a = cur[("t", "a")]
+            b_shape, b = cur[("t", "b")]
+            cases.append({"a_shape": a_shape, "a": a, "b_shape": b_shape, "b": b, "expected_shape": eshape,
+                          "expected": edata})
+    out["dot_exact"] = cases
+    out["dot_exact_zero_cases"] = [
+        {"a_shape": [10, 1, 28, 28], "b_shape": [784, 100], "expected_shape": [10, 1, 1, 100]},
+        {"a_shape": [35, 124], "b_shape": [124, 21], "expected_shape": [35, 21]},
+    ]
+
+    # ---- Keras-layout network goldens --------------------------------------------------------
+    tnp = open(os.path.join(ref, "Tests/NonReg/TestNetworkPropagation.cs"), encoding="utf-8-sig").read()
+    out["X_1_1_4_4"] = _const(tnp, "X_1_1_4_4")
+    out["X_2_1_4_4"] = _const(tnp, "X_2_1_4_4")
+    out["W_N_1_4_4"] = _const(tnp, "W_N_1_4_4")          # [16, 3]  = [in, out]
+    blk = _between(tnp, "public void TestSigmoidActivation_NCHW_1_1_4_4", "const int num_epochs")
+    out["sigmoid_1_1_4_4_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))
+    out["sigmoid_1_1_4_4_loss"] = _numbers(re.search(r"TestLossAccuracy\(network, X, Y, ([0-9.]+)", blk).group(1))[0]
+    blk = _between(tnp, "public void TestSigmoidActivation_NCHW_2_1_4_4", "const int num_epochs")
+    out["sigmoid_2_1_4_4_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))
+    out["sigmoid_2_1_4_4_loss"] = _numbers(re.search(r"TestLossAccuracy\(network, X, Y, ([0-9.]+)", blk).group(1))[0]
+    blk = _between(tnp, "public void TestSigmoidActivation_NCHW_1_1_1_1", "const int num_epochs")
+    out["sigmoid_1_1_1_1_w"] = _nth_numpy_literal(blk, 0)
+    out["sigmoid_1_1_1_1_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))
+
+    # ---- PyTorch-layout network goldens ------------------------------------------------------
+    pt = open(os.path.join(ref, "Tests/NonReg/ParallelRunWithPyTorch.cs"), encoding="utf-8-sig").read()
+    blk = _between(pt, "public void TestParallelRunWithPyTorch_Mse()", "public void TestParallelRunWithPyTorch_Mse_AdamW")
+    out["pt_mse_w1"] = _nth_numpy_literal(blk, 0)         # [3, 5]  = [out, in]
+    out["pt_mse_w2"] = _nth_numpy_literal(blk, 1)         # [3, 36]
+    out["pt_mse_loss_before"] = _numbers(re.search(r"Assert.AreEqual\(([0-9.]+), loss_before", blk).group(1))[0]
+    blk = _between(pt, "public void TestReluActivation_NCHW_2_1_4_4()", "//test_save_sharpnet")
+    out["pt_relu_w1"] = _nth_numpy_literal(blk, 0)        # [3, 16]
+    out["pt_relu_w2"] = _nth_numpy_literal(blk, 1)        # [3, 3]
+    out["pt_relu_loss_before"] = _numbers(re.search(r"Assert.AreEqual\(([0-9.]+), loss_before", blk).group(1))[0]
+
+    dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json")
+    with open(dst, "w") as f:
+        json.dump(out, f, indent=1)
+    print("wrote", dst, {k: (len(v) if isinstance(v, list) else v) for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

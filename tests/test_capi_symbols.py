@@ -1,0 +1,43 @@
+"""The C-ABI library must build, load without a GPU, and export every symbol the header declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "sharpnet_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(snb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(built_library):
+    lib = ctypes.CDLL(built_library)
+    names = _declared_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/sharpnet_b200.h but not exported"
+
+
+def test_binding_table_matches_header(built_library):
+    from sharpnet_b200 import _capi
+    assert sorted(_capi.SIGNATURES) == _declared_symbols()
+    lib = _capi.load()
+    assert lib.snb200_get_version() >= 100
+
+
+def test_create_fails_loudly_without_a_device(built_library):
+    import torch
+    if torch.cuda.is_available():
+        return
+    from sharpnet_b200 import _capi
+    lib = _capi.load()
+    h = ctypes.c_void_p()
+    assert lib.snb200_create(ctypes.byref(h), 0) != 0       # no CPU fallback
+    assert not h.value
+    assert lib.snb200_gemm(None, 0, 0, 1, 1, 1, 1, 1.0, None, None, 0.0, None) == 1   # NOT_INITIALIZED
+    import pytest
+    from sharpnet_b200.tensor import GPUWrapper
+    with pytest.raises(RuntimeError):
+        GPUWrapper(0)

@@ -1,0 +1,123 @@
+"""Pins the CPU oracle on the known-answer vectors SharpNet's own tests hold for the path
+(extracted by tests/golden/make_golden.py)."""
+import numpy as np
+
+from oracle import sharpnet_oracle as orc
+
+
+def _dot(a, a_shape, b, b_shape, tA=False, tB=False, alpha=1.0, beta=0.0, c=None):
+    aH, aW = a_shape[0], int(np.prod(a_shape[1:]))
+    bH, bW = b_shape[0], int(np.prod(b_shape[1:]))
+    M, N, _, _, _, _ = orc.gemm_dims(aH, aW, tA, bH, bW, tB)
+    out = np.zeros(M * N, dtype=np.float32) if c is None else c.astype(np.float32).ravel().copy()
+    return orc.dot_mkl(np.asarray(a, np.float32), aH, aW, tA, np.asarray(b, np.float32), bH, bW, tB, out, alpha, beta)
+
+
+def test_exact_dot_cases(golden):
+    # Tests/GPU/TestGpuTensor.cs:50-120, tolerance 1e-9
+    assert len(golden["dot_exact"]) == 5
+    for case in golden["dot_exact"]:
+        got = _dot(case["a"], case["a_shape"], case["b"], case["b_shape"])
+        np.testing.assert_allclose(got.ravel(), case["expected"], rtol=0, atol=1e-9)
+        f64 = orc.dot_f64(case["a"], case["a_shape"][0], int(np.prod(case["a_shape"][1:])), False, case["b"],
+                          case["b_shape"][0], int(np.prod(case["b_shape"][1:])), False, None, 1.0, 0.0)
+        np.testing.assert_allclose(f64.ravel(), case["expected"], rtol=0, atol=1e-12)
+    for case in golden["dot_exact_zero_cases"]:
+        a = np.zeros(case["a_shape"], np.float32)
+        b = np.zeros(case["b_shape"], np.float32)
+        got = _dot(a.ravel(), case["a_shape"], b.ravel(), case["b_shape"])
+        assert got.size == int(np.prod(case["expected_shape"])) and not got.any()
+
+
+def test_keras_layout_sigmoid_predictions(golden):
+    # Tests/NonReg/TestNetworkPropagation.cs:80-132: Linear(3, bias=0) + Sigmoid, weights [in, out], tol 1e-6
+    W = np.asarray(golden["W_N_1_4_4"], np.float32).reshape(16, 3)
+    for key, rows in (("1_1_4_4", 1), ("2_1_4_4", 2)):
+        x = np.asarray(golden["X_" + key], np.float32).reshape(rows, 16)
+        _, y = orc.dense_forward(x, W, np.zeros(3, np.float32), orc.ACT_SIGMOID, orc.W_IN_OUT)
+        np.testing.assert_allclose(y.ravel(), golden[f"sigmoid_{key}_pred"], rtol=0, atol=1e-6)
+    y_true = np.asarray([[1, 0, 0]], np.float32)
+    x = np.asarray(golden["X_1_1_4_4"], np.float32).reshape(1, 16)
+    _, y = orc.dense_forward(x, W, None, orc.ACT_SIGMOID, orc.W_IN_OUT)
+    assert abs(orc.binary_crossentropy(y_true, y) - golden["sigmoid_1_1_4_4_loss"]) < 1e-5
+    # 1x1x1x1 input, Linear(2): both layouts coincide
+    w = np.asarray(golden["sigmoid_1_1_1_1_w"], np.float32).reshape(1, 2)
+    _, y = orc.dense_forward(np.ones((1, 1), np.float32), w, None, orc.ACT_SIGMOID, orc.W_IN_OUT)
+    np.testing.assert_allclose(y.ravel(), golden["sigmoid_1_1_1_1_pred"], rtol=0, atol=1e-6)
+
+
+def test_pytorch_layout_relu_network_loss(golden):
+    # Tests/NonReg/ParallelRunWithPyTorch.cs:179-214: Linear(16->3)+ReLU+Linear(3->3)+Sigmoid, BCE, [out, in]
+    x = orc.numpy_array_for_tests(2, 1, 4, 4).reshape(2, 16)
+    y_true = orc.y_numpy_array_for_tests(2, 3)
+    w1 = np.asarray(golden["pt_relu_w1"], np.float32).reshape(3, 16)
+    w2 = np.asarray(golden["pt_relu_w2"], np.float32).reshape(3, 3)
+    _, h = orc.dense_forward(x, w1, np.zeros(3, np.float32), orc.ACT_RELU, orc.W_OUT_IN)
+    _, p = orc.dense_forward(h, w2, np.zeros(3, np.float32), orc.ACT_SIGMOID, orc.W_OUT_IN)
+    assert abs(orc.binary_crossentropy(y_true, p) - golden["pt_relu_loss_before"]) < 1e-6
+
+
+def test_pytorch_layout_last_dim_flatten_mse(golden):
+    # Tests/NonReg/ParallelRunWithPyTorch.cs:102-138: Linear(5->3 on the last dim)+ReLU+Flatten+Linear(36->3), Mse
+    x = orc.numpy_array_for_tests(2, 3, 4, 5)
+    y_true = orc.y_numpy_array_for_tests(2, 3)
+    w1 = np.asarray(golden["pt_mse_w1"], np.float32).reshape(3, 5)
+    w2 = np.asarray(golden["pt_mse_w2"], np.float32).reshape(3, 36)
+    _, h = orc.dense_forward(x.reshape(-1, 5), w1, np.zeros(3, np.float32), orc.ACT_RELU, orc.W_OUT_IN)
+    _, p = orc.dense_forward(h.reshape(2, 36), w2, np.zeros(3, np.float32), orc.ACT_IDENTITY, orc.W_OUT_IN)
+    assert abs(orc.mse(y_true, p) - golden["pt_mse_loss_before"]) < 1e-6
+
+
+def test_mkl_agrees_with_float64_on_all_transposes():
+    rng = np.random.default_rng(3)
+    M, N, K = 37, 29, 53
+    for tA in (False, True):
+        for tB in (False, True):
+            a = rng.uniform(-1.5, 1.5, (K, M) if tA else (M, K)).astype(np.float32)
+            b = rng.uniform(-1.5, 1.5, (N, K) if tB else (K, N)).astype(np.float32)
+            c = rng.uniform(-1.5, 1.5, (M, N)).astype(np.float32)
+            got = _dot(a.ravel(), a.shape, b.ravel(), b.shape, tA, tB, 0.25, 1.0, c)
+            ref = orc.dot_f64(a.ravel(), a.shape[0], a.shape[1], tA, b.ravel(), b.shape[0], b.shape[1], tB,
+                              c.ravel(), 0.25, 1.0)
+            assert orc.scaled_error(got, ref, K, 1.5, 1.5) < 1e-6
+
+
+def test_gradient_check_dense_backward():
+    # Tests/TestGradient.cs:20-36: central differences vs analytic dW/db, relative error <= 1e-3
+    rng = np.random.default_rng(5)
+    M, K, N = 6, 7, 4
+    x = rng.normal(size=(M, K)).astype(np.float32)
+    W = rng.normal(size=(N, K)).astype(np.float32) * 0.5
+    b = rng.normal(size=N).astype(np.float32) * 0.1
+    dy = rng.normal(size=(M, N)).astype(np.float32)
+    for act in (orc.ACT_TANH, orc.ACT_SIGMOID, orc.ACT_SWISH):
+        z, y = orc.dense_forward(x, W, b, act, orc.W_OUT_IN)
+        _, dW, db, dx = orc.dense_backward(x, W, dy, act, y, z, 1.0, orc.W_OUT_IN)
+
+        def loss(Wp, bp):
+            _, yy = orc.dense_forward(x, Wp, bp, act, orc.W_OUT_IN, f64=True)
+            return float((yy * dy).sum())
+        eps = 1e-3
+        for (i, j) in ((0, 0), (1, 3), (3, 6)):
+            Wp, Wm = W.astype(np.float64).copy(), W.astype(np.float64).copy()
+            Wp[i, j] += eps
+            Wm[i, j] -= eps
+            num = (loss(Wp, b) - loss(Wm, b)) / (2 * eps)
+            assert abs(num - dW[i, j]) <= 1e-3 * max(1.0, abs(num))
+        bp, bm = b.astype(np.float64).copy(), b.astype(np.float64).copy()
+        bp[2] += eps
+        bm[2] -= eps
+        num = (loss(W, bp) - loss(W, bm)) / (2 * eps)
+        assert abs(num - db[2]) <= 1e-3 * max(1.0, abs(num))
+
+
+def test_bias_gradient_and_bias_add():
+    rng = np.random.default_rng(7)
+    dy = rng.uniform(-1.5, 1.5, (9, 1632)).astype(np.float32)   # shape of TestCompute_BiasGradient_from_dy
+    db = orc.compute_bias_gradient_from_dy(dy)
+    np.testing.assert_allclose(db, dy.astype(np.float64).sum(0), rtol=0, atol=1e-5)
+    y = rng.uniform(-1.5, 1.5, (9, 1632)).astype(np.float32)
+    bias = rng.uniform(-1.5, 1.5, 1632).astype(np.float32)
+    ref = y + bias[None, :]
+    orc.broadcast_add_vector_to_output(bias, y)
+    np.testing.assert_array_equal(y, ref)
