@@ -86,8 +86,8 @@ int snb200_get_version(void);
 /* Kernel-selection overrides for experiments and tests (no counterpart in SharpNet).
  * key 0: path (0 automatic, 1 tensor cores whenever the operands allow TMA, 2 SIMT fp32);
  * key 1: tile width of the tensor-core kernel (0 automatic, else 32, 64, 128 or 256);
- * key 2: 3xTF32 writes the rounded hi plane back to shared memory (1, default) or lets the
- *        tensor core truncate the raw fp32 words itself (0). */
+ * key 2: 3xTF32 writes the rounded hi plane back to shared memory (1) or lets the
+ *        tensor core truncate the raw fp32 words itself (0, default). */
 int snb200_set_tuning(snb200_handle_t handle, int key, int value);
 
 /* ---- Tensor.Dot -----------------------------------------------------------------------------

@@ -47,8 +47,12 @@ struct UmmaTile {
   static constexpr int KMAJ_ROW_BYTES = BK * 4;
   static constexpr int KMAJ_SBO = 8 * KMAJ_ROW_BYTES;
   static constexpr int KMAJ_LAYOUT = (BK == 32) ? 2 : 4;
-  // MN-major tiles: chunks of 32 fp32 (128 B) along M/N, BK rows each, 128-byte swizzle.
+  // MN-major tiles: chunks of 32 fp32 (128 B) along M/N, BK rows each.  32-bit MN-major operands
+  // use the 128-byte swizzle with 32-byte atoms (descriptor layout 1, TMA SWIZZLE_128B_ATOM_32B):
+  // the pattern repeats every 4 rows, so the stride between K groups is 4 x 128 B.
   static constexpr int MNMAJ_CHUNK_BYTES = BK * 128;
+  static constexpr int MNMAJ_SBO = 512;
+  static constexpr int MNMAJ_LAYOUT = 1;
   static_assert(BK == 32 || BK == 16, "BK must be 16 or 32");
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
   static_assert(STAGES >= 2, "need at least two stages");
@@ -179,10 +183,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t b_step = p.b_mn ? 1024u : 32u;
       const uint32_t a_lbo = p.a_mn ? T::MNMAJ_CHUNK_BYTES : 16u;
       const uint32_t b_lbo = p.b_mn ? T::MNMAJ_CHUNK_BYTES : 16u;
-      const uint32_t a_sbo = p.a_mn ? 1024u : T::KMAJ_SBO;
-      const uint32_t b_sbo = p.b_mn ? 1024u : T::KMAJ_SBO;
-      const uint32_t a_lay = p.a_mn ? 2u : T::KMAJ_LAYOUT;
-      const uint32_t b_lay = p.b_mn ? 2u : T::KMAJ_LAYOUT;
+      const uint32_t a_sbo = p.a_mn ? T::MNMAJ_SBO : T::KMAJ_SBO;
+      const uint32_t b_sbo = p.b_mn ? T::MNMAJ_SBO : T::KMAJ_SBO;
+      const uint32_t a_lay = p.a_mn ? T::MNMAJ_LAYOUT : T::KMAJ_LAYOUT;
+      const uint32_t b_lay = p.b_mn ? T::MNMAJ_LAYOUT : T::KMAJ_LAYOUT;
       int s = 0;
       uint32_t ph = 0;
       uint32_t acc_ph = 0;  // bit b = phase of accumulator b

@@ -98,7 +98,7 @@ extern "C" int snb200_create(snb200_handle_t* handle, int device_id) {
   h->sm_count = prop.multiProcessorCount;
   h->stream = 0;
   h->math_mode = SNB200_MATH_3XTF32;
-  h->tune[TUNE_REWRITE_HI] = 1;
+  h->tune[TUNE_REWRITE_HI] = 0;
   const char* env = getenv("SNB200_MATH_MODE");
   if (env && env[0] >= '0' && env[0] <= '2' && env[1] == 0) h->math_mode = env[0] - '0';
   h->workspace_floats = 1u << 20;
@@ -209,11 +209,11 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g) {
   if (!g.transA)  // stored [M x K]: K-major tile, box = BK x 128 rows
     ok = encode_3d(&tmA, g.A, g.K, g.M, g.batch, g.lda, pitchA2, T::BK, T::BM, kmaj_sw);
   else            // stored [K x M]: MN-major tile, box = 32 m x BK rows
-    ok = encode_3d(&tmA, g.A, g.M, g.K, g.batch, g.lda, pitchA2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    ok = encode_3d(&tmA, g.A, g.M, g.K, g.batch, g.lda, pitchA2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (g.transB)   // stored [N x K]: K-major tile
     ok = ok && encode_3d(&tmB, g.B, g.K, g.N, g.batch, g.ldb, pitchB2, T::BK, T::BN, kmaj_sw);
   else            // stored [K x N]: MN-major tile
-    ok = ok && encode_3d(&tmB, g.B, g.N, g.K, g.batch, g.ldb, pitchB2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    ok = ok && encode_3d(&tmB, g.B, g.N, g.K, g.batch, g.ldb, pitchB2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (!ok) return fail(h, SNB200_STATUS_INTERNAL_ERROR, "cuTensorMapEncodeTiled rejected the operand layout");
 
   UmmaParams p;
