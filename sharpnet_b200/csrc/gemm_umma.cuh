@@ -3,12 +3,12 @@
 //   C[b] = epi(alpha * op(A[b]) * op(B[b]) + beta * C[b])
 //
 // One persistent CTA per SM walks over 128 x BN output tiles.  Warp roles:
-//   warp 0        TMA producer: fp32 tiles of A and B -> shared memory ring (swizzled)
-//   warp 1        owns TMEM; one lane issues tcgen05.mma (kind::tf32) into a TMEM accumulator
-//   warps 2..5    epilogue: TMEM -> registers -> alpha/beta/bias/activation -> global memory
-//   warps 6..13   (3xTF32 only) split every fp32 operand tile into hi + lo TF32 planes
-// The accumulator is double buffered in TMEM, so the epilogue of tile i overlaps the main loop
-// of tile i+1.
+//   warp 0         TMA producer: fp32 tiles of A and B -> shared memory ring (swizzled)
+//   warp 1         owns TMEM; one lane issues tcgen05.mma (kind::tf32) into a TMEM accumulator
+//   warps 4..7/11  epilogue: TMEM partial sums -> fp32 registers -> alpha/beta/bias/activation -> global
+//   last 4 warps   (3xTF32 only) split every fp32 operand tile into hi + lo TF32 planes
+// The TMEM accumulator is double buffered, so draining one partial sum (or the epilogue of tile i)
+// overlaps the tensor-core work on the next.
 //
 // Transposes never move data: an operand whose contraction dimension is contiguous in memory is
 // loaded as a K-major tile, the other kind as an MN-major tile, and the tcgen05 descriptors name
@@ -41,8 +41,18 @@ struct UmmaTile {
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;    // + slack to align the ring to 1 KB
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; power of two
-  static constexpr int N_SPLIT_THREADS = SPLIT ? 256 : 0;
-  static constexpr int THREADS = 192 + N_SPLIT_THREADS;
+  // Warps are grouped in fours so that setmaxnreg can move registers between the roles:
+  //   group 0: TMA producer, MMA issuer (two idle warps); then the epilogue groups; then the split group.
+  static constexpr int EPI_GROUPS = (BN > 128) ? 2 : 1;             // each epilogue warp owns <= 128 columns
+  static constexpr int EPI_THREADS = 128 * EPI_GROUPS;
+  static constexpr int EPI_COLS = BN / EPI_GROUPS;                  // columns per epilogue warp
+  static constexpr int N_SPLIT_THREADS = SPLIT ? 128 : 0;
+  static constexpr int SPLIT_THREAD0 = 128 + EPI_THREADS;
+  static constexpr int THREADS = 128 + EPI_THREADS + N_SPLIT_THREADS;
+  static constexpr int REGS_CTRL = 72;
+  static constexpr int REGS_SPLIT = 64;
+  static constexpr int REGS_EPI_RAW = (65536 / 128 - REGS_CTRL - (SPLIT ? REGS_SPLIT : 0)) / EPI_GROUPS;
+  static constexpr int REGS_EPI = (REGS_EPI_RAW > 232 ? 232 : REGS_EPI_RAW) / 8 * 8;
   // K-major tiles: one row = BK fp32.  128-byte swizzle for BK = 32, 64-byte for BK = 16.
   static constexpr int KMAJ_ROW_BYTES = BK * 4;
   static constexpr int KMAJ_SBO = 8 * KMAJ_ROW_BYTES;
@@ -54,14 +64,16 @@ struct UmmaTile {
   static constexpr int MNMAJ_SBO = 512;
   static constexpr int MNMAJ_LAYOUT = 1;
   static_assert(BK == 32 || BK == 16, "BK must be 16 or 32");
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
+  static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "BN must be 32, 64, 128 or 256");
   static_assert(STAGES >= 2, "need at least two stages");
+  static_assert(EPI_COLS % 32 == 0 && EPI_COLS <= 128, "an epilogue warp keeps at most 128 columns in registers");
 };
 
 struct UmmaParams {
   int M, N, K, batch;
   int tiles_m, tiles_n, k_blocks;
-  int a_mn, b_mn;  // 1 = operand tile is MN-major (A stored [K x M] / B stored [K x N])
+  int chunk_kblocks;  // k-blocks accumulated inside the tensor core before the sum moves to registers
+  int a_mn, b_mn;     // 1 = operand tile is MN-major (A stored [K x M] / B stored [K x N])
   int ldc;
   long long strideC;
   float* C;
@@ -70,7 +82,7 @@ struct UmmaParams {
   float alpha, beta;
   int act;
   int rewrite_hi;   // 3xTF32: store the rounded hi plane back over the raw tile
-  int vec_ok;       // C (and Z) rows are 16-byte aligned
+  int vec_ok;       // C (and Z, bias) rows are 16-byte aligned
   int* error_word;  // set to 1 when a pipeline wait timed out
 };
 
@@ -95,6 +107,20 @@ __device__ __forceinline__ uint32_t to_tf32_rna(float x) {
   return r;
 }
 
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// The tensor core adds into its fp32 accumulator with truncation, so a long K loop drifts towards
+// zero by about 1e-8 * K (relative to sqrt(K)).  The MMA warp therefore accumulates only
+// `chunk_kblocks` k-blocks in TMEM; the epilogue warps add every such partial sum into fp32
+// registers (round-to-nearest), alternating between the two TMEM buffers so that the tensor core
+// never waits for them.
 template <class T>
 __global__ void __launch_bounds__(T::THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -104,8 +130,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ uint64_t full_bar[STAGES];    // TMA bytes landed
   __shared__ uint64_t split_bar[STAGES];   // hi/lo planes written (3xTF32)
   __shared__ uint64_t empty_bar[STAGES];   // MMAs that read the stage retired
-  __shared__ uint64_t acc_full_bar[2];     // accumulator complete in TMEM
-  __shared__ uint64_t acc_empty_bar[2];    // accumulator drained by the epilogue
+  __shared__ uint64_t acc_full_bar[2];     // partial sum complete in TMEM
+  __shared__ uint64_t acc_empty_bar[2];    // partial sum moved to registers
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
 
@@ -121,7 +147,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full_bar[b], 1);
-      mbar_init(&acc_empty_bar[b], 128);
+      mbar_init(&acc_empty_bar[b], T::EPI_THREADS);
     }
     abort_flag = 0;
     fence_mbar_init();
@@ -139,10 +165,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile int* abortp = &abort_flag;
 
   const int total_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int n_chunks = (p.k_blocks + p.chunk_kblocks - 1) / p.chunk_kblocks;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+  if (warp < 4) {
+    reg_dealloc<T::REGS_CTRL>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -173,11 +201,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
       const uint32_t idesc = make_idesc_tf32(BM, BN, p.a_mn, p.b_mn);
       const uint32_t a_step = p.a_mn ? 1024u : 32u;   // bytes per K = 8 slice
       const uint32_t b_step = p.b_mn ? 1024u : 32u;
@@ -189,119 +214,135 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t b_lay = p.b_mn ? T::MNMAJ_LAYOUT : T::KMAJ_LAYOUT;
       int s = 0;
       uint32_t ph = 0;
-      uint32_t acc_ph = 0;  // bit b = phase of accumulator b
-      int it = 0;
+      uint32_t acc_ph = 0;  // bit b = phase of TMEM buffer b
+      uint32_t chunk_id = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
-        const int buf = it & 1;
-        if (!mbar_wait(&acc_empty_bar[buf], ((acc_ph >> buf) & 1u) ^ 1u, abortp)) { ok = false; break; }
-        acc_ph ^= 1u << buf;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          uint64_t* ready = T::SPLIT ? &split_bar[s] : &full_bar[s];
-          if (!mbar_wait(ready, ph, abortp)) { ok = false; break; }
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += p.chunk_kblocks, ++chunk_id) {
+          const int buf = chunk_id & 1;
+          if (!mbar_wait(&acc_empty_bar[buf], ((acc_ph >> buf) & 1u) ^ 1u, abortp)) { ok = false; break; }
+          acc_ph ^= 1u << buf;
           tc_fence_after_sync();
-          const uint32_t a_hi = smem_u32(ring + s * T::STAGE_BYTES);
-          const uint32_t b_hi = a_hi + T::A_BYTES;
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          const int kb1 = min(p.k_blocks, kb0 + p.chunk_kblocks);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            uint64_t* ready = T::SPLIT ? &split_bar[s] : &full_bar[s];
+            if (!mbar_wait(ready, ph, abortp)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t a_hi = smem_u32(ring + s * T::STAGE_BYTES);
+            const uint32_t b_hi = a_hi + T::A_BYTES;
 #pragma unroll
-          for (int ks = 0; ks < BK / kUmmaK; ++ks) {
-            const uint64_t da_hi = make_smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lay);
-            const uint64_t db_hi = make_smem_desc(b_hi + ks * b_step, b_lbo, b_sbo, b_lay);
-            const uint32_t first = (kb == 0 && ks == 0) ? 0u : 1u;
-            if (T::SPLIT) {
-              const uint64_t da_lo = make_smem_desc(a_hi + T::RAW_BYTES + ks * a_step, a_lbo, a_sbo, a_lay);
-              const uint64_t db_lo = make_smem_desc(b_hi + T::RAW_BYTES + ks * b_step, b_lbo, b_sbo, b_lay);
-              umma_tf32_ss(d_tmem, da_lo, db_hi, idesc, first);
-              umma_tf32_ss(d_tmem, da_hi, db_lo, idesc, 1u);
-              umma_tf32_ss(d_tmem, da_hi, db_hi, idesc, 1u);
-            } else {
-              umma_tf32_ss(d_tmem, da_hi, db_hi, idesc, first);
+            for (int ks = 0; ks < BK / kUmmaK; ++ks) {
+              const uint64_t da_hi = make_smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lay);
+              const uint64_t db_hi = make_smem_desc(b_hi + ks * b_step, b_lbo, b_sbo, b_lay);
+              const uint32_t first = (kb == kb0 && ks == 0) ? 0u : 1u;
+              if (T::SPLIT) {
+                const uint64_t da_lo = make_smem_desc(a_hi + T::RAW_BYTES + ks * a_step, a_lbo, a_sbo, a_lay);
+                const uint64_t db_lo = make_smem_desc(b_hi + T::RAW_BYTES + ks * b_step, b_lbo, b_sbo, b_lay);
+                umma_tf32_ss(d_tmem, da_lo, db_hi, idesc, first);
+                umma_tf32_ss(d_tmem, da_hi, db_lo, idesc, 1u);
+                umma_tf32_ss(d_tmem, da_hi, db_hi, idesc, 1u);
+              } else {
+                umma_tf32_ss(d_tmem, da_hi, db_hi, idesc, first);
+              }
             }
+            umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+            if (++s == STAGES) { s = 0; ph ^= 1; }
           }
-          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (ok) umma_commit(&acc_full_bar[buf]);
         }
-        if (ok) umma_commit(&acc_full_bar[buf]);
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
+  } else if (warp < 4 + 4 * T::EPI_GROUPS) {
     // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    uint32_t acc_ph = 0;  // bit b = phase of accumulator b
-    int it = 0;
+    reg_alloc<T::REGS_EPI>();
+    constexpr int NC = T::EPI_COLS;          // columns this warp owns
+    const int q = warp & 3;                  // TMEM lane quarter this warp may read
+    const int col_base = ((warp - 4) >> 2) * NC;
+    uint32_t acc_ph = 0;
+    uint32_t chunk_id = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int b, tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
-      const int buf = it & 1;
-      if (!mbar_wait(&acc_full_bar[buf], (acc_ph >> buf) & 1u, abortp)) { ok = false; break; }
-      acc_ph ^= 1u << buf;
-      tc_fence_after_sync();
+      float acc[NC];
+#pragma unroll
+      for (int j = 0; j < NC; ++j) acc[j] = 0.0f;
+      for (int c = 0; c < n_chunks && ok; ++c, ++chunk_id) {
+        const int buf = chunk_id & 1;
+        if (!mbar_wait(&acc_full_bar[buf], (acc_ph >> buf) & 1u, abortp)) { ok = false; break; }
+        acc_ph ^= 1u << buf;
+        tc_fence_after_sync();
+        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + col_base;
+#pragma unroll
+        for (int g = 0; g < NC / 32; ++g) {
+          float v[32];
+          tmem_ld_32x32(t_addr + g * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[g * 32 + j] += v[j];
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&acc_empty_bar[buf]);
+      }
+      if (!ok) break;
       const int row = tm * BM + q * 32 + lane;
-      const int n0 = tn * BN;
-      const size_t row_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
-      float* crow = p.C + row_off;
-      float* zrow = p.Z ? p.Z + row_off : nullptr;
-      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;  // warp-uniform
-        float v[32];
-        tmem_ld_32x32(t_addr + c * 32, v);
-        tmem_ld_wait();
-        if (row < p.M) {
-          if (p.vec_ok && col0 + 32 <= p.N) {
+      const int n0 = tn * BN + col_base;
+      if (row < p.M) {
+        const size_t row_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
+        float* crow = p.C + row_off;
+        float* zrow = p.Z ? p.Z + row_off : nullptr;
+        if (p.vec_ok && n0 + NC <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 o;
-              o.x = p.alpha * v[4 * j + 0];
-              o.y = p.alpha * v[4 * j + 1];
-              o.z = p.alpha * v[4 * j + 2];
-              o.w = p.alpha * v[4 * j + 3];
-              if (p.beta != 0.0f) {
-                const float4 cin = *reinterpret_cast<const float4*>(crow + col0 + 4 * j);
-                o.x = fmaf(p.beta, cin.x, o.x);
-                o.y = fmaf(p.beta, cin.y, o.y);
-                o.z = fmaf(p.beta, cin.z, o.z);
-                o.w = fmaf(p.beta, cin.w, o.w);
-              }
-              if (p.bias) {
-                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + 4 * j));
-                o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
-              }
-              if (zrow) *reinterpret_cast<float4*>(zrow + col0 + 4 * j) = o;
-              if (p.act != ACT_IDENTITY) {
-                o.x = act_forward(p.act, o.x);
-                o.y = act_forward(p.act, o.y);
-                o.z = act_forward(p.act, o.z);
-                o.w = act_forward(p.act, o.w);
-              }
-              *reinterpret_cast<float4*>(crow + col0 + 4 * j) = o;
+          for (int j = 0; j < NC / 4; ++j) {
+            const int col = n0 + 4 * j;
+            float4 o;
+            o.x = p.alpha * acc[4 * j + 0];
+            o.y = p.alpha * acc[4 * j + 1];
+            o.z = p.alpha * acc[4 * j + 2];
+            o.w = p.alpha * acc[4 * j + 3];
+            if (p.beta != 0.0f) {
+              const float4 cin = *reinterpret_cast<const float4*>(crow + col);
+              o.x = fmaf(p.beta, cin.x, o.x);
+              o.y = fmaf(p.beta, cin.y, o.y);
+              o.z = fmaf(p.beta, cin.z, o.z);
+              o.w = fmaf(p.beta, cin.w, o.w);
             }
-          } else {
+            if (p.bias) {
+              const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+              o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+            }
+            if (zrow) *reinterpret_cast<float4*>(zrow + col) = o;
+            if (p.act != ACT_IDENTITY) {
+              o.x = act_forward(p.act, o.x);
+              o.y = act_forward(p.act, o.y);
+              o.z = act_forward(p.act, o.z);
+              o.w = act_forward(p.act, o.w);
+            }
+            *reinterpret_cast<float4*>(crow + col) = o;
+            asm volatile("" ::: "memory");   // keep the loads of later columns from piling up in registers
+          }
+        } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = col0 + j;
-              if (col < p.N) {
-                float o = p.alpha * v[j];
-                if (p.beta != 0.0f) o = fmaf(p.beta, crow[col], o);
-                if (p.bias) o += __ldg(p.bias + col);
-                if (zrow) zrow[col] = o;
-                crow[col] = act_forward(p.act, o);
-              }
+          for (int j = 0; j < NC; ++j) {
+            const int col = n0 + j;
+            if (col < p.N) {
+              float o = p.alpha * acc[j];
+              if (p.beta != 0.0f) o = fmaf(p.beta, crow[col], o);
+              if (p.bias) o += __ldg(p.bias + col);
+              if (zrow) zrow[col] = o;
+              crow[col] = act_forward(p.act, o);
             }
+            asm volatile("" ::: "memory");
           }
         }
       }
-      tc_fence_before_sync();
-      mbar_arrive(&acc_empty_bar[buf]);
     }
   } else if (T::SPLIT) {
     // ------------------------------------------------------------------ hi / lo split
-    const int tid = threadIdx.x - 192;
+    reg_dealloc<T::REGS_SPLIT>();
+    const int tid = threadIdx.x - T::SPLIT_THREAD0;
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -309,7 +350,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait(&full_bar[s], ph, abortp)) { ok = false; break; }
         uint8_t* raw = ring + s * T::STAGE_BYTES;
-#pragma unroll
+#pragma unroll 4
         for (int i = tid; i < T::RAW_BYTES / 16; i += T::N_SPLIT_THREADS) {
           float4 x = *reinterpret_cast<const float4*>(raw + i * 16);
           uint4 hi, lo;

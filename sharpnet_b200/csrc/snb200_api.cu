@@ -16,7 +16,7 @@
 using namespace snb;
 
 // ------------------------------------------------------------------------------------ handle
-enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_COUNT = 8 };
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_COUNT = 8 };
 
 struct snb200_context {
   int device;
@@ -99,6 +99,7 @@ extern "C" int snb200_create(snb200_handle_t* handle, int device_id) {
   h->stream = 0;
   h->math_mode = SNB200_MATH_3XTF32;
   h->tune[TUNE_REWRITE_HI] = 0;
+  h->tune[TUNE_CHUNK_K] = 128;
   const char* env = getenv("SNB200_MATH_MODE");
   if (env && env[0] >= '0' && env[0] <= '2' && env[1] == 0) h->math_mode = env[0] - '0';
   h->workspace_floats = 1u << 20;
@@ -221,6 +222,10 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g) {
   p.tiles_m = (g.M + T::BM - 1) / T::BM;
   p.tiles_n = (g.N + T::BN - 1) / T::BN;
   p.k_blocks = (g.K + T::BK - 1) / T::BK;
+  // 3xTF32 moves the running sum out of the truncating tensor-core accumulator every `chunk` of K.
+  int chunk_k = T::SPLIT ? h->tune[TUNE_CHUNK_K] : 0;
+  p.chunk_kblocks = chunk_k > 0 ? (chunk_k + T::BK - 1) / T::BK : p.k_blocks;
+  if (p.chunk_kblocks < 1) p.chunk_kblocks = 1;
   p.a_mn = g.transA ? 1 : 0;
   p.b_mn = g.transB ? 0 : 1;
   p.ldc = g.ldc; p.strideC = g.strideC;
