@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the Tensor.Dot / Dense path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-shapes] [--no-cpu]
+  (N > 1: launched by torch.distributed.run, one rank per GPU)
+
+A step is one forward + backward pass of the 3-layer MLP of BASELINE config 5
+(batch 65536, 4096 -> 4096 -> 4096 -> 1000, ReLU, ReLU, identity; Glorot weights, zero biases,
+x ~ N(0,1), upstream gradient ~ N(0,1)) through snb200_dense_fwd / snb200_dense_bwd, the batch rows
+sharded over the N GPUs and the weight / bias gradients summed with one all-reduce per layer.
+`value` is algorithmic TFLOP/s of the whole job (12.61 TFLOP per step), timed on the device with
+inputs resident in HBM; `e2e` is the same step driven from pinned HOST buffers (x and the upstream
+gradient copied in, the bias gradients copied out, every step).  `shapes` lists every Dot / batched /
+Dense shape of BASELINE configs 1-5 with its own TFLOP/s, roofline fraction and error vs fp64 (N = 1).
+
+--impl reference times the reference's CPU path (MKL sgemm through the oracle) on a row sample of
+the same step, with every host core.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GLOBAL_BATCH = 65536
+DIMS = (4096, 4096, 4096, 1000)
+CPU_SAMPLE_ROWS = 4096
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "src": "measured"}
+    return {"hbm": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs (read-only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.idx = device_index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        self.p.wait()
+        self.f.flush()
+        rows = [r.strip().split(", ") for r in open(self.f.name) if r.strip()]
+        os.unlink(self.f.name)
+        sm, mx, pw, reasons = [], [], [], set()
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2])); pw.append(float(r[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.strip().lower() == "active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = sorted(s for s, p in zip(sm, pw) if p > 0.5 * max(pw)) or sorted(sm)
+        return {"sm_mhz": busy[len(busy) // 2], "sm_max_mhz": max(mx), "power_w_max": max(pw), "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the CPU path of SharpNet (MKL sgemm), through the oracle
+# ------------------------------------------------------------------------------------------------
+def cpu_step_sample(rows, seed=17):
+    """One forward+backward of the MLP over `rows` batch rows with the CPU oracle; returns a closure."""
+    import numpy as np
+    import torch
+    from oracle import sharpnet_oracle as orc
+    torch.set_num_threads(os.cpu_count())
+    x = orc.normal((rows, DIMS[0]), 0, 1, seed)
+    dy = orc.normal((rows, DIMS[-1]), 0, 1, seed + 1)
+    Ws = [orc.glorot_uniform((DIMS[i + 1], DIMS[i]), 14 + i) for i in range(3)]
+    bs = [np.zeros(DIMS[i + 1], np.float32) for i in range(3)]
+    acts = (orc.ACT_RELU, orc.ACT_RELU, orc.ACT_IDENTITY)
+
+    def step():
+        a = [x]
+        for i in range(3):
+            _, y = orc.dense_forward(a[-1], Ws[i], bs[i], acts[i], orc.W_OUT_IN)
+            a.append(y)
+        g = dy
+        for i in (2, 1, 0):
+            _, dW, db, g = orc.dense_backward(a[i], Ws[i], g, acts[i], a[i + 1], None, 1.0, orc.W_OUT_IN,
+                                              need_dx=(i > 0))
+        return db
+    return step
+
+
+def time_cpu(rows, reps):
+    from sharpnet_b200.data_parallel import mlp_step_flops
+    step = cpu_step_sample(rows)
+    step()
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        step()
+        ts.append(time.perf_counter() - t0)
+    t = sorted(ts)[len(ts) // 2]
+    return mlp_step_flops(rows, DIMS) / t / 1e12, t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from sharpnet_b200.data_parallel import mlp_step_flops
+    step = cpu_step_sample(CPU_SAMPLE_ROWS)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    v = mlp_step_flops(CPU_SAMPLE_ROWS, DIMS) / dt / 1e12
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": "dot_tflops", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"{CPU_SAMPLE_ROWS} of {GLOBAL_BATCH} batch rows per step, MKL sgemm via torch CPU "
+                                   "(SharpNet's C# cannot be built here: no .NET)"},
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "BASELINE config 5: 3-layer MLP training step (Dense fwd+bwd), batch 65536, "
+                        "4096->4096->4096->1000, ReLU, fp32; rows sharded over the GPUs, dW/db all-reduced",
+            "global_batch": GLOBAL_BATCH, "dims": list(DIMS), "parallelism": f"dp{n}",
+            "math_mode": "3xTF32 (fp32-accurate)", "l2": "inputs (>1 GB per operand) exceed the 126 MB L2"}
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def per_shape_table(w, torch, peaks):
+    """TFLOP/s, roofline fraction and error vs fp64 of every Dot / batched shape in BASELINE configs 1-5."""
+    import numpy as np
+    from oracle import sharpnet_oracle as orc
+    from sharpnet_b200 import MATH_3XTF32, MATH_TF32
+    from sharpnet_b200.tensor import GPUTensor
+    flush = torch.empty(L2_BYTES * 2 // 4, dtype=torch.float32, device=w.device)
+    tpeak3 = peaks["bf16_burst"] / 2 / 3
+    out = []
+
+    def one(name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows=64):
+        w.set_math_mode(mode)
+        sa = (batch, K, M) if tA else (batch, M, K)
+        sb = (batch, N, K) if tB else (batch, K, N)
+        A, B, C = GPUTensor(sa, None, w), GPUTensor(sb, None, w), GPUTensor((batch, M, N), None, w)
+        A.storage.uniform_(lo, hi); B.storage.uniform_(lo, hi); C.storage.uniform_(lo, hi)
+        c0 = C.storage.clone()
+        call = (lambda: C.BatchMatrixMultiplication(A, tA, B, tB, 1.0, beta))
+        call()
+        # error vs fp64 on a few output rows of matrix 0 (full-size fp64 on the host would take minutes)
+        rows = min(check_rows, M)
+        a0 = A.storage[: sa[1] * sa[2]].view(sa[1], sa[2]).double()
+        b0 = B.storage[: sb[1] * sb[2]].view(sb[1], sb[2]).double()
+        opa = (a0.t() if tA else a0)[:rows]
+        opb = b0.t() if tB else b0
+        ref = opa @ opb + beta * c0[: M * N].view(M, N)[:rows].double()
+        err = (C.storage[: M * N].view(M, N)[:rows].double() - ref).abs().max().item() / (math.sqrt(K) * hi * hi)
+        C.storage.copy_(c0)
+        ts = []
+        for _ in range(7):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); call(); e1.record(); torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+            if beta != 0:
+                C.storage.copy_(c0)
+        ms = sorted(ts)[len(ts) // 2]
+        flops = 2.0 * M * N * K * batch
+        byts = 4.0 * batch * (M * K + K * N + M * N * (2 if beta != 0 else 1))
+        tf = flops / ms / 1e9
+        gbs = byts / ms / 1e6
+        tens = tpeak3 if mode == MATH_3XTF32 else tpeak3 * 3
+        t_tensor, t_hbm = flops / (tens * 1e12), byts / (peaks["hbm"] * 1e9)
+        bound = "tensor" if t_tensor >= t_hbm else "hbm"
+        frac = max(t_tensor, t_hbm) / (ms * 1e-3)
+        out.append({"shape": name, "mode": "3xTF32" if mode == MATH_3XTF32 else "TF32", "kernel": w.last_kernel(),
+                    "ms": round(ms, 4), "tflops": round(tf, 2), "gbs": round(gbs, 1), "bound": bound,
+                    "roofline_frac": round(frac, 3), "scaled_err_vs_f64": float(f"{err:.3e}")})
+        del A, B, C
+
+    for mode in (MATH_3XTF32, MATH_TF32):
+        one("cfg1 1024x1024x1024 NN", 1024, 1024, 1024, False, False, 0.0, 1, -1, 1, mode)
+        for tA in (False, True):
+            for tB in (False, True):
+                tag = ("T" if tA else "N") + ("T" if tB else "N")
+                one(f"cfg2 2048x1536x768 {tag} beta=1", 2048, 1536, 768, tA, tB, 1.0, 1, -1, 1, mode)
+        for tA in (False, True):
+            for tB in (False, True):
+                tag = ("T" if tA else "N") + ("T" if tB else "N")
+                one(f"cfg2 skinny 32x4096x4096 {tag} beta=1", 32, 4096, 4096, tA, tB, 1.0, 1, -1, 1, mode)
+        one("cfg4a 64x[256x64]x[256x64]^T", 256, 256, 64, False, True, 0.0, 64, -0.1, 0.1, mode)
+        one("cfg4b 256x4096x2048 NN (LSTM gates)", 256, 4096, 2048, False, False, 0.0, 1, -0.1, 0.1, mode)
+        one("cfg5a 16384^3 NN", 16384, 16384, 16384, False, False, 0.0, 1, -1, 1, mode, check_rows=8)
+    w.set_math_mode(MATH_3XTF32)
+    return out
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from sharpnet_b200 import MATH_3XTF32
+    from sharpnet_b200.data_parallel import (MLP_ACTS, DenseStack, GradientAllReduce, mlp_step_flops, shard_rows,
+                                             training_step)
+    from sharpnet_b200.tensor import GPUWrapper
+    from oracle import sharpnet_oracle as orc
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    peaks = _peaks()
+    w = GPUWrapper.FromDeviceId(local)
+    w.set_math_mode(MATH_3XTF32)
+    r0, r1 = shard_rows(GLOBAL_BATCH, world, rank)
+    rows = r1 - r0
+    weights = [orc.glorot_uniform((DIMS[i + 1], DIMS[i]), 14 + i) for i in range(3)]
+    stack = DenseStack(w, rows, DIMS, MLP_ACTS, weights)
+    # synthetic inputs of the named shape, generated on the host and pinned for the e2e leg
+    g = torch.Generator().manual_seed(17 + rank)
+    x_host = torch.randn(rows, DIMS[0], generator=g).pin_memory()
+    dy_host = torch.randn(rows, DIMS[-1], generator=g).pin_memory()
+    stack.x.storage.copy_(x_host.view(-1))
+    stack.dy.storage.copy_(dy_host.view(-1))
+    db_host = [torch.empty(DIMS[i + 1]).pin_memory() for i in range(3)]
+    compute_stream = torch.cuda.default_stream()
+    reducer = None
+    if world > 1:
+        def bcast(b):
+            obj = [b]
+            dist.broadcast_object_list(obj, src=0)
+            return obj[0]
+        reducer = GradientAllReduce(local, world, rank, bcast)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    step = lambda: training_step(stack, reducer, compute_stream)  # noqa: E731
+    for _ in range(max(args.warmup, 3)):
+        step()
+    w.check_device_status()
+
+    # ---- device-resident timing ------------------------------------------------------------
+    sampler = ClockSampler(local)
+    launches0 = w.launch_count()
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    launches = w.launch_count() - launches0
+    w.check_device_status()
+    flops = mlp_step_flops(GLOBAL_BATCH, DIMS)
+    value = flops / ms / 1e9
+
+    # ---- per-kernel timing of the GEMMs inside the step (events around every GEMM launch) ---
+    gemm_ms, gemm_flops = time_gemms_in_step(stack, torch)
+    gemm_ms = max_over_ranks(gemm_ms)
+
+    # ---- end to end: host buffers in, bias gradients out, every step ----------------------
+    def e2e_step():
+        stack.x.storage.copy_(x_host.view(-1), non_blocking=True)
+        stack.dy.storage.copy_(dy_host.view(-1), non_blocking=True)
+        step()
+        for i in range(3):
+            db_host[i].copy_(stack.db[i].storage, non_blocking=True)
+    e2e_step()
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1) / args.steps)
+    h2d = (x_host.numel() + dy_host.numel()) * 4
+    d2h = sum(t.numel() for t in db_host) * 4
+
+    shapes = per_shape_table(w, torch, peaks) if (world == 1 and not args.no_shapes) else None
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, t = time_cpu(CPU_SAMPLE_ROWS, 3)
+        cpu = {"value": v, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{CPU_SAMPLE_ROWS} of {GLOBAL_BATCH} batch rows of the same step, MKL sgemm via torch CPU, "
+                         f"median of 3 ({t:.2f} s each)"}
+    if rank == 0:
+        peak3 = peaks["bf16_sustained"] / 2 / 3
+        achieved = gemm_flops / gemm_ms / 1e9   # per-GPU rate of the GEMM kernel (this rank's shard)
+        line = {
+            "metric": "dot_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world),
+            "clocks": clocks,
+            "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
+                    "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms},
+            "gpu_launches": launches * world,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak3, "unit": "TFLOP/s",
+                         "frac": achieved / peak3, "traffic": None,
+                         "kernel": "umma_gemm_kernel (3xTF32), the 8 GEMM launches of the step",
+                         "peak_source": f"{peaks['src']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32) / 3 "
+                                        "(three TF32 products per fp32 product); flops counted once (2*M*N*K)",
+                         "gemm_ms_per_step": gemm_ms},
+            "cpu_baseline": cpu,
+        }
+        if shapes is not None:
+            line["shapes"] = shapes
+        print(json.dumps(line), flush=True)
+    if reducer is not None:
+        reducer.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def time_gemms_in_step(stack, torch):
+    """Runs one step with a CUDA-event pair around every GEMM-carrying call on the launching stream;
+    returns (sum of GEMM ms, algorithmic GEMM flops of this rank's shard)."""
+    from sharpnet_b200._capi import check
+    lib, h = stack.w.lib, stack.w.handle
+    pairs = []
+
+    def timed(fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        pairs.append((a, b))
+    B, d = stack.batch, stack.dims
+    flops = 0.0
+    src = stack.x
+    for i in range(3):
+        timed(lambda i=i, src=src: check(h, lib.snb200_dense_fwd(h, stack.layout, B, d[i], d[i + 1], src.Pointer,
+              stack.W[i].Pointer, stack.b[i].Pointer, stack.acts[i], None, stack.y[i].Pointer)))
+        flops += 2.0 * B * d[i] * d[i + 1]
+        src = stack.y[i]
+    # backward GEMMs through the plain gemm entry point on the dz the last step left behind
+    grad = stack.dy
+    for i in (2, 1, 0):
+        src = stack.x if i == 0 else stack.y[i - 1]
+        dz = stack.dz[i] if stack.dz[i] is not None else grad
+        timed(lambda i=i, dz=dz, src=src: check(h, lib.snb200_gemm(h, 1, 0, B, d[i + 1], B, d[i], 1.0, dz.Pointer,
+              src.Pointer, 0.0, stack.dW[i].Pointer)))
+        flops += 2.0 * B * d[i] * d[i + 1]
+        if i > 0:
+            timed(lambda i=i, dz=dz: check(h, lib.snb200_gemm(h, 0, 0, B, d[i + 1], d[i + 1], d[i], 1.0, dz.Pointer,
+                  stack.W[i].Pointer, 0.0, stack.dx[i].Pointer)))
+            flops += 2.0 * B * d[i] * d[i + 1]
+            grad = stack.dx[i]
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in pairs), flops
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape table (N = 1 only)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,152 @@
+"""Data-parallel Dense training step: the host logic of SharpNet's multi-GPU support for the
+Dense path, one process (or thread) per GPU.
+
+SharpNet splits every mini-batch by rows among its workers -- worker 0 (the master) takes rows
+[0, b), worker 1+i takes rows [(1+i)*b, (2+i)*b) (Prod/Networks/Network.cs:1121-1123,1229-1258) --
+runs forward and backward on each replica, then SUMS the gradients of all replicas on the master
+(Prod/Networks/NetworkMultiGPUSupport.cs:161-173) and divides by the global batch in the optimizer
+(Prod/Optimizers/Optimizer.cs:26-29).  Here the sum is one all-reduce per layer over NVLink, issued
+on a side stream as soon as that layer's dW is produced so that it overlaps the remaining backward
+GEMMs; every replica ends the step with the same summed gradients.
+
+Nothing in this file computes: the arithmetic is the C ABI's (GEMMs, fused Dense passes, NCCL).
+"""
+from . import _capi
+from ._capi import ACT_IDENTITY, ACT_RELU, W_OUT_IN, check
+from .tensor import GPUTensor, GPUWrapper
+
+
+def shard_rows(global_batch, world_size, rank):
+    """Row range [start, stop) of ``rank``: contiguous blocks in rank order, as the reference slices
+    the mini-batch (Prod/Networks/Network.cs:1233,1243).  The batch must be a multiple of the
+    number of workers (:1121-1122)."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError(f"bad rank {rank} of {world_size}")
+    if global_batch % world_size != 0:
+        raise ValueError("the mini-batch size must be a multiple of the number of workers")
+    b = global_batch // world_size
+    return rank * b, (rank + 1) * b
+
+
+def mlp_step_flops(global_batch, dims):
+    """Algorithmic flops of one forward+backward step of a Dense stack ``dims[0] -> ... -> dims[-1]``
+    over the whole batch: forward and dW for every layer, dx for every layer but the first
+    (Prod/Layers/Linear.cs:184-187)."""
+    pairs = list(zip(dims[:-1], dims[1:]))
+    fwd = sum(2 * global_batch * i * o for i, o in pairs)
+    dx = sum(2 * global_batch * i * o for i, o in pairs[1:])
+    return fwd + fwd + dx
+
+
+class DenseStack:
+    """A stack of Dense layers with fused activations on one GPU: the buffers one replica needs for
+    forward + backward, allocated once (the role of PropagationManager + TensorMemoryPool,
+    Prod/Networks/PropagationManager.cs:46-145)."""
+
+    def __init__(self, wrapper, local_batch, dims, activations, weights=None, w_layout=W_OUT_IN):
+        assert len(activations) == len(dims) - 1
+        self.w = wrapper
+        self.batch = local_batch
+        self.dims = list(dims)
+        self.acts = list(activations)
+        self.layout = w_layout
+        n = len(dims) - 1
+        shape = (lambda i: (dims[i + 1], dims[i])) if w_layout == W_OUT_IN else (lambda i: (dims[i], dims[i + 1]))
+        self.W = [GPUTensor(shape(i), None if weights is None else weights[i], wrapper) for i in range(n)]
+        self.b = [GPUTensor((dims[i + 1],), None, wrapper) for i in range(n)]
+        self.dW = [GPUTensor(shape(i), None, wrapper) for i in range(n)]
+        self.db = [GPUTensor((dims[i + 1],), None, wrapper) for i in range(n)]
+        self.x = GPUTensor((local_batch, dims[0]), None, wrapper)
+        self.y = [GPUTensor((local_batch, dims[i + 1]), None, wrapper) for i in range(n)]
+        # dz scratch per activated layer, gradient w.r.t. each hidden activation
+        self.dz = [None if activations[i] == ACT_IDENTITY else GPUTensor((local_batch, dims[i + 1]), None, wrapper)
+                   for i in range(n)]
+        self.dx = [None] + [GPUTensor((local_batch, dims[i]), None, wrapper) for i in range(1, n)]
+        self.dy = GPUTensor((local_batch, dims[-1]), None, wrapper)
+
+    def forward(self):
+        lib, h = self.w.lib, self.w.handle
+        src = self.x
+        for i, W in enumerate(self.W):
+            st = lib.snb200_dense_fwd(h, self.layout, self.batch, self.dims[i], self.dims[i + 1], src.Pointer,
+                                      W.Pointer, self.b[i].Pointer, self.acts[i], None, self.y[i].Pointer)
+            check(h, st)
+            src = self.y[i]
+
+    def backward(self, after_layer=None):
+        """Backward through every layer, last to first.  ``after_layer(i)`` is called right after the
+        gradients of layer ``i`` have been queued (the hook the gradient all-reduce hangs on)."""
+        lib, h = self.w.lib, self.w.handle
+        grad = self.dy
+        for i in reversed(range(len(self.W))):
+            src = self.x if i == 0 else self.y[i - 1]
+            st = lib.snb200_dense_bwd(
+                h, self.layout, self.batch, self.dims[i], self.dims[i + 1], src.Pointer, self.W[i].Pointer,
+                grad.Pointer, self.acts[i], None if self.acts[i] == ACT_IDENTITY else self.y[i].Pointer, None, 1.0,
+                None if self.dz[i] is None else self.dz[i].Pointer, None if i == 0 else self.dx[i].Pointer,
+                self.dW[i].Pointer, self.db[i].Pointer)
+            check(h, st)
+            if after_layer is not None:
+                after_layer(i)
+            grad = self.dx[i]
+
+
+class GradientAllReduce:
+    """Sums dW and db of every layer over all replicas with NCCL, on a side stream.
+
+    One process per GPU: rank 0 creates the NCCL id and ``broadcast_bytes`` (any callable that
+    ships 128 bytes from rank 0 to everyone, e.g. built on torch.distributed) distributes it."""
+
+    def __init__(self, device_id, world_size, rank, broadcast_bytes):
+        import ctypes
+        import torch
+        self.torch = torch
+        self.world = world_size
+        self.comm_wrapper = GPUWrapper(device_id)          # a second handle: owns the communicator and its stream
+        self.stream = torch.cuda.Stream(device=device_id)
+        self.comm_wrapper.set_stream(self.stream)
+        lib = _capi.load()
+        ident = ctypes.create_string_buffer(128)
+        if rank == 0:
+            st = lib.snb200_comm_get_unique_id(ident)
+            if st != 0:
+                raise _capi.SharpNetB200Error(st, "NCCL could not be loaded")
+        ident = ctypes.create_string_buffer(broadcast_bytes(bytes(ident.raw)), 128)
+        check(self.comm_wrapper.handle,
+              lib.snb200_comm_init_rank(self.comm_wrapper.handle, world_size, rank, ident))
+
+    def reduce_layer(self, stack, i, compute_stream):
+        """Queues the all-reduce of layer ``i``'s gradients behind the work already on ``compute_stream``."""
+        ev = self.torch.cuda.Event()
+        ev.record(compute_stream)
+        self.stream.wait_event(ev)
+        lib, h = self.comm_wrapper.lib, self.comm_wrapper.handle
+        check(h, lib.snb200_allreduce_sum(h, stack.dW[i].Pointer, stack.dW[i].Count))
+        check(h, lib.snb200_allreduce_sum(h, stack.db[i].Pointer, stack.db[i].Count))
+
+    def join(self, compute_stream):
+        """Makes ``compute_stream`` wait for every queued all-reduce."""
+        ev = self.torch.cuda.Event()
+        ev.record(self.stream)
+        compute_stream.wait_event(ev)
+
+    def close(self):
+        lib = self.comm_wrapper.lib
+        lib.snb200_comm_destroy(self.comm_wrapper.handle)
+        lib.snb200_destroy(self.comm_wrapper.handle)
+        self.comm_wrapper.handle = None
+
+
+def training_step(stack, reducer=None, compute_stream=None):
+    """One forward + backward of ``stack`` on this replica's rows, with the per-layer gradient
+    all-reduce overlapped when ``reducer`` is given."""
+    stack.forward()
+    if reducer is None:
+        stack.backward()
+        return
+    stack.backward(after_layer=lambda i: reducer.reduce_layer(stack, i, compute_stream))
+    reducer.join(compute_stream)
+
+
+MLP_DIMS = (4096, 4096, 4096, 1000)
+MLP_ACTS = (ACT_RELU, ACT_RELU, ACT_IDENTITY)

@@ -141,10 +141,10 @@ class GPUTensor:
     def Dot(self, a, transposeA=False, b=None, transposeB=False, alpha=1.0, beta=0.0):
         """this = alpha * op(a) * op(b) + beta * this   (Prod/Data/Tensor.cs:388-397;
         GPU: Prod/GPU/GpuTensor.cs:1196-1227).  ``Dot(a, b)`` is the convenience form of Tensor.cs:60."""
+        if isinstance(transposeA, GPUTensor):   # Dot(a, b)
+            b, transposeA = transposeA, False
         if b is None:
             raise TypeError("Dot needs two operands")
-        if isinstance(transposeA, GPUTensor):   # Dot(a, b)
-            a, b, transposeA = a, transposeA, False
         w = self.wrapper
         st = w.lib.snb200_gemm(w.handle, int(bool(transposeA)), int(bool(transposeB)), a.Shape[0], a.MultDim0,
                                b.Shape[0], b.MultDim0, float(alpha), a.Pointer, b.Pointer, float(beta), self.Pointer)

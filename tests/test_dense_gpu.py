@@ -1,0 +1,207 @@
+"""Parity of the Dense-layer entry points (snb200_dense_fwd / snb200_dense_bwd and the companions
+behind BroadcastAddVectorToOutput, Compute_BiasGradient_from_dy, ActivationForward/Backward,
+Update_Adding_Alpha_X) against the CPU oracle, on a B200."""
+import numpy as np
+import pytest
+
+from oracle import sharpnet_oracle as orc
+from sharpnet_b200 import (ACT_IDENTITY, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH, MATH_3XTF32, MATH_TF32, W_IN_OUT,
+                           W_OUT_IN)
+from sharpnet_b200._capi import TUNE_FORCE_PATH
+from sharpnet_b200.linear import (DenseBackwardPropagation, DenseForwardPropagation, FusedDenseBackward,
+                                  FusedDenseForward)
+from sharpnet_b200.tensor import GPUTensor
+
+from gpu_util import TOL_3XTF32, TOL_TF32
+
+pytestmark = pytest.mark.gpu
+ACTS = [ACT_IDENTITY, ACT_RELU, ACT_SWISH, ACT_TANH, ACT_SIGMOID]
+
+
+@pytest.fixture(autouse=True)
+def _reset(wrapper):
+    wrapper.set_math_mode(MATH_3XTF32)
+    wrapper.set_tuning(TUNE_FORCE_PATH, 0)
+    yield
+    wrapper.set_math_mode(MATH_3XTF32)
+    wrapper.set_tuning(TUNE_FORCE_PATH, 0)
+
+
+def _t(w, arr):
+    return GPUTensor(arr.shape, arr, w)
+
+
+def test_golden_keras_layout_predictions(wrapper, golden):
+    # Tests/NonReg/TestNetworkPropagation.cs:80-132: Linear(3) + Sigmoid, weights [in, out], 1e-6
+    W = np.asarray(golden["W_N_1_4_4"], np.float32).reshape(16, 3)
+    for key, rows in (("1_1_4_4", 1), ("2_1_4_4", 2)):
+        x = np.asarray(golden["X_" + key], np.float32).reshape(rows, 1, 4, 4)
+        y = GPUTensor((rows, 3), None, wrapper)
+        FusedDenseForward(y, _t(wrapper, x), _t(wrapper, W), _t(wrapper, np.zeros(3, np.float32)), ACT_SIGMOID,
+                          w_layout=W_IN_OUT)
+        np.testing.assert_allclose(y.ContentAsFloatArray().ravel(), golden[f"sigmoid_{key}_pred"], rtol=0, atol=1e-6)
+
+
+def test_golden_pytorch_layout_networks(wrapper, golden):
+    # Tests/NonReg/ParallelRunWithPyTorch.cs:179-214 (BCE 0.67267912...) through the unfused call
+    # sequence of Linear.cs + ActivationLayer.cs, and :102-138 (Mse 0.29795372...) through the fused one.
+    x = _t(wrapper, orc.numpy_array_for_tests(2, 1, 4, 4))
+    w1 = _t(wrapper, np.asarray(golden["pt_relu_w1"], np.float32).reshape(3, 16))
+    w2 = _t(wrapper, np.asarray(golden["pt_relu_w2"], np.float32).reshape(3, 3))
+    zeros = _t(wrapper, np.zeros(3, np.float32))
+    h, ha = GPUTensor((2, 3), None, wrapper), GPUTensor((2, 3), None, wrapper)
+    p, pa = GPUTensor((2, 3), None, wrapper), GPUTensor((2, 3), None, wrapper)
+    DenseForwardPropagation(h, x, w1, zeros)
+    h.ActivationForward(ACT_RELU, None, ha)
+    DenseForwardPropagation(p, ha, w2, zeros)
+    p.ActivationForward(ACT_SIGMOID, None, pa)
+    loss = orc.binary_crossentropy(orc.y_numpy_array_for_tests(2, 3), pa.ContentAsFloatArray())
+    assert abs(loss - golden["pt_relu_loss_before"]) < 1e-6
+
+    x = _t(wrapper, orc.numpy_array_for_tests(2, 3, 4, 5))
+    w1 = _t(wrapper, np.asarray(golden["pt_mse_w1"], np.float32).reshape(3, 5))
+    w2 = _t(wrapper, np.asarray(golden["pt_mse_w2"], np.float32).reshape(3, 36))
+    h = GPUTensor((2, 3, 4, 3), None, wrapper)
+    FusedDenseForward(h, x, w1, zeros, ACT_RELU, flattenInputTensorOnLastDimension=True)
+    p = GPUTensor((2, 3), None, wrapper)
+    FusedDenseForward(p, h.Reshape(2, 36), w2, zeros, ACT_IDENTITY)
+    loss = orc.mse(orc.y_numpy_array_for_tests(2, 3), p.ContentAsFloatArray())
+    assert abs(loss - golden["pt_mse_loss_before"]) < 1e-6
+
+
+def _dense_case(wrapper, M, K, N, act, layout, seed, tol, with_bias=True, need_dx=True, mult=1.0):
+    x = orc.normal((M, K), 0, 1, seed)
+    Wl = orc.glorot_uniform((N, K) if layout == W_OUT_IN else (K, N), seed + 1)
+    b = orc.uniform((N,), -0.5, 0.5, seed + 2) if with_bias else None
+    dy = orc.normal((M, N), 0, 1, seed + 3)
+    wmax = float(np.abs(Wl).max())
+    X, W, DY = _t(wrapper, x), _t(wrapper, Wl), _t(wrapper, dy)
+    B = _t(wrapper, b) if with_bias else None
+    Y, Z = GPUTensor((M, N), None, wrapper), GPUTensor((M, N), None, wrapper)
+    FusedDenseForward(Y, X, W, B, act, z=Z, w_layout=layout)
+    wrapper.check_device_status()
+    z64, y64 = orc.dense_forward(x, Wl, b, act, layout, f64=True)
+    zm, ym = orc.dense_forward(x, Wl, b, act, layout)
+    y, z = Y.ContentAsFloatArray(), Z.ContentAsFloatArray()
+    for got, r64, rm in ((z, z64, zm), (y, y64, ym)):
+        assert orc.scaled_error(got, r64, K, 4.0, wmax) <= tol
+        assert orc.scaled_error(got, rm, K, 4.0, wmax) <= tol
+    # backward, from the GPU's own y / z (what the layer would have kept)
+    DZ = GPUTensor((M, N), None, wrapper)
+    DX = GPUTensor((M, K), None, wrapper) if need_dx else None
+    DW = GPUTensor(Wl.shape, None, wrapper)
+    DB = GPUTensor((N,), None, wrapper) if with_bias else None
+    FusedDenseBackward(DX, DW, DB, X, DY, W, act, y=Y, z=Z, multiplier=mult, dz_scratch=DZ, w_layout=layout)
+    wrapper.check_device_status()
+    dz64, dW64, db64, dx64 = orc.dense_backward(x, Wl, dy, act, y, z, mult, layout, need_dx, f64=True)
+    dzm, dWm, dbm, dxm = orc.dense_backward(x, Wl, dy, act, y, z, mult, layout, need_dx)
+    if act != ACT_IDENTITY:
+        np.testing.assert_allclose(DZ.ContentAsFloatArray(), dzm, rtol=2e-6, atol=1e-6)
+    gmax = 4.0 * 1.2  # |dz| <= |dy| * max|act'| (1.1 for Swish)
+    assert orc.scaled_error(DW.ContentAsFloatArray(), dW64, M, 4.0, gmax) <= tol * max(1.0, abs(mult))
+    assert orc.scaled_error(DW.ContentAsFloatArray(), dWm, M, 4.0, gmax) <= tol * max(1.0, abs(mult))
+    if with_bias:
+        assert orc.scaled_error(DB.ContentAsFloatArray(), db64, M, 1.0, gmax) <= TOL_3XTF32
+        assert orc.scaled_error(DB.ContentAsFloatArray(), dbm, M, 1.0, gmax) <= TOL_3XTF32
+    if need_dx:
+        assert orc.scaled_error(DX.ContentAsFloatArray(), dx64, N, gmax, wmax) <= tol
+        assert orc.scaled_error(DX.ContentAsFloatArray(), dxm, N, gmax, wmax) <= tol
+
+
+@pytest.mark.parametrize("act", ACTS)
+@pytest.mark.parametrize("layout", [W_OUT_IN, W_IN_OUT])
+def test_dense_fwd_bwd_small_simt(wrapper, act, layout):
+    _dense_case(wrapper, 9, 21, 5, act, layout, 40 + act, TOL_3XTF32)
+    _dense_case(wrapper, 33, 7, 3, act, layout, 60 + act, TOL_3XTF32, with_bias=False, need_dx=False, mult=1.0 / 33)
+
+
+@pytest.mark.parametrize("act", ACTS)
+@pytest.mark.parametrize("layout", [W_OUT_IN, W_IN_OUT])
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+def test_dense_fwd_bwd_tensor_core(wrapper, act, layout, mode, tol):
+    wrapper.set_math_mode(mode)
+    _dense_case(wrapper, 512, 384, 256, act, layout, 80 + act, tol)
+    assert wrapper.last_kernel().startswith("umma")
+    _dense_case(wrapper, 300, 200, 136, act, layout, 90 + act, tol, mult=1.0 / 300)
+
+
+@pytest.mark.parametrize("act", [ACT_RELU, ACT_SWISH])
+@pytest.mark.parametrize("layout", [W_IN_OUT, W_OUT_IN])
+def test_config_3_dense_4096x3072x1024(wrapper, act, layout):
+    # BASELINE config 3: x[4096x3072] N(0,1), W Glorot, dy N(0,1); bias drawn non-zero to exercise the add
+    _dense_case(wrapper, 4096, 3072, 1024, act, layout, 6, TOL_3XTF32)
+
+
+def test_unfused_sequence_matches_fused(wrapper):
+    # Linear.cs call sequence (Dot, bias add, activation; activation backward, Dot, bias gradient, Dot)
+    # against the fused entry points on the same inputs
+    M, K, N = 256, 192, 128
+    x, Wl = orc.normal((M, K), 0, 1, 1), orc.glorot_uniform((N, K), 2)
+    b, dy = orc.uniform((N,), -0.5, 0.5, 3), orc.normal((M, N), 0, 1, 4)
+    X, W, B, DY = (_t(wrapper, v) for v in (x, Wl, b, dy))
+    for act in ACTS:
+        z1, y1 = GPUTensor((M, N), None, wrapper), GPUTensor((M, N), None, wrapper)
+        DenseForwardPropagation(z1, X, W, B)
+        z1.ActivationForward(act, None, y1)
+        z2, y2 = GPUTensor((M, N), None, wrapper), GPUTensor((M, N), None, wrapper)
+        FusedDenseForward(y2, X, W, B, act, z=z2)
+        np.testing.assert_array_equal(z1.ContentAsFloatArray(), z2.ContentAsFloatArray())
+        np.testing.assert_array_equal(y1.ContentAsFloatArray(), y2.ContentAsFloatArray())
+        dz1 = GPUTensor((M, N), None, wrapper)
+        dz1.ActivationBackward(act, None, DY, z1, y1)
+        dx1, dW1, db1 = GPUTensor((M, K), None, wrapper), GPUTensor((N, K), None, wrapper), GPUTensor((N,), None, wrapper)
+        DenseBackwardPropagation(dx1, dW1, db1, X, dz1, W, multiplier=0.5)
+        dz2 = GPUTensor((M, N), None, wrapper)
+        dx2, dW2, db2 = GPUTensor((M, K), None, wrapper), GPUTensor((N, K), None, wrapper), GPUTensor((N,), None, wrapper)
+        FusedDenseBackward(dx2, dW2, db2, X, DY, W, act, y=y2, z=z2, multiplier=0.5, dz_scratch=dz2)
+        np.testing.assert_array_equal(dW1.ContentAsFloatArray(), dW2.ContentAsFloatArray())
+        np.testing.assert_array_equal(dx1.ContentAsFloatArray(), dx2.ContentAsFloatArray())
+        np.testing.assert_allclose(db1.ContentAsFloatArray(), db2.ContentAsFloatArray(), rtol=0, atol=1e-4)
+
+
+def test_bias_add_and_bias_gradient(wrapper):
+    # Tests/TestParallelRunCpuVersusGpu.cs:730-736 (9 x 1632) and :938-944, plus odd and tall shapes
+    for (M, N) in ((9, 1632), (1, 1), (3, 7), (4096, 1024), (1000, 333), (70000, 8)):
+        dy = orc.uniform((M, N), -1.5, 1.5, M + N)
+        bias = orc.uniform((N,), -1.5, 1.5, M)
+        DB = GPUTensor((N,), None, wrapper)
+        _t(wrapper, dy).Compute_BiasGradient_from_dy(DB)
+        ref64 = dy.astype(np.float64).sum(0)
+        assert np.max(np.abs(DB.ContentAsFloatArray() - ref64)) <= 1e-5 * np.sqrt(M) * 1.5 + 1e-6
+        if M <= 4096:
+            assert np.max(np.abs(DB.ContentAsFloatArray() - orc.compute_bias_gradient_from_dy(dy))) <= 1e-2
+        Y = _t(wrapper, dy)
+        _t(wrapper, bias).BroadcastAddVectorToOutput(Y)
+        np.testing.assert_array_equal(Y.ContentAsFloatArray(), orc.broadcast_add_vector_to_output(bias, dy.copy()))
+
+
+def test_activations_and_axpy(wrapper):
+    # Tests/TestParallelRunCpuVersusGpu.cs:759-835 shapes; fp32 device math vs the double-precision host formulas
+    for shape in ((1, 1), (5, 3), (2, 3, 4, 5), (1000, 257)):
+        x = orc.uniform(shape, -1.5, 1.5, 7)
+        x.ravel()[0] = 5e-5   # inside the |x| < 1e-4 branch of the Swish gradient
+        dy = orc.uniform(shape, -1.5, 1.5, 8)
+        X, DY = _t(wrapper, x), _t(wrapper, dy)
+        for act in ACTS:
+            Y, DX = GPUTensor(shape, None, wrapper), GPUTensor(shape, None, wrapper)
+            X.ActivationForward(act, None, Y)
+            y = Y.ContentAsFloatArray()
+            np.testing.assert_allclose(y, orc.activation_forward(act, x), rtol=1e-6, atol=1e-7)
+            DX.ActivationBackward(act, None, DY, X, Y)
+            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y), rtol=2e-6,
+                                       atol=1e-6)
+        Yv = _t(wrapper, dy)
+        Yv.Update_Adding_Alpha_X(0.25, X)
+        np.testing.assert_allclose(Yv.ContentAsFloatArray(), orc.update_adding_alpha_x(dy.copy(), 0.25, x), rtol=0,
+                                   atol=1e-7)
+
+
+def test_dense_argument_errors(wrapper):
+    lib, h = wrapper.lib, wrapper.handle
+    T = GPUTensor((4, 4), None, wrapper)
+    assert lib.snb200_dense_fwd(h, 2, 4, 4, 4, T.Pointer, T.Pointer, None, ACT_RELU, None, T.Pointer) == 7
+    assert lib.snb200_dense_fwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, None, 4, None, T.Pointer) == 15   # ELU not fused
+    # Swish backward without the pre-activation
+    assert lib.snb200_dense_bwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, T.Pointer, ACT_SWISH, T.Pointer, None, 1.0,
+                                T.Pointer, None, T.Pointer, None) == 7
+    assert b"pre-activation" in lib.snb200_last_error_string(h)

@@ -1,0 +1,243 @@
+"""Parity of snb200_gemm / snb200_batched_gemm (through the GPUTensor mirror of Tensor.Dot and
+Tensor.BatchMatrixMultiplication) against the CPU oracle, on a B200."""
+import numpy as np
+import pytest
+
+from oracle import sharpnet_oracle as orc
+from sharpnet_b200 import MATH_3XTF32, MATH_FP32_SIMT, MATH_TF32
+from sharpnet_b200._capi import TUNE_FORCE_BN, TUNE_FORCE_PATH, SharpNetB200Error
+from sharpnet_b200.tensor import GPUTensor
+
+from gpu_util import TOL_3XTF32, TOL_TF32, run_dot
+
+pytestmark = pytest.mark.gpu
+
+MODES = [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32), (MATH_FP32_SIMT, TOL_3XTF32)]
+
+
+@pytest.fixture(autouse=True)
+def _reset(wrapper):
+    wrapper.set_math_mode(MATH_3XTF32)
+    wrapper.set_tuning(TUNE_FORCE_PATH, 0)
+    wrapper.set_tuning(TUNE_FORCE_BN, 0)
+    yield
+    wrapper.set_math_mode(MATH_3XTF32)
+    wrapper.set_tuning(TUNE_FORCE_PATH, 0)
+    wrapper.set_tuning(TUNE_FORCE_BN, 0)
+
+
+def _check(w, M, N, K, tA, tB, alpha, beta, seed, tol, lo=-1.0, hi=1.0, batch=None):
+    got, mkl, f64 = run_dot(w, M, N, K, tA, tB, alpha, beta, seed, lo, hi, batch)
+    amax = max(abs(lo), abs(hi))
+    scale = abs(alpha) if alpha != 0 else 1.0
+    e64 = orc.scaled_error(got, f64, K, amax, amax) / scale
+    emkl = orc.scaled_error(got, mkl, K, amax, amax) / scale
+    assert e64 <= tol and emkl <= tol, (w.last_kernel(), M, N, K, tA, tB, e64, emkl)
+    return e64
+
+
+def test_reference_exact_cases(wrapper, golden):
+    # Tests/GPU/TestGpuTensor.cs:50-120 -- small integer matrices, tolerance 1e-9, every math mode
+    for mode, _ in MODES:
+        wrapper.set_math_mode(mode)
+        for case in golden["dot_exact"]:
+            a = GPUTensor(case["a_shape"], case["a"], wrapper)
+            b = GPUTensor(case["b_shape"], case["b"], wrapper)
+            r = GPUTensor(case["expected_shape"], None, wrapper)
+            r.Dot(a, False, b, False, 1, 0)
+            np.testing.assert_allclose(r.ContentAsFloatArray().ravel(), case["expected"], rtol=0, atol=1e-9)
+        for case in golden["dot_exact_zero_cases"]:
+            a = GPUTensor(case["a_shape"], None, wrapper)
+            b = GPUTensor(case["b_shape"], None, wrapper)
+            r = GPUTensor(case["expected_shape"], np.ones(case["expected_shape"], np.float32), wrapper)
+            r.Dot(a, False, b, False, 1, 0)
+            assert not r.ContentAsFloatArray().any()
+
+
+def test_integer_matrices_are_exact_on_tensor_cores(wrapper):
+    # Small integers are exactly representable in TF32: the tensor-core paths must be bit exact.
+    rng = np.random.default_rng(0)
+    a = rng.integers(-8, 9, (128, 64)).astype(np.float32)
+    b = rng.integers(-8, 9, (64, 96)).astype(np.float32)
+    want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    wrapper.set_tuning(TUNE_FORCE_PATH, 1)
+    for mode in (MATH_3XTF32, MATH_TF32):
+        wrapper.set_math_mode(mode)
+        A, B, C = GPUTensor(a.shape, a, wrapper), GPUTensor(b.shape, b, wrapper), GPUTensor((128, 96), None, wrapper)
+        C.Dot(A, B)
+        assert wrapper.last_kernel().startswith("umma")
+        np.testing.assert_array_equal(C.ContentAsFloatArray(), want)
+
+
+def test_differential_cases_of_the_reference(wrapper):
+    # Tests/TestParallelRunCpuVersusGpu.cs:368-375,436-456: 8x10 * 10x12 and 2x20000 * 20000x2,
+    # U[-1.5, 1.5); the reference accepts an absolute error of 1e-2, we hold the scaled bound.
+    for mode, tol in MODES:
+        wrapper.set_math_mode(mode)
+        _check(wrapper, 8, 12, 10, False, False, 1, 0, 1, tol, -1.5, 1.5)
+        _check(wrapper, 2, 2, 20000, False, False, 1, 0, 2, tol, -1.5, 1.5)
+        got, mkl, _ = run_dot(wrapper, 2, 2, 20000, False, False, 1, 0, 2, -1.5, 1.5)
+        if mode != MATH_TF32:
+            assert np.max(np.abs(got - mkl)) < 1e-2
+
+
+def test_batched_cases_of_the_reference(wrapper):
+    # Tests/TestParallelRunCpuVersusGpu.cs:377-401: batch 3, 12x12 / 12x7, (N,T) alpha 0.25, (N,N), (T,N)
+    for mode, tol in MODES:
+        wrapper.set_math_mode(mode)
+        _check(wrapper, 12, 12, 7, False, True, 0.25, 0, 3, tol, -1.5, 1.5, batch=3)
+        _check(wrapper, 12, 7, 12, False, False, 1, 0, 4, tol, -1.5, 1.5, batch=3)
+        _check(wrapper, 12, 7, 12, True, False, 1, 0, 5, tol, -1.5, 1.5, batch=3)
+
+
+@pytest.mark.parametrize("tA", [False, True])
+@pytest.mark.parametrize("tB", [False, True])
+def test_small_shape_sweep_simt(wrapper, tA, tB):
+    # every (M, N, K) in a small grid, beta in {0, 1}; these shapes take the SIMT kernel
+    wrapper.set_math_mode(MATH_3XTF32)
+    seed = 100
+    for M in (1, 2, 3, 5, 17, 40):
+        for N in (1, 2, 7, 33, 40):
+            for K in (1, 2, 9, 31, 40):
+                for beta in (0.0, 1.0):
+                    seed += 1
+                    _check(wrapper, M, N, K, tA, tB, 1.0, beta, seed, TOL_3XTF32, -1.5, 1.5)
+    assert wrapper.last_kernel().startswith("simt")
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+@pytest.mark.parametrize("tA", [False, True])
+@pytest.mark.parametrize("tB", [False, True])
+def test_tensor_core_ragged_shapes(wrapper, mode, tol, tA, tB):
+    # sizes that are not multiples of the tile, every tile width, alpha/beta accumulate
+    wrapper.set_math_mode(mode)
+    wrapper.set_tuning(TUNE_FORCE_PATH, 1)
+    seed = 500
+    for bn in (32, 64, 128, 256):
+        wrapper.set_tuning(TUNE_FORCE_BN, bn)
+        for (M, N, K) in ((128, 256, 64), (132, 260, 36), (200, 328, 100), (4, 8, 4), (260, 516, 20), (96, 40, 520)):
+            seed += 1
+            _check(wrapper, M, N, K, tA, tB, 0.5, 1.0, seed, tol)
+            assert wrapper.last_kernel().startswith("umma"), wrapper.last_kernel()
+    wrapper.set_tuning(TUNE_FORCE_BN, 0)
+    _check(wrapper, 300, 200, 72, tA, tB, -2.0, 0.0, 999, tol)
+
+
+def test_beta_zero_ignores_nan_in_c(wrapper):
+    # BLAS semantics: with beta = 0 the old content of C is not read
+    rng = np.random.default_rng(9)
+    for force, (M, N, K) in ((2, (9, 11, 13)), (1, (256, 256, 64))):
+        wrapper.set_tuning(TUNE_FORCE_PATH, force)
+        a = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+        b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+        C = GPUTensor((M, N), np.full((M, N), np.nan, np.float32), wrapper)
+        C.Dot(GPUTensor(a.shape, a, wrapper), False, GPUTensor(b.shape, b, wrapper), False, 1, 0)
+        assert np.isfinite(C.ContentAsFloatArray()).all()
+
+
+def test_unaligned_views_fall_back_to_simt(wrapper):
+    # SharpNet slices tensors at 4-byte granularity: a pointer that is not 16-byte aligned must work
+    import torch
+    rng = np.random.default_rng(11)
+    M, N, K = 128, 128, 64
+    a = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    base = torch.zeros(M * K + 1, dtype=torch.float32, device=wrapper.device)
+    base[1:] = torch.from_numpy(a.ravel()).to(wrapper.device)
+    A = GPUTensor((M, K), wrapper=wrapper, storage=base[1:])
+    B = GPUTensor((K, N), b, wrapper)
+    C = GPUTensor((M, N), None, wrapper)
+    wrapper.set_tuning(TUNE_FORCE_PATH, 1)
+    C.Dot(A, False, B, False, 1, 0)
+    assert wrapper.last_kernel().startswith("simt")
+    ref = orc.dot_f64(a.ravel(), M, K, False, b.ravel(), K, N, False, None, 1.0, 0.0)
+    assert orc.scaled_error(C.ContentAsFloatArray(), ref, K, 1, 1) <= TOL_3XTF32
+
+
+def test_empty_and_invalid_arguments(wrapper):
+    C = GPUTensor((4, 4), np.ones((4, 4), np.float32), wrapper)
+    A = GPUTensor((4, 3), None, wrapper)
+    B = GPUTensor((5, 4), None, wrapper)
+    with pytest.raises(SharpNetB200Error) as e:
+        C.Dot(A, False, B, False, 1, 0)          # inner dimensions 3 vs 5
+    assert e.value.status == 7
+    lib, h = wrapper.lib, wrapper.handle
+    assert lib.snb200_gemm(h, 0, 0, 0, 3, 3, 4, 1.0, None, None, 0.0, None) == 0       # M = 0: nothing to do
+    assert lib.snb200_gemm(h, 0, 0, -1, 3, 3, 4, 1.0, None, None, 0.0, None) == 7
+    assert lib.snb200_gemm(h, 0, 0, 4, 3, 3, 4, 1.0, None, B.Pointer, 0.0, C.Pointer) == 7  # null A
+    # K = 0: C = beta * C
+    A0 = GPUTensor((4, 0), None, wrapper)
+    B0 = GPUTensor((0, 4), None, wrapper)
+    C.Dot(A0, False, B0, False, 1, 2.0)
+    np.testing.assert_array_equal(C.ContentAsFloatArray(), np.full((4, 4), 2.0, np.float32))
+
+
+def test_inputs_may_alias(wrapper):
+    # VanillaSgdOrtho computes Dot(W, false, W, true, ...) (Prod/Optimizers/VanillaSgdOrtho.cs:83)
+    rng = np.random.default_rng(13)
+    w_ = rng.uniform(-1, 1, (256, 128)).astype(np.float32)
+    W = GPUTensor(w_.shape, w_, wrapper)
+    C = GPUTensor((256, 256), None, wrapper)
+    C.Dot(W, False, W, True, 1, 0)
+    ref = w_.astype(np.float64) @ w_.astype(np.float64).T
+    # every product on the diagonal is positive, so the sum grows like K, not sqrt(K): bound the relative error
+    assert np.max(np.abs(C.ContentAsFloatArray() - ref)) / np.max(np.abs(ref)) <= TOL_3XTF32
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_config_1_square_1024(wrapper, mode, tol):
+    wrapper.set_math_mode(mode)
+    _check(wrapper, 1024, 1024, 1024, False, False, 1, 0, 0, tol)
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+def test_config_2_four_transposes_beta_one(wrapper, mode, tol):
+    wrapper.set_math_mode(mode)
+    seed = 1
+    for tA in (False, True):
+        for tB in (False, True):
+            _check(wrapper, 2048, 1536, 768, tA, tB, 1, 1, seed, tol)
+            assert wrapper.last_kernel().startswith("umma")
+            _check(wrapper, 32, 4096, 4096, tA, tB, 1, 1, 5, tol)
+            seed += 1
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+def test_config_4_batched_and_lstm_gate(wrapper, mode, tol):
+    wrapper.set_math_mode(mode)
+    # 64 x [256x64] * [256x64]^T, U[-0.1, 0.1), alpha = 1 and 1/sqrt(64)
+    _check(wrapper, 256, 256, 64, False, True, 1.0, 0, 9, tol, -0.1, 0.1, batch=64)
+    _check(wrapper, 256, 256, 64, False, True, 0.125, 0, 9, tol, -0.1, 0.1, batch=64)
+    # LSTM gate GEMM [256 x 2048] * [2048 x 4096] as Dot and as a batch of one
+    _check(wrapper, 256, 4096, 2048, False, False, 1, 0, 11, tol, -0.1, 0.1)
+    _check(wrapper, 256, 4096, 2048, False, False, 1, 0, 11, tol, -0.1, 0.1, batch=1)
+
+
+def test_long_k_keeps_fp32_accuracy(wrapper):
+    # the tensor-core accumulator truncates; the kernel must not let that grow with K
+    wrapper.set_math_mode(MATH_3XTF32)
+    e = _check(wrapper, 256, 256, 16384, False, True, 1, 0, 21, TOL_3XTF32)
+    assert e < 5e-6
+
+
+def test_linearity_at_full_size(wrapper):
+    # size-independent property at a size the CPU oracle would take minutes for (4096^3 per product):
+    # (A1 + A2) * B == A1 * B + A2 * B up to rounding, and C == C^T for A * A^T
+    import torch
+    n = 4096
+    g = torch.Generator(device="cpu").manual_seed(31)
+    a1 = torch.rand(n, n, generator=g) * 2 - 1
+    a2 = torch.rand(n, n, generator=g) * 2 - 1
+    b = torch.rand(n, n, generator=g) * 2 - 1
+    T = lambda t: GPUTensor((n, n), wrapper=wrapper, storage=t.to(wrapper.device).contiguous().view(-1))  # noqa: E731
+    A1, A2, A12, B = T(a1), T(a2), T(a1 + a2), T(b)
+    C1, C2 = GPUTensor((n, n), None, wrapper), GPUTensor((n, n), None, wrapper)
+    C1.Dot(A1, False, B, False, 1, 0)
+    C1.Dot(A2, False, B, False, 1, 1)          # accumulate with beta = 1
+    C2.Dot(A12, False, B, False, 1, 0)
+    wrapper.check_device_status()
+    d = (C1.storage - C2.storage).abs().max().item()
+    assert d / (np.sqrt(n) * 2.0) <= 2 * TOL_3XTF32
+    C1.Dot(A1, False, A1, True, 1, 0)
+    sym = (C1.storage.view(n, n) - C1.storage.view(n, n).t()).abs().max().item()
+    assert sym / np.sqrt(n) <= 2 * TOL_3XTF32
