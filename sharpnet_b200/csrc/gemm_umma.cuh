@@ -39,13 +39,15 @@ struct UmmaTile {
   static constexpr int SMEM_BUDGET = 196 * 1024;
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;    // + slack to align the ring to 1 KB
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;              // one 32 x 32 fp32 block per epilogue warp
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; power of two
   // Warps are grouped in fours so that setmaxnreg can move registers between the roles:
   //   group 0: TMA producer, MMA issuer (two idle warps); then the epilogue groups; then the split group.
   static constexpr int EPI_GROUPS = (BN > 128) ? 2 : 1;             // each epilogue warp owns <= 128 columns
   static constexpr int EPI_THREADS = 128 * EPI_GROUPS;
   static constexpr int EPI_COLS = BN / EPI_GROUPS;                  // columns per epilogue warp
+  static constexpr int SMEM_BYTES = RING_BYTES + EPI_STAGE_BYTES * 4 * EPI_GROUPS + 1024;  // + 1 KB alignment slack
   static constexpr int N_SPLIT_THREADS = SPLIT ? 128 : 0;
   static constexpr int SPLIT_THREAD0 = 128 + EPI_THREADS;
   static constexpr int THREADS = 128 + EPI_THREADS + N_SPLIT_THREADS;
@@ -271,7 +273,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int j = 0; j < NC; ++j) acc[j] = 0.0f;
       for (int c = 0; c < n_chunks && ok; ++c, ++chunk_id) {
         const int buf = chunk_id & 1;
-        if (!mbar_wait(&acc_full_bar[buf], (acc_ph >> buf) & 1u, abortp)) { ok = false; break; }
+        if (!mbar_wait_warp(&acc_full_bar[buf], (acc_ph >> buf) & 1u, abortp)) { ok = false; break; }
         acc_ph ^= 1u << buf;
         tc_fence_after_sync();
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + col_base;
@@ -287,56 +289,75 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         mbar_arrive(&acc_empty_bar[buf]);
       }
       if (!ok) break;
-      const int row = tm * BM + q * 32 + lane;
+      // Store phase.  Each lane holds one output row (NC columns).  A 32 x 32 block goes through a
+      // per-warp shared-memory tile (16-byte chunks XOR-swizzled by row) so that every global access of
+      // C, Z and bias is a run of whole 128-byte lines instead of 32 scattered 16-byte pieces.
+      float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
+      const int row_base = tm * BM + q * 32;
       const int n0 = tn * BN + col_base;
-      if (row < p.M) {
-        const size_t row_off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
-        float* crow = p.C + row_off;
-        float* zrow = p.Z ? p.Z + row_off : nullptr;
-        if (p.vec_ok && n0 + NC <= p.N) {
+      const size_t tile_off = static_cast<size_t>(b) * p.strideC;
 #pragma unroll
-          for (int j = 0; j < NC / 4; ++j) {
-            const int col = n0 + 4 * j;
-            float4 o;
-            o.x = p.alpha * acc[4 * j + 0];
-            o.y = p.alpha * acc[4 * j + 1];
-            o.z = p.alpha * acc[4 * j + 2];
-            o.w = p.alpha * acc[4 * j + 3];
-            if (p.beta != 0.0f) {
-              const float4 cin = *reinterpret_cast<const float4*>(crow + col);
-              o.x = fmaf(p.beta, cin.x, o.x);
-              o.y = fmaf(p.beta, cin.y, o.y);
-              o.z = fmaf(p.beta, cin.z, o.z);
-              o.w = fmaf(p.beta, cin.w, o.w);
-            }
-            if (p.bias) {
-              const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+      for (int g = 0; g < NC / 32; ++g) {
+        const int col0 = n0 + g * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const float4 v4 = make_float4(acc[g * 32 + 4 * j4], acc[g * 32 + 4 * j4 + 1], acc[g * 32 + 4 * j4 + 2],
+                                        acc[g * 32 + 4 * j4 + 3]);
+          *reinterpret_cast<float4*>(stage + lane * 32 + ((j4 ^ (lane & 7)) << 2)) = v4;
+        }
+        __syncwarp();
+        if (p.vec_ok && col0 + 32 <= p.N) {
+          const int c4 = lane & 7;
+          const int col = col0 + 4 * c4;
+          float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p.bias) bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3);
+            const int row = row_base + r;
+            if (row < p.M) {
+              const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
+              const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
+              float4 o;
+              o.x = p.alpha * a4.x; o.y = p.alpha * a4.y; o.z = p.alpha * a4.z; o.w = p.alpha * a4.w;
+              if (p.beta != 0.0f) {
+                const float4 cin = *reinterpret_cast<const float4*>(p.C + off);
+                o.x = fmaf(p.beta, cin.x, o.x);
+                o.y = fmaf(p.beta, cin.y, o.y);
+                o.z = fmaf(p.beta, cin.z, o.z);
+                o.w = fmaf(p.beta, cin.w, o.w);
+              }
               o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+              if (p.Z) *reinterpret_cast<float4*>(p.Z + off) = o;
+              if (p.act != ACT_IDENTITY) {
+                o.x = act_forward(p.act, o.x);
+                o.y = act_forward(p.act, o.y);
+                o.z = act_forward(p.act, o.z);
+                o.w = act_forward(p.act, o.w);
+              }
+              *reinterpret_cast<float4*>(p.C + off) = o;
             }
-            if (zrow) *reinterpret_cast<float4*>(zrow + col) = o;
-            if (p.act != ACT_IDENTITY) {
-              o.x = act_forward(p.act, o.x);
-              o.y = act_forward(p.act, o.y);
-              o.z = act_forward(p.act, o.z);
-              o.w = act_forward(p.act, o.w);
-            }
-            *reinterpret_cast<float4*>(crow + col) = o;
-            asm volatile("" ::: "memory");   // keep the loads of later columns from piling up in registers
           }
         } else {
-#pragma unroll
-          for (int j = 0; j < NC; ++j) {
-            const int col = n0 + j;
-            if (col < p.N) {
-              float o = p.alpha * acc[j];
-              if (p.beta != 0.0f) o = fmaf(p.beta, crow[col], o);
-              if (p.bias) o += __ldg(p.bias + col);
-              if (zrow) zrow[col] = o;
-              crow[col] = act_forward(p.act, o);
+          // ragged right edge or rows that are not 16-byte aligned: one column per lane
+          const int col = col0 + lane;
+          if (col < p.N) {
+            const float bv = p.bias ? __ldg(p.bias + col) : 0.0f;
+            for (int r = 0; r < 32; ++r) {
+              const int row = row_base + r;
+              if (row >= p.M) break;
+              const float a1 = stage[r * 32 + ((((lane >> 2) ^ (r & 7)) << 2) | (lane & 3))];
+              const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
+              float o = p.alpha * a1;
+              if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
+              o += bv;
+              if (p.Z) p.Z[off] = o;
+              p.C[off] = act_forward(p.act, o);
             }
-            asm volatile("" ::: "memory");
           }
         }
+        __syncwarp();
       }
     }
   } else if (T::SPLIT) {
@@ -348,7 +369,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (!mbar_wait(&full_bar[s], ph, abortp)) { ok = false; break; }
+        if (!mbar_wait_warp(&full_bar[s], ph, abortp)) { ok = false; break; }
         uint8_t* raw = ring + s * T::STAGE_BYTES;
 #pragma unroll 4
         for (int i = tid; i < T::RAW_BYTES / 16; i += T::N_SPLIT_THREADS) {

@@ -84,6 +84,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Warp-wide wait: lane 0 spins, the other lanes park at the warp barrier and then observe the
+// completed phase themselves (one successful try_wait each), so a waiting warp costs the shared
+// memory pipe one poll at a time instead of thirty-two.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (ok && !mbar_try_wait(bar, parity)) ok = mbar_wait(bar, parity, abort_flag);
+  return ok;
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

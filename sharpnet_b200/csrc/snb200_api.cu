@@ -295,7 +295,7 @@ static int choose_bn(const snb200_context* h, const GemmProblem& g) {
     const int bn = cand[i];
     const long long tiles = static_cast<long long>(g.batch) * ((g.M + 127) / 128) * ((g.N + bn - 1) / bn);
     const long long waves = (tiles + h->sm_count - 1) / h->sm_count;
-    const double cost = static_cast<double>(waves) * ((bn < 64 ? 64 : bn) + 32);
+    const double cost = static_cast<double>(waves) * (bn + 128);   // a narrow tile costs more per flop
     if (cost < best_cost * 0.999) { best_cost = cost; best = bn; }
   }
   return best;
