@@ -143,6 +143,23 @@ int snb200_bias_add(snb200_handle_t handle, int M, int N, const float* bias, flo
 /* db[n] = sum_m dy[m,n].  Tensor.Compute_BiasGradient_from_dy (Prod/Data/Tensor.cs:710,
  * Prod/GPU/GpuTensor.cs:686-701, Prod/CPU/CpuTensor.cs:1736-1740,3343-3362). */
 int snb200_bias_grad(snb200_handle_t handle, int M, int N, const float* dy, float* db);
+/* db[n] = sum_m dy[m,n] without a handle and without any allocation.  It has no counterpart in
+ * SharpNet.  It exists for hosts that cannot call cudaMalloc once they are running -- an engine
+ * whose own pool already holds all of the device memory (a later cudaMalloc fails), or a
+ * latency-critical loop that cannot take the device-wide synchronisation cudaMalloc / cudaFree
+ * imply -- and that therefore cannot create a handle either (snb200_create allocates a workspace).
+ * The slab partial sums of the reduction live in a fixed 1 MiB array inside the library's device
+ * image (held by every GPU that loads the library until the process exits), which limits the
+ * matrix to SNB200_NOALLOC_MAX_COLUMNS columns; wider matrices are refused with NOT_SUPPORTED and
+ * a message.  The device address of that array is looked up on the first call on each device, so
+ * make that first call before starting any stream capture.  All calls on a device share the
+ * array: calls queued on one stream are safe, calls that overlap on the GPU race.  Nothing needs
+ * clearing between calls (every word read back is written first by the same call).
+ * cuda_stream is a cudaStream_t (NULL = legacy default stream); err, when not NULL, receives the
+ * text of a refusal or failure. */
+#define SNB200_NOALLOC_MAX_COLUMNS 65536
+int snb200_bias_grad_noalloc(int device_id, void* cuda_stream, int M, int N, const float* dy, float* db, char* err,
+                             int err_len);
 /* y = act(x) element-wise.  Tensor.ActivationForward (Prod/Data/Tensor.cs:618,
  * Prod/GPU/GpuTensor.cs:397-443, Prod/CPU/CpuTensorActivationFunctions.cs:152-244). */
 int snb200_activation_fwd(snb200_handle_t handle, int act, long long count, const float* x, float* y);

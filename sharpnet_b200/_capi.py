@@ -44,6 +44,7 @@ SIGNATURES = {
     "snb200_dense_bwd": (_I, [_H, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P]),
     "snb200_bias_add": (_I, [_H, _I, _I, _P, _P]),
     "snb200_bias_grad": (_I, [_H, _I, _I, _P, _P]),
+    "snb200_bias_grad_noalloc": (_I, [_I, _P, _I, _I, _P, _P, _c.c_char_p, _I]),
     "snb200_activation_fwd": (_I, [_H, _I, _L, _P, _P]),
     "snb200_activation_bwd": (_I, [_H, _I, _L, _P, _P, _P, _P]),
     "snb200_axpy": (_I, [_H, _L, _F, _P, _P]),

@@ -11,7 +11,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libsharpnet_b200.so")
-SOURCES = [os.path.join(CSRC, "snb200_api.cu")]
+SOURCES = [os.path.join(CSRC, "snb200_api.cu"), os.path.join(CSRC, "noalloc.cu")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC", "-diag-suppress", "550",

@@ -7,12 +7,12 @@
 namespace snb {
 
 // y[m, n] += bias[n]                               (Prod/CPU/CpuTensor.cs:1468-1487)
-__global__ void bias_add_kernel(long long total, int N, const float* __restrict__ bias, float* __restrict__ y) {
+static __global__ void bias_add_kernel(long long total, int N, const float* __restrict__ bias, float* __restrict__ y) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride)
     y[i] += __ldg(bias + (i % N));
 }
-__global__ void bias_add_vec4_kernel(long long total4, int N4, const float4* __restrict__ bias,
+static __global__ void bias_add_vec4_kernel(long long total4, int N4, const float4* __restrict__ bias,
                                      float4* __restrict__ y) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total4; i += stride) {
@@ -23,12 +23,12 @@ __global__ void bias_add_vec4_kernel(long long total4, int N4, const float4* __r
   }
 }
 
-__global__ void activation_fwd_kernel(int act, long long n, const float* __restrict__ x, float* __restrict__ y) {
+static __global__ void activation_fwd_kernel(int act, long long n, const float* __restrict__ x, float* __restrict__ y) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
     y[i] = act_forward(act, x[i]);
 }
-__global__ void activation_bwd_kernel(int act, long long n, const float* __restrict__ dy, const float* __restrict__ x,
+static __global__ void activation_bwd_kernel(int act, long long n, const float* __restrict__ dy, const float* __restrict__ x,
                                       const float* __restrict__ y, float* __restrict__ dx) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
@@ -38,7 +38,7 @@ __global__ void activation_bwd_kernel(int act, long long n, const float* __restr
   }
 }
 // y += alpha * x                                    (Prod/CPU/CpuTensor.cs:1032-1038)
-__global__ void axpy_kernel(long long n, float alpha, const float* __restrict__ x, float* __restrict__ y) {
+static __global__ void axpy_kernel(long long n, float alpha, const float* __restrict__ x, float* __restrict__ y) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
     y[i] = fmaf(alpha, x[i], y[i]);
@@ -112,7 +112,7 @@ colsum_slab_kernel(int M, int N, int rows_per_slab, int act, const float* __rest
   }
 }
 
-__global__ void colsum_finish_kernel(int N, int slabs, const float* __restrict__ partial, float* __restrict__ db) {
+static __global__ void colsum_finish_kernel(int N, int slabs, const float* __restrict__ partial, float* __restrict__ db) {
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= N) return;
   float t = 0.0f;
