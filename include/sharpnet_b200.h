@@ -84,6 +84,9 @@ int snb200_get_launch_count(snb200_handle_t handle, long long* count);
 int snb200_get_last_kernel(snb200_handle_t handle, char* buf, int buf_len);
 int snb200_get_version(void);
 /* Kernel-selection overrides for experiments and tests (no counterpart in SharpNet).
+ * key 3: K extent accumulated inside the tensor core before the sum moves to registers (3xTF32; default 128,
+ *        0 = whole K); key 4: CTA-pair kernel (0 automatic, 1 always, 2 never); key 5: split-K and
+ *        swapped-operand plans for problems with few tiles (0 automatic, 1 never).
  * key 0: path (0 automatic, 1 tensor cores whenever the operands allow TMA, 2 SIMT fp32);
  * key 1: tile width of the tensor-core kernel (0 automatic, else 32, 64, 128 or 256);
  * key 2: 3xTF32 writes the rounded hi plane back to shared memory (1) or lets the

@@ -16,7 +16,7 @@ STATUS_NAMES = {
 MATH_3XTF32, MATH_TF32, MATH_FP32_SIMT = 0, 1, 2
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
 W_OUT_IN, W_IN_OUT = 0, 1
-TUNE_FORCE_PATH, TUNE_FORCE_BN, TUNE_REWRITE_HI = 0, 1, 2
+TUNE_FORCE_PATH, TUNE_FORCE_BN, TUNE_REWRITE_HI, TUNE_CHUNK_K, TUNE_PAIR, TUNE_SPLITK = 0, 1, 2, 3, 4, 5
 
 _c = ctypes
 _H = _c.c_void_p

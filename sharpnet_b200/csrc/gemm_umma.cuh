@@ -86,6 +86,12 @@ struct UmmaParams {
   int rewrite_hi;   // 3xTF32: store the rounded hi plane back over the raw tile
   int vec_ok;       // C (and Z, bias) rows are 16-byte aligned
   int* error_word;  // set to 1 when a pipeline wait timed out
+  // split-K: work unit = (tile, split); each split covers kb_per_split k-blocks and stores its raw
+  // partial sums to partial + split * partial_stride (dense [batch, M, N]); a second kernel combines them
+  int splits;
+  int kb_per_split;
+  float* partial;
+  long long partial_stride;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
@@ -118,6 +124,103 @@ __device__ __forceinline__ void reg_alloc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+// Store phase of the epilogue.  Each lane holds one output row (NC columns of it) in `acc`.  A
+// 32 x 32 block goes through a per-warp shared-memory tile (16-byte chunks XOR-swizzled by row) so
+// that every global access of C, Z and bias is a run of whole 128-byte lines instead of 32 scattered
+// 16-byte pieces.  `row_base` is the first of the warp's 32 rows, `n0` its first column.
+template <int NC>
+__device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const float (&acc)[NC], float* stage, int b,
+                                              int row_base, int n0, int lane) {
+  const size_t tile_off = static_cast<size_t>(b) * p.strideC;
+#pragma unroll
+  for (int g = 0; g < NC / 32; ++g) {
+    const int col0 = n0 + g * 32;
+    if (col0 >= p.N) break;  // warp-uniform
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      const float4 v4 = make_float4(acc[g * 32 + 4 * j4], acc[g * 32 + 4 * j4 + 1], acc[g * 32 + 4 * j4 + 2],
+                                    acc[g * 32 + 4 * j4 + 3]);
+      *reinterpret_cast<float4*>(stage + lane * 32 + ((j4 ^ (lane & 7)) << 2)) = v4;
+    }
+    __syncwarp();
+    if (p.vec_ok && col0 + 32 <= p.N) {
+      const int c4 = lane & 7;
+      const int col = col0 + 4 * c4;
+      float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.bias) bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        const int row = row_base + r;
+        if (row < p.M) {
+          const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
+          const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
+          float4 o;
+          o.x = p.alpha * a4.x; o.y = p.alpha * a4.y; o.z = p.alpha * a4.z; o.w = p.alpha * a4.w;
+          if (p.beta != 0.0f) {
+            const float4 cin = *reinterpret_cast<const float4*>(p.C + off);
+            o.x = fmaf(p.beta, cin.x, o.x);
+            o.y = fmaf(p.beta, cin.y, o.y);
+            o.z = fmaf(p.beta, cin.z, o.z);
+            o.w = fmaf(p.beta, cin.w, o.w);
+          }
+          o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+          if (p.Z) *reinterpret_cast<float4*>(p.Z + off) = o;
+          if (p.act != ACT_IDENTITY) {
+            o.x = act_forward(p.act, o.x);
+            o.y = act_forward(p.act, o.y);
+            o.z = act_forward(p.act, o.z);
+            o.w = act_forward(p.act, o.w);
+          }
+          *reinterpret_cast<float4*>(p.C + off) = o;
+        }
+      }
+    } else {
+      // ragged right edge or rows that are not 16-byte aligned: one column per lane
+      const int col = col0 + lane;
+      if (col < p.N) {
+        const float bv = p.bias ? __ldg(p.bias + col) : 0.0f;
+        for (int r = 0; r < 32; ++r) {
+          const int row = row_base + r;
+          if (row >= p.M) break;
+          const float a1 = stage[r * 32 + ((((lane >> 2) ^ (r & 7)) << 2) | (lane & 3))];
+          const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
+          float o = p.alpha * a1;
+          if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
+          o += bv;
+          if (p.Z) p.Z[off] = o;
+          p.C[off] = act_forward(p.act, o);
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// 3xTF32 operand split of one landed stage: lo = tf32(x - hi) goes to the second plane, RAW_BYTES
+// after the raw tile, at the same (swizzled) offset.
+template <int RAW_BYTES, int NTHREADS>
+__device__ __forceinline__ void split_stage(uint8_t* raw, int tid, int rewrite_hi) {
+#pragma unroll 8
+  for (int i = tid; i < RAW_BYTES / 16; i += NTHREADS) {
+    float4 x = *reinterpret_cast<const float4*>(raw + i * 16);
+    uint4 hi, lo;
+    if (rewrite_hi) {
+      hi.x = to_tf32_rna(x.x); hi.y = to_tf32_rna(x.y); hi.z = to_tf32_rna(x.z); hi.w = to_tf32_rna(x.w);
+    } else {
+      // The tensor core reads only the top 19 bits of each word: the raw tile is the hi plane.
+      hi.x = __float_as_uint(x.x) & 0xffffe000u; hi.y = __float_as_uint(x.y) & 0xffffe000u;
+      hi.z = __float_as_uint(x.z) & 0xffffe000u; hi.w = __float_as_uint(x.w) & 0xffffe000u;
+    }
+    lo.x = to_tf32_rna(x.x - __uint_as_float(hi.x));
+    lo.y = to_tf32_rna(x.y - __uint_as_float(hi.y));
+    lo.z = to_tf32_rna(x.z - __uint_as_float(hi.z));
+    lo.w = to_tf32_rna(x.w - __uint_as_float(hi.w));
+    if (rewrite_hi) *reinterpret_cast<uint4*>(raw + i * 16) = hi;
+    *reinterpret_cast<uint4*>(raw + RAW_BYTES + i * 16) = lo;
+  }
+}
+
 // The tensor core adds into its fp32 accumulator with truncation, so a long K loop drifts towards
 // zero by about 1e-8 * K (relative to sqrt(K)).  The MMA warp therefore accumulates only
 // `chunk_kblocks` k-blocks in TMEM; the epilogue warps add every such partial sum into fp32
@@ -144,12 +247,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&split_bar[s], T::SPLIT ? T::N_SPLIT_THREADS : 1);
+      mbar_init(&split_bar[s], T::SPLIT ? T::N_SPLIT_THREADS / 32 : 1);   // one arrival per split warp
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full_bar[b], 1);
-      mbar_init(&acc_empty_bar[b], T::EPI_THREADS);
+      mbar_init(&acc_empty_bar[b], T::EPI_THREADS / 32);   // one arrival per epilogue warp
     }
     abort_flag = 0;
     fence_mbar_init();
@@ -166,8 +269,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = tmem_base_holder;
   volatile int* abortp = &abort_flag;
 
-  const int total_tiles = p.batch * p.tiles_m * p.tiles_n;
-  const int n_chunks = (p.k_blocks + p.chunk_kblocks - 1) / p.chunk_kblocks;
+  const int n_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int total_tiles = n_tiles * p.splits;   // work units: (tile, K split)
 
   if (warp < 4) {
     reg_dealloc<T::REGS_CTRL>();
@@ -178,9 +281,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int b, tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
+        tile_coords(t % n_tiles, p.tiles_m, p.tiles_n, b, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int kb_begin = (t / n_tiles) * p.kb_per_split;
+        const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) { ok = false; break; }
           uint8_t* a_dst = ring + s * T::STAGE_BYTES;
           uint8_t* b_dst = a_dst + T::A_BYTES;
@@ -220,13 +325,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t chunk_id = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += p.chunk_kblocks, ++chunk_id) {
+        const int kb_begin = (t / n_tiles) * p.kb_per_split;
+        const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+        for (int kb0 = kb_begin; kb0 < kb_end && ok; kb0 += p.chunk_kblocks, ++chunk_id) {
           const int buf = chunk_id & 1;
           if (!mbar_wait(&acc_empty_bar[buf], ((acc_ph >> buf) & 1u) ^ 1u, abortp)) { ok = false; break; }
           acc_ph ^= 1u << buf;
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + buf * BN;
-          const int kb1 = min(p.k_blocks, kb0 + p.chunk_kblocks);
+          const int kb1 = min(kb_end, kb0 + p.chunk_kblocks);
           for (int kb = kb0; kb < kb1; ++kb) {
             uint64_t* ready = T::SPLIT ? &split_bar[s] : &full_bar[s];
             if (!mbar_wait(ready, ph, abortp)) { ok = false; break; }
@@ -267,7 +374,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int b, tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, b, tm, tn);
+      tile_coords(t % n_tiles, p.tiles_m, p.tiles_n, b, tm, tn);
+      const int split = t / n_tiles;
+      const int kb_count = min(p.k_blocks, (split + 1) * p.kb_per_split) - split * p.kb_per_split;
+      const int n_chunks = (kb_count + p.chunk_kblocks - 1) / p.chunk_kblocks;
       float acc[NC];
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] = 0.0f;
@@ -286,78 +396,22 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int j = 0; j < 32; ++j) acc[g * 32 + j] += v[j];
         }
         tc_fence_before_sync();
-        mbar_arrive(&acc_empty_bar[buf]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
       }
       if (!ok) break;
-      // Store phase.  Each lane holds one output row (NC columns).  A 32 x 32 block goes through a
-      // per-warp shared-memory tile (16-byte chunks XOR-swizzled by row) so that every global access of
-      // C, Z and bias is a run of whole 128-byte lines instead of 32 scattered 16-byte pieces.
       float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
-      const int row_base = tm * BM + q * 32;
-      const int n0 = tn * BN + col_base;
-      const size_t tile_off = static_cast<size_t>(b) * p.strideC;
-#pragma unroll
-      for (int g = 0; g < NC / 32; ++g) {
-        const int col0 = n0 + g * 32;
-        if (col0 >= p.N) break;  // warp-uniform
-#pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-          const float4 v4 = make_float4(acc[g * 32 + 4 * j4], acc[g * 32 + 4 * j4 + 1], acc[g * 32 + 4 * j4 + 2],
-                                        acc[g * 32 + 4 * j4 + 3]);
-          *reinterpret_cast<float4*>(stage + lane * 32 + ((j4 ^ (lane & 7)) << 2)) = v4;
-        }
-        __syncwarp();
-        if (p.vec_ok && col0 + 32 <= p.N) {
-          const int c4 = lane & 7;
-          const int col = col0 + 4 * c4;
-          float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (p.bias) bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int r = it * 4 + (lane >> 3);
-            const int row = row_base + r;
-            if (row < p.M) {
-              const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
-              const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
-              float4 o;
-              o.x = p.alpha * a4.x; o.y = p.alpha * a4.y; o.z = p.alpha * a4.z; o.w = p.alpha * a4.w;
-              if (p.beta != 0.0f) {
-                const float4 cin = *reinterpret_cast<const float4*>(p.C + off);
-                o.x = fmaf(p.beta, cin.x, o.x);
-                o.y = fmaf(p.beta, cin.y, o.y);
-                o.z = fmaf(p.beta, cin.z, o.z);
-                o.w = fmaf(p.beta, cin.w, o.w);
-              }
-              o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
-              if (p.Z) *reinterpret_cast<float4*>(p.Z + off) = o;
-              if (p.act != ACT_IDENTITY) {
-                o.x = act_forward(p.act, o.x);
-                o.y = act_forward(p.act, o.y);
-                o.z = act_forward(p.act, o.z);
-                o.w = act_forward(p.act, o.w);
-              }
-              *reinterpret_cast<float4*>(p.C + off) = o;
-            }
-          }
-        } else {
-          // ragged right edge or rows that are not 16-byte aligned: one column per lane
-          const int col = col0 + lane;
-          if (col < p.N) {
-            const float bv = p.bias ? __ldg(p.bias + col) : 0.0f;
-            for (int r = 0; r < 32; ++r) {
-              const int row = row_base + r;
-              if (row >= p.M) break;
-              const float a1 = stage[r * 32 + ((((lane >> 2) ^ (r & 7)) << 2) | (lane & 3))];
-              const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
-              float o = p.alpha * a1;
-              if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
-              o += bv;
-              if (p.Z) p.Z[off] = o;
-              p.C[off] = act_forward(p.act, o);
-            }
-          }
-        }
-        __syncwarp();
+      if (p.partial == nullptr) {
+        epilogue_store_rows<NC>(p, acc, stage, b, tm * BM + q * 32, tn * BN + col_base, lane);
+      } else {
+        // split-K: raw partial sums, dense [batch, M, N], combined by splitk_reduce_kernel
+        UmmaParams pp = p;
+        pp.C = p.partial + static_cast<size_t>(split) * p.partial_stride;
+        pp.ldc = p.N;
+        pp.strideC = static_cast<long long>(p.M) * p.N;
+        pp.alpha = 1.0f; pp.beta = 0.0f; pp.bias = nullptr; pp.Z = nullptr; pp.act = ACT_IDENTITY;
+        pp.vec_ok = (p.N % 4 == 0) ? 1 : 0;
+        epilogue_store_rows<NC>(pp, acc, stage, b, tm * BM + q * 32, tn * BN + col_base, lane);
       }
     }
   } else if (T::SPLIT) {
@@ -368,29 +422,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t ph = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      const int kb_begin = (t / n_tiles) * p.kb_per_split;
+      const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait_warp(&full_bar[s], ph, abortp)) { ok = false; break; }
-        uint8_t* raw = ring + s * T::STAGE_BYTES;
-#pragma unroll 4
-        for (int i = tid; i < T::RAW_BYTES / 16; i += T::N_SPLIT_THREADS) {
-          float4 x = *reinterpret_cast<const float4*>(raw + i * 16);
-          uint4 hi, lo;
-          if (p.rewrite_hi) {
-            hi.x = to_tf32_rna(x.x); hi.y = to_tf32_rna(x.y); hi.z = to_tf32_rna(x.z); hi.w = to_tf32_rna(x.w);
-          } else {
-            // The tensor core reads only the top 19 bits of each word: the raw tile is the hi plane.
-            hi.x = __float_as_uint(x.x) & 0xffffe000u; hi.y = __float_as_uint(x.y) & 0xffffe000u;
-            hi.z = __float_as_uint(x.z) & 0xffffe000u; hi.w = __float_as_uint(x.w) & 0xffffe000u;
-          }
-          lo.x = to_tf32_rna(x.x - __uint_as_float(hi.x));
-          lo.y = to_tf32_rna(x.y - __uint_as_float(hi.y));
-          lo.z = to_tf32_rna(x.z - __uint_as_float(hi.z));
-          lo.w = to_tf32_rna(x.w - __uint_as_float(hi.w));
-          if (p.rewrite_hi) *reinterpret_cast<uint4*>(raw + i * 16) = hi;
-          *reinterpret_cast<uint4*>(raw + T::RAW_BYTES + i * 16) = lo;
-        }
+        split_stage<T::RAW_BYTES, T::N_SPLIT_THREADS>(ring + s * T::STAGE_BYTES, tid, p.rewrite_hi);
         fence_proxy_async_smem();   // make the generic-proxy stores visible to tcgen05.mma
-        mbar_arrive(&split_bar[s]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&split_bar[s]);
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
@@ -404,6 +443,42 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_dealloc(tmem_base, T::TMEM_COLS);
   }
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.error_word, 1);
+}
+
+// Second pass of a split-K (or swapped-operand) GEMM: sums the `splits` raw partial results and applies
+// the epilogue  v = alpha * sum + beta * C + bias ; Z = v ; C = act(v).  The partials are dense
+// [batch, M, N], or [batch, N, M] when the GEMM ran with its operands swapped (`transposed`), in which
+// case this pass also undoes the transposition.  One thread per output element, n fastest.
+struct SplitKReduceParams {
+  int M, N, batch, splits, transposed;
+  const float* partial;
+  long long partial_stride;
+  float* C;
+  float* Z;
+  const float* bias;
+  int ldc;
+  long long strideC;
+  float alpha, beta;
+  int act;
+};
+static __global__ void splitk_reduce_kernel(const SplitKReduceParams p) {
+  const long long per_batch = static_cast<long long>(p.M) * p.N;
+  const long long total = per_batch * p.batch;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
+    const long long b = i / per_batch;
+    const long long r = i - b * per_batch;
+    const int m = static_cast<int>(r / p.N), n = static_cast<int>(r - static_cast<long long>(m) * p.N);
+    const long long src = b * per_batch + (p.transposed ? static_cast<long long>(n) * p.M + m : r);
+    float sum = 0.0f;
+    for (int s = 0; s < p.splits; ++s) sum += p.partial[s * p.partial_stride + src];
+    const size_t off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(m) * p.ldc + n;
+    float v = p.alpha * sum;
+    if (p.beta != 0.0f) v = fmaf(p.beta, p.C[off], v);
+    if (p.bias) v += __ldg(p.bias + n);
+    if (p.Z) p.Z[off] = v;
+    p.C[off] = act_forward(p.act, v);
+  }
 }
 
 }  // namespace snb

@@ -12,11 +12,12 @@
 #include "elementwise.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_umma.cuh"
+#include "gemm_umma2.cuh"
 
 using namespace snb;
 
 // ------------------------------------------------------------------------------------ handle
-enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_COUNT = 8 };
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_COUNT = 8 };
 
 struct snb200_context {
   int device;
@@ -102,7 +103,7 @@ extern "C" int snb200_create(snb200_handle_t* handle, int device_id) {
   h->tune[TUNE_CHUNK_K] = 128;
   const char* env = getenv("SNB200_MATH_MODE");
   if (env && env[0] >= '0' && env[0] <= '2' && env[1] == 0) h->math_mode = env[0] - '0';
-  h->workspace_floats = 1u << 20;
+  h->workspace_floats = 8u << 20;   // 32 MB: column-sum slabs and split-K partial sums
   if (cudaMalloc(&h->workspace, h->workspace_floats * sizeof(float)) != cudaSuccess ||
       cudaMalloc(&h->error_word, sizeof(int)) != cudaSuccess ||
       cudaMemset(h->error_word, 0, sizeof(int)) != cudaSuccess) {
@@ -198,31 +199,30 @@ static bool tma_eligible(const GemmProblem& g) {
   return true;
 }
 
+// Tensor maps and kernel parameters shared by the single-CTA and the CTA-pair kernels.  `bn_box` is
+// the number of B columns one CTA loads per stage (BN, or BN / 2 in a pair).
 template <class T>
-static int launch_umma_t(snb200_handle_t h, const GemmProblem& g) {
-  static bool configured[64] = {};
-  CUtensorMap tmA, tmB;
+static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, CUtensorMap* tmA, CUtensorMap* tmB,
+                          UmmaParams* pp) {
   const uint64_t a_rows = g.transA ? g.K : g.M, b_rows = g.transB ? g.N : g.K;
   const uint64_t pitchA2 = g.batch > 1 ? static_cast<uint64_t>(g.strideA) : a_rows * g.lda;
   const uint64_t pitchB2 = g.batch > 1 ? static_cast<uint64_t>(g.strideB) : b_rows * g.ldb;
   const CUtensorMapSwizzle kmaj_sw = (T::BK == 32) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   bool ok;
-  if (!g.transA)  // stored [M x K]: K-major tile, box = BK x 128 rows
-    ok = encode_3d(&tmA, g.A, g.K, g.M, g.batch, g.lda, pitchA2, T::BK, T::BM, kmaj_sw);
-  else            // stored [K x M]: MN-major tile, box = 32 m x BK rows
-    ok = encode_3d(&tmA, g.A, g.M, g.K, g.batch, g.lda, pitchA2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-  if (g.transB)   // stored [N x K]: K-major tile
-    ok = ok && encode_3d(&tmB, g.B, g.K, g.N, g.batch, g.ldb, pitchB2, T::BK, T::BN, kmaj_sw);
-  else            // stored [K x N]: MN-major tile
-    ok = ok && encode_3d(&tmB, g.B, g.N, g.K, g.batch, g.ldb, pitchB2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  if (!g.transA)
+    ok = encode_3d(tmA, g.A, g.K, g.M, g.batch, g.lda, pitchA2, T::BK, T::BM, kmaj_sw);
+  else
+    ok = encode_3d(tmA, g.A, g.M, g.K, g.batch, g.lda, pitchA2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  if (g.transB)
+    ok = ok && encode_3d(tmB, g.B, g.K, g.N, g.batch, g.ldb, pitchB2, T::BK, bn_box, kmaj_sw);
+  else
+    ok = ok && encode_3d(tmB, g.B, g.N, g.K, g.batch, g.ldb, pitchB2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (!ok) return fail(h, SNB200_STATUS_INTERNAL_ERROR, "cuTensorMapEncodeTiled rejected the operand layout");
-
-  UmmaParams p;
+  UmmaParams& p = *pp;
   p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.batch;
   p.tiles_m = (g.M + T::BM - 1) / T::BM;
   p.tiles_n = (g.N + T::BN - 1) / T::BN;
   p.k_blocks = (g.K + T::BK - 1) / T::BK;
-  // 3xTF32 moves the running sum out of the truncating tensor-core accumulator every `chunk` of K.
   int chunk_k = T::SPLIT ? h->tune[TUNE_CHUNK_K] : 0;
   p.chunk_kblocks = chunk_k > 0 ? (chunk_k + T::BK - 1) / T::BK : p.k_blocks;
   if (p.chunk_kblocks < 1) p.chunk_kblocks = 1;
@@ -235,34 +235,116 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g) {
   p.vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (g.batch == 1 || g.strideC % 4 == 0) &&
              (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias));
   p.error_word = h->error_word;
+  p.splits = 1;
+  p.kb_per_split = p.k_blocks;
+  p.partial = nullptr;
+  p.partial_stride = 0;
+  return 0;
+}
 
+// How a problem is cut along K when it has too few output tiles to fill the GPU: `splits` work
+// units per tile, each covering `k_per_split` of K and writing raw partial sums to the workspace.
+struct SplitPlan { int splits; int k_per_split; int transposed; int parts; };   // parts: partial results actually written
+
+template <class T>
+static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& plan) {
+  static bool configured[64] = {};
+  CUtensorMap tmA, tmB;
+  UmmaParams p;
+  int st = fill_umma_args<T>(h, g, T::BN, &tmA, &tmB, &p);
+  if (st) return st;
+  if (plan.splits > 0) {   // partial sums go to the workspace; splitk_reduce_kernel finishes the job
+    p.kb_per_split = (plan.k_per_split + T::BK - 1) / T::BK;
+    p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+    p.partial = h->workspace;
+    p.partial_stride = static_cast<long long>(g.batch) * g.M * g.N;
+  }
   if (!configured[h->device]) {
     SNB_CUDA(h, cudaFuncSetAttribute(umma_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     configured[h->device] = true;
   }
-  const long long tiles = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
-  const int grid = static_cast<int>(tiles < h->sm_count ? tiles : h->sm_count);
+  const long long units = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n * p.splits;
+  const int grid = static_cast<int>(units < h->sm_count ? units : h->sm_count);
   umma_gemm_kernel<T><<<grid, T::THREADS, T::SMEM_BYTES, h->stream>>>(tmA, tmB, p);
+  plan.parts = plan.splits > 0 ? p.splits : 0;
   return check_launch(h, "umma_gemm_kernel launch");
 }
 
-static int launch_umma(snb200_handle_t h, const GemmProblem& g, bool split, int bn) {
+template <class T>
+static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g) {
+  static bool configured[64] = {};
+  static int max_pairs[64] = {};
+  CUtensorMap tmA, tmB;
+  UmmaParams p;
+  int st = fill_umma_args<T>(h, g, T::BNH, &tmA, &tmB, &p);
+  if (st) return st;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(T::THREADS);
+  cfg.dynamicSmemBytes = T::SMEM_BYTES;
+  cfg.stream = h->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (!configured[h->device]) {
+    SNB_CUDA(h, cudaFuncSetAttribute(umma2_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    cfg.gridDim = dim3(h->sm_count & ~1);
+    int n = 0;
+    SNB_CUDA(h, cudaOccupancyMaxActiveClusters(&n, umma2_gemm_kernel<T>, &cfg));
+    if (n < 1) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "no CTA pair of this kernel fits on the device");
+    max_pairs[h->device] = n;
+    configured[h->device] = true;
+  }
+  const long long tiles = static_cast<long long>(p.batch) * ((g.M + 2 * T::BM - 1) / (2 * T::BM)) * p.tiles_n;
+  const long long pairs = tiles < max_pairs[h->device] ? tiles : max_pairs[h->device];
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  {
+    const size_t len = strlen(h->last_kernel);
+    snprintf(h->last_kernel + len, sizeof(h->last_kernel) - len, "_p%lld", pairs);
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, umma2_gemm_kernel<T>, tmA, tmB, p);
+  if (e != cudaSuccess) return cuda_fail(h, e, "umma2_gemm_kernel launch");
+  return check_launch(h, "umma2_gemm_kernel launch");
+}
+
+static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int bn) {
   char name[64];
-  snprintf(name, sizeof(name), "umma_%s_128x%d", split ? "3xtf32" : "tf32", bn);
+  snprintf(name, sizeof(name), "umma2_%s_256x%d", split ? "3xtf32" : "tf32", bn);
   note_kernel(h, name, 1);
   if (split) {
     switch (bn) {
-      case 256: return launch_umma_t<UmmaTile<256, 16, true>>(h, g);
-      case 128: return launch_umma_t<UmmaTile<128, 16, true>>(h, g);
-      case 64: return launch_umma_t<UmmaTile<64, 16, true>>(h, g);
-      default: return launch_umma_t<UmmaTile<32, 16, true>>(h, g);
+      case 256: return launch_umma2_t<Umma2Tile<256, 16, true>>(h, g);
+      case 128: return launch_umma2_t<Umma2Tile<128, 16, true>>(h, g);
+      default: return launch_umma2_t<Umma2Tile<64, 16, true>>(h, g);
     }
   }
   switch (bn) {
-    case 256: return launch_umma_t<UmmaTile<256, 32, false>>(h, g);
-    case 128: return launch_umma_t<UmmaTile<128, 32, false>>(h, g);
-    case 64: return launch_umma_t<UmmaTile<64, 32, false>>(h, g);
-    default: return launch_umma_t<UmmaTile<32, 32, false>>(h, g);
+    case 256: return launch_umma2_t<Umma2Tile<256, 32, false>>(h, g);
+    case 128: return launch_umma2_t<Umma2Tile<128, 32, false>>(h, g);
+    default: return launch_umma2_t<Umma2Tile<64, 32, false>>(h, g);
+  }
+}
+
+static int launch_umma(snb200_handle_t h, const GemmProblem& g, bool split, int bn, SplitPlan& plan) {
+  char name[64];
+  snprintf(name, sizeof(name), "umma_%s_128x%d%s", split ? "3xtf32" : "tf32", bn,
+           plan.splits > 0 ? (plan.transposed ? "_swapAB_splitk" : "_splitk") : "");
+  note_kernel(h, name, 1);
+  if (split) {
+    switch (bn) {
+      case 256: return launch_umma_t<UmmaTile<256, 16, true>>(h, g, plan);
+      case 128: return launch_umma_t<UmmaTile<128, 16, true>>(h, g, plan);
+      case 64: return launch_umma_t<UmmaTile<64, 16, true>>(h, g, plan);
+      default: return launch_umma_t<UmmaTile<32, 16, true>>(h, g, plan);
+    }
+  }
+  switch (bn) {
+    case 256: return launch_umma_t<UmmaTile<256, 32, false>>(h, g, plan);
+    case 128: return launch_umma_t<UmmaTile<128, 32, false>>(h, g, plan);
+    case 64: return launch_umma_t<UmmaTile<64, 32, false>>(h, g, plan);
+    default: return launch_umma_t<UmmaTile<32, 32, false>>(h, g, plan);
   }
 }
 
@@ -286,19 +368,62 @@ static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
   return check_launch(h, "simt_gemm_kernel launch");
 }
 
-// Picks the tile width whose wave count wastes the fewest SM-cycles.
-static int choose_bn(const snb200_context* h, const GemmProblem& g) {
-  const int cand[4] = {256, 128, 64, 32};
-  int best = 256;
+// Picks the kernel (one CTA per 128 x BN tile, or a CTA pair per 256 x BN tile) and the tile width
+// whose wave count wastes the fewest SM-cycles.  A narrow tile costs more per flop (the A operand is
+// re-read for fewer columns); a pair runs the same tile area about 15 % faster in 3xTF32 mode because
+// each SM loads, splits and reads only half of B.
+struct TileChoice { int pair; int bn; int splits; };   // splits > 1: cut K, partial sums through the workspace
+static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, bool split) {
+  TileChoice best = {0, 256, 1};
+  const bool allow_splitk = h->tune[TUNE_SPLITK] == 0;
+  const size_t per_split = static_cast<size_t>(g.batch) * g.M * g.N;
   double best_cost = 1e300;
-  for (int i = 0; i < 4; ++i) {
-    const int bn = cand[i];
-    const long long tiles = static_cast<long long>(g.batch) * ((g.M + 127) / 128) * ((g.N + bn - 1) / bn);
-    const long long waves = (tiles + h->sm_count - 1) / h->sm_count;
-    const double cost = static_cast<double>(waves) * (bn + 128);   // a narrow tile costs more per flop
-    if (cost < best_cost * 0.999) { best_cost = cost; best = bn; }
+  const int pair_mode = h->tune[TUNE_PAIR];   // 0 automatic, 1 always, 2 never
+  const int forced_bn = h->tune[TUNE_FORCE_BN];
+  const int cand[4] = {256, 128, 64, 32};
+  for (int pair = 0; pair < 2; ++pair) {
+    if (pair == 0 && pair_mode == 1) continue;
+    if (pair == 1 && (pair_mode == 2 || (pair_mode == 0 && g.M <= 128))) continue;
+    for (int i = 0; i < 4; ++i) {
+      const int bn = cand[i];
+      if (pair && bn < 64) continue;
+      if (forced_bn && bn != forced_bn) continue;
+      const int rows = pair ? 256 : 128;
+      const long long tiles = static_cast<long long>(g.batch) * ((g.M + rows - 1) / rows) * ((g.N + bn - 1) / bn);
+      const long long slots = pair ? h->sm_count / 2 : h->sm_count;
+      long long ks = 1;   // K splits: only the single-CTA kernel, only when its tiles leave SMs idle
+      if (!pair && allow_splitk && tiles * 2 <= slots) {
+        ks = slots / tiles;
+        if (ks > g.K / 512) ks = g.K / 512;
+        if (ks * per_split > h->workspace_floats) ks = static_cast<long long>(h->workspace_floats / per_split);
+        if (ks < 1) ks = 1;
+      }
+      const long long waves = (tiles * ks + slots - 1) / slots;
+      double f = 1.0;
+      if (pair) f = bn < 128 ? 1.05 : (split ? 0.85 : ((!g.transA && g.transB) ? 0.97 : 1.1));
+      const double cost = static_cast<double>(waves) * (bn + 128) * f / ks + (ks > 1 ? 40.0 : 0.0);
+      if (cost < best_cost * 0.999) {
+        best_cost = cost; best.pair = pair; best.bn = bn; best.splits = static_cast<int>(ks);
+      }
+    }
   }
+  if (best_cost > 1e299) { best.pair = (pair_mode == 1); best.bn = 256; best.splits = 1; }   // forced width not offered by the forced kernel
   return best;
+}
+
+static int launch_reduce(snb200_handle_t h, const GemmProblem& g, int parts, int transposed) {
+  SplitKReduceParams r;
+  r.M = g.M; r.N = g.N; r.batch = g.batch; r.splits = parts; r.transposed = transposed;
+  r.partial = h->workspace;
+  r.partial_stride = static_cast<long long>(g.batch) * g.M * g.N;
+  r.C = g.C; r.Z = g.Z; r.bias = g.bias; r.ldc = g.ldc; r.strideC = g.strideC;
+  r.alpha = g.alpha; r.beta = g.beta; r.act = g.act;
+  const long long total = r.partial_stride;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 8LL * h->sm_count) blocks = 8LL * h->sm_count;
+  splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, h->stream>>>(r);
+  h->launches += 1;
+  return check_launch(h, "splitk_reduce_kernel launch");
 }
 
 static int run_gemm(snb200_handle_t h, const GemmProblem& g) {
@@ -308,12 +433,45 @@ static int run_gemm(snb200_handle_t h, const GemmProblem& g) {
   if (use_umma && force != 1) {
     // Tiny problems do not amortise a 128-row tensor-core tile.
     const double macs = static_cast<double>(g.M) * g.N * g.K * g.batch;
-    if (macs < 64.0 * 64 * 64 || g.M < 16 || g.N < 8) use_umma = false;
+    const bool swappable = h->tune[TUNE_SPLITK] == 0 && g.N >= 256 && g.K >= 256;   // few rows run transposed
+    if (macs < 64.0 * 64 * 64 || (g.M < 16 && !swappable) || g.N < 8) use_umma = false;
   }
   if (!use_umma) return launch_simt(h, g);
-  int bn = h->tune[TUNE_FORCE_BN];
-  if (bn != 256 && bn != 128 && bn != 64 && bn != 32) bn = choose_bn(h, g);
-  return launch_umma(h, g, h->math_mode == SNB200_MATH_3XTF32, bn);
+  const bool split = h->math_mode == SNB200_MATH_3XTF32;
+  const int splitk_mode = h->tune[TUNE_SPLITK];   // 0 automatic, 1 never
+  // Few rows (M <= 64): run the transposed problem C^T = op(B)^T * op(A)^T, so that the long N dimension
+  // fills the 128 rows of the tensor-core tile and the short M dimension becomes a narrow tile width.
+  if (splitk_mode == 0 && h->tune[TUNE_PAIR] != 1 && g.M <= 64 && g.N >= 256 && g.K >= 256) {
+    GemmProblem t = g;
+    t.M = g.N; t.N = g.M;
+    t.A = g.B; t.lda = g.ldb; t.strideA = g.strideB; t.transA = g.transB ? 0 : 1;
+    t.B = g.A; t.ldb = g.lda; t.strideB = g.strideA; t.transB = g.transA ? 0 : 1;
+    const int bn = t.N <= 32 ? 32 : 64;
+    const long long tiles = static_cast<long long>(t.batch) * ((t.M + 127) / 128) * ((t.N + bn - 1) / bn);
+    long long s = h->sm_count / (tiles > 0 ? tiles : 1);
+    if (s < 1) s = 1;
+    if (s > g.K / 256) s = g.K / 256;
+    const size_t per_split = static_cast<size_t>(g.batch) * g.M * g.N;
+    if (s * per_split > h->workspace_floats) s = static_cast<long long>(h->workspace_floats / per_split);
+    if (s >= 1) {
+      SplitPlan plan = {static_cast<int>(s), static_cast<int>((g.K + s - 1) / s), 1, 0};
+      plan.k_per_split = (plan.k_per_split + 127) / 128 * 128;
+      const int st = launch_umma(h, t, split, bn, plan);
+      if (st) return st;
+      return launch_reduce(h, g, plan.parts, 1);
+    }
+  }
+  const TileChoice c = choose_tile(h, g, split);
+  if (c.pair) return launch_umma2(h, g, split, c.bn);
+  // Too few tiles for the SMs and a long K: cut K.
+  SplitPlan plan = {0, 0, 0, 0};
+  if (c.splits > 1) {
+    plan.splits = c.splits;
+    plan.k_per_split = ((g.K + c.splits - 1) / c.splits + 127) / 128 * 128;
+  }
+  const int st = launch_umma(h, g, split, c.bn, plan);
+  if (st || plan.parts == 0) return st;
+  return launch_reduce(h, g, plan.parts, 0);
 }
 
 static int check_ptrs(snb200_handle_t h, const void* a, const void* b, const void* c) {

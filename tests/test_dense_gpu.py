@@ -127,6 +127,15 @@ def test_dense_fwd_bwd_tensor_core(wrapper, act, layout, mode, tol):
 
 @pytest.mark.parametrize("act", [ACT_RELU, ACT_SWISH])
 @pytest.mark.parametrize("layout", [W_IN_OUT, W_OUT_IN])
+def test_dense_small_batch_takes_the_split_k_plans(wrapper, act, layout):
+    # inference-sized batches: forward runs with swapped operands, the gradients with K cut in pieces;
+    # bias, activation and the pre-activation output then come from the reduction kernel
+    _dense_case(wrapper, 32, 2048, 512, act, layout, 300 + act, TOL_3XTF32)
+    _dense_case(wrapper, 8, 1024, 260, act, layout, 320 + act, TOL_3XTF32, mult=0.125)
+
+
+@pytest.mark.parametrize("act", [ACT_RELU, ACT_SWISH])
+@pytest.mark.parametrize("layout", [W_IN_OUT, W_OUT_IN])
 def test_config_3_dense_4096x3072x1024(wrapper, act, layout):
     # BASELINE config 3: x[4096x3072] N(0,1), W Glorot, dy N(0,1); bias drawn non-zero to exercise the add
     _dense_case(wrapper, 4096, 3072, 1024, act, layout, 6, TOL_3XTF32)

@@ -5,7 +5,7 @@ import pytest
 
 from oracle import sharpnet_oracle as orc
 from sharpnet_b200 import MATH_3XTF32, MATH_FP32_SIMT, MATH_TF32
-from sharpnet_b200._capi import TUNE_FORCE_BN, TUNE_FORCE_PATH, SharpNetB200Error
+from sharpnet_b200._capi import TUNE_FORCE_BN, TUNE_FORCE_PATH, TUNE_PAIR, SharpNetB200Error
 from sharpnet_b200.tensor import GPUTensor
 
 from gpu_util import TOL_3XTF32, TOL_TF32, run_dot
@@ -20,10 +20,12 @@ def _reset(wrapper):
     wrapper.set_math_mode(MATH_3XTF32)
     wrapper.set_tuning(TUNE_FORCE_PATH, 0)
     wrapper.set_tuning(TUNE_FORCE_BN, 0)
+    wrapper.set_tuning(TUNE_PAIR, 0)
     yield
     wrapper.set_math_mode(MATH_3XTF32)
     wrapper.set_tuning(TUNE_FORCE_PATH, 0)
     wrapper.set_tuning(TUNE_FORCE_BN, 0)
+    wrapper.set_tuning(TUNE_PAIR, 0)
 
 
 def _check(w, M, N, K, tA, tB, alpha, beta, seed, tol, lo=-1.0, hi=1.0, batch=None):
@@ -105,20 +107,23 @@ def test_small_shape_sweep_simt(wrapper, tA, tB):
     assert wrapper.last_kernel().startswith("simt")
 
 
+@pytest.mark.parametrize("pair", [2, 1])
 @pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
 @pytest.mark.parametrize("tA", [False, True])
 @pytest.mark.parametrize("tB", [False, True])
-def test_tensor_core_ragged_shapes(wrapper, mode, tol, tA, tB):
-    # sizes that are not multiples of the tile, every tile width, alpha/beta accumulate
+def test_tensor_core_ragged_shapes(wrapper, mode, tol, tA, tB, pair):
+    # sizes that are not multiples of the tile, every tile width, alpha/beta accumulate;
+    # pair = 2: one CTA per 128-row tile, pair = 1: CTA pairs on 256-row tiles
     wrapper.set_math_mode(mode)
     wrapper.set_tuning(TUNE_FORCE_PATH, 1)
+    wrapper.set_tuning(TUNE_PAIR, pair)
     seed = 500
-    for bn in (32, 64, 128, 256):
+    for bn in ((32, 64, 128, 256) if pair == 2 else (64, 128, 256)):
         wrapper.set_tuning(TUNE_FORCE_BN, bn)
         for (M, N, K) in ((128, 256, 64), (132, 260, 36), (200, 328, 100), (4, 8, 4), (260, 516, 20), (96, 40, 520)):
             seed += 1
             _check(wrapper, M, N, K, tA, tB, 0.5, 1.0, seed, tol)
-            assert wrapper.last_kernel().startswith("umma"), wrapper.last_kernel()
+            assert wrapper.last_kernel().startswith("umma2" if pair == 1 else "umma_"), wrapper.last_kernel()
     wrapper.set_tuning(TUNE_FORCE_BN, 0)
     _check(wrapper, 300, 200, 72, tA, tB, -2.0, 0.0, 999, tol)
 
@@ -211,6 +216,41 @@ def test_config_4_batched_and_lstm_gate(wrapper, mode, tol):
     # LSTM gate GEMM [256 x 2048] * [2048 x 4096] as Dot and as a batch of one
     _check(wrapper, 256, 4096, 2048, False, False, 1, 0, 11, tol, -0.1, 0.1)
     _check(wrapper, 256, 4096, 2048, False, False, 1, 0, 11, tol, -0.1, 0.1, batch=1)
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+def test_cta_pair_kernel_batched_and_many_tiles(wrapper, mode, tol):
+    # the CTA-pair kernel on batches, on more tiles than there are SM pairs, and on an odd number of row tiles
+    wrapper.set_math_mode(mode)
+    wrapper.set_tuning(TUNE_FORCE_PATH, 1)
+    wrapper.set_tuning(TUNE_PAIR, 1)
+    _check(wrapper, 300, 200, 96, False, True, 1.0, 0.0, 41, tol, batch=5)
+    _check(wrapper, 300, 200, 96, True, False, 0.5, 1.0, 42, tol, batch=3)
+    wrapper.set_tuning(TUNE_FORCE_BN, 64)
+    _check(wrapper, 1920, 1984, 80, False, False, 1.0, 1.0, 43, tol)      # 8 x 31 = 248 pair tiles > 74 pairs
+    _check(wrapper, 384, 512, 4096, False, True, 1.0, 0.0, 44, tol)       # 3 row tiles: the odd CTA's rows are all padding
+    assert wrapper.last_kernel().startswith("umma2")
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+@pytest.mark.parametrize("tA", [False, True])
+@pytest.mark.parametrize("tB", [False, True])
+def test_few_tiles_split_k_and_swapped_operands(wrapper, mode, tol, tA, tB):
+    # problems with fewer tiles than SMs: K is cut into partial sums (workspace + reduction kernel), and
+    # with few rows the operands are swapped so that N fills the 128-row tile
+    wrapper.set_math_mode(mode)
+    seed = 700
+    for (M, N, K) in ((256, 512, 4096), (132, 300, 2052), (512, 128, 8192)):
+        seed += 1
+        _check(wrapper, M, N, K, tA, tB, 0.5, 1.0, seed, tol)
+        assert "splitk" in wrapper.last_kernel(), wrapper.last_kernel()
+    for (M, N, K) in ((32, 4096, 4096), (1, 512, 1024), (5, 1000, 516), (64, 260, 256), (17, 256, 300)):
+        for beta in (0.0, 1.0):
+            seed += 1
+            _check(wrapper, M, N, K, tA, tB, 1.0, beta, seed, tol)
+            tma_ok = (not tA or M % 4 == 0)      # a transposed A is stored [K x M]: its pitch M must be a 16-byte multiple
+            assert ("swapAB" in wrapper.last_kernel()) == tma_ok, wrapper.last_kernel()
+    _check(wrapper, 8, 512, 1024, tA, tB, 1.0, 0.0, 777, tol, batch=6)       # batched, swapped
 
 
 def test_long_k_keeps_fp32_accuracy(wrapper):
