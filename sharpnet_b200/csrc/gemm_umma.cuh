@@ -481,4 +481,35 @@ static __global__ void splitk_reduce_kernel(const SplitKReduceParams p) {
   }
 }
 
+// Same reduction for the swapped-operand plan, where the partials are [batch, N, M]: 32 x 32 tiles go
+// through shared memory so that both the partial reads (m fastest) and the C accesses (n fastest) are
+// coalesced.  Block = 32 x 8 threads; grid = (ceil(N/32), ceil(M/32), batch).
+static __global__ void __launch_bounds__(256) splitk_reduce_transposed_kernel(const SplitKReduceParams p) {
+  __shared__ float tile[32][33];
+  const int n0 = blockIdx.x * 32, m0 = blockIdx.y * 32, b = blockIdx.z;
+  const long long per_batch = static_cast<long long>(p.M) * p.N;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int j = ty; j < 32; j += 8) {
+    const int n = n0 + j, m = m0 + tx;
+    float sum = 0.0f;
+    if (n < p.N && m < p.M) {
+      const long long src = b * per_batch + static_cast<long long>(n) * p.M + m;
+      for (int s = 0; s < p.splits; ++s) sum += p.partial[s * p.partial_stride + src];
+    }
+    tile[j][tx] = sum;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int m = m0 + j, n = n0 + tx;
+    if (m < p.M && n < p.N) {
+      const size_t off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(m) * p.ldc + n;
+      float v = p.alpha * tile[tx][j];
+      if (p.beta != 0.0f) v = fmaf(p.beta, p.C[off], v);
+      if (p.bias) v += __ldg(p.bias + n);
+      if (p.Z) p.Z[off] = v;
+      p.C[off] = act_forward(p.act, v);
+    }
+  }
+}
+
 }  // namespace snb

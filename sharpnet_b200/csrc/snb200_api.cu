@@ -336,8 +336,9 @@ static int launch_umma(snb200_handle_t h, const GemmProblem& g, bool split, int 
     switch (bn) {
       case 256: return launch_umma_t<UmmaTile<256, 16, true>>(h, g, plan);
       case 128: return launch_umma_t<UmmaTile<128, 16, true>>(h, g, plan);
-      case 64: return launch_umma_t<UmmaTile<64, 16, true>>(h, g, plan);
-      default: return launch_umma_t<UmmaTile<32, 16, true>>(h, g, plan);
+      // narrow tiles leave room for 32-wide K blocks: half as many stage hand-offs per unit of K
+      case 64: return launch_umma_t<UmmaTile<64, 32, true>>(h, g, plan);
+      default: return launch_umma_t<UmmaTile<32, 32, true>>(h, g, plan);
     }
   }
   switch (bn) {
@@ -421,7 +422,12 @@ static int launch_reduce(snb200_handle_t h, const GemmProblem& g, int parts, int
   const long long total = r.partial_stride;
   long long blocks = (total + 255) / 256;
   if (blocks > 8LL * h->sm_count) blocks = 8LL * h->sm_count;
-  splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, h->stream>>>(r);
+  if (transposed && g.batch <= 65535 && (g.M + 31) / 32 <= 65535) {
+    dim3 grid((g.N + 31) / 32, (g.M + 31) / 32, g.batch);
+    splitk_reduce_transposed_kernel<<<grid, 256, 0, h->stream>>>(r);
+  } else {
+    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, h->stream>>>(r);
+  }
   h->launches += 1;
   return check_launch(h, "splitk_reduce_kernel launch");
 }

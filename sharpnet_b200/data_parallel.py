@@ -137,6 +137,52 @@ class GradientAllReduce:
         self.comm_wrapper.handle = None
 
 
+class HostStaging:
+    """Double-buffered host-to-device staging of a replica's mini-batch (x and the upstream gradient).
+
+    SharpNet copies every mini-batch from pinned host memory to the device before it runs the
+    step (Prod/Networks/Network.cs:1211-1258, Prod/GPU/GpuTensor.cs:88-93).  Here the copy of step
+    i+1 runs on its own stream while step i computes; the compute stream only waits for the copy it
+    is about to consume, and a buffer is not overwritten before the step that read it has finished."""
+
+    def __init__(self, stack, x_host, dy_host, compute_stream):
+        import torch
+        self.torch = torch
+        self.stack = stack
+        self.x_host, self.dy_host = x_host, dy_host
+        self.compute = compute_stream
+        self.copy = torch.cuda.Stream(device=stack.w.device)
+        w = stack.w
+        self.buffers = [(stack.x, stack.dy),
+                        (GPUTensor(stack.x.Shape, None, w), GPUTensor(stack.dy.Shape, None, w))]
+        self.copied = [None, None]     # event: copy into buffer b finished
+        self.consumed = [None, None]   # event: the step that read buffer b finished
+
+    def issue(self, i):
+        """Queues the copy of step ``i``'s inputs into buffer ``i % 2``."""
+        b = i % 2
+        if self.consumed[b] is not None:
+            self.copy.wait_event(self.consumed[b])
+        with self.torch.cuda.stream(self.copy):
+            self.buffers[b][0].storage.copy_(self.x_host.view(-1), non_blocking=True)
+            self.buffers[b][1].storage.copy_(self.dy_host.view(-1), non_blocking=True)
+            ev = self.torch.cuda.Event()
+            ev.record(self.copy)
+        self.copied[b] = ev
+
+    def bind(self, i):
+        """Points the stack at buffer ``i % 2`` and makes the compute stream wait for its copy."""
+        b = i % 2
+        self.compute.wait_event(self.copied[b])
+        self.stack.x, self.stack.dy = self.buffers[b]
+
+    def release(self, i):
+        """Call after step ``i`` has been queued: marks when its buffer may be overwritten."""
+        ev = self.torch.cuda.Event()
+        ev.record(self.compute)
+        self.consumed[i % 2] = ev
+
+
 def training_step(stack, reducer=None, compute_stream=None):
     """One forward + backward of ``stack`` on this replica's rows, with the per-layer gradient
     all-reduce overlapped when ``reducer`` is given."""

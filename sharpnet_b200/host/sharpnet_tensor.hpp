@@ -1,0 +1,167 @@
+// C++ host-side mirror of SharpNet's GPU tensor API for the matrix-multiply path, on top of the
+// C ABI of libsharpnet_b200.  SharpNet itself is C#; where no .NET toolchain exists this header is
+// the compiled-language stand-in for the P/Invoke shim: same class and method names, same argument
+// order and meaning, status codes turned into exceptions as GPUWrapper.CheckStatus does
+// (Prod/GPU/GPUWrapper.cs:662-668).  Header only; link with -lsharpnet_b200 -lcudart.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <numeric>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/sharpnet_b200.h"
+
+namespace SharpNet {
+
+enum class cudnnActivationMode_t : int {   // Prod/GPU/CudnnWrapper.cs:267-281
+  CUDNN_ACTIVATION_SIGMOID = 0, CUDNN_ACTIVATION_RELU = 1, CUDNN_ACTIVATION_TANH = 2,
+  CUDNN_ACTIVATION_IDENTITY = 5, CUDNN_ACTIVATION_SWISH = 6
+};
+
+// One per device: owns the library handle (the role of Prod/GPU/GPUWrapper.cs:99-160).
+class GPUWrapper {
+ public:
+  explicit GPUWrapper(int deviceId) : DeviceId(deviceId) {
+    const int st = snb200_create(&handle_, deviceId);
+    if (st != 0) throw std::runtime_error("snb200_create failed with status " + std::to_string(st));
+  }
+  ~GPUWrapper() { if (handle_) snb200_destroy(handle_); }
+  GPUWrapper(const GPUWrapper&) = delete;
+  GPUWrapper& operator=(const GPUWrapper&) = delete;
+  void CheckStatus(int status) const {
+    if (status != 0) throw std::runtime_error(std::string(snb200_last_error_string(handle_)) + " (status " +
+                                              std::to_string(status) + ")");
+  }
+  snb200_handle_t Handle() const { return handle_; }
+  void SetMathMode(int mode) { CheckStatus(snb200_set_math_mode(handle_, mode)); }
+  const int DeviceId;
+ private:
+  snb200_handle_t handle_ = nullptr;
+};
+
+// fp32 tensor of up to 4 dimensions in device memory (Prod/GPU/GpuTensor.cs); owns its buffer unless
+// it was made by Reshape (a view, like Prod/GPU/GpuTensor.cs:585-620).
+class GPUTensor {
+ public:
+  GPUTensor(std::vector<int> shape, const float* hostDataOrNull, GPUWrapper& wrapper)
+      : Shape(std::move(shape)), wrapper_(&wrapper), owner_(true) {
+    const size_t bytes = sizeof(float) * static_cast<size_t>(std::max<long long>(Count(), 2));   // min 8 bytes, GpuTensor.cs:38
+    if (cudaMalloc(&ptr_, bytes) != cudaSuccess) throw std::runtime_error("cudaMalloc failed");
+    if (hostDataOrNull) cudaMemcpy(ptr_, hostDataOrNull, sizeof(float) * Count(), cudaMemcpyHostToDevice);
+    else cudaMemset(ptr_, 0, bytes);
+  }
+  ~GPUTensor() { if (owner_ && ptr_) cudaFree(ptr_); }
+  GPUTensor(const GPUTensor&) = delete;
+  GPUTensor& operator=(const GPUTensor&) = delete;
+  GPUTensor(GPUTensor&& o) noexcept : Shape(std::move(o.Shape)), wrapper_(o.wrapper_), ptr_(o.ptr_), owner_(o.owner_) {
+    o.ptr_ = nullptr;
+  }
+
+  std::vector<int> Shape;
+  long long Count() const { return std::accumulate(Shape.begin(), Shape.end(), 1LL, std::multiplies<long long>()); }
+  int MultDim0() const {   // product of the trailing dimensions, Prod/Data/Tensor.cs:1521-1526
+    return static_cast<int>(std::accumulate(Shape.begin() + 1, Shape.end(), 1LL, std::multiplies<long long>()));
+  }
+  float* Pointer() const { return ptr_; }
+  GPUTensor Reshape(std::vector<int> shape) const {
+    GPUTensor v(*this, std::move(shape));
+    return v;
+  }
+  GPUTensor As2DTensor(bool flattenInputTensorOnLastDimension) const {   // Prod/Data/Tensor.cs:1645-1654
+    if (flattenInputTensorOnLastDimension) return Reshape({static_cast<int>(Count() / Shape.back()), Shape.back()});
+    return Reshape({Shape[0], MultDim0()});
+  }
+  std::vector<float> ContentAsFloatArray() const {
+    std::vector<float> out(static_cast<size_t>(Count()));
+    cudaMemcpy(out.data(), ptr_, sizeof(float) * out.size(), cudaMemcpyDeviceToHost);
+    return out;
+  }
+
+  // this = alpha * op(a) * op(b) + beta * this          (Prod/Data/Tensor.cs:388-397, Prod/GPU/GpuTensor.cs:1196-1227)
+  void Dot(const GPUTensor& a, bool transposeA, const GPUTensor& b, bool transposeB, float alpha, float beta) {
+    wrapper_->CheckStatus(snb200_gemm(wrapper_->Handle(), transposeA, transposeB, a.Shape[0], a.MultDim0(), b.Shape[0],
+                                      b.MultDim0(), alpha, a.ptr_, b.ptr_, beta, ptr_));
+  }
+  void Dot(const GPUTensor& a, const GPUTensor& b) { Dot(a, false, b, false, 1.0f, 0.0f); }   // Tensor.cs:60
+  // this[i] = alpha * op(a[i]) * op(b[i]) + beta * this[i]   (Tensor.cs:400-415, GpuTensor.cs:1163-1194)
+  void BatchMatrixMultiplication(const GPUTensor& a_3D, bool transposeA, const GPUTensor& b_3D, bool transposeB,
+                                 float alpha, float beta) {
+    wrapper_->CheckStatus(snb200_batched_gemm(wrapper_->Handle(), transposeA, transposeB, a_3D.Shape[1], a_3D.Shape[2],
+                                              a_3D.MultDim0(), b_3D.Shape[1], b_3D.Shape[2], b_3D.MultDim0(), MultDim0(),
+                                              a_3D.Shape[0], alpha, a_3D.ptr_, b_3D.ptr_, beta, ptr_));
+  }
+  // y[m, :] += this (the bias)                           (Tensor.cs:495, GpuTensor.cs:633-644)
+  void BroadcastAddVectorToOutput(GPUTensor& y) const {
+    wrapper_->CheckStatus(snb200_bias_add(wrapper_->Handle(), y.Shape[0], y.MultDim0(), ptr_, y.ptr_));
+  }
+  // biasGradient[n] = sum_m this[m, n] (this = dy)       (Tensor.cs:710, GpuTensor.cs:686-701)
+  void Compute_BiasGradient_from_dy(GPUTensor& biasGradient_1D) const {
+    wrapper_->CheckStatus(snb200_bias_grad(wrapper_->Handle(), Shape[0], MultDim0(), ptr_, biasGradient_1D.ptr_));
+  }
+  // y = act(this)                                         (Tensor.cs:618, GpuTensor.cs:397-443)
+  void ActivationForward(cudnnActivationMode_t activationType, GPUTensor& y) const {
+    wrapper_->CheckStatus(snb200_activation_fwd(wrapper_->Handle(), static_cast<int>(activationType), Count(), ptr_, y.ptr_));
+  }
+  // this = dx = act'(x, y) * dy                           (Tensor.cs:628, GpuTensor.cs:445-490)
+  void ActivationBackward(cudnnActivationMode_t activationType, const GPUTensor& dy, const GPUTensor* x,
+                          const GPUTensor* y) {
+    wrapper_->CheckStatus(snb200_activation_bwd(wrapper_->Handle(), static_cast<int>(activationType), Count(), dy.ptr_,
+                                                x ? x->ptr_ : nullptr, y ? y->ptr_ : nullptr, ptr_));
+  }
+  // this += alpha * x                                     (Tensor.cs:555, GpuTensor.cs:1359-1362)
+  void Update_Adding_Alpha_X(float alpha, const GPUTensor& x) {
+    wrapper_->CheckStatus(snb200_axpy(wrapper_->Handle(), Count(), alpha, x.ptr_, ptr_));
+  }
+  GPUWrapper& Wrapper() const { return *wrapper_; }
+
+ private:
+  GPUTensor(const GPUTensor& base, std::vector<int> shape)
+      : Shape(std::move(shape)), wrapper_(base.wrapper_), ptr_(base.ptr_), owner_(false) {}
+  GPUWrapper* wrapper_;
+  float* ptr_ = nullptr;
+  bool owner_;
+};
+
+// Static methods of the Dense layer (Prod/Layers/Linear.cs:125-191), weights stored [out, in].
+struct Linear {
+  static void DenseForwardPropagation(GPUTensor& y, const GPUTensor& x, const GPUTensor& weights,
+                                      const GPUTensor* biasIfAny_1D, bool flattenInputTensorOnLastDimension) {
+    GPUTensor x2 = x.As2DTensor(flattenInputTensorOnLastDimension);
+    GPUTensor y2 = y.As2DTensor(flattenInputTensorOnLastDimension);
+    y2.Dot(x2, false, weights, true, 1.0f, 0.0f);
+    if (biasIfAny_1D) biasIfAny_1D->BroadcastAddVectorToOutput(y2);
+  }
+  static void DenseBackwardPropagation(GPUTensor* dx, GPUTensor& weightGradients, GPUTensor* biasGradients_1D,
+                                       const GPUTensor& x, const GPUTensor& dy, const GPUTensor& weights,
+                                       float multiplier, bool prevLayerIsInputLayer,
+                                       bool flattenInputTensorOnLastDimension) {
+    GPUTensor x2 = x.As2DTensor(flattenInputTensorOnLastDimension);
+    GPUTensor dy2 = dy.As2DTensor(flattenInputTensorOnLastDimension);
+    weightGradients.Dot(dy2, true, x2, false, multiplier, 0.0f);
+    if (biasGradients_1D) dy2.Compute_BiasGradient_from_dy(*biasGradients_1D);
+    if (prevLayerIsInputLayer || !dx) return;
+    GPUTensor dx2 = dx->As2DTensor(flattenInputTensorOnLastDimension);
+    dx2.Dot(dy2, false, weights, false, 1.0f, 0.0f);
+  }
+  // Dense + following ActivationLayer in one call each way (snb200_dense_fwd / snb200_dense_bwd).
+  static void FusedForward(GPUTensor& y, const GPUTensor& x, const GPUTensor& weights, const GPUTensor* bias,
+                           cudnnActivationMode_t act, GPUTensor* z) {
+    GPUWrapper& w = y.Wrapper();
+    w.CheckStatus(snb200_dense_fwd(w.Handle(), SNB200_W_OUT_IN, x.Shape[0], x.MultDim0(), y.MultDim0(), x.Pointer(),
+                                   weights.Pointer(), bias ? bias->Pointer() : nullptr, static_cast<int>(act),
+                                   z ? z->Pointer() : nullptr, y.Pointer()));
+  }
+  static void FusedBackward(GPUTensor* dx, GPUTensor& dW, GPUTensor* db, const GPUTensor& x, const GPUTensor& dy,
+                            const GPUTensor& weights, cudnnActivationMode_t act, const GPUTensor* y, const GPUTensor* z,
+                            float multiplier, GPUTensor* dzScratch) {
+    GPUWrapper& w = dW.Wrapper();
+    w.CheckStatus(snb200_dense_bwd(w.Handle(), SNB200_W_OUT_IN, x.Shape[0], x.MultDim0(), dy.MultDim0(), x.Pointer(),
+                                   weights.Pointer(), dy.Pointer(), static_cast<int>(act), y ? y->Pointer() : nullptr,
+                                   z ? z->Pointer() : nullptr, multiplier, dzScratch ? dzScratch->Pointer() : nullptr,
+                                   dx ? dx->Pointer() : nullptr, dW.Pointer(), db ? db->Pointer() : nullptr));
+  }
+};
+
+}  // namespace SharpNet

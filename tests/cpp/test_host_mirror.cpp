@@ -1,0 +1,142 @@
+// Drives the C ABI from compiled host code through the C++ mirror of SharpNet's tensor API, the way
+// the C# shim would: the reference's exact Dot cases (Tests/GPU/TestGpuTensor.cs:50-120, 1e-9), a
+// differential Dot / BatchMatrixMultiplication case against a double-precision host loop, and the
+// Dense forward / backward call sequence of Prod/Layers/Linear.cs against the fused entry points.
+// Prints "OK <n checks>" and exits 0, or the first mismatch and exits 1.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+
+#include "../../sharpnet_b200/host/sharpnet_tensor.hpp"
+
+using namespace SharpNet;
+
+static int g_checks = 0;
+#define EXPECT(cond, ...)                                             \
+  do {                                                                \
+    ++g_checks;                                                       \
+    if (!(cond)) { std::printf("FAILED %s:%d: ", __FILE__, __LINE__); std::printf(__VA_ARGS__); std::printf("\n"); std::exit(1); } \
+  } while (0)
+
+static std::vector<float> uniform(size_t n, float lo, float hi, unsigned seed) {
+  std::mt19937 g(seed);
+  std::uniform_real_distribution<float> d(lo, hi);
+  std::vector<float> v(n);
+  for (auto& x : v) x = d(g);
+  return v;
+}
+// C[m, n] = alpha * sum_k opA(m, k) * opB(k, n) + beta * C[m, n] in double
+static std::vector<double> ref_gemm(const std::vector<float>& A, int aH, int aW, bool tA, const std::vector<float>& B,
+                                    int bH, int bW, bool tB, const std::vector<float>& C, double alpha, double beta) {
+  const int M = tA ? aW : aH, N = tB ? bH : bW, K = tA ? aH : aW;
+  std::vector<double> out(static_cast<size_t>(M) * N);
+  for (int m = 0; m < M; ++m)
+    for (int n = 0; n < N; ++n) {
+      double s = 0;
+      for (int k = 0; k < K; ++k) {
+        const double a = tA ? A[static_cast<size_t>(k) * aW + m] : A[static_cast<size_t>(m) * aW + k];
+        const double b = tB ? B[static_cast<size_t>(n) * bW + k] : B[static_cast<size_t>(k) * bW + n];
+        s += a * b;
+      }
+      out[static_cast<size_t>(m) * N + n] = alpha * s + beta * C[static_cast<size_t>(m) * N + n];
+    }
+  return out;
+}
+static double max_abs_diff(const std::vector<float>& got, const std::vector<double>& want) {
+  double d = 0;
+  for (size_t i = 0; i < got.size(); ++i) d = std::fmax(d, std::fabs(got[i] - want[i]));
+  return d;
+}
+
+int main() {
+  GPUWrapper gpu(0);
+  {  // exact cases of the reference
+    float a1[] = {2}, b1[] = {5};
+    GPUTensor a({1, 1}, a1, gpu), b({1, 1}, b1, gpu), r({1, 1}, nullptr, gpu);
+    r.Dot(a, false, b, false, 1, 0);
+    EXPECT(std::fabs(r.ContentAsFloatArray()[0] - 10.0f) < 1e-9, "1x1");
+    float a2[] = {1, 2, 3, 4};
+    GPUTensor A2({2, 2}, a2, gpu), B2({2, 2}, a2, gpu), R2({2, 2}, nullptr, gpu);
+    R2.Dot(A2, B2);
+    const float want2[] = {7, 10, 15, 22};
+    auto got2 = R2.ContentAsFloatArray();
+    for (int i = 0; i < 4; ++i) EXPECT(std::fabs(got2[i] - want2[i]) < 1e-9, "2x2 element %d", i);
+    float a3[] = {1, 2}, b3[] = {3, 4};
+    GPUTensor A3({2, 1, 1}, a3, gpu), B3({1, 1, 2}, b3, gpu), R3({2, 2}, nullptr, gpu);   // 3-D inputs flattened
+    R3.Dot(A3, false, B3, false, 1, 0);
+    const float want3[] = {3, 4, 6, 8};
+    auto got3 = R3.ContentAsFloatArray();
+    for (int i = 0; i < 4; ++i) EXPECT(std::fabs(got3[i] - want3[i]) < 1e-9, "2x1x1 * 1x1x2 element %d", i);
+  }
+  for (int mode = 0; mode < 3; ++mode) {  // every math mode, every transposition, beta = 1
+    gpu.SetMathMode(mode);
+    const double tol = (mode == 1 ? 2e-3 : 1e-5);
+    const int M = 200, N = 328, K = 100;
+    unsigned seed = 1;
+    for (int tA = 0; tA < 2; ++tA)
+      for (int tB = 0; tB < 2; ++tB) {
+        const int aH = tA ? K : M, aW = tA ? M : K, bH = tB ? N : K, bW = tB ? K : N;
+        auto a = uniform(static_cast<size_t>(aH) * aW, -1, 1, seed++), b = uniform(static_cast<size_t>(bH) * bW, -1, 1, seed++);
+        auto c = uniform(static_cast<size_t>(M) * N, -1, 1, seed++);
+        GPUTensor A({aH, aW}, a.data(), gpu), B({bH, bW}, b.data(), gpu), C({M, N}, c.data(), gpu);
+        C.Dot(A, tA, B, tB, 0.5f, 1.0f);
+        const double e = max_abs_diff(C.ContentAsFloatArray(), ref_gemm(a, aH, aW, tA, b, bH, bW, tB, c, 0.5, 1.0)) / std::sqrt(K);
+        EXPECT(e <= tol, "Dot mode %d tA %d tB %d: scaled error %.3e", mode, tA, tB, e);
+      }
+  }
+  gpu.SetMathMode(0);
+  {  // BatchMatrixMultiplication, batch 3, 12x12 * (12x7)^T ... as Tests/TestParallelRunCpuVersusGpu.cs:377-401
+    const int nb = 3, L = 12, D = 7;
+    auto dy = uniform(nb * L * D, -1.5f, 1.5f, 50), V = uniform(nb * L * D, -1.5f, 1.5f, 51);
+    GPUTensor DY({nb, L, D}, dy.data(), gpu), Vt({nb, L, D}, V.data(), gpu), W({nb, L, L}, nullptr, gpu);
+    W.BatchMatrixMultiplication(DY, false, Vt, true, 0.25f, 0.0f);
+    auto got = W.ContentAsFloatArray();
+    for (int i = 0; i < nb; ++i) {
+      std::vector<float> a(dy.begin() + i * L * D, dy.begin() + (i + 1) * L * D), b(V.begin() + i * L * D, V.begin() + (i + 1) * L * D);
+      std::vector<float> c(L * L, 0.0f), g(got.begin() + i * L * L, got.begin() + (i + 1) * L * L);
+      EXPECT(max_abs_diff(g, ref_gemm(a, L, D, false, b, L, D, true, c, 0.25, 0.0)) < 1e-5, "batched matrix %d", i);
+    }
+  }
+  {  // Dense: the Linear.cs sequence (Dot, bias add, activation) against the fused call, forward and backward
+    const int M = 256, K = 192, N = 128;
+    auto x = uniform(M * K, -2, 2, 60), W = uniform(N * K, -0.1f, 0.1f, 61), b = uniform(N, -0.5f, 0.5f, 62), dy = uniform(M * N, -2, 2, 63);
+    GPUTensor X({M, K}, x.data(), gpu), Wt({N, K}, W.data(), gpu), Bt({N}, b.data(), gpu), DY({M, N}, dy.data(), gpu);
+    GPUTensor z1({M, N}, nullptr, gpu), y1({M, N}, nullptr, gpu), z2({M, N}, nullptr, gpu), y2({M, N}, nullptr, gpu);
+    Linear::DenseForwardPropagation(z1, X, Wt, &Bt, false);
+    z1.ActivationForward(cudnnActivationMode_t::CUDNN_ACTIVATION_SWISH, y1);
+    Linear::FusedForward(y2, X, Wt, &Bt, cudnnActivationMode_t::CUDNN_ACTIVATION_SWISH, &z2);
+    auto a1 = y1.ContentAsFloatArray(), a2 = y2.ContentAsFloatArray();
+    for (size_t i = 0; i < a1.size(); ++i) EXPECT(a1[i] == a2[i], "fused forward differs at %zu", i);
+    std::vector<float> zeros(M * N, 0.0f);
+    auto zref = ref_gemm(x, M, K, false, W, N, K, true, zeros, 1.0, 0.0);
+    for (int m = 0; m < M; ++m) for (int n = 0; n < N; ++n) zref[m * N + n] += b[n];
+    EXPECT(max_abs_diff(z2.ContentAsFloatArray(), zref) / std::sqrt(K) < 1e-5, "pre-activation vs double");
+    GPUTensor dz1({M, N}, nullptr, gpu), dx1({M, K}, nullptr, gpu), dW1({N, K}, nullptr, gpu), db1({N}, nullptr, gpu);
+    dz1.ActivationBackward(cudnnActivationMode_t::CUDNN_ACTIVATION_SWISH, DY, &z1, &y1);
+    Linear::DenseBackwardPropagation(&dx1, dW1, &db1, X, dz1, Wt, 1.0f / M, false, false);
+    GPUTensor dz2({M, N}, nullptr, gpu), dx2({M, K}, nullptr, gpu), dW2({N, K}, nullptr, gpu), db2({N}, nullptr, gpu);
+    Linear::FusedBackward(&dx2, dW2, &db2, X, DY, Wt, cudnnActivationMode_t::CUDNN_ACTIVATION_SWISH, &y2, &z2, 1.0f / M, &dz2);
+    auto w1 = dW1.ContentAsFloatArray(), w2 = dW2.ContentAsFloatArray();
+    for (size_t i = 0; i < w1.size(); ++i) EXPECT(w1[i] == w2[i], "fused dW differs at %zu", i);
+    auto g1 = dx1.ContentAsFloatArray(), g2 = dx2.ContentAsFloatArray();
+    for (size_t i = 0; i < g1.size(); ++i) EXPECT(g1[i] == g2[i], "fused dx differs at %zu", i);
+    auto dzv = dz2.ContentAsFloatArray();
+    auto dWref = ref_gemm(dzv, M, N, true, x, M, K, false, std::vector<float>(N * K, 0.0f), 1.0 / M, 0.0);
+    EXPECT(max_abs_diff(w2, dWref) * M / std::sqrt(M) / 8.0 < 1e-5, "dW vs double");
+    auto dbv = db2.ContentAsFloatArray();
+    for (int n = 0; n < N; ++n) {
+      double s = 0;
+      for (int m = 0; m < M; ++m) s += dzv[m * N + n];
+      EXPECT(std::fabs(dbv[n] - s) < 1e-3, "db[%d]", n);
+    }
+  }
+  {  // errors surface as exceptions, like GPUWrapper.CheckStatus
+    GPUTensor A({4, 3}, nullptr, gpu), B({5, 4}, nullptr, gpu), C({4, 4}, nullptr, gpu);
+    bool thrown = false;
+    try { C.Dot(A, false, B, false, 1, 0); } catch (const std::runtime_error&) { thrown = true; }
+    EXPECT(thrown, "mismatched inner dimensions must throw");
+  }
+  std::printf("OK %d checks\n", g_checks);
+  return 0;
+}
