@@ -174,6 +174,26 @@ int snb200_activation_bwd(snb200_handle_t handle, int act, long long count, cons
  * Prod/GPU/GpuTensor.cs:1359-1362); used for weight decay on dW (Prod/Layers/Linear.cs:176). */
 int snb200_axpy(snb200_handle_t handle, long long count, float alpha, const float* x, float* y);
 
+/* ---- optimizer updates (the step right after the path in every training iteration) -----------
+ * One kernel, one pass over the tensors.
+ * SGD:  velocity = momentum * velocity - learning_rate * dW ;
+ *       W += nesterov ? momentum * velocity - learning_rate * dW : velocity.
+ * Replaces Tensor.UpdateSGDOptimizer (Prod/GPU/GpuTensor.cs:1147-1161: cudnnAddTensor + one or two
+ * axpy passes; Prod/CPU/CpuTensor.cs:470-489) as called by Sgd.UpdateWeights
+ * (Prod/Optimizers/Sgd.cs:43-52).  velocity == NULL gives W -= learning_rate * dW, the VanillaSgd
+ * update (Prod/Optimizers/VanillaSgd.cs:12-21).  learning_rate is the already "pondered" rate
+ * lr / batchSize (Prod/Optimizers/Optimizer.cs:26-29). */
+int snb200_sgd_update(snb200_handle_t handle, long long count, float learning_rate, float momentum, int nesterov,
+                      const float* dW, float* W, float* velocity);
+/* Adam / AdamW:  v = beta1 v + (1 - beta1) dW ; s = beta2 s + (1 - beta2) dW^2 ;
+ *       W -= lr * sqrt(1 - beta2^t) / (1 - beta1^t) * v / (sqrt(s) + epsilon) + weight_decay * W.
+ * Replaces Tensor.UpdateAdamOptimizer (Prod/GPU/GpuTensor.cs:1136-1145 -> NVRTC kernel
+ * Prod/GPU/Kernels/SinglePrecision.cu:19-28; Prod/CPU/CpuTensor.cs:1755-1769) as called by
+ * Adam.UpdateWeights (Prod/Optimizers/Adam.cs:59-72); weight_decay is the pondered decay of :67. */
+int snb200_adam_update(snb200_handle_t handle, long long count, double learning_rate, double beta1, double beta2,
+                       double epsilon, double weight_decay, int time_step, const float* dW, float* W, float* adam_vW,
+                       float* adam_sW);
+
 /* ---- data-parallel gradient sum -------------------------------------------------------------
  * Sum of the per-replica dW/db buffers, left on every replica.  Replaces the
  * copy-to-master-and-add loop of Network.AddGradientFromSlaveNetwork

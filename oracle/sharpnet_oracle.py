@@ -158,6 +158,36 @@ def activation_backward(act, dy, x, y):
     raise ValueError(f"activation {act} is not on the path")
 
 
+def update_sgd_optimizer(W, learning_rate, momentum, nesterov, dW, velocity):
+    """In place, fp32, element by element as CpuTensor.UpdateSGDOptimizer does
+    (Prod/CPU/CpuTensor.cs:470-489).  velocity None: the VanillaSgd update (Prod/Optimizers/VanillaSgd.cs:18-20)."""
+    lr, mom = np.float32(learning_rate), np.float32(momentum)
+    if velocity is None:
+        W += (-lr) * dW
+        return W
+    velocity[...] = (mom * velocity) - (dW * lr)
+    if nesterov:
+        W += mom * velocity - (dW * lr)
+    else:
+        W += velocity
+    return W
+
+
+def update_adam_optimizer(W, learning_rate, beta1, beta2, epsilon, weight_decay, dW, adam_vW, adam_sW, time_step):
+    """In place; every expression in double then cast to float, as CpuTensor.UpdateAdamOptimizer does
+    (Prod/CPU/CpuTensor.cs:1755-1769)."""
+    b1p, b2p = beta1 ** time_step, beta2 ** time_step
+    dw = dW.astype(np.float64)
+    adam_vW[...] = (beta1 * adam_vW.astype(np.float64) + (1 - beta1) * dw).astype(np.float32)
+    adam_sW[...] = (beta2 * adam_sW.astype(np.float64) + (1 - beta2) * dw * dw).astype(np.float32)
+    factor = learning_rate * (math.sqrt(1.0 - b2p) / (1.0 - b1p))
+    w = W.astype(np.float64)
+    with np.errstate(invalid="ignore"):
+        W[...] = (w - (factor * (adam_vW.astype(np.float64) / (np.sqrt(adam_sW.astype(np.float64)) + epsilon))
+                       + weight_decay * w)).astype(np.float32)
+    return W
+
+
 # --------------------------------------------------------------------------------------------
 # Dense layer
 # --------------------------------------------------------------------------------------------

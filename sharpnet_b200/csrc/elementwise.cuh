@@ -120,4 +120,45 @@ static __global__ void colsum_finish_kernel(int N, int slabs, const float* __res
   db[col] = t;
 }
 
+// ---------------------------------------------------------------- optimizer updates
+// One pass each over the parameter tensors; SharpNet's GPU path makes two or three
+// (cudnnAddTensor + axpy, Prod/GPU/GpuTensor.cs:1147-1161) or launches an NVRTC kernel
+// (UpdateAdamOptimizer, Prod/GPU/Kernels/SinglePrecision.cu:19-28).
+
+// velocity = momentum * velocity - lr * dW ;  W += nesterov ? momentum * velocity - lr * dW : velocity
+// (Prod/CPU/CpuTensor.cs:470-489).  velocity == nullptr: plain W -= lr * dW (Prod/Optimizers/VanillaSgd.cs:18-20).
+static __global__ void sgd_update_kernel(long long n, float lr, float momentum, int nesterov,
+                                         const float* __restrict__ dW, float* __restrict__ W,
+                                         float* __restrict__ velocity) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+    const float g = dW[i];
+    if (velocity == nullptr) {
+      W[i] = fmaf(-lr, g, W[i]);
+    } else {
+      const float v = momentum * velocity[i] - g * lr;
+      velocity[i] = v;
+      W[i] += nesterov ? (momentum * v - g * lr) : v;
+    }
+  }
+}
+
+// v = beta1 v + (1 - beta1) dW ; s = beta2 s + (1 - beta2) dW^2 ;
+// W -= factor * v / (sqrt(s) + eps) + weight_decay * W, factor = lr * sqrt(1 - beta2^t) / (1 - beta1^t) computed
+// by the host in double (Prod/GPU/GpuTensor.cs:1136-1145, Prod/CPU/CpuTensor.cs:1755-1769).
+static __global__ void adam_update_kernel(long long n, float beta1, float beta2, float eps, float weight_decay,
+                                          float factor, const float* __restrict__ dW, float* __restrict__ W,
+                                          float* __restrict__ vW, float* __restrict__ sW) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+    const float g = dW[i];
+    const float v = beta1 * vW[i] + (1.0f - beta1) * g;
+    const float s = beta2 * sW[i] + (1.0f - beta2) * g * g;
+    vW[i] = v;
+    sW[i] = s;
+    const float w = W[i];
+    W[i] = w - ((factor * v) / (sqrtf(s) + eps) + weight_decay * w);
+  }
+}
+
 }  // namespace snb

@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
+#include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -713,6 +714,36 @@ extern "C" int snb200_axpy(snb200_handle_t h, long long count, float alpha, cons
   axpy_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, alpha, x, y);
   note_kernel(h, "axpy", 1);
   return check_launch(h, "axpy launch");
+}
+
+extern "C" int snb200_sgd_update(snb200_handle_t h, long long count, float learning_rate, float momentum, int nesterov,
+                                 const float* dW, float* W, float* velocity) {
+  int st = enter(h);
+  if (st) return st;
+  if (count < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative count");
+  if (count == 0) return 0;
+  if (!dW || !W) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  sgd_update_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, learning_rate, momentum, nesterov ? 1 : 0, dW, W,
+                                                                  velocity);
+  note_kernel(h, "sgd_update", 1);
+  return check_launch(h, "sgd_update launch");
+}
+
+extern "C" int snb200_adam_update(snb200_handle_t h, long long count, double learning_rate, double beta1, double beta2,
+                                  double epsilon, double weight_decay, int time_step, const float* dW, float* W,
+                                  float* adam_vW, float* adam_sW) {
+  int st = enter(h);
+  if (st) return st;
+  if (count < 0 || time_step < 1) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative count or time step below 1");
+  if (count == 0) return 0;
+  if (!dW || !W || !adam_vW || !adam_sW) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  const double b1p = pow(beta1, time_step), b2p = pow(beta2, time_step);
+  const double factor = learning_rate * (sqrt(1.0 - b2p) / (1.0 - b1p));
+  adam_update_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(
+      count, static_cast<float>(beta1), static_cast<float>(beta2), static_cast<float>(epsilon),
+      static_cast<float>(weight_decay), static_cast<float>(factor), dW, W, adam_vW, adam_sW);
+  note_kernel(h, "adam_update", 1);
+  return check_launch(h, "adam_update launch");
 }
 
 // ------------------------------------------------------------------------------------ NCCL (loaded at run time)

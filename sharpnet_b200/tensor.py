@@ -193,3 +193,18 @@ class GPUTensor:
         assert x.Count == self.Count
         w = self.wrapper
         check(w.handle, w.lib.snb200_axpy(w.handle, self.Count, float(alpha), x.Pointer, self.Pointer))
+
+    def UpdateSGDOptimizer(self, learningRate, momentum, nesterov, dW, velocity):
+        """this = W: SGD with momentum   (Prod/GPU/GpuTensor.cs:1147-1161, Prod/CPU/CpuTensor.cs:470-489).
+        ``velocity`` None gives the VanillaSgd update W -= learningRate * dW."""
+        w = self.wrapper
+        check(w.handle, w.lib.snb200_sgd_update(w.handle, self.Count, float(learningRate), float(momentum),
+                                                int(bool(nesterov)), dW.Pointer, self.Pointer,
+                                                None if velocity is None else velocity.Pointer))
+
+    def UpdateAdamOptimizer(self, learningRate, beta1, beta2, epsilon, weight_decay, dW, adam_vW, adam_sW, timeStep):
+        """this = W: Adam / AdamW   (Prod/GPU/GpuTensor.cs:1136-1145, Prod/CPU/CpuTensor.cs:1755-1769)."""
+        w = self.wrapper
+        check(w.handle, w.lib.snb200_adam_update(w.handle, self.Count, float(learningRate), float(beta1), float(beta2),
+                                                 float(epsilon), float(weight_decay), int(timeStep), dW.Pointer,
+                                                 self.Pointer, adam_vW.Pointer, adam_sW.Pointer))

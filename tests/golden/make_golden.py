@@ -8,7 +8,8 @@ Nothing at test or run time reads the reference: the JSON file is committed.
 Sources (paths inside the reference):
   Tests/GPU/TestGpuTensor.cs:50-120              exact Dot cases (tolerance 1e-9)
   Tests/NonReg/TestNetworkPropagation.cs:24-34   inputs X_1_1_4_4, X_2_1_4_4 and weights W_N_1_4_4
-  Tests/NonReg/TestNetworkPropagation.cs:80-132  Linear + Sigmoid predictions before training ([in,out] weights)
+  Tests/NonReg/TestNetworkPropagation.cs:80-132  Linear + Sigmoid predictions before training and after 10 epochs of
+                                                 VanillaSGD ([in,out] weights)
   Tests/NonReg/ParallelRunWithPyTorch.cs:102-138 Linear(5->3, last-dim flatten)+ReLU+Flatten+Linear(36->3), Mse
   Tests/NonReg/ParallelRunWithPyTorch.cs:179-214 Linear(16->3)+ReLU+Linear(3->3)+Sigmoid, BCE ([out,in] weights)
 """
@@ -86,6 +87,12 @@ def main(ref):
     blk = _between(tnp, "public void TestSigmoidActivation_NCHW_2_1_4_4", "const int num_epochs")
     out["sigmoid_2_1_4_4_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))
     out["sigmoid_2_1_4_4_loss"] = _numbers(re.search(r"TestLossAccuracy\(network, X, Y, ([0-9.]+)", blk).group(1))[0]
+    # predictions and loss after 10 epochs of VanillaSGD (lr 0.1, TensorFlow compatibility mode): pins dW, db, update
+    for key in ("1_1_4_4", "2_1_4_4"):
+        blk = _between(tnp, "public void TestSigmoidActivation_NCHW_" + key, "public void Test" + ("SigmoidActivation_NCHW_2_1_4_4" if key == "1_1_4_4" else "SoftmaxActivation_NCHW_2_1_4_4"))
+        after = blk[blk.index("//predictions after training"):]
+        out[f"sigmoid_{key}_pred_after"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', after).group(1))
+        out[f"sigmoid_{key}_loss_after"] = _numbers(re.search(r"TestLossAccuracy\(network, X, Y, ([0-9.]+)", after).group(1))[0]
     blk = _between(tnp, "public void TestSigmoidActivation_NCHW_1_1_1_1", "const int num_epochs")
     out["sigmoid_1_1_1_1_w"] = _nth_numpy_literal(blk, 0)
     out["sigmoid_1_1_1_1_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))

@@ -214,3 +214,53 @@ def test_dense_argument_errors(wrapper):
     assert lib.snb200_dense_bwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, T.Pointer, ACT_SWISH, T.Pointer, None, 1.0,
                                 T.Pointer, None, T.Pointer, None) == 7
     assert b"pre-activation" in lib.snb200_last_error_string(h)
+
+
+def test_optimizer_updates(wrapper):
+    # Tests/TestParallelRunCpuVersusGpu.cs:944-977: Adam, AdamW (timestep 5) and the four SGD cases on a 32 x 17 tensor
+    rng = np.random.default_rng(21)
+    shape = (32, 17)
+    W0, dW = (rng.uniform(-1.5, 1.5, shape).astype(np.float32) for _ in range(2))
+    for wd in (0.0, 0.0005):
+        vW, sW = rng.uniform(-1.5, 1.5, shape).astype(np.float32), rng.uniform(0, 1.5, shape).astype(np.float32)
+        sW[0, 0] = -0.5            # a negative second moment gives NaN on both sides, as in the reference's random test
+        Wg, dWg, vg, sg = (_t(wrapper, a) for a in (W0, dW, vW, sW))
+        Wg.UpdateAdamOptimizer(0.001, 0.9, 0.999, 1e-8, wd, dWg, vg, sg, 5)
+        Wc, vc, sc = W0.copy(), vW.copy(), sW.copy()
+        orc.update_adam_optimizer(Wc, 0.001, 0.9, 0.999, 1e-8, wd, dW, vc, sc, 5)
+        np.testing.assert_allclose(vg.ContentAsFloatArray(), vc, rtol=2e-6, atol=1e-7)
+        np.testing.assert_allclose(sg.ContentAsFloatArray(), sc, rtol=2e-6, atol=1e-7)
+        np.testing.assert_allclose(Wg.ContentAsFloatArray(), Wc, rtol=2e-6, atol=1e-6, equal_nan=True)
+        assert np.isnan(Wg.ContentAsFloatArray()[0, 0])
+    for nesterov in (True, False):
+        v = rng.uniform(-1.5, 1.5, shape).astype(np.float32)
+        Wg, dWg, vg = (_t(wrapper, a) for a in (W0, dW, v))
+        Wg.UpdateSGDOptimizer(0.1, 0.9, nesterov, dWg, vg)
+        Wc, vc = W0.copy(), v.copy()
+        orc.update_sgd_optimizer(Wc, 0.1, 0.9, nesterov, dW, vc)
+        np.testing.assert_allclose(vg.ContentAsFloatArray(), vc, rtol=1e-6, atol=1e-7)
+        np.testing.assert_allclose(Wg.ContentAsFloatArray(), Wc, rtol=1e-6, atol=1e-6)
+    big = rng.uniform(-1, 1, 1 << 20).astype(np.float32)       # grid-stride path
+    Wg, dWg = _t(wrapper, big), _t(wrapper, big)
+    Wg.UpdateSGDOptimizer(0.5, 0.0, False, dWg, None)
+    np.testing.assert_allclose(Wg.ContentAsFloatArray(), big * np.float32(0.5), rtol=0, atol=1e-7)
+
+
+def test_golden_ten_epochs_of_training(wrapper, golden):
+    # Tests/NonReg/TestNetworkPropagation.cs:80-132: forward, backward and VanillaSGD for 10 epochs through the C ABI;
+    # predictions after training at 1e-6
+    from sharpnet_b200.optimizers import VanillaSgd
+    for key, rows, y_true in (("1_1_4_4", 1, [[1, 0, 0]]), ("2_1_4_4", 2, [[1, 0, 0], [0, 0, 1]])):
+        x = _t(wrapper, np.asarray(golden["X_" + key], np.float32).reshape(rows, 16))
+        W = _t(wrapper, np.asarray(golden["W_N_1_4_4"], np.float32).reshape(16, 3))
+        b = GPUTensor((3,), None, wrapper)
+        y_true = np.asarray(y_true, np.float32)
+        p, dW, db = GPUTensor((rows, 3), None, wrapper), GPUTensor((16, 3), None, wrapper), GPUTensor((3,), None, wrapper)
+        opt = VanillaSgd()
+        for _ in range(10):
+            FusedDenseForward(p, x, W, b, ACT_SIGMOID, w_layout=W_IN_OUT)
+            dy = _t(wrapper, ((p.ContentAsFloatArray() - y_true) / 3).astype(np.float32))   # loss gradient (host side: out of scope)
+            FusedDenseBackward(None, dW, db, x, dy, W, ACT_IDENTITY, multiplier=1.0, w_layout=W_IN_OUT)
+            opt.UpdateWeights(0.1, 0.1, rows, W, dW, b, db)
+        FusedDenseForward(p, x, W, b, ACT_SIGMOID, w_layout=W_IN_OUT)
+        np.testing.assert_allclose(p.ContentAsFloatArray().ravel(), golden[f"sigmoid_{key}_pred_after"], rtol=0, atol=1e-6)

@@ -121,3 +121,42 @@ def test_bias_gradient_and_bias_add():
     ref = y + bias[None, :]
     orc.broadcast_add_vector_to_output(bias, y)
     np.testing.assert_array_equal(y, ref)
+
+
+def _train_10_epochs(x, y_true, W, lr=0.1):
+    # TensorFlow compatibility mode (dW multiplier 1), VanillaSGD with lr / batchSize, sigmoid output layer whose
+    # gradient is folded into the loss gradient (1/numClass)(p - y): Tests/NonReg/TestNetworkPropagation.cs:80-132
+    W, b = W.copy(), np.zeros(W.shape[1], np.float32)
+    for _ in range(10):
+        _, p = orc.dense_forward(x, W, b, orc.ACT_SIGMOID, orc.W_IN_OUT)
+        dy = ((p - y_true) / y_true.shape[1]).astype(np.float32)
+        _, dW, db, _ = orc.dense_backward(x, W, dy, orc.ACT_IDENTITY, None, None, 1.0, orc.W_IN_OUT, need_dx=False)
+        orc.update_sgd_optimizer(W, lr / x.shape[0], 0.0, False, dW, None)
+        orc.update_sgd_optimizer(b, lr / x.shape[0], 0.0, False, db, None)
+    return orc.dense_forward(x, W, b, orc.ACT_SIGMOID, orc.W_IN_OUT)[1]
+
+
+def test_predictions_after_ten_epochs_of_sgd(golden):
+    # pins the backward pass (dW, db) and the VanillaSGD update on the reference's after-training goldens
+    W = np.asarray(golden["W_N_1_4_4"], np.float32).reshape(16, 3)
+    for key, rows, y_true in (("1_1_4_4", 1, [[1, 0, 0]]), ("2_1_4_4", 2, [[1, 0, 0], [0, 0, 1]])):
+        x = np.asarray(golden["X_" + key], np.float32).reshape(rows, 16)
+        y_true = np.asarray(y_true, np.float32)
+        p = _train_10_epochs(x, y_true, W)
+        np.testing.assert_allclose(p.ravel(), golden[f"sigmoid_{key}_pred_after"], rtol=0, atol=1e-6)
+        assert abs(orc.binary_crossentropy(y_true, p) - golden[f"sigmoid_{key}_loss_after"]) < 1e-5
+
+
+def test_optimizer_updates_against_closed_forms():
+    rng = np.random.default_rng(11)
+    W, dW, v = (rng.uniform(-1.5, 1.5, (32, 17)).astype(np.float32) for _ in range(3))
+    W0, v0 = W.copy(), v.copy()
+    orc.update_sgd_optimizer(W, 0.1, 0.9, True, dW, v)
+    v_want = 0.9 * v0.astype(np.float64) - 0.1 * dW
+    np.testing.assert_allclose(v, v_want, rtol=0, atol=1e-6)
+    np.testing.assert_allclose(W, W0 + 0.9 * v_want - 0.1 * dW, rtol=0, atol=1e-6)
+    W = W0.copy()
+    m, s = np.zeros_like(W), np.zeros_like(W)
+    orc.update_adam_optimizer(W, 0.001, 0.9, 0.999, 1e-8, 0.0, dW, m, s, 1)
+    # first Adam step moves every weight by lr * sign(dW) (bias-corrected moments cancel)
+    np.testing.assert_allclose(W0 - W, 0.001 * np.sign(dW), rtol=0, atol=1e-6)
