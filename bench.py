@@ -229,6 +229,44 @@ def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi,
             "operand_sets": n_sets, "calls": calls}
 
 
+def companion_table(w, torch, peaks):
+    """Achieved HBM GB/s of the bandwidth-bound kernels of the path on config-sized tensors
+    (4096 x 4096 fp32 = 64 MiB per tensor; several tensors per call, so every call exceeds the L2)."""
+    import ctypes
+    lib, h = w.lib, w.handle
+    M = N = 4096
+    n = M * N
+    t = [torch.empty(n, dtype=torch.float32, device=w.device).uniform_(0.1, 1.0) for _ in range(6)]
+    db = torch.empty(N, dtype=torch.float32, device=w.device)
+    P = lambda x: ctypes.c_void_p(x.data_ptr())  # noqa: E731
+    f = ctypes.c_float
+    cases = [
+        ("bias_grad 4096x4096", 4 * n, lambda: lib.snb200_bias_grad(h, M, N, P(t[0]), P(db))),
+        ("bias_add 4096x4096", 8 * n, lambda: lib.snb200_bias_add(h, M, N, P(db), P(t[1]))),
+        ("activation_fwd swish", 8 * n, lambda: lib.snb200_activation_fwd(h, 6, n, P(t[0]), P(t[1]))),
+        ("activation_bwd swish", 16 * n, lambda: lib.snb200_activation_bwd(h, 6, n, P(t[2]), P(t[0]), P(t[1]), P(t[3]))),
+        ("axpy", 12 * n, lambda: lib.snb200_axpy(h, n, f(0.5), P(t[0]), P(t[4]))),
+        ("sgd_update momentum", 20 * n, lambda: lib.snb200_sgd_update(h, n, f(1e-3), f(0.9), 0, P(t[0]), P(t[4]), P(t[5]))),
+        ("adam_update", 28 * n, lambda: lib.snb200_adam_update(h, n, 1e-3, 0.9, 0.999, 1e-8, 0.0, 5, P(t[0]), P(t[4]), P(t[5]), P(t[3]))),
+    ]
+    out = []
+    for name, byts, call in cases:
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 20
+        gbs = byts / ms / 1e6
+        out.append({"kernel": name, "ms": round(ms, 4), "gbs": round(gbs, 1), "bound": "hbm",
+                    "roofline_frac": round(gbs / peaks["hbm"], 3)})
+    return out
+
+
 def per_shape_table(w, torch, peaks):
     """TFLOP/s, roofline fraction and error vs fp64 of every Dot / batched shape in BASELINE configs 1-5."""
     import numpy as np
@@ -368,6 +406,7 @@ def run_ours(args):
     d2h = sum(t.numel() for t in db_host) * 4
 
     shapes = per_shape_table(w, torch, peaks) if (world == 1 and not args.no_shapes) else None
+    companions = companion_table(w, torch, peaks) if (world == 1 and not args.no_shapes) else None
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         v, t = time_cpu(CPU_SAMPLE_ROWS, 3)
@@ -387,7 +426,7 @@ def run_ours(args):
             "gpu_launches": launches * world,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak3, "unit": "TFLOP/s",
                          "frac": achieved / peak3, "traffic": None,
-                         "kernel": "umma_gemm_kernel (3xTF32), the 8 GEMM launches of the step",
+                         "kernel": "umma2_gemm_kernel (CTA-pair tcgen05 GEMM, 3xTF32), the 8 GEMM launches of the step",
                          "peak_source": f"{peaks['src']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32) / 3 "
                                         "(three TF32 products per fp32 product); flops counted once (2*M*N*K)",
                          "gemm_ms_per_step": gemm_ms},
@@ -395,6 +434,7 @@ def run_ours(args):
         }
         if shapes is not None:
             line["shapes"] = shapes
+            line["companions"] = companions
         _emit(json.dumps(line))
     if reducer is not None:
         reducer.close()

@@ -115,14 +115,18 @@ class GradientAllReduce:
         check(self.comm_wrapper.handle,
               lib.snb200_comm_init_rank(self.comm_wrapper.handle, world_size, rank, ident))
 
-    def reduce_layer(self, stack, i, compute_stream):
-        """Queues the all-reduce of layer ``i``'s gradients behind the work already on ``compute_stream``."""
+    def reduce_layer(self, stack, i, compute_stream, update=None):
+        """Queues the all-reduce of layer ``i``'s gradients behind the work already on ``compute_stream``.
+        ``update(lib, handle, stack, i)``, when given, queues the optimizer step of that layer on the same
+        side stream right behind the reduction, so it also overlaps the rest of the backward pass."""
         ev = self.torch.cuda.Event()
         ev.record(compute_stream)
         self.stream.wait_event(ev)
         lib, h = self.comm_wrapper.lib, self.comm_wrapper.handle
         check(h, lib.snb200_allreduce_sum(h, stack.dW[i].Pointer, stack.dW[i].Count))
         check(h, lib.snb200_allreduce_sum(h, stack.db[i].Pointer, stack.db[i].Count))
+        if update is not None:
+            update(lib, h, stack, i)
 
     def join(self, compute_stream):
         """Makes ``compute_stream`` wait for every queued all-reduce."""
@@ -183,14 +187,35 @@ class HostStaging:
         self.consumed[i % 2] = ev
 
 
-def training_step(stack, reducer=None, compute_stream=None):
+class SgdUpdate:
+    """The optimizer step of every replica after the gradient sum: W -= lr / globalBatch * dW with optional
+    (Nesterov) momentum -- SharpNet runs it on the master only and then re-broadcasts the parameters
+    (Prod/Networks/Network.cs:1275-1290, NetworkMultiGPUSupport.cs:255); here every replica applies the
+    identical update to identical sums, so no broadcast is needed."""
+
+    def __init__(self, stack, learning_rate, global_batch, momentum=0.0, nesterov=False):
+        self.lr = learning_rate / global_batch          # PonderedLearning, Prod/Optimizers/Optimizer.cs:26-29
+        self.momentum, self.nesterov = momentum, nesterov
+        self.vW = self.vb = None
+        if momentum != 0.0:
+            self.vW = [GPUTensor(t.Shape, None, stack.w) for t in stack.W]
+            self.vb = [GPUTensor(t.Shape, None, stack.w) for t in stack.b]
+
+    def __call__(self, lib, handle, stack, i):
+        for W, g, v in ((stack.W[i], stack.dW[i], self.vW), (stack.b[i], stack.db[i], self.vb)):
+            check(handle, lib.snb200_sgd_update(handle, W.Count, self.lr, self.momentum, int(self.nesterov), g.Pointer,
+                                                W.Pointer, None if v is None else v[i].Pointer))
+
+
+def training_step(stack, reducer=None, compute_stream=None, update=None):
     """One forward + backward of ``stack`` on this replica's rows, with the per-layer gradient
-    all-reduce overlapped when ``reducer`` is given."""
+    all-reduce (and, when ``update`` is given, the optimizer step) overlapped with the backward pass."""
     stack.forward()
     if reducer is None:
-        stack.backward()
+        after = None if update is None else (lambda i: update(stack.w.lib, stack.w.handle, stack, i))
+        stack.backward(after_layer=after)
         return
-    stack.backward(after_layer=lambda i: reducer.reduce_layer(stack, i, compute_stream))
+    stack.backward(after_layer=lambda i: reducer.reduce_layer(stack, i, compute_stream, update))
     reducer.join(compute_stream)
 
 
