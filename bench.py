@@ -231,18 +231,18 @@ def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi,
 
 def companion_table(w, torch, peaks):
     """Achieved HBM GB/s of the bandwidth-bound kernels of the path on config-sized tensors
-    (4096 x 4096 fp32 = 64 MiB per tensor; several tensors per call, so every call exceeds the L2)."""
+    (16384 x 4096 fp32 = 256 MiB per tensor, so every call streams more than the L2 holds)."""
     import ctypes
     lib, h = w.lib, w.handle
-    M = N = 4096
+    M, N = 16384, 4096          # 256 MiB per tensor: every call streams more than the L2 holds
     n = M * N
     t = [torch.empty(n, dtype=torch.float32, device=w.device).uniform_(0.1, 1.0) for _ in range(6)]
     db = torch.empty(N, dtype=torch.float32, device=w.device)
     P = lambda x: ctypes.c_void_p(x.data_ptr())  # noqa: E731
     f = ctypes.c_float
     cases = [
-        ("bias_grad 4096x4096", 4 * n, lambda: lib.snb200_bias_grad(h, M, N, P(t[0]), P(db))),
-        ("bias_add 4096x4096", 8 * n, lambda: lib.snb200_bias_add(h, M, N, P(db), P(t[1]))),
+        ("bias_grad 16384x4096", 4 * n, lambda: lib.snb200_bias_grad(h, M, N, P(t[0]), P(db))),
+        ("bias_add 16384x4096", 8 * n, lambda: lib.snb200_bias_add(h, M, N, P(db), P(t[1]))),
         ("activation_fwd swish", 8 * n, lambda: lib.snb200_activation_fwd(h, 6, n, P(t[0]), P(t[1]))),
         ("activation_bwd swish", 16 * n, lambda: lib.snb200_activation_bwd(h, 6, n, P(t[2]), P(t[0]), P(t[1]), P(t[3]))),
         ("axpy", 12 * n, lambda: lib.snb200_axpy(h, n, f(0.5), P(t[0]), P(t[4]))),

@@ -23,25 +23,66 @@ static __global__ void bias_add_vec4_kernel(long long total4, int N4, const floa
   }
 }
 
+// Element-wise kernels: grid-stride over 16-byte vectors when every pointer is 16-byte aligned
+// (VEC = 4), scalar otherwise (VEC = 1); the last n % 4 elements of the vector form are done one by one.
+template <int VEC> struct Pack;
+template <> struct Pack<4> { typedef float4 type; };
+template <> struct Pack<1> { typedef float type; };
+__device__ __forceinline__ float lane_get(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+__device__ __forceinline__ float lane_get(const float& v, int) { return v; }
+__device__ __forceinline__ void lane_set(float4& v, int i, float x) { if (i == 0) v.x = x; else if (i == 1) v.y = x; else if (i == 2) v.z = x; else v.w = x; }
+__device__ __forceinline__ void lane_set(float& v, int, float x) { v = x; }
+
+template <int VEC>
 static __global__ void activation_fwd_kernel(int act, long long n, const float* __restrict__ x, float* __restrict__ y) {
+  typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
-    y[i] = act_forward(act, x[i]);
-}
-static __global__ void activation_bwd_kernel(int act, long long n, const float* __restrict__ dy, const float* __restrict__ x,
-                                      const float* __restrict__ y, float* __restrict__ dx) {
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
-    const float xv = (act == ACT_SWISH) ? x[i] : 0.0f;
-    const float yv = (act == ACT_IDENTITY) ? 0.0f : y[i];
-    dx[i] = act_backward(act, dy[i], xv, yv);
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nv = n / VEC;
+  for (long long i = tid; i < nv; i += stride) {
+    const P xv = reinterpret_cast<const P*>(x)[i];
+    P yv;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) lane_set(yv, k, act_forward(act, lane_get(xv, k)));
+    reinterpret_cast<P*>(y)[i] = yv;
   }
+  for (long long i = nv * VEC + tid; i < n; i += stride) y[i] = act_forward(act, x[i]);
+}
+template <int VEC>
+static __global__ void activation_bwd_kernel(int act, long long n, const float* __restrict__ dy, const float* __restrict__ x,
+                                             const float* __restrict__ y, float* __restrict__ dx) {
+  typedef typename Pack<VEC>::type P;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nv = n / VEC;
+  const bool need_x = (act == ACT_SWISH), need_y = (act != ACT_IDENTITY);
+  for (long long i = tid; i < nv; i += stride) {
+    const P g = reinterpret_cast<const P*>(dy)[i];
+    P xv = P(), yv = P(), o;
+    if (need_x) xv = reinterpret_cast<const P*>(x)[i];
+    if (need_y) yv = reinterpret_cast<const P*>(y)[i];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) lane_set(o, k, act_backward(act, lane_get(g, k), lane_get(xv, k), lane_get(yv, k)));
+    reinterpret_cast<P*>(dx)[i] = o;
+  }
+  for (long long i = nv * VEC + tid; i < n; i += stride)
+    dx[i] = act_backward(act, dy[i], need_x ? x[i] : 0.0f, need_y ? y[i] : 0.0f);
 }
 // y += alpha * x                                    (Prod/CPU/CpuTensor.cs:1032-1038)
+template <int VEC>
 static __global__ void axpy_kernel(long long n, float alpha, const float* __restrict__ x, float* __restrict__ y) {
+  typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
-    y[i] = fmaf(alpha, x[i], y[i]);
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nv = n / VEC;
+  for (long long i = tid; i < nv; i += stride) {
+    const P xv = reinterpret_cast<const P*>(x)[i];
+    P yv = reinterpret_cast<P*>(y)[i];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) lane_set(yv, k, fmaf(alpha, lane_get(xv, k), lane_get(yv, k)));
+    reinterpret_cast<P*>(y)[i] = yv;
+  }
+  for (long long i = nv * VEC + tid; i < n; i += stride) y[i] = fmaf(alpha, x[i], y[i]);
 }
 
 // Column sums of g[M x N] over a slab of rows, optionally fused with the activation gradient:
@@ -127,37 +168,76 @@ static __global__ void colsum_finish_kernel(int N, int slabs, const float* __res
 
 // velocity = momentum * velocity - lr * dW ;  W += nesterov ? momentum * velocity - lr * dW : velocity
 // (Prod/CPU/CpuTensor.cs:470-489).  velocity == nullptr: plain W -= lr * dW (Prod/Optimizers/VanillaSgd.cs:18-20).
+__device__ __forceinline__ void sgd_one(float lr, float momentum, int nesterov, bool has_v, float g, float& w, float& v) {
+  if (!has_v) { w = fmaf(-lr, g, w); return; }
+  v = momentum * v - g * lr;
+  w += nesterov ? (momentum * v - g * lr) : v;
+}
+template <int VEC>
 static __global__ void sgd_update_kernel(long long n, float lr, float momentum, int nesterov,
                                          const float* __restrict__ dW, float* __restrict__ W,
                                          float* __restrict__ velocity) {
+  typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
-    const float g = dW[i];
-    if (velocity == nullptr) {
-      W[i] = fmaf(-lr, g, W[i]);
-    } else {
-      const float v = momentum * velocity[i] - g * lr;
-      velocity[i] = v;
-      W[i] += nesterov ? (momentum * v - g * lr) : v;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nv = n / VEC;
+  const bool has_v = velocity != nullptr;
+  for (long long i = tid; i < nv; i += stride) {
+    const P g = reinterpret_cast<const P*>(dW)[i];
+    P w = reinterpret_cast<P*>(W)[i];
+    P v = P();
+    if (has_v) v = reinterpret_cast<P*>(velocity)[i];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      float wk = lane_get(w, k), vk = lane_get(v, k);
+      sgd_one(lr, momentum, nesterov, has_v, lane_get(g, k), wk, vk);
+      lane_set(w, k, wk); lane_set(v, k, vk);
     }
+    reinterpret_cast<P*>(W)[i] = w;
+    if (has_v) reinterpret_cast<P*>(velocity)[i] = v;
+  }
+  for (long long i = nv * VEC + tid; i < n; i += stride) {
+    float wk = W[i], vk = has_v ? velocity[i] : 0.0f;
+    sgd_one(lr, momentum, nesterov, has_v, dW[i], wk, vk);
+    W[i] = wk;
+    if (has_v) velocity[i] = vk;
   }
 }
 
 // v = beta1 v + (1 - beta1) dW ; s = beta2 s + (1 - beta2) dW^2 ;
 // W -= factor * v / (sqrt(s) + eps) + weight_decay * W, factor = lr * sqrt(1 - beta2^t) / (1 - beta1^t) computed
 // by the host in double (Prod/GPU/GpuTensor.cs:1136-1145, Prod/CPU/CpuTensor.cs:1755-1769).
+__device__ __forceinline__ void adam_one(float beta1, float beta2, float eps, float wd, float factor, float g, float& w,
+                                         float& v, float& s) {
+  v = beta1 * v + (1.0f - beta1) * g;
+  s = beta2 * s + (1.0f - beta2) * g * g;
+  w = w - ((factor * v) / (sqrtf(s) + eps) + wd * w);
+}
+template <int VEC>
 static __global__ void adam_update_kernel(long long n, float beta1, float beta2, float eps, float weight_decay,
                                           float factor, const float* __restrict__ dW, float* __restrict__ W,
                                           float* __restrict__ vW, float* __restrict__ sW) {
+  typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
-    const float g = dW[i];
-    const float v = beta1 * vW[i] + (1.0f - beta1) * g;
-    const float s = beta2 * sW[i] + (1.0f - beta2) * g * g;
-    vW[i] = v;
-    sW[i] = s;
-    const float w = W[i];
-    W[i] = w - ((factor * v) / (sqrtf(s) + eps) + weight_decay * w);
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nv = n / VEC;
+  for (long long i = tid; i < nv; i += stride) {
+    const P g = reinterpret_cast<const P*>(dW)[i];
+    P w = reinterpret_cast<P*>(W)[i], v = reinterpret_cast<P*>(vW)[i], s = reinterpret_cast<P*>(sW)[i];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      float wk = lane_get(w, k), vk = lane_get(v, k), sk = lane_get(s, k);
+      adam_one(beta1, beta2, eps, weight_decay, factor, lane_get(g, k), wk, vk, sk);
+      lane_set(w, k, wk); lane_set(v, k, vk); lane_set(s, k, sk);
+    }
+    reinterpret_cast<P*>(W)[i] = w;
+    reinterpret_cast<P*>(vW)[i] = v;
+    reinterpret_cast<P*>(sW)[i] = s;
+  }
+  for (long long i = nv * VEC + tid; i < n; i += stride) {
+    float wk = W[i], vk = vW[i], sk = sW[i];
+    adam_one(beta1, beta2, eps, weight_decay, factor, dW[i], wk, vk, sk);
+    W[i] = wk; vW[i] = vk; sW[i] = sk;
   }
 }
 

@@ -645,7 +645,7 @@ extern "C" int snb200_dense_bwd(snb200_handle_t h, int w_layout, int M, int K, i
 // ------------------------------------------------------------------------------------ companions
 static int ew_grid(const snb200_context* h, long long n, int block) {
   long long want = (n + block - 1) / block;
-  const long long cap = static_cast<long long>(h->sm_count) * 8;
+  const long long cap = static_cast<long long>(h->sm_count) * 16;
   if (want > cap) want = cap;
   return static_cast<int>(want < 1 ? 1 : want);
 }
@@ -686,7 +686,10 @@ extern "C" int snb200_activation_fwd(snb200_handle_t h, int act, long long count
   if (!act_supported(act)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "activation %d is not implemented", act);
   if (count == 0) return 0;
   if (!x || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
-  activation_fwd_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(act, count, x, y);
+  if (aligned16(x) && aligned16(y))
+    activation_fwd_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(act, count, x, y);
+  else
+    activation_fwd_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(act, count, x, y);
   note_kernel(h, "activation_fwd", 1);
   return check_launch(h, "activation_fwd launch");
 }
@@ -700,7 +703,10 @@ extern "C" int snb200_activation_bwd(snb200_handle_t h, int act, long long count
   if (count == 0) return 0;
   if (!dy || !dx || (act != ACT_IDENTITY && !y) || (act == ACT_SWISH && !x))
     return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
-  activation_bwd_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(act, count, dy, x, y, dx);
+  if (aligned16(dy) && aligned16(dx) && (!x || aligned16(x)) && (!y || aligned16(y)))
+    activation_bwd_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(act, count, dy, x, y, dx);
+  else
+    activation_bwd_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(act, count, dy, x, y, dx);
   note_kernel(h, "activation_bwd", 1);
   return check_launch(h, "activation_bwd launch");
 }
@@ -711,7 +717,10 @@ extern "C" int snb200_axpy(snb200_handle_t h, long long count, float alpha, cons
   if (count < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative count");
   if (count == 0) return 0;
   if (!x || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
-  axpy_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, alpha, x, y);
+  if (aligned16(x) && aligned16(y))
+    axpy_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(count, alpha, x, y);
+  else
+    axpy_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, alpha, x, y);
   note_kernel(h, "axpy", 1);
   return check_launch(h, "axpy launch");
 }
@@ -723,8 +732,12 @@ extern "C" int snb200_sgd_update(snb200_handle_t h, long long count, float learn
   if (count < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative count");
   if (count == 0) return 0;
   if (!dW || !W) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
-  sgd_update_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, learning_rate, momentum, nesterov ? 1 : 0, dW, W,
-                                                                  velocity);
+  if (aligned16(dW) && aligned16(W) && (!velocity || aligned16(velocity)))
+    sgd_update_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(count, learning_rate, momentum,
+                                                                               nesterov ? 1 : 0, dW, W, velocity);
+  else
+    sgd_update_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, learning_rate, momentum,
+                                                                       nesterov ? 1 : 0, dW, W, velocity);
   note_kernel(h, "sgd_update", 1);
   return check_launch(h, "sgd_update launch");
 }
@@ -739,9 +752,13 @@ extern "C" int snb200_adam_update(snb200_handle_t h, long long count, double lea
   if (!dW || !W || !adam_vW || !adam_sW) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   const double b1p = pow(beta1, time_step), b2p = pow(beta2, time_step);
   const double factor = learning_rate * (sqrt(1.0 - b2p) / (1.0 - b1p));
-  adam_update_kernel<<<ew_grid(h, count, 256), 256, 0, h->stream>>>(
-      count, static_cast<float>(beta1), static_cast<float>(beta2), static_cast<float>(epsilon),
-      static_cast<float>(weight_decay), static_cast<float>(factor), dW, W, adam_vW, adam_sW);
+  const float b1 = static_cast<float>(beta1), b2 = static_cast<float>(beta2), ep = static_cast<float>(epsilon);
+  const float wd = static_cast<float>(weight_decay), fc = static_cast<float>(factor);
+  if (aligned16(dW) && aligned16(W) && aligned16(adam_vW) && aligned16(adam_sW))
+    adam_update_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(count, b1, b2, ep, wd, fc, dW, W, adam_vW,
+                                                                                adam_sW);
+  else
+    adam_update_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, b1, b2, ep, wd, fc, dW, W, adam_vW, adam_sW);
   note_kernel(h, "adam_update", 1);
   return check_launch(h, "adam_update launch");
 }
