@@ -86,7 +86,8 @@ int snb200_get_version(void);
 /* Kernel-selection overrides for experiments and tests (no counterpart in SharpNet).
  * key 3: K extent accumulated inside the tensor core before the sum moves to registers (3xTF32; default 128,
  *        0 = whole K); key 4: CTA-pair kernel (0 automatic, 1 always, 2 never); key 5: split-K and
- *        swapped-operand plans for problems with few tiles (0 automatic, 1 never).
+ *        swapped-operand plans for problems with few tiles (0 automatic, 1 never); key 6: 1 selects the
+ *        16-wide K blocks in 3xTF32 mode instead of the default 32-wide ones (A/B measurements).
  * key 0: path (0 automatic, 1 tensor cores whenever the operands allow TMA, 2 SIMT fp32);
  * key 1: tile width of the tensor-core kernel (0 automatic, else 32, 64, 128 or 256);
  * key 2: 3xTF32 writes the rounded hi plane back to shared memory (1) or lets the

@@ -18,7 +18,7 @@
 using namespace snb;
 
 // ------------------------------------------------------------------------------------ handle
-enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_COUNT = 8 };
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_COUNT = 8 };
 
 struct snb200_context {
   int device;
@@ -316,9 +316,12 @@ static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int
   note_kernel(h, name, 1);
   if (split) {
     switch (bn) {
-      case 256: return launch_umma2_t<Umma2Tile<256, 16, true>>(h, g);
-      case 128: return launch_umma2_t<Umma2Tile<128, 16, true>>(h, g);
-      default: return launch_umma2_t<Umma2Tile<64, 16, true>>(h, g);
+      // 32-wide K blocks: three 64 KB stages beat six 32 KB ones (fewer hand-offs per byte), measured +8..35 %
+      case 256:
+        if (h->tune[TUNE_VARIANT] == 1) return launch_umma2_t<Umma2Tile<256, 16, true>>(h, g);
+        return launch_umma2_t<Umma2Tile<256, 32, true>>(h, g);
+      case 128: return launch_umma2_t<Umma2Tile<128, 32, true>>(h, g);
+      default: return launch_umma2_t<Umma2Tile<64, 32, true>>(h, g);
     }
   }
   switch (bn) {
@@ -335,8 +338,12 @@ static int launch_umma(snb200_handle_t h, const GemmProblem& g, bool split, int 
   note_kernel(h, name, 1);
   if (split) {
     switch (bn) {
-      case 256: return launch_umma_t<UmmaTile<256, 16, true>>(h, g, plan);
-      case 128: return launch_umma_t<UmmaTile<128, 16, true>>(h, g, plan);
+      case 256:
+        if (h->tune[TUNE_VARIANT] == 1) return launch_umma_t<UmmaTile<256, 16, true>>(h, g, plan);
+        return launch_umma_t<UmmaTile<256, 32, true>>(h, g, plan);
+      case 128:
+        if (h->tune[TUNE_VARIANT] == 1) return launch_umma_t<UmmaTile<128, 16, true>>(h, g, plan);
+        return launch_umma_t<UmmaTile<128, 32, true>>(h, g, plan);
       // narrow tiles leave room for 32-wide K blocks: half as many stage hand-offs per unit of K
       case 64: return launch_umma_t<UmmaTile<64, 32, true>>(h, g, plan);
       default: return launch_umma_t<UmmaTile<32, 32, true>>(h, g, plan);
