@@ -55,6 +55,10 @@ enum {
   SNB200_ACT_SWISH = 6
 };
 
+/* Losses whose gradient the library produces (Prod/Data/Tensor.cs:1182-1217): dy = scale * (yPredicted - yExpected)
+ * with scale = 1/numClass, 1 and 2/numClass. */
+enum { SNB200_LOSS_BINARY_CROSSENTROPY = 0, SNB200_LOSS_CATEGORICAL_CROSSENTROPY = 1, SNB200_LOSS_MSE = 2 };
+
 /* Storage of the Dense weight matrix.
  * OUT_IN: W is [out_features, in_features], y = x * W^T   (Prod/Layers/Linear.cs:26-33,130).
  * IN_OUT: W is [in_features, out_features], y = x * W     (the Keras layout the golden network
@@ -139,6 +143,23 @@ int snb200_dense_fwd(snb200_handle_t handle, int w_layout, int M, int K, int N, 
 int snb200_dense_bwd(snb200_handle_t handle, int w_layout, int M, int K, int N, const float* x, const float* W,
                      const float* dy, int act, const float* y, const float* z, float dW_multiplier,
                      float* dz_scratch, float* dx, float* dW, float* db);
+
+/* ---- loss gradient, alone and fused into the last Dense layer's backward ------------------------
+ * dy = scale * (yPredicted - yExpected), [rows x cols].  Replaces
+ * Tensor.ComputeGradientForEvaluationMetric for BinaryCrossentropy, CategoricalCrossentropy and Mse
+ * (Prod/Data/Tensor.cs:1182-1217 -> :1379-1395 copy + cudnnAddTensor, and the MseGradient NVRTC kernel
+ * Prod/GPU/Kernels/SinglePrecision.cu:1008-1020; CPU Prod/CPU/CpuTensor.cs:2458-2475). */
+int snb200_loss_gradient(snb200_handle_t handle, int loss, int rows, int cols, const float* yExpected,
+                         const float* yPredicted, float* dy);
+/* Backward of the output Dense layer straight from the labels: one pass computes
+ * dz = scale * (yPredicted - yExpected) into dz_scratch together with db (its column sums), then dW and dx as in
+ * snb200_dense_bwd.  This folds three passes of SharpNet over the [M x N] output -- the loss gradient
+ * (Tensor.cs:1182-1217), the output ActivationLayer's dy.CopyTo(dx) shortcut
+ * (Prod/Layers/ActivationLayer.cs:60-63) and Compute_BiasGradient_from_dy (Prod/Layers/Linear.cs:160-165) --
+ * into one. */
+int snb200_dense_bwd_from_loss(snb200_handle_t handle, int w_layout, int M, int K, int N, const float* x,
+                               const float* W, int loss, const float* yExpected, const float* yPredicted,
+                               float dW_multiplier, float* dz_scratch, float* dx, float* dW, float* db);
 
 /* ---- Dense companions, callable on their own ------------------------------------------------ */
 /* y[m,n] += bias[n].  Tensor.BroadcastAddVectorToOutput (Prod/Data/Tensor.cs:495,

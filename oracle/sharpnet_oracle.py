@@ -26,6 +26,7 @@ import torch
 # cudnnActivationMode_t values (Prod/GPU/CudnnWrapper.cs:267-281)
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
 W_OUT_IN, W_IN_OUT = 0, 1
+LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
 
 
 # --------------------------------------------------------------------------------------------
@@ -156,6 +157,24 @@ def activation_backward(act, dy, x, y):
     if act == ACT_IDENTITY:
         return dy.copy()
     raise ValueError(f"activation {act} is not on the path")
+
+
+def loss_gradient(loss, y_expected, y_predicted):
+    """dy of the loss w.r.t. the prediction, in fp32 with the reference's operation order:
+    BinaryCrossentropy  m*p - m*y, m = 1/numClass   (Prod/Data/Tensor.cs:1379-1387, AddTensor(-m, y, m));
+    CategoricalCrossentropy  p - y                  (:1389-1395);
+    Mse  (2*(p - y)) / numClass                     (Prod/CPU/CpuTensor.cs:2466-2475)."""
+    p = np.asarray(y_predicted, dtype=np.float32)
+    t = np.asarray(y_expected, dtype=np.float32)
+    n = np.float32(p.shape[-1])
+    if loss == LOSS_BINARY_CROSSENTROPY:
+        m = np.float32(1) / n
+        return (-m) * t + m * p
+    if loss == LOSS_CATEGORICAL_CROSSENTROPY:
+        return p - t
+    if loss == LOSS_MSE:
+        return (np.float32(2) * (p - t)) / n
+    raise ValueError(f"loss {loss} is not on the path")
 
 
 def update_sgd_optimizer(W, learning_rate, momentum, nesterov, dW, velocity):

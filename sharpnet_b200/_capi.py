@@ -16,6 +16,7 @@ STATUS_NAMES = {
 MATH_3XTF32, MATH_TF32, MATH_FP32_SIMT = 0, 1, 2
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
 W_OUT_IN, W_IN_OUT = 0, 1
+LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
 TUNE_FORCE_PATH, TUNE_FORCE_BN, TUNE_REWRITE_HI, TUNE_CHUNK_K, TUNE_PAIR, TUNE_SPLITK = 0, 1, 2, 3, 4, 5
 
 _c = ctypes
@@ -42,6 +43,8 @@ SIGNATURES = {
     "snb200_batched_gemm": (_I, [_H, _I, _I, _I, _I, _L, _I, _I, _L, _L, _I, _F, _P, _P, _F, _P]),
     "snb200_dense_fwd": (_I, [_H, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P]),
     "snb200_dense_bwd": (_I, [_H, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P]),
+    "snb200_loss_gradient": (_I, [_H, _I, _I, _I, _P, _P, _P]),
+    "snb200_dense_bwd_from_loss": (_I, [_H, _I, _I, _I, _I, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P]),
     "snb200_bias_add": (_I, [_H, _I, _I, _P, _P]),
     "snb200_bias_grad": (_I, [_H, _I, _I, _P, _P]),
     "snb200_bias_grad_noalloc": (_I, [_I, _P, _I, _I, _P, _P, _c.c_char_p, _I]),

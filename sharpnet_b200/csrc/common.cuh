@@ -8,6 +8,10 @@ namespace snb {
 
 // Values of cudnnActivationMode_t (Prod/GPU/CudnnWrapper.cs:267-281).
 enum Act : int { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_IDENTITY = 5, ACT_SWISH = 6 };
+// Internal selector of the fused column-sum pass: dz = scale * (yPredicted - yExpected), the gradient of
+// the BinaryCrossentropy / CategoricalCrossentropy / Mse losses (Prod/Data/Tensor.cs:1379-1395,
+// Prod/CPU/CpuTensor.cs:2458-2475).
+constexpr int ACT_LOSS_DIFF = 100;
 
 // One (possibly strided-batched) GEMM  C[b] = epi(alpha * op(A[b]) * op(B[b]) + beta * C[b]).
 // All matrices are dense row-major fp32.

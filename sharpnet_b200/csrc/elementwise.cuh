@@ -88,6 +88,7 @@ static __global__ void axpy_kernel(long long n, float alpha, const float* __rest
 // Column sums of g[M x N] over a slab of rows, optionally fused with the activation gradient:
 //   g = dy                        (FUSE_ACT = false:  db = sum_m dy,  CpuTensor.cs:3343-3362)
 //   g = act'(z, y) * dy -> dz     (FUSE_ACT = true:   ActivationBackward + bias gradient in one pass)
+//   g = scale * (p - t)  -> dz     (FUSE_ACT = true, act = ACT_LOSS_DIFF: loss gradient + bias gradient in one pass)
 // Block = 256 threads = 8 warps; a warp covers 32*VEC consecutive columns, the 8 warps stride over
 // the rows of the slab.  The slab's sums go to partial[slab, N] (or straight to db when there is
 // one slab); colsum_finish_kernel adds the slabs in a fixed order, so results are deterministic.
@@ -95,7 +96,7 @@ template <int VEC, bool FUSE_ACT>
 __global__ void __launch_bounds__(256)
 colsum_slab_kernel(int M, int N, int rows_per_slab, int act, const float* __restrict__ dy,
                    const float* __restrict__ y, const float* __restrict__ z, float* __restrict__ dz,
-                   float* __restrict__ out) {
+                   float* __restrict__ out, float scale = 1.0f) {
   __shared__ float red[8][32 * VEC];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int col = (blockIdx.x * 32 + lane) * VEC;
@@ -127,7 +128,9 @@ colsum_slab_kernel(int M, int N, int rows_per_slab, int act, const float* __rest
           if (act == ACT_SWISH) zv[0] = z[off];
         }
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) g[v] = act_backward(act, g[v], act == ACT_SWISH ? zv[v] : 0.0f, yv[v]);
+        for (int v = 0; v < VEC; ++v)
+          g[v] = (act == ACT_LOSS_DIFF) ? scale * (g[v] - yv[v])      // dy = yPredicted, y = yExpected
+                                        : act_backward(act, g[v], act == ACT_SWISH ? zv[v] : 0.0f, yv[v]);
         if (VEC == 4) {
           *reinterpret_cast<float4*>(dz + off) = make_float4(g[0], g[1], g[2], g[3]);
         } else {
@@ -159,6 +162,24 @@ static __global__ void colsum_finish_kernel(int N, int slabs, const float* __res
   float t = 0.0f;
   for (int s = 0; s < slabs; ++s) t += partial[static_cast<size_t>(s) * N + col];
   db[col] = t;
+}
+
+// dy = scale * (yPredicted - yExpected)
+template <int VEC>
+static __global__ void loss_gradient_kernel(long long n, float scale, const float* __restrict__ expected,
+                                            const float* __restrict__ predicted, float* __restrict__ dy) {
+  typedef typename Pack<VEC>::type P;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nv = n / VEC;
+  for (long long i = tid; i < nv; i += stride) {
+    const P e = reinterpret_cast<const P*>(expected)[i], p = reinterpret_cast<const P*>(predicted)[i];
+    P o;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) lane_set(o, k, scale * (lane_get(p, k) - lane_get(e, k)));
+    reinterpret_cast<P*>(dy)[i] = o;
+  }
+  for (long long i = nv * VEC + tid; i < n; i += stride) dy[i] = scale * (predicted[i] - expected[i]);
 }
 
 // ---------------------------------------------------------------- optimizer updates

@@ -563,7 +563,7 @@ extern "C" int snb200_dense_fwd(snb200_handle_t h, int w_layout, int M, int K, i
 
 template <bool FUSE>
 static int launch_colsum(snb200_handle_t h, int M, int N, int act, const float* dy, const float* y, const float* z,
-                         float* dz, float* db) {
+                         float* dz, float* db, float scale = 1.0f) {
   const bool vec = (N % 4 == 0) && aligned16(dy) && (!FUSE || (aligned16(y) && aligned16(dz) && (!z || aligned16(z))));
   const int cols_per_block = vec ? 128 : 32;
   const int col_blocks = (N + cols_per_block - 1) / cols_per_block;
@@ -581,9 +581,9 @@ static int launch_colsum(snb200_handle_t h, int M, int N, int act, const float* 
   float* out = db ? (slabs == 1 ? db : h->workspace) : nullptr;
   dim3 grid(col_blocks, slabs);
   if (vec)
-    colsum_slab_kernel<4, FUSE><<<grid, 256, 0, h->stream>>>(M, N, rows_per_slab, act, dy, y, z, dz, out);
+    colsum_slab_kernel<4, FUSE><<<grid, 256, 0, h->stream>>>(M, N, rows_per_slab, act, dy, y, z, dz, out, scale);
   else
-    colsum_slab_kernel<1, FUSE><<<grid, 256, 0, h->stream>>>(M, N, rows_per_slab, act, dy, y, z, dz, out);
+    colsum_slab_kernel<1, FUSE><<<grid, 256, 0, h->stream>>>(M, N, rows_per_slab, act, dy, y, z, dz, out, scale);
   int launches = 1;
   if (db && slabs > 1) {
     colsum_finish_kernel<<<(N + 255) / 256, 256, 0, h->stream>>>(N, slabs, h->workspace, db);
@@ -591,6 +591,92 @@ static int launch_colsum(snb200_handle_t h, int M, int N, int act, const float* 
   }
   note_kernel(h, FUSE ? "dz_db_colsum" : "colsum", launches);
   return check_launch(h, "colsum launch");
+}
+
+static int ew_grid(const snb200_context* h, long long n, int block) {
+  long long want = (n + block - 1) / block;
+  const long long cap = static_cast<long long>(h->sm_count) * 16;
+  if (want > cap) want = cap;
+  return static_cast<int>(want < 1 ? 1 : want);
+}
+
+static bool loss_scale(int loss, int N, float* scale) {
+  switch (loss) {
+    case SNB200_LOSS_BINARY_CROSSENTROPY: *scale = 1.0f / N; return true;      // Prod/Data/Tensor.cs:1379-1387
+    case SNB200_LOSS_CATEGORICAL_CROSSENTROPY: *scale = 1.0f; return true;     // :1389-1395
+    case SNB200_LOSS_MSE: *scale = 2.0f / N; return true;                      // Prod/CPU/CpuTensor.cs:2466-2475
+    default: return false;
+  }
+}
+
+// dW and dx of the Dense backward from dz (the gradient w.r.t. the pre-activation).
+static int dense_bwd_gemms(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
+                           const float* dz, float dW_multiplier, float* dx, float* dW) {
+  int st = 0;
+  GemmProblem g;
+  memset(&g, 0, sizeof(g));
+  g.batch = 1; g.act = ACT_IDENTITY; g.beta = 0.0f;
+  // dW, in the layout of W.
+  if (w_layout == SNB200_W_OUT_IN) {   // dW [N x K] = mult * dz^T * x          (Linear.cs:158)
+    g.M = N; g.N = K; g.K = M;
+    g.transA = 1; g.A = dz; g.lda = N;
+    g.transB = 0; g.B = x; g.ldb = K;
+  } else {                             // dW [K x N] = mult * x^T * dz
+    g.M = K; g.N = N; g.K = M;
+    g.transA = 1; g.A = x; g.lda = K;
+    g.transB = 0; g.B = dz; g.ldb = N;
+  }
+  g.C = dW; g.ldc = g.N; g.alpha = dW_multiplier;
+  st = run_gemm(h, g);
+  if (st) return st;
+  if (dx) {
+    g.M = M; g.N = K; g.K = N;
+    g.transA = 0; g.A = dz; g.lda = N;
+    if (w_layout == SNB200_W_OUT_IN) { g.transB = 0; g.B = W; g.ldb = K; }   // dx = dz * W      (Linear.cs:190)
+    else                             { g.transB = 1; g.B = W; g.ldb = N; }   // dx = dz * W^T
+    g.C = dx; g.ldc = K; g.alpha = 1.0f;
+    st = run_gemm(h, g);
+    if (st) return st;
+  }
+  return 0;
+}
+
+extern "C" int snb200_loss_gradient(snb200_handle_t h, int loss, int rows, int cols, const float* yExpected,
+                                    const float* yPredicted, float* dy) {
+  int st = enter(h);
+  if (st) return st;
+  if (rows < 0 || cols < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  float scale;
+  if (!loss_scale(loss, cols, &scale)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "loss %d is not implemented", loss);
+  const long long n = static_cast<long long>(rows) * cols;
+  if (n == 0) return 0;
+  if (!yExpected || !yPredicted || !dy) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  if (aligned16(yExpected) && aligned16(yPredicted) && aligned16(dy))
+    loss_gradient_kernel<4><<<ew_grid(h, n / 4 + 1, 256), 256, 0, h->stream>>>(n, scale, yExpected, yPredicted, dy);
+  else
+    loss_gradient_kernel<1><<<ew_grid(h, n, 256), 256, 0, h->stream>>>(n, scale, yExpected, yPredicted, dy);
+  note_kernel(h, "loss_gradient", 1);
+  return check_launch(h, "loss_gradient launch");
+}
+
+extern "C" int snb200_dense_bwd_from_loss(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x,
+                                          const float* W, int loss, const float* yExpected, const float* yPredicted,
+                                          float dW_multiplier, float* dz_scratch, float* dx, float* dW, float* db) {
+  int st = enter(h);
+  if (st) return st;
+  if (M < 0 || K < 0 || N < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (w_layout != SNB200_W_OUT_IN && w_layout != SNB200_W_IN_OUT)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "unknown weight layout %d", w_layout);
+  float scale;
+  if (!loss_scale(loss, N, &scale)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "loss %d is not implemented", loss);
+  st = check_ptrs(h, x, W, yPredicted);
+  if (st) return st;
+  if (!yExpected || !dz_scratch || !dW) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  if (M > 0 && N > 0) {
+    st = launch_colsum<true>(h, M, N, ACT_LOSS_DIFF, yPredicted, yExpected, nullptr, dz_scratch, db, scale);
+    if (st) return st;
+  }
+  return dense_bwd_gemms(h, w_layout, M, K, N, x, W, dz_scratch, dW_multiplier, dx, dW);
 }
 
 extern "C" int snb200_dense_bwd(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
@@ -620,42 +706,11 @@ extern "C" int snb200_dense_bwd(snb200_handle_t h, int w_layout, int M, int K, i
     st = launch_colsum<false>(h, M, N, act, dy, nullptr, nullptr, nullptr, db);
     if (st) return st;
   }
-  GemmProblem g;
-  memset(&g, 0, sizeof(g));
-  g.batch = 1; g.act = ACT_IDENTITY; g.beta = 0.0f;
-  // dW, in the layout of W.
-  if (w_layout == SNB200_W_OUT_IN) {   // dW [N x K] = mult * dz^T * x          (Linear.cs:158)
-    g.M = N; g.N = K; g.K = M;
-    g.transA = 1; g.A = dz; g.lda = N;
-    g.transB = 0; g.B = x; g.ldb = K;
-  } else {                             // dW [K x N] = mult * x^T * dz
-    g.M = K; g.N = N; g.K = M;
-    g.transA = 1; g.A = x; g.lda = K;
-    g.transB = 0; g.B = dz; g.ldb = N;
-  }
-  g.C = dW; g.ldc = g.N; g.alpha = dW_multiplier;
-  st = run_gemm(h, g);
-  if (st) return st;
-  if (dx) {
-    g.M = M; g.N = K; g.K = N;
-    g.transA = 0; g.A = dz; g.lda = N;
-    if (w_layout == SNB200_W_OUT_IN) { g.transB = 0; g.B = W; g.ldb = K; }   // dx = dz * W      (Linear.cs:190)
-    else                             { g.transB = 1; g.B = W; g.ldb = N; }   // dx = dz * W^T
-    g.C = dx; g.ldc = K; g.alpha = 1.0f;
-    st = run_gemm(h, g);
-    if (st) return st;
-  }
   (void)launches0;
-  return 0;
+  return dense_bwd_gemms(h, w_layout, M, K, N, x, W, dz, dW_multiplier, dx, dW);
 }
 
 // ------------------------------------------------------------------------------------ companions
-static int ew_grid(const snb200_context* h, long long n, int block) {
-  long long want = (n + block - 1) / block;
-  const long long cap = static_cast<long long>(h->sm_count) * 16;
-  if (want > cap) want = cap;
-  return static_cast<int>(want < 1 ? 1 : want);
-}
 
 extern "C" int snb200_bias_add(snb200_handle_t h, int M, int N, const float* bias, float* y) {
   int st = enter(h);

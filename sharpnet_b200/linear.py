@@ -65,3 +65,17 @@ def FusedDenseBackward(dx, weightGradients, biasGradients_1D, x, dy, weights, ac
                                 p(y), p(z), float(multiplier), p(dz_scratch), p(dx), weightGradients.Pointer,
                                 p(biasGradients_1D))
     check(w.handle, st)
+
+
+def FusedDenseBackwardFromLoss(dx, weightGradients, biasGradients_1D, x, yExpected, yPredicted, weights, loss,
+                               multiplier=1.0, dz_scratch=None, w_layout=W_OUT_IN):
+    """Backward of the output Dense layer from the labels: loss gradient + bias gradient in one pass, then dW, dx."""
+    x2 = x.As2DTensor(False)
+    M, K = x2.Shape
+    N = yPredicted.MultDim0
+    w = yPredicted.wrapper
+    p = lambda t: None if t is None else t.Pointer  # noqa: E731
+    st = w.lib.snb200_dense_bwd_from_loss(w.handle, w_layout, M, K, N, x2.Pointer, weights.Pointer, int(loss),
+                                          yExpected.Pointer, yPredicted.Pointer, float(multiplier), p(dz_scratch), p(dx),
+                                          weightGradients.Pointer, p(biasGradients_1D))
+    check(w.handle, st)

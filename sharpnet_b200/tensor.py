@@ -208,3 +208,10 @@ class GPUTensor:
         check(w.handle, w.lib.snb200_adam_update(w.handle, self.Count, float(learningRate), float(beta1), float(beta2),
                                                  float(epsilon), float(weight_decay), int(timeStep), dW.Pointer,
                                                  self.Pointer, adam_vW.Pointer, adam_sW.Pointer))
+
+    def ComputeGradientForEvaluationMetric(self, yExpected, yPredicted, loss):
+        """this = dyPredicted = scale * (yPredicted - yExpected) for BinaryCrossentropy, CategoricalCrossentropy
+        and Mse (Prod/Data/Tensor.cs:1182-1217); ``loss`` is one of the LOSS_* constants."""
+        w = self.wrapper
+        check(w.handle, w.lib.snb200_loss_gradient(w.handle, int(loss), self.Shape[0], self.MultDim0, yExpected.Pointer,
+                                                   yPredicted.Pointer, self.Pointer))

@@ -8,8 +8,9 @@ from oracle import sharpnet_oracle as orc
 from sharpnet_b200 import (ACT_IDENTITY, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH, MATH_3XTF32, MATH_TF32, W_IN_OUT,
                            W_OUT_IN)
 from sharpnet_b200._capi import TUNE_FORCE_PATH
+from sharpnet_b200._capi import LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE
 from sharpnet_b200.linear import (DenseBackwardPropagation, DenseForwardPropagation, FusedDenseBackward,
-                                  FusedDenseForward)
+                                  FusedDenseBackwardFromLoss, FusedDenseForward)
 from sharpnet_b200.tensor import GPUTensor
 
 from gpu_util import TOL_3XTF32, TOL_TF32
@@ -261,6 +262,54 @@ def test_golden_ten_epochs_of_training(wrapper, golden):
             FusedDenseForward(p, x, W, b, ACT_SIGMOID, w_layout=W_IN_OUT)
             dy = _t(wrapper, ((p.ContentAsFloatArray() - y_true) / 3).astype(np.float32))   # loss gradient (host side: out of scope)
             FusedDenseBackward(None, dW, db, x, dy, W, ACT_IDENTITY, multiplier=1.0, w_layout=W_IN_OUT)
+            opt.UpdateWeights(0.1, 0.1, rows, W, dW, b, db)
+        FusedDenseForward(p, x, W, b, ACT_SIGMOID, w_layout=W_IN_OUT)
+        np.testing.assert_allclose(p.ContentAsFloatArray().ravel(), golden[f"sigmoid_{key}_pred_after"], rtol=0, atol=1e-6)
+
+
+def test_loss_gradients_alone_and_fused_into_the_output_layer(wrapper):
+    # dy = scale (p - t) for BCE / CCE / Mse against the reference's operation order, then the fused
+    # "loss gradient + bias gradient + dW + dx" call against the three-step sequence on the same inputs
+    rng = np.random.default_rng(31)
+    for (M, K, N) in ((2, 16, 3), (37, 20, 10), (512, 256, 128)):
+        x = orc.normal((M, K), 0, 1, M)
+        Wl = orc.glorot_uniform((N, K), M + 1)
+        p = rng.uniform(0.01, 0.99, (M, N)).astype(np.float32)
+        t = (rng.uniform(0, 1, (M, N)) > 0.7).astype(np.float32)
+        X, W, P, T = (_t(wrapper, a) for a in (x, Wl, p, t))
+        for loss in (LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE):
+            DY = GPUTensor((M, N), None, wrapper)
+            DY.ComputeGradientForEvaluationMetric(T, P, loss)
+            want = orc.loss_gradient(loss, t, p)
+            np.testing.assert_allclose(DY.ContentAsFloatArray(), want, rtol=1e-6, atol=1e-7)
+            dx1, dW1, db1 = GPUTensor((M, K), None, wrapper), GPUTensor((N, K), None, wrapper), GPUTensor((N,), None, wrapper)
+            DenseBackwardPropagation(dx1, dW1, db1, X, DY, W, multiplier=1.0)
+            dz, dx2 = GPUTensor((M, N), None, wrapper), GPUTensor((M, K), None, wrapper)
+            dW2, db2 = GPUTensor((N, K), None, wrapper), GPUTensor((N,), None, wrapper)
+            FusedDenseBackwardFromLoss(dx2, dW2, db2, X, T, P, W, loss, multiplier=1.0, dz_scratch=dz)
+            np.testing.assert_array_equal(dz.ContentAsFloatArray(), DY.ContentAsFloatArray())
+            np.testing.assert_array_equal(dW1.ContentAsFloatArray(), dW2.ContentAsFloatArray())
+            np.testing.assert_array_equal(dx1.ContentAsFloatArray(), dx2.ContentAsFloatArray())
+            np.testing.assert_allclose(db1.ContentAsFloatArray(), db2.ContentAsFloatArray(), rtol=0, atol=1e-5)
+            _, dW64, db64, _ = orc.dense_backward(x, Wl, want, orc.ACT_IDENTITY, None, None, 1.0, orc.W_OUT_IN, f64=True)
+            assert orc.scaled_error(dW2.ContentAsFloatArray(), dW64, M, 4.0, 2.0) <= TOL_3XTF32
+            assert orc.scaled_error(db2.ContentAsFloatArray(), db64, M, 1.0, 2.0) <= TOL_3XTF32
+
+
+def test_golden_ten_epochs_entirely_on_the_device(wrapper, golden):
+    # the same golden as above with nothing on the host between the steps: fused forward, fused
+    # "loss gradient + backward" and the SGD update, all through the C ABI
+    from sharpnet_b200.optimizers import VanillaSgd
+    for key, rows, y_true in (("1_1_4_4", 1, [[1, 0, 0]]), ("2_1_4_4", 2, [[1, 0, 0], [0, 0, 1]])):
+        x = _t(wrapper, np.asarray(golden["X_" + key], np.float32).reshape(rows, 16))
+        W = _t(wrapper, np.asarray(golden["W_N_1_4_4"], np.float32).reshape(16, 3))
+        T = _t(wrapper, np.asarray(y_true, np.float32))
+        b, p = GPUTensor((3,), None, wrapper), GPUTensor((rows, 3), None, wrapper)
+        dz, dW, db = GPUTensor((rows, 3), None, wrapper), GPUTensor((16, 3), None, wrapper), GPUTensor((3,), None, wrapper)
+        opt = VanillaSgd()
+        for _ in range(10):
+            FusedDenseForward(p, x, W, b, ACT_SIGMOID, w_layout=W_IN_OUT)
+            FusedDenseBackwardFromLoss(None, dW, db, x, T, p, W, LOSS_BINARY_CROSSENTROPY, 1.0, dz, W_IN_OUT)
             opt.UpdateWeights(0.1, 0.1, rows, W, dW, b, db)
         FusedDenseForward(p, x, W, b, ACT_SIGMOID, w_layout=W_IN_OUT)
         np.testing.assert_allclose(p.ContentAsFloatArray().ravel(), golden[f"sigmoid_{key}_pred_after"], rtol=0, atol=1e-6)
