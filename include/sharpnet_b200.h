@@ -196,6 +196,31 @@ int snb200_activation_bwd(snb200_handle_t handle, int act, long long count, cons
  * Prod/GPU/GpuTensor.cs:1359-1362); used for weight decay on dW (Prod/Layers/Linear.cs:176). */
 int snb200_axpy(snb200_handle_t handle, long long count, float alpha, const float* x, float* y);
 
+/* ---- attention around BatchMatrixMultiplication ------------------------------------------------
+ * Row softmax over the last dimension and its gradient.  Replace Tensor.ActivationForward /
+ * ActivationBackward with CUDNN_ACTIVATION_SOFTMAX_LAST_DIMENSION (Prod/GPU/GpuTensor.cs:397-443 ->
+ * cudnnSoftmaxForward, :445-490 -> cudnnSoftmaxBackward; CPU forward
+ * Prod/CPU/CpuTensorActivationFunctions.cs:14-46).  The gradient is the softmax Jacobian
+ * dx = y * (dy - sum(dy * y)), what the GPU path of SharpNet computes; x may equal y, dy may equal dx. */
+int snb200_softmax_fwd(snb200_handle_t handle, long long rows, int cols, const float* x, float* y);
+int snb200_softmax_bwd(snb200_handle_t handle, long long rows, int cols, const float* dy, const float* y, float* dx);
+/* Scaled dot-product attention, Q [batch, q_steps, E], K and V [batch, v_steps, E], y [batch, q_steps, E]:
+ * weights = softmax(mask(scaling * Q K^T)), y = weights V, scaling = use_scale ? 1/sqrt(E) : 1.
+ * Replaces ScaledDotProductAttentionLayer.ScaledDotProductAttentionForwardPropagation
+ * (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-91): two strided-batched GEMMs with, between them, the
+ * causal overwrite (SetAllElementsAboveMainDiagonal, -1e12) and the softmax as ONE in-place pass over
+ * `weights` [batch, q_steps, v_steps] (caller-provided; the layer's _weights_buffer, kept for the backward).
+ * The separate scores buffer of the reference is not needed. */
+int snb200_sdpa_fwd(snb200_handle_t handle, int batch, int q_steps, int v_steps, int embedding_dim, int use_scale,
+                    int is_causal, const float* Q, const float* K, const float* V, float* weights, float* y);
+/* Replaces ScaledDotProductAttentionBackwardPropagation (ScaledDotProductAttentionLayer.cs:108-129):
+ * dV = weights^T dy; dScores = softmax'(scaling * dy V^T) in place in scores_grad_scratch
+ * [batch, q_steps, v_steps] (caller-provided; the reference takes it from its memory pool);
+ * dQ = dScores K; dK = dScores^T Q. */
+int snb200_sdpa_bwd(snb200_handle_t handle, int batch, int q_steps, int v_steps, int embedding_dim, int use_scale,
+                    const float* Q, const float* K, const float* V, const float* dy, const float* weights,
+                    float* scores_grad_scratch, float* dQ, float* dK, float* dV);
+
 /* ---- optimizer updates (the step right after the path in every training iteration) -----------
  * One kernel, one pass over the tensors.
  * SGD:  velocity = momentum * velocity - learning_rate * dW ;

@@ -159,6 +159,69 @@ def activation_backward(act, dy, x, y):
     raise ValueError(f"activation {act} is not on the path")
 
 
+def softmax_last_dimension(x):
+    """Row softmax exactly as CpuTensorActivationFunctions.Softmax computes it
+    (Prod/CPU/CpuTensorActivationFunctions.cs:19-46): row max, exp in double cast to float, fp32 running sum,
+    fp32 division."""
+    x2 = np.asarray(x, dtype=np.float32).reshape(-1, x.shape[-1])
+    out = np.empty_like(x2)
+    for r in range(x2.shape[0]):
+        e = np.exp((x2[r] - x2[r].max()).astype(np.float64)).astype(np.float32)
+        acc = np.float32(0)
+        for v in e:
+            acc = np.float32(acc + v)
+        out[r] = e / acc
+    return out.reshape(x.shape)
+
+
+def softmax_gradient_last_dimension(dy, y, f64=False):
+    """dx = y * (dy - sum_j dy_j y_j): the Jacobian product cudnnSoftmaxBackward(CUDNN_SOFTMAX_ACCURATE,
+    MODE_INSTANCE) applies on SharpNet's GPU path (Prod/GPU/GpuTensor.cs:445-490).  cuDNN's source is not part
+    of the reference; this restates its documented formula.  (SharpNet's CPU shortcut,
+    CpuTensorActivationFunctions.cs:109-121, is a different, loss-specific approximation and is not followed.)"""
+    t = np.float64 if f64 else np.float32
+    g, p = np.asarray(dy, dtype=t), np.asarray(y, dtype=t)
+    return (p * (g - (g * p).sum(axis=-1, keepdims=True))).astype(t)
+
+
+def sdpa_forward(Q, K, V, use_scale, is_causal, f64=False):
+    """Returns (weights, y) of ScaledDotProductAttentionLayer.ScaledDotProductAttentionForwardPropagation
+    (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-91): scores = scaling * Q K^T per batch element,
+    -1e12 above the main diagonal when causal (Prod/CPU/CpuTensor.cs:3037-3052), softmax over the last
+    dimension, y = weights V."""
+    B, Tq, E = Q.shape
+    Tk = K.shape[1]
+    scaling = (1.0 / math.sqrt(E)) if use_scale else 1.0
+    if f64:
+        s = scaling * np.einsum("bqe,bke->bqk", Q.astype(np.float64), K.astype(np.float64))
+    else:
+        s = np.zeros((B, Tq, Tk), dtype=np.float32)
+        batch_matrix_multiplication(Q, False, K, True, s, np.float32(scaling), 0.0)
+    if is_causal:
+        s = s.copy()
+        rows, cols = np.triu_indices(Tq, 1, Tk)
+        s[:, rows, cols] = -1e12
+    if f64:
+        e = np.exp(s - s.max(-1, keepdims=True))
+        w = e / e.sum(-1, keepdims=True)
+        return w, np.einsum("bqk,bke->bqe", w, V.astype(np.float64))
+    w = softmax_last_dimension(s)
+    y = np.zeros((B, Tq, E), dtype=np.float32)
+    batch_matrix_multiplication(w, False, V, False, y, 1.0, 0.0)
+    return w, y
+
+
+def sdpa_backward(Q, K, V, dy, weights, use_scale):
+    """Returns (dQ, dK, dV) in float64 following ScaledDotProductAttentionBackwardPropagation
+    (Prod/Layers/ScaledDotProductAttentionLayer.cs:108-129)."""
+    E = Q.shape[2]
+    scaling = (1.0 / math.sqrt(E)) if use_scale else 1.0
+    Qd, Kd, Vd, g, w = (np.asarray(a, dtype=np.float64) for a in (Q, K, V, dy, weights))
+    dV = np.einsum("bqk,bqe->bke", w, g)
+    ds = softmax_gradient_last_dimension(scaling * np.einsum("bqe,bke->bqk", g, Vd), w, f64=True)
+    return np.einsum("bqk,bke->bqe", ds, Kd), np.einsum("bqk,bqe->bke", ds, Qd), dV
+
+
 def loss_gradient(loss, y_expected, y_predicted):
     """dy of the loss w.r.t. the prediction, in fp32 with the reference's operation order:
     BinaryCrossentropy  m*p - m*y, m = 1/numClass   (Prod/Data/Tensor.cs:1379-1387, AddTensor(-m, y, m));

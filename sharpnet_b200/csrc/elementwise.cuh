@@ -182,6 +182,81 @@ static __global__ void loss_gradient_kernel(long long n, float scale, const floa
   for (long long i = nv * VEC + tid; i < n; i += stride) dy[i] = scale * (predicted[i] - expected[i]);
 }
 
+// ---------------------------------------------------------------- row softmax (attention weights)
+// y[r, :] = softmax(x[r, :]) over the last dimension, one warp per row; `causal_rows` > 0 masks the
+// columns above the main diagonal of every [causal_rows x cols] matrix first, i.e. the -1e12 overwrite of
+// Tensor.SetAllElementsAboveMainDiagonal (Prod/CPU/CpuTensor.cs:3037-3052) that
+// ScaledDotProductAttentionLayer applies before the softmax (Prod/Layers/ScaledDotProductAttentionLayer.cs:73-81),
+// folded into the same pass.  Formula of CpuTensorActivationFunctions.Softmax (Prod/CPU/CpuTensorActivationFunctions.cs:19-46).
+// x may equal y.  Rows of up to 1024 columns stay in registers; longer rows are re-read.
+template <int PER_LANE>
+static __global__ void __launch_bounds__(256)
+softmax_fwd_kernel(long long rows, int cols, int causal_rows, const float* x, float* y) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r = warp; r < rows; r += n_warps) {
+    const float* xr = x + r * cols;
+    float* yr = y + r * cols;
+    const int limit = causal_rows > 0 ? static_cast<int>(r % causal_rows) : cols;   // columns > limit are masked
+    float v[PER_LANE > 0 ? PER_LANE : 1];
+    float mx = -3.402823466e38f;
+    if (PER_LANE > 0) {
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = (c < cols) ? ((c > limit) ? -1e12f : xr[c]) : -3.402823466e38f;
+        mx = fmaxf(mx, v[i]);
+      }
+    } else {
+      for (int c = lane; c < cols; c += 32) mx = fmaxf(mx, (c > limit) ? -1e12f : xr[c]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+    if (PER_LANE > 0) {
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = (c < cols) ? expf(v[i] - mx) : 0.0f;
+        sum += v[i];
+      }
+    } else {
+      for (int c = lane; c < cols; c += 32) sum += expf(((c > limit) ? -1e12f : xr[c]) - mx);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (PER_LANE > 0) {
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        if (c < cols) yr[c] = v[i] / sum;
+      }
+    } else {
+      for (int c = lane; c < cols; c += 32) yr[c] = expf(((c > limit) ? -1e12f : xr[c]) - mx) / sum;
+    }
+  }
+}
+
+// dx[r, :] = y[r, :] * (dy[r, :] - sum_j dy[r, j] * y[r, j]): the softmax Jacobian that
+// cudnnSoftmaxBackward applies on SharpNet's GPU path (Prod/GPU/GpuTensor.cs:445-490).  dx may equal dy.
+static __global__ void __launch_bounds__(256)
+softmax_bwd_kernel(long long rows, int cols, const float* dy, const float* __restrict__ y, float* dx) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r = warp; r < rows; r += n_warps) {
+    const float* gr = dy + r * cols;
+    const float* yr = y + r * cols;
+    float* dr = dx + r * cols;
+    float dot = 0.0f;
+    for (int c = lane; c < cols; c += 32) dot = fmaf(gr[c], yr[c], dot);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    for (int c = lane; c < cols; c += 32) dr[c] = yr[c] * (gr[c] - dot);
+  }
+}
+
 // ---------------------------------------------------------------- optimizer updates
 // One pass each over the parameter tensors; SharpNet's GPU path makes two or three
 // (cudnnAddTensor + axpy, Prod/GPU/GpuTensor.cs:1147-1161) or launches an NVRTC kernel

@@ -825,6 +825,121 @@ extern "C" int snb200_adam_update(snb200_handle_t h, long long count, double lea
   return check_launch(h, "adam_update launch");
 }
 
+// ------------------------------------------------------------------------------------ attention
+static int launch_softmax_fwd(snb200_handle_t h, long long rows, int cols, int causal_rows, const float* x, float* y) {
+  long long blocks = (rows + 7) / 8;   // 8 warps (rows) per block
+  const long long cap = 16LL * h->sm_count;
+  if (blocks > cap) blocks = cap;
+  const unsigned g = static_cast<unsigned>(blocks < 1 ? 1 : blocks);
+  if (cols <= 128) softmax_fwd_kernel<4><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
+  else if (cols <= 256) softmax_fwd_kernel<8><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
+  else if (cols <= 512) softmax_fwd_kernel<16><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
+  else if (cols <= 1024) softmax_fwd_kernel<32><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
+  else softmax_fwd_kernel<0><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
+  note_kernel(h, "softmax_fwd", 1);
+  return check_launch(h, "softmax_fwd launch");
+}
+static int launch_softmax_bwd(snb200_handle_t h, long long rows, int cols, const float* dy, const float* y, float* dx) {
+  long long blocks = (rows + 7) / 8;
+  const long long cap = 16LL * h->sm_count;
+  if (blocks > cap) blocks = cap;
+  softmax_bwd_kernel<<<static_cast<unsigned>(blocks < 1 ? 1 : blocks), 256, 0, h->stream>>>(rows, cols, dy, y, dx);
+  note_kernel(h, "softmax_bwd", 1);
+  return check_launch(h, "softmax_bwd launch");
+}
+
+extern "C" int snb200_softmax_fwd(snb200_handle_t h, long long rows, int cols, const float* x, float* y) {
+  int st = enter(h);
+  if (st) return st;
+  if (rows < 0 || cols < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (rows == 0 || cols == 0) return 0;
+  if (!x || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  return launch_softmax_fwd(h, rows, cols, 0, x, y);
+}
+extern "C" int snb200_softmax_bwd(snb200_handle_t h, long long rows, int cols, const float* dy, const float* y,
+                                  float* dx) {
+  int st = enter(h);
+  if (st) return st;
+  if (rows < 0 || cols < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (rows == 0 || cols == 0) return 0;
+  if (!dy || !y || !dx) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  return launch_softmax_bwd(h, rows, cols, dy, y, dx);
+}
+
+static void bmm_problem(GemmProblem* g, int batch, int M, int N, int K, int tA, int tB, const float* A, int lda,
+                        long long sA, const float* B, int ldb, long long sB, float* C, float alpha) {
+  memset(g, 0, sizeof(*g));
+  g->M = M; g->N = N; g->K = K; g->transA = tA; g->transB = tB;
+  g->A = A; g->lda = lda; g->strideA = sA;
+  g->B = B; g->ldb = ldb; g->strideB = sB;
+  g->C = C; g->ldc = N; g->strideC = static_cast<long long>(M) * N;
+  g->batch = batch; g->alpha = alpha; g->beta = 0.0f; g->act = ACT_IDENTITY;
+}
+
+extern "C" int snb200_sdpa_fwd(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim,
+                               int use_scale, int is_causal, const float* Q, const float* K, const float* V,
+                               float* weights, float* y) {
+  int st = enter(h);
+  if (st) return st;
+  if (batch < 0 || q_steps < 0 || v_steps < 0 || embedding_dim < 0)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (batch == 0 || q_steps == 0 || v_steps == 0 || embedding_dim == 0) return 0;
+  st = check_ptrs(h, Q, K, V);
+  if (st) return st;
+  if (!weights || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  const int Tq = q_steps, Tk = v_steps, E = embedding_dim;
+  const float scaling = use_scale ? 1.0f / sqrtf(static_cast<float>(E)) : 1.0f;
+  GemmProblem g;
+  // scores = scaling * Q * K^T                       (ScaledDotProductAttentionLayer.cs:66-71)
+  bmm_problem(&g, batch, Tq, Tk, E, 0, 1, Q, E, static_cast<long long>(Tq) * E, K, E, static_cast<long long>(Tk) * E,
+              weights, scaling);
+  st = run_gemm(h, g);
+  if (st) return st;
+  // causal mask + softmax over the last dimension, in place   (:73-81)
+  st = launch_softmax_fwd(h, static_cast<long long>(batch) * Tq, Tk, is_causal ? Tq : 0, weights, weights);
+  if (st) return st;
+  // y = weights * V                                   (:85)
+  bmm_problem(&g, batch, Tq, E, Tk, 0, 0, weights, Tk, static_cast<long long>(Tq) * Tk, V, E,
+              static_cast<long long>(Tk) * E, y, 1.0f);
+  return run_gemm(h, g);
+}
+
+extern "C" int snb200_sdpa_bwd(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim,
+                               int use_scale, const float* Q, const float* K, const float* V, const float* dy,
+                               const float* weights, float* scores_grad_scratch, float* dQ, float* dK, float* dV) {
+  int st = enter(h);
+  if (st) return st;
+  if (batch < 0 || q_steps < 0 || v_steps < 0 || embedding_dim < 0)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (batch == 0 || q_steps == 0 || v_steps == 0 || embedding_dim == 0) return 0;
+  st = check_ptrs(h, Q, K, V);
+  if (st) return st;
+  if (!dy || !weights || !scores_grad_scratch || !dQ || !dK || !dV)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  const int Tq = q_steps, Tk = v_steps, E = embedding_dim;
+  const long long sQ = static_cast<long long>(Tq) * E, sK = static_cast<long long>(Tk) * E;
+  const long long sW = static_cast<long long>(Tq) * Tk;
+  const float scaling = use_scale ? 1.0f / sqrtf(static_cast<float>(E)) : 1.0f;
+  GemmProblem g;
+  // dV = weights^T * dy                               (ScaledDotProductAttentionLayer.cs:113)
+  bmm_problem(&g, batch, Tk, E, Tq, 1, 0, weights, Tk, sW, dy, E, sQ, dV, 1.0f);
+  st = run_gemm(h, g);
+  if (st) return st;
+  // gradient w.r.t. the weights, scaled: scaling * dy * V^T    (:119)
+  bmm_problem(&g, batch, Tq, Tk, E, 0, 1, dy, E, sQ, V, E, sK, scores_grad_scratch, scaling);
+  st = run_gemm(h, g);
+  if (st) return st;
+  // ... turned into the gradient w.r.t. the scores by the softmax Jacobian, in place    (:121)
+  st = launch_softmax_bwd(h, static_cast<long long>(batch) * Tq, Tk, scores_grad_scratch, weights, scores_grad_scratch);
+  if (st) return st;
+  // dQ = dScores * K ; dK = dScores^T * Q             (:123-124)
+  bmm_problem(&g, batch, Tq, E, Tk, 0, 0, scores_grad_scratch, Tk, sW, K, E, sK, dQ, 1.0f);
+  st = run_gemm(h, g);
+  if (st) return st;
+  bmm_problem(&g, batch, Tk, E, Tq, 1, 0, scores_grad_scratch, Tk, sW, Q, E, sQ, dK, 1.0f);
+  return run_gemm(h, g);
+}
+
 // ------------------------------------------------------------------------------------ NCCL (loaded at run time)
 struct NcclId { char bytes[128]; };
 typedef int (*nccl_get_id_t)(NcclId*);

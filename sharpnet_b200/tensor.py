@@ -215,3 +215,16 @@ class GPUTensor:
         w = self.wrapper
         check(w.handle, w.lib.snb200_loss_gradient(w.handle, int(loss), self.Shape[0], self.MultDim0, yExpected.Pointer,
                                                    yPredicted.Pointer, self.Pointer))
+
+    def SoftmaxLastDimension(self, y):
+        """y = softmax(this) over the last dimension (ActivationForward with
+        CUDNN_ACTIVATION_SOFTMAX_LAST_DIMENSION, Prod/GPU/GpuTensor.cs:411-413)."""
+        w = self.wrapper
+        cols = self.Shape[-1]
+        check(w.handle, w.lib.snb200_softmax_fwd(w.handle, self.Count // cols, cols, self.Pointer, y.Pointer))
+
+    def SoftmaxGradientLastDimension(self, dy, y):
+        """this = dx = y * (dy - sum(dy * y)) over the last dimension (cudnnSoftmaxBackward, Prod/GPU/GpuTensor.cs:445-490)."""
+        w = self.wrapper
+        cols = self.Shape[-1]
+        check(w.handle, w.lib.snb200_softmax_bwd(w.handle, self.Count // cols, cols, dy.Pointer, y.Pointer, self.Pointer))

@@ -10,6 +10,7 @@ Sources (paths inside the reference):
   Tests/NonReg/TestNetworkPropagation.cs:24-34   inputs X_1_1_4_4, X_2_1_4_4 and weights W_N_1_4_4
   Tests/NonReg/TestNetworkPropagation.cs:80-132  Linear + Sigmoid predictions before training and after 10 epochs of
                                                  VanillaSGD ([in,out] weights)
+  Tests/NonReg/TestNetworkPropagation.cs:500-575 attention block: predictions before training, plain and causal
   Tests/NonReg/ParallelRunWithPyTorch.cs:102-138 Linear(5->3, last-dim flatten)+ReLU+Flatten+Linear(36->3), Mse
   Tests/NonReg/ParallelRunWithPyTorch.cs:179-214 Linear(16->3)+ReLU+Linear(3->3)+Sigmoid, BCE ([out,in] weights)
 """
@@ -96,6 +97,15 @@ def main(ref):
     blk = _between(tnp, "public void TestSigmoidActivation_NCHW_1_1_1_1", "const int num_epochs")
     out["sigmoid_1_1_1_1_w"] = _nth_numpy_literal(blk, 0)
     out["sigmoid_1_1_1_1_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))
+
+    # ---- attention goldens: Conv1D(k=1) Q/K/V projections -> ScaledDotProductAttention -> Flatten -> Linear -> Softmax
+    out["X_3_4_5"] = _const(tnp, "X_3_4_5")
+    for name, key in (("Test_ScaledDotProductAttention(", "sdpa"), ("Test_ScaledDotProductAttention_with_Causal_Mask(", "sdpa_causal")):
+        blk = _between(tnp, "public void " + name, "TestNetwork.Fit")
+        convs = re.findall(r'FromTensorFlowConvNumpyArray\("(.*?)"\)', blk)
+        out[key + "_wq"], out[key + "_wk"], out[key + "_wv"] = (_numbers(c) for c in convs)      # each [4 in, 2 out]
+        out[key + "_wlinear"] = _numbers(re.findall(r'FromNumpyArray\("(\[\[.*?\]\])"\)\.CopyTo', blk)[0])   # [10, 3]
+        out[key + "_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))
 
     # ---- PyTorch-layout network goldens ------------------------------------------------------
     pt = open(os.path.join(ref, "Tests/NonReg/ParallelRunWithPyTorch.cs"), encoding="utf-8-sig").read()
