@@ -267,6 +267,65 @@ def companion_table(w, torch, peaks):
     return out
 
 
+def dense_and_attention_table(w, torch, peaks):
+    """BASELINE config 3 (Dense 4096 x 3072 -> 1024, bias, ReLU and Swish, forward and backward through the fused
+    entry points) and an attention block of the reference's own timing sandbox
+    (Tests/NonReg/ParallelRunWithTensorFlow.cs:415-490: 256 heads x [128 x 64]), timed like the Dot shapes."""
+    import ctypes
+    from sharpnet_b200 import ACT_RELU, ACT_SWISH, MATH_3XTF32
+    lib, h = w.lib, w.handle
+    w.set_math_mode(MATH_3XTF32)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    new = lambda *shape: torch.empty(*shape, dtype=torch.float32, device=w.device)  # noqa: E731
+    tpeak3 = peaks["bf16_burst"] / 2 / 3
+    out = []
+
+    def timed(name, flops, byts, sets, call):
+        for i in range(3):
+            call(sets[i % len(sets)])
+        torch.cuda.synchronize()
+        n = max(10, len(sets))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            call(sets[i % len(sets)])
+        e1.record()
+        torch.cuda.synchronize()
+        w.check_device_status()
+        ms = e0.elapsed_time(e1) / n
+        t_tensor, t_hbm = flops / (tpeak3 * 1e12), byts / (peaks["hbm"] * 1e9)
+        out.append({"shape": name, "mode": "3xTF32", "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 2),
+                    "gbs": round(byts / ms / 1e6, 1), "bound": "tensor" if t_tensor >= t_hbm else "hbm",
+                    "roofline_frac": round(max(t_tensor, t_hbm) / (ms * 1e-3), 3), "operand_sets": len(sets)})
+
+    M, K, N = 4096, 3072, 1024
+    sets = []
+    for _ in range(3):    # 3 x ~190 MB of operands: more than twice the L2
+        d = {"x": new(M, K).normal_(), "W": new(K, N).uniform_(-0.038, 0.038), "b": new(N).zero_(), "dy": new(M, N).normal_(),
+             "y": new(M, N), "z": new(M, N), "dz": new(M, N), "dx": new(M, K), "dW": new(K, N), "db": new(N)}
+        sets.append(d)
+    for act, an in ((ACT_RELU, "ReLU"), (ACT_SWISH, "Swish")):
+        zarg = (lambda d: P(d["z"])) if act == ACT_SWISH else (lambda d: None)
+        timed(f"cfg3 dense_fwd 4096x3072->1024 bias+{an} (W [in,out])", 2.0 * M * K * N,
+              4.0 * (M * K + K * N + N + M * N * (2 if act == ACT_SWISH else 1)), sets,
+              lambda d: lib.snb200_dense_fwd(h, 1, M, K, N, P(d["x"]), P(d["W"]), P(d["b"]), act, zarg(d), P(d["y"])))
+        timed(f"cfg3 dense_bwd 4096x3072->1024 {an}: dz, db, dW, dx", 4.0 * M * K * N,
+              4.0 * (2 * M * N + 2 * M * K + 2 * K * N + N), sets,
+              lambda d: lib.snb200_dense_bwd(h, 1, M, K, N, P(d["x"]), P(d["W"]), P(d["dy"]), act, P(d["y"]), zarg(d),
+                                             ctypes.c_float(1.0), P(d["dz"]), P(d["dx"]), P(d["dW"]), P(d["db"])))
+    B, T, E = 256, 128, 64
+    asets = []
+    for _ in range(8):    # 8 x 42 MB
+        asets.append({k: new(B, T, E).uniform_(-1, 1) for k in ("Q", "K", "V", "dy", "y", "dQ", "dK", "dV")} |
+                     {"w": new(B, T, T), "ds": new(B, T, T)})
+    timed("attention fwd 256 x [128x64], scaled, causal", 4.0 * B * T * T * E, 4.0 * (4 * B * T * E + B * T * T), asets,
+          lambda d: lib.snb200_sdpa_fwd(h, B, T, T, E, 1, 1, P(d["Q"]), P(d["K"]), P(d["V"]), P(d["w"]), P(d["y"])))
+    timed("attention bwd 256 x [128x64]", 8.0 * B * T * T * E, 4.0 * (7 * B * T * E + B * T * T), asets,
+          lambda d: lib.snb200_sdpa_bwd(h, B, T, T, E, 1, P(d["Q"]), P(d["K"]), P(d["V"]), P(d["dy"]), P(d["w"]),
+                                        P(d["ds"]), P(d["dQ"]), P(d["dK"]), P(d["dV"])))
+    return out
+
+
 def per_shape_table(w, torch, peaks):
     """TFLOP/s, roofline fraction and error vs fp64 of every Dot / batched shape in BASELINE configs 1-5."""
     import numpy as np
@@ -425,6 +484,8 @@ def run_ours(args):
         del a8, b8
     shapes = per_shape_table(w, torch, peaks) if (world == 1 and not args.no_shapes) else None
     companions = companion_table(w, torch, peaks) if (world == 1 and not args.no_shapes) else None
+    if shapes is not None:
+        shapes = shapes + dense_and_attention_table(w, torch, peaks)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         v, t = time_cpu(CPU_SAMPLE_ROWS, 3)
@@ -443,7 +504,10 @@ def run_ours(args):
                     "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms},
             "gpu_launches": launches * world,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak3, "unit": "TFLOP/s",
-                         "frac": achieved / peak3, "traffic": None,
+                         "frac": achieved / peak3,
+                         # DRAM bytes per GEMM launch of this step from the ncu launch list (one-pass metrics on the
+                         # same command): 3.60 GB read + 0.57 GB written on average; algorithmic bytes 1.89 GB
+                         "traffic": 4.17e9 if world == 1 else None, "algorithmic_bytes_per_launch": 1.89e9,
                          "kernel": "umma2_gemm_kernel (CTA-pair tcgen05 GEMM, 3xTF32), the 8 GEMM launches of the step",
                          "peak_source": f"{peaks['src']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32) / 3 "
                                         "(three TF32 products per fp32 product); flops counted once (2*M*N*K)",
