@@ -124,6 +124,53 @@ __device__ __forceinline__ void reg_alloc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+// One 32 x 32 block of the store phase, rows 16-byte aligned: every lane moves one float4 of 8 rows.
+// HEAVY selects the transcendental activations (Swish, Tanh, Sigmoid).  Their inlined code is long, and
+// fully unrolled it outgrows the instruction cache (the fetch misses cost more than the stores), so that
+// variant keeps the row loop rolled; Identity and Relu are a select and stay unrolled so that the
+// loads of beta*C overlap.
+template <bool HEAVY>
+__device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, const float* stage, size_t tile_off,
+                                                         int row_base, int col0, int lane) {
+  const int c4 = lane & 7;
+  const int col = col0 + 4 * c4;
+  float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (p.bias) bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+  const bool relu = p.act == ACT_RELU;
+#pragma unroll(HEAVY ? 1 : 8)
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + (lane >> 3);
+    const int row = row_base + r;
+    if (row < p.M) {
+      const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
+      const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
+      float4 o;
+      o.x = p.alpha * a4.x; o.y = p.alpha * a4.y; o.z = p.alpha * a4.z; o.w = p.alpha * a4.w;
+      if (p.beta != 0.0f) {
+        const float4 cin = *reinterpret_cast<const float4*>(p.C + off);
+        o.x = fmaf(p.beta, cin.x, o.x);
+        o.y = fmaf(p.beta, cin.y, o.y);
+        o.z = fmaf(p.beta, cin.z, o.z);
+        o.w = fmaf(p.beta, cin.w, o.w);
+      }
+      o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+      if (p.Z) *reinterpret_cast<float4*>(p.Z + off) = o;
+      if (HEAVY) {
+        o.x = act_forward(p.act, o.x);
+        o.y = act_forward(p.act, o.y);
+        o.z = act_forward(p.act, o.z);
+        o.w = act_forward(p.act, o.w);
+      } else {
+        o.x = relu ? fmaxf(o.x, 0.0f) : o.x;
+        o.y = relu ? fmaxf(o.y, 0.0f) : o.y;
+        o.z = relu ? fmaxf(o.z, 0.0f) : o.z;
+        o.w = relu ? fmaxf(o.w, 0.0f) : o.w;
+      }
+      *reinterpret_cast<float4*>(p.C + off) = o;
+    }
+  }
+}
+
 // Store phase of the epilogue.  Each lane holds one output row (NC columns of it) in `acc`.  A
 // 32 x 32 block goes through a per-warp shared-memory tile (16-byte chunks XOR-swizzled by row) so
 // that every global access of C, Z and bias is a run of whole 128-byte lines instead of 32 scattered
@@ -132,6 +179,7 @@ template <int NC>
 __device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const float (&acc)[NC], float* stage, int b,
                                               int row_base, int n0, int lane) {
   const size_t tile_off = static_cast<size_t>(b) * p.strideC;
+  const bool heavy = p.act != ACT_IDENTITY && p.act != ACT_RELU;
 #pragma unroll
   for (int g = 0; g < NC / 32; ++g) {
     const int col0 = n0 + g * 32;
@@ -144,37 +192,8 @@ __device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const f
     }
     __syncwarp();
     if (p.vec_ok && col0 + 32 <= p.N) {
-      const int c4 = lane & 7;
-      const int col = col0 + 4 * c4;
-      float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (p.bias) bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int r = it * 4 + (lane >> 3);
-        const int row = row_base + r;
-        if (row < p.M) {
-          const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
-          const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
-          float4 o;
-          o.x = p.alpha * a4.x; o.y = p.alpha * a4.y; o.z = p.alpha * a4.z; o.w = p.alpha * a4.w;
-          if (p.beta != 0.0f) {
-            const float4 cin = *reinterpret_cast<const float4*>(p.C + off);
-            o.x = fmaf(p.beta, cin.x, o.x);
-            o.y = fmaf(p.beta, cin.y, o.y);
-            o.z = fmaf(p.beta, cin.z, o.z);
-            o.w = fmaf(p.beta, cin.w, o.w);
-          }
-          o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
-          if (p.Z) *reinterpret_cast<float4*>(p.Z + off) = o;
-          if (p.act != ACT_IDENTITY) {
-            o.x = act_forward(p.act, o.x);
-            o.y = act_forward(p.act, o.y);
-            o.z = act_forward(p.act, o.z);
-            o.w = act_forward(p.act, o.w);
-          }
-          *reinterpret_cast<float4*>(p.C + off) = o;
-        }
-      }
+      if (heavy) epilogue_store_block_vec<true>(p, stage, tile_off, row_base, col0, lane);
+      else       epilogue_store_block_vec<false>(p, stage, tile_off, row_base, col0, lane);
     } else {
       // ragged right edge or rows that are not 16-byte aligned: one column per lane
       const int col = col0 + lane;
