@@ -86,13 +86,35 @@ struct UmmaParams {
   int rewrite_hi;   // 3xTF32: store the rounded hi plane back over the raw tile
   int vec_ok;       // C (and Z, bias) rows are 16-byte aligned
   int* error_word;  // set to 1 when a pipeline wait timed out
-  // split-K: work unit = (tile, split); each split covers kb_per_split k-blocks and stores its raw
-  // partial sums to partial + split * partial_stride (dense [batch, M, N]); a second kernel combines them
+  // split-K.  The first `whole_tiles` tiles (in tile_coords order) are computed whole; each of the
+  // remaining "tail" tiles is cut into `splits` work units of kb_per_split k-blocks that store raw partial
+  // sums to the workspace, and a second kernel combines them.  Two workspace layouts:
+  //   dense (partial_tiled = 0, whole_tiles = 0): split s writes a [batch, M, N] matrix at partial + s * partial_stride;
+  //   tiled (partial_tiled = 1): unit (tail tile j, split s) writes its tile, row pitch BN, at
+  //                              partial + (s * tail + j) * partial_stride.
   int splits;
   int kb_per_split;
+  int whole_tiles;
+  int partial_tiled;
   float* partial;
   long long partial_stride;
 };
+
+// Work unit u of a launch over n_tiles output tiles: which tile, which K range, and (split >= 0) which
+// partial result it produces.
+__device__ __forceinline__ void unit_decode(const UmmaParams& p, int n_tiles, int u, int& tile, int& split,
+                                            int& kb_begin, int& kb_end) {
+  if (u < p.whole_tiles) {
+    tile = u; split = -1; kb_begin = 0; kb_end = p.k_blocks;
+  } else {
+    const int tail = n_tiles - p.whole_tiles;
+    const int v = u - p.whole_tiles;
+    split = v / tail;
+    tile = p.whole_tiles + (v - split * tail);
+    kb_begin = split * p.kb_per_split;
+    kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+  }
+}
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
   // Walk tiles in bands of 8 tile-rows so that CTAs running at the same time share A and B
@@ -130,7 +152,7 @@ __device__ __forceinline__ void reg_alloc() {
 // variant keeps the row loop rolled; Identity and Relu are a select and stay unrolled so that the
 // loads of beta*C overlap.
 template <bool HEAVY>
-__device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, const float* stage, size_t tile_off,
+__device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, const float* stage, long long tile_off,
                                                          int row_base, int col0, int lane) {
   const int c4 = lane & 7;
   const int col = col0 + 4 * c4;
@@ -143,7 +165,7 @@ __device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, co
     const int row = row_base + r;
     if (row < p.M) {
       const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
-      const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
+      const long long off = tile_off + static_cast<long long>(row) * p.ldc + col;
       float4 o;
       o.x = p.alpha * a4.x; o.y = p.alpha * a4.y; o.z = p.alpha * a4.z; o.w = p.alpha * a4.w;
       if (p.beta != 0.0f) {
@@ -174,11 +196,11 @@ __device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, co
 // Store phase of the epilogue.  Each lane holds one output row (NC columns of it) in `acc`.  A
 // 32 x 32 block goes through a per-warp shared-memory tile (16-byte chunks XOR-swizzled by row) so
 // that every global access of C, Z and bias is a run of whole 128-byte lines instead of 32 scattered
-// 16-byte pieces.  `row_base` is the first of the warp's 32 rows, `n0` its first column.
+// 16-byte pieces.  `row_base` is the first of the warp's 32 rows, `n0` its first column; element
+// (row, col) goes to p.C[tile_off + row * p.ldc + col].
 template <int NC>
-__device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const float (&acc)[NC], float* stage, int b,
-                                              int row_base, int n0, int lane) {
-  const size_t tile_off = static_cast<size_t>(b) * p.strideC;
+__device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const float (&acc)[NC], float* stage,
+                                              long long tile_off, int row_base, int n0, int lane) {
   const bool heavy = p.act != ACT_IDENTITY && p.act != ACT_RELU;
 #pragma unroll
   for (int g = 0; g < NC / 32; ++g) {
@@ -203,7 +225,7 @@ __device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const f
           const int row = row_base + r;
           if (row >= p.M) break;
           const float a1 = stage[r * 32 + ((((lane >> 2) ^ (r & 7)) << 2) | (lane & 3))];
-          const size_t off = tile_off + static_cast<size_t>(row) * p.ldc + col;
+          const long long off = tile_off + static_cast<long long>(row) * p.ldc + col;
           float o = p.alpha * a1;
           if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
           o += bv;
@@ -214,6 +236,35 @@ __device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const f
     }
     __syncwarp();
   }
+}
+
+// Final store of one work unit: the fused epilogue into C, or (split >= 0) the raw partial sums into
+// the workspace.  `tile_row0`/`tile_col0` are the first row and column of the unit's whole tile,
+// `tile_elems` the size of that tile in the tiled workspace layout (rows x BN), `bn` its row pitch there.
+template <int NC>
+__device__ __forceinline__ void epilogue_store_unit(const UmmaParams& p, const float (&acc)[NC], float* stage, int b,
+                                                    int n_tiles, int tile, int split, int tile_row0, int tile_col0,
+                                                    int bn, int row_base, int n0, int lane) {
+  if (split < 0 || p.partial == nullptr) {
+    epilogue_store_rows<NC>(p, acc, stage, static_cast<long long>(b) * p.strideC, row_base, n0, lane);
+    return;
+  }
+  UmmaParams pp = p;
+  pp.C = p.partial;
+  pp.alpha = 1.0f; pp.beta = 0.0f; pp.bias = nullptr; pp.Z = nullptr; pp.act = ACT_IDENTITY;
+  long long off;
+  if (p.partial_tiled) {
+    const int tail = n_tiles - p.whole_tiles;
+    const long long slot = static_cast<long long>(split) * tail + (tile - p.whole_tiles);
+    pp.ldc = bn;
+    pp.vec_ok = 1;
+    off = slot * p.partial_stride - (static_cast<long long>(tile_row0) * bn + tile_col0);
+  } else {
+    pp.ldc = p.N;
+    pp.vec_ok = (p.N % 4 == 0) ? 1 : 0;
+    off = static_cast<long long>(split) * p.partial_stride + static_cast<long long>(b) * p.M * p.N;
+  }
+  epilogue_store_rows<NC>(pp, acc, stage, off, row_base, n0, lane);
 }
 
 // 3xTF32 operand split of one landed stage: lo = tf32(x - hi) goes to the second plane, RAW_BYTES
@@ -289,7 +340,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile int* abortp = &abort_flag;
 
   const int n_tiles = p.batch * p.tiles_m * p.tiles_n;
-  const int total_tiles = n_tiles * p.splits;   // work units: (tile, K split)
+  const int total_tiles = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;   // work units
 
   if (warp < 4) {
     reg_dealloc<T::REGS_CTRL>();
@@ -299,11 +350,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int b, tm, tn;
-        tile_coords(t % n_tiles, p.tiles_m, p.tiles_n, b, tm, tn);
+        int tile, split, kb_begin, kb_end, b, tm, tn;
+        unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
+        tile_coords(tile, p.tiles_m, p.tiles_n, b, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        const int kb_begin = (t / n_tiles) * p.kb_per_split;
-        const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) { ok = false; break; }
           uint8_t* a_dst = ring + s * T::STAGE_BYTES;
@@ -344,8 +394,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t chunk_id = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int kb_begin = (t / n_tiles) * p.kb_per_split;
-        const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+        int tile, split, kb_begin, kb_end;
+        unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
         for (int kb0 = kb_begin; kb0 < kb_end && ok; kb0 += p.chunk_kblocks, ++chunk_id) {
           const int buf = chunk_id & 1;
           if (!mbar_wait(&acc_empty_bar[buf], ((acc_ph >> buf) & 1u) ^ 1u, abortp)) { ok = false; break; }
@@ -392,11 +442,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t chunk_id = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      int b, tm, tn;
-      tile_coords(t % n_tiles, p.tiles_m, p.tiles_n, b, tm, tn);
-      const int split = t / n_tiles;
-      const int kb_count = min(p.k_blocks, (split + 1) * p.kb_per_split) - split * p.kb_per_split;
-      const int n_chunks = (kb_count + p.chunk_kblocks - 1) / p.chunk_kblocks;
+      int tile, split, kb_begin, kb_end, b, tm, tn;
+      unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
+      tile_coords(tile, p.tiles_m, p.tiles_n, b, tm, tn);
+      const int n_chunks = (kb_end - kb_begin + p.chunk_kblocks - 1) / p.chunk_kblocks;
       float acc[NC];
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] = 0.0f;
@@ -420,18 +469,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) break;
       float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
-      if (p.partial == nullptr) {
-        epilogue_store_rows<NC>(p, acc, stage, b, tm * BM + q * 32, tn * BN + col_base, lane);
-      } else {
-        // split-K: raw partial sums, dense [batch, M, N], combined by splitk_reduce_kernel
-        UmmaParams pp = p;
-        pp.C = p.partial + static_cast<size_t>(split) * p.partial_stride;
-        pp.ldc = p.N;
-        pp.strideC = static_cast<long long>(p.M) * p.N;
-        pp.alpha = 1.0f; pp.beta = 0.0f; pp.bias = nullptr; pp.Z = nullptr; pp.act = ACT_IDENTITY;
-        pp.vec_ok = (p.N % 4 == 0) ? 1 : 0;
-        epilogue_store_rows<NC>(pp, acc, stage, b, tm * BM + q * 32, tn * BN + col_base, lane);
-      }
+      epilogue_store_unit<NC>(p, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN, BN, tm * BM + q * 32,
+                              tn * BN + col_base, lane);
     }
   } else if (T::SPLIT) {
     // ------------------------------------------------------------------ hi / lo split
@@ -441,8 +480,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t ph = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int kb_begin = (t / n_tiles) * p.kb_per_split;
-      const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+      int tile, split, kb_begin, kb_end;
+      unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait_warp(&full_bar[s], ph, abortp)) { ok = false; break; }
         split_stage<T::RAW_BYTES, T::N_SPLIT_THREADS>(ring + s * T::STAGE_BYTES, tid, p.rewrite_hi);
@@ -527,6 +566,70 @@ static __global__ void __launch_bounds__(256) splitk_reduce_transposed_kernel(co
       if (p.bias) v += __ldg(p.bias + n);
       if (p.Z) p.Z[off] = v;
       p.C[off] = act_forward(p.act, v);
+    }
+  }
+}
+
+// Second pass for the tiled workspace layout: sums the `splits` partial tiles of every tail tile and
+// applies the epilogue.  Grid = (tail tiles, tile_rows / 32); a block of 256 threads covers 32 rows of
+// one tile, a float4 per thread and step.
+struct TailReduceParams {
+  int M, N, tiles_m, tiles_n;   // tile grid as the GEMM kernel walked it (tile = tile_rows x bn)
+  int tile_rows, bn;
+  int whole_tiles, tail, splits;
+  const float* partial;
+  long long tile_elems;         // tile_rows * bn
+  float* C;
+  float* Z;
+  const float* bias;
+  int ldc;
+  long long strideC;
+  float alpha, beta;
+  int act;
+  int vec_ok;
+};
+static __global__ void __launch_bounds__(256) tail_reduce_kernel(const TailReduceParams p) {
+  int b, tm, tn;
+  tile_coords(p.whole_tiles + blockIdx.x, p.tiles_m, p.tiles_n, b, tm, tn);
+  const int r0 = blockIdx.y * 32;
+  const int q_per_row = p.bn >> 2;
+  const float* src = p.partial + static_cast<long long>(blockIdx.x) * p.tile_elems;
+  const long long split_stride = static_cast<long long>(p.tail) * p.tile_elems;
+  for (int i = threadIdx.x; i < 32 * q_per_row; i += 256) {
+    const int r = r0 + i / q_per_row;
+    const int c = (i % q_per_row) << 2;
+    const int row = tm * p.tile_rows + r, col = tn * p.bn + c;
+    if (row >= p.M || col >= p.N) continue;
+    const float* s0 = src + static_cast<long long>(r) * p.bn + c;
+    float4 sum = *reinterpret_cast<const float4*>(s0);
+    for (int s = 1; s < p.splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(s0 + s * split_stride);
+      sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    const long long off = static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc + col;
+    float o[4] = {p.alpha * sum.x, p.alpha * sum.y, p.alpha * sum.z, p.alpha * sum.w};
+    if (p.vec_ok && col + 4 <= p.N) {
+      if (p.beta != 0.0f) {
+        const float4 cin = *reinterpret_cast<const float4*>(p.C + off);
+        o[0] = fmaf(p.beta, cin.x, o[0]); o[1] = fmaf(p.beta, cin.y, o[1]);
+        o[2] = fmaf(p.beta, cin.z, o[2]); o[3] = fmaf(p.beta, cin.w, o[3]);
+      }
+      if (p.bias) {
+        const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
+        o[0] += bv.x; o[1] += bv.y; o[2] += bv.z; o[3] += bv.w;
+      }
+      if (p.Z) *reinterpret_cast<float4*>(p.Z + off) = make_float4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = act_forward(p.act, o[e]);
+      *reinterpret_cast<float4*>(p.C + off) = make_float4(o[0], o[1], o[2], o[3]);
+    } else {
+      for (int e = 0; e < 4 && col + e < p.N; ++e) {
+        float v = o[e];
+        if (p.beta != 0.0f) v = fmaf(p.beta, p.C[off + e], v);
+        if (p.bias) v += __ldg(p.bias + col + e);
+        if (p.Z) p.Z[off + e] = v;
+        p.C[off + e] = act_forward(p.act, v);
+      }
     }
   }
 }

@@ -108,10 +108,10 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   volatile int* abortp = &abort_flag;
 
   const int pair_tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
-  const int total_tiles = p.batch * pair_tiles_m * p.tiles_n;
+  const int n_tiles = p.batch * pair_tiles_m * p.tiles_n;
+  const int total_tiles = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;   // work units
   const int n_pairs = gridDim.x >> 1;
   const int pair_id = blockIdx.x >> 1;
-  const int n_chunks = (p.k_blocks + p.chunk_kblocks - 1) / p.chunk_kblocks;
 
   if (warp < 4) {
     reg_dealloc<T::REGS_CTRL>();
@@ -121,11 +121,12 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ph = 0;
       bool ok = true;
       for (int t = pair_id; t < total_tiles && ok; t += n_pairs) {
-        int b, tm, tn;
-        tile_coords(t, pair_tiles_m, p.tiles_n, b, tm, tn);
+        int tile, split, kb_begin, kb_end, b, tm, tn;
+        unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
+        tile_coords(tile, pair_tiles_m, p.tiles_n, b, tm, tn);
         const int m0 = tm * 2 * BM + rank * BM;      // this CTA's rows of A
         const int n0 = tn * BN + rank * BNH;         // this CTA's half of B
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait_cluster(&empty_bar[s], ph ^ 1, abortp)) { ok = false; break; }
           uint8_t* a_dst = ring + s * T::STAGE_BYTES;
           uint8_t* b_dst = a_dst + T::A_BYTES;
@@ -165,13 +166,15 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t chunk_id = 0;
       bool ok = true;
       for (int t = pair_id; t < total_tiles && ok; t += n_pairs) {
-        for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += p.chunk_kblocks, ++chunk_id) {
+        int tile, split, kb_begin, kb_end;
+        unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
+        for (int kb0 = kb_begin; kb0 < kb_end && ok; kb0 += p.chunk_kblocks, ++chunk_id) {
           const int buf = chunk_id & 1;
           if (!mbar_wait_cluster(&acc_empty_bar[buf], ((acc_ph >> buf) & 1u) ^ 1u, abortp)) { ok = false; break; }
           acc_ph ^= 1u << buf;
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + buf * BN;
-          const int kb1 = min(p.k_blocks, kb0 + p.chunk_kblocks);
+          const int kb1 = min(kb_end, kb0 + p.chunk_kblocks);
           for (int kb = kb0; kb < kb1; ++kb) {
             if (!mbar_wait_cluster(&ready_bar[s], ph, abortp)) { ok = false; break; }
             tc_fence_after_sync();
@@ -205,7 +208,9 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ph = 0;
       bool ok = true;
       for (int t = pair_id; t < total_tiles && ok; t += n_pairs) {
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        int tile, split, kb_begin, kb_end;
+        unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abortp)) { ok = false; break; }
           mbar_arrive_cluster(map_to_cta(smem_u32(&ready_bar[s]), 0));
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -223,8 +228,10 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint32_t chunk_id = 0;
     bool ok = true;
     for (int t = pair_id; t < total_tiles && ok; t += n_pairs) {
-      int b, tm, tn;
-      tile_coords(t, pair_tiles_m, p.tiles_n, b, tm, tn);
+      int tile, split, kb_begin, kb_end, b, tm, tn;
+      unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
+      tile_coords(tile, pair_tiles_m, p.tiles_n, b, tm, tn);
+      const int n_chunks = (kb_end - kb_begin + p.chunk_kblocks - 1) / p.chunk_kblocks;
       float acc[NC];
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] = 0.0f;
@@ -248,7 +255,8 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
       if (!ok) break;
       float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
-      epilogue_store_rows<NC>(p, acc, stage, b, tm * 2 * BM + rank * BM + q * 32, tn * BN + col_base, lane);
+      epilogue_store_unit<NC>(p, acc, stage, b, n_tiles, tile, split, tm * 2 * BM, tn * BN, BN,
+                              tm * 2 * BM + rank * BM + q * 32, tn * BN + col_base, lane);
     }
   } else if (T::SPLIT) {
     // ------------------------------------------------------------------ hi / lo split (both CTAs)
@@ -258,7 +266,9 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint32_t ph = 0;
     bool ok = true;
     for (int t = pair_id; t < total_tiles && ok; t += n_pairs) {
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      int tile, split, kb_begin, kb_end;
+      unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait_warp(&full_bar[s], ph, abortp)) { ok = false; break; }
         split_stage<T::RAW_BYTES, T::N_SPLIT_THREADS>(ring + s * T::STAGE_BYTES, tid, p.rewrite_hi);
         fence_proxy_async_smem();

@@ -104,7 +104,7 @@ extern "C" int snb200_create(snb200_handle_t* handle, int device_id) {
   h->tune[TUNE_CHUNK_K] = 128;
   const char* env = getenv("SNB200_MATH_MODE");
   if (env && env[0] >= '0' && env[0] <= '2' && env[1] == 0) h->math_mode = env[0] - '0';
-  h->workspace_floats = 8u << 20;   // 32 MB: column-sum slabs and split-K partial sums
+  h->workspace_floats = 32u << 20;   // 128 MB: column-sum slabs and split-K partial sums
   if (cudaMalloc(&h->workspace, h->workspace_floats * sizeof(float)) != cudaSuccess ||
       cudaMalloc(&h->error_word, sizeof(int)) != cudaSuccess ||
       cudaMemset(h->error_word, 0, sizeof(int)) != cudaSuccess) {
@@ -238,14 +238,48 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
   p.error_word = h->error_word;
   p.splits = 1;
   p.kb_per_split = p.k_blocks;
+  p.whole_tiles = 0;       // set by the launcher: it knows the tile grid of its kernel
+  p.partial_tiled = 0;
   p.partial = nullptr;
   p.partial_stride = 0;
   return 0;
 }
 
-// How a problem is cut along K when it has too few output tiles to fill the GPU: `splits` work
-// units per tile, each covering `k_per_split` of K and writing raw partial sums to the workspace.
-struct SplitPlan { int splits; int k_per_split; int transposed; int parts; };   // parts: partial results actually written
+// How a problem is cut along K when its output tiles do not fill the SMs evenly.  The first
+// `whole_tiles` tiles run whole; each remaining tile becomes `splits` work units of `k_per_split` of K that
+// write raw partial sums to the workspace (`tiled`: one tile per unit; otherwise one dense matrix per
+// split, all tiles split), and a second kernel combines them.
+struct SplitPlan {
+  int splits; int k_per_split; int transposed;
+  int parts;        // out: partial results per tail tile actually written (0 = none, C is final)
+  int tiled; int whole_tiles;
+  int tail;         // out: tiles whose partial sums are in the workspace
+  int tiles_m;      // out: tile rows of the grid the kernel walked
+};
+
+template <class T>
+static void apply_split_plan(snb200_handle_t h, const GemmProblem& g, int tile_rows, long long n_tiles, UmmaParams& p,
+                             SplitPlan& plan) {
+  p.whole_tiles = static_cast<int>(n_tiles);
+  plan.parts = 0; plan.tail = 0;
+  if (plan.splits <= 0) return;
+  const int chunk = p.chunk_kblocks < p.k_blocks ? p.chunk_kblocks : 1;
+  int kbps = (plan.k_per_split + T::BK - 1) / T::BK;
+  kbps = (kbps + chunk - 1) / chunk * chunk;          // whole accumulation chunks per unit
+  p.kb_per_split = kbps;
+  p.splits = (p.k_blocks + kbps - 1) / kbps;
+  p.partial = h->workspace;
+  if (plan.tiled) {
+    p.partial_tiled = 1;
+    p.whole_tiles = plan.whole_tiles;
+    p.partial_stride = static_cast<long long>(tile_rows) * T::BN;
+  } else {
+    p.whole_tiles = 0;
+    p.partial_stride = static_cast<long long>(g.batch) * g.M * g.N;
+  }
+  plan.parts = p.splits;
+  plan.tail = static_cast<int>(n_tiles) - p.whole_tiles;
+}
 
 template <class T>
 static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& plan) {
@@ -254,25 +288,21 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pla
   UmmaParams p;
   int st = fill_umma_args<T>(h, g, T::BN, &tmA, &tmB, &p);
   if (st) return st;
-  if (plan.splits > 0) {   // partial sums go to the workspace; splitk_reduce_kernel finishes the job
-    p.kb_per_split = (plan.k_per_split + T::BK - 1) / T::BK;
-    p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
-    p.partial = h->workspace;
-    p.partial_stride = static_cast<long long>(g.batch) * g.M * g.N;
-  }
+  const long long n_tiles = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
+  apply_split_plan<T>(h, g, T::BM, n_tiles, p, plan);
+  plan.tiles_m = p.tiles_m;
   if (!configured[h->device]) {
     SNB_CUDA(h, cudaFuncSetAttribute(umma_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     configured[h->device] = true;
   }
-  const long long units = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n * p.splits;
+  const long long units = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;
   const int grid = static_cast<int>(units < h->sm_count ? units : h->sm_count);
   umma_gemm_kernel<T><<<grid, T::THREADS, T::SMEM_BYTES, h->stream>>>(tmA, tmB, p);
-  plan.parts = plan.splits > 0 ? p.splits : 0;
   return check_launch(h, "umma_gemm_kernel launch");
 }
 
 template <class T>
-static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g) {
+static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& plan) {
   static bool configured[64] = {};
   static int max_pairs[64] = {};
   CUtensorMap tmA, tmB;
@@ -298,8 +328,12 @@ static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g) {
     max_pairs[h->device] = n;
     configured[h->device] = true;
   }
-  const long long tiles = static_cast<long long>(p.batch) * ((g.M + 2 * T::BM - 1) / (2 * T::BM)) * p.tiles_n;
-  const long long pairs = tiles < max_pairs[h->device] ? tiles : max_pairs[h->device];
+  const int pair_tiles_m = (g.M + 2 * T::BM - 1) / (2 * T::BM);
+  const long long tiles = static_cast<long long>(p.batch) * pair_tiles_m * p.tiles_n;
+  apply_split_plan<T>(h, g, 2 * T::BM, tiles, p, plan);
+  plan.tiles_m = pair_tiles_m;
+  const long long units = p.whole_tiles + (tiles - p.whole_tiles) * p.splits;
+  const long long pairs = units < max_pairs[h->device] ? units : max_pairs[h->device];
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
   {
     const size_t len = strlen(h->last_kernel);
@@ -310,24 +344,24 @@ static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g) {
   return check_launch(h, "umma2_gemm_kernel launch");
 }
 
-static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int bn) {
+static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int bn, SplitPlan& plan) {
   char name[64];
-  snprintf(name, sizeof(name), "umma2_%s_256x%d", split ? "3xtf32" : "tf32", bn);
+  snprintf(name, sizeof(name), "umma2_%s_256x%d%s", split ? "3xtf32" : "tf32", bn, plan.splits > 0 ? "_splitk" : "");
   note_kernel(h, name, 1);
   if (split) {
     switch (bn) {
       // 32-wide K blocks: three 64 KB stages beat six 32 KB ones (fewer hand-offs per byte), measured +8..35 %
       case 256:
-        if (h->tune[TUNE_VARIANT] == 1) return launch_umma2_t<Umma2Tile<256, 16, true>>(h, g);
-        return launch_umma2_t<Umma2Tile<256, 32, true>>(h, g);
-      case 128: return launch_umma2_t<Umma2Tile<128, 32, true>>(h, g);
-      default: return launch_umma2_t<Umma2Tile<64, 32, true>>(h, g);
+        if (h->tune[TUNE_VARIANT] == 1) return launch_umma2_t<Umma2Tile<256, 16, true>>(h, g, plan);
+        return launch_umma2_t<Umma2Tile<256, 32, true>>(h, g, plan);
+      case 128: return launch_umma2_t<Umma2Tile<128, 32, true>>(h, g, plan);
+      default: return launch_umma2_t<Umma2Tile<64, 32, true>>(h, g, plan);
     }
   }
   switch (bn) {
-    case 256: return launch_umma2_t<Umma2Tile<256, 32, false>>(h, g);
-    case 128: return launch_umma2_t<Umma2Tile<128, 32, false>>(h, g);
-    default: return launch_umma2_t<Umma2Tile<64, 32, false>>(h, g);
+    case 256: return launch_umma2_t<Umma2Tile<256, 32, false>>(h, g, plan);
+    case 128: return launch_umma2_t<Umma2Tile<128, 32, false>>(h, g, plan);
+    default: return launch_umma2_t<Umma2Tile<64, 32, false>>(h, g, plan);
   }
 }
 
@@ -377,19 +411,32 @@ static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
   return check_launch(h, "simt_gemm_kernel launch");
 }
 
-// Picks the kernel (one CTA per 128 x BN tile, or a CTA pair per 256 x BN tile) and the tile width
-// whose wave count wastes the fewest SM-cycles.  A narrow tile costs more per flop (the A operand is
-// re-read for fewer columns); a pair runs the same tile area about 15 % faster in 3xTF32 mode because
-// each SM loads, splits and reads only half of B.
-struct TileChoice { int pair; int bn; int splits; };   // splits > 1: cut K, partial sums through the workspace
+// Picks the kernel (one CTA per 128 x BN tile, or a CTA pair per 256 x BN tile), the tile width and the
+// K split of the last, partly filled wave, by a time estimate in microseconds:
+//   launch + [whole waves * K blocks + tail waves * K blocks per split] * (time of one 32-deep K block) + last
+//   epilogue + the reduction pass over the workspace.
+// The per-block times are measured on a B200 (3xTF32: a pair does 256 x 256 x 32 in 0.98 us, one CTA 128 x 256 x 32
+// in 1.6 us; narrow tiles cost more per flop because the A operand is re-read for fewer columns).
+struct TileChoice { int pair; int bn; int splits; int whole_tiles; };   // splits > 1: cut K of the tail tiles
+static double kblock_us(bool split3x, int pair, int bn, const GemmProblem& g) {
+  const int i = bn == 256 ? 0 : bn == 128 ? 1 : bn == 64 ? 2 : 3;
+  if (split3x) {
+    static const double single[4] = {1.60, 0.86, 0.50, 0.34}, paired[4] = {0.98, 0.84, 0.77, 0.77};
+    return pair ? paired[i] : single[i];
+  }
+  static const double single[4] = {0.457, 0.305, 0.23, 0.19}, paired[4] = {0.443, 0.32, 0.25, 0.25};
+  const bool nt = !g.transA && g.transB;   // both operands K-major: the layout the pair kernel feeds fastest
+  return pair ? paired[i] * (nt ? 1.0 : 1.13) : single[i];
+}
 static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, bool split) {
-  TileChoice best = {0, 256, 1};
+  TileChoice best = {0, 256, 1, 0};
   const bool allow_splitk = h->tune[TUNE_SPLITK] == 0;
-  const size_t per_split = static_cast<size_t>(g.batch) * g.M * g.N;
   double best_cost = 1e300;
   const int pair_mode = h->tune[TUNE_PAIR];   // 0 automatic, 1 always, 2 never
   const int forced_bn = h->tune[TUNE_FORCE_BN];
   const int cand[4] = {256, 128, 64, 32};
+  const int ks_cand[11] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 16};
+  const long long kb = (g.K + 31) / 32;
   for (int pair = 0; pair < 2; ++pair) {
     if (pair == 0 && pair_mode == 1) continue;
     if (pair == 1 && (pair_mode == 2 || (pair_mode == 0 && g.M <= 128))) continue;
@@ -400,24 +447,45 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
       const int rows = pair ? 256 : 128;
       const long long tiles = static_cast<long long>(g.batch) * ((g.M + rows - 1) / rows) * ((g.N + bn - 1) / bn);
       const long long slots = pair ? h->sm_count / 2 : h->sm_count;
-      long long ks = 1;   // K splits: only the single-CTA kernel, only when its tiles leave SMs idle
-      if (!pair && allow_splitk && tiles * 2 <= slots) {
-        ks = slots / tiles;
-        if (ks > g.K / 512) ks = g.K / 512;
-        if (ks * per_split > h->workspace_floats) ks = static_cast<long long>(h->workspace_floats / per_split);
-        if (ks < 1) ks = 1;
-      }
-      const long long waves = (tiles * ks + slots - 1) / slots;
-      double f = 1.0;
-      if (pair) f = bn < 128 ? 1.05 : (split ? 0.85 : ((!g.transA && g.transB) ? 0.97 : 1.1));
-      const double cost = static_cast<double>(waves) * (bn + 128) * f / ks + (ks > 1 ? 40.0 : 0.0);
-      if (cost < best_cost * 0.999) {
-        best_cost = cost; best.pair = pair; best.bn = bn; best.splits = static_cast<int>(ks);
+      const long long whole = tiles / slots * slots, tail = tiles - whole;
+      const double c = kblock_us(split, pair, bn, g);
+      const double fixed = 8.0 + 6.0 * bn / 256.0;
+      for (int j = 0; j < 11; ++j) {
+        const long long ks = ks_cand[j];
+        if (ks > 1 && (!allow_splitk || tail == 0 || kb / ks < 8)) break;   // at least 256 of K per unit
+        const long long tail_floats = tail * rows * bn;
+        if (ks > 1 && ks * tail_floats > static_cast<long long>(h->workspace_floats)) break;
+        const long long kbps = ((kb + ks - 1) / ks + 3) / 4 * 4;
+        const long long tail_waves = (tail * ks + slots - 1) / slots;
+        double cost = fixed + c * (static_cast<double>(whole / slots) * kb + static_cast<double>(tail_waves) * (ks > 1 ? kbps : kb));
+        if (ks > 1) cost += 5.0 + static_cast<double>(ks + 1) * tail_floats * 4.0 / 5.0e6;
+        if (cost < best_cost * 0.999) {
+          best_cost = cost; best.pair = pair; best.bn = bn; best.splits = static_cast<int>(ks);
+          best.whole_tiles = static_cast<int>(whole);
+        }
       }
     }
   }
   if (best_cost > 1e299) { best.pair = (pair_mode == 1); best.bn = 256; best.splits = 1; }   // forced width not offered by the forced kernel
   return best;
+}
+
+static int launch_tail_reduce(snb200_handle_t h, const GemmProblem& g, const SplitPlan& plan, int tile_rows, int bn) {
+  TailReduceParams r;
+  r.M = g.M; r.N = g.N;
+  r.tiles_m = plan.tiles_m; r.tiles_n = (g.N + bn - 1) / bn;
+  r.tile_rows = tile_rows; r.bn = bn;
+  r.whole_tiles = plan.whole_tiles; r.tail = plan.tail; r.splits = plan.parts;
+  r.partial = h->workspace;
+  r.tile_elems = static_cast<long long>(tile_rows) * bn;
+  r.C = g.C; r.Z = g.Z; r.bias = g.bias; r.ldc = g.ldc; r.strideC = g.strideC;
+  r.alpha = g.alpha; r.beta = g.beta; r.act = g.act;
+  r.vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (g.batch == 1 || g.strideC % 4 == 0) &&
+             (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias));
+  dim3 grid(plan.tail, tile_rows / 32);
+  tail_reduce_kernel<<<grid, 256, 0, h->stream>>>(r);
+  h->launches += 1;
+  return check_launch(h, "tail_reduce_kernel launch");
 }
 
 static int launch_reduce(snb200_handle_t h, const GemmProblem& g, int parts, int transposed) {
@@ -468,7 +536,7 @@ static int run_gemm(snb200_handle_t h, const GemmProblem& g) {
     const size_t per_split = static_cast<size_t>(g.batch) * g.M * g.N;
     if (s * per_split > h->workspace_floats) s = static_cast<long long>(h->workspace_floats / per_split);
     if (s >= 1) {
-      SplitPlan plan = {static_cast<int>(s), static_cast<int>((g.K + s - 1) / s), 1, 0};
+      SplitPlan plan = {static_cast<int>(s), static_cast<int>((g.K + s - 1) / s), 1, 0, 0, 0, 0, 0};
       plan.k_per_split = (plan.k_per_split + 127) / 128 * 128;
       const int st = launch_umma(h, t, split, bn, plan);
       if (st) return st;
@@ -476,16 +544,17 @@ static int run_gemm(snb200_handle_t h, const GemmProblem& g) {
     }
   }
   const TileChoice c = choose_tile(h, g, split);
-  if (c.pair) return launch_umma2(h, g, split, c.bn);
-  // Too few tiles for the SMs and a long K: cut K.
-  SplitPlan plan = {0, 0, 0, 0};
+  // Tiles that would leave most SMs idle in the last wave are cut along K.
+  SplitPlan plan = {0, 0, 0, 0, 0, 0, 0, 0};
   if (c.splits > 1) {
     plan.splits = c.splits;
-    plan.k_per_split = ((g.K + c.splits - 1) / c.splits + 127) / 128 * 128;
+    plan.k_per_split = (g.K + c.splits - 1) / c.splits;
+    plan.tiled = 1;
+    plan.whole_tiles = c.whole_tiles;
   }
-  const int st = launch_umma(h, g, split, c.bn, plan);
+  const int st = c.pair ? launch_umma2(h, g, split, c.bn, plan) : launch_umma(h, g, split, c.bn, plan);
   if (st || plan.parts == 0) return st;
-  return launch_reduce(h, g, plan.parts, 0);
+  return launch_tail_reduce(h, g, plan, c.pair ? 256 : 128, c.bn);
 }
 
 static int check_ptrs(snb200_handle_t h, const void* a, const void* b, const void* c) {

@@ -135,6 +135,14 @@ def test_dense_small_batch_takes_the_split_k_plans(wrapper, act, layout):
     _dense_case(wrapper, 8, 1024, 260, act, layout, 320 + act, TOL_3XTF32, mult=0.125)
 
 
+@pytest.mark.parametrize("act", [ACT_RELU, ACT_SWISH, ACT_TANH])
+@pytest.mark.parametrize("layout", [W_IN_OUT, W_OUT_IN])
+def test_dense_with_a_cut_last_wave(wrapper, act, layout):
+    # 9 x 9 pair tiles on 74 SM pairs: the last 7 tiles are cut along K, so bias, activation and the
+    # pre-activation copy of those tiles come from the tile reduction kernel, the rest from the GEMM epilogue
+    _dense_case(wrapper, 2300, 1032, 2292, act, layout, 340 + act, TOL_3XTF32)
+
+
 @pytest.mark.parametrize("act", [ACT_RELU, ACT_SWISH])
 @pytest.mark.parametrize("layout", [W_IN_OUT, W_OUT_IN])
 def test_config_3_dense_4096x3072x1024(wrapper, act, layout):

@@ -253,6 +253,25 @@ def test_few_tiles_split_k_and_swapped_operands(wrapper, mode, tol, tA, tB):
     _check(wrapper, 8, 512, 1024, tA, tB, 1.0, 0.0, 777, tol, batch=6)       # batched, swapped
 
 
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+@pytest.mark.parametrize("tA,tB", [(False, False), (False, True), (True, False), (True, True)])
+def test_partly_filled_last_wave_is_cut_along_k(wrapper, mode, tol, tA, tB):
+    # more tiles than SM pairs, with a last wave that would leave most SMs idle: the first waves run whole
+    # tiles, the tiles of the last wave are cut along K (tile-shaped partial sums + reduction kernel).
+    # Ragged right and bottom edges, beta = 1, and a batch whose tiles straddle the whole / cut boundary.
+    wrapper.set_math_mode(mode)
+    _check(wrapper, 2308, 2300, 1028, tA, tB, 0.5, 1.0, 811, tol)
+    _check(wrapper, 772, 1000, 1536, tA, tB, 1.0, 0.0, 812, tol, batch=7)
+    wrapper.set_tuning(TUNE_FORCE_BN, 256)
+    for pair in (1, 2):                       # the same on the CTA-pair and on the single-CTA kernel
+        wrapper.set_tuning(TUNE_PAIR, pair)
+        _check(wrapper, 2308, 2300, 1028, tA, tB, 1.0, 1.0, 813 + pair, tol)
+        assert wrapper.last_kernel().startswith("umma2" if pair == 1 else "umma_"), wrapper.last_kernel()
+        if mode == MATH_3XTF32:               # 81 (171) tiles on 74 (148) slots: the model must cut the 7 (23) left over
+            assert "splitk" in wrapper.last_kernel(), wrapper.last_kernel()
+        _check(wrapper, 772, 1000, 1536, tA, tB, 1.0, 1.0, 815 + pair, tol, batch=7)
+
+
 def test_long_k_keeps_fp32_accuracy(wrapper):
     # the tensor-core accumulator truncates; the kernel must not let that grow with K
     wrapper.set_math_mode(MATH_3XTF32)
