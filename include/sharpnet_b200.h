@@ -87,6 +87,13 @@ int snb200_check_device_status(snb200_handle_t handle);
 int snb200_get_launch_count(snb200_handle_t handle, long long* count);
 int snb200_get_last_kernel(snb200_handle_t handle, char* buf, int buf_len);
 int snb200_get_version(void);
+/* Device time of the matrix products (no counterpart in SharpNet; the role of a profiler range).
+ * Between _begin and _end the handle records a CUDA-event pair on its stream around every matrix
+ * product it launches -- the Dot / batched entry points and the products inside the Dense and attention
+ * entry points, with their reduction pass when K is cut -- at most 4096 of them.  _end waits for the
+ * stream and returns the sum of the pairs' elapsed times and the number of products timed. */
+int snb200_gemm_timing_begin(snb200_handle_t handle);
+int snb200_gemm_timing_end(snb200_handle_t handle, double* total_ms, int* gemm_calls);
 /* Kernel-selection overrides for experiments and tests (no counterpart in SharpNet).
  * key 3: K extent accumulated inside the tensor core before the sum moves to registers (3xTF32; default 128,
  *        0 = whole K); key 4: CTA-pair kernel (0 automatic, 1 always, 2 never); key 5: split-K and

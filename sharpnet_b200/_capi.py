@@ -39,6 +39,8 @@ SIGNATURES = {
     "snb200_get_launch_count": (_I, [_H, _c.POINTER(_L)]),
     "snb200_get_last_kernel": (_I, [_H, _c.c_char_p, _I]),
     "snb200_get_version": (_I, []),
+    "snb200_gemm_timing_begin": (_I, [_H]),
+    "snb200_gemm_timing_end": (_I, [_H, _c.POINTER(_c.c_double), _c.POINTER(_I)]),
     "snb200_gemm": (_I, [_H, _I, _I, _I, _I, _I, _I, _F, _P, _P, _F, _P]),
     "snb200_batched_gemm": (_I, [_H, _I, _I, _I, _I, _L, _I, _I, _L, _L, _I, _F, _P, _P, _F, _P]),
     "snb200_dense_fwd": (_I, [_H, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P]),

@@ -571,11 +571,12 @@ static __global__ void __launch_bounds__(256) splitk_reduce_transposed_kernel(co
 }
 
 // Second pass for the tiled workspace layout: sums the `splits` partial tiles of every tail tile and
-// applies the epilogue.  Grid = (tail tiles, tile_rows / 32); a block of 256 threads covers 32 rows of
-// one tile, a float4 per thread and step.
+// applies the epilogue.  Grid = (tail tiles, tile_rows / rows_per_block) with rows_per_block = 1024 / bn: a
+// block of 256 threads covers 1024 elements of one tile, one float4 per thread, so that even a handful of
+// tail tiles spreads over all SMs.
 struct TailReduceParams {
   int M, N, tiles_m, tiles_n;   // tile grid as the GEMM kernel walked it (tile = tile_rows x bn)
-  int tile_rows, bn;
+  int tile_rows, bn, rows_per_block;
   int whole_tiles, tail, splits;
   const float* partial;
   long long tile_elems;         // tile_rows * bn
@@ -591,17 +592,18 @@ struct TailReduceParams {
 static __global__ void __launch_bounds__(256) tail_reduce_kernel(const TailReduceParams p) {
   int b, tm, tn;
   tile_coords(p.whole_tiles + blockIdx.x, p.tiles_m, p.tiles_n, b, tm, tn);
-  const int r0 = blockIdx.y * 32;
+  const int r0 = blockIdx.y * p.rows_per_block;
   const int q_per_row = p.bn >> 2;
   const float* src = p.partial + static_cast<long long>(blockIdx.x) * p.tile_elems;
   const long long split_stride = static_cast<long long>(p.tail) * p.tile_elems;
-  for (int i = threadIdx.x; i < 32 * q_per_row; i += 256) {
+  for (int i = threadIdx.x; i < p.rows_per_block * q_per_row; i += 256) {
     const int r = r0 + i / q_per_row;
     const int c = (i % q_per_row) << 2;
     const int row = tm * p.tile_rows + r, col = tn * p.bn + c;
     if (row >= p.M || col >= p.N) continue;
     const float* s0 = src + static_cast<long long>(r) * p.bn + c;
     float4 sum = *reinterpret_cast<const float4*>(s0);
+#pragma unroll 4
     for (int s = 1; s < p.splits; ++s) {
       const float4 v = *reinterpret_cast<const float4*>(s0 + s * split_stride);
       sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;

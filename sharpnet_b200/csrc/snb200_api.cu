@@ -33,7 +33,11 @@ struct snb200_context {
   char last_kernel[64];
   char last_error[256];
   void* nccl_comm;
+  int time_gemms;              // snb200_gemm_timing_begin .. _end: an event pair around every GEMM
+  cudaEvent_t* gemm_events;
+  int gemm_events_used;        // events recorded so far (two per GEMM)
 };
+constexpr int kMaxTimedGemms = 4096;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -123,6 +127,10 @@ extern "C" int snb200_destroy(snb200_handle_t h) {
   if (h->nccl_comm) snb200_comm_destroy(h);
   cudaFree(h->workspace);
   cudaFree(h->error_word);
+  if (h->gemm_events) {
+    for (int i = 0; i < 2 * kMaxTimedGemms; ++i) cudaEventDestroy(h->gemm_events[i]);
+    free(h->gemm_events);
+  }
   free(h);
   return 0;
 }
@@ -413,20 +421,32 @@ static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
 
 // Picks the kernel (one CTA per 128 x BN tile, or a CTA pair per 256 x BN tile), the tile width and the
 // K split of the last, partly filled wave, by a time estimate in microseconds:
-//   launch + [whole waves * K blocks + tail waves * K blocks per split] * (time of one 32-deep K block) + last
-//   epilogue + the reduction pass over the workspace.
-// The per-block times are measured on a B200 (3xTF32: a pair does 256 x 256 x 32 in 0.98 us, one CTA 128 x 256 x 32
-// in 1.6 us; narrow tiles cost more per flop because the A operand is re-read for fewer columns).
+//   fixed + [whole waves * K blocks + tail waves * K blocks per split] * (time of one 32-deep K block)
+//   + the reduction pass over the workspace.
+// Both constants are measured on a B200, one wave of tiles at K = 1024 and K = 4096, per kernel, tile width and
+// operand layout.  What they show: the tensor core reads both operand slices from shared memory for every
+// instruction, so a narrow tile (which re-reads its 128 rows of A for few columns) costs almost as much per K
+// block as a tile twice as wide -- narrow tiles only pay when they fill a wave that wide tiles cannot -- and a
+// pair, where each SM holds half of B, runs a 256-wide tile 1.45x faster than one CTA does in 3xTF32 mode.
 struct TileChoice { int pair; int bn; int splits; int whole_tiles; };   // splits > 1: cut K of the tail tiles
-static double kblock_us(bool split3x, int pair, int bn, const GemmProblem& g) {
+struct TileCost { double kblock_us, fixed_us; };
+static TileCost tile_cost(bool split3x, int pair, int bn, const GemmProblem& g) {
   const int i = bn == 256 ? 0 : bn == 128 ? 1 : bn == 64 ? 2 : 3;
-  if (split3x) {
-    static const double single[4] = {1.60, 0.86, 0.50, 0.34}, paired[4] = {0.98, 0.84, 0.77, 0.77};
+  if (split3x) {   // the hi/lo split and three products per block hide the operand layout
+    static const TileCost single[4] = {{1.48, 15.5}, {0.81, 12.4}, {0.81, 9.4}, {0.69, 7.8}};
+    static const TileCost paired[4] = {{1.02, 14.8}, {0.805, 13.6}, {0.69, 11.2}, {0.69, 11.2}};
     return pair ? paired[i] : single[i];
   }
-  static const double single[4] = {0.457, 0.305, 0.23, 0.19}, paired[4] = {0.443, 0.32, 0.25, 0.25};
-  const bool nt = !g.transA && g.transB;   // both operands K-major: the layout the pair kernel feeds fastest
-  return pair ? paired[i] * (nt ? 1.0 : 1.13) : single[i];
+  // TF32: K-major operands (A not transposed, B transposed) are the fastest to feed
+  static const TileCost single_nt[4] = {{0.396, 10.5}, {0.348, 9.7}, {0.325, 8.6}, {0.318, 6.8}};
+  static const TileCost paired_nt[4] = {{0.377, 12.9}, {0.355, 11.6}, {0.321, 10.4}, {0.321, 10.4}};
+  static const TileCost single_nn[4] = {{0.469, 11.7}, {0.366, 10.4}, {0.324, 8.4}, {0.322, 6.5}};
+  static const TileCost paired_nn[4] = {{0.428, 13.3}, {0.351, 11.7}, {0.334, 9.8}, {0.334, 9.8}};
+  static const TileCost single_tn[4] = {{0.546, 11.3}, {0.432, 10.6}, {0.372, 7.8}, {0.339, 6.2}};
+  static const TileCost paired_tn[4] = {{0.548, 11.8}, {0.448, 11.9}, {0.390, 10.3}, {0.390, 10.3}};
+  if (g.transA) return pair ? paired_tn[i] : single_tn[i];
+  if (!g.transB) return pair ? paired_nn[i] : single_nn[i];
+  return pair ? paired_nt[i] : single_nt[i];
 }
 static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, bool split) {
   TileChoice best = {0, 256, 1, 0};
@@ -448,8 +468,8 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
       const long long tiles = static_cast<long long>(g.batch) * ((g.M + rows - 1) / rows) * ((g.N + bn - 1) / bn);
       const long long slots = pair ? h->sm_count / 2 : h->sm_count;
       const long long whole = tiles / slots * slots, tail = tiles - whole;
-      const double c = kblock_us(split, pair, bn, g);
-      const double fixed = 8.0 + 6.0 * bn / 256.0;
+      const TileCost tc = tile_cost(split, pair, bn, g);
+      const double c = tc.kblock_us, fixed = tc.fixed_us;
       for (int j = 0; j < 11; ++j) {
         const long long ks = ks_cand[j];
         if (ks > 1 && (!allow_splitk || tail == 0 || kb / ks < 8)) break;   // at least 256 of K per unit
@@ -458,7 +478,9 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
         const long long kbps = ((kb + ks - 1) / ks + 3) / 4 * 4;
         const long long tail_waves = (tail * ks + slots - 1) / slots;
         double cost = fixed + c * (static_cast<double>(whole / slots) * kb + static_cast<double>(tail_waves) * (ks > 1 ? kbps : kb));
-        if (ks > 1) cost += 5.0 + static_cast<double>(ks + 1) * tail_floats * 4.0 / 5.0e6;
+        // a cut costs: the reduction kernel (launch + its traffic) and, per wave of cut units, one more
+        // pipeline fill and a partial-tile store that nothing overlaps
+        if (ks > 1) cost += 7.0 + static_cast<double>(ks + 1) * tail_floats * 4.0 / 4.0e6 + 2.0 * tail_waves;
         if (cost < best_cost * 0.999) {
           best_cost = cost; best.pair = pair; best.bn = bn; best.splits = static_cast<int>(ks);
           best.whole_tiles = static_cast<int>(whole);
@@ -474,7 +496,7 @@ static int launch_tail_reduce(snb200_handle_t h, const GemmProblem& g, const Spl
   TailReduceParams r;
   r.M = g.M; r.N = g.N;
   r.tiles_m = plan.tiles_m; r.tiles_n = (g.N + bn - 1) / bn;
-  r.tile_rows = tile_rows; r.bn = bn;
+  r.tile_rows = tile_rows; r.bn = bn; r.rows_per_block = 1024 / bn;
   r.whole_tiles = plan.whole_tiles; r.tail = plan.tail; r.splits = plan.parts;
   r.partial = h->workspace;
   r.tile_elems = static_cast<long long>(tile_rows) * bn;
@@ -482,7 +504,7 @@ static int launch_tail_reduce(snb200_handle_t h, const GemmProblem& g, const Spl
   r.alpha = g.alpha; r.beta = g.beta; r.act = g.act;
   r.vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (g.batch == 1 || g.strideC % 4 == 0) &&
              (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias));
-  dim3 grid(plan.tail, tile_rows / 32);
+  dim3 grid(plan.tail, tile_rows / r.rows_per_block);
   tail_reduce_kernel<<<grid, 256, 0, h->stream>>>(r);
   h->launches += 1;
   return check_launch(h, "tail_reduce_kernel launch");
@@ -508,7 +530,49 @@ static int launch_reduce(snb200_handle_t h, const GemmProblem& g, int parts, int
   return check_launch(h, "splitk_reduce_kernel launch");
 }
 
+static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g);
 static int run_gemm(snb200_handle_t h, const GemmProblem& g) {
+  const bool timed = h->time_gemms && h->gemm_events_used + 2 <= 2 * kMaxTimedGemms;
+  if (timed) SNB_CUDA(h, cudaEventRecord(h->gemm_events[h->gemm_events_used], h->stream));
+  const int st = run_gemm_untimed(h, g);
+  if (timed) {
+    SNB_CUDA(h, cudaEventRecord(h->gemm_events[h->gemm_events_used + 1], h->stream));
+    h->gemm_events_used += 2;
+  }
+  return st;
+}
+
+extern "C" int snb200_gemm_timing_begin(snb200_handle_t h) {
+  int st = enter(h);
+  if (st) return st;
+  if (!h->gemm_events) {
+    h->gemm_events = static_cast<cudaEvent_t*>(calloc(2 * kMaxTimedGemms, sizeof(cudaEvent_t)));
+    if (!h->gemm_events) return fail(h, SNB200_STATUS_ALLOC_FAILED, "out of host memory");
+    for (int i = 0; i < 2 * kMaxTimedGemms; ++i) SNB_CUDA(h, cudaEventCreate(&h->gemm_events[i]));
+  }
+  h->gemm_events_used = 0;
+  h->time_gemms = 1;
+  return 0;
+}
+
+extern "C" int snb200_gemm_timing_end(snb200_handle_t h, double* total_ms, int* gemm_calls) {
+  int st = enter(h);
+  if (st) return st;
+  if (!h->time_gemms) return fail(h, SNB200_STATUS_INVALID_VALUE, "snb200_gemm_timing_begin was not called");
+  h->time_gemms = 0;
+  SNB_CUDA(h, cudaStreamSynchronize(h->stream));
+  double sum = 0.0;
+  for (int i = 0; i + 1 < h->gemm_events_used; i += 2) {
+    float ms = 0.0f;
+    SNB_CUDA(h, cudaEventElapsedTime(&ms, h->gemm_events[i], h->gemm_events[i + 1]));
+    sum += ms;
+  }
+  if (total_ms) *total_ms = sum;
+  if (gemm_calls) *gemm_calls = h->gemm_events_used / 2;
+  return 0;
+}
+
+static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
   if (g.M == 0 || g.N == 0 || g.batch == 0) return 0;
   const int force = h->tune[TUNE_FORCE_PATH];  // 0 auto, 1 tensor cores whenever eligible, 2 SIMT
   bool use_umma = h->math_mode != SNB200_MATH_FP32_SIMT && force != 2 && tma_eligible(g);

@@ -70,6 +70,16 @@ class GPUWrapper:
     def check_device_status(self):
         check(self.handle, self.lib.snb200_check_device_status(self.handle))
 
+    def gemm_timing_begin(self):
+        """Starts recording a CUDA-event pair around every matrix product this handle launches."""
+        check(self.handle, self.lib.snb200_gemm_timing_begin(self.handle))
+
+    def gemm_timing_end(self):
+        """Waits for the stream; returns (device milliseconds spent in matrix products, how many)."""
+        ms, n = ctypes.c_double(), ctypes.c_int()
+        check(self.handle, self.lib.snb200_gemm_timing_end(self.handle, ctypes.byref(ms), ctypes.byref(n)))
+        return ms.value, n.value
+
     def Dispose(self):
         if self.handle is not None:
             self.lib.snb200_destroy(self.handle)
