@@ -228,6 +228,12 @@ int snb200_sdpa_bwd(snb200_handle_t handle, int batch, int q_steps, int v_steps,
                     const float* Q, const float* K, const float* V, const float* dy, const float* weights,
                     float* scores_grad_scratch, float* dQ, float* dK, float* dV);
 
+/* dst[a, c, b, :] = src[a, b, c, :] for a dense src of shape [A, B, C, D] (D = product of the trailing
+ * dimensions): Tensor.TransposeSecondAndThirdDimension (Prod/Data/Tensor.cs, GPU Prod/GPU/GpuTensor.cs:672-684,
+ * CPU Prod/CPU/CpuTensor.cs:301-322), the head split and merge of MultiheadAttention
+ * (Prod/Layers/MultiheadAttention.cs:209-236).  src and dst must not overlap. */
+int snb200_transpose_second_third(snb200_handle_t handle, int A, int B, int C, int D, const float* src, float* dst);
+
 /* ---- optimizer updates (the step right after the path in every training iteration) -----------
  * One kernel, one pass over the tensors.
  * SGD:  velocity = momentum * velocity - learning_rate * dW ;

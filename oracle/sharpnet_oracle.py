@@ -222,6 +222,63 @@ def sdpa_backward(Q, K, V, dy, weights, use_scale):
     return np.einsum("bqk,bke->bqe", ds, Kd), np.einsum("bqk,bqe->bke", ds, Qd), dV
 
 
+def transpose_second_third(x):
+    """target[a, c, b, :] = x[a, b, c, :]   (Tensor.TransposeSecondAndThirdDimension, Prod/CPU/CpuTensor.cs:301-322)."""
+    return np.ascontiguousarray(np.swapaxes(x, 1, 2))
+
+
+def multihead_attention_forward(Q, K, V, weights, biases, num_heads, key_dim, value_dim, is_causal,
+                                w_layout=W_OUT_IN, f64=False):
+    """MultiheadAttention.ForwardPropagation (Prod/Layers/MultiheadAttention.cs:178-238).
+
+    Q [batch, q_steps, embed], K and V [batch, v_steps, embed]; ``weights`` = (w_Q, w_K, w_V, out_proj_weight),
+    ``biases`` the four matching vectors or None each.  Every projection is Linear.DenseForwardPropagation on the
+    last dimension, the heads are split with TransposeSecondAndThirdDimension ([b, t, h, d] -> [b, h, t, d]),
+    attention always scales by 1/sqrt(key_dim) (use_scale is a constant of the layer, :32), the heads are merged by
+    the inverse permutation and projected by out_proj_weight.  Returns (y, cache) with the tensors the backward pass
+    reads: the per-head Q, K, V, the attention weights and the merged heads."""
+    B, Tq, E = Q.shape
+    Tk = V.shape[1]
+    wq, wk, wv, wo = weights
+    bq, bk, bv, bo = biases if biases is not None else (None, None, None, None)
+    H = num_heads
+
+    def project(x, W, b, d):
+        y = dense_forward(x.reshape(-1, x.shape[-1]), W, b, ACT_IDENTITY, w_layout, f64)[1]
+        return transpose_second_third(y.reshape(B, -1, H, d)).reshape(B * H, -1, d)
+    dt = np.float64 if f64 else np.float32
+    Qh, Kh, Vh = project(Q, wq, bq, key_dim), project(K, wk, bk, key_dim), project(V, wv, bv, value_dim)
+    w, a = sdpa_forward(Qh.astype(dt), Kh.astype(dt), Vh.astype(dt), True, is_causal, f64)
+    merged = transpose_second_third(a.reshape(B, H, Tq, value_dim)).reshape(B * Tq, H * value_dim)
+    y = dense_forward(merged.astype(dt), wo, bo, ACT_IDENTITY, w_layout, f64)[1].reshape(B, Tq, -1)
+    return y, {"Qh": Qh, "Kh": Kh, "Vh": Vh, "weights": w, "merged": merged}
+
+
+def multihead_attention_backward(Q, K, V, dy, weights, cache, num_heads, key_dim, value_dim, multiplier=1.0,
+                                 w_layout=W_OUT_IN):
+    """MultiheadAttention.BackwardPropagation (Prod/Layers/MultiheadAttention.cs:240-295) in float64.
+    Returns (dQ, dK, dV, [dw_Q, dw_K, dw_V, d_out_proj_weight], [db_Q, db_K, db_V, db_O])."""
+    B, Tq, E = Q.shape
+    Tk = V.shape[1]
+    H = num_heads
+    wq, wk, wv, wo = weights
+    g2 = np.asarray(dy, np.float64).reshape(B * Tq, -1)
+    _, dwo, dbo, dmerged = dense_backward(cache["merged"], wo, g2, ACT_IDENTITY, None, None, multiplier, w_layout, True,
+                                          f64=True)
+    da = transpose_second_third(dmerged.reshape(B, Tq, H, value_dim)).reshape(B * H, Tq, value_dim)
+    dQh, dKh, dVh = sdpa_backward(cache["Qh"], cache["Kh"], cache["Vh"], da, cache["weights"], True)
+
+    def unproject(dh, x, W, T, d):
+        flat = transpose_second_third(dh.reshape(B, H, T, d)).reshape(B * T, H * d)
+        _, dW, db, dx = dense_backward(x.reshape(-1, x.shape[-1]), W, flat, ACT_IDENTITY, None, None, multiplier,
+                                       w_layout, True, f64=True)
+        return dx.reshape(x.shape), dW, db
+    dQ, dwq, dbq = unproject(dQh, Q, wq, Tq, key_dim)
+    dK, dwk, dbk = unproject(dKh, K, wk, Tk, key_dim)
+    dV, dwv, dbv = unproject(dVh, V, wv, Tk, value_dim)
+    return dQ, dK, dV, [dwq, dwk, dwv, dwo], [dbq, dbk, dbv, dbo]
+
+
 def loss_gradient(loss, y_expected, y_predicted):
     """dy of the loss w.r.t. the prediction, in fp32 with the reference's operation order:
     BinaryCrossentropy  m*p - m*y, m = 1/numClass   (Prod/Data/Tensor.cs:1379-1387, AddTensor(-m, y, m));

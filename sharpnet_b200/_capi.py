@@ -57,6 +57,7 @@ SIGNATURES = {
     "snb200_softmax_bwd": (_I, [_H, _L, _I, _P, _P, _P]),
     "snb200_sdpa_fwd": (_I, [_H, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "snb200_sdpa_bwd": (_I, [_H, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "snb200_transpose_second_third": (_I, [_H, _I, _I, _I, _I, _P, _P]),
     "snb200_sgd_update": (_I, [_H, _L, _F, _F, _I, _P, _P, _P]),
     "snb200_adam_update": (_I, [_H, _L, _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_double, _I, _P, _P, _P, _P]),
     "snb200_comm_get_unique_id": (_I, [_P]),

@@ -1,8 +1,12 @@
-"""Host-side mirror of SharpNet's scaled dot-product attention layer
-(Prod/Layers/ScaledDotProductAttentionLayer.cs) on top of the C ABI: same static-method names and
-argument meaning; each direction is one ``snb200_sdpa_*`` call (strided-batched GEMMs + one fused
-mask/softmax pass)."""
-from ._capi import check
+"""Host-side mirror of SharpNet's attention layers on top of the C ABI.
+
+``ScaledDotProductAttention*Propagation`` (Prod/Layers/ScaledDotProductAttentionLayer.cs): same static-method
+names and argument meaning; each direction is one ``snb200_sdpa_*`` call (strided-batched GEMMs + one fused
+mask/softmax pass).  ``MultiheadAttention`` (Prod/Layers/MultiheadAttention.cs): the four Dense projections,
+the head split / merge permutations and the attention core, in the reference's call order."""
+
+from ._capi import ACT_IDENTITY, W_OUT_IN, check
+from .linear import FusedDenseBackward, FusedDenseForward
 from .tensor import GPUTensor
 
 
@@ -39,3 +43,115 @@ def ScaledDotProductAttentionBackwardPropagation(dQ, dK, dV, Q, K, V, dy, weight
                                dy.Pointer, weights_buffer.Pointer, scores_gradients_buffer.Pointer, dQ.Pointer,
                                dK.Pointer, dV.Pointer)
     check(w.handle, st)
+
+
+class MultiheadAttention:
+    """Multi-head attention over Q [batch, q_steps, embed] and K, V [batch, v_steps, embed]
+    (Prod/Layers/MultiheadAttention.cs:24-295).
+
+    Parameters live in one weights tensor [2*heads*key_dim + 2*heads*value_dim, embed] and one bias vector, sliced
+    into w_Q, w_K, w_V, out_proj_weight and their biases as the layer does (:37-50,137-140).  ``w_layout`` selects
+    [out, in] rows (the layer's own form, Linear.cs:125-132) or the [in, out] form of the Keras-derived goldens.
+    Forward keeps the per-head Q, K, V, the attention weights and the merged heads for the backward pass."""
+
+    def __init__(self, num_heads, key_dim, value_dim, use_bias_Q_K_V, use_bias_O, is_causal, embed_dim, wrapper,
+                 w_layout=W_OUT_IN):
+        if num_heads * value_dim != embed_dim:
+            # out_proj_weight is declared [heads*value_dim, embed] and used as [embed, heads*value_dim] (:121-126,236)
+            raise ValueError("num_heads * value_dim must equal the embedding dimension")
+        self.num_heads, self.key_dim, self.value_dim = num_heads, key_dim, value_dim
+        self.is_causal, self.embed_dim, self.layout, self.w = bool(is_causal), embed_dim, w_layout, wrapper
+        outs = [num_heads * key_dim, num_heads * key_dim, num_heads * value_dim, embed_dim]
+        ins = [embed_dim, embed_dim, embed_dim, num_heads * value_dim]
+        self._w_shapes = [(o, i) if w_layout == W_OUT_IN else (i, o) for o, i in zip(outs, ins)]
+        self._w_counts = [o * i for o, i in zip(outs, ins)]
+        self._b_counts = [o if use else 0 for o, use in zip(outs, (use_bias_Q_K_V,) * 3 + (use_bias_O,))]
+        self.Weights = GPUTensor((sum(self._w_counts) // embed_dim, embed_dim), None, wrapper)
+        self.WeightGradients = GPUTensor(self.Weights.Shape, None, wrapper)
+        nb = sum(self._b_counts)
+        self.Bias = GPUTensor((nb,), None, wrapper) if nb else None
+        self.BiasGradients = GPUTensor((nb,), None, wrapper) if nb else None
+        self._cache = None
+
+    # -- slices of the parameter tensors (Prod/Layers/MultiheadAttention.cs:344-376) -------------
+    def _w(self, t, i):
+        return t.Slice(sum(self._w_counts[:i]), self._w_shapes[i])
+
+    def _b(self, t, i):
+        if t is None or self._b_counts[i] == 0:
+            return None
+        return t.Slice(sum(self._b_counts[:i]), (self._b_counts[i],))
+
+    w_Q = property(lambda self: self._w(self.Weights, 0))
+    w_K = property(lambda self: self._w(self.Weights, 1))
+    w_V = property(lambda self: self._w(self.Weights, 2))
+    out_proj_weight = property(lambda self: self._w(self.Weights, 3))
+    w_Q_bias = property(lambda self: self._b(self.Bias, 0))
+    w_K_bias = property(lambda self: self._b(self.Bias, 1))
+    w_V_bias = property(lambda self: self._b(self.Bias, 2))
+    out_proj_bias = property(lambda self: self._b(self.Bias, 3))
+
+    def gradients(self):
+        """([dw_Q, dw_K, dw_V, d_out_proj_weight], [db_Q, db_K, db_V, db_O]) as views of the gradient tensors."""
+        return ([self._w(self.WeightGradients, i) for i in range(4)],
+                [self._b(self.BiasGradients, i) for i in range(4)])
+
+    def _split_heads(self, x, W, b, d, scratch):
+        """Dense projection on the last dimension, then [b, t, h, d] -> [b * h, t, d]."""
+        B, T = x.Shape[0], x.Shape[1]
+        H = self.num_heads
+        flat = scratch.Slice(0, (B * T, H * d))
+        FusedDenseForward(flat, x, W, b, ACT_IDENTITY, None, self.layout, flattenInputTensorOnLastDimension=True)
+        heads = GPUTensor((B, H, T, d), None, self.w)
+        flat.Reshape(B, T, H, d).TransposeSecondAndThirdDimension(heads)
+        return heads.Reshape(B * H, T, d)
+
+    def ForwardPropagation(self, allX, y, isTraining=True):
+        """(Prod/Layers/MultiheadAttention.cs:178-238)"""
+        Q, K, V = allX
+        if V.Shape != K.Shape:
+            raise ValueError(f"V.Shape and K.Shape must be equal, but are {V.Shape} and {K.Shape}")
+        if Q.Shape[2] != V.Shape[2]:
+            raise ValueError("queries.Shape[2] and values.Shape[2] must be equal (same embedding dim)")
+        B, Tq, E = Q.Shape
+        Tk = V.Shape[1]
+        if y.Shape != [B, Tq, E]:
+            raise ValueError("y must be [batch, query_timeSteps, embed_dim]")
+        H, kd, vd = self.num_heads, self.key_dim, self.value_dim
+        scratch = GPUTensor((max(B * Tq * H * kd, B * Tk * H * kd, B * Tk * H * vd, B * Tq * H * vd),), None, self.w)
+        Qh = self._split_heads(Q, self.w_Q, self.w_Q_bias, kd, scratch)
+        Kh = self._split_heads(K, self.w_K, self.w_K_bias, kd, scratch)
+        Vh = self._split_heads(V, self.w_V, self.w_V_bias, vd, scratch)
+        heads = scratch.Slice(0, (B * H, Tq, vd))
+        weights = ScaledDotProductAttentionForwardPropagation(Qh, Kh, Vh, heads, isTraining, None, True, self.is_causal)
+        merged = GPUTensor((B, Tq, H, vd), None, self.w)
+        heads.Reshape(B, H, Tq, vd).TransposeSecondAndThirdDimension(merged)
+        merged = merged.Reshape(B, Tq, H * vd)
+        FusedDenseForward(y, merged, self.out_proj_weight, self.out_proj_bias, ACT_IDENTITY, None, self.layout,
+                          flattenInputTensorOnLastDimension=True)
+        self._cache = (Qh, Kh, Vh, weights, merged) if isTraining else None
+
+    def BackwardPropagation(self, allX, dy, allDx, multiplier=1.0):
+        """(Prod/Layers/MultiheadAttention.cs:240-295); ``multiplier`` is the dW factor of Linear.cs:152-158."""
+        Q, K, V = allX
+        dQ, dK, dV = allDx
+        Qh, Kh, Vh, weights, merged = self._cache
+        B, Tq, _ = Q.Shape
+        Tk = V.Shape[1]
+        H, kd, vd = self.num_heads, self.key_dim, self.value_dim
+        dws, dbs = self.gradients()
+        scratch = GPUTensor((max(B * Tq * H * kd, B * Tk * H * kd, B * Tk * H * vd, B * Tq * H * vd),), None, self.w)
+        d_merged = scratch.Slice(0, (B, Tq, H * vd))
+        FusedDenseBackward(d_merged, dws[3], dbs[3], merged, dy, self.out_proj_weight, ACT_IDENTITY, None, None,
+                           multiplier, None, self.layout, flattenInputTensorOnLastDimension=True)
+        d_heads = GPUTensor((B, H, Tq, vd), None, self.w)
+        d_merged.Reshape(B, Tq, H, vd).TransposeSecondAndThirdDimension(d_heads)
+        dQh, dKh, dVh = (GPUTensor(t.Shape, None, self.w) for t in (Qh, Kh, Vh))
+        ScaledDotProductAttentionBackwardPropagation(dQh, dKh, dVh, Qh, Kh, Vh, d_heads.Reshape(B * H, Tq, vd), weights,
+                                                     True)
+        for dh, x, dx, i, T, d in ((dQh, Q, dQ, 0, Tq, kd), (dKh, K, dK, 1, Tk, kd), (dVh, V, dV, 2, Tk, vd)):
+            flat = scratch.Slice(0, (B, T, H, d))
+            dh.Reshape(B, H, T, d).TransposeSecondAndThirdDimension(flat)
+            FusedDenseBackward(dx, dws[i], dbs[i], x, flat.Reshape(B * T, H * d), self._w(self.Weights, i), ACT_IDENTITY,
+                               None, None, multiplier, None, self.layout, flattenInputTensorOnLastDimension=True)
+        self._cache = None

@@ -85,6 +85,26 @@ static __global__ void axpy_kernel(long long n, float alpha, const float* __rest
   for (long long i = nv * VEC + tid; i < n; i += stride) y[i] = fmaf(alpha, x[i], y[i]);
 }
 
+// dst[a, c, b, :] = src[a, b, c, :] for src [A, B, C, D]: the head split / merge of multi-head attention
+// (Prod/CPU/CpuTensor.cs:301-322, Prod/GPU/GpuTensor.cs:672-684).  One thread per VEC consecutive floats
+// of a D-run, enumerated in destination order so that writes are fully coalesced; reads are D-long runs.
+template <int VEC>
+static __global__ void transpose_second_third_kernel(long long total_vec, int B, int C, int Dv,
+                                                     const float* __restrict__ src, float* __restrict__ dst) {
+  typedef typename Pack<VEC>::type P;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total_vec; i += stride) {
+    const int d = static_cast<int>(i % Dv);
+    long long r = i / Dv;                       // destination row index (a, c, b)
+    const int b = static_cast<int>(r % B);
+    r /= B;
+    const int c = static_cast<int>(r % C);
+    const long long a = r / C;
+    const long long s = ((a * B + b) * C + c) * Dv + d;
+    reinterpret_cast<P*>(dst)[i] = reinterpret_cast<const P*>(src)[s];
+  }
+}
+
 // Column sums of g[M x N] over a slab of rows, optionally fused with the activation gradient:
 //   g = dy                        (FUSE_ACT = false:  db = sum_m dy,  CpuTensor.cs:3343-3362)
 //   g = act'(z, y) * dy -> dz     (FUSE_ACT = true:   ActivationBackward + bias gradient in one pass)

@@ -920,6 +920,23 @@ extern "C" int snb200_axpy(snb200_handle_t h, long long count, float alpha, cons
   return check_launch(h, "axpy launch");
 }
 
+extern "C" int snb200_transpose_second_third(snb200_handle_t h, int A, int B, int C, int D, const float* src,
+                                             float* dst) {
+  int st = enter(h);
+  if (st) return st;
+  if (A < 0 || B < 0 || C < 0 || D < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  const long long total = static_cast<long long>(A) * B * C * D;
+  if (total == 0) return 0;
+  if (!src || !dst) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  if (src == dst) return fail(h, SNB200_STATUS_INVALID_VALUE, "the permutation is not done in place");
+  if (D % 4 == 0 && aligned16(src) && aligned16(dst))
+    transpose_second_third_kernel<4><<<ew_grid(h, total / 4, 256), 256, 0, h->stream>>>(total / 4, B, C, D / 4, src, dst);
+  else
+    transpose_second_third_kernel<1><<<ew_grid(h, total, 256), 256, 0, h->stream>>>(total, B, C, D, src, dst);
+  note_kernel(h, "transpose_second_third", 1);
+  return check_launch(h, "transpose_second_third launch");
+}
+
 extern "C" int snb200_sgd_update(snb200_handle_t h, long long count, float learning_rate, float momentum, int nesterov,
                                  const float* dW, float* W, float* velocity) {
   int st = enter(h);

@@ -137,6 +137,23 @@ class GPUTensor:
             return self.Reshape(-1, self.Shape[-1])
         return self.Reshape(self.Shape[0], -1)
 
+    def Slice(self, startIndex, sliceShape):
+        """A view of ``Count(sliceShape)`` elements starting at element ``startIndex``, sharing this tensor's memory
+        (Prod/GPU/GpuTensor.cs:606-620)."""
+        count = int(np.prod(sliceShape))
+        assert 0 <= startIndex and startIndex + count <= self.storage.numel()
+        return GPUTensor(sliceShape, wrapper=self.wrapper, storage=self.storage[startIndex:startIndex + count])
+
+    def TransposeSecondAndThirdDimension(self, target):
+        """target[a, c, b, :] = this[a, b, c, :]; ``target`` takes the permuted shape
+        (Prod/GPU/GpuTensor.cs:672-684, Prod/CPU/CpuTensor.cs:301-322)."""
+        assert len(self.Shape) >= 3 and target.Count == self.Count
+        A, B, C = self.Shape[:3]
+        D = self.Count // (A * B * C) if A * B * C else 0
+        target.Shape = [A, C, B] + self.Shape[3:]
+        w = self.wrapper
+        check(w.handle, w.lib.snb200_transpose_second_third(w.handle, A, B, C, D, self.Pointer, target.Pointer))
+
     def ZeroMemory(self):
         self.storage[: self.Count].zero_()
 

@@ -11,6 +11,10 @@ Sources (paths inside the reference):
   Tests/NonReg/TestNetworkPropagation.cs:80-132  Linear + Sigmoid predictions before training and after 10 epochs of
                                                  VanillaSGD ([in,out] weights)
   Tests/NonReg/TestNetworkPropagation.cs:500-575 attention block: predictions before training, plain and causal
+  Tests/NonReg/TestNetworkPropagation.cs:580-623 MultiHeadAttention (3 heads x 5, [in,out] weights): predictions before
+                                                 training, plain and causal
+  Tests/NonReg/ParallelRunWithPyTorch.cs:1013-1129 MultiHeadAttention (3 heads x 2, [out,in] weights), with and without
+                                                 bias, plain and causal: CategoricalCrossentropy loss before training
   Tests/NonReg/ParallelRunWithPyTorch.cs:102-138 Linear(5->3, last-dim flatten)+ReLU+Flatten+Linear(36->3), Mse
   Tests/NonReg/ParallelRunWithPyTorch.cs:179-214 Linear(16->3)+ReLU+Linear(3->3)+Sigmoid, BCE ([out,in] weights)
 """
@@ -107,8 +111,37 @@ def main(ref):
         out[key + "_wlinear"] = _numbers(re.findall(r'FromNumpyArray\("(\[\[.*?\]\])"\)\.CopyTo', blk)[0])   # [10, 3]
         out[key + "_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))
 
+    # ---- multi-head attention, Keras layout: Conv1D(k=1) Q/K/V -> MultiHeadAttention(3 heads, key_dim 5) -> Flatten
+    #      -> Linear(30 -> 3, [in, out]) -> Softmax on X = numpy_array_for_tests(3, 7, 15)
+    i = tnp.index("public void Test_MultiHeadAttention_GPU")
+    blk = tnp[i:tnp.index("//predictions before training", i)]
+    head = tnp[tnp.rindex("[TestCase(false, false, false", 0, i):i]
+    convs = re.findall(r'FromTensorFlowConvNumpyArray\("(.*?)"\)', blk)
+    lits = re.findall(r'FromNumpyArray\("(\[\[.*?\]\])"\)\.CopyTo', blk)
+    out["mha_tf"] = {
+        "conv_q": _numbers(convs[0]), "conv_k": _numbers(convs[1]), "conv_v": _numbers(convs[2]),     # [7 in, 2 out]
+        "w_q": _numbers(lits[0]), "w_k": _numbers(lits[1]), "w_v": _numbers(lits[2]),                 # [15 in, 3 x 5 out]
+        "w_o": _numbers(lits[3]), "w_linear": _numbers(lits[4]),                                      # [15, 15], [30, 3]
+        "cases": [{"use_bias": c[0] == "true", "causal": c[2] == "true", "pred_before": _numbers(c[3])}
+                  for c in re.findall(r'\[TestCase\((\w+), (\w+), (\w+), "(.*?)", "(.*?)"\)', head)],
+    }
+
     # ---- PyTorch-layout network goldens ------------------------------------------------------
     pt = open(os.path.join(ref, "Tests/NonReg/ParallelRunWithPyTorch.cs"), encoding="utf-8-sig").read()
+    # multi-head attention, PyTorch layout: Conv1D(k=1) Q/K/V ([out, in, 1]) -> MultiHeadAttention(3 heads, key_dim 2,
+    # in_proj_weight [18, 6] = w_Q | w_K | w_V, out_proj_weight [6, 6]) -> Flatten -> Linear(12 -> 3, [out, in]) -> Softmax
+    # on X = numpy_array_for_tests(10, 2, 6), Y = y_numpy_array_for_tests(10, 3)
+    for name in ("no_bias", "with_bias"):
+        i = pt.index("public void Test_MultiHeadAttention_" + name)
+        blk = pt[i:pt.index("Train(model, X, Y)", i)]
+        head = pt[pt.rindex("[TestCase(false", 0, i):i]
+        lits = [_numbers(c) for c in re.findall(r'FromNumpyArray\("(\[\[.*?\]\])"\)\.CopyTo', blk)]
+        out["mha_pt_" + name] = {
+            "conv_q": lits[0], "conv_k": lits[1], "conv_v": lits[2], "in_proj_weight": lits[3], "out_proj_weight": lits[4],
+            "w_linear": lits[5],
+            "cases": [{"causal": c[0] == "true", "loss_before": float(c[1]), "loss_after": float(c[2])}
+                      for c in re.findall(r"\[TestCase\((\w+), ([0-9.]+), ([0-9.]+)\)", head)],
+        }
     blk = _between(pt, "public void TestParallelRunWithPyTorch_Mse()", "public void TestParallelRunWithPyTorch_Mse_AdamW")
     out["pt_mse_w1"] = _nth_numpy_literal(blk, 0)         # [3, 5]  = [out, in]
     out["pt_mse_w2"] = _nth_numpy_literal(blk, 1)         # [3, 36]

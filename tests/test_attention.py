@@ -129,3 +129,175 @@ def test_gpu_softmax_alone(wrapper):
                                    rtol=0, atol=2e-6)
         DY.SoftmaxGradientLastDimension(DY, Y)       # in place, as the attention layer calls it
         np.testing.assert_array_equal(DY.ContentAsFloatArray(), DX.ContentAsFloatArray())
+
+
+# ------------------------------------------------------------------------------------------ multi-head attention
+from sharpnet_b200._capi import W_IN_OUT, W_OUT_IN  # noqa: E402
+
+
+def _softmax64(z):
+    e = np.exp(z - z.max(1, keepdims=True))
+    return e / e.sum(1, keepdims=True)
+
+
+def _mha_tf_network(golden, case, mha):
+    """Tests/NonReg/TestNetworkPropagation.cs:580-623: X [3, 7 channels, 15] -> three Conv1D(kernel 1, 2 filters)
+    -> MultiHeadAttention(3 heads x 5) on Q, K, V [3, 2 steps, 15] -> Flatten -> Linear(30 -> 3) -> Softmax, all
+    weights [in, out].  ``mha(Q, K, V, weights, biases, heads, key_dim, value_dim, causal, layout)`` -> y."""
+    g = golden["mha_tf"]
+    X = orc.numpy_array_for_tests(3, 7, 15)
+    Q, K, V = (np.stack([np.asarray(g[k], np.float32).reshape(7, 2).T @ X[b] for b in range(3)]).astype(np.float32)
+               for k in ("conv_q", "conv_k", "conv_v"))
+    weights = [np.asarray(g[k], np.float32).reshape(15, 15) for k in ("w_q", "w_k", "w_v", "w_o")]
+    biases = [np.zeros(15, np.float32)] * 4 if case["use_bias"] else None       # biases start at zero (:300)
+    y = mha(Q, K, V, weights, biases, 3, 5, 5, case["causal"], W_IN_OUT)
+    return _softmax64(y.reshape(3, 30).astype(np.float64) @ np.asarray(g["w_linear"], np.float64).reshape(30, 3))
+
+
+def _mha_pt_loss(golden, name, case, mha):
+    """Tests/NonReg/ParallelRunWithPyTorch.cs:1013-1129: X [10, 2 channels, 6] -> three Conv1D(kernel 1, 2 filters,
+    [out, in, 1]) -> MultiHeadAttention(3 heads x 2, in_proj_weight [18, 6]) -> Flatten -> Linear(12 -> 3) -> Softmax,
+    all weights [out, in]; returns the CategoricalCrossentropy loss on Y = y_numpy_array_for_tests(10, 3)."""
+    g = golden["mha_pt_" + name]
+    X = orc.numpy_array_for_tests(10, 2, 6)
+    Y = orc.y_numpy_array_for_tests(10, 3)
+    Q, K, V = (np.stack([np.asarray(g[k], np.float32).reshape(2, 2) @ X[b] for b in range(10)]).astype(np.float32)
+               for k in ("conv_q", "conv_k", "conv_v"))
+    inw = np.asarray(g["in_proj_weight"], np.float32).reshape(18, 6)
+    weights = [inw[:6].copy(), inw[6:12].copy(), inw[12:].copy(), np.asarray(g["out_proj_weight"], np.float32).reshape(6, 6)]
+    biases = [np.zeros(6, np.float32)] * 4 if name == "with_bias" else None
+    y = mha(Q, K, V, weights, biases, 3, 2, 2, case["causal"], W_OUT_IN)
+    p = _softmax64(y.reshape(10, 12).astype(np.float64) @ np.asarray(g["w_linear"], np.float64).reshape(3, 12).T)
+    return float(-(Y * np.log(p)).sum(1).mean())
+
+
+def _oracle_mha(f64):
+    return lambda Q, K, V, w, b, H, kd, vd, causal, layout: orc.multihead_attention_forward(
+        Q, K, V, w, b, H, kd, vd, causal, layout, f64=f64)[0]
+
+
+@pytest.mark.parametrize("f64", [False, True])
+def test_oracle_multihead_attention_matches_reference_goldens(golden, f64):
+    for case in golden["mha_tf"]["cases"]:
+        p = _mha_tf_network(golden, case, _oracle_mha(f64))
+        np.testing.assert_allclose(p.ravel(), case["pred_before"], rtol=0, atol=1e-6)
+    for name in ("no_bias", "with_bias"):
+        for case in golden["mha_pt_" + name]["cases"]:
+            assert abs(_mha_pt_loss(golden, name, case, _oracle_mha(f64)) - case["loss_before"]) <= 1e-6
+
+
+def _mha_random(B, Tq, Tk, H, kd, seed, bias):
+    rng = np.random.default_rng(seed)
+    E = H * kd
+    Q, K, V = (rng.normal(size=s).astype(np.float32) for s in ((B, Tq, E), (B, Tk, E), (B, Tk, E)))
+    lim = np.sqrt(6.0 / (2 * E))
+    weights = [rng.uniform(-lim, lim, (E, E)).astype(np.float32) for _ in range(4)]
+    biases = [rng.uniform(-0.2, 0.2, E).astype(np.float32) for _ in range(4)] if bias else None
+    dy = rng.normal(size=(B, Tq, E)).astype(np.float32)
+    return Q, K, V, weights, biases, dy
+
+
+@pytest.mark.parametrize("layout", [W_OUT_IN, W_IN_OUT])
+def test_oracle_multihead_attention_backward_by_finite_differences(layout):
+    B, Tq, Tk, H, kd = 2, 3, 3, 2, 2
+    Q, K, V, weights, biases, dy = _mha_random(B, Tq, Tk, H, kd, 5, True)
+    y, cache = orc.multihead_attention_forward(Q, K, V, weights, biases, H, kd, kd, True, layout, f64=True)
+    dQ, dK, dV, dws, dbs = orc.multihead_attention_backward(Q, K, V, dy, weights, cache, H, kd, kd, 1.0, layout)
+
+    def loss(Q_, K_, V_, w_, b_):
+        return float((orc.multihead_attention_forward(Q_, K_, V_, w_, b_, H, kd, kd, True, layout, f64=True)[0] * dy).sum())
+    eps = 1e-6
+    checks = [("Q", dQ, (1, 2, 3)), ("K", dK, (0, 1, 2)), ("V", dV, (1, 0, 0))]
+    checks += [(("w", i), dws[i], (1, 3)) for i in range(4)] + [(("b", i), dbs[i], (2,)) for i in range(4)]
+    for which, grad, idx in checks:
+        vals = {"Q": Q.astype(np.float64), "K": K.astype(np.float64), "V": V.astype(np.float64),
+                "w": [w.astype(np.float64) for w in weights], "b": [b.astype(np.float64) for b in biases]}
+        num = []
+        for sign in (1, -1):
+            v = {k: ([a.copy() for a in x] if isinstance(x, list) else x.copy()) for k, x in vals.items()}
+            target = v[which] if isinstance(which, str) else v[which[0]][which[1]]
+            target[idx] += sign * eps
+            num.append(loss(v["Q"], v["K"], v["V"], v["w"], v["b"]))
+        num = (num[0] - num[1]) / (2 * eps)
+        assert abs(num - grad[idx]) < 2e-6 * max(1.0, abs(num)), (which, num, grad[idx])
+
+
+def _gpu_mha(wrapper, keep=None):
+    from sharpnet_b200.attention import MultiheadAttention
+    from sharpnet_b200.tensor import GPUTensor
+
+    def run(Q, K, V, weights, biases, H, kd, vd, causal, layout):
+        layer = MultiheadAttention(H, kd, vd, biases is not None, biases is not None, causal, Q.shape[2], wrapper, layout)
+        flat_w = np.concatenate([w.ravel() for w in weights])
+        layer.Weights.storage[: flat_w.size].copy_(GPUTensor((flat_w.size,), flat_w, wrapper).storage)
+        if biases is not None:
+            flat_b = np.concatenate(biases)
+            layer.Bias.storage[: flat_b.size].copy_(GPUTensor((flat_b.size,), flat_b, wrapper).storage)
+        Qg, Kg, Vg = (GPUTensor(a.shape, a, wrapper) for a in (Q, K, V))
+        y = GPUTensor(Q.shape, None, wrapper)
+        layer.ForwardPropagation([Qg, Kg, Vg], y, True)
+        wrapper.check_device_status()
+        if keep is not None:
+            keep.update(layer=layer, X=[Qg, Kg, Vg])
+        return y.ContentAsFloatArray()
+    return run
+
+
+@pytest.mark.gpu
+def test_gpu_multihead_attention_matches_reference_goldens(wrapper, golden):
+    for case in golden["mha_tf"]["cases"]:
+        p = _mha_tf_network(golden, case, _gpu_mha(wrapper))
+        np.testing.assert_allclose(p.ravel(), case["pred_before"], rtol=0, atol=1e-6)
+    for name in ("no_bias", "with_bias"):
+        for case in golden["mha_pt_" + name]["cases"]:
+            assert abs(_mha_pt_loss(golden, name, case, _gpu_mha(wrapper)) - case["loss_before"]) <= 1e-6
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layout", [W_OUT_IN, W_IN_OUT])
+@pytest.mark.parametrize("shape,causal,bias", [((2, 3, 3, 2, 2), True, True), ((3, 7, 7, 3, 5), False, False),
+                                               ((4, 64, 64, 8, 32), True, True), ((2, 128, 128, 4, 64), False, True),
+                                               ((2, 48, 80, 4, 16), False, True)])
+def test_gpu_multihead_attention_forward_backward_against_oracle(wrapper, layout, shape, causal, bias):
+    from sharpnet_b200.tensor import GPUTensor
+    B, Tq, Tk, H, kd = shape
+    E = H * kd
+    Q, K, V, weights, biases, dy = _mha_random(B, Tq, Tk, H, kd, 11 + B + Tq, bias)
+    keep = {}
+    y = _gpu_mha(wrapper, keep)(Q, K, V, weights, biases, H, kd, kd, causal, layout)
+    y64, cache = orc.multihead_attention_forward(Q, K, V, weights, biases, H, kd, kd, causal, layout, f64=True)
+    # four chained products of O(1) values over K = E or T terms each: the 1e-5 * sqrt(K) bound, with head room
+    tol = 1e-5 * np.sqrt(max(E, Tk)) * 4 + 2e-5
+    assert np.abs(y - y64).max() <= tol
+    if B * Tq * E <= 40000:
+        ym = orc.multihead_attention_forward(Q, K, V, weights, biases, H, kd, kd, causal, layout)[0]
+        assert np.abs(y - ym).max() <= tol
+    layer = keep["layer"]
+    dX = [GPUTensor(a.shape, None, wrapper) for a in (Q, K, V)]
+    layer.BackwardPropagation(keep["X"], GPUTensor(dy.shape, dy, wrapper), dX, 1.0)
+    wrapper.check_device_status()
+    dQ, dK, dV, dws, dbs = orc.multihead_attention_backward(Q, K, V, dy, weights, cache, H, kd, kd, 1.0, layout)
+    gtol = 1e-5 * np.sqrt(max(E, Tk, B * max(Tq, Tk))) * 16 + 1e-4
+    for got, ref in zip(dX, (dQ, dK, dV)):
+        assert np.abs(got.ContentAsFloatArray() - ref).max() <= gtol
+    gws, gbs = layer.gradients()
+    for got, ref in zip(gws, dws):
+        assert np.abs(got.ContentAsFloatArray() - ref).max() <= gtol
+    if bias:
+        for got, ref in zip(gbs, dbs):
+            assert np.abs(got.ContentAsFloatArray() - ref).max() <= gtol
+
+
+@pytest.mark.gpu
+def test_gpu_transpose_second_and_third_dimension(wrapper):
+    from sharpnet_b200.tensor import GPUTensor
+    for shape in ((1, 1, 1, 1), (2, 3, 4, 5), (3, 7, 2, 8), (4, 16, 33, 64), (2, 5, 3), (6, 128, 8, 32), (3, 2, 1000, 3)):
+        x = orc.uniform(shape, -1, 1, sum(shape))
+        src = GPUTensor(shape, x, wrapper)
+        dst = GPUTensor(shape, None, wrapper)
+        src.TransposeSecondAndThirdDimension(dst)
+        assert dst.Shape == [shape[0], shape[2], shape[1]] + list(shape[3:])
+        np.testing.assert_array_equal(dst.ContentAsFloatArray(), orc.transpose_second_third(x))
+        back = GPUTensor(shape, None, wrapper)
+        dst.TransposeSecondAndThirdDimension(back)                    # the permutation is its own inverse
+        np.testing.assert_array_equal(back.ContentAsFloatArray(), x)
