@@ -520,8 +520,8 @@ def run_ours(args):
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak3, "unit": "TFLOP/s",
                          "frac": achieved / peak3,
                          # DRAM bytes per GEMM launch of this step from the ncu launch list (one-pass metrics on the
-                         # same command): 3.60 GB read + 0.57 GB written on average; algorithmic bytes 1.89 GB
-                         "traffic": 4.17e9 if world == 1 else None, "algorithmic_bytes_per_launch": 1.89e9,
+                         # same command): 3.65 GB read + 0.59 GB written on average; algorithmic bytes 1.89 GB
+                         "traffic": 4.24e9 if world == 1 else None, "algorithmic_bytes_per_launch": 1.89e9,
                          "kernel": "umma2_gemm_kernel (CTA-pair tcgen05 GEMM, 3xTF32), the 8 GEMM launches of the step",
                          "peak_source": f"{peaks['src']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32) / 3 "
                                         "(three TF32 products per fp32 product); flops counted once (2*M*N*K)",
