@@ -125,7 +125,9 @@ int snb200_batched_gemm(snb200_handle_t handle, int transA, int transB, int aH, 
                         const float* B, float beta, float* C);
 
 /* ---- Dense forward --------------------------------------------------------------------------
- * y = act(x * op(W) + bias), x [M x K], y [M x N], bias [N] or NULL, in ONE kernel.
+ * y = act(x * op(W) + bias), x [M x K], y [M x N], bias [N] or NULL: the bias, the activation and the
+ * optional pre-activation copy are applied where the product is stored (the GEMM epilogue, or the
+ * reduction pass when K is cut), never in a pass of their own.
  * Replaces Linear.DenseForwardPropagation (Prod/Layers/Linear.cs:125-132: Dot, then
  * BroadcastAddVectorToOutput -> cudnnAddTensor, Prod/GPU/GpuTensor.cs:633-644) followed by
  * ActivationLayer.ForwardPropagation (Prod/Layers/ActivationLayer.cs:32-38 ->
