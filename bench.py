@@ -229,6 +229,39 @@ def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi,
             "operand_sets": n_sets, "calls": calls}
 
 
+def sharded_gemm(w, torch, world, rank, barrier, max_over_ranks, calls=5):
+    """BASELINE config 5a on N GPUs: C = A * B with 16384^3 operands, A and C sharded by rows of M over the ranks, B
+    replicated; no collective on the data path.  Returns aggregate TFLOP/s = 2 * 16384^3 / (max over ranks of the
+    device time per call)."""
+    import ctypes
+    from sharpnet_b200 import MATH_3XTF32
+    n = 16384
+    rows = n // world
+    w.set_math_mode(MATH_3XTF32)
+    g = torch.Generator(device="cuda").manual_seed(13 + rank)
+    A = torch.empty(rows, n, device="cuda").uniform_(-1, 1, generator=g)
+    B = torch.empty(n, n, device="cuda").uniform_(-1, 1, generator=torch.Generator(device="cuda").manual_seed(13))
+    C = torch.empty(rows, n, device="cuda")
+    P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    call = lambda: w.lib.snb200_gemm(w.handle, 0, 0, rows, n, n, n, ctypes.c_float(1.0), P(A), P(B),  # noqa: E731
+                                     ctypes.c_float(0.0), P(C))
+    for _ in range(3):
+        if call() != 0:
+            raise RuntimeError(w.lib.snb200_last_error_string(w.handle))
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(calls):
+        call()
+    e1.record()
+    barrier()
+    w.check_device_status()
+    ms = max_over_ranks(e0.elapsed_time(e1) / calls)
+    return {"shape": f"cfg5a 16384^3 NN, rows of A and C sharded over {world} GPUs, B replicated, no collective",
+            "mode": "3xTF32", "kernel": w.last_kernel(), "ms": round(ms, 4), "calls": calls,
+            "tflops_aggregate": round(2.0 * n ** 3 / ms / 1e9, 2)}
+
+
 def companion_table(w, torch, peaks):
     """Achieved HBM GB/s of the bandwidth-bound kernels of the path on config-sized tensors
     (16384 x 4096 fp32 = 256 MiB per tensor, so every call streams more than the L2 holds)."""
@@ -424,6 +457,11 @@ def run_ours(args):
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
 
+    sharded = None
+    if world > 1 and not args.no_shapes:
+        sharded = sharded_gemm(w, torch, world, rank, barrier, max_over_ranks)
+        torch.cuda.empty_cache()
+
     step = lambda: training_step(stack, reducer, compute_stream)  # noqa: E731
     for _ in range(max(args.warmup, 3)):
         step()
@@ -543,6 +581,8 @@ def run_ours(args):
         if shapes is not None:
             line["shapes"] = shapes
             line["companions"] = companions
+        if sharded is not None:
+            line["sharded_gemm"] = sharded
         _emit(json.dumps(line))
     if reducer is not None:
         reducer.close()
