@@ -41,6 +41,15 @@ __device__ __forceinline__ float act_forward(int act, float v) {
   }
 }
 
+// For fully unrolled epilogues: Identity and Relu inline, the transcendental activations through one
+// out-of-line copy, so that the unrolled code stays small enough for the instruction cache.
+static __device__ __noinline__ float act_forward_call(int act, float v) { return act_forward(act, v); }
+__device__ __forceinline__ float act_forward_compact(int act, float v) {
+  if (act == ACT_IDENTITY) return v;
+  if (act == ACT_RELU) return fmaxf(v, 0.0f);
+  return act_forward_call(act, v);
+}
+
 // Gradient with respect to the pre-activation, from the upstream gradient dy, the activation
 // output y and (SWISH only) the pre-activation x.
 __device__ __forceinline__ float act_backward(int act, float dy, float x, float y) {

@@ -410,12 +410,20 @@ static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
   p.ldc = g.ldc;
   p.A = g.A; p.B = g.B; p.C = g.C; p.Z = g.Z; p.bias = g.bias;
   p.alpha = g.alpha; p.beta = g.beta; p.act = g.act;
-  p.tiles_m = (g.M + kSimtBM - 1) / kSimtBM;
-  p.tiles_n = (g.N + kSimtBN - 1) / kSimtBN;
+  // 128 x 128 tiles once they fill most of the SMs; 64 x 64 tiles for everything smaller
+  const long long big_tiles = static_cast<long long>((g.M + kSimtBigBM - 1) / kSimtBigBM) *
+                              ((g.N + kSimtBigBN - 1) / kSimtBigBN) * g.batch;
+  const bool big = big_tiles >= h->sm_count && g.K >= 64;
+  const int bm = big ? kSimtBigBM : kSimtBM, bn = big ? kSimtBigBN : kSimtBN;
+  p.tiles_m = (g.M + bm - 1) / bm;
+  p.tiles_n = (g.N + bn - 1) / bn;
   const long long blocks = static_cast<long long>(p.tiles_m) * p.tiles_n * g.batch;
   if (blocks > 0x7fffffffLL) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "too many tiles for one launch");
-  note_kernel(h, "simt_fp32_64x64", 1);
-  simt_gemm_kernel<<<static_cast<unsigned>(blocks), kSimtThreads, 0, h->stream>>>(p);
+  note_kernel(h, big ? "simt_fp32_128x128" : "simt_fp32_64x64", 1);
+  if (big)
+    simt_gemm_big_kernel<<<static_cast<unsigned>(blocks), kSimtThreads, 0, h->stream>>>(p);
+  else
+    simt_gemm_kernel<<<static_cast<unsigned>(blocks), kSimtThreads, 0, h->stream>>>(p);
   return check_launch(h, "simt_gemm_kernel launch");
 }
 
