@@ -281,6 +281,9 @@ def companion_table(w, torch, peaks):
         ("axpy", 12 * n, lambda: lib.snb200_axpy(h, n, f(0.5), P(t[0]), P(t[4]))),
         ("sgd_update momentum", 20 * n, lambda: lib.snb200_sgd_update(h, n, f(1e-3), f(0.9), 0, P(t[0]), P(t[4]), P(t[5]))),
         ("adam_update", 28 * n, lambda: lib.snb200_adam_update(h, n, 1e-3, 0.9, 0.999, 1e-8, 0.0, 5, P(t[0]), P(t[4]), P(t[5]), P(t[3]))),
+        # head split of 128 sequences x 512 steps x 16 heads x 64: [128, 512, 16, 64] -> [128, 16, 512, 64]
+        ("transpose_second_third 128x512x16x64", 8 * n, lambda: lib.snb200_transpose_second_third(h, 128, 512, 16, 64, P(t[0]), P(t[1]))),
+        ("softmax_fwd 524288x128", 8 * n, lambda: lib.snb200_softmax_fwd(h, n // 128, 128, P(t[0]), P(t[1]))),
     ]
     out = []
     for name, byts, call in cases:
@@ -356,6 +359,32 @@ def dense_and_attention_table(w, torch, peaks):
     timed("attention bwd 256 x [128x64]", 8.0 * B * T * T * E, 4.0 * (7 * B * T * E + B * T * T), asets,
           lambda d: lib.snb200_sdpa_bwd(h, B, T, T, E, 1, P(d["Q"]), P(d["K"]), P(d["V"]), P(d["dy"]), P(d["w"]),
                                         P(d["ds"]), P(d["dQ"]), P(d["dK"]), P(d["dV"])))
+    # multi-head attention layer (Prod/Layers/MultiheadAttention.cs): 32 sequences x 128 steps, embed 512 = 8 heads x 64,
+    # through the layer mirror (4 Dense projections, head split / merge permutations, attention core)
+    from sharpnet_b200.attention import MultiheadAttention
+    from sharpnet_b200.tensor import GPUTensor
+    Bm, Tm, Em, Hm = 32, 128, 512, 8
+    layer = MultiheadAttention(Hm, Em // Hm, Em // Hm, True, True, True, Em, w)
+    layer.Weights.storage.uniform_(-0.05, 0.05)
+    xs = [GPUTensor((Bm, Tm, Em), None, w) for _ in range(3)]
+    for t in xs:
+        t.storage.normal_()
+    ym, dym = GPUTensor((Bm, Tm, Em), None, w), GPUTensor((Bm, Tm, Em), None, w)
+    dym.storage.normal_()
+    dxs = [GPUTensor((Bm, Tm, Em), None, w) for _ in range(3)]
+    proj = 2.0 * Bm * Tm * Em * Em * 4
+    core = 4.0 * Bm * Hm * Tm * Tm * (Em // Hm)
+    launches0 = w.launch_count()
+    layer.ForwardPropagation(xs, ym, True)
+    n_fwd = w.launch_count() - launches0
+    timed(f"multi-head attention fwd 32 x 128 x 512, 8 heads, causal ({n_fwd} launches; host side in Python)",
+          proj + core, 4.0 * (4 * Bm * Tm * Em + 4 * Em * Em), [None], lambda d: layer.ForwardPropagation(xs, ym, True))
+
+    def fwd_bwd(d):
+        layer.ForwardPropagation(xs, ym, True)
+        layer.BackwardPropagation(xs, dym, dxs)
+    timed("multi-head attention fwd + bwd 32 x 128 x 512, 8 heads, causal", 3.0 * (proj + core),
+          4.0 * (8 * Bm * Tm * Em + 8 * Em * Em), [None], fwd_bwd)
     return out
 
 

@@ -28,7 +28,13 @@ struct GemmProblem {
   const float* bias;      // [N] or nullptr: added to every row
   float* Z;               // optional copy of the value before the activation (pitch ldc, stride strideC)
   int act;                // Act
+  // Row operation applied to alpha * op(A) * op(B) before it is stored, for products whose whole row lies in one
+  // tile (N <= 128): the two softmax passes of scaled dot-product attention.
+  int row_op;             // RowOp
+  int causal;             // ROW_SOFTMAX: columns above the main diagonal of every matrix count as -1e12
+  const float* aux;       // ROW_SOFTMAX_GRAD: the softmax output y, laid out like C
 };
+enum RowOp : int { ROW_NONE = 0, ROW_SOFTMAX = 1, ROW_SOFTMAX_GRAD = 2 };
 
 __device__ __forceinline__ float act_forward(int act, float v) {
   // Formulas of Prod/CPU/CpuTensorActivationFunctions.cs:152-244 and Prod/Utils.cs:888-891.

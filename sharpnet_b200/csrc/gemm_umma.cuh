@@ -98,6 +98,10 @@ struct UmmaParams {
   int partial_tiled;
   float* partial;
   long long partial_stride;
+  // row operation on alpha * acc before the store (single-CTA kernel, one tile column, BN <= 128): see RowOp
+  int row_op;
+  int causal;
+  const float* aux;
 };
 
 // Work unit u of a launch over n_tiles output tiles: which tile, which K range, and (split >= 0) which
@@ -238,6 +242,85 @@ __device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const f
   }
 }
 
+// Coalesced read of a 32 x 32 block of a row-major matrix (rows 16-byte aligned) through the warp's shared-memory
+// tile, the mirror image of the store phase: afterwards lane l holds row l of the block in `out`.  Rows at or
+// beyond `rows_valid` and columns at or beyond `cols_valid` read as 0.
+__device__ __forceinline__ void epilogue_load_block(const float* src, int ld, int rows_valid, int cols_valid, float* stage,
+                                                    int lane, float (&out)[32]) {
+  const int c4 = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + (lane >> 3);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < rows_valid && 4 * c4 < cols_valid) v = *reinterpret_cast<const float4*>(src + static_cast<long long>(r) * ld + 4 * c4);
+    *reinterpret_cast<float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2)) = v;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    const float4 v = *reinterpret_cast<const float4*>(stage + lane * 32 + ((j4 ^ (lane & 7)) << 2));
+    out[4 * j4] = v.x; out[4 * j4 + 1] = v.y; out[4 * j4 + 2] = v.z; out[4 * j4 + 3] = v.w;
+  }
+  __syncwarp();
+}
+
+// Row operation of the attention products, on the NC = BN <= 128 columns of the output row this lane holds
+// (the whole row: the launcher guarantees one tile column and N a multiple of 4 with 16-byte aligned rows).
+// On return acc holds the values to store as they are.
+//   ROW_SOFTMAX       acc = softmax(mask(alpha * acc)) over the N valid columns: the causal overwrite with -1e12
+//                     (Prod/CPU/CpuTensor.cs:3037-3052) and CpuTensorActivationFunctions.Softmax (:19-46).
+//                     One thread owns a whole row here, so the exponential is the hardware's ex2 (relative error
+//                     2^-22) and the division a multiplication by the reciprocal of the row sum.
+//   ROW_SOFTMAX_GRAD  acc = y * (g - sum_j g_j * y_j) with g = alpha * acc, y = aux row: the softmax Jacobian
+//                     cudnnSoftmaxBackward applies (Prod/GPU/GpuTensor.cs:445-490)
+template <int NC>
+__device__ __forceinline__ void epilogue_row_op(const UmmaParams& p, float (&acc)[NC], float* stage, int b, int row_base,
+                                                int lane) {
+  const int ncols = p.N < NC ? p.N : NC;
+  const int row = row_base + lane;
+  if (p.row_op == ROW_SOFTMAX) {
+    const int limit = p.causal ? row : 0x7fffffff;   // columns > limit are masked
+    float mx = -3.402823466e38f;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      float v = p.alpha * acc[j];
+      v = (j > limit) ? -1e12f : v;
+      v = (j < ncols) ? v : -3.402823466e38f;
+      acc[j] = v;
+      mx = fmaxf(mx, v);
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      acc[j] = (j < ncols) ? __expf(acc[j] - mx) : 0.0f;
+      sum += acc[j];
+    }
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) acc[j] *= inv;
+  } else {
+    const float* yb = p.aux + static_cast<long long>(b) * p.strideC + static_cast<long long>(row_base) * p.ldc;
+    const int rows_valid = p.M - row_base;
+    float dot = 0.0f;
+#pragma unroll
+    for (int g = 0; g < NC / 32; ++g) {
+      if (g * 32 >= ncols) break;   // warp-uniform
+      float y[32];
+      epilogue_load_block(yb + g * 32, p.ldc, rows_valid, ncols - g * 32, stage, lane, y);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) dot = fmaf(p.alpha * acc[g * 32 + j], y[j], dot);
+    }
+#pragma unroll
+    for (int g = 0; g < NC / 32; ++g) {
+      if (g * 32 >= ncols) break;
+      float y[32];
+      epilogue_load_block(yb + g * 32, p.ldc, rows_valid, ncols - g * 32, stage, lane, y);   // second read: L1 / L2
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[g * 32 + j] = y[j] * (p.alpha * acc[g * 32 + j] - dot);
+    }
+  }
+}
+
 // Final store of one work unit: the fused epilogue into C, or (split >= 0) the raw partial sums into
 // the workspace.  `tile_row0`/`tile_col0` are the first row and column of the unit's whole tile,
 // `tile_elems` the size of that tile in the tiled workspace layout (rows x BN), `bn` its row pitch there.
@@ -296,7 +379,9 @@ __device__ __forceinline__ void split_stage(uint8_t* raw, int tid, int rewrite_h
 // `chunk_kblocks` k-blocks in TMEM; the epilogue warps add every such partial sum into fp32
 // registers (round-to-nearest), alternating between the two TMEM buffers so that the tensor core
 // never waits for them.
-template <class T>
+// ROWOP instantiates the epilogue with the row operations of attention (epilogue_row_op); the plain
+// instantiation carries none of their code or registers.
+template <class T, bool ROWOP = false>
 __global__ void __launch_bounds__(T::THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const UmmaParams p) {
@@ -469,8 +554,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) break;
       float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
-      epilogue_store_unit<NC>(p, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN, BN, tm * BM + q * 32,
-                              tn * BN + col_base, lane);
+      if (ROWOP && T::EPI_GROUPS == 1 && p.row_op != ROW_NONE) {
+        epilogue_row_op<NC>(p, acc, stage, b, tm * BM + q * 32, lane);
+        UmmaParams pp = p;
+        pp.alpha = 1.0f;          // the row operation has consumed alpha
+        epilogue_store_unit<NC>(pp, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN, BN, tm * BM + q * 32,
+                                tn * BN + col_base, lane);
+      } else {
+        epilogue_store_unit<NC>(p, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN, BN, tm * BM + q * 32,
+                                tn * BN + col_base, lane);
+      }
     }
   } else if (T::SPLIT) {
     // ------------------------------------------------------------------ hi / lo split

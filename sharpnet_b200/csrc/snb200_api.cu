@@ -246,6 +246,7 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
   p.error_word = h->error_word;
   p.splits = 1;
   p.kb_per_split = p.k_blocks;
+  p.row_op = g.row_op; p.causal = g.causal; p.aux = g.aux;
   p.whole_tiles = 0;       // set by the launcher: it knows the tile grid of its kernel
   p.partial_tiled = 0;
   p.partial = nullptr;
@@ -289,7 +290,7 @@ static void apply_split_plan(snb200_handle_t h, const GemmProblem& g, int tile_r
   plan.tail = static_cast<int>(n_tiles) - p.whole_tiles;
 }
 
-template <class T>
+template <class T, bool ROWOP = false>
 static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& plan) {
   static bool configured[64] = {};
   CUtensorMap tmA, tmB;
@@ -300,12 +301,13 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pla
   apply_split_plan<T>(h, g, T::BM, n_tiles, p, plan);
   plan.tiles_m = p.tiles_m;
   if (!configured[h->device]) {
-    SNB_CUDA(h, cudaFuncSetAttribute(umma_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    SNB_CUDA(h, cudaFuncSetAttribute(umma_gemm_kernel<T, ROWOP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     T::SMEM_BYTES));
     configured[h->device] = true;
   }
   const long long units = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;
   const int grid = static_cast<int>(units < h->sm_count ? units : h->sm_count);
-  umma_gemm_kernel<T><<<grid, T::THREADS, T::SMEM_BYTES, h->stream>>>(tmA, tmB, p);
+  umma_gemm_kernel<T, ROWOP><<<grid, T::THREADS, T::SMEM_BYTES, h->stream>>>(tmA, tmB, p);
   return check_launch(h, "umma_gemm_kernel launch");
 }
 
@@ -592,6 +594,23 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
   }
   if (!use_umma) return launch_simt(h, g);
   const bool split = h->math_mode == SNB200_MATH_3XTF32;
+  if (g.row_op != ROW_NONE) {
+    // whole rows in one tile of the single-CTA kernel, K never cut (the caller checked row_op_fits)
+    SplitPlan none = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int bn = g.N <= 32 ? 32 : g.N <= 64 ? 64 : 128;
+    char name[64];
+    snprintf(name, sizeof(name), "umma_%s_128x%d_%s", split ? "3xtf32" : "tf32", bn,
+             g.row_op == ROW_SOFTMAX ? "softmax" : "softmax_grad");
+    note_kernel(h, name, 1);
+    if (split) {
+      if (bn == 32) return launch_umma_t<UmmaTile<32, 32, true>, true>(h, g, none);
+      if (bn == 64) return launch_umma_t<UmmaTile<64, 32, true>, true>(h, g, none);
+      return launch_umma_t<UmmaTile<128, 32, true>, true>(h, g, none);
+    }
+    if (bn == 32) return launch_umma_t<UmmaTile<32, 32, false>, true>(h, g, none);
+    if (bn == 64) return launch_umma_t<UmmaTile<64, 32, false>, true>(h, g, none);
+    return launch_umma_t<UmmaTile<128, 32, false>, true>(h, g, none);
+  }
   const int splitk_mode = h->tune[TUNE_SPLITK];   // 0 automatic, 1 never
   // Few rows (M <= 64): run the transposed problem C^T = op(B)^T * op(A)^T, so that the long N dimension
   // fills the 128 rows of the tensor-core tile and the short M dimension becomes a narrow tile width.
@@ -1034,6 +1053,17 @@ static void bmm_problem(GemmProblem* g, int batch, int M, int N, int K, int tA, 
   g->batch = batch; g->alpha = alpha; g->beta = 0.0f; g->act = ACT_IDENTITY;
 }
 
+// Can the product run on the tensor-core kernel with its whole rows in one tile, so that a row operation
+// (softmax, softmax gradient) can be applied where the product is stored?  Otherwise the caller runs the plain
+// product and a separate row pass.
+static bool row_op_fits(const snb200_context* h, const GemmProblem& g) {
+  if (h->math_mode == SNB200_MATH_FP32_SIMT || h->tune[TUNE_FORCE_PATH] == 2 || !tma_eligible(g)) return false;
+  if (g.N > 128 || g.N < 8 || g.M < 16) return false;
+  // the row operation reads and writes whole float4s of 16-byte aligned rows
+  if ((g.N & 3) || !aligned16(g.C) || (g.aux && !aligned16(g.aux)) || (g.batch > 1 && (g.strideC & 3))) return false;
+  return static_cast<double>(g.M) * g.N * g.K * g.batch >= 64.0 * 64 * 64;
+}
+
 extern "C" int snb200_sdpa_fwd(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim,
                                int use_scale, int is_causal, const float* Q, const float* K, const float* V,
                                float* weights, float* y) {
@@ -1051,11 +1081,18 @@ extern "C" int snb200_sdpa_fwd(snb200_handle_t h, int batch, int q_steps, int v_
   // scores = scaling * Q * K^T                       (ScaledDotProductAttentionLayer.cs:66-71)
   bmm_problem(&g, batch, Tq, Tk, E, 0, 1, Q, E, static_cast<long long>(Tq) * E, K, E, static_cast<long long>(Tk) * E,
               weights, scaling);
-  st = run_gemm(h, g);
-  if (st) return st;
-  // causal mask + softmax over the last dimension, in place   (:73-81)
-  st = launch_softmax_fwd(h, static_cast<long long>(batch) * Tq, Tk, is_causal ? Tq : 0, weights, weights);
-  if (st) return st;
+  if (row_op_fits(h, g)) {
+    // causal mask + softmax over the last dimension where the scores are stored   (:73-81)
+    g.row_op = ROW_SOFTMAX; g.causal = is_causal ? 1 : 0;
+    st = run_gemm(h, g);
+    if (st) return st;
+  } else {
+    st = run_gemm(h, g);
+    if (st) return st;
+    // causal mask + softmax over the last dimension, in place   (:73-81)
+    st = launch_softmax_fwd(h, static_cast<long long>(batch) * Tq, Tk, is_causal ? Tq : 0, weights, weights);
+    if (st) return st;
+  }
   // y = weights * V                                   (:85)
   bmm_problem(&g, batch, Tq, E, Tk, 0, 0, weights, Tk, static_cast<long long>(Tq) * Tk, V, E,
               static_cast<long long>(Tk) * E, y, 1.0f);
@@ -1085,11 +1122,19 @@ extern "C" int snb200_sdpa_bwd(snb200_handle_t h, int batch, int q_steps, int v_
   if (st) return st;
   // gradient w.r.t. the weights, scaled: scaling * dy * V^T    (:119)
   bmm_problem(&g, batch, Tq, Tk, E, 0, 1, dy, E, sQ, V, E, sK, scores_grad_scratch, scaling);
-  st = run_gemm(h, g);
-  if (st) return st;
-  // ... turned into the gradient w.r.t. the scores by the softmax Jacobian, in place    (:121)
-  st = launch_softmax_bwd(h, static_cast<long long>(batch) * Tq, Tk, scores_grad_scratch, weights, scores_grad_scratch);
-  if (st) return st;
+  g.aux = weights;
+  if (row_op_fits(h, g)) {
+    // ... turned into the gradient w.r.t. the scores by the softmax Jacobian where it is stored    (:121)
+    g.row_op = ROW_SOFTMAX_GRAD;
+    st = run_gemm(h, g);
+    if (st) return st;
+  } else {
+    st = run_gemm(h, g);
+    if (st) return st;
+    // ... turned into the gradient w.r.t. the scores by the softmax Jacobian, in place    (:121)
+    st = launch_softmax_bwd(h, static_cast<long long>(batch) * Tq, Tk, scores_grad_scratch, weights, scores_grad_scratch);
+    if (st) return st;
+  }
   // dQ = dScores * K ; dK = dScores^T * Q             (:123-124)
   bmm_problem(&g, batch, Tq, E, Tk, 0, 0, scores_grad_scratch, Tk, sW, K, E, sK, dQ, 1.0f);
   st = run_gemm(h, g);
