@@ -102,7 +102,10 @@ int snb200_gemm_timing_end(snb200_handle_t handle, double* total_ms, int* gemm_c
  * key 0: path (0 automatic, 1 tensor cores whenever the operands allow TMA, 2 SIMT fp32);
  * key 1: tile width of the tensor-core kernel (0 automatic, else 32, 64, 128 or 256);
  * key 2: 3xTF32 writes the rounded hi plane back to shared memory (1) or lets the
- *        tensor core truncate the raw fp32 words itself (0, default). */
+ *        tensor core truncate the raw fp32 words itself (0, default);
+ * key 7: 1 launches the tensor-core kernels without programmatic dependent launch (by default their set-up
+ *        overlaps the tail of the previous kernel in the stream; they wait for its completion before touching
+ *        global memory). */
 int snb200_set_tuning(snb200_handle_t handle, int key, int value);
 
 /* ---- Tensor.Dot -----------------------------------------------------------------------------

@@ -423,6 +423,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_holder;
   volatile int* abortp = &abort_flag;
+  // Everything above touched only this CTA's shared memory, TMEM and kernel parameters, so it may overlap the
+  // tail of the previous kernel in the stream; everything below reads or writes global memory.
+  allow_dependent_launch();
+  grid_dependency_wait();
 
   const int n_tiles = p.batch * p.tiles_m * p.tiles_n;
   const int total_tiles = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;   // work units

@@ -106,6 +106,8 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_holder;
   volatile int* abortp = &abort_flag;
+  allow_dependent_launch();   // set-up done without touching global memory: see umma_gemm_kernel
+  grid_dependency_wait();
 
   const int pair_tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
   const int n_tiles = p.batch * pair_tiles_m * p.tiles_n;

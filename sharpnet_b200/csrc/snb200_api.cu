@@ -18,7 +18,7 @@
 using namespace snb;
 
 // ------------------------------------------------------------------------------------ handle
-enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_COUNT = 8 };
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_COUNT = 8 };
 
 struct snb200_context {
   int device;
@@ -307,7 +307,21 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pla
   }
   const long long units = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;
   const int grid = static_cast<int>(units < h->sm_count ? units : h->sm_count);
-  umma_gemm_kernel<T, ROWOP><<<grid, T::THREADS, T::SMEM_BYTES, h->stream>>>(tmA, tmB, p);
+  // launched so that its set-up may overlap the tail of the previous kernel in the stream; the kernel waits for
+  // that kernel's completion before it touches global memory
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(T::THREADS);
+  cfg.dynamicSmemBytes = T::SMEM_BYTES;
+  cfg.stream = h->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = h->tune[TUNE_PDL] == 1 ? 0 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T, ROWOP>, tmA, tmB, p);
+  if (e != cudaSuccess) return cuda_fail(h, e, "umma_gemm_kernel launch");
   return check_launch(h, "umma_gemm_kernel launch");
 }
 
@@ -321,14 +335,16 @@ static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pl
   if (st) return st;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see launch_umma_t
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(T::THREADS);
   cfg.dynamicSmemBytes = T::SMEM_BYTES;
   cfg.stream = h->stream;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = h->tune[TUNE_PDL] == 1 ? 1 : 2;
   if (!configured[h->device]) {
     SNB_CUDA(h, cudaFuncSetAttribute(umma2_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     cfg.gridDim = dim3(h->sm_count & ~1);
