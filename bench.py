@@ -360,31 +360,39 @@ def dense_and_attention_table(w, torch, peaks):
           lambda d: lib.snb200_sdpa_bwd(h, B, T, T, E, 1, P(d["Q"]), P(d["K"]), P(d["V"]), P(d["dy"]), P(d["w"]),
                                         P(d["ds"]), P(d["dQ"]), P(d["dK"]), P(d["dV"])))
     # multi-head attention layer (Prod/Layers/MultiheadAttention.cs): 32 sequences x 128 steps, embed 512 = 8 heads x 64,
-    # through the layer mirror (4 Dense projections, head split / merge permutations, attention core)
-    from sharpnet_b200.attention import MultiheadAttention
-    from sharpnet_b200.tensor import GPUTensor
+    # one snb200_mha_fwd / snb200_mha_bwd call each (4 Dense projections, head split / merge permutations, attention
+    # core); every buffer allocated once, as the layer's memory pool does
+    from sharpnet_b200 import _capi
     Bm, Tm, Em, Hm = 32, 128, 512, 8
-    layer = MultiheadAttention(Hm, Em // Hm, Em // Hm, True, True, True, Em, w)
-    layer.Weights.storage.uniform_(-0.05, 0.05)
-    xs = [GPUTensor((Bm, Tm, Em), None, w) for _ in range(3)]
-    for t in xs:
-        t.storage.normal_()
-    ym, dym = GPUTensor((Bm, Tm, Em), None, w), GPUTensor((Bm, Tm, Em), None, w)
-    dym.storage.normal_()
-    dxs = [GPUTensor((Bm, Tm, Em), None, w) for _ in range(3)]
+    dm = Em // Hm
+    desc = _capi.MhaDesc(0, Bm, Tm, Tm, Em, Hm, dm, dm, 1)
+    wts = [new(Em, Em).uniform_(-0.05, 0.05) for _ in range(4)] + [new(Em).uniform_(-0.1, 0.1) for _ in range(4)]
+    grads = [new(Em, Em) for _ in range(4)] + [new(Em) for _ in range(4)]
+    xs = [new(Bm, Tm, Em).normal_() for _ in range(3)]
+    dxs = [new(Bm, Tm, Em) for _ in range(3)]
+    ym, dym = new(Bm, Tm, Em), new(Bm, Tm, Em).normal_()
+    state = [new(Bm * Hm, Tm, dm), new(Bm * Hm, Tm, dm), new(Bm * Hm, Tm, dm), new(Bm, Tm, Em), new(Bm * Hm, Tm, Tm)]
+    scr = new(lib.snb200_mha_scratch_floats(desc, 1))
+    W_, S_, G_ = (_capi.MhaWeights(*[P(t) for t in wts]), _capi.MhaState(*[P(t) for t in state]),
+                  _capi.MhaWeights(*[P(t) for t in grads]))
     proj = 2.0 * Bm * Tm * Em * Em * 4
-    core = 4.0 * Bm * Hm * Tm * Tm * (Em // Hm)
-    launches0 = w.launch_count()
-    layer.ForwardPropagation(xs, ym, True)
-    n_fwd = w.launch_count() - launches0
-    timed(f"multi-head attention fwd 32 x 128 x 512, 8 heads, causal ({n_fwd} launches; host side in Python)",
-          proj + core, 4.0 * (4 * Bm * Tm * Em + 4 * Em * Em), [None], lambda d: layer.ForwardPropagation(xs, ym, True))
+    core = 4.0 * Bm * Hm * Tm * Tm * dm
 
-    def fwd_bwd(d):
-        layer.ForwardPropagation(xs, ym, True)
-        layer.BackwardPropagation(xs, dym, dxs)
-    timed("multi-head attention fwd + bwd 32 x 128 x 512, 8 heads, causal", 3.0 * (proj + core),
-          4.0 * (8 * Bm * Tm * Em + 8 * Em * Em), [None], fwd_bwd)
+    def mha_fwd(_):
+        return lib.snb200_mha_fwd(h, desc, W_, P(xs[0]), P(xs[1]), P(xs[2]), S_, P(scr), P(ym))
+
+    def mha_fwd_bwd(_):
+        mha_fwd(_)
+        return lib.snb200_mha_bwd(h, desc, W_, P(xs[0]), P(xs[1]), P(xs[2]), P(dym), S_, ctypes.c_float(1.0), P(scr), G_,
+                                  P(dxs[0]), P(dxs[1]), P(dxs[2]))
+    launches0 = w.launch_count()
+    if mha_fwd_bwd(None) != 0:
+        raise RuntimeError(lib.snb200_last_error_string(h))
+    n_launch = w.launch_count() - launches0
+    timed("multi-head attention fwd 32 x 128 x 512, 8 heads, causal (snb200_mha_fwd)", proj + core,
+          4.0 * (4 * Bm * Tm * Em + 4 * Em * Em), [None], mha_fwd)
+    timed(f"multi-head attention fwd + bwd 32 x 128 x 512, 8 heads, causal ({n_launch} kernels)", 3.0 * (proj + core),
+          4.0 * (8 * Bm * Tm * Em + 8 * Em * Em), [None], mha_fwd_bwd)
     return out
 
 

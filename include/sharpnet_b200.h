@@ -233,6 +233,48 @@ int snb200_sdpa_bwd(snb200_handle_t handle, int batch, int q_steps, int v_steps,
                     const float* Q, const float* K, const float* V, const float* dy, const float* weights,
                     float* scores_grad_scratch, float* dQ, float* dK, float* dV);
 
+/* ---- multi-head attention ------------------------------------------------------------------------
+ * MultiheadAttention.ForwardPropagation / BackwardPropagation (Prod/Layers/MultiheadAttention.cs:178-295) as one
+ * call each: the Dense projections of Q, K, V on the last dimension (Linear.DenseForwardPropagation), the head
+ * split [b, t, h, d] -> [b, h, t, d] (TransposeSecondAndThirdDimension), scaled dot-product attention per head
+ * (use_scale is always on, :32), the head merge and the output projection; the backward pass in the reverse order.
+ * The kernels of one call are queued back to back on the handle's stream, nothing is allocated.
+ *   Q [batch, q_steps, embed_dim]; K, V [batch, v_steps, embed_dim]; y [batch, q_steps, embed_dim];
+ *   embed_dim must equal num_heads * value_dim (the layer uses out_proj_weight that way, :121-126,236).
+ * Weights are [out, in] rows (w_layout 0, Linear.cs:125-132) or [in, out] (w_layout 1); biases may be NULL.
+ * snb200_mha_state holds what the layer keeps between the two passes (Q_heads_T, K_heads_T, V_heads_T,
+ * attention_heads_T, weights_buffer; :73-77), caller-provided:
+ *   Q_heads_T [batch*num_heads, q_steps, key_dim], K_heads_T [batch*num_heads, v_steps, key_dim],
+ *   V_heads_T [batch*num_heads, v_steps, value_dim], attention_heads_T [batch, q_steps, num_heads*value_dim],
+ *   weights_buffer [batch*num_heads, q_steps, v_steps].
+ * `scratch` is caller-provided device memory of at least snb200_mha_scratch_floats(desc, backward) floats
+ * (the layer's Q_K_V_heads_buffer, resp. dQ_dK_dV_heads_buffer, d_attention_heads, d*_heads_T and the gradient
+ * of the scores), 256-byte aligned. */
+typedef struct snb200_mha_desc {
+  int w_layout, batch, q_steps, v_steps, embed_dim, num_heads, key_dim, value_dim, is_causal;
+} snb200_mha_desc;
+typedef struct snb200_mha_weights {
+  const float *w_Q, *w_K, *w_V, *out_proj_weight;
+  const float *w_Q_bias, *w_K_bias, *w_V_bias, *out_proj_bias;
+} snb200_mha_weights;
+typedef struct snb200_mha_state {
+  float *Q_heads_T, *K_heads_T, *V_heads_T, *attention_heads_T, *weights_buffer;
+} snb200_mha_state;
+typedef struct snb200_mha_gradients {
+  float *w_Q, *w_K, *w_V, *out_proj_weight;
+  float *w_Q_bias, *w_K_bias, *w_V_bias, *out_proj_bias;      /* NULL where the layer has no bias */
+} snb200_mha_gradients;
+long long snb200_mha_scratch_floats(const snb200_mha_desc* desc, int backward);
+int snb200_mha_fwd(snb200_handle_t handle, const snb200_mha_desc* desc, const snb200_mha_weights* weights,
+                   const float* Q, const float* K, const float* V, const snb200_mha_state* state, float* scratch,
+                   float* y);
+/* dW_multiplier is the factor of the weight gradients (Linear.cs:152-158). */
+int snb200_mha_bwd(snb200_handle_t handle, const snb200_mha_desc* desc, const snb200_mha_weights* weights,
+                   const float* Q, const float* K, const float* V, const float* dy, const snb200_mha_state* state,
+                   float dW_multiplier, float* scratch, const snb200_mha_gradients* gradients, float* dQ, float* dK,
+                   float* dV);
+
+
 /* dst[a, c, b, :] = src[a, b, c, :] for a dense src of shape [A, B, C, D] (D = product of the trailing
  * dimensions): Tensor.TransposeSecondAndThirdDimension (Prod/Data/Tensor.cs, GPU Prod/GPU/GpuTensor.cs:672-684,
  * CPU Prod/CPU/CpuTensor.cs:301-322), the head split and merge of MultiheadAttention

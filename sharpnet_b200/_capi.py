@@ -26,6 +26,22 @@ _I = _c.c_int
 _L = _c.c_longlong
 _P = _c.c_void_p
 
+
+
+class MhaDesc(_c.Structure):        # snb200_mha_desc
+    _fields_ = [(n, _I) for n in ("w_layout", "batch", "q_steps", "v_steps", "embed_dim", "num_heads", "key_dim",
+                                  "value_dim", "is_causal")]
+
+
+class MhaWeights(_c.Structure):     # snb200_mha_weights and snb200_mha_gradients (same field order)
+    _fields_ = [(n, _P) for n in ("w_Q", "w_K", "w_V", "out_proj_weight", "w_Q_bias", "w_K_bias", "w_V_bias",
+                                  "out_proj_bias")]
+
+
+class MhaState(_c.Structure):       # snb200_mha_state
+    _fields_ = [(n, _P) for n in ("Q_heads_T", "K_heads_T", "V_heads_T", "attention_heads_T", "weights_buffer")]
+
+
 # name -> (restype, argtypes); every symbol include/sharpnet_b200.h declares.
 SIGNATURES = {
     "snb200_create": (_I, [_c.POINTER(_H), _I]),
@@ -58,6 +74,10 @@ SIGNATURES = {
     "snb200_sdpa_fwd": (_I, [_H, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "snb200_sdpa_bwd": (_I, [_H, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "snb200_transpose_second_third": (_I, [_H, _I, _I, _I, _I, _P, _P]),
+    "snb200_mha_scratch_floats": (_L, [_c.POINTER(MhaDesc), _I]),
+    "snb200_mha_fwd": (_I, [_H, _c.POINTER(MhaDesc), _c.POINTER(MhaWeights), _P, _P, _P, _c.POINTER(MhaState), _P, _P]),
+    "snb200_mha_bwd": (_I, [_H, _c.POINTER(MhaDesc), _c.POINTER(MhaWeights), _P, _P, _P, _P, _c.POINTER(MhaState), _F, _P,
+                           _c.POINTER(MhaWeights), _P, _P, _P]),
     "snb200_sgd_update": (_I, [_H, _L, _F, _F, _I, _P, _P, _P]),
     "snb200_adam_update": (_I, [_H, _L, _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_double, _I, _P, _P, _P, _P]),
     "snb200_comm_get_unique_id": (_I, [_P]),

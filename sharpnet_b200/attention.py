@@ -3,10 +3,11 @@
 ``ScaledDotProductAttention*Propagation`` (Prod/Layers/ScaledDotProductAttentionLayer.cs): same static-method
 names and argument meaning; each direction is one ``snb200_sdpa_*`` call (strided-batched GEMMs + one fused
 mask/softmax pass).  ``MultiheadAttention`` (Prod/Layers/MultiheadAttention.cs): the four Dense projections,
-the head split / merge permutations and the attention core, in the reference's call order."""
+the head split / merge permutations and the attention core, in the reference's call order, behind one
+``snb200_mha_fwd`` / ``snb200_mha_bwd`` call each."""
 
-from ._capi import ACT_IDENTITY, W_OUT_IN, check
-from .linear import FusedDenseBackward, FusedDenseForward
+from . import _capi
+from ._capi import W_OUT_IN, check
 from .tensor import GPUTensor
 
 
@@ -96,18 +97,17 @@ class MultiheadAttention:
         return ([self._w(self.WeightGradients, i) for i in range(4)],
                 [self._b(self.BiasGradients, i) for i in range(4)])
 
-    def _split_heads(self, x, W, b, d, scratch):
-        """Dense projection on the last dimension, then [b, t, h, d] -> [b * h, t, d]."""
-        B, T = x.Shape[0], x.Shape[1]
-        H = self.num_heads
-        flat = scratch.Slice(0, (B * T, H * d))
-        FusedDenseForward(flat, x, W, b, ACT_IDENTITY, None, self.layout, flattenInputTensorOnLastDimension=True)
-        heads = GPUTensor((B, H, T, d), None, self.w)
-        flat.Reshape(B, T, H, d).TransposeSecondAndThirdDimension(heads)
-        return heads.Reshape(B * H, T, d)
+    def _desc(self, B, Tq, Tk):
+        return _capi.MhaDesc(self.layout, B, Tq, Tk, self.embed_dim, self.num_heads, self.key_dim, self.value_dim,
+                             int(self.is_causal))
+
+    @staticmethod
+    def _ptrs(struct, tensors):
+        return struct(*[None if t is None else t.Pointer for t in tensors])
 
     def ForwardPropagation(self, allX, y, isTraining=True):
-        """(Prod/Layers/MultiheadAttention.cs:178-238)"""
+        """One ``snb200_mha_fwd`` call: projections, head split, attention, head merge, output projection
+        (Prod/Layers/MultiheadAttention.cs:178-238)."""
         Q, K, V = allX
         if V.Shape != K.Shape:
             raise ValueError(f"V.Shape and K.Shape must be equal, but are {V.Shape} and {K.Shape}")
@@ -118,40 +118,31 @@ class MultiheadAttention:
         if y.Shape != [B, Tq, E]:
             raise ValueError("y must be [batch, query_timeSteps, embed_dim]")
         H, kd, vd = self.num_heads, self.key_dim, self.value_dim
-        scratch = GPUTensor((max(B * Tq * H * kd, B * Tk * H * kd, B * Tk * H * vd, B * Tq * H * vd),), None, self.w)
-        Qh = self._split_heads(Q, self.w_Q, self.w_Q_bias, kd, scratch)
-        Kh = self._split_heads(K, self.w_K, self.w_K_bias, kd, scratch)
-        Vh = self._split_heads(V, self.w_V, self.w_V_bias, vd, scratch)
-        heads = scratch.Slice(0, (B * H, Tq, vd))
-        weights = ScaledDotProductAttentionForwardPropagation(Qh, Kh, Vh, heads, isTraining, None, True, self.is_causal)
-        merged = GPUTensor((B, Tq, H, vd), None, self.w)
-        heads.Reshape(B, H, Tq, vd).TransposeSecondAndThirdDimension(merged)
-        merged = merged.Reshape(B, Tq, H * vd)
-        FusedDenseForward(y, merged, self.out_proj_weight, self.out_proj_bias, ACT_IDENTITY, None, self.layout,
-                          flattenInputTensorOnLastDimension=True)
-        self._cache = (Qh, Kh, Vh, weights, merged) if isTraining else None
+        w = self.w
+        desc = self._desc(B, Tq, Tk)
+        state = [GPUTensor(s, None, w) for s in ((B * H, Tq, kd), (B * H, Tk, kd), (B * H, Tk, vd), (B, Tq, H * vd),
+                                                 (B * H, Tq, Tk))]
+        scratch = GPUTensor((w.lib.snb200_mha_scratch_floats(desc, 0),), None, w)
+        weights = self._ptrs(_capi.MhaWeights, [self._w(self.Weights, i) for i in range(4)] +
+                             [self._b(self.Bias, i) for i in range(4)])
+        check(w.handle, w.lib.snb200_mha_fwd(w.handle, desc, weights, Q.Pointer, K.Pointer, V.Pointer,
+                                             self._ptrs(_capi.MhaState, state), scratch.Pointer, y.Pointer))
+        self._cache = state if isTraining else None
 
     def BackwardPropagation(self, allX, dy, allDx, multiplier=1.0):
-        """(Prod/Layers/MultiheadAttention.cs:240-295); ``multiplier`` is the dW factor of Linear.cs:152-158."""
+        """One ``snb200_mha_bwd`` call (Prod/Layers/MultiheadAttention.cs:240-295); ``multiplier`` is the dW factor of
+        Linear.cs:152-158."""
         Q, K, V = allX
         dQ, dK, dV = allDx
-        Qh, Kh, Vh, weights, merged = self._cache
         B, Tq, _ = Q.Shape
         Tk = V.Shape[1]
-        H, kd, vd = self.num_heads, self.key_dim, self.value_dim
+        w = self.w
+        desc = self._desc(B, Tq, Tk)
+        scratch = GPUTensor((w.lib.snb200_mha_scratch_floats(desc, 1),), None, w)
+        weights = self._ptrs(_capi.MhaWeights, [self._w(self.Weights, i) for i in range(4)] +
+                             [self._b(self.Bias, i) for i in range(4)])
         dws, dbs = self.gradients()
-        scratch = GPUTensor((max(B * Tq * H * kd, B * Tk * H * kd, B * Tk * H * vd, B * Tq * H * vd),), None, self.w)
-        d_merged = scratch.Slice(0, (B, Tq, H * vd))
-        FusedDenseBackward(d_merged, dws[3], dbs[3], merged, dy, self.out_proj_weight, ACT_IDENTITY, None, None,
-                           multiplier, None, self.layout, flattenInputTensorOnLastDimension=True)
-        d_heads = GPUTensor((B, H, Tq, vd), None, self.w)
-        d_merged.Reshape(B, Tq, H, vd).TransposeSecondAndThirdDimension(d_heads)
-        dQh, dKh, dVh = (GPUTensor(t.Shape, None, self.w) for t in (Qh, Kh, Vh))
-        ScaledDotProductAttentionBackwardPropagation(dQh, dKh, dVh, Qh, Kh, Vh, d_heads.Reshape(B * H, Tq, vd), weights,
-                                                     True)
-        for dh, x, dx, i, T, d in ((dQh, Q, dQ, 0, Tq, kd), (dKh, K, dK, 1, Tk, kd), (dVh, V, dV, 2, Tk, vd)):
-            flat = scratch.Slice(0, (B, T, H, d))
-            dh.Reshape(B, H, T, d).TransposeSecondAndThirdDimension(flat)
-            FusedDenseBackward(dx, dws[i], dbs[i], x, flat.Reshape(B * T, H * d), self._w(self.Weights, i), ACT_IDENTITY,
-                               None, None, multiplier, None, self.layout, flattenInputTensorOnLastDimension=True)
+        check(w.handle, w.lib.snb200_mha_bwd(w.handle, desc, weights, Q.Pointer, K.Pointer, V.Pointer, dy.Pointer,
+                                             self._ptrs(_capi.MhaState, self._cache), float(multiplier), scratch.Pointer,
+                                             self._ptrs(_capi.MhaWeights, dws + dbs), dQ.Pointer, dK.Pointer, dV.Pointer))
         self._cache = None

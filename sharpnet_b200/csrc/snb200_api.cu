@@ -868,7 +868,6 @@ extern "C" int snb200_dense_bwd(snb200_handle_t h, int w_layout, int M, int K, i
   if (st) return st;
   if (!dW) return fail(h, SNB200_STATUS_INVALID_VALUE, "dW is null");
   const float* dz = dy;
-  long long launches0 = h->launches;
   if (act != ACT_IDENTITY) {
     if (!y) return fail(h, SNB200_STATUS_INVALID_VALUE, "activation output y is required for this activation");
     if (act == ACT_SWISH && !z) return fail(h, SNB200_STATUS_INVALID_VALUE, "pre-activation z is required for SWISH");
@@ -882,7 +881,6 @@ extern "C" int snb200_dense_bwd(snb200_handle_t h, int w_layout, int M, int K, i
     st = launch_colsum<false>(h, M, N, act, dy, nullptr, nullptr, nullptr, db);
     if (st) return st;
   }
-  (void)launches0;
   return dense_bwd_gemms(h, w_layout, M, K, N, x, W, dz, dW_multiplier, dx, dW);
 }
 
@@ -1157,6 +1155,109 @@ extern "C" int snb200_sdpa_bwd(snb200_handle_t h, int batch, int q_steps, int v_
   if (st) return st;
   bmm_problem(&g, batch, Tk, E, Tq, 1, 0, scores_grad_scratch, Tk, sW, Q, E, sQ, dK, 1.0f);
   return run_gemm(h, g);
+}
+
+// ------------------------------------------------------------------------------------ multi-head attention
+static long long round64(long long n) { return (n + 63) / 64 * 64; }   // 256-byte granules keep sub-buffers TMA-eligible
+
+static int mha_check(snb200_handle_t h, const snb200_mha_desc* d) {
+  if (!d) return fail(h, SNB200_STATUS_INVALID_VALUE, "null descriptor");
+  if (d->batch < 0 || d->q_steps < 0 || d->v_steps < 0 || d->embed_dim < 0 || d->num_heads <= 0 || d->key_dim <= 0 ||
+      d->value_dim <= 0)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "negative or zero dimension");
+  if (d->w_layout != SNB200_W_OUT_IN && d->w_layout != SNB200_W_IN_OUT)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "unknown weight layout %d", d->w_layout);
+  if (d->num_heads * d->value_dim != d->embed_dim)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "num_heads * value_dim (%d) must equal embed_dim (%d)",
+                d->num_heads * d->value_dim, d->embed_dim);
+  return 0;
+}
+
+extern "C" long long snb200_mha_scratch_floats(const snb200_mha_desc* d, int backward) {
+  if (!d) return 0;
+  const long long B = d->batch, Tq = d->q_steps, Tk = d->v_steps, H = d->num_heads, kd = d->key_dim, vd = d->value_dim;
+  long long flat = B * Tq * H * kd;
+  if (B * Tk * H * kd > flat) flat = B * Tk * H * kd;
+  if (B * Tk * H * vd > flat) flat = B * Tk * H * vd;
+  if (B * Tq * H * vd > flat) flat = B * Tq * H * vd;
+  if (!backward) return round64(flat);
+  // flat buffer, d_attention_heads, dQ_heads_T, dK_heads_T, dV_heads_T, gradient of the scores
+  return round64(flat) + round64(B * H * Tq * vd) + round64(B * H * Tq * kd) + round64(B * H * Tk * kd) +
+         round64(B * H * Tk * vd) + round64(B * H * Tq * Tk);
+}
+
+extern "C" int snb200_mha_fwd(snb200_handle_t h, const snb200_mha_desc* d, const snb200_mha_weights* w, const float* Q,
+                              const float* K, const float* V, const snb200_mha_state* s, float* scratch, float* y) {
+  int st = enter(h);
+  if (st) return st;
+  st = mha_check(h, d);
+  if (st) return st;
+  if (!w || !s || !scratch || !Q || !K || !V || !y || !w->w_Q || !w->w_K || !w->w_V || !w->out_proj_weight ||
+      !s->Q_heads_T || !s->K_heads_T || !s->V_heads_T || !s->attention_heads_T || !s->weights_buffer)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  const int B = d->batch, Tq = d->q_steps, Tk = d->v_steps, E = d->embed_dim, H = d->num_heads, kd = d->key_dim,
+            vd = d->value_dim;
+  if (B == 0 || Tq == 0 || Tk == 0 || E == 0) return 0;
+  // projections on the last dimension, each followed by the head split [b, t, h, d] -> [b, h, t, d]   (:201-218)
+  st = snb200_dense_fwd(h, d->w_layout, B * Tq, E, H * kd, Q, w->w_Q, w->w_Q_bias, ACT_IDENTITY, nullptr, scratch);
+  if (!st) st = snb200_transpose_second_third(h, B, Tq, H, kd, scratch, s->Q_heads_T);
+  if (!st) st = snb200_dense_fwd(h, d->w_layout, B * Tk, E, H * kd, K, w->w_K, w->w_K_bias, ACT_IDENTITY, nullptr, scratch);
+  if (!st) st = snb200_transpose_second_third(h, B, Tk, H, kd, scratch, s->K_heads_T);
+  if (!st) st = snb200_dense_fwd(h, d->w_layout, B * Tk, E, H * vd, V, w->w_V, w->w_V_bias, ACT_IDENTITY, nullptr, scratch);
+  if (!st) st = snb200_transpose_second_third(h, B, Tk, H, vd, scratch, s->V_heads_T);
+  // attention per head (always scaled, :32,221), heads merged back [b, h, t, d] -> [b, t, h, d]        (:220-226)
+  if (!st && kd != vd) st = fail(h, SNB200_STATUS_NOT_SUPPORTED, "key_dim and value_dim must be equal");
+  if (!st) st = snb200_sdpa_fwd(h, B * H, Tq, Tk, kd, 1, d->is_causal, s->Q_heads_T, s->K_heads_T, s->V_heads_T,
+                                s->weights_buffer, scratch);
+  if (!st) st = snb200_transpose_second_third(h, B, H, Tq, vd, scratch, s->attention_heads_T);
+  // output projection                                                                                   (:227)
+  if (!st) st = snb200_dense_fwd(h, d->w_layout, B * Tq, H * vd, E, s->attention_heads_T, w->out_proj_weight,
+                                 w->out_proj_bias, ACT_IDENTITY, nullptr, y);
+  if (!st) note_kernel(h, "multihead_attention_fwd", 0);
+  return st;
+}
+
+extern "C" int snb200_mha_bwd(snb200_handle_t h, const snb200_mha_desc* d, const snb200_mha_weights* w, const float* Q,
+                              const float* K, const float* V, const float* dy, const snb200_mha_state* s,
+                              float dW_multiplier, float* scratch, const snb200_mha_gradients* g, float* dQ, float* dK,
+                              float* dV) {
+  int st = enter(h);
+  if (st) return st;
+  st = mha_check(h, d);
+  if (st) return st;
+  if (!w || !s || !g || !scratch || !Q || !K || !V || !dy || !dQ || !dK || !dV || !w->w_Q || !w->w_K || !w->w_V ||
+      !w->out_proj_weight || !g->w_Q || !g->w_K || !g->w_V || !g->out_proj_weight || !s->Q_heads_T || !s->K_heads_T ||
+      !s->V_heads_T || !s->attention_heads_T || !s->weights_buffer)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
+  const int B = d->batch, Tq = d->q_steps, Tk = d->v_steps, E = d->embed_dim, H = d->num_heads, kd = d->key_dim,
+            vd = d->value_dim;
+  if (B == 0 || Tq == 0 || Tk == 0 || E == 0) return 0;
+  if (kd != vd) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "key_dim and value_dim must be equal");
+  float* flat = scratch;
+  float* d_heads = flat + snb200_mha_scratch_floats(d, 0);
+  float* dQh = d_heads + round64(static_cast<long long>(B) * H * Tq * vd);
+  float* dKh = dQh + round64(static_cast<long long>(B) * H * Tq * kd);
+  float* dVh = dKh + round64(static_cast<long long>(B) * H * Tk * kd);
+  float* dscores = dVh + round64(static_cast<long long>(B) * H * Tk * vd);
+  // output projection backward, then the head split of its dx                                           (:253-260)
+  st = snb200_dense_bwd(h, d->w_layout, B * Tq, H * vd, E, s->attention_heads_T, w->out_proj_weight, dy, ACT_IDENTITY,
+                        nullptr, nullptr, dW_multiplier, nullptr, flat, g->out_proj_weight, g->out_proj_bias);
+  if (!st) st = snb200_transpose_second_third(h, B, Tq, H, vd, flat, d_heads);
+  // attention backward per head                                                                         (:266-269)
+  if (!st) st = snb200_sdpa_bwd(h, B * H, Tq, Tk, kd, 1, s->Q_heads_T, s->K_heads_T, s->V_heads_T, d_heads,
+                                s->weights_buffer, dscores, dQh, dKh, dVh);
+  // heads merged back and the three input projections backward                                          (:271-278)
+  if (!st) st = snb200_transpose_second_third(h, B, H, Tq, kd, dQh, flat);
+  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tq, E, H * kd, Q, w->w_Q, flat, ACT_IDENTITY, nullptr, nullptr,
+                                 dW_multiplier, nullptr, dQ, g->w_Q, g->w_Q_bias);
+  if (!st) st = snb200_transpose_second_third(h, B, H, Tk, kd, dKh, flat);
+  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tk, E, H * kd, K, w->w_K, flat, ACT_IDENTITY, nullptr, nullptr,
+                                 dW_multiplier, nullptr, dK, g->w_K, g->w_K_bias);
+  if (!st) st = snb200_transpose_second_third(h, B, H, Tk, vd, dVh, flat);
+  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tk, E, H * vd, V, w->w_V, flat, ACT_IDENTITY, nullptr, nullptr,
+                                 dW_multiplier, nullptr, dV, g->w_V, g->w_V_bias);
+  if (!st) note_kernel(h, "multihead_attention_bwd", 0);
+  return st;
 }
 
 // ------------------------------------------------------------------------------------ NCCL (loaded at run time)
