@@ -238,6 +238,7 @@ int snb200_sdpa_bwd(snb200_handle_t handle, int batch, int q_steps, int v_steps,
  * call each: the Dense projections of Q, K, V on the last dimension (Linear.DenseForwardPropagation), the head
  * split [b, t, h, d] -> [b, h, t, d] (TransposeSecondAndThirdDimension), scaled dot-product attention per head
  * (use_scale is always on, :32), the head merge and the output projection; the backward pass in the reverse order.
+ * The permutations are not passes of their own: the product before each one stores its result already permuted.
  * The kernels of one call are queued back to back on the handle's stream, nothing is allocated.
  *   Q [batch, q_steps, embed_dim]; K, V [batch, v_steps, embed_dim]; y [batch, q_steps, embed_dim];
  *   embed_dim must equal num_heads * value_dim (the layer uses out_proj_weight that way, :121-126,236).
@@ -247,9 +248,9 @@ int snb200_sdpa_bwd(snb200_handle_t handle, int batch, int q_steps, int v_steps,
  *   Q_heads_T [batch*num_heads, q_steps, key_dim], K_heads_T [batch*num_heads, v_steps, key_dim],
  *   V_heads_T [batch*num_heads, v_steps, value_dim], attention_heads_T [batch, q_steps, num_heads*value_dim],
  *   weights_buffer [batch*num_heads, q_steps, v_steps].
- * `scratch` is caller-provided device memory of at least snb200_mha_scratch_floats(desc, backward) floats
- * (the layer's Q_K_V_heads_buffer, resp. dQ_dK_dV_heads_buffer, d_attention_heads, d*_heads_T and the gradient
- * of the scores), 256-byte aligned. */
+ * `scratch` is caller-provided device memory of at least snb200_mha_scratch_floats(desc, backward) floats, 256-byte
+ * aligned: nothing for the forward pass (0; scratch may be NULL), and for the backward pass the layer's
+ * d_attention_heads, the gradients of the three projections' outputs and the gradient of the scores. */
 typedef struct snb200_mha_desc {
   int w_layout, batch, q_steps, v_steps, embed_dim, num_heads, key_dim, value_dim, is_causal;
 } snb200_mha_desc;

@@ -122,11 +122,10 @@ class MultiheadAttention:
         desc = self._desc(B, Tq, Tk)
         state = [GPUTensor(s, None, w) for s in ((B * H, Tq, kd), (B * H, Tk, kd), (B * H, Tk, vd), (B, Tq, H * vd),
                                                  (B * H, Tq, Tk))]
-        scratch = GPUTensor((w.lib.snb200_mha_scratch_floats(desc, 0),), None, w)
         weights = self._ptrs(_capi.MhaWeights, [self._w(self.Weights, i) for i in range(4)] +
                              [self._b(self.Bias, i) for i in range(4)])
         check(w.handle, w.lib.snb200_mha_fwd(w.handle, desc, weights, Q.Pointer, K.Pointer, V.Pointer,
-                                             self._ptrs(_capi.MhaState, state), scratch.Pointer, y.Pointer))
+                                             self._ptrs(_capi.MhaState, state), None, y.Pointer))
         self._cache = state if isTraining else None
 
     def BackwardPropagation(self, allX, dy, allDx, multiplier=1.0):

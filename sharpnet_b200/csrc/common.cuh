@@ -13,6 +13,22 @@ enum Act : int { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_IDENTITY = 5, 
 // Prod/CPU/CpuTensor.cs:2458-2475).
 constexpr int ACT_LOSS_DIFF = 100;
 
+// Optional placement of the result: element (matrix i, row r, column c) of the logical [batch, M, N] result goes to
+//   (i / H) * s_io + (i % H) * s_ii + (r / T) * s_ro + (r % T) * s_ri + (c / d) * s_co + (c % d).
+// It lets a product store its result already permuted -- the head split [b, t, h, d] -> [b, h, t, d] of
+// multi-head attention and its inverse -- instead of a separate pass.  `on` = 0: the plain dense layout
+// i * strideC + r * ldc + c.  When on, d and every stride are multiples of 4 (whole float4s stay together).
+struct OutMap {
+  int on;
+  int H, T, d;
+  long long s_io, s_ii, s_ro, s_ri, s_co;
+};
+__host__ __device__ __forceinline__ long long out_offset(const OutMap& m, int i, int r, int c) {
+  return static_cast<long long>(i / m.H) * m.s_io + static_cast<long long>(i % m.H) * m.s_ii +
+         static_cast<long long>(r / m.T) * m.s_ro + static_cast<long long>(r % m.T) * m.s_ri +
+         static_cast<long long>(c / m.d) * m.s_co + (c % m.d);
+}
+
 // One (possibly strided-batched) GEMM  C[b] = epi(alpha * op(A[b]) * op(B[b]) + beta * C[b]).
 // All matrices are dense row-major fp32.
 struct GemmProblem {
@@ -33,6 +49,7 @@ struct GemmProblem {
   int row_op;             // RowOp
   int causal;             // ROW_SOFTMAX: columns above the main diagonal of every matrix count as -1e12
   const float* aux;       // ROW_SOFTMAX_GRAD: the softmax output y, laid out like C
+  OutMap omap;            // where C (and Z) go when not to the dense layout
 };
 enum RowOp : int { ROW_NONE = 0, ROW_SOFTMAX = 1, ROW_SOFTMAX_GRAD = 2 };
 

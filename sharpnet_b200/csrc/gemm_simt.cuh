@@ -23,6 +23,7 @@ struct SimtParams {
   float alpha, beta;
   int act;
   int tiles_m, tiles_n;
+  OutMap omap;
 };
 
 __global__ void __launch_bounds__(kSimtThreads)
@@ -81,20 +82,33 @@ simt_gemm_kernel(const SimtParams p) {
     __syncthreads();
   }
 
+  // Result placement: the column part of the address once per column, the row part once per row (with a mapped
+  // result each is an integer division, too long to repeat for every element of the unrolled loops).
+  long long cpart[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int col = n0 + tx * 4 + j;
+    cpart[j] = col;
+    if (p.omap.on) cpart[j] = static_cast<long long>(col / p.omap.d) * p.omap.s_co + (col % p.omap.d);
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int row = m0 + ty * 4 + i;
     if (row >= p.M) continue;
-    const size_t off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
+    long long rpart = static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc;
+    if (p.omap.on)
+      rpart = static_cast<long long>(b / p.omap.H) * p.omap.s_io + static_cast<long long>(b % p.omap.H) * p.omap.s_ii +
+              static_cast<long long>(row / p.omap.T) * p.omap.s_ro + static_cast<long long>(row % p.omap.T) * p.omap.s_ri;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int col = n0 + tx * 4 + j;
       if (col >= p.N) continue;
+      const long long off = rpart + cpart[j];
       float o = p.alpha * acc[i][j];
-      if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off + col], o);
+      if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
       if (p.bias) o += __ldg(p.bias + col);
-      if (p.Z) p.Z[off + col] = o;
-      p.C[off + col] = act_forward_compact(p.act, o);
+      if (p.Z) p.Z[off] = o;
+      p.C[off] = act_forward_compact(p.act, o);
     }
   }
 }
@@ -191,20 +205,31 @@ simt_gemm_big_kernel(const SimtParams p) {
     }
   }
 
+  long long cpart[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int col = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+    cpart[j] = col;
+    if (p.omap.on) cpart[j] = static_cast<long long>(col / p.omap.d) * p.omap.s_co + (col % p.omap.d);
+  }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int row = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
     if (row >= p.M) continue;
-    const size_t off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(row) * p.ldc;
+    long long rpart = static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc;
+    if (p.omap.on)
+      rpart = static_cast<long long>(b / p.omap.H) * p.omap.s_io + static_cast<long long>(b % p.omap.H) * p.omap.s_ii +
+              static_cast<long long>(row / p.omap.T) * p.omap.s_ro + static_cast<long long>(row % p.omap.T) * p.omap.s_ri;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int col = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
       if (col >= p.N) continue;
+      const long long off = rpart + cpart[j];
       float o = p.alpha * acc[i][j];
-      if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off + col], o);
+      if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
       if (p.bias) o += __ldg(p.bias + col);
-      if (p.Z) p.Z[off + col] = o;
-      p.C[off + col] = act_forward_compact(p.act, o);
+      if (p.Z) p.Z[off] = o;
+      p.C[off] = act_forward_compact(p.act, o);
     }
   }
 }

@@ -102,6 +102,7 @@ struct UmmaParams {
   int row_op;
   int causal;
   const float* aux;
+  OutMap omap;   // placement of C / Z when not dense (see OutMap)
 };
 
 // Work unit u of a launch over n_tiles output tiles: which tile, which K range, and (split >= 0) which
@@ -154,45 +155,66 @@ __device__ __forceinline__ void reg_alloc() {
 // HEAVY selects the transcendental activations (Swish, Tanh, Sigmoid).  Their inlined code is long, and
 // fully unrolled it outgrows the instruction cache (the fetch misses cost more than the stores), so that
 // variant keeps the row loop rolled; Identity and Relu are a select and stay unrolled so that the
-// loads of beta*C overlap.
-template <bool HEAVY>
-__device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, const float* stage, long long tile_off,
-                                                         int row_base, int col0, int lane) {
+// loads of beta*C overlap.  MAPPED places the result through p.omap (integer divisions per row: also rolled,
+// and kept out of the plain variants for the same reason).
+// Where and how one work unit's values are stored: the kernel's own epilogue parameters, or the workspace for
+// raw partial sums.  (A handful of fields instead of a copy of UmmaParams keeps the epilogue's register count.)
+struct StoreTarget {
+  float* C;
+  float* Z;
+  const float* bias;
+  float alpha, beta;
+  int act, ldc, vec_ok, mapped;
+};
+
+template <bool HEAVY, bool MAPPED>
+__device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, const StoreTarget& t, const float* stage,
+                                                         int b, long long tile_off, int row_base, int col0, int lane) {
   const int c4 = lane & 7;
   const int col = col0 + 4 * c4;
   float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (p.bias) bv = __ldg(reinterpret_cast<const float4*>(p.bias + col));
-  const bool relu = p.act == ACT_RELU;
-#pragma unroll(HEAVY ? 1 : 8)
+  if (t.bias) bv = __ldg(reinterpret_cast<const float4*>(t.bias + col));
+  const bool relu = t.act == ACT_RELU;
+  long long col_part = col;
+  if (MAPPED) {
+    col_part = static_cast<long long>(col / p.omap.d) * p.omap.s_co + (col % p.omap.d);
+    tile_off = static_cast<long long>(b / p.omap.H) * p.omap.s_io + static_cast<long long>(b % p.omap.H) * p.omap.s_ii;
+  }
+#pragma unroll((HEAVY || MAPPED) ? 1 : 8)
   for (int it = 0; it < 8; ++it) {
     const int r = it * 4 + (lane >> 3);
     const int row = row_base + r;
     if (row < p.M) {
       const float4 a4 = *reinterpret_cast<const float4*>(stage + r * 32 + ((c4 ^ (r & 7)) << 2));
-      const long long off = tile_off + static_cast<long long>(row) * p.ldc + col;
+      long long off;
+      if (MAPPED)
+        off = tile_off + static_cast<long long>(row / p.omap.T) * p.omap.s_ro +
+              static_cast<long long>(row % p.omap.T) * p.omap.s_ri + col_part;
+      else
+        off = tile_off + static_cast<long long>(row) * t.ldc + col;
       float4 o;
-      o.x = p.alpha * a4.x; o.y = p.alpha * a4.y; o.z = p.alpha * a4.z; o.w = p.alpha * a4.w;
-      if (p.beta != 0.0f) {
-        const float4 cin = *reinterpret_cast<const float4*>(p.C + off);
-        o.x = fmaf(p.beta, cin.x, o.x);
-        o.y = fmaf(p.beta, cin.y, o.y);
-        o.z = fmaf(p.beta, cin.z, o.z);
-        o.w = fmaf(p.beta, cin.w, o.w);
+      o.x = t.alpha * a4.x; o.y = t.alpha * a4.y; o.z = t.alpha * a4.z; o.w = t.alpha * a4.w;
+      if (t.beta != 0.0f) {
+        const float4 cin = *reinterpret_cast<const float4*>(t.C + off);
+        o.x = fmaf(t.beta, cin.x, o.x);
+        o.y = fmaf(t.beta, cin.y, o.y);
+        o.z = fmaf(t.beta, cin.z, o.z);
+        o.w = fmaf(t.beta, cin.w, o.w);
       }
       o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
-      if (p.Z) *reinterpret_cast<float4*>(p.Z + off) = o;
+      if (t.Z) *reinterpret_cast<float4*>(t.Z + off) = o;
       if (HEAVY) {
-        o.x = act_forward(p.act, o.x);
-        o.y = act_forward(p.act, o.y);
-        o.z = act_forward(p.act, o.z);
-        o.w = act_forward(p.act, o.w);
+        o.x = act_forward(t.act, o.x);
+        o.y = act_forward(t.act, o.y);
+        o.z = act_forward(t.act, o.z);
+        o.w = act_forward(t.act, o.w);
       } else {
         o.x = relu ? fmaxf(o.x, 0.0f) : o.x;
         o.y = relu ? fmaxf(o.y, 0.0f) : o.y;
         o.z = relu ? fmaxf(o.z, 0.0f) : o.z;
         o.w = relu ? fmaxf(o.w, 0.0f) : o.w;
       }
-      *reinterpret_cast<float4*>(p.C + off) = o;
+      *reinterpret_cast<float4*>(t.C + off) = o;
     }
   }
 }
@@ -201,11 +223,11 @@ __device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, co
 // 32 x 32 block goes through a per-warp shared-memory tile (16-byte chunks XOR-swizzled by row) so
 // that every global access of C, Z and bias is a run of whole 128-byte lines instead of 32 scattered
 // 16-byte pieces.  `row_base` is the first of the warp's 32 rows, `n0` its first column; element
-// (row, col) goes to p.C[tile_off + row * p.ldc + col].
+// (row, col) of matrix b goes to t.C[tile_off + row * t.ldc + col], or where p.omap places it.
 template <int NC>
-__device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const float (&acc)[NC], float* stage,
-                                              long long tile_off, int row_base, int n0, int lane) {
-  const bool heavy = p.act != ACT_IDENTITY && p.act != ACT_RELU;
+__device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const StoreTarget& t, const float (&acc)[NC],
+                                              float* stage, int b, long long tile_off, int row_base, int n0, int lane) {
+  const bool heavy = t.act != ACT_IDENTITY && t.act != ACT_RELU;
 #pragma unroll
   for (int g = 0; g < NC / 32; ++g) {
     const int col0 = n0 + g * 32;
@@ -217,24 +239,26 @@ __device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const f
       *reinterpret_cast<float4*>(stage + lane * 32 + ((j4 ^ (lane & 7)) << 2)) = v4;
     }
     __syncwarp();
-    if (p.vec_ok && col0 + 32 <= p.N) {
-      if (heavy) epilogue_store_block_vec<true>(p, stage, tile_off, row_base, col0, lane);
-      else       epilogue_store_block_vec<false>(p, stage, tile_off, row_base, col0, lane);
+    if (t.vec_ok && col0 + 32 <= p.N) {
+      if (t.mapped)   epilogue_store_block_vec<true, true>(p, t, stage, b, tile_off, row_base, col0, lane);
+      else if (heavy) epilogue_store_block_vec<true, false>(p, t, stage, b, tile_off, row_base, col0, lane);
+      else            epilogue_store_block_vec<false, false>(p, t, stage, b, tile_off, row_base, col0, lane);
     } else {
       // ragged right edge or rows that are not 16-byte aligned: one column per lane
       const int col = col0 + lane;
       if (col < p.N) {
-        const float bv = p.bias ? __ldg(p.bias + col) : 0.0f;
+        const float bv = t.bias ? __ldg(t.bias + col) : 0.0f;
         for (int r = 0; r < 32; ++r) {
           const int row = row_base + r;
           if (row >= p.M) break;
           const float a1 = stage[r * 32 + ((((lane >> 2) ^ (r & 7)) << 2) | (lane & 3))];
-          const long long off = tile_off + static_cast<long long>(row) * p.ldc + col;
-          float o = p.alpha * a1;
-          if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
+          long long off = tile_off + static_cast<long long>(row) * t.ldc + col;
+          if (t.mapped) off = out_offset(p.omap, b, row, col);
+          float o = t.alpha * a1;
+          if (t.beta != 0.0f) o = fmaf(t.beta, t.C[off], o);
           o += bv;
-          if (p.Z) p.Z[off] = o;
-          p.C[off] = act_forward(p.act, o);
+          if (t.Z) t.Z[off] = o;
+          t.C[off] = act_forward(t.act, o);
         }
       }
     }
@@ -324,30 +348,32 @@ __device__ __forceinline__ void epilogue_row_op(const UmmaParams& p, float (&acc
 // Final store of one work unit: the fused epilogue into C, or (split >= 0) the raw partial sums into
 // the workspace.  `tile_row0`/`tile_col0` are the first row and column of the unit's whole tile,
 // `tile_elems` the size of that tile in the tiled workspace layout (rows x BN), `bn` its row pitch there.
+// `alpha` is p.alpha, or 1 when a row operation has already applied it.
 template <int NC>
-__device__ __forceinline__ void epilogue_store_unit(const UmmaParams& p, const float (&acc)[NC], float* stage, int b,
-                                                    int n_tiles, int tile, int split, int tile_row0, int tile_col0,
-                                                    int bn, int row_base, int n0, int lane) {
-  if (split < 0 || p.partial == nullptr) {
-    epilogue_store_rows<NC>(p, acc, stage, static_cast<long long>(b) * p.strideC, row_base, n0, lane);
-    return;
+__device__ __forceinline__ void epilogue_store_unit(const UmmaParams& p, float alpha, const float (&acc)[NC], float* stage,
+                                                    int b, int n_tiles, int tile, int split, int tile_row0,
+                                                    int tile_col0, int bn, int row_base, int n0, int lane) {
+  // one call of the store phase (its code is long: a second copy costs instruction-cache misses); the
+  // partial-sum case redirects it to the workspace
+  StoreTarget t = {p.C, p.Z, p.bias, alpha, p.beta, p.act, p.ldc, p.vec_ok, p.omap.on};
+  long long off = static_cast<long long>(b) * p.strideC;
+  if (split >= 0 && p.partial != nullptr) {
+    t.C = p.partial;
+    t.mapped = 0;     // partial sums have their own layout; the reduction pass applies the placement
+    t.alpha = 1.0f; t.beta = 0.0f; t.bias = nullptr; t.Z = nullptr; t.act = ACT_IDENTITY;
+    if (p.partial_tiled) {
+      const int tail = n_tiles - p.whole_tiles;
+      const long long slot = static_cast<long long>(split) * tail + (tile - p.whole_tiles);
+      t.ldc = bn;
+      t.vec_ok = 1;
+      off = slot * p.partial_stride - (static_cast<long long>(tile_row0) * bn + tile_col0);
+    } else {
+      t.ldc = p.N;
+      t.vec_ok = (p.N % 4 == 0) ? 1 : 0;
+      off = static_cast<long long>(split) * p.partial_stride + static_cast<long long>(b) * p.M * p.N;
+    }
   }
-  UmmaParams pp = p;
-  pp.C = p.partial;
-  pp.alpha = 1.0f; pp.beta = 0.0f; pp.bias = nullptr; pp.Z = nullptr; pp.act = ACT_IDENTITY;
-  long long off;
-  if (p.partial_tiled) {
-    const int tail = n_tiles - p.whole_tiles;
-    const long long slot = static_cast<long long>(split) * tail + (tile - p.whole_tiles);
-    pp.ldc = bn;
-    pp.vec_ok = 1;
-    off = slot * p.partial_stride - (static_cast<long long>(tile_row0) * bn + tile_col0);
-  } else {
-    pp.ldc = p.N;
-    pp.vec_ok = (p.N % 4 == 0) ? 1 : 0;
-    off = static_cast<long long>(split) * p.partial_stride + static_cast<long long>(b) * p.M * p.N;
-  }
-  epilogue_store_rows<NC>(pp, acc, stage, off, row_base, n0, lane);
+  epilogue_store_rows<NC>(p, t, acc, stage, b, off, row_base, n0, lane);
 }
 
 // 3xTF32 operand split of one landed stage: lo = tf32(x - hi) goes to the second plane, RAW_BYTES
@@ -558,16 +584,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) break;
       float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
-      if (ROWOP && T::EPI_GROUPS == 1 && p.row_op != ROW_NONE) {
+      float alpha = p.alpha;
+      if (ROWOP && T::EPI_GROUPS == 1) {   // this instantiation is launched for row operations only
         epilogue_row_op<NC>(p, acc, stage, b, tm * BM + q * 32, lane);
-        UmmaParams pp = p;
-        pp.alpha = 1.0f;          // the row operation has consumed alpha
-        epilogue_store_unit<NC>(pp, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN, BN, tm * BM + q * 32,
-                                tn * BN + col_base, lane);
-      } else {
-        epilogue_store_unit<NC>(p, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN, BN, tm * BM + q * 32,
-                                tn * BN + col_base, lane);
+        alpha = 1.0f;                      // the row operation has consumed it
       }
+      epilogue_store_unit<NC>(p, alpha, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN, BN, tm * BM + q * 32,
+                              tn * BN + col_base, lane);
     }
   } else if (T::SPLIT) {
     // ------------------------------------------------------------------ hi / lo split
@@ -615,6 +638,7 @@ struct SplitKReduceParams {
   long long strideC;
   float alpha, beta;
   int act;
+  OutMap omap;
 };
 static __global__ void splitk_reduce_kernel(const SplitKReduceParams p) {
   const long long per_batch = static_cast<long long>(p.M) * p.N;
@@ -627,7 +651,8 @@ static __global__ void splitk_reduce_kernel(const SplitKReduceParams p) {
     const long long src = b * per_batch + (p.transposed ? static_cast<long long>(n) * p.M + m : r);
     float sum = 0.0f;
     for (int s = 0; s < p.splits; ++s) sum += p.partial[s * p.partial_stride + src];
-    const size_t off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(m) * p.ldc + n;
+    const long long off = p.omap.on ? out_offset(p.omap, static_cast<int>(b), m, n)
+                                    : b * p.strideC + static_cast<long long>(m) * p.ldc + n;
     float v = p.alpha * sum;
     if (p.beta != 0.0f) v = fmaf(p.beta, p.C[off], v);
     if (p.bias) v += __ldg(p.bias + n);
@@ -657,7 +682,8 @@ static __global__ void __launch_bounds__(256) splitk_reduce_transposed_kernel(co
   for (int j = ty; j < 32; j += 8) {
     const int m = m0 + j, n = n0 + tx;
     if (m < p.M && n < p.N) {
-      const size_t off = static_cast<size_t>(b) * p.strideC + static_cast<size_t>(m) * p.ldc + n;
+      const long long off = p.omap.on ? out_offset(p.omap, b, m, n)
+                                      : static_cast<long long>(b) * p.strideC + static_cast<long long>(m) * p.ldc + n;
       float v = p.alpha * tile[tx][j];
       if (p.beta != 0.0f) v = fmaf(p.beta, p.C[off], v);
       if (p.bias) v += __ldg(p.bias + n);
@@ -685,6 +711,7 @@ struct TailReduceParams {
   float alpha, beta;
   int act;
   int vec_ok;
+  OutMap omap;
 };
 static __global__ void __launch_bounds__(256) tail_reduce_kernel(const TailReduceParams p) {
   int b, tm, tn;
@@ -705,7 +732,8 @@ static __global__ void __launch_bounds__(256) tail_reduce_kernel(const TailReduc
       const float4 v = *reinterpret_cast<const float4*>(s0 + s * split_stride);
       sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
     }
-    const long long off = static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc + col;
+    const long long off = p.omap.on ? out_offset(p.omap, b, row, col)
+                                    : static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc + col;
     float o[4] = {p.alpha * sum.x, p.alpha * sum.y, p.alpha * sum.z, p.alpha * sum.w};
     if (p.vec_ok && col + 4 <= p.N) {
       if (p.beta != 0.0f) {

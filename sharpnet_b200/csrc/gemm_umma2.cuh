@@ -257,7 +257,7 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
       if (!ok) break;
       float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
-      epilogue_store_unit<NC>(p, acc, stage, b, n_tiles, tile, split, tm * 2 * BM, tn * BN, BN,
+      epilogue_store_unit<NC>(p, p.alpha, acc, stage, b, n_tiles, tile, split, tm * 2 * BM, tn * BN, BN,
                               tm * 2 * BM + rank * BM + q * 32, tn * BN + col_base, lane);
     }
   } else if (T::SPLIT) {

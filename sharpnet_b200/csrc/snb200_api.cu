@@ -208,6 +208,28 @@ static bool tma_eligible(const GemmProblem& g) {
   return true;
 }
 
+// Result placement (OutMap): may the stores move whole float4s?
+static bool omap_vec(const OutMap& m) {
+  return !m.on || (!(m.d & 3) && !(m.s_io & 3) && !(m.s_ii & 3) && !(m.s_ro & 3) && !(m.s_ri & 3) && !(m.s_co & 3));
+}
+constexpr int kNoDiv = 1 << 30;   // a divisor larger than any index: x / kNoDiv = 0, x % kNoDiv = x
+// A [B*T, H*d] result stored as [B, H, T, d]: the head split of multi-head attention.
+static OutMap head_split_map(int T, int H, int d) {
+  OutMap m;
+  m.on = 1; m.H = 1; m.s_io = 0; m.s_ii = 0;
+  m.T = T; m.s_ro = static_cast<long long>(H) * T * d; m.s_ri = d;
+  m.d = d; m.s_co = static_cast<long long>(T) * d;
+  return m;
+}
+// A batch of B*H [T x d] results stored as [B, T, H, d]: the head merge.
+static OutMap head_merge_map(int T, int H, int d) {
+  OutMap m;
+  m.on = 1; m.H = H; m.s_io = static_cast<long long>(T) * H * d; m.s_ii = d;
+  m.T = kNoDiv; m.s_ro = 0; m.s_ri = static_cast<long long>(H) * d;
+  m.d = kNoDiv; m.s_co = 0;
+  return m;
+}
+
 // Tensor maps and kernel parameters shared by the single-CTA and the CTA-pair kernels.  `bn_box` is
 // the number of B columns one CTA loads per stage (BN, or BN / 2 in a pair).
 template <class T>
@@ -247,6 +269,8 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
   p.splits = 1;
   p.kb_per_split = p.k_blocks;
   p.row_op = g.row_op; p.causal = g.causal; p.aux = g.aux;
+  p.omap = g.omap;
+  if (!omap_vec(g.omap)) p.vec_ok = 0;
   p.whole_tiles = 0;       // set by the launcher: it knows the tile grid of its kernel
   p.partial_tiled = 0;
   p.partial = nullptr;
@@ -428,6 +452,7 @@ static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
   p.ldc = g.ldc;
   p.A = g.A; p.B = g.B; p.C = g.C; p.Z = g.Z; p.bias = g.bias;
   p.alpha = g.alpha; p.beta = g.beta; p.act = g.act;
+  p.omap = g.omap;
   // 128 x 128 tiles once they fill most of the SMs; 64 x 64 tiles for everything smaller
   const long long big_tiles = static_cast<long long>((g.M + kSimtBigBM - 1) / kSimtBigBM) *
                               ((g.N + kSimtBigBN - 1) / kSimtBigBN) * g.batch;
@@ -528,8 +553,9 @@ static int launch_tail_reduce(snb200_handle_t h, const GemmProblem& g, const Spl
   r.tile_elems = static_cast<long long>(tile_rows) * bn;
   r.C = g.C; r.Z = g.Z; r.bias = g.bias; r.ldc = g.ldc; r.strideC = g.strideC;
   r.alpha = g.alpha; r.beta = g.beta; r.act = g.act;
+  r.omap = g.omap;
   r.vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (g.batch == 1 || g.strideC % 4 == 0) &&
-             (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias));
+             (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias)) && omap_vec(g.omap);
   dim3 grid(plan.tail, tile_rows / r.rows_per_block);
   tail_reduce_kernel<<<grid, 256, 0, h->stream>>>(r);
   h->launches += 1;
@@ -543,6 +569,7 @@ static int launch_reduce(snb200_handle_t h, const GemmProblem& g, int parts, int
   r.partial_stride = static_cast<long long>(g.batch) * g.M * g.N;
   r.C = g.C; r.Z = g.Z; r.bias = g.bias; r.ldc = g.ldc; r.strideC = g.strideC;
   r.alpha = g.alpha; r.beta = g.beta; r.act = g.act;
+  r.omap = g.omap;
   const long long total = r.partial_stride;
   long long blocks = (total + 255) / 256;
   if (blocks > 8LL * h->sm_count) blocks = 8LL * h->sm_count;
@@ -713,8 +740,15 @@ static bool act_supported(int act) {
   return act == ACT_SIGMOID || act == ACT_RELU || act == ACT_TANH || act == ACT_IDENTITY || act == ACT_SWISH;
 }
 
+static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
+                          const float* bias, int act, float* z, float* y, const OutMap* y_map);
 extern "C" int snb200_dense_fwd(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
                                 const float* bias, int act, float* z, float* y) {
+  return dense_fwd_impl(h, w_layout, M, K, N, x, W, bias, act, z, y, nullptr);
+}
+// `y_map`, when given, places y (and z) somewhere else than the dense [M, N] layout.
+static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
+                          const float* bias, int act, float* z, float* y, const OutMap* y_map) {
   int st = enter(h);
   if (st) return st;
   if (M < 0 || K < 0 || N < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
@@ -734,6 +768,7 @@ extern "C" int snb200_dense_fwd(snb200_handle_t h, int w_layout, int M, int K, i
   g.A = x; g.B = W; g.C = y;
   g.alpha = 1.0f; g.beta = 0.0f;
   g.bias = bias; g.Z = z; g.act = act;
+  if (y_map) g.omap = *y_map;
   return run_gemm(h, g);
 }
 
@@ -787,7 +822,7 @@ static bool loss_scale(int loss, int N, float* scale) {
 
 // dW and dx of the Dense backward from dz (the gradient w.r.t. the pre-activation).
 static int dense_bwd_gemms(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
-                           const float* dz, float dW_multiplier, float* dx, float* dW) {
+                           const float* dz, float dW_multiplier, float* dx, float* dW, const OutMap* dx_map = nullptr) {
   int st = 0;
   GemmProblem g;
   memset(&g, 0, sizeof(g));
@@ -811,6 +846,7 @@ static int dense_bwd_gemms(snb200_handle_t h, int w_layout, int M, int K, int N,
     if (w_layout == SNB200_W_OUT_IN) { g.transB = 0; g.B = W; g.ldb = K; }   // dx = dz * W      (Linear.cs:190)
     else                             { g.transB = 1; g.B = W; g.ldb = N; }   // dx = dz * W^T
     g.C = dx; g.ldc = K; g.alpha = 1.0f;
+    if (dx_map) g.omap = *dx_map;
     st = run_gemm(h, g);
     if (st) return st;
   }
@@ -855,9 +891,18 @@ extern "C" int snb200_dense_bwd_from_loss(snb200_handle_t h, int w_layout, int M
   return dense_bwd_gemms(h, w_layout, M, K, N, x, W, dz_scratch, dW_multiplier, dx, dW);
 }
 
+static int dense_bwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
+                          const float* dy, int act, const float* y, const float* z, float dW_multiplier,
+                          float* dz_scratch, float* dx, float* dW, float* db, const OutMap* dx_map);
 extern "C" int snb200_dense_bwd(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
                                 const float* dy, int act, const float* y, const float* z, float dW_multiplier,
                                 float* dz_scratch, float* dx, float* dW, float* db) {
+  return dense_bwd_impl(h, w_layout, M, K, N, x, W, dy, act, y, z, dW_multiplier, dz_scratch, dx, dW, db, nullptr);
+}
+// `dx_map`, when given, places dx somewhere else than the dense [M, K] layout.
+static int dense_bwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
+                          const float* dy, int act, const float* y, const float* z, float dW_multiplier,
+                          float* dz_scratch, float* dx, float* dW, float* db, const OutMap* dx_map) {
   int st = enter(h);
   if (st) return st;
   if (M < 0 || K < 0 || N < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
@@ -881,7 +926,7 @@ extern "C" int snb200_dense_bwd(snb200_handle_t h, int w_layout, int M, int K, i
     st = launch_colsum<false>(h, M, N, act, dy, nullptr, nullptr, nullptr, db);
     if (st) return st;
   }
-  return dense_bwd_gemms(h, w_layout, M, K, N, x, W, dz, dW_multiplier, dx, dW);
+  return dense_bwd_gemms(h, w_layout, M, K, N, x, W, dz, dW_multiplier, dx, dW, dx_map);
 }
 
 // ------------------------------------------------------------------------------------ companions
@@ -1078,9 +1123,17 @@ static bool row_op_fits(const snb200_context* h, const GemmProblem& g) {
   return static_cast<double>(g.M) * g.N * g.K * g.batch >= 64.0 * 64 * 64;
 }
 
+static int sdpa_fwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim, int use_scale,
+                         int is_causal, const float* Q, const float* K, const float* V, float* weights, float* y,
+                         const OutMap* y_map);
 extern "C" int snb200_sdpa_fwd(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim,
                                int use_scale, int is_causal, const float* Q, const float* K, const float* V,
                                float* weights, float* y) {
+  return sdpa_fwd_impl(h, batch, q_steps, v_steps, embedding_dim, use_scale, is_causal, Q, K, V, weights, y, nullptr);
+}
+static int sdpa_fwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim, int use_scale,
+                         int is_causal, const float* Q, const float* K, const float* V, float* weights, float* y,
+                         const OutMap* y_map) {
   int st = enter(h);
   if (st) return st;
   if (batch < 0 || q_steps < 0 || v_steps < 0 || embedding_dim < 0)
@@ -1110,12 +1163,25 @@ extern "C" int snb200_sdpa_fwd(snb200_handle_t h, int batch, int q_steps, int v_
   // y = weights * V                                   (:85)
   bmm_problem(&g, batch, Tq, E, Tk, 0, 0, weights, Tk, static_cast<long long>(Tq) * Tk, V, E,
               static_cast<long long>(Tk) * E, y, 1.0f);
+  if (y_map) g.omap = *y_map;
   return run_gemm(h, g);
 }
 
+static int sdpa_bwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim, int use_scale,
+                         const float* Q, const float* K, const float* V, const float* dy, const float* weights,
+                         float* scores_grad_scratch, float* dQ, float* dK, float* dV, const OutMap* dq_map,
+                         const OutMap* dkv_map);
 extern "C" int snb200_sdpa_bwd(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim,
                                int use_scale, const float* Q, const float* K, const float* V, const float* dy,
                                const float* weights, float* scores_grad_scratch, float* dQ, float* dK, float* dV) {
+  return sdpa_bwd_impl(h, batch, q_steps, v_steps, embedding_dim, use_scale, Q, K, V, dy, weights, scores_grad_scratch,
+                       dQ, dK, dV, nullptr, nullptr);
+}
+// `dq_map` places dQ, `dkv_map` places dK and dV, when they do not go to the dense per-matrix layout.
+static int sdpa_bwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim, int use_scale,
+                         const float* Q, const float* K, const float* V, const float* dy, const float* weights,
+                         float* scores_grad_scratch, float* dQ, float* dK, float* dV, const OutMap* dq_map,
+                         const OutMap* dkv_map) {
   int st = enter(h);
   if (st) return st;
   if (batch < 0 || q_steps < 0 || v_steps < 0 || embedding_dim < 0)
@@ -1132,6 +1198,7 @@ extern "C" int snb200_sdpa_bwd(snb200_handle_t h, int batch, int q_steps, int v_
   GemmProblem g;
   // dV = weights^T * dy                               (ScaledDotProductAttentionLayer.cs:113)
   bmm_problem(&g, batch, Tk, E, Tq, 1, 0, weights, Tk, sW, dy, E, sQ, dV, 1.0f);
+  if (dkv_map) g.omap = *dkv_map;
   st = run_gemm(h, g);
   if (st) return st;
   // gradient w.r.t. the weights, scaled: scaling * dy * V^T    (:119)
@@ -1151,9 +1218,11 @@ extern "C" int snb200_sdpa_bwd(snb200_handle_t h, int batch, int q_steps, int v_
   }
   // dQ = dScores * K ; dK = dScores^T * Q             (:123-124)
   bmm_problem(&g, batch, Tq, E, Tk, 0, 0, scores_grad_scratch, Tk, sW, K, E, sK, dQ, 1.0f);
+  if (dq_map) g.omap = *dq_map;
   st = run_gemm(h, g);
   if (st) return st;
   bmm_problem(&g, batch, Tk, E, Tq, 1, 0, scores_grad_scratch, Tk, sW, Q, E, sQ, dK, 1.0f);
+  if (dkv_map) g.omap = *dkv_map;
   return run_gemm(h, g);
 }
 
@@ -1174,16 +1243,11 @@ static int mha_check(snb200_handle_t h, const snb200_mha_desc* d) {
 }
 
 extern "C" long long snb200_mha_scratch_floats(const snb200_mha_desc* d, int backward) {
-  if (!d) return 0;
+  if (!d || !backward) return 0;   // the forward pass writes straight into the state tensors
   const long long B = d->batch, Tq = d->q_steps, Tk = d->v_steps, H = d->num_heads, kd = d->key_dim, vd = d->value_dim;
-  long long flat = B * Tq * H * kd;
-  if (B * Tk * H * kd > flat) flat = B * Tk * H * kd;
-  if (B * Tk * H * vd > flat) flat = B * Tk * H * vd;
-  if (B * Tq * H * vd > flat) flat = B * Tq * H * vd;
-  if (!backward) return round64(flat);
-  // flat buffer, d_attention_heads, dQ_heads_T, dK_heads_T, dV_heads_T, gradient of the scores
-  return round64(flat) + round64(B * H * Tq * vd) + round64(B * H * Tq * kd) + round64(B * H * Tk * kd) +
-         round64(B * H * Tk * vd) + round64(B * H * Tq * Tk);
+  // d_attention_heads, the gradients of the Q, K, V projections' outputs, the gradient of the scores
+  return round64(B * H * Tq * vd) + round64(B * Tq * H * kd) + round64(B * Tk * H * kd) + round64(B * Tk * H * vd) +
+         round64(B * H * Tq * Tk);
 }
 
 extern "C" int snb200_mha_fwd(snb200_handle_t h, const snb200_mha_desc* d, const snb200_mha_weights* w, const float* Q,
@@ -1192,27 +1256,28 @@ extern "C" int snb200_mha_fwd(snb200_handle_t h, const snb200_mha_desc* d, const
   if (st) return st;
   st = mha_check(h, d);
   if (st) return st;
-  if (!w || !s || !scratch || !Q || !K || !V || !y || !w->w_Q || !w->w_K || !w->w_V || !w->out_proj_weight ||
+  if (!w || !s || !Q || !K || !V || !y || !w->w_Q || !w->w_K || !w->w_V || !w->out_proj_weight ||
       !s->Q_heads_T || !s->K_heads_T || !s->V_heads_T || !s->attention_heads_T || !s->weights_buffer)
     return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   const int B = d->batch, Tq = d->q_steps, Tk = d->v_steps, E = d->embed_dim, H = d->num_heads, kd = d->key_dim,
             vd = d->value_dim;
   if (B == 0 || Tq == 0 || Tk == 0 || E == 0) return 0;
-  // projections on the last dimension, each followed by the head split [b, t, h, d] -> [b, h, t, d]   (:201-218)
-  st = snb200_dense_fwd(h, d->w_layout, B * Tq, E, H * kd, Q, w->w_Q, w->w_Q_bias, ACT_IDENTITY, nullptr, scratch);
-  if (!st) st = snb200_transpose_second_third(h, B, Tq, H, kd, scratch, s->Q_heads_T);
-  if (!st) st = snb200_dense_fwd(h, d->w_layout, B * Tk, E, H * kd, K, w->w_K, w->w_K_bias, ACT_IDENTITY, nullptr, scratch);
-  if (!st) st = snb200_transpose_second_third(h, B, Tk, H, kd, scratch, s->K_heads_T);
-  if (!st) st = snb200_dense_fwd(h, d->w_layout, B * Tk, E, H * vd, V, w->w_V, w->w_V_bias, ACT_IDENTITY, nullptr, scratch);
-  if (!st) st = snb200_transpose_second_third(h, B, Tk, H, vd, scratch, s->V_heads_T);
-  // attention per head (always scaled, :32,221), heads merged back [b, h, t, d] -> [b, t, h, d]        (:220-226)
+  // Projections on the last dimension; each product stores its result already split by head, [b, t, h, d] ->
+  // [b, h, t, d] (the layer's TransposeSecondAndThirdDimension, :201-218), so no permutation pass runs.
+  const OutMap split_q = head_split_map(Tq, H, kd), split_k = head_split_map(Tk, H, kd), split_v = head_split_map(Tk, H, vd);
+  st = dense_fwd_impl(h, d->w_layout, B * Tq, E, H * kd, Q, w->w_Q, w->w_Q_bias, ACT_IDENTITY, nullptr, s->Q_heads_T, &split_q);
+  if (!st) st = dense_fwd_impl(h, d->w_layout, B * Tk, E, H * kd, K, w->w_K, w->w_K_bias, ACT_IDENTITY, nullptr, s->K_heads_T, &split_k);
+  if (!st) st = dense_fwd_impl(h, d->w_layout, B * Tk, E, H * vd, V, w->w_V, w->w_V_bias, ACT_IDENTITY, nullptr, s->V_heads_T, &split_v);
+  // attention per head (always scaled, :32,221); its second product stores the heads merged, [b, h, t, d] ->
+  // [b, t, h, d]                                                                                        (:220-226)
   if (!st && kd != vd) st = fail(h, SNB200_STATUS_NOT_SUPPORTED, "key_dim and value_dim must be equal");
-  if (!st) st = snb200_sdpa_fwd(h, B * H, Tq, Tk, kd, 1, d->is_causal, s->Q_heads_T, s->K_heads_T, s->V_heads_T,
-                                s->weights_buffer, scratch);
-  if (!st) st = snb200_transpose_second_third(h, B, H, Tq, vd, scratch, s->attention_heads_T);
+  const OutMap merge = head_merge_map(Tq, H, vd);
+  if (!st) st = sdpa_fwd_impl(h, B * H, Tq, Tk, kd, 1, d->is_causal, s->Q_heads_T, s->K_heads_T, s->V_heads_T,
+                              s->weights_buffer, s->attention_heads_T, &merge);
   // output projection                                                                                   (:227)
   if (!st) st = snb200_dense_fwd(h, d->w_layout, B * Tq, H * vd, E, s->attention_heads_T, w->out_proj_weight,
                                  w->out_proj_bias, ACT_IDENTITY, nullptr, y);
+  (void)scratch;
   if (!st) note_kernel(h, "multihead_attention_fwd", 0);
   return st;
 }
@@ -1233,28 +1298,25 @@ extern "C" int snb200_mha_bwd(snb200_handle_t h, const snb200_mha_desc* d, const
             vd = d->value_dim;
   if (B == 0 || Tq == 0 || Tk == 0 || E == 0) return 0;
   if (kd != vd) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "key_dim and value_dim must be equal");
-  float* flat = scratch;
-  float* d_heads = flat + snb200_mha_scratch_floats(d, 0);
+  float* d_heads = scratch;
   float* dQh = d_heads + round64(static_cast<long long>(B) * H * Tq * vd);
   float* dKh = dQh + round64(static_cast<long long>(B) * H * Tq * kd);
   float* dVh = dKh + round64(static_cast<long long>(B) * H * Tk * kd);
   float* dscores = dVh + round64(static_cast<long long>(B) * H * Tk * vd);
-  // output projection backward, then the head split of its dx                                           (:253-260)
-  st = snb200_dense_bwd(h, d->w_layout, B * Tq, H * vd, E, s->attention_heads_T, w->out_proj_weight, dy, ACT_IDENTITY,
-                        nullptr, nullptr, dW_multiplier, nullptr, flat, g->out_proj_weight, g->out_proj_bias);
-  if (!st) st = snb200_transpose_second_third(h, B, Tq, H, vd, flat, d_heads);
-  // attention backward per head                                                                         (:266-269)
-  if (!st) st = snb200_sdpa_bwd(h, B * H, Tq, Tk, kd, 1, s->Q_heads_T, s->K_heads_T, s->V_heads_T, d_heads,
-                                s->weights_buffer, dscores, dQh, dKh, dVh);
-  // heads merged back and the three input projections backward                                          (:271-278)
-  if (!st) st = snb200_transpose_second_third(h, B, H, Tq, kd, dQh, flat);
-  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tq, E, H * kd, Q, w->w_Q, flat, ACT_IDENTITY, nullptr, nullptr,
+  // output projection backward; its dx product stores the gradient already split by head             (:253-260)
+  const OutMap split_o = head_split_map(Tq, H, vd);
+  st = dense_bwd_impl(h, d->w_layout, B * Tq, H * vd, E, s->attention_heads_T, w->out_proj_weight, dy, ACT_IDENTITY,
+                      nullptr, nullptr, dW_multiplier, nullptr, d_heads, g->out_proj_weight, g->out_proj_bias, &split_o);
+  // attention backward per head; dQ, dK, dV come out merged, [b, h, t, d] -> [b, t, h, d]               (:266-278)
+  const OutMap merge_q = head_merge_map(Tq, H, kd), merge_kv = head_merge_map(Tk, H, kd);
+  if (!st) st = sdpa_bwd_impl(h, B * H, Tq, Tk, kd, 1, s->Q_heads_T, s->K_heads_T, s->V_heads_T, d_heads,
+                              s->weights_buffer, dscores, dQh, dKh, dVh, &merge_q, &merge_kv);
+  // the three input projections backward
+  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tq, E, H * kd, Q, w->w_Q, dQh, ACT_IDENTITY, nullptr, nullptr,
                                  dW_multiplier, nullptr, dQ, g->w_Q, g->w_Q_bias);
-  if (!st) st = snb200_transpose_second_third(h, B, H, Tk, kd, dKh, flat);
-  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tk, E, H * kd, K, w->w_K, flat, ACT_IDENTITY, nullptr, nullptr,
+  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tk, E, H * kd, K, w->w_K, dKh, ACT_IDENTITY, nullptr, nullptr,
                                  dW_multiplier, nullptr, dK, g->w_K, g->w_K_bias);
-  if (!st) st = snb200_transpose_second_third(h, B, H, Tk, vd, dVh, flat);
-  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tk, E, H * vd, V, w->w_V, flat, ACT_IDENTITY, nullptr, nullptr,
+  if (!st) st = snb200_dense_bwd(h, d->w_layout, B * Tk, E, H * vd, V, w->w_V, dVh, ACT_IDENTITY, nullptr, nullptr,
                                  dW_multiplier, nullptr, dV, g->w_V, g->w_V_bias);
   if (!st) note_kernel(h, "multihead_attention_bwd", 0);
   return st;

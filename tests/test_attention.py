@@ -301,3 +301,27 @@ def test_gpu_transpose_second_and_third_dimension(wrapper):
         back = GPUTensor(shape, None, wrapper)
         dst.TransposeSecondAndThirdDimension(back)                    # the permutation is its own inverse
         np.testing.assert_array_equal(back.ContentAsFloatArray(), x)
+
+
+@pytest.mark.gpu
+def test_gpu_multihead_attention_argument_errors(wrapper):
+    from sharpnet_b200 import _capi
+    from sharpnet_b200.attention import MultiheadAttention
+    from sharpnet_b200.tensor import GPUTensor
+    with pytest.raises(ValueError):
+        MultiheadAttention(3, 2, 2, False, False, False, 8, wrapper)          # heads * value_dim != embed
+    layer = MultiheadAttention(2, 4, 4, True, True, False, 8, wrapper)
+    Q, K = GPUTensor((2, 3, 8), None, wrapper), GPUTensor((2, 5, 8), None, wrapper)
+    with pytest.raises(ValueError):
+        layer.ForwardPropagation([Q, K, GPUTensor((2, 4, 8), None, wrapper)], GPUTensor((2, 3, 8), None, wrapper))
+    lib, h = wrapper.lib, wrapper.handle
+    desc = _capi.MhaDesc(0, 2, 3, 5, 8, 2, 4, 4, 0)
+    # nothing for the forward pass; the backward pass: d_attention_heads, the three projection-output gradients, the
+    # gradient of the scores, each rounded up to 64 floats
+    assert lib.snb200_mha_scratch_floats(desc, 0) == 0
+    assert lib.snb200_mha_scratch_floats(desc, 1) == 64 + 64 + 128 + 128 + 64
+    bad = _capi.MhaDesc(0, 2, 3, 5, 8, 3, 4, 4, 0)
+    assert lib.snb200_mha_fwd(h, bad, _capi.MhaWeights(), None, None, None, _capi.MhaState(), None, None) == 7
+    assert "embed_dim" in lib.snb200_last_error_string(h).decode()
+    assert lib.snb200_mha_fwd(h, desc, _capi.MhaWeights(), None, None, None, _capi.MhaState(), None, None) == 7
+    assert lib.snb200_mha_fwd(h, None, None, None, None, None, None, None, None) == 7

@@ -300,3 +300,48 @@ def test_linearity_at_full_size(wrapper):
     C1.Dot(A1, False, A1, True, 1, 0)
     sym = (C1.storage.view(n, n) - C1.storage.view(n, n).t()).abs().max().item()
     assert sym / np.sqrt(n) <= 2 * TOL_3XTF32
+
+
+def test_gemm_timing_entry_points(wrapper):
+    # event pairs around every product between _begin and _end; nothing is recorded outside
+    import ctypes
+    a = GPUTensor((512, 256), orc.uniform((512, 256), -1, 1, 1), wrapper)
+    b = GPUTensor((256, 384), orc.uniform((256, 384), -1, 1, 2), wrapper)
+    c = GPUTensor((512, 384), None, wrapper)
+    ms, n = ctypes.c_double(), ctypes.c_int()
+    assert wrapper.lib.snb200_gemm_timing_end(wrapper.handle, ctypes.byref(ms), ctypes.byref(n)) == 7   # not begun
+    c.Dot(a, b)
+    wrapper.gemm_timing_begin()
+    for _ in range(3):
+        c.Dot(a, b)
+    total, calls = wrapper.gemm_timing_end()
+    assert calls == 3 and 0.0 < total < 50.0
+    c.Dot(a, b)
+    wrapper.gemm_timing_begin()
+    total, calls = wrapper.gemm_timing_end()
+    assert calls == 0 and total == 0.0
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+def test_dependent_launch_on_and_off_give_the_same_bits(wrapper, mode, tol):
+    # a chain of products, each reading what the previous one wrote, with the kernels' set-up overlapping the
+    # previous kernel's tail (default) and without: identical results
+    from sharpnet_b200._capi import TUNE_PDL
+    wrapper.set_math_mode(mode)
+    x = orc.uniform((384, 384), -1, 1, 5)
+    W = orc.uniform((384, 384), -0.08, 0.08, 6)
+    outs = []
+    for off in (0, 1):
+        wrapper.set_tuning(TUNE_PDL, off)
+        bufs = [GPUTensor(x.shape, x, wrapper), GPUTensor(x.shape, None, wrapper)]
+        Wg = GPUTensor(W.shape, W, wrapper)
+        for i in range(12):
+            bufs[(i + 1) % 2].Dot(bufs[i % 2], False, Wg, i % 2 == 1, 1.0, 0.0)
+        wrapper.check_device_status()
+        outs.append(bufs[0].ContentAsFloatArray())
+    wrapper.set_tuning(TUNE_PDL, 0)
+    np.testing.assert_array_equal(outs[0], outs[1])
+    ref = x.astype(np.float64)
+    for i in range(12):
+        ref = ref @ (W.T if i % 2 == 1 else W).astype(np.float64)
+    assert np.abs(outs[0] - ref).max() <= 12 * tol * np.sqrt(384) * np.abs(ref).max() + 1e-12
