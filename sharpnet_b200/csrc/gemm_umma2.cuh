@@ -234,9 +234,12 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
       tile_coords(tile, pair_tiles_m, p.tiles_n, b, tm, tn);
       const int n_chunks = (kb_end - kb_begin + p.chunk_kblocks - 1) / p.chunk_kblocks;
+      float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
       float acc[NC];
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] = 0.0f;
+      const bool c_folded = epilogue_fold_c<NC>(p, acc, stage, b, split, tm * 2 * BM + rank * BM + q * 32,
+                                                tn * BN + col_base, lane);
       for (int c = 0; c < n_chunks && ok; ++c, ++chunk_id) {
         const int buf = chunk_id & 1;
         if (!mbar_wait_cluster_warp(&acc_full_bar[buf], (acc_ph >> buf) & 1u, abortp)) { ok = false; break; }
@@ -256,8 +259,7 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[buf]), 0));
       }
       if (!ok) break;
-      float* stage = reinterpret_cast<float*>(ring + T::RING_BYTES) + (warp - 4) * (T::EPI_STAGE_BYTES / 4);
-      epilogue_store_unit<NC>(p, p.alpha, acc, stage, b, n_tiles, tile, split, tm * 2 * BM, tn * BN, BN,
+      epilogue_store_unit<NC>(p, p.alpha, c_folded ? 0.0f : p.beta, acc, stage, b, n_tiles, tile, split, tm * 2 * BM, tn * BN, BN,
                               tm * 2 * BM + rank * BM + q * 32, tn * BN + col_base, lane);
     }
   } else if (T::SPLIT) {
