@@ -6,6 +6,21 @@
 
 namespace snb {
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may
+// start while the kernel before it in the stream is still running; grid_dependency_wait() returns once that
+// kernel has completed and its memory operations are visible, and must come before the first access to global
+// memory.  allow_dependent_launch() lets the next such kernel be scheduled as soon as every CTA of this grid
+// has started; it does not weaken what that kernel's own wait guarantees.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// First statement of every kernel of this library: let the next kernel of the stream be scheduled early, and wait
+// for the previous one before touching global memory.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_prologue() {
+  allow_dependent_launch();
+  grid_dependency_wait();
+}
+
 // Values of cudnnActivationMode_t (Prod/GPU/CudnnWrapper.cs:267-281).
 enum Act : int { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_IDENTITY = 5, ACT_SWISH = 6 };
 // Internal selector of the fused column-sum pass: dz = scale * (yPredicted - yExpected), the gradient of

@@ -8,12 +8,14 @@ namespace snb {
 
 // y[m, n] += bias[n]                               (Prod/CPU/CpuTensor.cs:1468-1487)
 static __global__ void bias_add_kernel(long long total, int N, const float* __restrict__ bias, float* __restrict__ y) {
+  pdl_prologue();
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride)
     y[i] += __ldg(bias + (i % N));
 }
 static __global__ void bias_add_vec4_kernel(long long total4, int N4, const float4* __restrict__ bias,
                                      float4* __restrict__ y) {
+  pdl_prologue();
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total4; i += stride) {
     float4 v = y[i];
@@ -35,6 +37,7 @@ __device__ __forceinline__ void lane_set(float& v, int, float x) { v = x; }
 
 template <int VEC>
 static __global__ void activation_fwd_kernel(int act, long long n, const float* __restrict__ x, float* __restrict__ y) {
+  pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -51,6 +54,7 @@ static __global__ void activation_fwd_kernel(int act, long long n, const float* 
 template <int VEC>
 static __global__ void activation_bwd_kernel(int act, long long n, const float* __restrict__ dy, const float* __restrict__ x,
                                              const float* __restrict__ y, float* __restrict__ dx) {
+  pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -71,6 +75,7 @@ static __global__ void activation_bwd_kernel(int act, long long n, const float* 
 // y += alpha * x                                    (Prod/CPU/CpuTensor.cs:1032-1038)
 template <int VEC>
 static __global__ void axpy_kernel(long long n, float alpha, const float* __restrict__ x, float* __restrict__ y) {
+  pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -91,6 +96,7 @@ static __global__ void axpy_kernel(long long n, float alpha, const float* __rest
 template <int VEC>
 static __global__ void transpose_second_third_kernel(long long total_vec, int B, int C, int Dv,
                                                      const float* __restrict__ src, float* __restrict__ dst) {
+  pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total_vec; i += stride) {
@@ -117,6 +123,7 @@ __global__ void __launch_bounds__(256)
 colsum_slab_kernel(int M, int N, int rows_per_slab, int act, const float* __restrict__ dy,
                    const float* __restrict__ y, const float* __restrict__ z, float* __restrict__ dz,
                    float* __restrict__ out, float scale = 1.0f) {
+  pdl_prologue();
   __shared__ float red[8][32 * VEC];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int col = (blockIdx.x * 32 + lane) * VEC;
@@ -177,6 +184,7 @@ colsum_slab_kernel(int M, int N, int rows_per_slab, int act, const float* __rest
 }
 
 static __global__ void colsum_finish_kernel(int N, int slabs, const float* __restrict__ partial, float* __restrict__ db) {
+  pdl_prologue();
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= N) return;
   float t = 0.0f;
@@ -188,6 +196,7 @@ static __global__ void colsum_finish_kernel(int N, int slabs, const float* __res
 template <int VEC>
 static __global__ void loss_gradient_kernel(long long n, float scale, const float* __restrict__ expected,
                                             const float* __restrict__ predicted, float* __restrict__ dy) {
+  pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -212,6 +221,7 @@ static __global__ void loss_gradient_kernel(long long n, float scale, const floa
 template <int PER_LANE>
 static __global__ void __launch_bounds__(256)
 softmax_fwd_kernel(long long rows, int cols, int causal_rows, const float* x, float* y) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -262,6 +272,7 @@ softmax_fwd_kernel(long long rows, int cols, int causal_rows, const float* x, fl
 // cudnnSoftmaxBackward applies on SharpNet's GPU path (Prod/GPU/GpuTensor.cs:445-490).  dx may equal dy.
 static __global__ void __launch_bounds__(256)
 softmax_bwd_kernel(long long rows, int cols, const float* dy, const float* __restrict__ y, float* dx) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -293,6 +304,7 @@ template <int VEC>
 static __global__ void sgd_update_kernel(long long n, float lr, float momentum, int nesterov,
                                          const float* __restrict__ dW, float* __restrict__ W,
                                          float* __restrict__ velocity) {
+  pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -333,6 +345,7 @@ template <int VEC>
 static __global__ void adam_update_kernel(long long n, float beta1, float beta2, float eps, float weight_decay,
                                           float factor, const float* __restrict__ dW, float* __restrict__ W,
                                           float* __restrict__ vW, float* __restrict__ sW) {
+  pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;

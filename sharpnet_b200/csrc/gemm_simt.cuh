@@ -28,6 +28,7 @@ struct SimtParams {
 
 __global__ void __launch_bounds__(kSimtThreads)
 simt_gemm_kernel(const SimtParams p) {
+  pdl_prologue();
   __shared__ float As[kSimtBK][kSimtBM + 4];
   __shared__ float Bs[kSimtBK][kSimtBN + 4];
   const int tid = threadIdx.x;
@@ -121,6 +122,7 @@ constexpr int kSimtBigBM = 128, kSimtBigBN = 128, kSimtBigBK = 8;
 
 __global__ void __launch_bounds__(kSimtThreads, 2)
 simt_gemm_big_kernel(const SimtParams p) {
+  pdl_prologue();
   __shared__ float As[2][kSimtBigBK][kSimtBigBM + 4];
   __shared__ float Bs[2][kSimtBigBK][kSimtBigBN + 4];
   const int tid = threadIdx.x;

@@ -671,6 +671,7 @@ struct SplitKReduceParams {
   OutMap omap;
 };
 static __global__ void splitk_reduce_kernel(const SplitKReduceParams p) {
+  pdl_prologue();
   const long long per_batch = static_cast<long long>(p.M) * p.N;
   const long long total = per_batch * p.batch;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -695,6 +696,7 @@ static __global__ void splitk_reduce_kernel(const SplitKReduceParams p) {
 // through shared memory so that both the partial reads (m fastest) and the C accesses (n fastest) are
 // coalesced.  Block = 32 x 8 threads; grid = (ceil(N/32), ceil(M/32), batch).
 static __global__ void __launch_bounds__(256) splitk_reduce_transposed_kernel(const SplitKReduceParams p) {
+  pdl_prologue();
   __shared__ float tile[32][33];
   const int n0 = blockIdx.x * 32, m0 = blockIdx.y * 32, b = blockIdx.z;
   const long long per_batch = static_cast<long long>(p.M) * p.N;
@@ -744,6 +746,7 @@ struct TailReduceParams {
   OutMap omap;
 };
 static __global__ void __launch_bounds__(256) tail_reduce_kernel(const TailReduceParams p) {
+  pdl_prologue();
   int b, tm, tn;
   tile_coords(p.whole_tiles + blockIdx.x, p.tiles_m, p.tiles_n, b, tm, tn);
   const int r0 = blockIdx.y * p.rows_per_block;

@@ -107,14 +107,6 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 }
 
 // ---------------------------------------------------------------- TMA
-// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may
-// start while the kernel before it in the stream is still running; grid_dependency_wait() returns once that
-// kernel has completed and its memory operations are visible, and must come before the first access to global
-// memory.  allow_dependent_launch() lets the next such kernel be scheduled as soon as every CTA of this grid
-// has started; it does not weaken what that kernel's own wait guarantees.
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
@@ -127,7 +119,6 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-
 // ---------------------------------------------------------------- TMEM / tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)),

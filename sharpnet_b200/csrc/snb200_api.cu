@@ -184,6 +184,25 @@ extern "C" int snb200_check_device_status(snb200_handle_t h) {
   return 0;
 }
 
+// Launch of one of this library's kernels on the handle's stream with programmatic dependent launch: every kernel
+// here starts with pdl_prologue() (or, for the tensor-core kernels, runs its set-up first), so its launch latency
+// overlaps the tail of the previous kernel and it waits for that kernel before touching memory.
+template <typename... KArgs, typename... Args>
+static void launch_pdl(snb200_handle_t h, void (*kernel)(KArgs...), dim3 grid, dim3 block, Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = h->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = h->tune[TUNE_PDL] == 1 ? 0 : 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in check_launch (cudaGetLastError)
+}
+
 // ------------------------------------------------------------------------------------ GEMM
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -464,9 +483,9 @@ static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
   if (blocks > 0x7fffffffLL) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "too many tiles for one launch");
   note_kernel(h, big ? "simt_fp32_128x128" : "simt_fp32_64x64", 1);
   if (big)
-    simt_gemm_big_kernel<<<static_cast<unsigned>(blocks), kSimtThreads, 0, h->stream>>>(p);
+    launch_pdl(h, simt_gemm_big_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kSimtThreads), p);
   else
-    simt_gemm_kernel<<<static_cast<unsigned>(blocks), kSimtThreads, 0, h->stream>>>(p);
+    launch_pdl(h, simt_gemm_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kSimtThreads), p);
   return check_launch(h, "simt_gemm_kernel launch");
 }
 
@@ -557,7 +576,7 @@ static int launch_tail_reduce(snb200_handle_t h, const GemmProblem& g, const Spl
   r.vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (g.batch == 1 || g.strideC % 4 == 0) &&
              (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias)) && omap_vec(g.omap);
   dim3 grid(plan.tail, tile_rows / r.rows_per_block);
-  tail_reduce_kernel<<<grid, 256, 0, h->stream>>>(r);
+  launch_pdl(h, tail_reduce_kernel, grid, dim3(256), r);
   h->launches += 1;
   return check_launch(h, "tail_reduce_kernel launch");
 }
@@ -575,9 +594,9 @@ static int launch_reduce(snb200_handle_t h, const GemmProblem& g, int parts, int
   if (blocks > 8LL * h->sm_count) blocks = 8LL * h->sm_count;
   if (transposed && g.batch <= 65535 && (g.M + 31) / 32 <= 65535) {
     dim3 grid((g.N + 31) / 32, (g.M + 31) / 32, g.batch);
-    splitk_reduce_transposed_kernel<<<grid, 256, 0, h->stream>>>(r);
+    launch_pdl(h, splitk_reduce_transposed_kernel, grid, dim3(256), r);
   } else {
-    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, h->stream>>>(r);
+    launch_pdl(h, splitk_reduce_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), r);
   }
   h->launches += 1;
   return check_launch(h, "splitk_reduce_kernel launch");
@@ -792,12 +811,12 @@ static int launch_colsum(snb200_handle_t h, int M, int N, int act, const float* 
   float* out = db ? (slabs == 1 ? db : h->workspace) : nullptr;
   dim3 grid(col_blocks, slabs);
   if (vec)
-    colsum_slab_kernel<4, FUSE><<<grid, 256, 0, h->stream>>>(M, N, rows_per_slab, act, dy, y, z, dz, out, scale);
+    launch_pdl(h, colsum_slab_kernel<4, FUSE>, grid, dim3(256), M, N, rows_per_slab, act, dy, y, z, dz, out, scale);
   else
-    colsum_slab_kernel<1, FUSE><<<grid, 256, 0, h->stream>>>(M, N, rows_per_slab, act, dy, y, z, dz, out, scale);
+    launch_pdl(h, colsum_slab_kernel<1, FUSE>, grid, dim3(256), M, N, rows_per_slab, act, dy, y, z, dz, out, scale);
   int launches = 1;
   if (db && slabs > 1) {
-    colsum_finish_kernel<<<(N + 255) / 256, 256, 0, h->stream>>>(N, slabs, h->workspace, db);
+    launch_pdl(h, colsum_finish_kernel, dim3((N + 255) / 256), dim3(256), N, slabs, h->workspace, db);
     ++launches;
   }
   note_kernel(h, FUSE ? "dz_db_colsum" : "colsum", launches);
@@ -864,9 +883,9 @@ extern "C" int snb200_loss_gradient(snb200_handle_t h, int loss, int rows, int c
   if (n == 0) return 0;
   if (!yExpected || !yPredicted || !dy) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (aligned16(yExpected) && aligned16(yPredicted) && aligned16(dy))
-    loss_gradient_kernel<4><<<ew_grid(h, n / 4 + 1, 256), 256, 0, h->stream>>>(n, scale, yExpected, yPredicted, dy);
+    launch_pdl(h, loss_gradient_kernel<4>, dim3(ew_grid(h, n / 4 + 1, 256)), dim3(256), n, scale, yExpected, yPredicted, dy);
   else
-    loss_gradient_kernel<1><<<ew_grid(h, n, 256), 256, 0, h->stream>>>(n, scale, yExpected, yPredicted, dy);
+    launch_pdl(h, loss_gradient_kernel<1>, dim3(ew_grid(h, n, 256)), dim3(256), n, scale, yExpected, yPredicted, dy);
   note_kernel(h, "loss_gradient", 1);
   return check_launch(h, "loss_gradient launch");
 }
@@ -939,10 +958,10 @@ extern "C" int snb200_bias_add(snb200_handle_t h, int M, int N, const float* bia
   if (!bias || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   const long long total = static_cast<long long>(M) * N;
   if (N % 4 == 0 && aligned16(bias) && aligned16(y))
-    bias_add_vec4_kernel<<<ew_grid(h, total / 4, 256), 256, 0, h->stream>>>(
+    launch_pdl(h, bias_add_vec4_kernel, dim3(ew_grid(h, total / 4, 256)), dim3(256), 
         total / 4, N / 4, reinterpret_cast<const float4*>(bias), reinterpret_cast<float4*>(y));
   else
-    bias_add_kernel<<<ew_grid(h, total, 256), 256, 0, h->stream>>>(total, N, bias, y);
+    launch_pdl(h, bias_add_kernel, dim3(ew_grid(h, total, 256)), dim3(256), total, N, bias, y);
   note_kernel(h, "bias_add", 1);
   return check_launch(h, "bias_add launch");
 }
@@ -968,9 +987,9 @@ extern "C" int snb200_activation_fwd(snb200_handle_t h, int act, long long count
   if (count == 0) return 0;
   if (!x || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (aligned16(x) && aligned16(y))
-    activation_fwd_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(act, count, x, y);
+    launch_pdl(h, activation_fwd_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), act, count, x, y);
   else
-    activation_fwd_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(act, count, x, y);
+    launch_pdl(h, activation_fwd_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), act, count, x, y);
   note_kernel(h, "activation_fwd", 1);
   return check_launch(h, "activation_fwd launch");
 }
@@ -985,9 +1004,9 @@ extern "C" int snb200_activation_bwd(snb200_handle_t h, int act, long long count
   if (!dy || !dx || (act != ACT_IDENTITY && !y) || (act == ACT_SWISH && !x))
     return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (aligned16(dy) && aligned16(dx) && (!x || aligned16(x)) && (!y || aligned16(y)))
-    activation_bwd_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(act, count, dy, x, y, dx);
+    launch_pdl(h, activation_bwd_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), act, count, dy, x, y, dx);
   else
-    activation_bwd_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(act, count, dy, x, y, dx);
+    launch_pdl(h, activation_bwd_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), act, count, dy, x, y, dx);
   note_kernel(h, "activation_bwd", 1);
   return check_launch(h, "activation_bwd launch");
 }
@@ -999,9 +1018,9 @@ extern "C" int snb200_axpy(snb200_handle_t h, long long count, float alpha, cons
   if (count == 0) return 0;
   if (!x || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (aligned16(x) && aligned16(y))
-    axpy_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(count, alpha, x, y);
+    launch_pdl(h, axpy_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), count, alpha, x, y);
   else
-    axpy_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, alpha, x, y);
+    launch_pdl(h, axpy_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), count, alpha, x, y);
   note_kernel(h, "axpy", 1);
   return check_launch(h, "axpy launch");
 }
@@ -1016,9 +1035,9 @@ extern "C" int snb200_transpose_second_third(snb200_handle_t h, int A, int B, in
   if (!src || !dst) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (src == dst) return fail(h, SNB200_STATUS_INVALID_VALUE, "the permutation is not done in place");
   if (D % 4 == 0 && aligned16(src) && aligned16(dst))
-    transpose_second_third_kernel<4><<<ew_grid(h, total / 4, 256), 256, 0, h->stream>>>(total / 4, B, C, D / 4, src, dst);
+    launch_pdl(h, transpose_second_third_kernel<4>, dim3(ew_grid(h, total / 4, 256)), dim3(256), total / 4, B, C, D / 4, src, dst);
   else
-    transpose_second_third_kernel<1><<<ew_grid(h, total, 256), 256, 0, h->stream>>>(total, B, C, D, src, dst);
+    launch_pdl(h, transpose_second_third_kernel<1>, dim3(ew_grid(h, total, 256)), dim3(256), total, B, C, D, src, dst);
   note_kernel(h, "transpose_second_third", 1);
   return check_launch(h, "transpose_second_third launch");
 }
@@ -1031,10 +1050,10 @@ extern "C" int snb200_sgd_update(snb200_handle_t h, long long count, float learn
   if (count == 0) return 0;
   if (!dW || !W) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (aligned16(dW) && aligned16(W) && (!velocity || aligned16(velocity)))
-    sgd_update_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(count, learning_rate, momentum,
+    launch_pdl(h, sgd_update_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), count, learning_rate, momentum,
                                                                                nesterov ? 1 : 0, dW, W, velocity);
   else
-    sgd_update_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, learning_rate, momentum,
+    launch_pdl(h, sgd_update_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), count, learning_rate, momentum,
                                                                        nesterov ? 1 : 0, dW, W, velocity);
   note_kernel(h, "sgd_update", 1);
   return check_launch(h, "sgd_update launch");
@@ -1053,10 +1072,10 @@ extern "C" int snb200_adam_update(snb200_handle_t h, long long count, double lea
   const float b1 = static_cast<float>(beta1), b2 = static_cast<float>(beta2), ep = static_cast<float>(epsilon);
   const float wd = static_cast<float>(weight_decay), fc = static_cast<float>(factor);
   if (aligned16(dW) && aligned16(W) && aligned16(adam_vW) && aligned16(adam_sW))
-    adam_update_kernel<4><<<ew_grid(h, count / 4 + 1, 256), 256, 0, h->stream>>>(count, b1, b2, ep, wd, fc, dW, W, adam_vW,
+    launch_pdl(h, adam_update_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), count, b1, b2, ep, wd, fc, dW, W, adam_vW,
                                                                                 adam_sW);
   else
-    adam_update_kernel<1><<<ew_grid(h, count, 256), 256, 0, h->stream>>>(count, b1, b2, ep, wd, fc, dW, W, adam_vW, adam_sW);
+    launch_pdl(h, adam_update_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), count, b1, b2, ep, wd, fc, dW, W, adam_vW, adam_sW);
   note_kernel(h, "adam_update", 1);
   return check_launch(h, "adam_update launch");
 }
@@ -1067,11 +1086,11 @@ static int launch_softmax_fwd(snb200_handle_t h, long long rows, int cols, int c
   const long long cap = 16LL * h->sm_count;
   if (blocks > cap) blocks = cap;
   const unsigned g = static_cast<unsigned>(blocks < 1 ? 1 : blocks);
-  if (cols <= 128) softmax_fwd_kernel<4><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
-  else if (cols <= 256) softmax_fwd_kernel<8><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
-  else if (cols <= 512) softmax_fwd_kernel<16><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
-  else if (cols <= 1024) softmax_fwd_kernel<32><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
-  else softmax_fwd_kernel<0><<<g, 256, 0, h->stream>>>(rows, cols, causal_rows, x, y);
+  if (cols <= 128) launch_pdl(h, softmax_fwd_kernel<4>, dim3(g), dim3(256), rows, cols, causal_rows, x, y);
+  else if (cols <= 256) launch_pdl(h, softmax_fwd_kernel<8>, dim3(g), dim3(256), rows, cols, causal_rows, x, y);
+  else if (cols <= 512) launch_pdl(h, softmax_fwd_kernel<16>, dim3(g), dim3(256), rows, cols, causal_rows, x, y);
+  else if (cols <= 1024) launch_pdl(h, softmax_fwd_kernel<32>, dim3(g), dim3(256), rows, cols, causal_rows, x, y);
+  else launch_pdl(h, softmax_fwd_kernel<0>, dim3(g), dim3(256), rows, cols, causal_rows, x, y);
   note_kernel(h, "softmax_fwd", 1);
   return check_launch(h, "softmax_fwd launch");
 }
@@ -1079,7 +1098,7 @@ static int launch_softmax_bwd(snb200_handle_t h, long long rows, int cols, const
   long long blocks = (rows + 7) / 8;
   const long long cap = 16LL * h->sm_count;
   if (blocks > cap) blocks = cap;
-  softmax_bwd_kernel<<<static_cast<unsigned>(blocks < 1 ? 1 : blocks), 256, 0, h->stream>>>(rows, cols, dy, y, dx);
+  launch_pdl(h, softmax_bwd_kernel, dim3(static_cast<unsigned>(blocks < 1 ? 1 : blocks)), dim3(256), rows, cols, dy, y, dx);
   note_kernel(h, "softmax_bwd", 1);
   return check_launch(h, "softmax_bwd launch");
 }
