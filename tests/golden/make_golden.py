@@ -12,9 +12,10 @@ Sources (paths inside the reference):
                                                  VanillaSGD ([in,out] weights)
   Tests/NonReg/TestNetworkPropagation.cs:500-575 attention block: predictions before training, plain and causal
   Tests/NonReg/TestNetworkPropagation.cs:580-623 MultiHeadAttention (3 heads x 5, [in,out] weights): predictions before
-                                                 training, plain and causal
+                                                 training and after 10 epochs of SGD with momentum, plain and causal
   Tests/NonReg/ParallelRunWithPyTorch.cs:1013-1129 MultiHeadAttention (3 heads x 2, [out,in] weights), with and without
                                                  bias, plain and causal: CategoricalCrossentropy loss before training
+                                                 and after 10 epochs of SGD with momentum in batches of 2
   Tests/NonReg/ParallelRunWithPyTorch.cs:102-138 Linear(5->3, last-dim flatten)+ReLU+Flatten+Linear(36->3), Mse
   Tests/NonReg/ParallelRunWithPyTorch.cs:179-214 Linear(16->3)+ReLU+Linear(3->3)+Sigmoid, BCE ([out,in] weights)
 """
@@ -122,7 +123,8 @@ def main(ref):
         "conv_q": _numbers(convs[0]), "conv_k": _numbers(convs[1]), "conv_v": _numbers(convs[2]),     # [7 in, 2 out]
         "w_q": _numbers(lits[0]), "w_k": _numbers(lits[1]), "w_v": _numbers(lits[2]),                 # [15 in, 3 x 5 out]
         "w_o": _numbers(lits[3]), "w_linear": _numbers(lits[4]),                                      # [15, 15], [30, 3]
-        "cases": [{"use_bias": c[0] == "true", "causal": c[2] == "true", "pred_before": _numbers(c[3])}
+        "cases": [{"use_bias": c[0] == "true", "causal": c[2] == "true", "pred_before": _numbers(c[3]),
+                   "pred_after": _numbers(c[4])}     # after 10 epochs of SGD (lr 0.01, momentum 0.9), one batch of 3
                   for c in re.findall(r'\[TestCase\((\w+), (\w+), (\w+), "(.*?)", "(.*?)"\)', head)],
     }
 

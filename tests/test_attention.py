@@ -325,3 +325,153 @@ def test_gpu_multihead_attention_argument_errors(wrapper):
     assert "embed_dim" in lib.snb200_last_error_string(h).decode()
     assert lib.snb200_mha_fwd(h, desc, _capi.MhaWeights(), None, None, None, _capi.MhaState(), None, None) == 7
     assert lib.snb200_mha_fwd(h, None, None, None, None, None, None, None, None) == 7
+
+
+# ------------------------------------------------------------------------------------------ training replays
+# The reference's multi-head goldens after training pin the backward pass (dQ, dK, dV, weight and bias gradients)
+# and the momentum update: Tests/NonReg/TestNetworkPropagation.cs:580-623 (Keras layout, one batch of 3, SGD lr 0.01,
+# momentum 0.9, 10 epochs, predictions at 1e-6) and Tests/NonReg/ParallelRunWithPyTorch.cs:1013-1129 (PyTorch layout,
+# batches of 2 in order, lr 0.1, momentum 0.9, 10 epochs, CategoricalCrossentropy loss at 1e-6).
+# Network: X -> three Conv1D(kernel 1, 2 filters, with bias) -> MultiHeadAttention -> Flatten -> Linear(3, with
+# bias) -> Softmax.  The convolutions are not on the path: they run on the host in float64 in both replays.
+class _MhaNet:
+    def __init__(self, golden, key, case, use_bias):
+        g = golden[key]
+        self.tf = key == "mha_tf"
+        self.causal, self.use_bias = case["causal"], use_bias
+        if self.tf:
+            self.B, self.C, self.L, self.H, self.kd, self.batch, self.lr = 3, 7, 15, 3, 5, 3, 0.01
+            self.layout = W_IN_OUT
+            self.conv_w = [np.asarray(g[k], np.float64).reshape(7, 2).T.copy() for k in ("conv_q", "conv_k", "conv_v")]
+            self.mha_w = [np.asarray(g[k], np.float64).reshape(15, 15) for k in ("w_q", "w_k", "w_v", "w_o")]
+            self.lin_w = np.asarray(g["w_linear"], np.float64).reshape(30, 3)            # [in, out]
+        else:
+            self.B, self.C, self.L, self.H, self.kd, self.batch, self.lr = 10, 2, 6, 3, 2, 2, 0.1
+            self.layout = W_OUT_IN
+            self.conv_w = [np.asarray(g[k], np.float64).reshape(2, 2) for k in ("conv_q", "conv_k", "conv_v")]
+            inw = np.asarray(g["in_proj_weight"], np.float64).reshape(18, 6)
+            self.mha_w = [inw[:6].copy(), inw[6:12].copy(), inw[12:].copy(),
+                          np.asarray(g["out_proj_weight"], np.float64).reshape(6, 6)]
+            self.lin_w = np.asarray(g["w_linear"], np.float64).reshape(3, 12)            # [out, in]
+        self.E = self.H * self.kd
+        self.conv_b = [np.zeros(2) for _ in range(3)]
+        self.mha_b = [np.zeros(self.E) for _ in range(4)] if use_bias else None
+        self.lin_b = np.zeros(3)
+        self.X = orc.numpy_array_for_tests(self.B, self.C, self.L).astype(np.float64)
+        self.Y = orc.y_numpy_array_for_tests(self.B, 3).astype(np.float64)
+        self.momentum = 0.9
+
+    def conv_forward(self, Xb):
+        return [np.stack([w @ x + b[:, None] for x in Xb]) for w, b in zip(self.conv_w, self.conv_b)]   # [n, 2, L] each
+
+    def conv_gradients(self, Xb, dQKV):
+        return ([sum(d[i] @ Xb[i].T for i in range(len(Xb))) for d in dQKV], [d.sum((0, 2)) for d in dQKV])
+
+    def linear(self, flat):
+        return flat @ (self.lin_w if self.tf else self.lin_w.T) + self.lin_b
+
+    def batches(self):
+        return [slice(s, s + self.batch) for s in range(0, self.B, self.batch)]
+
+
+def _sgd_momentum(params, grads, velocities, lr, momentum):
+    for p, g, v in zip(params, grads, velocities):
+        v[...] = momentum * v - lr * g            # Prod/Optimizers/Sgd.cs:43-52, Prod/CPU/CpuTensor.cs:470-489
+        p += v
+
+
+def _train_with_oracle(net):
+    params = net.conv_w + net.conv_b + net.mha_w + (net.mha_b or []) + [net.lin_w, net.lin_b]
+    vel = [np.zeros_like(p) for p in params]
+
+    def forward(Xb):
+        Q, K, V = net.conv_forward(Xb)
+        y, cache = orc.multihead_attention_forward(Q, K, V, net.mha_w, net.mha_b, net.H, net.kd, net.kd, net.causal,
+                                                   net.layout, f64=True)
+        flat = y.reshape(len(Xb), -1)
+        return (Q, K, V), cache, flat, _softmax64(net.linear(flat))
+    for _ in range(10):
+        for sl in net.batches():
+            Xb, Yb = net.X[sl], net.Y[sl]
+            (Q, K, V), cache, flat, p = forward(Xb)
+            dz = p - Yb                                                       # softmax + CategoricalCrossentropy
+            d_lin_w = flat.T @ dz if net.tf else dz.T @ flat
+            dflat = dz @ (net.lin_w.T if net.tf else net.lin_w)
+            dQ, dK, dV, dws, dbs = orc.multihead_attention_backward(Q, K, V, dflat.reshape(len(Xb), 2, net.E), net.mha_w,
+                                                                    cache, net.H, net.kd, net.kd, 1.0, net.layout)
+            d_conv_w, d_conv_b = net.conv_gradients(Xb, (dQ, dK, dV))
+            grads = d_conv_w + d_conv_b + dws + (dbs if net.use_bias else []) + [d_lin_w, dz.sum(0)]
+            _sgd_momentum(params, grads, vel, net.lr / len(Xb), net.momentum)   # PonderedLearning, Optimizer.cs:26-29
+    return forward(net.X)[3]
+
+
+def _all_training_cases(golden):
+    for case in golden["mha_tf"]["cases"]:
+        yield "mha_tf", case, case["use_bias"]
+    for name in ("no_bias", "with_bias"):
+        for case in golden["mha_pt_" + name]["cases"]:
+            yield "mha_pt_" + name, case, name == "with_bias"
+
+
+def _check_after_training(net, case, p):
+    if net.tf:
+        np.testing.assert_allclose(p.ravel(), case["pred_after"], rtol=0, atol=1e-6)
+    else:
+        assert abs(float(-(net.Y * np.log(p)).sum(1).mean()) - case["loss_after"]) <= 1e-6
+
+
+def test_oracle_multihead_attention_training_matches_reference_goldens(golden):
+    for key, case, use_bias in _all_training_cases(golden):
+        net = _MhaNet(golden, key, case, use_bias)
+        _check_after_training(net, case, _train_with_oracle(net))
+
+
+@pytest.mark.gpu
+def test_gpu_multihead_attention_training_matches_reference_goldens(wrapper, golden):
+    # the same replays with the attention layer, the output Dense layer, the loss gradient and the momentum updates on
+    # the device through the C ABI (snb200_mha_fwd / _bwd, snb200_dense_fwd, snb200_softmax_fwd,
+    # snb200_dense_bwd_from_loss, snb200_sgd_update)
+    from sharpnet_b200._capi import ACT_IDENTITY, LOSS_CATEGORICAL_CROSSENTROPY
+    from sharpnet_b200.attention import MultiheadAttention
+    from sharpnet_b200.linear import FusedDenseBackwardFromLoss, FusedDenseForward
+    from sharpnet_b200.tensor import GPUTensor
+    T = lambda a: GPUTensor(np.shape(a), np.asarray(a, np.float32), wrapper)  # noqa: E731
+    for key, case, use_bias in _all_training_cases(golden):
+        net = _MhaNet(golden, key, case, use_bias)
+        layer = MultiheadAttention(net.H, net.kd, net.kd, use_bias, use_bias, net.causal, net.E, wrapper, net.layout)
+        flat_w = np.concatenate([w.ravel() for w in net.mha_w]).astype(np.float32)
+        layer.Weights.storage[: flat_w.size].copy_(T(flat_w).storage)
+        lin_w, lin_b = T(net.lin_w), T(net.lin_b)
+        vel = {id(t): GPUTensor(t.Shape, None, wrapper) for t in (layer.Weights, layer.Bias, lin_w, lin_b) if t is not None}
+        d_lin_w, d_lin_b = GPUTensor(lin_w.Shape, None, wrapper), GPUTensor((3,), None, wrapper)
+        conv_params = net.conv_w + net.conv_b
+        conv_vel = [np.zeros_like(p) for p in conv_params]
+
+        def forward(Xb, keep):
+            n = len(Xb)
+            Q, K, V = (T(a) for a in net.conv_forward(Xb))
+            y = GPUTensor((n, 2, net.E), None, wrapper)
+            layer.ForwardPropagation([Q, K, V], y, keep)
+            flat = y.Reshape(n, 2 * net.E)
+            logits, p = GPUTensor((n, 3), None, wrapper), GPUTensor((n, 3), None, wrapper)
+            FusedDenseForward(logits, flat, lin_w, lin_b, ACT_IDENTITY, None, net.layout)
+            logits.SoftmaxLastDimension(p)
+            return (Q, K, V), flat, p
+        for _ in range(10):
+            for sl in net.batches():
+                Xb, n = net.X[sl], net.batch
+                (Q, K, V), flat, p = forward(Xb, True)
+                dflat, dz = GPUTensor((n, 2 * net.E), None, wrapper), GPUTensor((n, 3), None, wrapper)
+                FusedDenseBackwardFromLoss(dflat, d_lin_w, d_lin_b, flat, T(net.Y[sl]), p, lin_w, LOSS_CATEGORICAL_CROSSENTROPY,
+                                           1.0, dz, net.layout)
+                dX = [GPUTensor((n, 2, net.E), None, wrapper) for _ in range(3)]
+                layer.BackwardPropagation([Q, K, V], dflat.Reshape(n, 2, net.E), dX, 1.0)
+                d_conv_w, d_conv_b = net.conv_gradients(Xb, [t.ContentAsFloatArray().astype(np.float64) for t in dX])
+                _sgd_momentum(conv_params, d_conv_w + d_conv_b, conv_vel, net.lr / n, net.momentum)
+                for W, dW in ((layer.Weights, layer.WeightGradients), (layer.Bias, layer.BiasGradients), (lin_w, d_lin_w),
+                              (lin_b, d_lin_b)):
+                    if W is not None:
+                        W.UpdateSGDOptimizer(net.lr / n, net.momentum, False, dW, vel[id(W)])
+        wrapper.check_device_status()
+        p = forward(net.X, False)[2].ContentAsFloatArray().astype(np.float64)
+        _check_after_training(net, case, p)
