@@ -635,7 +635,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape table (N = 1 only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--case", default=None, choices=["gemm"],
+    ap.add_argument("--case", default=None, choices=["gemm", "sdpa"],
                     help="time a single Dot shape instead of the training step (used for profiling)")
     ap.add_argument("--mnk", type=int, nargs=3, default=[4096, 4096, 4096])
     ap.add_argument("--trans", default="NN", help="NN, NT, TN or TT")
@@ -658,6 +658,37 @@ def main():
         r = time_gemm_shape(GPUWrapper.FromDeviceId(0), torch, _peaks(), "case", M, N, K, args.trans[0] == "T",
                             args.trans[1] == "T", args.beta, args.batch, -1.0, 1.0, args.math, min_calls=args.calls)
         _emit(json.dumps(r))
+    elif args.case == "sdpa":
+        # one attention core, forward + backward: --batch heads, --mnk q_steps v_steps head_dim
+        import ctypes
+        import torch
+        from sharpnet_b200.tensor import GPUWrapper
+        w = GPUWrapper.FromDeviceId(0)
+        w.set_math_mode(args.math)
+        B, (Tq, Tk, E) = args.batch, args.mnk
+        new = lambda *shape: torch.empty(*shape, dtype=torch.float32, device=w.device).uniform_(-1, 1)  # noqa: E731
+        P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        Q, dy, y, dQ = (new(B, Tq, E) for _ in range(4))
+        K, V, dK, dV = (new(B, Tk, E) for _ in range(4))
+        wts, ds = new(B, Tq, Tk), new(B, Tq, Tk)
+
+        def both():
+            st = w.lib.snb200_sdpa_fwd(w.handle, B, Tq, Tk, E, 1, 1, P(Q), P(K), P(V), P(wts), P(y))
+            return st or w.lib.snb200_sdpa_bwd(w.handle, B, Tq, Tk, E, 1, P(Q), P(K), P(V), P(dy), P(wts), P(ds), P(dQ),
+                                               P(dK), P(dV))
+        for _ in range(3):
+            if both() != 0:
+                raise RuntimeError(w.lib.snb200_last_error_string(w.handle))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.calls):
+            both()
+        e1.record()
+        torch.cuda.synchronize()
+        w.check_device_status()
+        _emit(json.dumps({"shape": f"sdpa fwd+bwd {B} x [{Tq} x {Tk} x {E}] causal", "calls": args.calls,
+                          "ms": round(e0.elapsed_time(e1) / args.calls, 4)}))
     elif args.impl == "reference":
         run_reference(args)
     else:
