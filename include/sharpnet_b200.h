@@ -220,7 +220,8 @@ int snb200_softmax_bwd(snb200_handle_t handle, long long rows, int cols, const f
  * weights = softmax(mask(scaling * Q K^T)), y = weights V, scaling = use_scale ? 1/sqrt(E) : 1.
  * Replaces ScaledDotProductAttentionLayer.ScaledDotProductAttentionForwardPropagation
  * (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-91): two strided-batched GEMMs with, between them, the
- * causal overwrite (SetAllElementsAboveMainDiagonal, -1e12) and the softmax as ONE in-place pass over
+ * causal overwrite (SetAllElementsAboveMainDiagonal, -1e12) and the softmax applied where the scores are stored
+ * (v_steps <= 256) or as ONE in-place pass over
  * `weights` [batch, q_steps, v_steps] (caller-provided; the layer's _weights_buffer, kept for the backward).
  * The separate scores buffer of the reference is not needed. */
 int snb200_sdpa_fwd(snb200_handle_t handle, int batch, int q_steps, int v_steps, int embedding_dim, int use_scale,

@@ -26,7 +26,9 @@ namespace snb {
 constexpr int kUmmaBM = 128;
 constexpr int kUmmaK = 8;  // K extent of one kind::tf32 instruction
 
-template <int BN_, int BK_, bool SPLIT_>
+// GROUPS_ = 0 picks the number of epilogue warp groups from the tile width; the row-operation kernels ask for 2 so
+// that two warps share every row (see epilogue_row_op).
+template <int BN_, int BK_, bool SPLIT_, int GROUPS_ = 0>
 struct UmmaTile {
   static constexpr int BM = kUmmaBM;
   static constexpr int BN = BN_;
@@ -44,7 +46,7 @@ struct UmmaTile {
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; power of two
   // Warps are grouped in fours so that setmaxnreg can move registers between the roles:
   //   group 0: TMA producer, MMA issuer (two idle warps); then the epilogue groups; then the split group.
-  static constexpr int EPI_GROUPS = (BN > 128) ? 2 : 1;             // each epilogue warp owns <= 128 columns
+  static constexpr int EPI_GROUPS = GROUPS_ ? GROUPS_ : ((BN > 128) ? 2 : 1);   // each epilogue warp owns <= 128 columns
   static constexpr int EPI_THREADS = 128 * EPI_GROUPS;
   static constexpr int EPI_COLS = BN / EPI_GROUPS;                  // columns per epilogue warp
   static constexpr int SMEM_BYTES = RING_BYTES + EPI_STAGE_BYTES * 4 * EPI_GROUPS + 1024;  // + 1 KB alignment slack
@@ -315,51 +317,80 @@ __device__ __forceinline__ bool epilogue_fold_c(const UmmaParams& p, float (&acc
   return true;
 }
 
-// Row operation of the attention products, on the NC = BN <= 128 columns of the output row this lane holds
-// (the whole row: the launcher guarantees one tile column and N a multiple of 4 with 16-byte aligned rows).
-// On return acc holds the values to store as they are.
+// Row operation of the attention products.  The launcher guarantees one tile column, so an output row lies in this
+// tile: in one lane's NC registers (GROUPS = 1), or split between the two warps that read the same TMEM lanes
+// (GROUPS = 2: warp 4 + q holds columns [0, NC), warp 8 + q columns [NC, 2 NC)); those two exchange the row maximum
+// and the row sum through shared memory (`xch`, [2][128] floats: one slot per group and row) and meet at the named
+// barrier 1 + q, once before a slot is overwritten and once before it is read.  Two warps per row halve the serial work of a lane and give every scheduler a second warp to
+// hide latencies with.  Rows are 16-byte aligned and N is a multiple of 4.  On return acc holds the values to store.
 //   ROW_SOFTMAX       acc = softmax(mask(alpha * acc)) over the N valid columns: the causal overwrite with -1e12
 //                     (Prod/CPU/CpuTensor.cs:3037-3052) and CpuTensorActivationFunctions.Softmax (:19-46).
-//                     One thread owns a whole row here, so the exponential is the hardware's ex2 (relative error
-//                     2^-22) and the division a multiplication by the reciprocal of the row sum.
+//                     The exponential is the hardware's ex2 (relative error 2^-22) and the division a multiplication
+//                     by the reciprocal of the row sum; maximum and sum run as four independent chains.
 //   ROW_SOFTMAX_GRAD  acc = y * (g - sum_j g_j * y_j) with g = alpha * acc, y = aux row: the softmax Jacobian
 //                     cudnnSoftmaxBackward applies (Prod/GPU/GpuTensor.cs:445-490)
-template <int NC>
-__device__ __forceinline__ void epilogue_row_op(const UmmaParams& p, float (&acc)[NC], float* stage, int b, int row_base,
-                                                int lane) {
-  const int ncols = p.N < NC ? p.N : NC;
+__device__ __forceinline__ void row_pair_barrier(int q) { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); }
+
+// This lane's value against the value of the lane that holds the other half of the row.
+__device__ __forceinline__ float row_pair_exchange(float* xch, int q, int group, int lane, float mine) {
+  row_pair_barrier(q);                       // the partner has read what the slot held before
+  xch[group * 128 + q * 32 + lane] = mine;
+  row_pair_barrier(q);
+  return xch[(group ^ 1) * 128 + q * 32 + lane];
+}
+
+template <int NC, int GROUPS>
+__device__ __forceinline__ void epilogue_row_op(const UmmaParams& p, float (&acc)[NC], float* stage, float* xch, int b,
+                                                int row_base, int col_base, int q, int group, int lane) {
+  const int ncols = max(0, min(NC, p.N - col_base));   // valid columns among this lane's NC
   const int row = row_base + lane;
   if (p.row_op == ROW_SOFTMAX) {
     const int limit = p.causal ? row : 0x7fffffff;   // columns > limit are masked
-    float mx = -3.402823466e38f;
+    float m4[4] = {-3.402823466e38f, -3.402823466e38f, -3.402823466e38f, -3.402823466e38f};
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
       float v = p.alpha * acc[j];
-      v = (j > limit) ? -1e12f : v;
+      v = (col_base + j > limit) ? -1e12f : v;
       v = (j < ncols) ? v : -3.402823466e38f;
       acc[j] = v;
-      mx = fmaxf(mx, v);
+      m4[j & 3] = fmaxf(m4[j & 3], v);
     }
-    float sum = 0.0f;
+    float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+    if (GROUPS == 2) mx = fmaxf(mx, row_pair_exchange(xch, q, group, lane, mx));
+    const float c = mx * 1.4426950408889634f;
+    float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
-      acc[j] = (j < ncols) ? __expf(acc[j] - mx) : 0.0f;
-      sum += acc[j];
+      float e;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fmaf(acc[j], 1.4426950408889634f, -c)));
+      e = (j < ncols) ? e : 0.0f;
+      acc[j] = e;
+      s4[j & 3] += e;
+    }
+    float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+    if (GROUPS == 2) {
+      const float other = row_pair_exchange(xch, q, group, lane, sum);
+      sum = group == 0 ? sum + other : other + sum;   // same order in both warps: identical results
     }
     const float inv = 1.0f / sum;
 #pragma unroll
     for (int j = 0; j < NC; ++j) acc[j] *= inv;
   } else {
-    const float* yb = p.aux + static_cast<long long>(b) * p.strideC + static_cast<long long>(row_base) * p.ldc;
+    const float* yb = p.aux + static_cast<long long>(b) * p.strideC + static_cast<long long>(row_base) * p.ldc + col_base;
     const int rows_valid = p.M - row_base;
-    float dot = 0.0f;
+    float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int g = 0; g < NC / 32; ++g) {
       if (g * 32 >= ncols) break;   // warp-uniform
       float y[32];
       epilogue_load_block(yb + g * 32, p.ldc, rows_valid, ncols - g * 32, stage, lane, y);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) dot = fmaf(p.alpha * acc[g * 32 + j], y[j], dot);
+      for (int j = 0; j < 32; ++j) d4[j & 3] = fmaf(p.alpha * acc[g * 32 + j], y[j], d4[j & 3]);
+    }
+    float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+    if (GROUPS == 2) {
+      const float other = row_pair_exchange(xch, q, group, lane, dot);
+      dot = group == 0 ? dot + other : other + dot;
     }
 #pragma unroll
     for (int g = 0; g < NC / 32; ++g) {
@@ -449,6 +480,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ uint64_t acc_empty_bar[2];    // partial sum moved to registers
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
+  __shared__ float row_xch[ROWOP ? 2 * 128 : 1];   // row maximum / sum exchange of the row operations
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -615,8 +647,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) break;
       float alpha = p.alpha;
-      if (ROWOP && T::EPI_GROUPS == 1) {   // this instantiation is launched for row operations only
-        epilogue_row_op<NC>(p, acc, stage, b, tm * BM + q * 32, lane);
+      if (ROWOP) {   // this instantiation is launched for row operations only
+        epilogue_row_op<NC, T::EPI_GROUPS>(p, acc, stage, row_xch, b, tm * BM + q * 32, col_base, q, (warp - 4) >> 2,
+                                           lane);
         alpha = 1.0f;                      // the row operation has consumed it
       }
       epilogue_store_unit<NC>(p, alpha, c_folded ? 0.0f : p.beta, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN,

@@ -659,19 +659,22 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
   if (g.row_op != ROW_NONE) {
     // whole rows in one tile of the single-CTA kernel, K never cut (the caller checked row_op_fits)
     SplitPlan none = {0, 0, 0, 0, 0, 0, 0, 0};
-    const int bn = g.N <= 32 ? 32 : g.N <= 64 ? 64 : 128;
+    const int bn = g.N <= 32 ? 32 : g.N <= 64 ? 64 : g.N <= 128 ? 128 : 256;
     char name[64];
     snprintf(name, sizeof(name), "umma_%s_128x%d_%s", split ? "3xtf32" : "tf32", bn,
              g.row_op == ROW_SOFTMAX ? "softmax" : "softmax_grad");
     note_kernel(h, name, 1);
+    // two epilogue warps per row (UmmaTile<..., 2>) except for the 32-wide tile
     if (split) {
       if (bn == 32) return launch_umma_t<UmmaTile<32, 32, true>, true>(h, g, none);
-      if (bn == 64) return launch_umma_t<UmmaTile<64, 32, true>, true>(h, g, none);
-      return launch_umma_t<UmmaTile<128, 32, true>, true>(h, g, none);
+      if (bn == 64) return launch_umma_t<UmmaTile<64, 32, true, 2>, true>(h, g, none);
+      if (bn == 128) return launch_umma_t<UmmaTile<128, 32, true, 2>, true>(h, g, none);
+      return launch_umma_t<UmmaTile<256, 32, true, 2>, true>(h, g, none);
     }
     if (bn == 32) return launch_umma_t<UmmaTile<32, 32, false>, true>(h, g, none);
-    if (bn == 64) return launch_umma_t<UmmaTile<64, 32, false>, true>(h, g, none);
-    return launch_umma_t<UmmaTile<128, 32, false>, true>(h, g, none);
+    if (bn == 64) return launch_umma_t<UmmaTile<64, 32, false, 2>, true>(h, g, none);
+    if (bn == 128) return launch_umma_t<UmmaTile<128, 32, false, 2>, true>(h, g, none);
+    return launch_umma_t<UmmaTile<256, 32, false, 2>, true>(h, g, none);
   }
   const int splitk_mode = h->tune[TUNE_SPLITK];   // 0 automatic, 1 never
   // Few rows (M <= 64): run the transposed problem C^T = op(B)^T * op(A)^T, so that the long N dimension
@@ -1132,11 +1135,11 @@ static void bmm_problem(GemmProblem* g, int batch, int M, int N, int K, int tA, 
 }
 
 // Can the product run on the tensor-core kernel with its whole rows in one tile, so that a row operation
-// (softmax, softmax gradient) can be applied where the product is stored?  Otherwise the caller runs the plain
+// (softmax, softmax gradient; rows of up to 256 columns) can be applied where the product is stored?  Otherwise the caller runs the plain
 // product and a separate row pass.
-static bool row_op_fits(const snb200_context* h, const GemmProblem& g) {
+static bool row_op_fits(const snb200_context* h, const GemmProblem& g, int max_cols) {
   if (h->math_mode == SNB200_MATH_FP32_SIMT || h->tune[TUNE_FORCE_PATH] == 2 || !tma_eligible(g)) return false;
-  if (g.N > 128 || g.N < 8 || g.M < 16) return false;
+  if (g.N > max_cols || g.N < 8 || g.M < 16) return false;
   // the row operation reads and writes whole float4s of 16-byte aligned rows
   if ((g.N & 3) || !aligned16(g.C) || (g.aux && !aligned16(g.aux)) || (g.batch > 1 && (g.strideC & 3))) return false;
   return static_cast<double>(g.M) * g.N * g.K * g.batch >= 64.0 * 64 * 64;
@@ -1167,7 +1170,7 @@ static int sdpa_fwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps,
   // scores = scaling * Q * K^T                       (ScaledDotProductAttentionLayer.cs:66-71)
   bmm_problem(&g, batch, Tq, Tk, E, 0, 1, Q, E, static_cast<long long>(Tq) * E, K, E, static_cast<long long>(Tk) * E,
               weights, scaling);
-  if (row_op_fits(h, g)) {
+  if (row_op_fits(h, g, 256)) {
     // causal mask + softmax over the last dimension where the scores are stored   (:73-81)
     g.row_op = ROW_SOFTMAX; g.causal = is_causal ? 1 : 0;
     st = run_gemm(h, g);
@@ -1223,7 +1226,7 @@ static int sdpa_bwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps,
   // gradient w.r.t. the weights, scaled: scaling * dy * V^T    (:119)
   bmm_problem(&g, batch, Tq, Tk, E, 0, 1, dy, E, sQ, V, E, sK, scores_grad_scratch, scaling);
   g.aux = weights;
-  if (row_op_fits(h, g)) {
+  if (row_op_fits(h, g, 128)) {   // measured: beyond 128 columns the 256-wide single-CTA tile loses to pair tiles + a pass
     // ... turned into the gradient w.r.t. the scores by the softmax Jacobian where it is stored    (:121)
     g.row_op = ROW_SOFTMAX_GRAD;
     st = run_gemm(h, g);
