@@ -46,7 +46,7 @@ struct UmmaTile {
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; power of two
   // Warps are grouped in fours so that setmaxnreg can move registers between the roles:
   //   group 0: TMA producer, MMA issuer (two idle warps); then the epilogue groups; then the split group.
-  static constexpr int EPI_GROUPS = GROUPS_ ? GROUPS_ : ((BN > 128) ? 2 : 1);   // each epilogue warp owns <= 128 columns
+  static constexpr int EPI_GROUPS = GROUPS_ ? GROUPS_ : ((BN >= 64) ? 2 : 1);   // each epilogue warp owns <= 128 columns
   static constexpr int EPI_THREADS = 128 * EPI_GROUPS;
   static constexpr int EPI_COLS = BN / EPI_GROUPS;                  // columns per epilogue warp
   static constexpr int SMEM_BYTES = RING_BYTES + EPI_STAGE_BYTES * 4 * EPI_GROUPS + 1024;  // + 1 KB alignment slack

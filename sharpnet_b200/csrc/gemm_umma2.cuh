@@ -38,7 +38,7 @@ struct Umma2Tile {
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int EPI_GROUPS = (BN > 128) ? 2 : 1;
+  static constexpr int EPI_GROUPS = (BN >= 64) ? 2 : 1;
   static constexpr int EPI_THREADS = 128 * EPI_GROUPS;
   static constexpr int EPI_COLS = BN / EPI_GROUPS;
   static constexpr int SMEM_BYTES = RING_BYTES + EPI_STAGE_BYTES * 4 * EPI_GROUPS + 1024;
