@@ -503,17 +503,17 @@ struct TileCost { double kblock_us, fixed_us; };
 static TileCost tile_cost(bool split3x, int pair, int bn, const GemmProblem& g) {
   const int i = bn == 256 ? 0 : bn == 128 ? 1 : bn == 64 ? 2 : 3;
   if (split3x) {   // the hi/lo split and three products per block hide the operand layout
-    static const TileCost single[4] = {{1.48, 15.5}, {0.81, 12.4}, {0.81, 9.4}, {0.69, 7.8}};
-    static const TileCost paired[4] = {{1.02, 14.8}, {0.805, 13.6}, {0.69, 11.2}, {0.69, 11.2}};
+    static const TileCost single[4] = {{1.46, 13.3}, {0.90, 8.5}, {0.81, 6.7}, {0.69, 5.7}};
+    static const TileCost paired[4] = {{1.00, 13.3}, {0.82, 9.4}, {0.72, 7.6}, {0.72, 7.6}};
     return pair ? paired[i] : single[i];
   }
   // TF32: K-major operands (A not transposed, B transposed) are the fastest to feed
-  static const TileCost single_nt[4] = {{0.396, 10.5}, {0.348, 9.7}, {0.325, 8.6}, {0.318, 6.8}};
-  static const TileCost paired_nt[4] = {{0.377, 12.9}, {0.355, 11.6}, {0.321, 10.4}, {0.321, 10.4}};
-  static const TileCost single_nn[4] = {{0.469, 11.7}, {0.366, 10.4}, {0.324, 8.4}, {0.322, 6.5}};
-  static const TileCost paired_nn[4] = {{0.428, 13.3}, {0.351, 11.7}, {0.334, 9.8}, {0.334, 9.8}};
-  static const TileCost single_tn[4] = {{0.546, 11.3}, {0.432, 10.6}, {0.372, 7.8}, {0.339, 6.2}};
-  static const TileCost paired_tn[4] = {{0.548, 11.8}, {0.448, 11.9}, {0.390, 10.3}, {0.390, 10.3}};
+  static const TileCost single_nt[4] = {{0.381, 9.2}, {0.357, 6.2}, {0.340, 4.8}, {0.307, 5.6}};
+  static const TileCost paired_nt[4] = {{0.371, 10.7}, {0.366, 7.4}, {0.345, 6.4}, {0.345, 6.4}};
+  static const TileCost single_nn[4] = {{0.489, 8.3}, {0.380, 6.0}, {0.332, 5.2}, {0.316, 4.7}};
+  static const TileCost paired_nn[4] = {{0.439, 10.1}, {0.365, 7.7}, {0.350, 6.2}, {0.350, 6.2}};
+  static const TileCost single_tn[4] = {{0.567, 7.8}, {0.454, 6.1}, {0.381, 5.1}, {0.336, 4.8}};
+  static const TileCost paired_tn[4] = {{0.551, 9.5}, {0.476, 7.0}, {0.420, 6.0}, {0.420, 6.0}};
   if (g.transA) return pair ? paired_tn[i] : single_tn[i];
   if (!g.transB) return pair ? paired_nn[i] : single_nn[i];
   return pair ? paired_nt[i] : single_nt[i];
