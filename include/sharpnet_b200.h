@@ -52,7 +52,11 @@ enum {
   SNB200_ACT_RELU = 1,
   SNB200_ACT_TANH = 2,
   SNB200_ACT_IDENTITY = 5,
-  SNB200_ACT_SWISH = 6
+  SNB200_ACT_SWISH = 6,
+  /* snb200_dense_fwd only: y = softmax over every row of x * op(W) + bias, a Linear layer followed by an
+   * ActivationLayer with CUDNN_ACTIVATION_SOFTMAX (Prod/GPU/GpuTensor.cs:411-413 -> cudnnSoftmaxForward): the output
+   * layer of every classification network.  Its gradient enters through snb200_dense_bwd_from_loss. */
+  SNB200_ACT_SOFTMAX = 1000
 };
 
 /* Losses whose gradient the library produces (Prod/Data/Tensor.cs:1182-1217): dy = scale * (yPredicted - yExpected)

@@ -25,6 +25,7 @@ import torch
 
 # cudnnActivationMode_t values (Prod/GPU/CudnnWrapper.cs:267-281)
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
+ACT_SOFTMAX = 1000          # CUDNN_ACTIVATION_SOFTMAX (Prod/GPU/CudnnWrapper.cs:276): softmax over every row
 W_OUT_IN, W_IN_OUT = 0, 1
 LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
 
@@ -134,6 +135,8 @@ def activation_forward(act, x):
         return np.tanh(x).astype(np.float32)
     if act == ACT_IDENTITY:
         return x.copy()
+    if act == ACT_SOFTMAX:
+        return softmax_last_dimension(x)
     raise ValueError(f"activation {act} is not on the path")
 
 
@@ -399,6 +402,9 @@ def _act_f64(act, z):
         return 1.0 / (1.0 + np.exp(-z))
     if act == ACT_TANH:
         return np.tanh(z)
+    if act == ACT_SOFTMAX:
+        e = np.exp(z - z.max(-1, keepdims=True))
+        return e / e.sum(-1, keepdims=True)
     return z.copy()
 
 

@@ -15,6 +15,7 @@ STATUS_NAMES = {
 }
 MATH_3XTF32, MATH_TF32, MATH_FP32_SIMT = 0, 1, 2
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
+ACT_SOFTMAX = 1000   # snb200_dense_fwd only
 W_OUT_IN, W_IN_OUT = 0, 1
 LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
 TUNE_FORCE_PATH, TUNE_FORCE_BN, TUNE_REWRITE_HI, TUNE_CHUNK_K, TUNE_PAIR, TUNE_SPLITK, TUNE_VARIANT, TUNE_PDL = range(8)

@@ -323,7 +323,7 @@ __device__ __forceinline__ bool epilogue_fold_c(const UmmaParams& p, float (&acc
 // and the row sum through shared memory (`xch`, [2][128] floats: one slot per group and row) and meet at the named
 // barrier 1 + q, once before a slot is overwritten and once before it is read.  Two warps per row halve the serial work of a lane and give every scheduler a second warp to
 // hide latencies with.  Rows are 16-byte aligned and N is a multiple of 4.  On return acc holds the values to store.
-//   ROW_SOFTMAX       acc = softmax(mask(alpha * acc)) over the N valid columns: the causal overwrite with -1e12
+//   ROW_SOFTMAX       acc = softmax(mask(alpha * acc + bias)) over the N valid columns: the causal overwrite with -1e12
 //                     (Prod/CPU/CpuTensor.cs:3037-3052) and CpuTensorActivationFunctions.Softmax (:19-46).
 //                     The exponential is the hardware's ex2 (relative error 2^-22) and the division a multiplication
 //                     by the reciprocal of the row sum; maximum and sum run as four independent chains.
@@ -350,6 +350,7 @@ __device__ __forceinline__ void epilogue_row_op(const UmmaParams& p, float (&acc
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
       float v = p.alpha * acc[j];
+      if (p.bias != nullptr && j < ncols) v += __ldg(p.bias + col_base + j);   // Dense + Softmax
       v = (col_base + j > limit) ? -1e12f : v;
       v = (j < ncols) ? v : -3.402823466e38f;
       acc[j] = v;
@@ -406,16 +407,16 @@ __device__ __forceinline__ void epilogue_row_op(const UmmaParams& p, float (&acc
 // Final store of one work unit: the fused epilogue into C, or (split >= 0) the raw partial sums into
 // the workspace.  `tile_row0`/`tile_col0` are the first row and column of the unit's whole tile,
 // `tile_elems` the size of that tile in the tiled workspace layout (rows x BN), `bn` its row pitch there.
-// `alpha` is p.alpha, or 1 when a row operation has already applied it; `beta` is p.beta, or 0 when beta * C is
-// already part of the accumulator.
+// `alpha` / `bias` are p.alpha / p.bias, or 1 / nullptr when a row operation has already applied them; `beta` is
+// p.beta, or 0 when beta * C is already part of the accumulator.
 template <int NC>
-__device__ __forceinline__ void epilogue_store_unit(const UmmaParams& p, float alpha, float beta, const float (&acc)[NC],
-                                                    float* stage,
+__device__ __forceinline__ void epilogue_store_unit(const UmmaParams& p, float alpha, float beta, const float* bias,
+                                                    const float (&acc)[NC], float* stage,
                                                     int b, int n_tiles, int tile, int split, int tile_row0, int tile_col0,
                                                     int bn, int row_base, int n0, int lane) {
   // one call of the store phase (its code is long: a second copy costs instruction-cache misses); the
   // partial-sum case redirects it to the workspace
-  StoreTarget t = {p.C, p.Z, p.bias, alpha, beta, p.act, p.ldc, p.vec_ok, p.omap.on};
+  StoreTarget t = {p.C, p.Z, bias, alpha, beta, p.act, p.ldc, p.vec_ok, p.omap.on};
   long long off = static_cast<long long>(b) * p.strideC;
   if (split >= 0 && p.partial != nullptr) {
     t.C = p.partial;
@@ -647,12 +648,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) break;
       float alpha = p.alpha;
+      const float* bias = p.bias;
       if (ROWOP) {   // this instantiation is launched for row operations only
         epilogue_row_op<NC, T::EPI_GROUPS>(p, acc, stage, row_xch, b, tm * BM + q * 32, col_base, q, (warp - 4) >> 2,
                                            lane);
-        alpha = 1.0f;                      // the row operation has consumed it
+        alpha = 1.0f;                      // the row operation has consumed both
+        bias = nullptr;
       }
-      epilogue_store_unit<NC>(p, alpha, c_folded ? 0.0f : p.beta, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN,
+      epilogue_store_unit<NC>(p, alpha, c_folded ? 0.0f : p.beta, bias, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN,
                               BN, tm * BM + q * 32, tn * BN + col_base, lane);
     }
   } else if (T::SPLIT) {

@@ -259,7 +259,7 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[buf]), 0));
       }
       if (!ok) break;
-      epilogue_store_unit<NC>(p, p.alpha, c_folded ? 0.0f : p.beta, acc, stage, b, n_tiles, tile, split, tm * 2 * BM, tn * BN, BN,
+      epilogue_store_unit<NC>(p, p.alpha, c_folded ? 0.0f : p.beta, p.bias, acc, stage, b, n_tiles, tile, split, tm * 2 * BM, tn * BN, BN,
                               tm * 2 * BM + rank * BM + q * 32, tn * BN + col_base, lane);
     }
   } else if (T::SPLIT) {

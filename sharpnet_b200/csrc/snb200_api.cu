@@ -764,6 +764,8 @@ static bool act_supported(int act) {
 
 static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
                           const float* bias, int act, float* z, float* y, const OutMap* y_map);
+static bool row_op_fits(const snb200_context* h, const GemmProblem& g, int max_cols);
+static int launch_softmax_fwd(snb200_handle_t h, long long rows, int cols, int causal_rows, const float* x, float* y);
 extern "C" int snb200_dense_fwd(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
                                 const float* bias, int act, float* z, float* y) {
   return dense_fwd_impl(h, w_layout, M, K, N, x, W, bias, act, z, y, nullptr);
@@ -776,6 +778,8 @@ static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, 
   if (M < 0 || K < 0 || N < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
   if (w_layout != SNB200_W_OUT_IN && w_layout != SNB200_W_IN_OUT)
     return fail(h, SNB200_STATUS_INVALID_VALUE, "unknown weight layout %d", w_layout);
+  const bool softmax = act == SNB200_ACT_SOFTMAX;   // Dense + Softmax over every row: forward only
+  if (softmax) act = ACT_IDENTITY;
   if (!act_supported(act)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "activation %d is not fused", act);
   if (M == 0 || N == 0) return 0;
   st = check_ptrs(h, x, W, y);
@@ -791,7 +795,15 @@ static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, 
   g.alpha = 1.0f; g.beta = 0.0f;
   g.bias = bias; g.Z = z; g.act = act;
   if (y_map) g.omap = *y_map;
-  return run_gemm(h, g);
+  if (!softmax) return run_gemm(h, g);
+  if (y_map) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "a softmax result is stored densely");
+  if (!z && row_op_fits(h, g, 256)) {   // softmax applied where the product is stored
+    g.row_op = ROW_SOFTMAX;
+    return run_gemm(h, g);
+  }
+  st = run_gemm(h, g);                   // logits (also kept in z when asked for), then one in-place pass
+  if (st) return st;
+  return launch_softmax_fwd(h, M, N, 0, y, y);
 }
 
 template <bool FUSE>

@@ -431,7 +431,7 @@ def test_gpu_multihead_attention_training_matches_reference_goldens(wrapper, gol
     # the same replays with the attention layer, the output Dense layer, the loss gradient and the momentum updates on
     # the device through the C ABI (snb200_mha_fwd / _bwd, snb200_dense_fwd, snb200_softmax_fwd,
     # snb200_dense_bwd_from_loss, snb200_sgd_update)
-    from sharpnet_b200._capi import ACT_IDENTITY, LOSS_CATEGORICAL_CROSSENTROPY
+    from sharpnet_b200._capi import ACT_SOFTMAX, LOSS_CATEGORICAL_CROSSENTROPY
     from sharpnet_b200.attention import MultiheadAttention
     from sharpnet_b200.linear import FusedDenseBackwardFromLoss, FusedDenseForward
     from sharpnet_b200.tensor import GPUTensor
@@ -453,9 +453,8 @@ def test_gpu_multihead_attention_training_matches_reference_goldens(wrapper, gol
             y = GPUTensor((n, 2, net.E), None, wrapper)
             layer.ForwardPropagation([Q, K, V], y, keep)
             flat = y.Reshape(n, 2 * net.E)
-            logits, p = GPUTensor((n, 3), None, wrapper), GPUTensor((n, 3), None, wrapper)
-            FusedDenseForward(logits, flat, lin_w, lin_b, ACT_IDENTITY, None, net.layout)
-            logits.SoftmaxLastDimension(p)
+            p = GPUTensor((n, 3), None, wrapper)
+            FusedDenseForward(p, flat, lin_w, lin_b, ACT_SOFTMAX, None, net.layout)      # Linear + Softmax output layer
             return (Q, K, V), flat, p
         for _ in range(10):
             for sl in net.batches():

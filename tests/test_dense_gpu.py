@@ -321,3 +321,40 @@ def test_golden_ten_epochs_entirely_on_the_device(wrapper, golden):
             opt.UpdateWeights(0.1, 0.1, rows, W, dW, b, db)
         FusedDenseForward(p, x, W, b, ACT_SIGMOID, w_layout=W_IN_OUT)
         np.testing.assert_allclose(p.ContentAsFloatArray().ravel(), golden[f"sigmoid_{key}_pred_after"], rtol=0, atol=1e-6)
+
+
+@pytest.mark.parametrize("layout", [W_OUT_IN, W_IN_OUT])
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+def test_dense_followed_by_softmax(wrapper, layout, mode, tol):
+    # Linear + ActivationLayer(CUDNN_ACTIVATION_SOFTMAX), the output layer of a classifier: softmax applied where the
+    # logits are stored (class counts that are multiples of 4, up to 256), or as a pass after the product (10 classes,
+    # 1000 classes, tiny batches, a kept pre-activation)
+    from sharpnet_b200._capi import ACT_SOFTMAX
+    wrapper.set_math_mode(mode)
+    for (M, K, N, with_z) in ((512, 384, 100, False), (300, 256, 256, False), (512, 384, 100, True), (64, 128, 10, False),
+                              (256, 512, 1000, False), (3, 30, 3, False)):
+        x = orc.normal((M, K), 0, 1, 50 + N)
+        Wl = orc.glorot_uniform((N, K) if layout == W_OUT_IN else (K, N), 51 + N)
+        b = orc.uniform((N,), -0.5, 0.5, 52 + N)
+        Y = GPUTensor((M, N), None, wrapper)
+        Z = GPUTensor((M, N), None, wrapper) if with_z else None
+        FusedDenseForward(Y, _t(wrapper, x), _t(wrapper, Wl), _t(wrapper, b), ACT_SOFTMAX, z=Z, w_layout=layout)
+        wrapper.check_device_status()
+        z64, y64 = orc.dense_forward(x, Wl, b, ACT_SOFTMAX, layout, f64=True)
+        y = Y.ContentAsFloatArray()
+        np.testing.assert_allclose(y.sum(1), 1.0, atol=2e-6)
+        # softmax has slope <= 1/4: the logits' bound carries over
+        wmax = float(np.abs(Wl).max())
+        assert np.abs(y - y64).max() <= tol * np.sqrt(K) * 4.0 * wmax
+        if with_z:
+            assert orc.scaled_error(Z.ContentAsFloatArray(), z64, K, 4.0, wmax) <= tol
+        if mode == MATH_3XTF32:
+            ym = orc.dense_forward(x, Wl, b, ACT_SOFTMAX, layout)[1]
+            assert np.abs(y - ym).max() <= tol * np.sqrt(K) * 4.0 * wmax
+
+
+def test_dense_backward_rejects_softmax(wrapper):
+    from sharpnet_b200._capi import ACT_SOFTMAX, SharpNetB200Error
+    t = GPUTensor((4, 4), None, wrapper)
+    with pytest.raises(SharpNetB200Error):
+        FusedDenseBackward(t, t, None, t, t, t, ACT_SOFTMAX, y=t)
