@@ -43,7 +43,12 @@ enum {
 enum {
   SNB200_MATH_3XTF32 = 0,    /* tcgen05 TF32 tensor cores, split fp32 = hi + lo, three products; default */
   SNB200_MATH_TF32 = 1,      /* single TF32 product: opt-in fast mode, ~1e-3 relative accuracy           */
-  SNB200_MATH_FP32_SIMT = 2  /* fp32 FMA on the CUDA cores for every shape                               */
+  SNB200_MATH_FP32_SIMT = 2, /* fp32 FMA on the CUDA cores for every shape                               */
+  /* opt-in: the hi * hi product in TF32 and both cross terms (a_lo * b_hi + a_hi * b_lo, 2^-11 of the result) as ONE
+   * bf16 instruction over the concatenated K slices: two instruction times per slice instead of three, error about
+   * 1.5x that of 3xTF32 and inside the same 1e-5 * sqrt(K) bound.  Implemented for Dot(a, false, b, true) shapes that
+   * run on the CTA-pair kernel (both operands K-major); every other product runs 3xTF32. */
+  SNB200_MATH_TF32_BF16X2 = 3
 };
 
 /* Activation selector: the values of cudnnActivationMode_t (Prod/GPU/CudnnWrapper.cs:267-281). */

@@ -13,7 +13,7 @@ STATUS_NAMES = {
     0: "SUCCESS", 1: "NOT_INITIALIZED", 3: "ALLOC_FAILED", 7: "INVALID_VALUE", 8: "ARCH_MISMATCH",
     13: "EXECUTION_FAILED", 14: "INTERNAL_ERROR", 15: "NOT_SUPPORTED",
 }
-MATH_3XTF32, MATH_TF32, MATH_FP32_SIMT = 0, 1, 2
+MATH_3XTF32, MATH_TF32, MATH_FP32_SIMT, MATH_TF32_BF16X2 = 0, 1, 2, 3
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
 ACT_SOFTMAX = 1000   # snb200_dense_fwd only
 W_OUT_IN, W_IN_OUT = 0, 1

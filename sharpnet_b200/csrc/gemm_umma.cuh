@@ -221,6 +221,44 @@ __device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, co
   }
 }
 
+// Operand split of the TF32 + bf16 scheme: x = hi + lo with hi = x truncated to TF32 (what the tensor core reads from
+// the raw tile).  The two cross terms a_lo*b_hi + a_hi*b_lo are 2^-11 of the product, so bf16 carries them: for every
+// 8-wide K slice the second plane holds 16 bf16 values per row -- [lo(8) | hi(8)] for A, [hi(8) | lo(8)] for B --
+// and ONE bf16 instruction of K = 16 over that slice yields both cross terms.  A 32-deep K block is 4 such slices
+// = 64 bf16 = one 128-byte row, so the plane has the size and the 128-byte swizzle of the fp32 tile it sits
+// behind; only K-major tiles are handled.  `raw` holds the A tile (A_BYTES) followed by the B tile.
+template <int A_BYTES, int RAW_BYTES, int NTHREADS>
+__device__ __forceinline__ void split_stage_bf16(uint8_t* raw, int tid) {
+  static_assert(NTHREADS == 128 && A_BYTES % 2048 == 0 && (RAW_BYTES - A_BYTES) % 2048 == 0, "16 rows per sweep");
+  // Thread t handles the 16-byte chunk t & 7 of row (t >> 3) + 16 j: row & 7 and the chunk, hence the K slice and
+  // every swizzled offset, are the same in all its iterations; only the row advances (2048 bytes per sweep).
+  const int r7 = (tid >> 3) & 7;
+  const int cl = (tid & 7) ^ r7;               // logical chunk = 4 consecutive k
+  const int g = cl >> 1, half = cl & 1;        // 8-wide K slice, and which half of it
+  const int row_off = (tid >> 3) * 128;
+  const int c_even = ((2 * g) ^ r7) << 4, c_odd = ((2 * g + 1) ^ r7) << 4;
+  auto sweep = [&](const uint8_t* src, uint8_t* dst_lo, uint8_t* dst_hi) {
+    const float4 x = *reinterpret_cast<const float4*>(src);
+    const float h0 = __uint_as_float(__float_as_uint(x.x) & 0xffffe000u), h1 = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
+    const float h2 = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u), h3 = __uint_as_float(__float_as_uint(x.w) & 0xffffe000u);
+    uint2 lo, hi;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo.x) : "f"(x.y - h1), "f"(x.x - h0));   // upper half <- first operand
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo.y) : "f"(x.w - h3), "f"(x.z - h2));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi.x) : "f"(h1), "f"(h0));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi.y) : "f"(h3), "f"(h2));
+    *reinterpret_cast<uint2*>(dst_lo) = lo;
+    *reinterpret_cast<uint2*>(dst_hi) = hi;
+  };
+  const uint8_t* src = raw + tid * 16;
+  uint8_t* plane = raw + RAW_BYTES + row_off + half * 8;
+#pragma unroll
+  for (int j = 0; j < A_BYTES / 2048; ++j)                      // A: [lo | hi]
+    sweep(src + j * 2048, plane + j * 2048 + c_even, plane + j * 2048 + c_odd);
+#pragma unroll
+  for (int j = A_BYTES / 2048; j < RAW_BYTES / 2048; ++j)       // B: [hi | lo]
+    sweep(src + j * 2048, plane + j * 2048 + c_odd, plane + j * 2048 + c_even);
+}
+
 // Store phase of the epilogue.  Each lane holds one output row (NC columns of it) in `acc`.  A
 // 32 x 32 block goes through a per-warp shared-memory tile (16-byte chunks XOR-swizzled by row) so
 // that every global access of C, Z and bias is a run of whole 128-byte lines instead of 32 scattered

@@ -21,8 +21,11 @@
 
 namespace snb {
 
-template <int BN_, int BK_, bool SPLIT_>
+// HYBRID_ (with SPLIT_): the second plane holds bf16 cross-term operands instead of TF32 lo values, and every 8-wide
+// K slice takes one TF32 and one bf16 instruction instead of three TF32 ones (see split_stage_bf16).
+template <int BN_, int BK_, bool SPLIT_, bool HYBRID_ = false>
 struct Umma2Tile {
+  static constexpr bool HYBRID = HYBRID_;
   static constexpr int BM = 128;                 // rows per CTA; the pair covers 256
   static constexpr int BN = BN_;                 // columns of the pair's tile
   static constexpr int BNH = BN_ / 2;            // B columns held by each CTA
@@ -154,6 +157,7 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     } else if (warp == 1 && lane == 0 && leader) {
       // ---------------------------------------------------------------- MMA issuer (even CTA only)
       const uint32_t idesc = make_idesc_tf32(2 * BM, BN, p.a_mn, p.b_mn);
+      const uint32_t idesc16 = make_idesc_bf16(2 * BM, BN);
       const uint32_t a_step = p.a_mn ? 1024u : 32u;
       const uint32_t b_step = p.b_mn ? 1024u : 32u;
       const uint32_t a_lbo = p.a_mn ? T::MNMAJ_CHUNK_BYTES : 16u;
@@ -187,7 +191,12 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               const uint64_t da_hi = make_smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lay);
               const uint64_t db_hi = make_smem_desc(b_hi + ks * b_step, b_lbo, b_sbo, b_lay);
               const uint32_t first = (kb == kb0 && ks == 0) ? 0u : 1u;
-              if (T::SPLIT) {
+              if (T::HYBRID) {
+                const uint64_t da_16 = make_smem_desc(a_hi + T::RAW_BYTES + ks * 32u, 16u, T::KMAJ_SBO, T::KMAJ_LAYOUT);
+                const uint64_t db_16 = make_smem_desc(b_hi + T::RAW_BYTES + ks * 32u, 16u, T::KMAJ_SBO, T::KMAJ_LAYOUT);
+                umma_bf16_ss_pair(d_tmem, da_16, db_16, idesc16, first);      // a_lo*b_hi + a_hi*b_lo
+                umma_tf32_ss_pair(d_tmem, da_hi, db_hi, idesc, 1u);
+              } else if (T::SPLIT) {
                 const uint64_t da_lo = make_smem_desc(a_hi + T::RAW_BYTES + ks * a_step, a_lbo, a_sbo, a_lay);
                 const uint64_t db_lo = make_smem_desc(b_hi + T::RAW_BYTES + ks * b_step, b_lbo, b_sbo, b_lay);
                 umma_tf32_ss_pair(d_tmem, da_lo, db_hi, idesc, first);
@@ -274,7 +283,8 @@ umma2_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait_warp(&full_bar[s], ph, abortp)) { ok = false; break; }
-        split_stage<T::RAW_BYTES, T::N_SPLIT_THREADS>(ring + s * T::STAGE_BYTES, tid, p.rewrite_hi);
+        if constexpr (T::HYBRID) split_stage_bf16<T::A_BYTES, T::RAW_BYTES, T::N_SPLIT_THREADS>(ring + s * T::STAGE_BYTES, tid);
+        else                     split_stage<T::RAW_BYTES, T::N_SPLIT_THREADS>(ring + s * T::STAGE_BYTES, tid, p.rewrite_hi);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ready_bar[s]), 0));

@@ -230,6 +230,18 @@ __device__ __forceinline__ void umma_tf32_ss_pair(uint32_t tmem_d, uint64_t desc
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same for bf16 operands (kind::f16 with the bf16 formats in the instruction descriptor): K = 16 per instruction.
+__device__ __forceinline__ void umma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair once every MMA issued
 // so far has retired (a commit carrying a CTA mask; it moves no data).
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
@@ -280,6 +292,16 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_tf32(uint32_t m, uint32_
   d |= 2u << 10;           // B format: TF32
   d |= (a_mn & 1u) << 15;  // A major-ness
   d |= (b_mn & 1u) << 16;  // B major-ness
+  d |= (n >> 3) << 17;     // N / 8
+  d |= (m >> 4) << 24;     // M / 16
+  return d;
+}
+// bf16 x bf16 -> f32, both operands K-major.
+__host__ __device__ __forceinline__ uint32_t make_idesc_bf16(uint32_t m, uint32_t n) {
+  uint32_t d = 0;
+  d |= 1u << 4;            // D format: F32
+  d |= 1u << 7;            // A format: BF16
+  d |= 1u << 10;           // B format: BF16
   d |= (n >> 3) << 17;     // N / 8
   d |= (m >> 4) << 24;     // M / 16
   return d;

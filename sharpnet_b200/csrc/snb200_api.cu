@@ -142,7 +142,7 @@ extern "C" int snb200_set_stream(snb200_handle_t h, void* s) {
 }
 extern "C" int snb200_set_math_mode(snb200_handle_t h, int m) {
   if (!h) return SNB200_STATUS_NOT_INITIALIZED;
-  if (m < 0 || m > 2) return fail(h, SNB200_STATUS_INVALID_VALUE, "math mode %d is not one of 0, 1, 2", m);
+  if (m < 0 || m > 3) return fail(h, SNB200_STATUS_INVALID_VALUE, "math mode %d is not one of 0, 1, 2, 3", m);
   h->math_mode = m;
   return 0;
 }
@@ -413,10 +413,16 @@ static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pl
   return check_launch(h, "umma2_gemm_kernel launch");
 }
 
-static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int bn, SplitPlan& plan) {
+static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int bn, SplitPlan& plan, bool hybrid) {
   char name[64];
-  snprintf(name, sizeof(name), "umma2_%s_256x%d%s", split ? "3xtf32" : "tf32", bn, plan.splits > 0 ? "_splitk" : "");
+  hybrid = hybrid && split && bn >= 128;
+  snprintf(name, sizeof(name), "umma2_%s_256x%d%s", hybrid ? "tf32bf16x2" : split ? "3xtf32" : "tf32", bn,
+           plan.splits > 0 ? "_splitk" : "");
   note_kernel(h, name, 1);
+  if (hybrid) {
+    if (bn == 256) return launch_umma2_t<Umma2Tile<256, 32, true, true>>(h, g, plan);
+    return launch_umma2_t<Umma2Tile<128, 32, true, true>>(h, g, plan);
+  }
   if (split) {
     switch (bn) {
       // 32-wide K blocks: three 64 KB stages beat six 32 KB ones (fewer hand-offs per byte), measured +8..35 %
@@ -518,7 +524,7 @@ static TileCost tile_cost(bool split3x, int pair, int bn, const GemmProblem& g) 
   if (!g.transB) return pair ? paired_nn[i] : single_nn[i];
   return pair ? paired_nt[i] : single_nt[i];
 }
-static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, bool split) {
+static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, bool split, bool hybrid) {
   TileChoice best = {0, 256, 1, 0};
   const bool allow_splitk = h->tune[TUNE_SPLITK] == 0;
   double best_cost = 1e300;
@@ -539,7 +545,8 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
       const long long slots = pair ? h->sm_count / 2 : h->sm_count;
       const long long whole = tiles / slots * slots, tail = tiles - whole;
       const TileCost tc = tile_cost(split, pair, bn, g);
-      const double c = tc.kblock_us, fixed = tc.fixed_us;
+      // TF32 + bf16 cross terms: two instruction times per K slice instead of three, on the pair kernel's wide tiles
+      const double c = tc.kblock_us * ((hybrid && pair && bn >= 128) ? 0.7 : 1.0), fixed = tc.fixed_us;
       for (int j = 0; j < 11; ++j) {
         const long long ks = ks_cand[j];
         if (ks > 1 && (!allow_splitk || tail == 0 || kb / ks < 8)) break;   // at least 256 of K per unit
@@ -655,7 +662,9 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
     if (macs < 64.0 * 64 * 64 || (g.M < 16 && !swappable) || g.N < 8) use_umma = false;
   }
   if (!use_umma) return launch_simt(h, g);
-  const bool split = h->math_mode == SNB200_MATH_3XTF32;
+  const bool split = h->math_mode == SNB200_MATH_3XTF32 || h->math_mode == SNB200_MATH_TF32_BF16X2;
+  // the bf16 cross-term scheme exists for K-major operands on the pair kernel; everything else runs 3xTF32
+  const bool hybrid = h->math_mode == SNB200_MATH_TF32_BF16X2 && !g.transA && g.transB;
   if (g.row_op != ROW_NONE) {
     // whole rows in one tile of the single-CTA kernel, K never cut (the caller checked row_op_fits)
     SplitPlan none = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -699,7 +708,7 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
       return launch_reduce(h, g, plan.parts, 1);
     }
   }
-  const TileChoice c = choose_tile(h, g, split);
+  const TileChoice c = choose_tile(h, g, split, hybrid);
   // Tiles that would leave most SMs idle in the last wave are cut along K.
   SplitPlan plan = {0, 0, 0, 0, 0, 0, 0, 0};
   if (c.splits > 1) {
@@ -708,7 +717,7 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
     plan.tiled = 1;
     plan.whole_tiles = c.whole_tiles;
   }
-  const int st = c.pair ? launch_umma2(h, g, split, c.bn, plan) : launch_umma(h, g, split, c.bn, plan);
+  const int st = c.pair ? launch_umma2(h, g, split, c.bn, plan, hybrid) : launch_umma(h, g, split, c.bn, plan);
   if (st || plan.parts == 0) return st;
   return launch_tail_reduce(h, g, plan, c.pair ? 256 : 128, c.bn);
 }

@@ -345,3 +345,29 @@ def test_dependent_launch_on_and_off_give_the_same_bits(wrapper, mode, tol):
     for i in range(12):
         ref = ref @ (W.T if i % 2 == 1 else W).astype(np.float64)
     assert np.abs(outs[0] - ref).max() <= 12 * tol * np.sqrt(384) * np.abs(ref).max() + 1e-12
+
+
+def test_tf32_bf16x2_mode(wrapper):
+    # opt-in math mode 3: hi * hi in TF32, both cross terms as one bf16 instruction.  Same 1e-5 bound as 3xTF32 on the
+    # shapes that reach its kernel (A not transposed, B transposed, M > 128), 3xTF32 itself on everything else.
+    from sharpnet_b200._capi import MATH_TF32_BF16X2
+    wrapper.set_math_mode(MATH_TF32_BF16X2)
+    assert wrapper.get_math_mode() == MATH_TF32_BF16X2
+    for (M, N, K) in ((512, 512, 512), (1000, 3108, 1028), (2304, 2300, 1028), (256, 256, 16384), (4096, 1024, 3072)):
+        e = _check(wrapper, M, N, K, False, True, 1.0, 0.0, 900 + M, TOL_3XTF32)
+        if M >= 1000:        # wide pair tiles; the smaller problems may be given narrower (3xTF32) kernels
+            assert "tf32bf16x2" in wrapper.last_kernel(), wrapper.last_kernel()
+        assert e < 5e-6
+    _check(wrapper, 2304, 2300, 1028, False, True, 0.5, 1.0, 950, TOL_3XTF32)            # beta, cut last wave
+    _check(wrapper, 772, 1000, 1536, False, True, 1.0, 0.0, 951, TOL_3XTF32, batch=3)
+    for tA, tB in ((False, False), (True, False), (True, True)):                            # other layouts: 3xTF32
+        _check(wrapper, 512, 384, 640, tA, tB, 1.0, 0.0, 960, TOL_3XTF32)
+        assert "3xtf32" in wrapper.last_kernel(), wrapper.last_kernel()
+    _check(wrapper, 64, 64, 64, False, True, 1.0, 0.0, 970, TOL_3XTF32)                   # small: single-CTA 3xTF32
+    # small integers are exact in TF32 and their low parts are zero: bit exact
+    rng = np.random.default_rng(5)
+    a = rng.integers(-8, 9, (300, 160)).astype(np.float32)
+    b = rng.integers(-8, 9, (280, 160)).astype(np.float32)
+    A, B, C = GPUTensor(a.shape, a, wrapper), GPUTensor(b.shape, b, wrapper), GPUTensor((300, 280), None, wrapper)
+    C.Dot(A, False, B, True, 1, 0)
+    np.testing.assert_array_equal(C.ContentAsFloatArray(), a @ b.T)
