@@ -220,9 +220,9 @@ def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi,
     flops = 2.0 * M * N * K * batch
     byts = bytes_set + (4.0 * batch * M * N if beta != 0 else 0.0)
     tpeak3 = peaks["bf16_burst"] / 2 / 3
-    tens = tpeak3 if mode == MATH_3XTF32 else tpeak3 * 3
+    tens = tpeak3 * 3 if mode == 1 else tpeak3
     t_tensor, t_hbm = flops / (tens * 1e12), byts / (peaks["hbm"] * 1e9)
-    return {"shape": name, "mode": "3xTF32" if mode == MATH_3XTF32 else "TF32", "kernel": w.last_kernel(),
+    return {"shape": name, "mode": {0: "3xTF32", 1: "TF32", 2: "FP32_SIMT", 3: "TF32+BF16x2"}[mode], "kernel": w.last_kernel(),
             "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 2), "gbs": round(byts / ms / 1e6, 1),
             "bound": "tensor" if t_tensor >= t_hbm else "hbm",
             "roofline_frac": round(max(t_tensor, t_hbm) / (ms * 1e-3), 3), "scaled_err_vs_f64": float(f"{err:.3e}"),
@@ -409,6 +409,11 @@ def per_shape_table(w, torch, peaks, large):
     def one(name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows=64):
         out.append(time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows))
 
+    if large:
+        # the opt-in TF32 + bf16 cross-term mode next to 3xTF32 on the layout it is implemented for
+        from sharpnet_b200._capi import MATH_TF32_BF16X2
+        for mode in (MATH_3XTF32, MATH_TF32_BF16X2):
+            one("8192^3 NT", 8192, 8192, 8192, False, True, 0.0, 1, -1, 1, mode, check_rows=16)
     for mode in (MATH_3XTF32, MATH_TF32):
         if large:
             one("cfg5a 16384^3 NN", 16384, 16384, 16384, False, False, 0.0, 1, -1, 1, mode, check_rows=8)
@@ -641,7 +646,7 @@ def main():
     ap.add_argument("--trans", default="NN", help="NN, NT, TN or TT")
     ap.add_argument("--beta", type=float, default=0.0)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--math", type=int, default=0, help="0 3xTF32, 1 TF32, 2 SIMT fp32")
+    ap.add_argument("--math", type=int, default=0, help="0 3xTF32, 1 TF32, 2 SIMT fp32, 3 TF32 + bf16 cross terms")
     ap.add_argument("--calls", type=int, default=20)
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) write to file descriptor 1; the contract is ONE JSON line on
