@@ -4,14 +4,14 @@
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-shapes] [--no-cpu]
   (N > 1: launched by torch.distributed.run, one rank per GPU)
 
-A step is one forward + backward pass of the 3-layer MLP of BASELINE config 5
+A step is one forward + backward pass of the 3-layer MLP of benchmark config 5
 (batch 65536, 4096 -> 4096 -> 4096 -> 1000, ReLU, ReLU, identity; Glorot weights, zero biases,
 x ~ N(0,1), upstream gradient ~ N(0,1)) through snb200_dense_fwd / snb200_dense_bwd, the batch rows
 sharded over the N GPUs and the weight / bias gradients summed with one all-reduce per layer.
 `value` is algorithmic TFLOP/s of the whole job (12.61 TFLOP per step), timed on the device with
 inputs resident in HBM; `e2e` is the same step driven from pinned HOST buffers (x and the upstream
 gradient copied in through double-buffered staging, the bias gradients copied out, every step).  `shapes` lists every Dot / batched /
-Dense shape of BASELINE configs 1-5 with its own TFLOP/s, roofline fraction and error vs fp64 (N = 1).
+Dense shape of benchmark configs 1-5 with its own TFLOP/s, roofline fraction and error vs fp64 (N = 1).
 
 --impl reference times the reference's CPU path (MKL sgemm through the oracle) on a row sample of
 the same step, with every host core.
@@ -159,7 +159,7 @@ def run_reference(args):
 
 
 def workload_config(n):
-    return {"workload": "BASELINE config 5: 3-layer MLP training step (Dense fwd+bwd), batch 65536, "
+    return {"workload": "benchmark config 5: 3-layer MLP training step (Dense fwd+bwd), batch 65536, "
                         "4096->4096->4096->1000, ReLU, fp32; rows sharded over the GPUs, dW/db all-reduced",
             "global_batch": GLOBAL_BATCH, "dims": list(DIMS), "parallelism": f"dp{n}",
             "math_mode": "3xTF32 (fp32-accurate)", "l2": "inputs (>1 GB per operand) exceed the 126 MB L2"}
@@ -230,7 +230,7 @@ def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi,
 
 
 def sharded_gemm(w, torch, world, rank, barrier, max_over_ranks, calls=5):
-    """BASELINE config 5a on N GPUs: C = A * B with 16384^3 operands, A and C sharded by rows of M over the ranks, B
+    """benchmark config 5a on N GPUs: C = A * B with 16384^3 operands, A and C sharded by rows of M over the ranks, B
     replicated; no collective on the data path.  Returns aggregate TFLOP/s = 2 * 16384^3 / (max over ranks of the
     device time per call)."""
     import ctypes
@@ -304,7 +304,7 @@ def companion_table(w, torch, peaks):
 
 
 def dense_and_attention_table(w, torch, peaks):
-    """BASELINE config 3 (Dense 4096 x 3072 -> 1024, bias, ReLU and Swish, forward and backward through the fused
+    """benchmark config 3 (Dense 4096 x 3072 -> 1024, bias, ReLU and Swish, forward and backward through the fused
     entry points) and an attention block of the reference's own timing sandbox
     (Tests/NonReg/ParallelRunWithTensorFlow.cs:415-490: 256 heads x [128 x 64]), timed like the Dot shapes."""
     import ctypes
@@ -397,7 +397,7 @@ def dense_and_attention_table(w, torch, peaks):
 
 
 def per_shape_table(w, torch, peaks, large):
-    """TFLOP/s, roofline fraction and error vs fp64 of every Dot / batched shape in BASELINE configs 1-4
+    """TFLOP/s, roofline fraction and error vs fp64 of every Dot / batched shape in benchmark configs 1-4
     (`large` false) or of the 16384^3 product of config 5 (`large` true: 35 ms launches that drive the GPU into its
     power cap, so they run after the short kernels)."""
     import numpy as np

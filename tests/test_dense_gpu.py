@@ -146,7 +146,7 @@ def test_dense_with_a_cut_last_wave(wrapper, act, layout):
 @pytest.mark.parametrize("act", [ACT_RELU, ACT_SWISH])
 @pytest.mark.parametrize("layout", [W_IN_OUT, W_OUT_IN])
 def test_config_3_dense_4096x3072x1024(wrapper, act, layout):
-    # BASELINE config 3: x[4096x3072] N(0,1), W Glorot, dy N(0,1); bias drawn non-zero to exercise the add
+    # benchmark config 3: x[4096x3072] N(0,1), W Glorot, dy N(0,1); bias drawn non-zero to exercise the add
     _dense_case(wrapper, 4096, 3072, 1024, act, layout, 6, TOL_3XTF32)
 
 
