@@ -104,7 +104,7 @@ def cpu_step_sample(rows, seed=17):
     bs = [np.zeros(DIMS[i + 1], np.float32) for i in range(3)]
     acts = (orc.ACT_RELU, orc.ACT_RELU, orc.ACT_IDENTITY)
 
-    def step():
+    def step(keep=None):
         a = [x]
         for i in range(3):
             _, y = orc.dense_forward(a[-1], Ws[i], bs[i], acts[i], orc.W_OUT_IN)
@@ -113,21 +113,113 @@ def cpu_step_sample(rows, seed=17):
         for i in (2, 1, 0):
             _, dW, db, g = orc.dense_backward(a[i], Ws[i], g, acts[i], a[i + 1], None, 1.0, orc.W_OUT_IN,
                                               need_dx=(i > 0))
+            if keep is not None:
+                keep[i] = (dW, db)
+        if keep is not None:
+            keep["a"] = a
         return db
+    step.inputs = (x, dy, Ws, bs, acts)
     return step
 
 
 def time_cpu(rows, reps):
+    """Times the oracle's step on `rows` rows; also returns the step's inputs and its results (MKL, fp32) so that
+    the device's step on the same rows can be compared with them."""
     from sharpnet_b200.data_parallel import mlp_step_flops
     step = cpu_step_sample(rows)
-    step()
+    results = {}
+    step(results)
     ts = []
     for _ in range(reps):
         t0 = time.perf_counter()
         step()
         ts.append(time.perf_counter() - t0)
     t = sorted(ts)[len(ts) // 2]
-    return mlp_step_flops(rows, DIMS) / t / 1e12, t
+    return mlp_step_flops(rows, DIMS) / t / 1e12, t, step.inputs, results
+
+
+def step_parity(w, torch, inputs, cpu_results):
+    """The device's training step on the rows the CPU baseline ran, compared with the oracle: the network output
+    against the oracle's own forward pass (MKL, fp32), and every dW / db against the oracle's backward pass in
+    float64 AND in MKL fp32, both evaluated on the device's activations (a pre-activation within rounding of zero
+    may fall on either side of the ReLU on the two machines; the gradient mask must come from the same values)."""
+    import numpy as np
+    from oracle import sharpnet_oracle as orc
+    from sharpnet_b200.data_parallel import MLP_ACTS, DenseStack, training_step
+    x, dy, Ws, bs, acts = inputs
+    rows = x.shape[0]
+    stack = DenseStack(w, rows, DIMS, MLP_ACTS, Ws)
+    stack.x.storage.copy_(torch.from_numpy(x).view(-1))
+    stack.dy.storage.copy_(torch.from_numpy(dy).view(-1))
+    training_step(stack)
+    w.check_device_status()
+    a_dev = [x] + [t.ContentAsFloatArray() for t in stack.y]
+    out = {"rows": rows, "bound": 1e-5, "measure": "max|gpu - ref| / (sqrt(K) * a_max * b_max)"}
+    worst = 0.0
+    for i in range(3):
+        e = orc.scaled_error(a_dev[i + 1], cpu_results["a"][i + 1], DIMS[i], float(np.abs(a_dev[i]).max()),
+                             float(np.abs(Ws[i]).max()))
+        out[f"y{i}_vs_mkl"] = float(f"{e:.3e}")
+        worst = max(worst, e / (i + 1))          # layer i's input already carries i rounded products
+    g64, g32 = dy, dy
+    for i in (2, 1, 0):
+        dz, dW64, db64, g64n = orc.dense_backward(a_dev[i], Ws[i], g64, acts[i], a_dev[i + 1], None, 1.0, orc.W_OUT_IN,
+                                                  need_dx=i > 0, f64=True)
+        _, dW32, db32, g32n = orc.dense_backward(a_dev[i], Ws[i], g32, acts[i], a_dev[i + 1], None, 1.0, orc.W_OUT_IN,
+                                                 need_dx=i > 0)
+        amax, gmax = float(np.abs(a_dev[i]).max()), float(np.abs(dz).max())
+        got_dW, got_db = stack.dW[i].ContentAsFloatArray(), stack.db[i].ContentAsFloatArray()
+        for name, got, r64, r32, am in (("dW", got_dW, dW64, dW32, amax), ("db", got_db, db64, db32, 1.0)):
+            e64, e32 = orc.scaled_error(got, r64, rows, am, gmax), orc.scaled_error(got, r32, rows, am, gmax)
+            out[f"{name}{i}_vs_f64"], out[f"{name}{i}_vs_mkl"] = float(f"{e64:.3e}"), float(f"{e32:.3e}")
+            worst = max(worst, e64, e32)
+        g64 = None if g64n is None else g64n.astype(np.float32)
+        g32 = g32n
+    out["worst"] = float(f"{worst:.3e}")
+    out["ok"] = bool(worst <= 1e-5)
+    del stack
+    return out
+
+
+def dp_check(w, torch, dist, world, rank, reducer, compute_stream):
+    """One step of a small stack (batch 1024 per GPU, 512 -> 256 -> 64) through the same training_step and the
+    same GradientAllReduce as the timed step; rank 0 compares the all-reduced dW / db it holds with the oracle on
+    the FULL batch (float64, masks from the device's activations, gathered from every rank)."""
+    import numpy as np
+    from oracle import sharpnet_oracle as orc
+    from sharpnet_b200 import ACT_IDENTITY, ACT_RELU
+    from sharpnet_b200.data_parallel import DenseStack, shard_rows, training_step
+    dims, batch = (512, 256, 64), 1024 * world
+    acts = (ACT_RELU, ACT_IDENTITY)
+    x, dy = orc.normal((batch, dims[0]), 0, 1, 31), orc.normal((batch, dims[-1]), 0, 1, 32)
+    Ws = [orc.glorot_uniform((dims[i + 1], dims[i]), 33 + i) for i in range(2)]
+    r0, r1 = shard_rows(batch, world, rank)
+    stack = DenseStack(w, r1 - r0, dims, acts, Ws)
+    stack.x.storage.copy_(torch.from_numpy(x[r0:r1]).reshape(-1))
+    stack.dy.storage.copy_(torch.from_numpy(dy[r0:r1]).reshape(-1))
+    training_step(stack, reducer, compute_stream)
+    torch.cuda.synchronize()
+    w.check_device_status()
+    y0 = stack.y[0].storage[: stack.y[0].Count].view(r1 - r0, dims[1])
+    if world > 1:
+        parts = [torch.empty_like(y0) for _ in range(world)] if rank == 0 else None
+        dist.gather(y0, parts, dst=0)
+        y0_full = torch.cat(parts).cpu().numpy() if rank == 0 else None
+    else:
+        y0_full = y0.cpu().numpy()
+    if rank != 0:
+        return None
+    a = [x, y0_full, None]
+    worst, g = 0.0, dy
+    for i in (1, 0):
+        dz, dW, db, g = orc.dense_backward(a[i], Ws[i], g, (orc.ACT_RELU, orc.ACT_IDENTITY)[i], a[i + 1], None, 1.0,
+                                           orc.W_OUT_IN, need_dx=i > 0, f64=True)
+        amax, gmax = float(np.abs(a[i]).max()), float(np.abs(dz).max())
+        worst = max(worst, orc.scaled_error(stack.dW[i].ContentAsFloatArray(), dW, batch, amax, gmax),
+                    orc.scaled_error(stack.db[i].ContentAsFloatArray(), db, batch, 1.0, gmax))
+        g = None if g is None else g.astype(np.float32)
+    return {"scaled_err": float(f"{worst:.3e}"), "bound": 1e-5, "ok": bool(worst <= 1e-5), "ranks": world,
+            "what": f"all-reduced dW/db of a {dims} stack, batch {batch} over {world} GPUs, vs the oracle on the full batch"}
 
 
 def run_reference(args):
@@ -149,7 +241,9 @@ def run_reference(args):
         "impl": "reference", "metric": "dot_tflops", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "config": dict(workload_config(args.gpus),
+                       sample=f"1/{GLOBAL_BATCH // CPU_SAMPLE_ROWS} row sample: {CPU_SAMPLE_ROWS} of the {GLOBAL_BATCH} "
+                              "batch rows per step (the rate, not the time, is what compares)"),
         "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                          "sample": f"{CPU_SAMPLE_ROWS} of {GLOBAL_BATCH} batch rows per step, MKL sgemm via torch CPU "
                                    "(SharpNet's C# cannot be built here: no .NET)"},
@@ -168,7 +262,8 @@ def workload_config(n):
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
-def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows=64, min_calls=20):
+def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows=64, min_calls=20,
+                    cpu=True, compare=True):
     """Times one Dot / BatchMatrixMultiplication shape.  The call cycles through enough distinct
     (A, B, C) sets that their total size exceeds twice the L2, so every call finds its operands in
     HBM; the whole loop is timed with one CUDA-event pair on the launching stream."""
@@ -185,17 +280,22 @@ def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi,
         A.storage.uniform_(lo, hi); B.storage.uniform_(lo, hi); C.storage.uniform_(lo, hi)
         sets.append((A, B, C))
     A, B, C = sets[0]
-    c0 = C.storage.clone()
-    C.BatchMatrixMultiplication(A, tA, B, tB, 1.0, beta)
-    # error vs fp64 on a few output rows of matrix 0 (a full-size fp64 product on the host would take minutes)
     rows = min(check_rows, M)
-    a0 = A.storage[: sa[1] * sa[2]].view(sa[1], sa[2]).double()
-    b0 = B.storage[: sb[1] * sb[2]].view(sb[1], sb[2]).double()
-    opa = (a0.t() if tA else a0)[:rows]
-    opb = b0.t() if tB else b0
-    ref = opa @ opb + beta * c0[: M * N].view(M, N)[:rows].double()
-    err = (C.storage[: M * N].view(M, N)[:rows].double() - ref).abs().max().item() / (math.sqrt(K) * hi * hi)
-    del a0, b0, opa, opb, ref, c0
+    # the rows of matrix 0 that get checked, copied out before the call overwrites C
+    a0 = A.storage[: sa[1] * sa[2]].view(sa[1], sa[2])
+    a_rows = (a0[:, :rows] if tA else a0[:rows]).contiguous().cpu().numpy()     # stored layout, `rows` rows of op(A)
+    b0 = B.storage[: sb[1] * sb[2]].view(sb[1], sb[2]).cpu().numpy()
+    c_rows = C.storage[: M * N].view(M, N)[:rows].cpu().numpy().copy()
+    C.BatchMatrixMultiplication(A, tA, B, tB, 1.0, beta)
+    got = C.storage[: M * N].view(M, N)[:rows].cpu().numpy()
+    # error against the CPU oracle on those rows: MKL sgemm (what CpuTensor.Dot runs) and float64
+    from oracle import sharpnet_oracle as orc
+    errs = {}
+    for key, f64 in (("mkl", False), ("f64", True)):
+        ref = orc.batch_matrix_multiplication(a_rows[None], tA, b0[None], tB, c_rows[None].copy(), 1.0, beta, f64=f64)
+        errs[key] = orc.scaled_error(got, ref[0], K, hi, hi)
+    err = errs["f64"]
+    del a0, b0, a_rows, c_rows, got
     calls = max(min_calls, n_sets) if bytes_set < 1e9 else 5
     # The timed loop calls the C ABI directly with arguments converted once, so that the host side of a
     # call is a few hundred nanoseconds, as it is for SharpNet's P/Invoke, and not Python bookkeeping.
@@ -226,7 +326,87 @@ def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi,
             "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 2), "gbs": round(byts / ms / 1e6, 1),
             "bound": "tensor" if t_tensor >= t_hbm else "hbm",
             "roofline_frac": round(max(t_tensor, t_hbm) / (ms * 1e-3), 3), "scaled_err_vs_f64": float(f"{err:.3e}"),
-            "operand_sets": n_sets, "calls": calls}
+            "scaled_err_vs_mkl": float(f"{errs['mkl']:.3e}"), "checked_rows": rows,
+            "operand_sets": n_sets, "calls": calls,
+            **(library_comparators(torch, sets, sa, sb, M, N, K, tA, tB, beta, batch, mode, calls, ms, cpu)
+               if compare else {})}
+
+
+def _median(v):
+    v = sorted(v)
+    return v[len(v) // 2]
+
+
+def library_comparators(torch, sets, sa, sb, M, N, K, tA, tB, beta, batch, mode, calls, our_ms, cpu):
+    """What SharpNet runs today on the same operands, timed beside our kernel (bench-only: nothing in the library
+    calls these).  cublas_sgemm_ms: torch on the device with TF32 off = cuBLAS sgemm default math, what
+    GPUTensor.Dot / BatchMatrixMultiplication reach (Prod/GPU/GpuTensor.cs:1218,1192); in TF32 mode also cuBLAS with
+    TF32 on.  mkl_ms: torch on the CPU (MKL sgemm, all host cores) = CpuTensor.Dot; a batch both as the reference's
+    serial loop of Dot calls (Prod/CPU/CpuTensor.cs:3012-3024) and as one baddbmm."""
+    out = {}
+    views = []
+    for A, B, C in sets:
+        a = A.storage[: batch * sa[1] * sa[2]].view(batch, sa[1], sa[2])
+        b = B.storage[: batch * sb[1] * sb[2]].view(batch, sb[1], sb[2])
+        c = C.storage[: batch * M * N].view(batch, M, N)
+        views.append((a.transpose(1, 2) if tA else a, b.transpose(1, 2) if tB else b, c))
+
+    def dev_time(allow_tf32):
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = allow_tf32
+        try:
+            def call(i):
+                a, b, c = views[i % len(views)]
+                if beta != 0:
+                    torch.baddbmm(c, a, b, beta=beta, alpha=1.0, out=c)
+                else:
+                    torch.bmm(a, b, out=c)
+            for i in range(min(3, calls)):
+                call(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(calls):
+                call(i)
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / calls
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+    sg = dev_time(False)
+    out["cublas_sgemm_ms"] = round(sg, 4)
+    out["x_vs_cublas_sgemm"] = round(sg / our_ms, 2)
+    if mode == 1:
+        tf = dev_time(True)
+        out["cublas_tf32_ms"] = round(tf, 4)
+        out["x_vs_cublas_tf32"] = round(tf / our_ms, 2)
+    if cpu and mode == 0:        # once per shape, not per math mode
+        a, b, c = (t.cpu() for t in views[0])
+        big = 2.0 * M * N * K * batch > 2e12
+        reps, warm = (1, 0) if big else (5, 3)
+
+        def cpu_time(fn):
+            for _ in range(warm):
+                fn()
+            ts = []
+            for _ in range(reps):
+                t0 = time.perf_counter()
+                fn()
+                ts.append(time.perf_counter() - t0)
+            return _median(ts) * 1e3
+        if batch == 1:
+            fn = (lambda: torch.addmm(c[0], a[0], b[0], beta=beta, alpha=1.0, out=c[0])) if beta != 0 else \
+                 (lambda: torch.mm(a[0], b[0], out=c[0]))
+            out["mkl_ms"] = round(cpu_time(fn), 3)
+        else:
+            def loop():
+                for i in range(batch):
+                    torch.mm(a[i], b[i], out=c[i])
+            out["mkl_serial_loop_ms"] = round(cpu_time(loop), 3)
+            out["mkl_ms"] = round(cpu_time(lambda: torch.bmm(a, b, out=c)), 3)
+        out["mkl_runs"] = "one run, no warm-up" if big else "median of 5 after 3 warm-ups"
+        out["x_vs_mkl"] = round(out["mkl_ms"] / our_ms, 1)
+    return out
 
 
 def sharded_gemm(w, torch, world, rank, barrier, max_over_ranks, calls=5):
@@ -349,6 +529,38 @@ def dense_and_attention_table(w, torch, peaks):
               4.0 * (2 * M * N + 2 * M * K + 2 * K * N + N), sets,
               lambda d: lib.snb200_dense_bwd(h, 1, M, K, N, P(d["x"]), P(d["W"]), P(d["dy"]), act, P(d["y"]), zarg(d),
                                              ctypes.c_float(1.0), P(d["dz"]), P(d["dx"]), P(d["dW"]), P(d["db"])))
+    # what Linear + ActivationLayer do on the GPU today (Prod/Layers/Linear.cs:125-132, ActivationLayer.cs:32-38):
+    # cuBLAS sgemm (default math), a bias pass and an activation pass -- library comparators, bench only
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        def unfused_fwd(d):
+            torch.mm(d["x"], d["W"], out=d["y"])
+            d["y"].add_(d["b"])
+            torch.relu_(d["y"])
+            return 0
+        timed("cfg3 UNFUSED reference sequence fwd: cuBLAS sgemm + bias pass + ReLU pass (comparator)", 2.0 * M * K * N,
+              4.0 * (M * K + K * N + N + M * N), sets, unfused_fwd)
+        out[-1]["mode"] = "cuBLAS fp32"
+
+        def unfused_bwd(d):
+            torch.mul(d["dy"], (d["y"] > 0), out=d["dz"])           # activation backward pass
+            torch.mm(d["x"].t(), d["dz"], out=d["dW"])              # dW
+            torch.sum(d["dz"], 0, out=d["db"])                      # bias gradient pass
+            torch.mm(d["dz"], d["W"].t(), out=d["dx"])              # dx
+            return 0
+        timed("cfg3 UNFUSED reference sequence bwd: ReLU' pass + 2 cuBLAS sgemm + column-sum pass (comparator)",
+              4.0 * M * K * N, 4.0 * (2 * M * N + 2 * M * K + 2 * K * N + N), sets, unfused_bwd)
+        out[-1]["mode"] = "cuBLAS fp32"
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    # the same sequence through this library's own separate entry points (Dot, bias add, activation)
+    def own_unfused_fwd(d):
+        st = lib.snb200_gemm(h, 0, 0, M, K, K, N, ctypes.c_float(1.0), P(d["x"]), P(d["W"]), ctypes.c_float(0.0), P(d["y"]))
+        st = st or lib.snb200_bias_add(h, M, N, P(d["b"]), P(d["y"]))
+        return st or lib.snb200_activation_fwd(h, ACT_RELU, M * N, P(d["y"]), P(d["y"]))
+    timed("cfg3 unfused through this library: snb200_gemm + bias_add + activation_fwd (3 launches)", 2.0 * M * K * N,
+          4.0 * (M * K + K * N + N + M * N), sets, own_unfused_fwd)
     B, T, E = 256, 128, 64
     asets = []
     for _ in range(8):    # 8 x 42 MB
@@ -396,18 +608,15 @@ def dense_and_attention_table(w, torch, peaks):
     return out
 
 
-def per_shape_table(w, torch, peaks, large):
+def per_shape_table(w, torch, peaks, large, cpu=True):
     """TFLOP/s, roofline fraction and error vs fp64 of every Dot / batched shape in benchmark configs 1-4
     (`large` false) or of the 16384^3 product of config 5 (`large` true: 35 ms launches that drive the GPU into its
     power cap, so they run after the short kernels)."""
-    import numpy as np
-    from oracle import sharpnet_oracle as orc
     from sharpnet_b200 import MATH_3XTF32, MATH_TF32
-    from sharpnet_b200.tensor import GPUTensor
     out = []
 
     def one(name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows=64):
-        out.append(time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows))
+        out.append(time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows, cpu=cpu))
 
     if large:
         # the opt-in TF32 + bf16 cross-term mode next to 3xTF32 on the layout it is implemented for
@@ -431,6 +640,73 @@ def per_shape_table(w, torch, peaks, large):
         one("cfg4b 256x4096x2048 NN (LSTM gates)", 256, 4096, 2048, False, False, 0.0, 1, -0.1, 0.1, mode)
     w.set_math_mode(MATH_3XTF32)
     return out
+
+
+def cublas_tf32_rate(torch, seconds):
+    """cuBLAS TF32 on 8192^3 through torch.matmul: best of 10 single calls (seconds = 0) or the average rate of
+    back-to-back calls for `seconds` -- the two figures the pool's bf16 peak file is made of, for TF32."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        n = 8192
+        a, b = torch.randn(n, n, device="cuda"), torch.randn(n, n, device="cuda")
+        c = torch.empty(n, n, device="cuda")
+        for _ in range(3):
+            torch.mm(a, b, out=c)
+        torch.cuda.synchronize()
+        flops = 2.0 * n ** 3
+        if seconds <= 0:
+            best = 0.0
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                torch.mm(a, b, out=c)
+                e1.record()
+                torch.cuda.synchronize()
+                best = max(best, flops / e0.elapsed_time(e1) / 1e9)
+            return best
+        done, t_ms = 0, 0.0
+        while t_ms < seconds * 1e3:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(100):
+                torch.mm(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            t_ms += e0.elapsed_time(e1)
+            done += 100
+        return done * flops / t_ms / 1e9
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def recorded_traffic(rows_per_gpu):
+    """DRAM bytes per GEMM launch of the step, from the committed ncu capture of the step's eight GEMMs on a small
+    case (profiles/mlp_step_gemm_dram_traffic.md: a few launches of one kernel, a few hundred MB on the device),
+    scaled to this run's rows per GPU: every GEMM of the step has the batch rows as its M or its K, and the kernel
+    walks both in blocks, so its traffic grows in proportion to them.  null when no capture is committed."""
+    path = os.path.join(ROOT, "profiles", "mlp_step_gemm_dram_traffic.md")
+    alg = None
+    try:
+        rec = None
+        for ln in open(path):
+            if ln.startswith("TRAFFIC_JSON "):
+                rec = json.loads(ln[len("TRAFFIC_JSON "):])
+        if rec is None:
+            raise ValueError("no TRAFFIC_JSON line")
+        scale = rows_per_gpu / rec["rows"]
+        r = rows_per_gpu
+        d = DIMS
+        # algorithmic bytes of the 8 GEMMs: each operand touched once
+        gemms = [(r, d[1], d[0]), (r, d[2], d[1]), (r, d[3], d[2]), (d[3], d[2], r), (r, d[2], d[3]), (d[2], d[1], r),
+                 (r, d[1], d[2]), (d[1], d[0], r)]
+        alg = sum(4.0 * (m * k + k * n + m * n) for m, n, k in gemms) / len(gemms)
+        return {"traffic": rec["dram_bytes_per_launch"] * scale, "algorithmic_bytes_per_launch": alg,
+                "traffic_source": f"profiles/mlp_step_gemm_dram_traffic.md: ncu dram__bytes_read.sum + dram__bytes_write.sum "
+                                  f"averaged over the step's 8 GEMM launches at {rec['rows']} rows, x {scale:g} for "
+                                  f"{rows_per_gpu} rows (traffic grows with the rows: they are M or K of every GEMM)"}
+    except (OSError, ValueError, KeyError) as e:
+        return {"traffic": None, "algorithmic_bytes_per_launch": alg, "traffic_source": f"no committed capture ({e})"}
 
 
 def run_ours(args):
@@ -488,14 +764,25 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
+    # ---- is the data-parallel result right?  checked before anything is timed, at every N
+    dp = dp_check(w, torch, dist, world, rank, reducer, compute_stream)
+    if rank == 0:
+        print(f"dp_check: {dp}", file=sys.stderr)
+
+    # ---- the tensor roofline's denominator, measured the way the pool's bf16 peak was: cuBLAS TF32 8192^3, best of
+    # 10 on the still cool GPU (burst); the 4-second back-to-back figure (sustained) is taken after the timed steps
+    tf32_peak = None
+    if rank == 0 and world == 1 and not args.no_shapes:
+        tf32_peak = {"burst_tflops": cublas_tf32_rate(torch, seconds=0.0)}
+
     # ---- isolated kernels first (N = 1): every shape of configs 1-5, the Dense and attention entry points and the
     # bandwidth-bound companions, each timed alone before the long step heats the GPU into its power cap
     shapes = companions = None
     if world == 1 and not args.no_shapes:
-        shapes = per_shape_table(w, torch, peaks, large=False)
+        shapes = per_shape_table(w, torch, peaks, large=False, cpu=not args.no_cpu)
         shapes = shapes + dense_and_attention_table(w, torch, peaks)
         companions = companion_table(w, torch, peaks)
-        shapes = shapes + per_shape_table(w, torch, peaks, large=True)
+        shapes = shapes + per_shape_table(w, torch, peaks, large=True, cpu=not args.no_cpu)
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
 
@@ -539,7 +826,7 @@ def run_ours(args):
     # Every step's x and upstream gradient are copied from pinned host memory inside the timed region;
     # the copy of step i+1 runs on a copy stream while step i computes (double-buffered staging).
     from sharpnet_b200.data_parallel import HostStaging
-    staging = HostStaging(stack, x_host, dy_host, compute_stream)
+    staging = HostStaging(stack, x_host, dy_host)
 
     def e2e_loop(n):
         staging.issue(0)
@@ -562,30 +849,21 @@ def run_ours(args):
     h2d = (x_host.numel() + dy_host.numel()) * 4
     d2h = sum(t.numel() for t in db_host) * 4
 
-    # context for the tensor roofline: what cuBLAS TF32 (the library kernel for this arithmetic) sustains right now
-    tf32_live = None
-    if rank == 0 and not args.no_shapes:
-        prev = torch.backends.cuda.matmul.allow_tf32
-        torch.backends.cuda.matmul.allow_tf32 = True
-        a8 = torch.randn(8192, 8192, device="cuda"); b8 = torch.randn(8192, 8192, device="cuda")
-        for _ in range(3):
-            a8 @ b8
-        torch.cuda.synchronize()
-        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        c0.record()
-        for _ in range(10):
-            a8 @ b8
-        c1.record()
-        torch.cuda.synchronize()
-        tf32_live = 10 * 2 * 8192 ** 3 / c0.elapsed_time(c1) / 1e9
-        torch.backends.cuda.matmul.allow_tf32 = prev
-        del a8, b8
-    cpu = None
+    staging.close()
+    # the sustained half of the TF32 peak: cuBLAS TF32 8192^3 back to back for 4 s, on the GPU the steps have heated
+    if tf32_peak is not None:
+        tf32_peak["sustained_tflops"] = cublas_tf32_rate(torch, seconds=4.0)
+        tf32_peak["how"] = ("torch.matmul fp32 with TF32 allowed (cuBLAS), 8192^3, 2*N^3 flops: best of 10 single calls "
+                            "before the tables (burst), back to back for 4 s after the timed steps (sustained)")
+    cpu = parity = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        v, t = time_cpu(CPU_SAMPLE_ROWS, 3)
+        v, t, inputs, cpu_results = time_cpu(CPU_SAMPLE_ROWS, 3)
         cpu = {"value": v, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                "sample": f"{CPU_SAMPLE_ROWS} of {GLOBAL_BATCH} batch rows of the same step, MKL sgemm via torch CPU, "
                          f"median of 3 ({t:.2f} s each)"}
+        # the device's step on those same rows against what the CPU leg computed
+        parity = step_parity(w, torch, inputs, cpu_results)
+        print(f"parity: {parity}", file=sys.stderr)
     if rank == 0:
         peak3 = peaks["bf16_sustained"] / 2 / 3
         achieved = gemm_flops / gemm_ms / 1e9   # per-GPU rate of the GEMM kernel (this rank's shard)
@@ -599,27 +877,32 @@ def run_ours(args):
             "gpu_launches": launches * world,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak3, "unit": "TFLOP/s",
                          "frac": achieved / peak3,
-                         # DRAM bytes per GEMM launch of this step from the ncu launch list (one-pass metrics on the
-                         # same command): 3.65 GB read + 0.59 GB written on average; algorithmic bytes 1.89 GB
-                         "traffic": 4.24e9 if world == 1 else None, "algorithmic_bytes_per_launch": 1.89e9,
+                         **recorded_traffic(rows),
                          "kernel": "umma2_gemm_kernel (CTA-pair tcgen05 GEMM, 3xTF32), the 8 GEMM launches of the step",
                          "peak_source": f"{peaks['src']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32) / 3 "
                                         "(three TF32 products per fp32 product); flops counted once (2*M*N*K)",
                          "gemm_ms_per_step": gemm_ms,
                          "gemm_timing": "CUDA-event pairs recorded by the library around every GEMM of the timed steps, "
                                         "on the launching stream",
-                         "cublas_tf32_8192_tflops_live": tf32_live,
+                         "measured_tf32": tf32_peak,
+                         "frac_vs_measured_tf32_sustained": (
+                             None if not tf32_peak else achieved / (tf32_peak["sustained_tflops"] / 3.0)),
+                         "frac_vs_measured_tf32_burst": (
+                             None if not tf32_peak else achieved / (tf32_peak["burst_tflops"] / 3.0)),
                          # nominal dense TF32 rate (1100 TFLOP/s at 1965 MHz) scaled to the SM clock sampled during the
                          # timed steps, / 3: what the tensor cores can deliver to this arithmetic under the power cap
                          "nominal_tf32_at_sampled_clock_over_3": (
                              None if not clocks or not clocks.get("sm_mhz")
                              else 1100.0 * clocks["sm_mhz"] / 1965.0 / 3.0),
-                         "note": "the peak is a proxy (no TF32 figure is measured for this pool): half of the measured "
-                                 "cuBLAS bf16 rate, / 3.  A fraction above 1 means this kernel keeps the tensor pipe busier "
-                                 "than cuBLAS does in bf16 or TF32 (see cublas_tf32_8192_tflops_live / 3); the bound that "
-                                 "remains is the SM clock under the 1000 W power cap"},
+                         "note": "`peak` is the pool's measured cuBLAS bf16 rate / 2 / 3 (a proxy: the pool file holds no "
+                                 "TF32 figure); measured_tf32 is cuBLAS TF32 on this GPU in this run, and the two "
+                                 "frac_vs_measured_tf32_* use it / 3.  A fraction above 1 means this kernel keeps the tensor "
+                                 "pipe busier than cuBLAS does; what remains is the SM clock under the 1000 W power cap"},
             "cpu_baseline": cpu,
+            "dp_check": dp,
         }
+        if parity is not None:
+            line["parity"] = parity
         if shapes is not None:
             line["shapes"] = shapes
             line["companions"] = companions
@@ -630,6 +913,8 @@ def run_ours(args):
         reducer.close()
     if world > 1:
         dist.destroy_process_group()
+    if rank == 0 and ((dp is not None and not dp["ok"]) or (parity is not None and not parity["ok"])):
+        raise SystemExit("bench: a correctness check failed (dp_check / parity in the line above)")
 
 
 def main():
@@ -640,8 +925,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape table (N = 1 only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--case", default=None, choices=["gemm", "sdpa"],
-                    help="time a single Dot shape instead of the training step (used for profiling)")
+    ap.add_argument("--case", default=None, choices=["gemm", "sdpa", "step"],
+                    help="time a single Dot shape, one attention core or the training step on --rows batch rows "
+                         "instead of the full step (small cases for profiling)")
+    ap.add_argument("--rows", type=int, default=8192, help="--case step: batch rows on the device")
     ap.add_argument("--mnk", type=int, nargs=3, default=[4096, 4096, 4096])
     ap.add_argument("--trans", default="NN", help="NN, NT, TN or TT")
     ap.add_argument("--beta", type=float, default=0.0)
@@ -661,8 +948,32 @@ def main():
         from sharpnet_b200.tensor import GPUWrapper
         M, N, K = args.mnk
         r = time_gemm_shape(GPUWrapper.FromDeviceId(0), torch, _peaks(), "case", M, N, K, args.trans[0] == "T",
-                            args.trans[1] == "T", args.beta, args.batch, -1.0, 1.0, args.math, min_calls=args.calls)
+                            args.trans[1] == "T", args.beta, args.batch, -1.0, 1.0, args.math, min_calls=args.calls,
+                            cpu=False, compare=False)
         _emit(json.dumps(r))
+    elif args.case == "step":
+        # the training step of the benchmark on a fraction of its rows: 8 GEMM launches per step
+        import torch
+        from oracle import sharpnet_oracle as orc
+        from sharpnet_b200.data_parallel import MLP_ACTS, DenseStack, mlp_step_flops, training_step
+        from sharpnet_b200.tensor import GPUWrapper
+        w = GPUWrapper.FromDeviceId(0)
+        w.set_math_mode(args.math)
+        stack = DenseStack(w, args.rows, DIMS, MLP_ACTS, [orc.glorot_uniform((DIMS[i + 1], DIMS[i]), 14 + i) for i in range(3)])
+        stack.x.storage.normal_()
+        stack.dy.storage.normal_()
+        training_step(stack)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.calls):
+            training_step(stack)
+        e1.record()
+        torch.cuda.synchronize()
+        w.check_device_status()
+        ms = e0.elapsed_time(e1) / args.calls
+        _emit(json.dumps({"shape": f"MLP training step on {args.rows} rows", "calls": args.calls, "ms": round(ms, 4),
+                          "tflops": round(mlp_step_flops(args.rows, DIMS) / ms / 1e9, 2)}))
     elif args.case == "sdpa":
         # one attention core, forward + backward: --batch heads, --mnk q_steps v_steps head_dim
         import ctypes

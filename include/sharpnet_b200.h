@@ -91,6 +91,11 @@ const char* snb200_last_error_string(snb200_handle_t handle);
 /* Waits for the handle's stream and returns EXECUTION_FAILED if a kernel reported a
  * device-side pipeline time-out since the last check. */
 int snb200_check_device_status(snb200_handle_t handle);
+/* Runs the failure path of the tensor-core kernels on purpose, harmlessly (no counterpart in SharpNet): one small
+ * kernel waits on a barrier that nothing signals, with a limit of limit_us microseconds (1 .. 100000) instead of
+ * the kernels' two seconds, gives up, records the time-out in the handle's error word and returns normally.  The
+ * next snb200_check_device_status reports EXECUTION_FAILED once; the handle and the context stay usable. */
+int snb200_selftest_wait_timeout(snb200_handle_t handle, int limit_us);
 /* Number of kernels this handle has launched so far, and the name of the kernel family chosen
  * by the last compute call ("umma_3xtf32", "umma_tf32", "simt", "skinny", ...). */
 int snb200_get_launch_count(snb200_handle_t handle, long long* count);
@@ -114,7 +119,9 @@ int snb200_gemm_timing_end(snb200_handle_t handle, double* total_ms, int* gemm_c
  *        tensor core truncate the raw fp32 words itself (0, default);
  * key 7: 1 launches the tensor-core kernels without programmatic dependent launch (by default their set-up
  *        overlaps the tail of the previous kernel in the stream; they wait for its completion before touching
- *        global memory). */
+ *        global memory);
+ * key 8: n > 1 cuts K of the tiles of a partly filled last wave exactly n times (one of 2..8, 10, 12, 16),
+ *        whatever the time estimate says (tests of the reduction pass). */
 int snb200_set_tuning(snb200_handle_t handle, int key, int value);
 
 /* ---- Tensor.Dot -----------------------------------------------------------------------------
@@ -160,7 +167,11 @@ int snb200_dense_fwd(snb200_handle_t handle, int w_layout, int M, int K, int N, 
  * y is the activation output (needed unless act is IDENTITY), z the pre-activation (needed for
  * SWISH only).  dz_scratch is a caller-provided [M x N] buffer (the ActivationLayer's dx in
  * SharpNet); it may be NULL when act is IDENTITY.  dx may be NULL (previous layer is the input,
- * Linear.cs:184-187); db may be NULL (layer without bias). */
+ * Linear.cs:184-187); db may be NULL (layer without bias).  dW may be NULL as well: the call then skips
+ * the weight-gradient product, so a host that overlaps the gradient sum of several replicas with the
+ * backward pass can run the two products of a layer as two calls (dW and db first, start their
+ * all-reduce, then a second call with act = IDENTITY on the dz it already holds for dx alone), or
+ * leave the smallest weight gradient for the very end of the step.  At least one output is required. */
 int snb200_dense_bwd(snb200_handle_t handle, int w_layout, int M, int K, int N, const float* x, const float* W,
                      const float* dy, int act, const float* y, const float* z, float dW_multiplier,
                      float* dz_scratch, float* dx, float* dW, float* db);
@@ -198,7 +209,10 @@ int snb200_bias_grad(snb200_handle_t handle, int M, int N, const float* dy, floa
  * image (held by every GPU that loads the library until the process exits), which limits the
  * matrix to SNB200_NOALLOC_MAX_COLUMNS columns; wider matrices are refused with NOT_SUPPORTED and
  * a message.  The device address of that array is looked up on the first call on each device, so
- * make that first call before starting any stream capture.  All calls on a device share the
+ * make that first call before starting any stream capture -- and before the host's pool takes the
+ * device memory: with CUDA's default lazy module loading that first call is also what loads the
+ * library's device image (the array and the kernels) onto the device, the one moment that needs free
+ * device memory (ALLOC_FAILED otherwise; CUDA_MODULE_LOADING=EAGER moves the load to start-up).  All calls on a device share the
  * array: calls queued on one stream are safe, calls that overlap on the GPU race.  Nothing needs
  * clearing between calls (every word read back is written first by the same call).
  * cuda_stream is a cudaStream_t (NULL = legacy default stream); err, when not NULL, receives the
@@ -251,7 +265,9 @@ int snb200_sdpa_bwd(snb200_handle_t handle, int batch, int q_steps, int v_steps,
  * The permutations are not passes of their own: the product before each one stores its result already permuted.
  * The kernels of one call are queued back to back on the handle's stream, nothing is allocated.
  *   Q [batch, q_steps, embed_dim]; K, V [batch, v_steps, embed_dim]; y [batch, q_steps, embed_dim];
- *   embed_dim must equal num_heads * value_dim (the layer uses out_proj_weight that way, :121-126,236).
+ *   embed_dim must equal num_heads * value_dim (the layer uses out_proj_weight that way, :121-126,236), and
+ *   key_dim must equal value_dim (NOT_SUPPORTED otherwise): the layer's attention core multiplies Q by K^T over
+ *   key_dim and takes V with the same embedding width (ScaledDotProductAttentionLayer.cs:56-60).
  * Weights are [out, in] rows (w_layout 0, Linear.cs:125-132) or [in, out] (w_layout 1); biases may be NULL.
  * snb200_mha_state holds what the layer keeps between the two passes (Q_heads_T, K_heads_T, V_heads_T,
  * attention_heads_T, weights_buffer; :73-77), caller-provided:
@@ -326,7 +342,36 @@ int snb200_comm_get_unique_id(void* id_128_bytes);
 int snb200_comm_init_rank(snb200_handle_t handle, int n_ranks, int rank, const void* id_128_bytes);
 int snb200_comm_init_all(snb200_handle_t* handles, int n);
 int snb200_allreduce_sum(snb200_handle_t handle, float* buf, long long count);
+/* The same for n buffers at once (a layer's dW and db): one NCCL group, hence one collective launch, instead of
+ * one launch per buffer -- for the small bias gradients the launch is all the cost. */
+int snb200_allreduce_sum_group(snb200_handle_t handle, int n, float* const* bufs, const long long* counts);
 int snb200_comm_destroy(snb200_handle_t handle);
+
+/* ---- mini-batch staging ------------------------------------------------------------------------
+ * The step before the path: SharpNet copies every mini-batch from pinned host memory to the device on its one
+ * stream before it runs the step (Prod/Networks/Network.cs:1211-1258: x_miniBatch_cpu.CopyTo(x_miniBatch);
+ * Prod/GPU/GpuTensor.cs:68-80 InitializeFromHostPinnedMemory -> cuMemcpyHtoDAsync_v2; pinning:
+ * Prod/CPU/HostPinnedMemory.cs).  A stager runs those copies on a stream of its own, `slots`-fold buffered, so
+ * that the copy of mini-batch i+1 overlaps the step on mini-batch i.  Device buffers and host memory belong to
+ * the caller (one set of device buffers per slot).  Per step i, with s = i % slots:
+ *   snb200_stager_issue(st, s, ...)   queue the host->device copies of that step's inputs into slot s; the copy
+ *                                     stream first waits until the step that last read slot s has finished;
+ *   snb200_stager_acquire(st, s)      the handle's stream waits for those copies (no host synchronisation);
+ *   ... the step's compute calls on the handle, reading the slot's device buffers ...
+ *   snb200_stager_release(st, s)      marks on the handle's stream where the slot's last reader ends.
+ * Issue step i+1 before computing step i to get the overlap.  Copies are queued one cudaMemcpyAsync per pair. */
+typedef struct snb200_stager* snb200_stager_t;
+int snb200_stager_create(snb200_handle_t handle, int slots, snb200_stager_t* stager);
+int snb200_stager_destroy(snb200_stager_t stager);
+int snb200_stager_issue(snb200_stager_t stager, int slot, int n_copies, void* const* device_dst,
+                        const void* const* host_src, const long long* bytes);
+int snb200_stager_acquire(snb200_stager_t stager, int slot);
+int snb200_stager_release(snb200_stager_t stager, int slot);
+/* Page-locks / unlocks caller-owned host memory so that the copies above run asynchronously at full speed: what
+ * HostPinnedMemory does for a managed array (Prod/CPU/HostPinnedMemory.cs:17-21; there the GC pin, here the CUDA
+ * registration the async copy needs). */
+int snb200_host_pin(void* host_ptr, long long bytes);
+int snb200_host_unpin(void* host_ptr);
 
 #ifdef __cplusplus
 }

@@ -18,7 +18,8 @@ ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
 ACT_SOFTMAX = 1000   # snb200_dense_fwd only
 W_OUT_IN, W_IN_OUT = 0, 1
 LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
-TUNE_FORCE_PATH, TUNE_FORCE_BN, TUNE_REWRITE_HI, TUNE_CHUNK_K, TUNE_PAIR, TUNE_SPLITK, TUNE_VARIANT, TUNE_PDL = range(8)
+(TUNE_FORCE_PATH, TUNE_FORCE_BN, TUNE_REWRITE_HI, TUNE_CHUNK_K, TUNE_PAIR, TUNE_SPLITK, TUNE_VARIANT, TUNE_PDL,
+ TUNE_FORCE_SPLITS) = range(9)
 
 _c = ctypes
 _H = _c.c_void_p
@@ -85,7 +86,16 @@ SIGNATURES = {
     "snb200_comm_init_rank": (_I, [_H, _I, _I, _P]),
     "snb200_comm_init_all": (_I, [_c.POINTER(_H), _I]),
     "snb200_allreduce_sum": (_I, [_H, _P, _L]),
+    "snb200_allreduce_sum_group": (_I, [_H, _I, _c.POINTER(_P), _c.POINTER(_L)]),
     "snb200_comm_destroy": (_I, [_H]),
+    "snb200_selftest_wait_timeout": (_I, [_H, _I]),
+    "snb200_stager_create": (_I, [_H, _I, _c.POINTER(_P)]),
+    "snb200_stager_destroy": (_I, [_P]),
+    "snb200_stager_issue": (_I, [_P, _I, _I, _c.POINTER(_P), _c.POINTER(_P), _c.POINTER(_L)]),
+    "snb200_stager_acquire": (_I, [_P, _I]),
+    "snb200_stager_release": (_I, [_P, _I]),
+    "snb200_host_pin": (_I, [_P, _L]),
+    "snb200_host_unpin": (_I, [_P]),
 }
 
 _lib = None

@@ -369,6 +369,16 @@ __device__ __forceinline__ bool epilogue_fold_c(const UmmaParams& p, float (&acc
 //                     cudnnSoftmaxBackward applies (Prod/GPU/GpuTensor.cs:445-490)
 __device__ __forceinline__ void row_pair_barrier(int q) { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); }
 
+// Both warps of a row pair must take the same decision before a row operation, or one would wait at the named
+// barrier for a partner that has left: each contributes its own `ok` (every wait behind it is bounded, so both
+// always arrive here) and both continue only if both are.  Slot use: [group][q * 32 + lane], like the exchanges.
+__device__ __forceinline__ bool row_pair_all(float* xch, int q, int group, int lane, bool ok) {
+  row_pair_barrier(q);
+  xch[group * 128 + q * 32 + lane] = ok ? 1.0f : 0.0f;
+  row_pair_barrier(q);
+  return ok && xch[(group ^ 1) * 128 + q * 32 + lane] != 0.0f;
+}
+
 // This lane's value against the value of the lane that holds the other half of the row.
 __device__ __forceinline__ float row_pair_exchange(float* xch, int q, int group, int lane, float mine) {
   row_pair_barrier(q);                       // the partner has read what the slot held before
@@ -684,6 +694,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
       }
+      if (ROWOP && T::EPI_GROUPS == 2) ok = row_pair_all(row_xch, q, (warp - 4) >> 2, lane, ok);
       if (!ok) break;
       float alpha = p.alpha;
       const float* bias = p.bias;
@@ -857,12 +868,14 @@ static __global__ void __launch_bounds__(256) tail_reduce_kernel(const TailReduc
       for (int e = 0; e < 4; ++e) o[e] = act_forward(p.act, o[e]);
       *reinterpret_cast<float4*>(p.C + off) = make_float4(o[0], o[1], o[2], o[3]);
     } else {
+      // a mapped result whose inner run d is not a multiple of 4: the four columns may lie in different runs
       for (int e = 0; e < 4 && col + e < p.N; ++e) {
+        const long long oe = p.omap.on ? out_offset(p.omap, b, row, col + e) : off + e;
         float v = o[e];
-        if (p.beta != 0.0f) v = fmaf(p.beta, p.C[off + e], v);
+        if (p.beta != 0.0f) v = fmaf(p.beta, p.C[oe], v);
         if (p.bias) v += __ldg(p.bias + col + e);
-        if (p.Z) p.Z[off + e] = v;
-        p.C[off + e] = act_forward(p.act, v);
+        if (p.Z) p.Z[oe] = v;
+        p.C[oe] = act_forward(p.act, v);
       }
     }
   }

@@ -9,6 +9,12 @@
 // the slab partial sums that the column reduction needs live in a fixed array in the library's own
 // device image.
 //
+// One moment does need free device memory: the library's device image (the array and the kernels) is loaded
+// onto a device on first use -- with CUDA's default lazy loading, in the first call of this entry point on that
+// device.  That first call must therefore come before the host's pool takes the memory (it is also the call that
+// must precede any stream capture), or the process runs with CUDA_MODULE_LOADING=EAGER; an out-of-memory at that
+// point is reported as ALLOC_FAILED with that advice.
+//
 // The array is 1 MiB per GPU that loads the library, for the life of the process.  All calls on a
 // device share it, so two calls that overlap on the GPU (different streams, or different host
 // threads) race on it; calls on one stream are safe.  The kernels overwrite every word of it that
@@ -63,7 +69,15 @@ extern "C" int snb200_bias_grad_noalloc(int device_id, void* cuda_stream, int M,
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     if (!g_scratch_addr[device_id]) {
       float* p = nullptr;
+      // With CUDA's lazy module loading this is where the device image that holds the array (1 MiB plus the
+      // kernels) is loaded onto the device -- the one moment this entry point needs free device memory.
       e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+      if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return report(err, err_len, SNB200_STATUS_ALLOC_FAILED,
+                      "no device memory left to load the library's device image: make the first call on a device "
+                      "before the host's pool takes the memory, or run with CUDA_MODULE_LOADING=EAGER");
+      }
       if (e != cudaSuccess || !p)
         return report(err, err_len, SNB200_STATUS_NOT_INITIALIZED, "cudaGetSymbolAddress: ", cudaGetErrorString(e));
       int sms = 0;

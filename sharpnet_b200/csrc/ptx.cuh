@@ -69,7 +69,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` lives in shared memory and is raised by whichever
 // wait gives up first; returns false when the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
@@ -79,9 +80,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > SNB_WAIT_TIMEOUT_NS) { *abort_flag = 1; return false; }
+      else if (now - t0 > limit_ns) { *abort_flag = 1; return false; }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, SNB_WAIT_TIMEOUT_NS);
 }
 
 // Warp-wide wait: lane 0 spins, the other lanes park at the warp barrier and then observe the

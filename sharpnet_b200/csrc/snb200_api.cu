@@ -18,7 +18,7 @@
 using namespace snb;
 
 // ------------------------------------------------------------------------------------ handle
-enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_COUNT = 8 };
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_FORCE_SPLITS = 8, TUNE_COUNT = 9 };
 
 struct snb200_context {
   int device;
@@ -182,6 +182,34 @@ extern "C" int snb200_check_device_status(snb200_handle_t h) {
     return fail(h, SNB200_STATUS_EXECUTION_FAILED, "a tensor-core pipeline wait timed out on the device");
   }
   return 0;
+}
+
+// The failure path of the tensor-core kernels, run on purpose and harmlessly: one warp waits on an mbarrier that
+// nothing ever arrives at, with a short limit; the wait gives up, raises the CTA's abort flag, and the kernel leaves
+// through the same teardown as the GEMM kernels (error word set, normal return).
+static __global__ void wait_timeout_selftest_kernel(int* error_word, unsigned long long limit_ns) {
+  __shared__ uint64_t never_signalled;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&never_signalled, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  volatile int* abortp = &abort_flag;
+  if (threadIdx.x == 0) mbar_wait_limit(&never_signalled, 0, abortp, limit_ns);
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag) atomicExch(error_word, 1);
+}
+
+extern "C" int snb200_selftest_wait_timeout(snb200_handle_t h, int limit_us) {
+  int st = enter(h);
+  if (st) return st;
+  if (limit_us < 1 || limit_us > 100000)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "the limit must lie between 1 and 100000 microseconds");
+  wait_timeout_selftest_kernel<<<1, 32, 0, h->stream>>>(h->error_word, 1000ull * static_cast<unsigned long long>(limit_us));
+  h->launches += 1;
+  return check_launch(h, "wait_timeout_selftest_kernel launch");
 }
 
 // Launch of one of this library's kernels on the handle's stream with programmatic dependent launch: every kernel
@@ -530,6 +558,7 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
   double best_cost = 1e300;
   const int pair_mode = h->tune[TUNE_PAIR];   // 0 automatic, 1 always, 2 never
   const int forced_bn = h->tune[TUNE_FORCE_BN];
+  const int forced_splits = allow_splitk ? h->tune[TUNE_FORCE_SPLITS] : 0;
   const int cand[4] = {256, 128, 64, 32};
   const int ks_cand[11] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 16};
   const long long kb = (g.K + 31) / 32;
@@ -549,6 +578,10 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
       const double c = tc.kblock_us * ((hybrid && pair && bn >= 128) ? 0.7 : 1.0), fixed = tc.fixed_us;
       for (int j = 0; j < 11; ++j) {
         const long long ks = ks_cand[j];
+        if (forced_splits > 1) {            // tests: cut the tail tiles this many times whatever it costs
+          if (ks != forced_splits) { if (ks > forced_splits) break; continue; }
+          if (tail == 0 || kb / ks < 1) break;
+        } else
         if (ks > 1 && (!allow_splitk || tail == 0 || kb / ks < 8)) break;   // at least 256 of K per unit
         const long long tail_floats = tail * rows * bn;
         if (ks > 1 && ks * tail_floats > static_cast<long long>(h->workspace_floats)) break;
@@ -881,8 +914,10 @@ static int dense_bwd_gemms(snb200_handle_t h, int w_layout, int M, int K, int N,
     g.transB = 0; g.B = dz; g.ldb = N;
   }
   g.C = dW; g.ldc = g.N; g.alpha = dW_multiplier;
-  st = run_gemm(h, g);
-  if (st) return st;
+  if (dW) {
+    st = run_gemm(h, g);
+    if (st) return st;
+  }
   if (dx) {
     g.M = M; g.N = K; g.K = N;
     g.transA = 0; g.A = dz; g.lda = N;
@@ -954,7 +989,7 @@ static int dense_bwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, 
   if (!act_supported(act)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "activation %d is not fused", act);
   st = check_ptrs(h, x, W, dy);
   if (st) return st;
-  if (!dW) return fail(h, SNB200_STATUS_INVALID_VALUE, "dW is null");
+  if (!dW && !dx && !db) return fail(h, SNB200_STATUS_INVALID_VALUE, "dW, dx and db are all null: nothing to compute");
   const float* dz = dy;
   if (act != ACT_IDENTITY) {
     if (!y) return fail(h, SNB200_STATUS_INVALID_VALUE, "activation output y is required for this activation");
@@ -1365,6 +1400,117 @@ extern "C" int snb200_mha_bwd(snb200_handle_t h, const snb200_mha_desc* d, const
   return st;
 }
 
+// ------------------------------------------------------------------------------------ mini-batch staging
+// Host -> device copies of the next mini-batch on a stream of their own, double (or n-fold) buffered: slot s is
+// written by the copy stream and read by the handle's compute stream, and two events per slot order them --
+// `copied` (the compute stream waits for it before it reads the slot) and `consumed` (the copy stream waits for it
+// before it overwrites the slot).  The device buffers and the pinned host memory belong to the caller.
+struct snb200_stager {
+  snb200_handle_t h;
+  int slots;
+  cudaStream_t copy_stream;
+  cudaEvent_t* copied;
+  cudaEvent_t* consumed;
+  unsigned char* has_copied;
+  unsigned char* has_consumed;
+};
+
+extern "C" int snb200_stager_create(snb200_handle_t h, int slots, snb200_stager_t* out) {
+  int st = enter(h);
+  if (st) return st;
+  if (!out || slots < 1 || slots > 16) return fail(h, SNB200_STATUS_INVALID_VALUE, "1 to 16 slots");
+  *out = nullptr;
+  snb200_stager* s = static_cast<snb200_stager*>(calloc(1, sizeof(snb200_stager)));
+  if (!s) return fail(h, SNB200_STATUS_ALLOC_FAILED, "out of host memory");
+  s->h = h; s->slots = slots;
+  s->copied = static_cast<cudaEvent_t*>(calloc(slots, sizeof(cudaEvent_t)));
+  s->consumed = static_cast<cudaEvent_t*>(calloc(slots, sizeof(cudaEvent_t)));
+  s->has_copied = static_cast<unsigned char*>(calloc(slots, 1));
+  s->has_consumed = static_cast<unsigned char*>(calloc(slots, 1));
+  bool ok = s->copied && s->consumed && s->has_copied && s->has_consumed &&
+            cudaStreamCreateWithFlags(&s->copy_stream, cudaStreamNonBlocking) == cudaSuccess;
+  for (int i = 0; ok && i < slots; ++i)
+    ok = cudaEventCreateWithFlags(&s->copied[i], cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&s->consumed[i], cudaEventDisableTiming) == cudaSuccess;
+  if (!ok) {
+    snb200_stager_destroy(s);
+    return fail(h, SNB200_STATUS_ALLOC_FAILED, "could not create the copy stream or its events");
+  }
+  *out = s;
+  return 0;
+}
+
+extern "C" int snb200_stager_destroy(snb200_stager_t s) {
+  if (!s) return SNB200_STATUS_NOT_INITIALIZED;
+  cudaSetDevice(s->h->device);
+  if (s->copy_stream) { cudaStreamSynchronize(s->copy_stream); cudaStreamDestroy(s->copy_stream); }
+  for (int i = 0; i < s->slots; ++i) {
+    if (s->copied && s->copied[i]) cudaEventDestroy(s->copied[i]);
+    if (s->consumed && s->consumed[i]) cudaEventDestroy(s->consumed[i]);
+  }
+  free(s->copied); free(s->consumed); free(s->has_copied); free(s->has_consumed);
+  free(s);
+  return 0;
+}
+
+extern "C" int snb200_stager_issue(snb200_stager_t s, int slot, int n_copies, void* const* device_dst,
+                                   const void* const* host_src, const long long* bytes) {
+  if (!s) return SNB200_STATUS_NOT_INITIALIZED;
+  snb200_handle_t h = s->h;
+  int st = enter(h);
+  if (st) return st;
+  if (slot < 0 || slot >= s->slots) return fail(h, SNB200_STATUS_INVALID_VALUE, "slot %d of %d", slot, s->slots);
+  if (n_copies < 0 || (n_copies > 0 && (!device_dst || !host_src || !bytes)))
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "bad copy list");
+  for (int i = 0; i < n_copies; ++i)
+    if (bytes[i] < 0 || (bytes[i] > 0 && (!device_dst[i] || !host_src[i])))
+      return fail(h, SNB200_STATUS_INVALID_VALUE, "bad copy %d", i);
+  // the slot may still be read by the step it was staged for
+  if (s->has_consumed[slot]) SNB_CUDA(h, cudaStreamWaitEvent(s->copy_stream, s->consumed[slot], 0));
+  for (int i = 0; i < n_copies; ++i)
+    if (bytes[i] > 0)
+      SNB_CUDA(h, cudaMemcpyAsync(device_dst[i], host_src[i], static_cast<size_t>(bytes[i]), cudaMemcpyHostToDevice,
+                                  s->copy_stream));
+  SNB_CUDA(h, cudaEventRecord(s->copied[slot], s->copy_stream));
+  s->has_copied[slot] = 1;
+  return 0;
+}
+
+extern "C" int snb200_stager_acquire(snb200_stager_t s, int slot) {
+  if (!s) return SNB200_STATUS_NOT_INITIALIZED;
+  snb200_handle_t h = s->h;
+  int st = enter(h);
+  if (st) return st;
+  if (slot < 0 || slot >= s->slots) return fail(h, SNB200_STATUS_INVALID_VALUE, "slot %d of %d", slot, s->slots);
+  if (!s->has_copied[slot]) return fail(h, SNB200_STATUS_INVALID_VALUE, "nothing was staged into slot %d", slot);
+  SNB_CUDA(h, cudaStreamWaitEvent(h->stream, s->copied[slot], 0));
+  return 0;
+}
+
+extern "C" int snb200_stager_release(snb200_stager_t s, int slot) {
+  if (!s) return SNB200_STATUS_NOT_INITIALIZED;
+  snb200_handle_t h = s->h;
+  int st = enter(h);
+  if (st) return st;
+  if (slot < 0 || slot >= s->slots) return fail(h, SNB200_STATUS_INVALID_VALUE, "slot %d of %d", slot, s->slots);
+  SNB_CUDA(h, cudaEventRecord(s->consumed[slot], h->stream));
+  s->has_consumed[slot] = 1;
+  return 0;
+}
+
+extern "C" int snb200_host_pin(void* host_ptr, long long bytes) {
+  if (!host_ptr || bytes <= 0) return SNB200_STATUS_INVALID_VALUE;
+  cudaError_t e = cudaHostRegister(host_ptr, static_cast<size_t>(bytes), cudaHostRegisterPortable);
+  if (e == cudaErrorHostMemoryAlreadyRegistered) { cudaGetLastError(); return 0; }
+  return e == cudaSuccess ? 0 : SNB200_STATUS_ALLOC_FAILED;
+}
+extern "C" int snb200_host_unpin(void* host_ptr) {
+  if (!host_ptr) return SNB200_STATUS_INVALID_VALUE;
+  cudaError_t e = cudaHostUnregister(host_ptr);
+  if (e != cudaSuccess) cudaGetLastError();
+  return e == cudaSuccess ? 0 : SNB200_STATUS_INVALID_VALUE;
+}
+
 // ------------------------------------------------------------------------------------ NCCL (loaded at run time)
 struct NcclId { char bytes[128]; };
 typedef int (*nccl_get_id_t)(NcclId*);
@@ -1372,6 +1518,7 @@ typedef int (*nccl_init_rank_t)(void**, int, NcclId, int);
 typedef int (*nccl_init_all_t)(void**, int, const int*);
 typedef int (*nccl_allreduce_t)(const void*, void*, size_t, int, int, void*, cudaStream_t);
 typedef int (*nccl_destroy_t)(void*);
+typedef int (*nccl_group_t)(void);
 typedef const char* (*nccl_errstr_t)(int);
 static struct {
   void* lib;
@@ -1380,6 +1527,7 @@ static struct {
   nccl_init_all_t init_all;
   nccl_allreduce_t allreduce;
   nccl_destroy_t destroy;
+  nccl_group_t group_start, group_end;
   nccl_errstr_t errstr;
 } g_nccl;
 
@@ -1396,7 +1544,10 @@ static bool load_nccl() {
   g_nccl.allreduce = reinterpret_cast<nccl_allreduce_t>(dlsym(lib, "ncclAllReduce"));
   g_nccl.destroy = reinterpret_cast<nccl_destroy_t>(dlsym(lib, "ncclCommDestroy"));
   g_nccl.errstr = reinterpret_cast<nccl_errstr_t>(dlsym(lib, "ncclGetErrorString"));
-  if (!g_nccl.get_id || !g_nccl.init_rank || !g_nccl.init_all || !g_nccl.allreduce || !g_nccl.destroy) {
+  g_nccl.group_start = reinterpret_cast<nccl_group_t>(dlsym(lib, "ncclGroupStart"));
+  g_nccl.group_end = reinterpret_cast<nccl_group_t>(dlsym(lib, "ncclGroupEnd"));
+  if (!g_nccl.get_id || !g_nccl.init_rank || !g_nccl.init_all || !g_nccl.allreduce || !g_nccl.destroy ||
+      !g_nccl.group_start || !g_nccl.group_end) {
     dlclose(lib);
     return false;
   }
@@ -1447,6 +1598,25 @@ extern "C" int snb200_allreduce_sum(snb200_handle_t h, float* buf, long long cou
   if (count == 0) return 0;
   int r = g_nccl.allreduce(buf, buf, static_cast<size_t>(count), /*ncclFloat32*/ 7, /*ncclSum*/ 0, h->nccl_comm, h->stream);
   if (r) return nccl_fail(h, r, "ncclAllReduce");
+  return 0;
+}
+extern "C" int snb200_allreduce_sum_group(snb200_handle_t h, int n, float* const* bufs, const long long* counts) {
+  int st = enter(h);
+  if (st) return st;
+  if (n < 0 || (n > 0 && (!bufs || !counts))) return fail(h, SNB200_STATUS_INVALID_VALUE, "bad buffer list");
+  for (int i = 0; i < n; ++i)
+    if (counts[i] < 0 || (counts[i] > 0 && !bufs[i])) return fail(h, SNB200_STATUS_INVALID_VALUE, "bad buffer %d", i);
+  if (!h->nccl_comm) return fail(h, SNB200_STATUS_NOT_INITIALIZED, "no communicator on this handle");
+  int r = g_nccl.group_start();
+  if (r) return nccl_fail(h, r, "ncclGroupStart");
+  int first_error = 0;
+  for (int i = 0; i < n && !first_error; ++i)
+    if (counts[i] > 0)
+      first_error = g_nccl.allreduce(bufs[i], bufs[i], static_cast<size_t>(counts[i]), /*ncclFloat32*/ 7, /*ncclSum*/ 0,
+                                     h->nccl_comm, h->stream);
+  r = g_nccl.group_end();   // always closes the group, also after a failed call inside it
+  if (first_error) return nccl_fail(h, first_error, "ncclAllReduce");
+  if (r) return nccl_fail(h, r, "ncclGroupEnd");
   return 0;
 }
 extern "C" int snb200_comm_destroy(snb200_handle_t h) {

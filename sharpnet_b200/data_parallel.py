@@ -73,22 +73,57 @@ class DenseStack:
             check(h, st)
             src = self.y[i]
 
-    def backward(self, after_layer=None):
-        """Backward through every layer, last to first.  ``after_layer(i)`` is called right after the
-        gradients of layer ``i`` have been queued (the hook the gradient all-reduce hangs on)."""
+    def _bwd(self, i, grad, act, dz, dx, dW, db):
+        """One snb200_dense_bwd call on layer ``i``; every output is optional."""
         lib, h = self.w.lib, self.w.handle
+        src = self.x if i == 0 else self.y[i - 1]
+        p = lambda t: None if t is None else t.Pointer  # noqa: E731
+        st = lib.snb200_dense_bwd(
+            h, self.layout, self.batch, self.dims[i], self.dims[i + 1], src.Pointer, self.W[i].Pointer, grad.Pointer,
+            act, None if act == ACT_IDENTITY else self.y[i].Pointer, None, 1.0, p(dz), p(dx), p(dW), p(db))
+        check(h, st)
+
+    def backward(self, after_gradients=None, after_layer=None, defer_smallest=False):
+        """Backward through every layer, last to first.
+
+        Per layer the two products are queued as two calls: first the activation gradient with the bias
+        gradient and the weight gradient, then ``after_gradients(i)`` (the hook the gradient all-reduce hangs on:
+        the reduction starts while the layer's dx product still runs), then dx alone, then ``after_layer(i)``
+        (everything that reads W[i] is queued: the place for an optimizer step on another stream).
+
+        ``defer_smallest``: the weight-gradient product of the layer with the fewest weights is queued last
+        instead of in its turn (it depends only on that layer's dz and input, which stay in place), so that the
+        reduction nothing is left to hide behind is the smallest one.  The arithmetic is the same in any order."""
+        n = len(self.W)
+        deferred = None
+        if defer_smallest and n > 1:
+            smallest = min(range(n), key=lambda i: self.W[i].Count)
+            if smallest != 0:            # layer 0's dW is the last product anyway
+                deferred = smallest
         grad = self.dy
-        for i in reversed(range(len(self.W))):
-            src = self.x if i == 0 else self.y[i - 1]
-            st = lib.snb200_dense_bwd(
-                h, self.layout, self.batch, self.dims[i], self.dims[i + 1], src.Pointer, self.W[i].Pointer,
-                grad.Pointer, self.acts[i], None if self.acts[i] == ACT_IDENTITY else self.y[i].Pointer, None, 1.0,
-                None if self.dz[i] is None else self.dz[i].Pointer, None if i == 0 else self.dx[i].Pointer,
-                self.dW[i].Pointer, self.db[i].Pointer)
-            check(h, st)
-            if after_layer is not None:
+        dz_of = {}
+        for i in reversed(range(n)):
+            act = self.acts[i]
+            dz = grad if act == ACT_IDENTITY else self.dz[i]
+            dz_of[i] = dz
+            dx = None if i == 0 else self.dx[i]
+            if i == deferred:
+                self._bwd(i, grad, act, self.dz[i], None, None, self.db[i])     # dz and db now, dW at the end
+            else:
+                self._bwd(i, grad, act, self.dz[i], None, self.dW[i], self.db[i])
+                if after_gradients is not None:
+                    after_gradients(i)
+            if dx is not None:
+                self._bwd(i, dz, ACT_IDENTITY, None, dx, None, None)
+            if after_layer is not None and i != deferred:
                 after_layer(i)
             grad = self.dx[i]
+        if deferred is not None:
+            self._bwd(deferred, dz_of[deferred], ACT_IDENTITY, None, None, self.dW[deferred], None)
+            if after_gradients is not None:
+                after_gradients(deferred)
+            if after_layer is not None:
+                after_layer(deferred)
 
 
 class GradientAllReduce:
@@ -115,18 +150,25 @@ class GradientAllReduce:
         check(self.comm_wrapper.handle,
               lib.snb200_comm_init_rank(self.comm_wrapper.handle, world_size, rank, ident))
 
-    def reduce_layer(self, stack, i, compute_stream, update=None):
-        """Queues the all-reduce of layer ``i``'s gradients behind the work already on ``compute_stream``.
-        ``update(lib, handle, stack, i)``, when given, queues the optimizer step of that layer on the same
-        side stream right behind the reduction, so it also overlaps the rest of the backward pass."""
+    def reduce_layer(self, stack, i, compute_stream):
+        """Queues the all-reduce of layer ``i``'s gradients (dW and db as one NCCL group, one launch) on the side
+        stream, behind the work already on ``compute_stream``."""
+        import ctypes
         ev = self.torch.cuda.Event()
         ev.record(compute_stream)
         self.stream.wait_event(ev)
         lib, h = self.comm_wrapper.lib, self.comm_wrapper.handle
-        check(h, lib.snb200_allreduce_sum(h, stack.dW[i].Pointer, stack.dW[i].Count))
-        check(h, lib.snb200_allreduce_sum(h, stack.db[i].Pointer, stack.db[i].Count))
-        if update is not None:
-            update(lib, h, stack, i)
+        bufs = (ctypes.c_void_p * 2)(stack.dW[i].Pointer, stack.db[i].Pointer)
+        counts = (ctypes.c_longlong * 2)(stack.dW[i].Count, stack.db[i].Count)
+        check(h, lib.snb200_allreduce_sum_group(h, 2, bufs, counts))
+
+    def update_layer(self, stack, i, compute_stream, update):
+        """Queues ``update(lib, handle, stack, i)`` -- the optimizer step of layer ``i`` -- on the side stream,
+        behind that layer's reduction and behind everything on ``compute_stream`` that still reads W[i]."""
+        ev = self.torch.cuda.Event()
+        ev.record(compute_stream)
+        self.stream.wait_event(ev)
+        update(self.comm_wrapper.lib, self.comm_wrapper.handle, stack, i)
 
     def join(self, compute_stream):
         """Makes ``compute_stream`` wait for every queued all-reduce."""
@@ -142,49 +184,51 @@ class GradientAllReduce:
 
 
 class HostStaging:
-    """Double-buffered host-to-device staging of a replica's mini-batch (x and the upstream gradient).
+    """Double-buffered host-to-device staging of a replica's mini-batch (x and the upstream gradient)
+    through the library's stager (snb200_stager_*).
 
     SharpNet copies every mini-batch from pinned host memory to the device before it runs the
-    step (Prod/Networks/Network.cs:1211-1258, Prod/GPU/GpuTensor.cs:88-93).  Here the copy of step
-    i+1 runs on its own stream while step i computes; the compute stream only waits for the copy it
+    step (Prod/Networks/Network.cs:1211-1258, Prod/GPU/GpuTensor.cs:68-80).  Here the copy of step
+    i+1 runs on the stager's stream while step i computes; the compute stream only waits for the copy it
     is about to consume, and a buffer is not overwritten before the step that read it has finished."""
 
-    def __init__(self, stack, x_host, dy_host, compute_stream):
-        import torch
-        self.torch = torch
+    def __init__(self, stack, x_host, dy_host, slots=2):
+        import ctypes
         self.stack = stack
         self.x_host, self.dy_host = x_host, dy_host
-        self.compute = compute_stream
-        self.copy = torch.cuda.Stream(device=stack.w.device)
         w = stack.w
-        self.buffers = [(stack.x, stack.dy),
-                        (GPUTensor(stack.x.Shape, None, w), GPUTensor(stack.dy.Shape, None, w))]
-        self.copied = [None, None]     # event: copy into buffer b finished
-        self.consumed = [None, None]   # event: the step that read buffer b finished
+        self.slots = slots
+        self.buffers = [(stack.x, stack.dy)] + [(GPUTensor(stack.x.Shape, None, w), GPUTensor(stack.dy.Shape, None, w))
+                                                for _ in range(slots - 1)]
+        self.handle = ctypes.c_void_p()
+        check(w.handle, w.lib.snb200_stager_create(w.handle, slots, ctypes.byref(self.handle)))
+        self._src = (ctypes.c_void_p * 2)(x_host.data_ptr(), dy_host.data_ptr())
+        self._bytes = (ctypes.c_longlong * 2)(x_host.numel() * 4, dy_host.numel() * 4)
+        self._dst = [(ctypes.c_void_p * 2)(bx.Pointer, bdy.Pointer) for bx, bdy in self.buffers]
 
     def issue(self, i):
-        """Queues the copy of step ``i``'s inputs into buffer ``i % 2``."""
-        b = i % 2
-        if self.consumed[b] is not None:
-            self.copy.wait_event(self.consumed[b])
-        with self.torch.cuda.stream(self.copy):
-            self.buffers[b][0].storage.copy_(self.x_host.view(-1), non_blocking=True)
-            self.buffers[b][1].storage.copy_(self.dy_host.view(-1), non_blocking=True)
-            ev = self.torch.cuda.Event()
-            ev.record(self.copy)
-        self.copied[b] = ev
+        """Queues the copy of step ``i``'s inputs into buffer ``i % slots``."""
+        w = self.stack.w
+        b = i % self.slots
+        check(w.handle, w.lib.snb200_stager_issue(self.handle, b, 2, self._dst[b], self._src, self._bytes))
 
     def bind(self, i):
-        """Points the stack at buffer ``i % 2`` and makes the compute stream wait for its copy."""
-        b = i % 2
-        self.compute.wait_event(self.copied[b])
+        """Points the stack at buffer ``i % slots`` and makes the compute stream wait for its copy."""
+        w = self.stack.w
+        b = i % self.slots
+        check(w.handle, w.lib.snb200_stager_acquire(self.handle, b))
         self.stack.x, self.stack.dy = self.buffers[b]
 
     def release(self, i):
         """Call after step ``i`` has been queued: marks when its buffer may be overwritten."""
-        ev = self.torch.cuda.Event()
-        ev.record(self.compute)
-        self.consumed[i % 2] = ev
+        w = self.stack.w
+        check(w.handle, w.lib.snb200_stager_release(self.handle, i % self.slots))
+
+    def close(self):
+        if self.handle is not None:
+            self.stack.w.lib.snb200_stager_destroy(self.handle)
+            self.handle = None
+        self.stack.x, self.stack.dy = self.buffers[0]
 
 
 class SgdUpdate:
@@ -207,15 +251,19 @@ class SgdUpdate:
                                                 W.Pointer, None if v is None else v[i].Pointer))
 
 
-def training_step(stack, reducer=None, compute_stream=None, update=None):
-    """One forward + backward of ``stack`` on this replica's rows, with the per-layer gradient
-    all-reduce (and, when ``update`` is given, the optimizer step) overlapped with the backward pass."""
+def training_step(stack, reducer=None, compute_stream=None, update=None, defer_smallest=True):
+    """One forward + backward of ``stack`` on this replica's rows.  With a ``reducer`` the gradients of each layer
+    are all-reduced on its side stream from the moment that layer's dW product is queued, overlapping the rest of
+    the backward pass; ``update`` (the optimizer step of a layer) follows its reduction on the same stream once
+    the products that read the layer's weights are queued."""
     stack.forward()
     if reducer is None:
         after = None if update is None else (lambda i: update(stack.w.lib, stack.w.handle, stack, i))
         stack.backward(after_layer=after)
         return
-    stack.backward(after_layer=lambda i: reducer.reduce_layer(stack, i, compute_stream, update))
+    stack.backward(after_gradients=lambda i: reducer.reduce_layer(stack, i, compute_stream),
+                   after_layer=None if update is None else (lambda i: reducer.update_layer(stack, i, compute_stream, update)),
+                   defer_smallest=defer_smallest)
     reducer.join(compute_stream)
 
 

@@ -289,6 +289,46 @@ def test_gpu_multihead_attention_forward_backward_against_oracle(wrapper, layout
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("layout", [W_OUT_IN, W_IN_OUT])
+def test_gpu_multihead_attention_head_width_not_a_multiple_of_four(wrapper, layout):
+    """Heads 6 wide with embed_dim a multiple of 4: the projections run on the tensor cores and store their result
+    split by head through runs of 6 floats, which a group of four columns straddles.  K of the last wave is cut on
+    purpose (tuning key 8) so that the reduction pass does that store."""
+    from sharpnet_b200 import _capi
+    from sharpnet_b200.tensor import GPUTensor
+    B, T, H, kd = 4, 128, 128, 6
+    E = H * kd
+    Q, K, V, weights, biases, dy = _mha_random(B, T, T, H, kd, 77, True)
+    y64, cache = orc.multihead_attention_forward(Q, K, V, weights, biases, H, kd, kd, True, layout, f64=True)
+    dQ, dK, dV, dws, dbs = orc.multihead_attention_backward(Q, K, V, dy, weights, cache, H, kd, kd, 1.0, layout)
+    tol = 1e-5 * np.sqrt(E) * 4 + 2e-5
+    gtol = 1e-5 * np.sqrt(B * T) * 16 + 1e-4
+    for splits in (0, 3):
+        wrapper.set_tuning(_capi.TUNE_FORCE_SPLITS, splits)
+        try:
+            if splits:      # the chooser does cut this projection's K when told to
+                x2, w2, y2 = GPUTensor((B * T, E), Q, wrapper), GPUTensor((E, E), weights[0], wrapper), GPUTensor((B * T, E), None, wrapper)
+                assert wrapper.lib.snb200_dense_fwd(wrapper.handle, layout, B * T, E, E, x2.Pointer, w2.Pointer, None, 5,
+                                                    None, y2.Pointer) == 0
+                assert "splitk" in wrapper.last_kernel()
+            keep = {}
+            y = _gpu_mha(wrapper, keep)(Q, K, V, weights, biases, H, kd, kd, True, layout)
+            assert np.abs(y - y64).max() <= tol
+            dX = [GPUTensor(a.shape, None, wrapper) for a in (Q, K, V)]
+            keep["layer"].BackwardPropagation(keep["X"], GPUTensor(dy.shape, dy, wrapper), dX, 1.0)
+            wrapper.check_device_status()
+        finally:
+            wrapper.set_tuning(_capi.TUNE_FORCE_SPLITS, 0)
+        for got, ref in zip(dX, (dQ, dK, dV)):
+            assert np.abs(got.ContentAsFloatArray() - ref).max() <= gtol
+        gws, gbs = keep["layer"].gradients()
+        for got, ref in zip(gws, dws):
+            assert np.abs(got.ContentAsFloatArray() - ref).max() <= gtol
+        for got, ref in zip(gbs, dbs):
+            assert np.abs(got.ContentAsFloatArray() - ref).max() <= gtol
+
+
+@pytest.mark.gpu
 def test_gpu_transpose_second_and_third_dimension(wrapper):
     from sharpnet_b200.tensor import GPUTensor
     for shape in ((1, 1, 1, 1), (2, 3, 4, 5), (3, 7, 2, 8), (4, 16, 33, 64), (2, 5, 3), (6, 128, 8, 32), (3, 2, 1000, 3)):

@@ -371,3 +371,31 @@ def test_tf32_bf16x2_mode(wrapper):
     A, B, C = GPUTensor(a.shape, a, wrapper), GPUTensor(b.shape, b, wrapper), GPUTensor((300, 280), None, wrapper)
     C.Dot(A, False, B, True, 1, 0)
     np.testing.assert_array_equal(C.ContentAsFloatArray(), a @ b.T)
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+def test_config_5_square_16384_on_row_samples(wrapper, mode, tol):
+    """benchmark config 5a at full size (16384^3, U[-1, 1), seed 13): the whole product runs on the device; three
+    blocks of 64 rows of it -- the first rows, rows from the middle of a tile band, the last rows -- are compared
+    with MKL sgemm and with float64 on the same operands (the full product on the host would take minutes)."""
+    import torch
+    n = 16384
+    wrapper.set_math_mode(mode)
+    rng = np.random.default_rng(13)
+    a = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    A, B, C = GPUTensor((n, n), a, wrapper), GPUTensor((n, n), b, wrapper), GPUTensor((n, n), None, wrapper)
+    C.Dot(A, False, B, False, 1.0, 0.0)
+    wrapper.check_device_status()
+    assert wrapper.last_kernel().startswith("umma2_")
+    b64 = b.astype(np.float64)
+    for r0 in (0, 8000, n - 64):
+        got = C.storage[r0 * n:(r0 + 64) * n].view(64, n).cpu().numpy()
+        rows = np.ascontiguousarray(a[r0:r0 + 64])
+        f64 = rows.astype(np.float64) @ b64
+        mkl = np.zeros((64, n), np.float32)
+        orc.dot_mkl(rows.ravel(), 64, n, False, b.ravel(), n, n, False, mkl.reshape(-1), 1.0, 0.0)
+        e64, emkl = orc.scaled_error(got, f64, n, 1.0, 1.0), orc.scaled_error(got, mkl, n, 1.0, 1.0)
+        assert e64 <= tol and emkl <= tol, (r0, e64, emkl)
+    del A, B, C
+    torch.cuda.empty_cache()

@@ -12,12 +12,12 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _noalloc(lib, dy_t, M, N, device=0):
+def _noalloc(lib, dy_t, M, N, device=0, stream=None):
     import torch
     db = torch.full((max(N, 1),), float("nan"), dtype=torch.float32, device=dy_t.device)
     err = ctypes.create_string_buffer(256)
-    st = lib.snb200_bias_grad_noalloc(device, None, M, N, ctypes.c_void_p(dy_t.data_ptr()),
-                                      ctypes.c_void_p(db.data_ptr()), err, 256)
+    st = lib.snb200_bias_grad_noalloc(device, None if stream is None else ctypes.c_void_p(stream.cuda_stream), M, N,
+                                      ctypes.c_void_p(dy_t.data_ptr()), ctypes.c_void_p(db.data_ptr()), err, 256)
     return st, db, err.value.decode()
 
 
@@ -27,13 +27,16 @@ def test_noalloc_bias_gradient_matches_the_handle_entry_point(wrapper):
     rng = np.random.default_rng(42)
     # first call: many slabs in the scratch array; second call: a different, smaller problem right after,
     # so stale partial sums of the first call would show up; then odd sizes that take the scalar kernel
-    for (M, N) in ((4096, 1024), (300, 64), (1000, 333), (9, 1632), (5, 65536)):
+    # (4096, 65536): the widest matrix allowed, where the slab count is cut down to what the array holds
+    side = torch.cuda.Stream(device=wrapper.device)
+    for (M, N) in ((4096, 1024), (300, 64), (1000, 333), (9, 1632), (5, 65536), (4096, 65536)):
         dy = rng.uniform(-1.5, 1.5, (M, N)).astype(np.float32)
         dy_t = torch.from_numpy(dy).to(wrapper.device)
         ref = torch.empty(N, dtype=torch.float32, device=wrapper.device)
         assert lib.snb200_bias_grad(h, M, N, ctypes.c_void_p(dy_t.data_ptr()), ctypes.c_void_p(ref.data_ptr())) == 0
-        for _ in range(2):   # two calls in a row on the shared scratch
-            st, db, msg = _noalloc(lib, dy_t, M, N)
+        torch.cuda.synchronize()
+        for stream in (None, side):   # two calls in a row on the shared scratch: default stream, then a stream of the caller's
+            st, db, msg = _noalloc(lib, dy_t, M, N, stream=stream)
             assert st == 0, msg
             torch.cuda.synchronize()
             tol = 1e-5 * np.sqrt(M) * 1.5 + 1e-6          # the bound test_dense_gpu.py uses for column sums
