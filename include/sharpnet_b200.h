@@ -121,7 +121,9 @@ int snb200_gemm_timing_end(snb200_handle_t handle, double* total_ms, int* gemm_c
  *        overlaps the tail of the previous kernel in the stream; they wait for its completion before touching
  *        global memory);
  * key 8: n > 1 cuts K of the tiles of a partly filled last wave exactly n times (one of 2..8, 10, 12, 16),
- *        whatever the time estimate says (tests of the reduction pass). */
+ *        whatever the time estimate says (tests of the reduction pass);
+ * key 9: 1 keeps the A operand of the single-CTA 3xTF32 kernel in shared memory instead of tensor memory
+ *        (A/B measurements). */
 int snb200_set_tuning(snb200_handle_t handle, int key, int value);
 
 /* ---- Tensor.Dot -----------------------------------------------------------------------------

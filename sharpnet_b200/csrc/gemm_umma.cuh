@@ -28,22 +28,34 @@ constexpr int kUmmaK = 8;  // K extent of one kind::tf32 instruction
 
 // GROUPS_ = 0 picks the number of epilogue warp groups from the tile width; the row-operation kernels ask for 2 so
 // that two warps share every row (see epilogue_row_op).
-template <int BN_, int BK_, bool SPLIT_, int GROUPS_ = 0>
+// TS_ (3xTF32, BN <= 128): the A operand goes to the tensor core from tensor memory instead of shared memory.  The
+// split warps, which read every landed A tile anyway, write its hi and lo planes into TMEM (64 columns per stage,
+// behind the two accumulators), so the 3 x BK/8 instructions of a K block read only B from shared memory: per K
+// block and SM the shared-memory traffic of a 128 x 32 tile falls from 120 KB to 56 KB, of a 128 x 128 tile from
+// 192 KB to 128 KB -- and shared-memory bandwidth is what bounds this kernel.
+template <int BN_, int BK_, bool SPLIT_, int GROUPS_ = 0, bool TS_ = false>
 struct UmmaTile {
   static constexpr int BM = kUmmaBM;
   static constexpr int BN = BN_;
   static constexpr int BK = BK_;
   static constexpr bool SPLIT = SPLIT_;
+  static constexpr bool TS = TS_;
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int RAW_BYTES = A_BYTES + B_BYTES;               // what TMA delivers per stage
-  static constexpr int STAGE_BYTES = RAW_BYTES * (SPLIT ? 2 : 1);   // + the lo planes
+  // + the lo planes: of A and B behind the raw tiles, or (TS) of B alone
+  static constexpr int STAGE_BYTES = TS ? RAW_BYTES + B_BYTES : RAW_BYTES * (SPLIT ? 2 : 1);
+  static constexpr int B_LO_OFFSET = TS ? B_BYTES : RAW_BYTES;      // from the raw B tile to its lo plane
   static constexpr int SMEM_BUDGET = 196 * 1024;
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TS_A_COLS = 2 * BK;                          // TMEM columns of one stage's A: hi plane, lo plane
+  static constexpr int STAGES_TMEM = TS ? (512 - 2 * BN) / TS_A_COLS : 8;
+  static constexpr int STAGES_CAP = STAGES_TMEM > 8 ? 8 : STAGES_TMEM;
+  static constexpr int STAGES = STAGES_RAW > STAGES_CAP ? STAGES_CAP : STAGES_RAW;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;              // one 32 x 32 fp32 block per epilogue warp
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; power of two
+  static constexpr int TMEM_COLS = TS ? 512 : (2 * BN < 32 ? 32 : 2 * BN);   // two accumulators (+ A stages); power of two
+  static constexpr int TS_A_COL0 = 2 * BN;                          // first TMEM column of the A stages
   // Warps are grouped in fours so that setmaxnreg can move registers between the roles:
   //   group 0: TMA producer, MMA issuer (two idle warps); then the epilogue groups; then the split group.
   static constexpr int EPI_GROUPS = GROUPS_ ? GROUPS_ : ((BN >= 64) ? 2 : 1);   // each epilogue warp owns <= 128 columns
@@ -54,7 +66,7 @@ struct UmmaTile {
   static constexpr int SPLIT_THREAD0 = 128 + EPI_THREADS;
   static constexpr int THREADS = 128 + EPI_THREADS + N_SPLIT_THREADS;
   static constexpr int REGS_CTRL = 72;
-  static constexpr int REGS_SPLIT = 64;
+  static constexpr int REGS_SPLIT = TS ? 112 : 64;                  // TS: a whole A row and its lo plane in registers
   static constexpr int REGS_EPI_RAW = (65536 / 128 - REGS_CTRL - (SPLIT ? REGS_SPLIT : 0)) / EPI_GROUPS;
   static constexpr int REGS_EPI = (REGS_EPI_RAW > 232 ? 232 : REGS_EPI_RAW) / 8 * 8;
   // K-major tiles: one row = BK fp32.  128-byte swizzle for BK = 32, 64-byte for BK = 16.
@@ -71,6 +83,7 @@ struct UmmaTile {
   static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "BN must be 32, 64, 128 or 256");
   static_assert(STAGES >= 2, "need at least two stages");
   static_assert(EPI_COLS % 32 == 0 && EPI_COLS <= 128, "an epilogue warp keeps at most 128 columns in registers");
+  static_assert(!TS || (SPLIT && BK == 32 && BN <= 128), "A from tensor memory: 3xTF32, 32-deep K blocks, BN <= 128");
 };
 
 struct UmmaParams {
@@ -509,6 +522,48 @@ __device__ __forceinline__ void split_stage(uint8_t* raw, int tid, int rewrite_h
   }
 }
 
+// Operand split of one landed stage when A goes to the tensor core from tensor memory.  Thread `tid` of the 128
+// split threads owns row `tid` of the A tile: it reads the row's 32 K values from shared memory (K-major tile: eight
+// swizzled 16-byte chunks; MN-major tile: one word per K row of the 32-wide chunk its row lies in, 32-byte atoms
+// XOR-swizzled by K row & 3), and writes them -- raw, the tensor core truncates to TF32 itself -- to TMEM columns
+// [0, 32) of the stage and lo = tf32(x - hi) to columns [32, 64), lane = row.  The B tile is split in shared memory
+// as before, its lo plane right behind it.
+template <class T>
+__device__ __forceinline__ void split_stage_ts(uint8_t* stage, uint32_t tmem_a, int tid, int a_mn) {
+  uint32_t x[32], lo[32];
+  if (!a_mn) {
+    const uint8_t* row = stage + tid * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 v = *reinterpret_cast<const uint4*>(row + ((c ^ (tid & 7)) << 4));
+      x[4 * c] = v.x; x[4 * c + 1] = v.y; x[4 * c + 2] = v.z; x[4 * c + 3] = v.w;
+    }
+  } else {
+    const uint8_t* chunk = stage + (tid >> 5) * T::MNMAJ_CHUNK_BYTES + (tid & 7) * 4;
+    const int atom = (tid >> 3) & 3;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) x[k] = *reinterpret_cast<const uint32_t*>(chunk + k * 128 + ((atom ^ (k & 3)) << 5));
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    lo[j] = to_tf32_rna(__uint_as_float(x[j]) - __uint_as_float(x[j] & 0xffffe000u));
+  const uint32_t lane_base = static_cast<uint32_t>(tid & ~31) << 16;     // this warp's TMEM lane quarter
+  tmem_st_32x32(tmem_a + lane_base, x);
+  tmem_st_32x32(tmem_a + lane_base + 32, lo);
+  uint8_t* b_raw = stage + T::A_BYTES;
+#pragma unroll 4
+  for (int i = tid; i < T::B_BYTES / 16; i += 128) {
+    const float4 v = *reinterpret_cast<const float4*>(b_raw + i * 16);
+    uint4 l;
+    l.x = to_tf32_rna(v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u));
+    l.y = to_tf32_rna(v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u));
+    l.z = to_tf32_rna(v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u));
+    l.w = to_tf32_rna(v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u));
+    *reinterpret_cast<uint4*>(b_raw + T::B_BYTES + i * 16) = l;
+  }
+  tmem_st_wait();
+}
+
 // The tensor core adds into its fp32 accumulator with truncation, so a long K loop drifts towards
 // zero by about 1e-8 * K (relative to sqrt(K)).  The MMA warp therefore accumulates only
 // `chunk_kblocks` k-blocks in TMEM; the epilogue warps add every such partial sum into fp32
@@ -604,7 +659,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer
-      const uint32_t idesc = make_idesc_tf32(BM, BN, p.a_mn, p.b_mn);
+      const uint32_t idesc = make_idesc_tf32(BM, BN, T::TS ? 0 : p.a_mn, p.b_mn);   // A in TMEM is always K-major
       const uint32_t a_step = p.a_mn ? 1024u : 32u;   // bytes per K = 8 slice
       const uint32_t b_step = p.b_mn ? 1024u : 32u;
       const uint32_t a_lbo = p.a_mn ? T::MNMAJ_CHUNK_BYTES : 16u;
@@ -634,12 +689,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tc_fence_after_sync();
             const uint32_t a_hi = smem_u32(ring + s * T::STAGE_BYTES);
             const uint32_t b_hi = a_hi + T::A_BYTES;
+            const uint32_t a_tmem = tmem_base + T::TS_A_COL0 + s * T::TS_A_COLS;   // TS: hi plane, lo plane 32 columns on
 #pragma unroll
             for (int ks = 0; ks < BK / kUmmaK; ++ks) {
               const uint64_t da_hi = make_smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lay);
               const uint64_t db_hi = make_smem_desc(b_hi + ks * b_step, b_lbo, b_sbo, b_lay);
               const uint32_t first = (kb == kb0 && ks == 0) ? 0u : 1u;
-              if (T::SPLIT) {
+              if (T::TS) {
+                const uint64_t db_lo = make_smem_desc(b_hi + T::B_LO_OFFSET + ks * b_step, b_lbo, b_sbo, b_lay);
+                umma_tf32_ts(d_tmem, a_tmem + BK + ks * kUmmaK, db_hi, idesc, first);
+                umma_tf32_ts(d_tmem, a_tmem + ks * kUmmaK, db_lo, idesc, 1u);
+                umma_tf32_ts(d_tmem, a_tmem + ks * kUmmaK, db_hi, idesc, 1u);
+              } else if (T::SPLIT) {
                 const uint64_t da_lo = make_smem_desc(a_hi + T::RAW_BYTES + ks * a_step, a_lbo, a_sbo, a_lay);
                 const uint64_t db_lo = make_smem_desc(b_hi + T::RAW_BYTES + ks * b_step, b_lbo, b_sbo, b_lay);
                 umma_tf32_ss(d_tmem, da_lo, db_hi, idesc, first);
@@ -719,7 +780,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait_warp(&full_bar[s], ph, abortp)) { ok = false; break; }
-        split_stage<T::RAW_BYTES, T::N_SPLIT_THREADS>(ring + s * T::STAGE_BYTES, tid, p.rewrite_hi);
+        if constexpr (T::TS) {
+          // the stage's TMEM columns are free: the producer refilled the stage only after the MMAs that read them retired
+          split_stage_ts<T>(ring + s * T::STAGE_BYTES, tmem_base + T::TS_A_COL0 + s * T::TS_A_COLS, tid, p.a_mn);
+          tc_fence_before_sync();
+        } else {
+          split_stage<T::RAW_BYTES, T::N_SPLIT_THREADS>(ring + s * T::STAGE_BYTES, tid, p.rewrite_hi);
+        }
         fence_proxy_async_smem();   // make the generic-proxy stores visible to tcgen05.mma
         __syncwarp();
         if (lane == 0) mbar_arrive(&split_bar[s]);

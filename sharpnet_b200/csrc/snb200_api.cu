@@ -14,11 +14,12 @@
 #include "gemm_simt.cuh"
 #include "gemm_umma.cuh"
 #include "gemm_umma2.cuh"
+#include "attention_umma.cuh"
 
 using namespace snb;
 
 // ------------------------------------------------------------------------------------ handle
-enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_FORCE_SPLITS = 8, TUNE_COUNT = 9 };
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_FORCE_SPLITS = 8, TUNE_NO_TS = 9, TUNE_NO_FUSED_ATTN = 10, TUNE_COUNT = 11 };
 
 struct snb200_context {
   int device;
@@ -108,6 +109,10 @@ extern "C" int snb200_create(snb200_handle_t* handle, int device_id) {
   h->tune[TUNE_CHUNK_K] = 128;
   const char* env = getenv("SNB200_MATH_MODE");
   if (env && env[0] >= '0' && env[0] <= '2' && env[1] == 0) h->math_mode = env[0] - '0';
+  env = getenv("SNB200_NO_FUSED_ATTENTION");          // A/B measurements: the attention core as separate products
+  if (env && env[0] == '1' && env[1] == 0) h->tune[TUNE_NO_FUSED_ATTN] = 1;
+  env = getenv("SNB200_TS");                         // A operand from tensor memory: off until SNB200_TS=1 says otherwise
+  h->tune[TUNE_NO_TS] = (env && env[0] == '1' && env[1] == 0) ? 0 : 1;
   h->workspace_floats = 32u << 20;   // 128 MB: column-sum slabs and split-K partial sums
   if (cudaMalloc(&h->workspace, h->workspace_floats * sizeof(float)) != cudaSuccess ||
       cudaMalloc(&h->error_word, sizeof(int)) != cudaSuccess ||
@@ -474,16 +479,22 @@ static int launch_umma(snb200_handle_t h, const GemmProblem& g, bool split, int 
            plan.splits > 0 ? (plan.transposed ? "_swapAB_splitk" : "_splitk") : "");
   note_kernel(h, name, 1);
   if (split) {
+    const bool ts = h->tune[TUNE_NO_TS] == 0;   // A operand from tensor memory (tiles up to 128 wide)
     switch (bn) {
       case 256:
         if (h->tune[TUNE_VARIANT] == 1) return launch_umma_t<UmmaTile<256, 16, true>>(h, g, plan);
         return launch_umma_t<UmmaTile<256, 32, true>>(h, g, plan);
       case 128:
         if (h->tune[TUNE_VARIANT] == 1) return launch_umma_t<UmmaTile<128, 16, true>>(h, g, plan);
+        if (ts) return launch_umma_t<UmmaTile<128, 32, true, 0, true>>(h, g, plan);
         return launch_umma_t<UmmaTile<128, 32, true>>(h, g, plan);
       // narrow tiles leave room for 32-wide K blocks: half as many stage hand-offs per unit of K
-      case 64: return launch_umma_t<UmmaTile<64, 32, true>>(h, g, plan);
-      default: return launch_umma_t<UmmaTile<32, 32, true>>(h, g, plan);
+      case 64:
+        if (ts) return launch_umma_t<UmmaTile<64, 32, true, 0, true>>(h, g, plan);
+        return launch_umma_t<UmmaTile<64, 32, true>>(h, g, plan);
+      default:
+        if (ts) return launch_umma_t<UmmaTile<32, 32, true, 0, true>>(h, g, plan);
+        return launch_umma_t<UmmaTile<32, 32, true>>(h, g, plan);
     }
   }
   switch (bn) {
@@ -708,6 +719,11 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
     note_kernel(h, name, 1);
     // two epilogue warps per row (UmmaTile<..., 2>) except for the 32-wide tile
     if (split) {
+      if (h->tune[TUNE_NO_TS] == 0) {
+        if (bn == 32) return launch_umma_t<UmmaTile<32, 32, true, 0, true>, true>(h, g, none);
+        if (bn == 64) return launch_umma_t<UmmaTile<64, 32, true, 2, true>, true>(h, g, none);
+        if (bn == 128) return launch_umma_t<UmmaTile<128, 32, true, 2, true>, true>(h, g, none);
+      }
       if (bn == 32) return launch_umma_t<UmmaTile<32, 32, true>, true>(h, g, none);
       if (bn == 64) return launch_umma_t<UmmaTile<64, 32, true, 2>, true>(h, g, none);
       if (bn == 128) return launch_umma_t<UmmaTile<128, 32, true, 2>, true>(h, g, none);
@@ -1201,6 +1217,77 @@ static bool row_op_fits(const snb200_context* h, const GemmProblem& g, int max_c
   return static_cast<double>(g.M) * g.N * g.K * g.batch >= 64.0 * 64 * 64;
 }
 
+// The attention core as one kernel (attn_fwd_kernel): score rows of up to 128 columns, embeddings of up to 128, the
+// 3xTF32 mode, operands TMA can load.  Returns -1 when the case does not qualify (the caller then runs the products
+// one by one).
+template <class T>
+static int launch_attn_fwd_t(snb200_handle_t h, const AttnParams& ap, const float* Q, const float* K, const float* V) {
+  static bool configured[64] = {};
+  CUtensorMap tmQ, tmK, tmV;
+  const uint64_t B = ap.batch, Tq = ap.q_steps, Tk = ap.v_steps, E = ap.embedding_dim;
+  bool ok = encode_3d(&tmQ, Q, E, Tq, B, E, Tq * E, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B) &&
+            encode_3d(&tmK, K, E, Tk, B, E, Tk * E, 32, T::TKN, CU_TENSOR_MAP_SWIZZLE_128B) &&
+            encode_3d(&tmV, V, E, Tk, B, E, Tk * E, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  if (!ok) return fail(h, SNB200_STATUS_INTERNAL_ERROR, "cuTensorMapEncodeTiled rejected an attention operand");
+  if (!configured[h->device]) {
+    SNB_CUDA(h, cudaFuncSetAttribute(attn_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    configured[h->device] = true;
+  }
+  const long long units = static_cast<long long>(ap.batch) * ap.tiles_q;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(units < h->sm_count ? units : h->sm_count));
+  cfg.blockDim = dim3(T::THREADS);
+  cfg.dynamicSmemBytes = T::SMEM_BYTES;
+  cfg.stream = h->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = h->tune[TUNE_PDL] == 1 ? 0 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<T>, tmQ, tmK, tmV, ap);
+  if (e != cudaSuccess) return cuda_fail(h, e, "attn_fwd_kernel launch");
+  return check_launch(h, "attn_fwd_kernel launch");
+}
+
+static int try_fused_attention_fwd(snb200_handle_t h, int batch, int Tq, int Tk, int E, float scaling, int is_causal,
+                                   const float* Q, const float* K, const float* V, float* weights, float* y,
+                                   const OutMap* y_map) {
+  if (h->tune[TUNE_NO_FUSED_ATTN] == 1 || h->tune[TUNE_FORCE_PATH] == 2) return -1;
+  if (h->math_mode != SNB200_MATH_3XTF32 && h->math_mode != SNB200_MATH_TF32_BF16X2) return -1;
+  if (Tk > 128 || E > 128 || Tk < 8 || Tq < 16 || (E & 3)) return -1;
+  if (!aligned16(Q) || !aligned16(K) || !aligned16(V)) return -1;
+  if (static_cast<double>(batch) * Tq * Tk * E < 64.0 * 64 * 64) return -1;
+  if (static_cast<long long>(batch) * ((Tq + 127) / 128) > 0x7fffffffLL) return -1;
+  AttnParams ap;
+  memset(&ap, 0, sizeof(ap));
+  ap.batch = batch; ap.q_steps = Tq; ap.v_steps = Tk; ap.embedding_dim = E;
+  ap.tiles_q = (Tq + 127) / 128;
+  ap.error_word = h->error_word;
+  UmmaParams& s = ap.s;
+  s.M = Tq; s.N = Tk; s.K = E; s.batch = batch;
+  s.ldc = Tk; s.strideC = static_cast<long long>(Tq) * Tk;
+  s.C = weights; s.alpha = scaling; s.beta = 0.0f; s.act = ACT_IDENTITY;
+  s.row_op = ROW_SOFTMAX; s.causal = is_causal ? 1 : 0;
+  s.vec_ok = aligned16(weights) && (Tk % 4 == 0);
+  UmmaParams& o = ap.o;
+  o.M = Tq; o.N = E; o.K = Tk; o.batch = batch;
+  o.ldc = E; o.strideC = static_cast<long long>(Tq) * E;
+  o.C = y; o.alpha = 1.0f; o.beta = 0.0f; o.act = ACT_IDENTITY;
+  o.vec_ok = aligned16(y);
+  if (y_map) { o.omap = *y_map; if (!omap_vec(*y_map)) o.vec_ok = 0; }
+  const int tkn = Tk <= 32 ? 32 : Tk <= 64 ? 64 : 128, en = E <= 32 ? 32 : E <= 64 ? 64 : 128;
+  char name[64];
+  snprintf(name, sizeof(name), "attention_fwd_3xtf32_%dx%d", tkn, en);
+  note_kernel(h, name, 1);
+#define SNB_ATTN_CASE(TK, EE) if (tkn == TK && en == EE) return launch_attn_fwd_t<AttnTile<TK, EE>>(h, ap, Q, K, V)
+  SNB_ATTN_CASE(32, 32); SNB_ATTN_CASE(32, 64); SNB_ATTN_CASE(32, 128);
+  SNB_ATTN_CASE(64, 32); SNB_ATTN_CASE(64, 64); SNB_ATTN_CASE(64, 128);
+  SNB_ATTN_CASE(128, 32); SNB_ATTN_CASE(128, 64); SNB_ATTN_CASE(128, 128);
+#undef SNB_ATTN_CASE
+  return -1;
+}
+
 static int sdpa_fwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps, int embedding_dim, int use_scale,
                          int is_causal, const float* Q, const float* K, const float* V, float* weights, float* y,
                          const OutMap* y_map);
@@ -1222,6 +1309,9 @@ static int sdpa_fwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps,
   if (!weights || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   const int Tq = q_steps, Tk = v_steps, E = embedding_dim;
   const float scaling = use_scale ? 1.0f / sqrtf(static_cast<float>(E)) : 1.0f;
+  // both products, the mask and the softmax in one kernel where a score row fits one tile
+  st = try_fused_attention_fwd(h, batch, Tq, Tk, E, scaling, is_causal, Q, K, V, weights, y, y_map);
+  if (st >= 0) return st;
   GemmProblem g;
   // scores = scaling * Q * K^T                       (ScaledDotProductAttentionLayer.cs:66-71)
   bmm_problem(&g, batch, Tq, Tk, E, 0, 1, Q, E, static_cast<long long>(Tq) * E, K, E, static_cast<long long>(Tk) * E,

@@ -200,11 +200,11 @@ def test_wait_that_runs_out_is_reported_once(wrapper):
     assert lib.snb200_check_device_status(h) == 13
     assert b"timed out" in lib.snb200_last_error_string(h)
     assert lib.snb200_check_device_status(h) == 0
-    a = orc.uniform((256, 256), -1, 1, 5)
-    A, C = GPUTensor(a.shape, a, wrapper), GPUTensor((256, 256), None, wrapper)
-    C.Dot(A, False, A, True, 1.0, 0.0)
+    a, b = orc.uniform((256, 256), -1, 1, 5), orc.uniform((256, 256), -1, 1, 6)
+    A, B, C = GPUTensor(a.shape, a, wrapper), GPUTensor(b.shape, b, wrapper), GPUTensor((256, 256), None, wrapper)
+    C.Dot(A, False, B, True, 1.0, 0.0)
     wrapper.check_device_status()
-    assert orc.scaled_error(C.ContentAsFloatArray(), a.astype(np.float64) @ a.astype(np.float64).T, 256, 1, 1) <= TOL
+    assert orc.scaled_error(C.ContentAsFloatArray(), a.astype(np.float64) @ b.astype(np.float64).T, 256, 1, 1) <= TOL
 
 
 def test_stager_orders_copies_and_steps(wrapper):
