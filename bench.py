@@ -263,7 +263,7 @@ def workload_config(n):
 # our arm
 # ------------------------------------------------------------------------------------------------
 def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows=64, min_calls=20,
-                    cpu=True, compare=True):
+                    cpu=True, compare=True, view_offset=0):
     """Times one Dot / BatchMatrixMultiplication shape.  The call cycles through enough distinct
     (A, B, C) sets that their total size exceeds twice the L2, so every call finds its operands in
     HBM; the whole loop is timed with one CUDA-event pair on the launching stream."""
@@ -276,7 +276,13 @@ def time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi,
     n_sets = int(min(64, max(1, math.ceil(2.0 * L2_BYTES / bytes_set))))
     sets = []
     for _ in range(n_sets):
-        A, B, C = GPUTensor(sa, None, w), GPUTensor(sb, None, w), GPUTensor((batch, M, N), None, w)
+        if view_offset:      # operands that start `view_offset` floats into their allocation: not 16-byte aligned
+            na, nb = batch * sa[1] * sa[2], batch * sb[1] * sb[2]
+            A = GPUTensor(sa, wrapper=w, storage=torch.empty(na + view_offset, device=w.device)[view_offset:])
+            B = GPUTensor(sb, wrapper=w, storage=torch.empty(nb + view_offset, device=w.device)[view_offset:])
+            C = GPUTensor((batch, M, N), None, w)
+        else:
+            A, B, C = GPUTensor(sa, None, w), GPUTensor(sb, None, w), GPUTensor((batch, M, N), None, w)
         A.storage.uniform_(lo, hi); B.storage.uniform_(lo, hi); C.storage.uniform_(lo, hi)
         sets.append((A, B, C))
     A, B, C = sets[0]
@@ -615,14 +621,20 @@ def per_shape_table(w, torch, peaks, large, cpu=True):
     from sharpnet_b200 import MATH_3XTF32, MATH_TF32
     out = []
 
-    def one(name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows=64):
-        out.append(time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows, cpu=cpu))
+    def one(name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows=64, view_offset=0):
+        out.append(time_gemm_shape(w, torch, peaks, name, M, N, K, tA, tB, beta, batch, lo, hi, mode, check_rows, cpu=cpu,
+                                   view_offset=view_offset))
 
     if large:
         # the opt-in TF32 + bf16 cross-term mode next to 3xTF32 on the layout it is implemented for
         from sharpnet_b200._capi import MATH_TF32_BF16X2
         for mode in (MATH_3XTF32, MATH_TF32_BF16X2):
             one("8192^3 NT", 8192, 8192, 8192, False, True, 0.0, 1, -1, 1, mode, check_rows=16)
+        # SharpNet slices tensors at float granularity (Prod/GPU/GpuTensor.cs:1518-1521): operands TMA cannot load
+        one("4096^3 NN, A and B views 4 bytes into their allocations", 4096, 4096, 4096, False, False, 0.0, 1, -1, 1,
+            MATH_3XTF32, check_rows=16, view_offset=1)
+        one("4096x4095x4097 NT (widths not multiples of 4 floats)", 4096, 4095, 4097, False, True, 0.0, 1, -1, 1,
+            MATH_3XTF32, check_rows=16)
     for mode in (MATH_3XTF32, MATH_TF32):
         if large:
             one("cfg5a 16384^3 NN", 16384, 16384, 16384, False, False, 0.0, 1, -1, 1, mode, check_rows=8)

@@ -123,7 +123,13 @@ int snb200_gemm_timing_end(snb200_handle_t handle, double* total_ms, int* gemm_c
  * key 8: n > 1 cuts K of the tiles of a partly filled last wave exactly n times (one of 2..8, 10, 12, 16),
  *        whatever the time estimate says (tests of the reduction pass);
  * key 9: 1 keeps the A operand of the single-CTA 3xTF32 kernel in shared memory instead of tensor memory
- *        (A/B measurements). */
+ *        (A/B measurements);
+ * key 10: 1 runs the attention core as separate products instead of the single fused kernel;
+ * key 11: 1 sends operands that TMA cannot load to the SIMT kernel instead of the tensor-core kernel with
+ *         loader warps;
+ * key 12: n keeps n SMs out of the persistent tensor-core grids launched from now on (0 = use all): a host that
+ *         has just queued a collective on another stream sets it for the next product, so that the collective's
+ *         CTAs find free SMs instead of displacing CTAs of a grid that counts on every SM. */
 int snb200_set_tuning(snb200_handle_t handle, int key, int value);
 
 /* ---- Tensor.Dot -----------------------------------------------------------------------------

@@ -33,8 +33,15 @@ constexpr int kUmmaK = 8;  // K extent of one kind::tf32 instruction
 // behind the two accumulators), so the 3 x BK/8 instructions of a K block read only B from shared memory: per K
 // block and SM the shared-memory traffic of a 128 x 32 tile falls from 120 KB to 56 KB, of a 128 x 128 tile from
 // 192 KB to 128 KB -- and shared-memory bandwidth is what bounds this kernel.
-template <int BN_, int BK_, bool SPLIT_, int GROUPS_ = 0, bool TS_ = false>
+// SWLOAD_: operands that TMA cannot load (a base that is only 4-byte aligned, a row pitch that is not a multiple of
+// 16 bytes -- SharpNet slices tensors at float granularity) are brought in by four loader warps instead, which
+// build in shared memory exactly the swizzled tiles TMA would have delivered (see sw_load_tile); everything after
+// the `full` barrier is unchanged.
+template <int BN_, int BK_, bool SPLIT_, int GROUPS_ = 0, bool TS_ = false, bool SWLOAD_ = false>
 struct UmmaTile {
+  static constexpr bool SWLOAD = SWLOAD_;
+  static constexpr int N_LOAD_THREADS = SWLOAD_ ? 128 : 0;
+  static constexpr int REGS_LOAD = 80;
   static constexpr int BM = kUmmaBM;
   static constexpr int BN = BN_;
   static constexpr int BK = BK_;
@@ -64,10 +71,12 @@ struct UmmaTile {
   static constexpr int SMEM_BYTES = RING_BYTES + EPI_STAGE_BYTES * 4 * EPI_GROUPS + 1024;  // + 1 KB alignment slack
   static constexpr int N_SPLIT_THREADS = SPLIT ? 128 : 0;
   static constexpr int SPLIT_THREAD0 = 128 + EPI_THREADS;
-  static constexpr int THREADS = 128 + EPI_THREADS + N_SPLIT_THREADS;
-  static constexpr int REGS_CTRL = 72;
+  static constexpr int LOAD_THREAD0 = 128 + EPI_THREADS + N_SPLIT_THREADS;
+  static constexpr int THREADS = 128 + EPI_THREADS + N_SPLIT_THREADS + N_LOAD_THREADS;
+  static constexpr int REGS_CTRL = SWLOAD ? 56 : 72;
   static constexpr int REGS_SPLIT = TS ? 112 : 64;                  // TS: a whole A row and its lo plane in registers
-  static constexpr int REGS_EPI_RAW = (65536 / 128 - REGS_CTRL - (SPLIT ? REGS_SPLIT : 0)) / EPI_GROUPS;
+  static constexpr int REGS_EPI_RAW =
+      (65536 / 128 - REGS_CTRL - (SPLIT ? REGS_SPLIT : 0) - (SWLOAD ? REGS_LOAD : 0)) / EPI_GROUPS;
   static constexpr int REGS_EPI = (REGS_EPI_RAW > 232 ? 232 : REGS_EPI_RAW) / 8 * 8;
   // K-major tiles: one row = BK fp32.  128-byte swizzle for BK = 32, 64-byte for BK = 16.
   static constexpr int KMAJ_ROW_BYTES = BK * 4;
@@ -84,6 +93,7 @@ struct UmmaTile {
   static_assert(STAGES >= 2, "need at least two stages");
   static_assert(EPI_COLS % 32 == 0 && EPI_COLS <= 128, "an epilogue warp keeps at most 128 columns in registers");
   static_assert(!TS || (SPLIT && BK == 32 && BN <= 128), "A from tensor memory: 3xTF32, 32-deep K blocks, BN <= 128");
+  static_assert(!SWLOAD || (BK == 32 && BN <= 128 && !TS), "loader warps: 32-deep K blocks, tiles up to 128 wide");
 };
 
 struct UmmaParams {
@@ -118,7 +128,22 @@ struct UmmaParams {
   int causal;
   const float* aux;
   OutMap omap;   // placement of C / Z when not dense (see OutMap)
+  // operands as plain pointers, for the kernels whose loader warps replace TMA
+  const float* A;
+  const float* B;
+  int lda, ldb;
+  long long strideA, strideB;
+#ifdef SNB_TRACE
+  unsigned long long* trace;   // development builds only: %globaltimer stamps of CTA 0 (see SNB_STAMP)
+#endif
 };
+
+// Development builds (-DSNB_TRACE) record where the time of one CTA goes; product builds compile none of it.
+#ifdef SNB_TRACE
+#define SNB_STAMP(p, slot) do { if ((p).trace != nullptr && blockIdx.x == 0) (p).trace[slot] = globaltimer_ns(); } while (0)
+#else
+#define SNB_STAMP(p, slot) do { } while (0)
+#endif
 
 // Work unit u of a launch over n_tiles output tiles: which tile, which K range, and (split >= 0) which
 // partial result it produces.
@@ -564,6 +589,66 @@ __device__ __forceinline__ void split_stage_ts(uint8_t* stage, uint32_t tmem_a, 
   tmem_st_wait();
 }
 
+// One operand tile built in shared memory by the loader warps, in the layout TMA delivers.
+//   K-major (`mn` = 0): `rows` tile rows (M or N index) of 32 K values; row r sits at r * 128 bytes, its 16-byte chunk
+//       c at position c ^ (r & 7).  Source element (r, k) = src[(r0 + r) * ld + k0 + k].
+//   MN-major (`mn` = 1): 32 K rows of `rows` contiguous M/N values, in chunks of 32 values: chunk j at j * 4096 bytes,
+//       K row k at k * 128, 32-byte atom a at position a ^ (k & 3).  Source element (k, r) = src[(k0 + k) * ld + r0 + r].
+// Every item is one 16-byte chunk of the tile.  Its four floats start at a source address that is only 4-byte
+// aligned, so the thread loads the two 16-byte aligned chunks that cover them and shifts.  A chunk is loaded only
+// if it holds at least one element that is inside the matrix, so no load leaves the pages the matrix lies in;
+// elements outside the matrix become zeros, as TMA's out-of-bounds fill does.
+__device__ __forceinline__ void sw_load_tile(uint8_t* dst, const float* src, long long ld, int mn, int rows, int r0,
+                                             int r_limit, int k0, int k_limit, int tid, int nthreads) {
+  // run = the contiguous direction of the source: K for K-major tiles, M/N for MN-major ones
+  const int run_len = mn ? rows : 32, n_runs = mn ? 32 : rows;
+  const int chunks_per_run = run_len >> 2;
+  const int items = n_runs * chunks_per_run;
+  for (int it0 = tid; it0 < items; it0 += 4 * nthreads) {
+    float4 lo4[4], hi4[4];
+    int shift[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int it = it0 + u * nthreads;
+      lo4[u] = make_float4(0.f, 0.f, 0.f, 0.f); hi4[u] = lo4[u]; shift[u] = 0;
+      if (it < items) {
+        const int run = it / chunks_per_run, c = it - run * chunks_per_run;
+        const int outer = (mn ? k0 : r0) + run;                 // index along the strided direction
+        const int inner0 = (mn ? r0 : k0) + 4 * c;              // first index along the contiguous direction
+        const int outer_limit = mn ? k_limit : r_limit, inner_limit = mn ? r_limit : k_limit;
+        if (outer < outer_limit && inner0 < inner_limit) {
+          const float* ptr = src + static_cast<long long>(outer) * ld + inner0;
+          const int sh = static_cast<int>((reinterpret_cast<uintptr_t>(ptr) >> 2) & 3);
+          const float4* aligned = reinterpret_cast<const float4*>(ptr - sh);
+          shift[u] = sh;
+          lo4[u] = __ldg(aligned);                               // holds element inner0: inside the matrix
+          if (sh != 0 && inner0 + 4 - sh < inner_limit) hi4[u] = __ldg(aligned + 1);   // holds element inner0 + 4 - sh
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int it = it0 + u * nthreads;
+      if (it >= items) break;
+      const int run = it / chunks_per_run, c = it - run * chunks_per_run;
+      const int inner0 = (mn ? r0 : k0) + 4 * c;
+      const int inner_limit = mn ? r_limit : k_limit;
+      const float w[8] = {lo4[u].x, lo4[u].y, lo4[u].z, lo4[u].w, hi4[u].x, hi4[u].y, hi4[u].z, hi4[u].w};
+      float t[7], v[4];
+#pragma unroll
+      for (int i = 0; i < 7; ++i) t[i] = (shift[u] & 1) ? w[i + 1] : w[i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = (shift[u] & 2) ? t[i + 2] : t[i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = (inner0 + i < inner_limit) ? v[i] : 0.0f;   // ragged edge inside a loaded chunk
+      uint32_t off;
+      if (!mn) off = run * 128 + ((c ^ (run & 7)) << 4);
+      else     off = (c >> 3) * 4096 + run * 128 + (((((c >> 1) & 3) ^ (run & 3)) << 5) | ((c & 1) << 4));
+      *reinterpret_cast<float4*>(dst + off) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  }
+}
+
 // The tensor core adds into its fp32 accumulator with truncation, so a long K loop drifts towards
 // zero by about 1e-8 * K (relative to sqrt(K)).  The MMA warp therefore accumulates only
 // `chunk_kblocks` k-blocks in TMEM; the epilogue warps add every such partial sum into fp32
@@ -589,10 +674,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   uint8_t* ring = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+  if (threadIdx.x == 0) SNB_STAMP(p, 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], T::SWLOAD ? T::N_LOAD_THREADS / 32 : 1);     // TMA bytes, or one arrival per loader warp
       mbar_init(&split_bar[s], T::SPLIT ? T::N_SPLIT_THREADS / 32 : 1);   // one arrival per split warp
       mbar_init(&empty_bar[s], 1);
     }
@@ -602,8 +688,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     abort_flag = 0;
     fence_mbar_init();
-    prefetch_tmap(&tmA);
-    prefetch_tmap(&tmB);
+    if (!T::SWLOAD) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+    }
   }
   if (warp == 1) {
     tmem_alloc(&tmem_base_holder, T::TMEM_COLS);
@@ -616,15 +704,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile int* abortp = &abort_flag;
   // Everything above touched only this CTA's shared memory, TMEM and kernel parameters, so it may overlap the
   // tail of the previous kernel in the stream; everything below reads or writes global memory.
+  if (threadIdx.x == 0) SNB_STAMP(p, 1);
   allow_dependent_launch();
   grid_dependency_wait();
+  if (threadIdx.x == 0) SNB_STAMP(p, 2);
 
   const int n_tiles = p.batch * p.tiles_m * p.tiles_n;
   const int total_tiles = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;   // work units
 
   if (warp < 4) {
     reg_dealloc<T::REGS_CTRL>();
-    if (warp == 0 && lane == 0) {
+    if (warp == 0 && lane == 0 && !T::SWLOAD) {
       // ---------------------------------------------------------------- TMA producer
       int s = 0;
       uint32_t ph = 0;
@@ -640,6 +730,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* b_dst = a_dst + T::A_BYTES;
           mbar_arrive_expect_tx(&full_bar[s], T::RAW_BYTES);
           const int k0 = kb * BK;
+          if (t == blockIdx.x && kb == kb_begin) SNB_STAMP(p, 3);
           if (!p.a_mn) {
             tma_load_3d(a_dst, &tmA, &full_bar[s], k0, m0, b);
           } else {
@@ -686,6 +777,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int kb = kb0; kb < kb1; ++kb) {
             uint64_t* ready = T::SPLIT ? &split_bar[s] : &full_bar[s];
             if (!mbar_wait(ready, ph, abortp)) { ok = false; break; }
+            if (t == blockIdx.x && kb == kb_begin) SNB_STAMP(p, 5);
             tc_fence_after_sync();
             const uint32_t a_hi = smem_u32(ring + s * T::STAGE_BYTES);
             const uint32_t b_hi = a_hi + T::A_BYTES;
@@ -715,6 +807,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (ok) umma_commit(&acc_full_bar[buf]);
         }
+        if (t == blockIdx.x) SNB_STAMP(p, 6);
       }
     }
     __syncwarp();
@@ -740,6 +833,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int c = 0; c < n_chunks && ok; ++c, ++chunk_id) {
         const int buf = chunk_id & 1;
         if (!mbar_wait_warp(&acc_full_bar[buf], (acc_ph >> buf) & 1u, abortp)) { ok = false; break; }
+        if (warp == 4 && lane == 0 && t == blockIdx.x && c == 0) SNB_STAMP(p, 7);
         acc_ph ^= 1u << buf;
         tc_fence_after_sync();
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + col_base;
@@ -754,6 +848,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+        if (warp == 4 && lane == 0 && t == blockIdx.x && c == n_chunks - 1) SNB_STAMP(p, 8);
       }
       if (ROWOP && T::EPI_GROUPS == 2) ok = row_pair_all(row_xch, q, (warp - 4) >> 2, lane, ok);
       if (!ok) break;
@@ -767,8 +862,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       epilogue_store_unit<NC>(p, alpha, c_folded ? 0.0f : p.beta, bias, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN,
                               BN, tm * BM + q * 32, tn * BN + col_base, lane);
+      if (warp == 4 && lane == 0) SNB_STAMP(p, t == blockIdx.x ? 9 : 10);
     }
-  } else if (T::SPLIT) {
+  } else if (T::SPLIT && threadIdx.x < T::LOAD_THREAD0) {
     // ------------------------------------------------------------------ hi / lo split
     reg_dealloc<T::REGS_SPLIT>();
     const int tid = threadIdx.x - T::SPLIT_THREAD0;
@@ -780,6 +876,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait_warp(&full_bar[s], ph, abortp)) { ok = false; break; }
+        if (tid == 0 && t == blockIdx.x && kb == kb_begin) SNB_STAMP(p, 4);
         if constexpr (T::TS) {
           // the stage's TMEM columns are free: the producer refilled the stage only after the MMAs that read them retired
           split_stage_ts<T>(ring + s * T::STAGE_BYTES, tmem_base + T::TS_A_COL0 + s * T::TS_A_COLS, tid, p.a_mn);
@@ -794,8 +891,34 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   }
+  if (T::SWLOAD && threadIdx.x >= T::LOAD_THREAD0) {
+    // ------------------------------------------------------------------ loader warps (operands TMA cannot load)
+    reg_dealloc<T::REGS_LOAD>();
+    const int tid = threadIdx.x - T::LOAD_THREAD0;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int tile, split, kb_begin, kb_end, b, tm, tn;
+      unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
+      tile_coords(tile, p.tiles_m, p.tiles_n, b, tm, tn);
+      const float* Ab = p.A + static_cast<long long>(b) * p.strideA;
+      const float* Bb = p.B + static_cast<long long>(b) * p.strideB;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait_warp(&empty_bar[s], ph ^ 1, abortp)) { ok = false; break; }
+        uint8_t* a_dst = ring + s * T::STAGE_BYTES;
+        sw_load_tile(a_dst, Ab, p.lda, p.a_mn, BM, tm * BM, p.M, kb * BK, p.K, tid, T::N_LOAD_THREADS);
+        sw_load_tile(a_dst + T::A_BYTES, Bb, p.ldb, p.b_mn, BN, tn * BN, p.N, kb * BK, p.K, tid, T::N_LOAD_THREADS);
+        fence_proxy_async_smem();   // the tensor core (TF32 mode) reads these tiles through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_bar[s]);
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+    }
+  }
 
   // ---------------------------------------------------------------------- teardown
+  if (threadIdx.x == 0) SNB_STAMP(p, 11);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -803,6 +926,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_dealloc(tmem_base, T::TMEM_COLS);
   }
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.error_word, 1);
+  if (threadIdx.x == 0) SNB_STAMP(p, 12);
 }
 
 // Second pass of a split-K (or swapped-operand) GEMM: sums the `splits` raw partial results and applies

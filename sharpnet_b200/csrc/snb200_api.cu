@@ -19,7 +19,7 @@
 using namespace snb;
 
 // ------------------------------------------------------------------------------------ handle
-enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_FORCE_SPLITS = 8, TUNE_NO_TS = 9, TUNE_NO_FUSED_ATTN = 10, TUNE_COUNT = 11 };
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_FORCE_SPLITS = 8, TUNE_NO_TS = 9, TUNE_NO_FUSED_ATTN = 10, TUNE_NO_SWLOAD = 11, TUNE_SM_RESERVE = 12, TUNE_COUNT = 13 };
 
 struct snb200_context {
   int device;
@@ -39,6 +39,14 @@ struct snb200_context {
   int gemm_events_used;        // events recorded so far (two per GEMM)
 };
 constexpr int kMaxTimedGemms = 4096;
+// SMs the persistent tensor-core grids may use: all of them, minus the ones the caller keeps free for a concurrent
+// kernel (a collective on another stream), rounded so that CTA pairs stay whole.
+static int usable_sms(const snb200_context* h) {
+  int r = h->tune[TUNE_SM_RESERVE];
+  if (r < 0) r = 0;
+  if (r > h->sm_count - 2) r = h->sm_count - 2;
+  return h->sm_count - r;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -80,6 +88,15 @@ static int check_launch(snb200_handle_t h, const char* what) {
 }
 
 extern "C" int snb200_get_version(void) { return 100; }
+#ifdef SNB_TRACE
+// development builds only: the %globaltimer stamps CTA 0 of the last tensor-core kernel left behind
+extern "C" int snb200_trace_read(snb200_handle_t h, unsigned long long* out16) {
+  if (!h || !out16) return SNB200_STATUS_INVALID_VALUE;
+  cudaSetDevice(h->device);
+  cudaStreamSynchronize(h->stream);
+  return cudaMemcpy(out16, h->workspace + (h->workspace_floats - 64), 128, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 13;
+}
+#endif
 
 extern "C" int snb200_create(snb200_handle_t* handle, int device_id) {
   if (!handle) return SNB200_STATUS_INVALID_VALUE;
@@ -292,6 +309,11 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
   const uint64_t pitchB2 = g.batch > 1 ? static_cast<uint64_t>(g.strideB) : b_rows * g.ldb;
   const CUtensorMapSwizzle kmaj_sw = (T::BK == 32) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   bool ok;
+  if (!tma_eligible(g)) {       // the kernel's loader warps read the operands through plain pointers
+    memset(tmA, 0, sizeof(*tmA));
+    memset(tmB, 0, sizeof(*tmB));
+    ok = true;
+  } else {
   if (!g.transA)
     ok = encode_3d(tmA, g.A, g.K, g.M, g.batch, g.lda, pitchA2, T::BK, T::BM, kmaj_sw);
   else
@@ -300,6 +322,7 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
     ok = ok && encode_3d(tmB, g.B, g.K, g.N, g.batch, g.ldb, pitchB2, T::BK, bn_box, kmaj_sw);
   else
     ok = ok && encode_3d(tmB, g.B, g.N, g.K, g.batch, g.ldb, pitchB2, 32, T::BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  }
   if (!ok) return fail(h, SNB200_STATUS_INTERNAL_ERROR, "cuTensorMapEncodeTiled rejected the operand layout");
   UmmaParams& p = *pp;
   p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.batch;
@@ -323,6 +346,11 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
   p.row_op = g.row_op; p.causal = g.causal; p.aux = g.aux;
   p.omap = g.omap;
   if (!omap_vec(g.omap)) p.vec_ok = 0;
+  p.A = g.A; p.B = g.B; p.lda = g.lda; p.ldb = g.ldb;
+  p.strideA = g.batch > 1 ? g.strideA : 0; p.strideB = g.batch > 1 ? g.strideB : 0;
+#ifdef SNB_TRACE
+  p.trace = reinterpret_cast<unsigned long long*>(h->workspace + (h->workspace_floats - 64));   // last 256 bytes of the workspace
+#endif
   p.whole_tiles = 0;       // set by the launcher: it knows the tile grid of its kernel
   p.partial_tiled = 0;
   p.partial = nullptr;
@@ -382,7 +410,7 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pla
     configured[h->device] = true;
   }
   const long long units = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;
-  const int grid = static_cast<int>(units < h->sm_count ? units : h->sm_count);
+  const int grid = static_cast<int>(units < usable_sms(h) ? units : usable_sms(h));
   // launched so that its set-up may overlap the tail of the previous kernel in the stream; the kernel waits for
   // that kernel's completion before it touches global memory
   cudaLaunchConfig_t cfg;
@@ -435,7 +463,8 @@ static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pl
   apply_split_plan<T>(h, g, 2 * T::BM, tiles, p, plan);
   plan.tiles_m = pair_tiles_m;
   const long long units = p.whole_tiles + (tiles - p.whole_tiles) * p.splits;
-  const long long pairs = units < max_pairs[h->device] ? units : max_pairs[h->device];
+  const int pair_cap = max_pairs[h->device] < usable_sms(h) / 2 ? max_pairs[h->device] : usable_sms(h) / 2;
+  const long long pairs = units < pair_cap ? units : pair_cap;
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
   {
     const size_t len = strlen(h->last_kernel);
@@ -503,6 +532,24 @@ static int launch_umma(snb200_handle_t h, const GemmProblem& g, bool split, int 
     case 64: return launch_umma_t<UmmaTile<64, 32, false>>(h, g, plan);
     default: return launch_umma_t<UmmaTile<32, 32, false>>(h, g, plan);
   }
+}
+
+// Operands TMA cannot load (4-byte aligned base, pitch not a multiple of 16 bytes): the same tensor-core kernel fed
+// by loader warps.  Whole tiles only: K is not cut and operands are not swapped on this path.
+static int launch_umma_swload(snb200_handle_t h, const GemmProblem& g, bool split) {
+  const int bn = g.N > 64 ? 128 : g.N > 32 ? 64 : 32;
+  char name[64];
+  snprintf(name, sizeof(name), "umma_%s_128x%d_swload", split ? "3xtf32" : "tf32", bn);
+  note_kernel(h, name, 1);
+  SplitPlan none = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (split) {
+    if (bn == 128) return launch_umma_t<UmmaTile<128, 32, true, 0, false, true>>(h, g, none);
+    if (bn == 64) return launch_umma_t<UmmaTile<64, 32, true, 0, false, true>>(h, g, none);
+    return launch_umma_t<UmmaTile<32, 32, true, 0, false, true>>(h, g, none);
+  }
+  if (bn == 128) return launch_umma_t<UmmaTile<128, 32, false, 0, false, true>>(h, g, none);
+  if (bn == 64) return launch_umma_t<UmmaTile<64, 32, false, 0, false, true>>(h, g, none);
+  return launch_umma_t<UmmaTile<32, 32, false, 0, false, true>>(h, g, none);
 }
 
 static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
@@ -582,7 +629,7 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
       if (forced_bn && bn != forced_bn) continue;
       const int rows = pair ? 256 : 128;
       const long long tiles = static_cast<long long>(g.batch) * ((g.M + rows - 1) / rows) * ((g.N + bn - 1) / bn);
-      const long long slots = pair ? h->sm_count / 2 : h->sm_count;
+      const long long slots = pair ? usable_sms(h) / 2 : usable_sms(h);
       const long long whole = tiles / slots * slots, tail = tiles - whole;
       const TileCost tc = tile_cost(split, pair, bn, g);
       // TF32 + bf16 cross terms: two instruction times per K slice instead of three, on the pair kernel's wide tiles
@@ -705,8 +752,13 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
     const bool swappable = h->tune[TUNE_SPLITK] == 0 && g.N >= 256 && g.K >= 256;   // few rows run transposed
     if (macs < 64.0 * 64 * 64 || (g.M < 16 && !swappable) || g.N < 8) use_umma = false;
   }
-  if (!use_umma) return launch_simt(h, g);
   const bool split = h->math_mode == SNB200_MATH_3XTF32 || h->math_mode == SNB200_MATH_TF32_BF16X2;
+  // unaligned operands of a problem large enough for 128-row tiles: tensor cores fed by loader warps
+  if (!use_umma && h->math_mode != SNB200_MATH_FP32_SIMT && force != 2 && !tma_eligible(g) && g.K >= 1 &&
+      g.row_op == ROW_NONE && h->tune[TUNE_NO_SWLOAD] == 0 &&
+      (force == 1 || (g.M >= 64 && g.N >= 16 && static_cast<double>(g.M) * g.N * g.K * g.batch >= 128.0 * 128 * 128)))
+    return launch_umma_swload(h, g, split);
+  if (!use_umma) return launch_simt(h, g);
   // the bf16 cross-term scheme exists for K-major operands on the pair kernel; everything else runs 3xTF32
   const bool hybrid = h->math_mode == SNB200_MATH_TF32_BF16X2 && !g.transA && g.transB;
   if (g.row_op != ROW_NONE) {
@@ -744,7 +796,7 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
     t.B = g.A; t.ldb = g.lda; t.strideB = g.strideA; t.transB = g.transA ? 0 : 1;
     const int bn = t.N <= 32 ? 32 : 64;
     const long long tiles = static_cast<long long>(t.batch) * ((t.M + 127) / 128) * ((t.N + bn - 1) / bn);
-    long long s = h->sm_count / (tiles > 0 ? tiles : 1);
+    long long s = usable_sms(h) / (tiles > 0 ? tiles : 1);
     if (s < 1) s = 1;
     if (s > g.K / 256) s = g.K / 256;
     const size_t per_split = static_cast<size_t>(g.batch) * g.M * g.N;

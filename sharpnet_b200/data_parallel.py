@@ -63,6 +63,7 @@ class DenseStack:
                    for i in range(n)]
         self.dx = [None] + [GPUTensor((local_batch, dims[i]), None, wrapper) for i in range(1, n)]
         self.dy = GPUTensor((local_batch, dims[-1]), None, wrapper)
+        self.reserve_pending = False
 
     def forward(self):
         lib, h = self.w.lib, self.w.handle
@@ -82,6 +83,10 @@ class DenseStack:
             h, self.layout, self.batch, self.dims[i], self.dims[i + 1], src.Pointer, self.W[i].Pointer, grad.Pointer,
             act, None if act == ACT_IDENTITY else self.y[i].Pointer, None, 1.0, p(dz), p(dx), p(dW), p(db))
         check(h, st)
+        if self.reserve_pending and (dx is not None or dW is not None):
+            # one product has run beside the collective queued before it: back to every SM
+            self.w.set_tuning(_capi.TUNE_SM_RESERVE, 0)
+            self.reserve_pending = False
 
     def backward(self, after_gradients=None, after_layer=None, defer_smallest=False):
         """Backward through every layer, last to first.
@@ -132,11 +137,18 @@ class GradientAllReduce:
     One process per GPU: rank 0 creates the NCCL id and ``broadcast_bytes`` (any callable that
     ships 128 bytes from rank 0 to everyone, e.g. built on torch.distributed) distributes it."""
 
+    # CTAs the collective may use, and therefore the SMs the product queued right behind a reduction leaves free
+    # for it: a persistent GEMM grid counts on every SM it was launched for, so a collective that has to squeeze
+    # in displaces some of its CTAs for as long as it runs and the GEMM ends that much later -- the overlap is lost.
+    COLLECTIVE_CTAS = 16
+
     def __init__(self, device_id, world_size, rank, broadcast_bytes):
         import ctypes
+        import os
         import torch
         self.torch = torch
         self.world = world_size
+        os.environ.setdefault("NCCL_MAX_CTAS", str(self.COLLECTIVE_CTAS))
         self.comm_wrapper = GPUWrapper(device_id)          # a second handle: owns the communicator and its stream
         self.stream = torch.cuda.Stream(device=device_id)
         self.comm_wrapper.set_stream(self.stream)
@@ -161,6 +173,9 @@ class GradientAllReduce:
         bufs = (ctypes.c_void_p * 2)(stack.dW[i].Pointer, stack.db[i].Pointer)
         counts = (ctypes.c_longlong * 2)(stack.dW[i].Count, stack.db[i].Count)
         check(h, lib.snb200_allreduce_sum_group(h, 2, bufs, counts))
+        # the next product of the compute handle leaves room for the collective (see COLLECTIVE_CTAS)
+        stack.w.set_tuning(_capi.TUNE_SM_RESERVE, self.COLLECTIVE_CTAS)
+        stack.reserve_pending = True
 
     def update_layer(self, stack, i, compute_stream, update):
         """Queues ``update(lib, handle, stack, i)`` -- the optimizer step of layer ``i`` -- on the side stream,

@@ -140,6 +140,41 @@ def test_beta_zero_ignores_nan_in_c(wrapper):
         assert np.isfinite(C.ContentAsFloatArray()).all()
 
 
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+@pytest.mark.parametrize("tA", [False, True])
+@pytest.mark.parametrize("tB", [False, True])
+def test_unaligned_operands_run_on_the_tensor_cores(wrapper, mode, tol, tA, tB):
+    """Views that start 4 bytes into an allocation and widths that are not multiples of 4 floats (SharpNet slices
+    tensors at float granularity, Prod/GPU/GpuTensor.cs:1518-1521): TMA cannot load them, loader warps do, and the
+    product still runs on the tensor cores."""
+    import torch
+    wrapper.set_math_mode(mode)
+    rng = np.random.default_rng(21)
+    for (M, N, K, off_a, off_b, beta, batch) in ((512, 384, 768, 1, 0, 0.0, 1), (517, 389, 771, 0, 0, 1.0, 1),
+                                                 (517, 389, 771, 3, 2, 0.0, 1), (130, 70, 203, 1, 1, 1.0, 3),
+                                                 (128, 33, 64, 1, 0, 0.0, 1)):
+        sa = (batch,) + ((K, M) if tA else (M, K))
+        sb = (batch,) + ((N, K) if tB else (K, N))
+        a = rng.uniform(-1, 1, sa).astype(np.float32)
+        b = rng.uniform(-1, 1, sb).astype(np.float32)
+        c = rng.uniform(-1, 1, (batch, M, N)).astype(np.float32)
+        base_a = torch.zeros(a.size + off_a, dtype=torch.float32, device=wrapper.device)
+        base_b = torch.zeros(b.size + off_b, dtype=torch.float32, device=wrapper.device)
+        base_a[off_a:] = torch.from_numpy(a.ravel()).to(wrapper.device)
+        base_b[off_b:] = torch.from_numpy(b.ravel()).to(wrapper.device)
+        A = GPUTensor(sa, wrapper=wrapper, storage=base_a[off_a:])
+        B = GPUTensor(sb, wrapper=wrapper, storage=base_b[off_b:])
+        C = GPUTensor((batch, M, N), c, wrapper)
+        C.BatchMatrixMultiplication(A, tA, B, tB, 1.0, beta)
+        wrapper.check_device_status()
+        assert "swload" in wrapper.last_kernel(), wrapper.last_kernel()
+        f64 = orc.batch_matrix_multiplication(a, tA, b, tB, c, 1.0, beta, f64=True)
+        mkl = orc.batch_matrix_multiplication(a, tA, b, tB, c.copy(), 1.0, beta)
+        got = C.ContentAsFloatArray()
+        e64, emkl = orc.scaled_error(got, f64, K, 1, 1), orc.scaled_error(got, mkl, K, 1, 1)
+        assert e64 <= tol and emkl <= tol, (M, N, K, tA, tB, off_a, off_b, e64, emkl)
+
+
 def test_unaligned_views_fall_back_to_simt(wrapper):
     # SharpNet slices tensors at 4-byte granularity: a pointer that is not 16-byte aligned must work
     import torch
@@ -152,8 +187,11 @@ def test_unaligned_views_fall_back_to_simt(wrapper):
     A = GPUTensor((M, K), wrapper=wrapper, storage=base[1:])
     B = GPUTensor((K, N), b, wrapper)
     C = GPUTensor((M, N), None, wrapper)
-    wrapper.set_tuning(TUNE_FORCE_PATH, 1)
-    C.Dot(A, False, B, False, 1, 0)
+    wrapper.set_tuning(11, 1)        # loader-warp kernel off: the SIMT kernel is the net under it
+    try:
+        C.Dot(A, False, B, False, 1, 0)
+    finally:
+        wrapper.set_tuning(11, 0)
     assert wrapper.last_kernel().startswith("simt")
     ref = orc.dot_f64(a.ravel(), M, K, False, b.ravel(), K, N, False, None, 1.0, 0.0)
     assert orc.scaled_error(C.ContentAsFloatArray(), ref, K, 1, 1) <= TOL_3XTF32
