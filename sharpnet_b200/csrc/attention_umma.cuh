@@ -42,6 +42,8 @@ struct AttnTile {
   static constexpr int TMEM_COLS = 512;
   static constexpr int COL_S = 0, COL_PLO = TKN, COL_O = 2 * TKN;   // TMEM columns
   static constexpr int REGS_CTRL = 72, REGS_SPLIT = 64, REGS_EPI = 232;
+  static constexpr int REGS_LAUNCH = (65536 / THREADS) / 8 * 8;   // what the CTA is launched with, per thread
+  static_assert(REGS_CTRL + REGS_SPLIT + REGS_EPI <= THREADS / 128 * REGS_LAUNCH, "register shares exceed the CTA's pool");
   static constexpr int MN_CHUNK_BYTES = BK * 128;
   static_assert(TKN == 32 || TKN == 64 || TKN == 128, "score tile 32, 64 or 128 wide");
   static_assert(EN == 32 || EN == 64 || EN == 128, "embedding tile 32, 64 or 128 wide");

@@ -75,9 +75,18 @@ struct UmmaTile {
   static constexpr int THREADS = 128 + EPI_THREADS + N_SPLIT_THREADS + N_LOAD_THREADS;
   static constexpr int REGS_CTRL = SWLOAD ? 56 : 72;
   static constexpr int REGS_SPLIT = TS ? 112 : 64;                  // TS: a whole A row and its lo plane in registers
+  // setmaxnreg only moves registers inside what the CTA was launched with: THREADS x (the per-thread count the
+  // kernel is compiled for, 65536 / THREADS rounded down to a multiple of 8).  A group that asks for more than the
+  // other groups have given back waits for ever, so the shares must add up to at most that pool.
+  static constexpr int REGS_LAUNCH = (65536 / THREADS) / 8 * 8 > 255 ? 248 : (65536 / THREADS) / 8 * 8;
+  static constexpr int REG_POOL_PER_128 = THREADS / 128 * REGS_LAUNCH;
   static constexpr int REGS_EPI_RAW =
-      (65536 / 128 - REGS_CTRL - (SPLIT ? REGS_SPLIT : 0) - (SWLOAD ? REGS_LOAD : 0)) / EPI_GROUPS;
+      (REG_POOL_PER_128 - REGS_CTRL - (SPLIT ? REGS_SPLIT : 0) - (SWLOAD ? REGS_LOAD : 0)) / EPI_GROUPS;
   static constexpr int REGS_EPI = (REGS_EPI_RAW > 232 ? 232 : REGS_EPI_RAW) / 8 * 8;
+  static_assert(REGS_CTRL + EPI_GROUPS * REGS_EPI + (SPLIT ? REGS_SPLIT : 0) + (SWLOAD ? REGS_LOAD : 0) <= REG_POOL_PER_128,
+                "register shares exceed what the CTA is launched with");
+  static_assert(REGS_CTRL <= REGS_LAUNCH && REGS_SPLIT <= REGS_LAUNCH && REGS_LOAD <= REGS_LAUNCH,
+                "setmaxnreg.dec must not raise the count");
   // K-major tiles: one row = BK fp32.  128-byte swizzle for BK = 32, 64-byte for BK = 16.
   static constexpr int KMAJ_ROW_BYTES = BK * 4;
   static constexpr int KMAJ_SBO = 8 * KMAJ_ROW_BYTES;
@@ -143,6 +152,12 @@ struct UmmaParams {
 #define SNB_STAMP(p, slot) do { if ((p).trace != nullptr && blockIdx.x == 0) (p).trace[slot] = globaltimer_ns(); } while (0)
 #else
 #define SNB_STAMP(p, slot) do { } while (0)
+#endif
+
+#ifdef SNB_SLOW_ISSUE
+constexpr bool kSlowIssue = true;    // development builds: every descriptor rebuilt from scratch (A/B measurements)
+#else
+constexpr bool kSlowIssue = false;
 #endif
 
 // Work unit u of a launch over n_tiles output tiles: which tile, which K range, and (split >= 0) which
@@ -759,6 +774,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t b_sbo = p.b_mn ? T::MNMAJ_SBO : T::KMAJ_SBO;
       const uint32_t a_lay = p.a_mn ? T::MNMAJ_LAYOUT : T::KMAJ_LAYOUT;
       const uint32_t b_lay = p.b_mn ? T::MNMAJ_LAYOUT : T::KMAJ_LAYOUT;
+      const uint64_t desc_a0 = make_smem_desc(0, a_lbo, a_sbo, a_lay), desc_b0 = make_smem_desc(0, b_lbo, b_sbo, b_lay);
+      const uint32_t a_step16 = a_step >> 4, b_step16 = b_step >> 4;
       int s = 0;
       uint32_t ph = 0;
       uint32_t acc_ph = 0;  // bit b = phase of TMEM buffer b
@@ -778,10 +795,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint64_t* ready = T::SPLIT ? &split_bar[s] : &full_bar[s];
             if (!mbar_wait(ready, ph, abortp)) { ok = false; break; }
             if (t == blockIdx.x && kb == kb_begin) SNB_STAMP(p, 5);
+            if (t == blockIdx.x && kb - kb_begin < 8) SNB_STAMP(p, 16 + 2 * (kb - kb_begin));
             tc_fence_after_sync();
             const uint32_t a_hi = smem_u32(ring + s * T::STAGE_BYTES);
             const uint32_t b_hi = a_hi + T::A_BYTES;
             const uint32_t a_tmem = tmem_base + T::TS_A_COL0 + s * T::TS_A_COLS;   // TS: hi plane, lo plane 32 columns on
+            if (!T::TS && !kSlowIssue) {
+              // Descriptors differ from slice to slice and from plane to plane only in their start-address field (bits
+              // 0-13, in 16-byte units), so they are formed by additions to one descriptor per operand and K block:
+              // the issuing lane spends a few instructions per tcgen05.mma instead of rebuilding every descriptor.
+              const uint64_t da0 = desc_a0 + (a_hi >> 4), db0 = desc_b0 + (b_hi >> 4);
+#pragma unroll
+              for (int ks = 0; ks < BK / kUmmaK; ++ks) {
+                const uint64_t da_hi = da0 + ks * a_step16, db_hi = db0 + ks * b_step16;
+                const uint32_t first = (kb == kb0 && ks == 0) ? 0u : 1u;
+                if (T::SPLIT) {
+                  umma_tf32_ss(d_tmem, da_hi + (T::RAW_BYTES >> 4), db_hi, idesc, first);
+                  umma_tf32_ss(d_tmem, da_hi, db_hi + (T::RAW_BYTES >> 4), idesc, 1u);
+                  umma_tf32_ss(d_tmem, da_hi, db_hi, idesc, 1u);
+                } else {
+                  umma_tf32_ss(d_tmem, da_hi, db_hi, idesc, first);
+                }
+              }
+            } else
 #pragma unroll
             for (int ks = 0; ks < BK / kUmmaK; ++ks) {
               const uint64_t da_hi = make_smem_desc(a_hi + ks * a_step, a_lbo, a_sbo, a_lay);
@@ -803,6 +839,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
             umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+            if (t == blockIdx.x && kb - kb_begin < 8) SNB_STAMP(p, 17 + 2 * (kb - kb_begin));
             if (++s == STAGES) { s = 0; ph ^= 1; }
           }
           if (ok) umma_commit(&acc_full_bar[buf]);

@@ -90,11 +90,11 @@ static int check_launch(snb200_handle_t h, const char* what) {
 extern "C" int snb200_get_version(void) { return 100; }
 #ifdef SNB_TRACE
 // development builds only: the %globaltimer stamps CTA 0 of the last tensor-core kernel left behind
-extern "C" int snb200_trace_read(snb200_handle_t h, unsigned long long* out16) {
-  if (!h || !out16) return SNB200_STATUS_INVALID_VALUE;
+extern "C" int snb200_trace_read(snb200_handle_t h, unsigned long long* out32) {
+  if (!h || !out32) return SNB200_STATUS_INVALID_VALUE;
   cudaSetDevice(h->device);
   cudaStreamSynchronize(h->stream);
-  return cudaMemcpy(out16, h->workspace + (h->workspace_floats - 64), 128, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 13;
+  return cudaMemcpy(out32, h->workspace + (h->workspace_floats - 64), 256, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 13;
 }
 #endif
 

@@ -129,6 +129,10 @@ class DenseStack:
                 after_gradients(deferred)
             if after_layer is not None:
                 after_layer(deferred)
+        if self.reserve_pending:
+            # nothing of this pass runs beside the last collective; what comes next gets every SM again
+            self.w.set_tuning(_capi.TUNE_SM_RESERVE, 0)
+            self.reserve_pending = False
 
 
 class GradientAllReduce:

@@ -75,3 +75,83 @@ def test_shard_rows_follows_the_reference_split():
 def test_step_flops_match_the_stated_work():
     # 12.61 TFLOP per step for batch 65536, 4096 -> 4096 -> 4096 -> 1000
     assert abs(mlp_step_flops(65536, MLP_DIMS) / 1e12 - 12.61) < 0.01
+
+
+class _FakeTensor:
+    def __init__(self, count, name):
+        self.Count, self.Pointer, self.Shape = count, name, [count]
+
+
+class _FakeLib:
+    """Records the C-ABI calls the host logic makes (no device needed): the order of the backward products, where
+    the gradient hooks fire, and when SMs are kept free for the collective."""
+    def __init__(self):
+        self.calls = []
+
+    def snb200_dense_fwd(self, h, layout, M, K, N, x, W, b, act, z, y):
+        self.calls.append(("fwd", y))
+        return 0
+
+    def snb200_dense_bwd(self, h, layout, M, K, N, x, W, dy, act, y, z, mult, dz, dx, dW, db):
+        self.calls.append(("bwd", dW, dx, db, act))
+        return 0
+
+
+class _FakeWrapper:
+    def __init__(self):
+        self.lib, self.handle, self.tuning = _FakeLib(), "h", []
+
+    def set_tuning(self, key, value):
+        self.tuning.append((len(self.lib.calls), key, value))
+
+
+def _fake_stack(dims, acts):
+    from sharpnet_b200.data_parallel import DenseStack
+    s = DenseStack.__new__(DenseStack)
+    s.w, s.batch, s.dims, s.acts, s.layout = _FakeWrapper(), 8, list(dims), list(acts), 0
+    n = len(dims) - 1
+    s.W = [_FakeTensor(dims[i] * dims[i + 1], f"W{i}") for i in range(n)]
+    s.b = [_FakeTensor(dims[i + 1], f"b{i}") for i in range(n)]
+    s.dW = [_FakeTensor(dims[i] * dims[i + 1], f"dW{i}") for i in range(n)]
+    s.db = [_FakeTensor(dims[i + 1], f"db{i}") for i in range(n)]
+    s.x = _FakeTensor(8 * dims[0], "x")
+    s.y = [_FakeTensor(8 * dims[i + 1], f"y{i}") for i in range(n)]
+    s.dz = [None if acts[i] == 5 else _FakeTensor(8 * dims[i + 1], f"dz{i}") for i in range(n)]
+    s.dx = [None] + [_FakeTensor(8 * dims[i], f"dx{i}") for i in range(1, n)]
+    s.dy = _FakeTensor(8 * dims[-1], "dy")
+    s.reserve_pending = False
+    return s
+
+
+def test_backward_queues_gradients_before_dx_and_the_smallest_gradient_last():
+    stack = _fake_stack((4096, 4096, 4096, 1000), (1, 1, 5))          # ReLU, ReLU, identity
+    events = []
+    stack.backward(after_gradients=lambda i: events.append(("grads", i, len(stack.w.lib.calls))),
+                   after_layer=lambda i: events.append(("layer", i, len(stack.w.lib.calls))), defer_smallest=True)
+    calls = stack.w.lib.calls
+    # layer 2 (the smallest weights): db now, dx, dW at the very end; layers 1 and 0: dW + db, then dx
+    assert [(c[1], c[2]) for c in calls] == [(None, None), (None, "dx2"), ("dW1", None), (None, "dx1"), ("dW0", None),
+                                             ("dW2", None)]
+    assert calls[0][3] == "db2" and calls[-1][3] is None            # the bias gradient is not recomputed
+    assert calls[1][4] == 5 and calls[3][4] == 5                     # dx alone runs on the stored dz: no activation
+    # the gradient hook fires right behind each dW product, before that layer's dx
+    assert events == [("grads", 1, 3), ("layer", 1, 4), ("grads", 0, 5), ("layer", 0, 5), ("grads", 2, 6), ("layer", 2, 6)]
+    # without deferral: layer order 2, 1, 0
+    stack2 = _fake_stack((64, 32, 16), (1, 5))
+    order = []
+    stack2.backward(after_gradients=order.append)
+    assert order == [1, 0]
+    assert [(c[1], c[2]) for c in stack2.w.lib.calls] == [("dW1", None), (None, "dx1"), ("dW0", None)]
+
+
+def test_sm_reservation_covers_exactly_one_product_after_each_reduction():
+    from sharpnet_b200 import _capi
+    stack = _fake_stack((64, 32, 16), (1, 5))
+
+    def fake_reduce(i):             # what GradientAllReduce.reduce_layer does on the compute handle
+        stack.w.set_tuning(_capi.TUNE_SM_RESERVE, 16)
+        stack.reserve_pending = True
+    stack.backward(after_gradients=fake_reduce)
+    # calls: dW1(+db1) | reduce -> reserve | dx1 -> release | dW0 | reduce -> reserve | end of the pass -> release
+    assert stack.w.tuning == [(1, _capi.TUNE_SM_RESERVE, 16), (2, _capi.TUNE_SM_RESERVE, 0), (3, _capi.TUNE_SM_RESERVE, 16),
+                              (3, _capi.TUNE_SM_RESERVE, 0)]
