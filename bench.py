@@ -707,16 +707,19 @@ def recorded_traffic(rows_per_gpu):
         if rec is None:
             raise ValueError("no TRAFFIC_JSON line")
         scale = rows_per_gpu / rec["rows"]
+        total = sum(g["read"] * scale + g["write"] * (scale if g["rows_are"] == "M" else 1.0) for g in rec["launches"])
+        per_launch = total / len(rec["launches"])
         r = rows_per_gpu
         d = DIMS
         # algorithmic bytes of the 8 GEMMs: each operand touched once
         gemms = [(r, d[1], d[0]), (r, d[2], d[1]), (r, d[3], d[2]), (d[3], d[2], r), (r, d[2], d[3]), (d[2], d[1], r),
                  (r, d[1], d[2]), (d[1], d[0], r)]
         alg = sum(4.0 * (m * k + k * n + m * n) for m, n, k in gemms) / len(gemms)
-        return {"traffic": rec["dram_bytes_per_launch"] * scale, "algorithmic_bytes_per_launch": alg,
+        return {"traffic": per_launch, "algorithmic_bytes_per_launch": alg,
                 "traffic_source": f"profiles/mlp_step_gemm_dram_traffic.md: ncu dram__bytes_read.sum + dram__bytes_write.sum "
-                                  f"averaged over the step's 8 GEMM launches at {rec['rows']} rows, x {scale:g} for "
-                                  f"{rows_per_gpu} rows (traffic grows with the rows: they are M or K of every GEMM)"}
+                                  f"of the step's 8 GEMM launches captured at {rec['rows']} rows, scaled x {scale:g} to "
+                                  f"{rows_per_gpu} rows (reads, and the writes of the products whose M is the rows, grow "
+                                  "with the rows; the dW results do not), averaged per launch"}
     except (OSError, ValueError, KeyError) as e:
         return {"traffic": None, "algorithmic_bytes_per_launch": alg, "traffic_source": f"no committed capture ({e})"}
 
@@ -738,6 +741,11 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
     if world > 1:
+        # the collective's CTA budget (see GradientAllReduce.COLLECTIVE_CTAS) must be in the environment before the
+        # first NCCL communicator of the process reads it
+        ctas = int(os.environ.get("SNB200_COLLECTIVE_CTAS", "16"))
+        if ctas > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(ctas))
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     peaks = _peaks()

@@ -604,62 +604,47 @@ __device__ __forceinline__ void split_stage_ts(uint8_t* stage, uint32_t tmem_a, 
   tmem_st_wait();
 }
 
-// One operand tile built in shared memory by the loader warps, in the layout TMA delivers.
+// One operand tile built in shared memory by the loader warps, in the layout TMA delivers, with asynchronous 4-byte
+// copies (cp.async): no alignment beyond a float's is needed, nothing is staged in registers, and a thread keeps
+// the copies of several stages in flight (the loader loop waits for a stage's copies only when it signals it).
 //   K-major (`mn` = 0): `rows` tile rows (M or N index) of 32 K values; row r sits at r * 128 bytes, its 16-byte chunk
 //       c at position c ^ (r & 7).  Source element (r, k) = src[(r0 + r) * ld + k0 + k].
 //   MN-major (`mn` = 1): 32 K rows of `rows` contiguous M/N values, in chunks of 32 values: chunk j at j * 4096 bytes,
 //       K row k at k * 128, 32-byte atom a at position a ^ (k & 3).  Source element (k, r) = src[(k0 + k) * ld + r0 + r].
-// Every item is one 16-byte chunk of the tile.  Its four floats start at a source address that is only 4-byte
-// aligned, so the thread loads the two 16-byte aligned chunks that cover them and shifts.  A chunk is loaded only
-// if it holds at least one element that is inside the matrix, so no load leaves the pages the matrix lies in;
-// elements outside the matrix become zeros, as TMA's out-of-bounds fill does.
-__device__ __forceinline__ void sw_load_tile(uint8_t* dst, const float* src, long long ld, int mn, int rows, int r0,
-                                             int r_limit, int k0, int k_limit, int tid, int nthreads) {
-  // run = the contiguous direction of the source: K for K-major tiles, M/N for MN-major ones
-  const int run_len = mn ? rows : 32, n_runs = mn ? 32 : rows;
-  const int chunks_per_run = run_len >> 2;
-  const int items = n_runs * chunks_per_run;
-  for (int it0 = tid; it0 < items; it0 += 4 * nthreads) {
-    float4 lo4[4], hi4[4];
-    int shift[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int it = it0 + u * nthreads;
-      lo4[u] = make_float4(0.f, 0.f, 0.f, 0.f); hi4[u] = lo4[u]; shift[u] = 0;
-      if (it < items) {
-        const int run = it / chunks_per_run, c = it - run * chunks_per_run;
-        const int outer = (mn ? k0 : r0) + run;                 // index along the strided direction
-        const int inner0 = (mn ? r0 : k0) + 4 * c;              // first index along the contiguous direction
-        const int outer_limit = mn ? k_limit : r_limit, inner_limit = mn ? r_limit : k_limit;
-        if (outer < outer_limit && inner0 < inner_limit) {
-          const float* ptr = src + static_cast<long long>(outer) * ld + inner0;
-          const int sh = static_cast<int>((reinterpret_cast<uintptr_t>(ptr) >> 2) & 3);
-          const float4* aligned = reinterpret_cast<const float4*>(ptr - sh);
-          shift[u] = sh;
-          lo4[u] = __ldg(aligned);                               // holds element inner0: inside the matrix
-          if (sh != 0 && inner0 + 4 - sh < inner_limit) hi4[u] = __ldg(aligned + 1);   // holds element inner0 + 4 - sh
-        }
-      }
+// A warp copies 32 consecutive source floats per instruction (one 128-byte line).  Elements outside the matrix are
+// zero-filled (source size 0 with the address clamped into the matrix), as TMA's out-of-bounds fill does.
+__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const float* src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void sw_issue_tile(uint8_t* dst, const float* src, long long ld, int mn, int rows, int r0,
+                                              int r_limit, int k0, int k_limit, int tid, int nthreads) {
+  const uint32_t d0 = smem_u32(dst);
+  const int lane = tid & 31, w = tid >> 5, nw = nthreads >> 5;
+  if (!mn) {
+    // one warp instruction = one tile row: lane = K index
+    const int k = k0 + lane;
+    const bool k_ok = k < k_limit;
+    const uint32_t in_row = ((lane >> 2) << 4) | ((lane & 3) << 2);          // chunk lane / 4, word lane % 4
+    for (int r = w; r < rows; r += nw) {
+      const int row = r0 + r;
+      const bool ok = k_ok && row < r_limit;
+      const float* ptr = ok ? src + static_cast<long long>(row) * ld + k : src;
+      cp_async_4(d0 + r * 128 + (in_row ^ ((r & 7) << 4)), ptr, ok ? 4u : 0u);
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int it = it0 + u * nthreads;
-      if (it >= items) break;
-      const int run = it / chunks_per_run, c = it - run * chunks_per_run;
-      const int inner0 = (mn ? r0 : k0) + 4 * c;
-      const int inner_limit = mn ? r_limit : k_limit;
-      const float w[8] = {lo4[u].x, lo4[u].y, lo4[u].z, lo4[u].w, hi4[u].x, hi4[u].y, hi4[u].z, hi4[u].w};
-      float t[7], v[4];
-#pragma unroll
-      for (int i = 0; i < 7; ++i) t[i] = (shift[u] & 1) ? w[i + 1] : w[i];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = (shift[u] & 2) ? t[i + 2] : t[i];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = (inner0 + i < inner_limit) ? v[i] : 0.0f;   // ragged edge inside a loaded chunk
-      uint32_t off;
-      if (!mn) off = run * 128 + ((c ^ (run & 7)) << 4);
-      else     off = (c >> 3) * 4096 + run * 128 + (((((c >> 1) & 3) ^ (run & 3)) << 5) | ((c & 1) << 4));
-      *reinterpret_cast<float4*>(dst + off) = make_float4(v[0], v[1], v[2], v[3]);
+  } else {
+    // one warp instruction = 32 consecutive M/N values of one K row: lane = position in the 32-wide chunk
+    const int chunks = rows >> 5;
+    const uint32_t in_row = ((lane >> 3) << 5) | ((lane & 7) << 2);          // atom lane / 8, word lane % 8
+    for (int i = w; i < 32 * chunks; i += nw) {
+      const int kr = i & 31, j = i >> 5;
+      const int k = k0 + kr, col = r0 + 32 * j + lane;
+      const bool ok = k < k_limit && col < r_limit;
+      const float* ptr = ok ? src + static_cast<long long>(k) * ld + col : src;
+      cp_async_4(d0 + j * 4096 + kr * 128 + (in_row ^ ((kr & 3) << 5)), ptr, ok ? 4u : 0u);
     }
   }
 }
@@ -932,9 +917,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------------ loader warps (operands TMA cannot load)
     reg_dealloc<T::REGS_LOAD>();
     const int tid = threadIdx.x - T::LOAD_THREAD0;
-    int s = 0;
+    constexpr int DEPTH = 2;      // stages whose copies stay in flight behind the one being signalled (< STAGES)
+    static_assert(!T::SWLOAD || STAGES > DEPTH, "the loader keeps fewer stages in flight than the ring holds");
+    int s = 0, s_signal = 0, pending = 0;
     uint32_t ph = 0;
     bool ok = true;
+    // The copies of a stage are complete for this thread after cp.async.wait_group; the fence then orders them
+    // before the tensor core's reads (async proxy), and one arrival per warp signals the stage.
+    auto signal = [&]() {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_bar[s_signal]);
+      if (++s_signal == STAGES) s_signal = 0;
+      --pending;
+    };
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int tile, split, kb_begin, kb_end, b, tm, tn;
       unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
@@ -944,14 +940,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait_warp(&empty_bar[s], ph ^ 1, abortp)) { ok = false; break; }
         uint8_t* a_dst = ring + s * T::STAGE_BYTES;
-        sw_load_tile(a_dst, Ab, p.lda, p.a_mn, BM, tm * BM, p.M, kb * BK, p.K, tid, T::N_LOAD_THREADS);
-        sw_load_tile(a_dst + T::A_BYTES, Bb, p.ldb, p.b_mn, BN, tn * BN, p.N, kb * BK, p.K, tid, T::N_LOAD_THREADS);
-        fence_proxy_async_smem();   // the tensor core (TF32 mode) reads these tiles through the async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_bar[s]);
+        sw_issue_tile(a_dst, Ab, p.lda, p.a_mn, BM, tm * BM, p.M, kb * BK, p.K, tid, T::N_LOAD_THREADS);
+        sw_issue_tile(a_dst + T::A_BYTES, Bb, p.ldb, p.b_mn, BN, tn * BN, p.N, kb * BK, p.K, tid, T::N_LOAD_THREADS);
+        cp_async_commit();
+        ++pending;
         if (++s == STAGES) { s = 0; ph ^= 1; }
+        if (pending > DEPTH) {
+          cp_async_wait<DEPTH>();
+          signal();
+        }
       }
     }
+    cp_async_wait<0>();           // the tail: everything has landed (also when the CTA is aborting)
+    while (ok && pending > 0) signal();
   }
 
   // ---------------------------------------------------------------------- teardown

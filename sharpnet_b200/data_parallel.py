@@ -152,7 +152,10 @@ class GradientAllReduce:
         import torch
         self.torch = torch
         self.world = world_size
-        os.environ.setdefault("NCCL_MAX_CTAS", str(self.COLLECTIVE_CTAS))
+        # SNB200_COLLECTIVE_CTAS overrides the count; 0 leaves NCCL alone and reserves nothing (A/B measurements)
+        self.COLLECTIVE_CTAS = int(os.environ.get("SNB200_COLLECTIVE_CTAS", self.COLLECTIVE_CTAS))
+        if self.COLLECTIVE_CTAS > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(self.COLLECTIVE_CTAS))
         self.comm_wrapper = GPUWrapper(device_id)          # a second handle: owns the communicator and its stream
         self.stream = torch.cuda.Stream(device=device_id)
         self.comm_wrapper.set_stream(self.stream)
@@ -178,8 +181,9 @@ class GradientAllReduce:
         counts = (ctypes.c_longlong * 2)(stack.dW[i].Count, stack.db[i].Count)
         check(h, lib.snb200_allreduce_sum_group(h, 2, bufs, counts))
         # the next product of the compute handle leaves room for the collective (see COLLECTIVE_CTAS)
-        stack.w.set_tuning(_capi.TUNE_SM_RESERVE, self.COLLECTIVE_CTAS)
-        stack.reserve_pending = True
+        if self.COLLECTIVE_CTAS > 0:
+            stack.w.set_tuning(_capi.TUNE_SM_RESERVE, self.COLLECTIVE_CTAS)
+            stack.reserve_pending = True
 
     def update_layer(self, stack, i, compute_stream, update):
         """Queues ``update(lib, handle, stack, i)`` -- the optimizer step of layer ``i`` -- on the side stream,
