@@ -626,25 +626,30 @@ __device__ __forceinline__ void sw_issue_tile(uint8_t* dst, const float* src, lo
   const int lane = tid & 31, w = tid >> 5, nw = nthreads >> 5;
   if (!mn) {
     // one warp instruction = one tile row: lane = K index
-    const int k = k0 + lane;
-    const bool k_ok = k < k_limit;
+    const bool k_ok = k0 + lane < k_limit;
     const uint32_t in_row = ((lane >> 2) << 4) | ((lane & 3) << 2);          // chunk lane / 4, word lane % 4
-    for (int r = w; r < rows; r += nw) {
-      const int row = r0 + r;
-      const bool ok = k_ok && row < r_limit;
-      const float* ptr = ok ? src + static_cast<long long>(row) * ld + k : src;
-      cp_async_4(d0 + r * 128 + (in_row ^ ((r & 7) << 4)), ptr, ok ? 4u : 0u);
+    const float* ptr = src + static_cast<long long>(r0 + w) * ld + k0 + lane;
+    const long long step = static_cast<long long>(nw) * ld;
+#pragma unroll 4
+    for (int r = w; r < rows; r += nw, ptr += step) {
+      const bool ok = k_ok && r0 + r < r_limit;
+      cp_async_4(d0 + r * 128 + (in_row ^ ((r & 7) << 4)), ok ? ptr : src, ok ? 4u : 0u);
     }
   } else {
-    // one warp instruction = 32 consecutive M/N values of one K row: lane = position in the 32-wide chunk
+    // one warp instruction = 32 consecutive M/N values of one K row: lane = position in the 32-wide chunk.
+    // Warp w takes K rows w, w + nw, ... of every chunk.
     const int chunks = rows >> 5;
     const uint32_t in_row = ((lane >> 3) << 5) | ((lane & 7) << 2);          // atom lane / 8, word lane % 8
-    for (int i = w; i < 32 * chunks; i += nw) {
-      const int kr = i & 31, j = i >> 5;
-      const int k = k0 + kr, col = r0 + 32 * j + lane;
-      const bool ok = k < k_limit && col < r_limit;
-      const float* ptr = ok ? src + static_cast<long long>(k) * ld + col : src;
-      cp_async_4(d0 + j * 4096 + kr * 128 + (in_row ^ ((kr & 3) << 5)), ptr, ok ? 4u : 0u);
+    const long long step = static_cast<long long>(nw) * ld;
+    for (int j = 0; j < chunks; ++j) {
+      const int col = r0 + 32 * j + lane;
+      const bool col_ok = col < r_limit;
+      const float* ptr = src + static_cast<long long>(k0 + w) * ld + col;
+#pragma unroll 4
+      for (int kr = w; kr < 32; kr += nw, ptr += step) {
+        const bool ok = col_ok && k0 + kr < k_limit;
+        cp_async_4(d0 + j * 4096 + kr * 128 + (in_row ^ ((kr & 3) << 5)), ok ? ptr : src, ok ? 4u : 0u);
+      }
     }
   }
 }
@@ -917,8 +922,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------------ loader warps (operands TMA cannot load)
     reg_dealloc<T::REGS_LOAD>();
     const int tid = threadIdx.x - T::LOAD_THREAD0;
-    constexpr int DEPTH = 2;      // stages whose copies stay in flight behind the one being signalled (< STAGES)
-    static_assert(!T::SWLOAD || STAGES > DEPTH, "the loader keeps fewer stages in flight than the ring holds");
+    constexpr int DEPTH = STAGES - 1 < 3 ? STAGES - 1 : 3;   // stages whose copies stay in flight behind the one being signalled
     int s = 0, s_signal = 0, pending = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -938,6 +942,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const float* Ab = p.A + static_cast<long long>(b) * p.strideA;
       const float* Bb = p.B + static_cast<long long>(b) * p.strideB;
       for (int kb = kb_begin; kb < kb_end; ++kb) {
+        // about to wait for the consumers: first hand over everything that is in flight, they may be waiting for it
+        const bool must_wait = __shfl_sync(0xffffffffu, mbar_try_wait(&empty_bar[s], ph ^ 1) ? 0 : 1, 0) != 0;
+        if (must_wait && pending > 0) {
+          cp_async_wait<0>();
+          while (pending > 0) signal();
+        }
         if (!mbar_wait_warp(&empty_bar[s], ph ^ 1, abortp)) { ok = false; break; }
         uint8_t* a_dst = ring + s * T::STAGE_BYTES;
         sw_issue_tile(a_dst, Ab, p.lda, p.a_mn, BM, tm * BM, p.M, kb * BK, p.K, tid, T::N_LOAD_THREADS);

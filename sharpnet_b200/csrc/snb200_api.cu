@@ -1328,6 +1328,9 @@ static int try_fused_attention_fwd(snb200_handle_t h, int batch, int Tq, int Tk,
   o.C = y; o.alpha = 1.0f; o.beta = 0.0f; o.act = ACT_IDENTITY;
   o.vec_ok = aligned16(y);
   if (y_map) { o.omap = *y_map; if (!omap_vec(*y_map)) o.vec_ok = 0; }
+#ifdef SNB_TRACE
+  s.trace = reinterpret_cast<unsigned long long*>(h->workspace + (h->workspace_floats - 64));
+#endif
   const int tkn = Tk <= 32 ? 32 : Tk <= 64 ? 64 : 128, en = E <= 32 ? 32 : E <= 64 ? 64 : 128;
   char name[64];
   snprintf(name, sizeof(name), "attention_fwd_3xtf32_%dx%d", tkn, en);

@@ -180,10 +180,22 @@ class GradientAllReduce:
         bufs = (ctypes.c_void_p * 2)(stack.dW[i].Pointer, stack.db[i].Pointer)
         counts = (ctypes.c_longlong * 2)(stack.dW[i].Count, stack.db[i].Count)
         check(h, lib.snb200_allreduce_sum_group(h, 2, bufs, counts))
-        # the next product of the compute handle leaves room for the collective (see COLLECTIVE_CTAS)
-        if self.COLLECTIVE_CTAS > 0:
+        # the next product of the compute handle leaves room for the collective (see COLLECTIVE_CTAS) -- where that
+        # pays: the product gives up COLLECTIVE_CTAS / 148 of its SMs for its whole duration, the collective needs
+        # them for its own, so the reservation is made only when the collective is not short against the product
+        if self.COLLECTIVE_CTAS > 0 and self._worth_reserving(stack, i):
             stack.w.set_tuning(_capi.TUNE_SM_RESERVE, self.COLLECTIVE_CTAS)
             stack.reserve_pending = True
+
+    def _worth_reserving(self, stack, i):
+        """Rough durations: the all-reduce of layer ``i`` at ~350 GB/s of bus bandwidth against the product queued
+        next (this layer's dx, or the next dW) at ~240 TFLOP/s.  Reserve when the collective takes at least as long
+        as the slice of the product it would otherwise delay."""
+        n = self.world
+        t_collective = 2.0 * (n - 1) / n * 4.0 * (stack.dW[i].Count + stack.db[i].Count) / 350e9
+        j = i if i > 0 else 0                                       # layer whose product follows
+        t_product = 2.0 * stack.batch * stack.dims[j] * stack.dims[j + 1] / 240e12
+        return t_collective >= t_product * self.COLLECTIVE_CTAS / 148.0 * 1.5
 
     def update_layer(self, stack, i, compute_stream, update):
         """Queues ``update(lib, handle, stack, i)`` -- the optimizer step of layer ``i`` -- on the side stream,
