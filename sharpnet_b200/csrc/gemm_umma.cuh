@@ -904,6 +904,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         if (!mbar_wait_warp(&full_bar[s], ph, abortp)) { ok = false; break; }
         if (tid == 0 && t == blockIdx.x && kb == kb_begin) SNB_STAMP(p, 4);
+        if (tid == 0 && t == blockIdx.x && kb - kb_begin < 8) SNB_STAMP(p, 32 + 2 * (kb - kb_begin));
         if constexpr (T::TS) {
           // the stage's TMEM columns are free: the producer refilled the stage only after the MMAs that read them retired
           split_stage_ts<T>(ring + s * T::STAGE_BYTES, tmem_base + T::TS_A_COL0 + s * T::TS_A_COLS, tid, p.a_mn);
@@ -914,6 +915,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_proxy_async_smem();   // make the generic-proxy stores visible to tcgen05.mma
         __syncwarp();
         if (lane == 0) mbar_arrive(&split_bar[s]);
+        if (tid == 0 && t == blockIdx.x && kb - kb_begin < 8) SNB_STAMP(p, 33 + 2 * (kb - kb_begin));
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }

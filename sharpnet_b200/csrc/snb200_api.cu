@@ -94,7 +94,7 @@ extern "C" int snb200_trace_read(snb200_handle_t h, unsigned long long* out32) {
   if (!h || !out32) return SNB200_STATUS_INVALID_VALUE;
   cudaSetDevice(h->device);
   cudaStreamSynchronize(h->stream);
-  return cudaMemcpy(out32, h->workspace + (h->workspace_floats - 64), 256, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 13;
+  return cudaMemcpy(out32, h->workspace + (h->workspace_floats - 128), 512, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 13;
 }
 #endif
 
@@ -349,7 +349,7 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
   p.A = g.A; p.B = g.B; p.lda = g.lda; p.ldb = g.ldb;
   p.strideA = g.batch > 1 ? g.strideA : 0; p.strideB = g.batch > 1 ? g.strideB : 0;
 #ifdef SNB_TRACE
-  p.trace = reinterpret_cast<unsigned long long*>(h->workspace + (h->workspace_floats - 64));   // last 256 bytes of the workspace
+  p.trace = reinterpret_cast<unsigned long long*>(h->workspace + (h->workspace_floats - 128));   // last 512 bytes of the workspace
 #endif
   p.whole_tiles = 0;       // set by the launcher: it knows the tile grid of its kernel
   p.partial_tiled = 0;
@@ -1329,7 +1329,7 @@ static int try_fused_attention_fwd(snb200_handle_t h, int batch, int Tq, int Tk,
   o.vec_ok = aligned16(y);
   if (y_map) { o.omap = *y_map; if (!omap_vec(*y_map)) o.vec_ok = 0; }
 #ifdef SNB_TRACE
-  s.trace = reinterpret_cast<unsigned long long*>(h->workspace + (h->workspace_floats - 64));
+  s.trace = reinterpret_cast<unsigned long long*>(h->workspace + (h->workspace_floats - 128));
 #endif
   const int tkn = Tk <= 32 ? 32 : Tk <= 64 ? 64 : 128, en = E <= 32 ? 32 : E <= 64 ? 64 : 128;
   char name[64];
