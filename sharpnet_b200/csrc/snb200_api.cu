@@ -34,6 +34,7 @@ struct snb200_context {
   char last_kernel[64];
   char last_error[256];
   void* nccl_comm;
+  int realigning;              // inside the product of realigned operand copies (no second realignment)
   int time_gemms;              // snb200_gemm_timing_begin .. _end: an event pair around every GEMM
   cudaEvent_t* gemm_events;
   int gemm_events_used;        // events recorded so far (two per GEMM)
@@ -753,6 +754,61 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
     if (macs < 64.0 * 64 * 64 || (g.M < 16 && !swappable) || g.N < 8) use_umma = false;
   }
   const bool split = h->math_mode == SNB200_MATH_3XTF32 || h->math_mode == SNB200_MATH_TF32_BF16X2;
+  // Operands TMA cannot load (a base that is only float-aligned, a width that is not a multiple of 4 floats): when
+  // the product is large against its operands and they fit the front half of the workspace, they are first copied
+  // into aligned, padded rows there (one bandwidth-bound pass, O(n^2) bytes before O(n^3) flops) and the product
+  // then runs on the TMA kernels like any other, with the rest of the workspace for its partial sums.
+  if (!use_umma && h->math_mode != SNB200_MATH_FP32_SIMT && force != 2 && !tma_eligible(g) && g.K >= 1 &&
+      h->tune[TUNE_NO_SWLOAD] == 0 && !h->realigning &&
+      g.M >= 64 && g.N >= 16 && static_cast<double>(g.M) * g.N * g.K * g.batch >= 128.0 * 128 * 128) {
+    const bool fixA = !aligned16(g.A) || (g.lda & 3) || (g.batch > 1 && (g.strideA & 3));
+    const bool fixB = !aligned16(g.B) || (g.ldb & 3) || (g.batch > 1 && (g.strideB & 3));
+    const long long a_rows = g.transA ? g.K : g.M, b_rows = g.transB ? g.N : g.K;
+    const int a_pitch = (g.lda + 3) & ~3, b_pitch = (g.ldb + 3) & ~3;
+    const long long a_mat = (a_rows * a_pitch + 63) / 64 * 64, b_mat = (b_rows * b_pitch + 63) / 64 * 64;   // 256-byte granules
+    const long long need = (fixA ? a_mat * g.batch : 0) + (fixB ? b_mat * g.batch : 0);
+    // the copies move (reads + writes) 8 bytes per operand float; worth it when the product does far more work
+    const double flops_per_copied_float = 2.0 * g.M * g.N * g.K * g.batch / static_cast<double>(need > 0 ? need : 1);
+    // one copy launch per matrix: worth it for a few large matrices, not for a batch of many small ones
+    if (need > 0 && need <= static_cast<long long>(h->workspace_floats / 2) && flops_per_copied_float >= 256.0 && g.batch <= 16) {
+      GemmProblem t = g;
+      float* ws = h->workspace;
+      auto copy = [&](const float* src, float* dst, long long rows, int cols, int pitch) {
+        const long long quads = rows * (pitch >> 2);
+        long long blocks = (quads + 255) / 256;
+        if (blocks > 16LL * h->sm_count) blocks = 16LL * h->sm_count;
+        launch_pdl(h, realign_rows_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), src, dst, rows, cols, pitch);
+        h->launches += 1;
+      };
+      if (fixA) {
+        for (int b = 0; b < g.batch; ++b) copy(g.A + b * g.strideA, ws + b * a_mat, a_rows, g.lda, a_pitch);
+        t.A = ws; t.lda = a_pitch; t.strideA = a_mat;
+        ws += a_mat * g.batch;
+      }
+      if (fixB) {
+        for (int b = 0; b < g.batch; ++b) copy(g.B + b * g.strideB, ws + b * b_mat, b_rows, g.ldb, b_pitch);
+        t.B = ws; t.ldb = b_pitch; t.strideB = b_mat;
+        ws += b_mat * g.batch;
+      }
+      int st = check_launch(h, "realign_rows_kernel launch");
+      if (st) return st;
+      // the product sees the rest of the workspace
+      float* ws0 = h->workspace;
+      const size_t wf0 = h->workspace_floats;
+      h->workspace_floats -= static_cast<size_t>(ws - ws0);
+      h->workspace = ws;
+      h->realigning = 1;
+      st = run_gemm_untimed(h, t);
+      h->realigning = 0;
+      h->workspace = ws0;
+      h->workspace_floats = wf0;
+      if (!st) {
+        const size_t len = strlen(h->last_kernel);
+        snprintf(h->last_kernel + len, sizeof(h->last_kernel) - len, "_realigned");
+      }
+      return st;
+    }
+  }
   // unaligned operands of a problem large enough for 128-row tiles: tensor cores fed by loader warps
   if (!use_umma && h->math_mode != SNB200_MATH_FP32_SIMT && force != 2 && !tma_eligible(g) && g.K >= 1 &&
       g.row_op == ROW_NONE && h->tune[TUNE_NO_SWLOAD] == 0 &&

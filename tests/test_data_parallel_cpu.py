@@ -155,3 +155,16 @@ def test_sm_reservation_covers_exactly_one_product_after_each_reduction():
     # calls: dW1(+db1) | reduce -> reserve | dx1 -> release | dW0 | reduce -> reserve | end of the pass -> release
     assert stack.w.tuning == [(1, _capi.TUNE_SM_RESERVE, 16), (2, _capi.TUNE_SM_RESERVE, 0), (3, _capi.TUNE_SM_RESERVE, 16),
                               (3, _capi.TUNE_SM_RESERVE, 0)]
+
+
+def test_reservation_is_made_only_where_the_collective_is_long_against_the_product():
+    """At 8 GPUs the 67 MB reduction of a 4096 x 4096 layer takes about as long as a third of the product queued
+    behind it, so that product leaves SMs free; at 2 GPUs the same product is four times longer and keeps them."""
+    from sharpnet_b200.data_parallel import GradientAllReduce
+    for world, rows, expected in ((8, 8192, True), (2, 32768, False)):
+        stack = _fake_stack((4096, 4096, 4096, 1000), (1, 1, 5))
+        stack.batch = rows
+        r = object.__new__(GradientAllReduce)
+        r.world, r.COLLECTIVE_CTAS = world, 16
+        assert r._worth_reserving(stack, 1) is expected
+        assert r._worth_reserving(stack, 2) is expected   # the 16 MB reduction of the output layer scales the same way
