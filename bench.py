@@ -743,7 +743,7 @@ def run_ours(args):
     if world > 1:
         # the collective's CTA budget (see GradientAllReduce.COLLECTIVE_CTAS) must be in the environment before the
         # first NCCL communicator of the process reads it
-        ctas = int(os.environ.get("SNB200_COLLECTIVE_CTAS", "16"))
+        ctas = int(os.environ.get("SNB200_COLLECTIVE_CTAS", "0"))
         if ctas > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(ctas))
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

@@ -27,12 +27,12 @@ static __global__ void bias_add_vec4_kernel(long long total4, int N4, const floa
 
 // Element-wise kernels: grid-stride over 16-byte vectors when every pointer is 16-byte aligned
 // (VEC = 4), scalar otherwise (VEC = 1); the last n % 4 elements of the vector form are done one by one.
-// Copy of a dense [batch, rows, cols] fp32 matrix (row pitch = cols) whose base is only 4-byte aligned, or whose
-// width is not a multiple of 4 floats, into a 16-byte aligned buffer with a row pitch that is a multiple of 4
+// Copy of `cols` columns of a row-major fp32 matrix (row pitch src_pitch) whose base is only 4-byte aligned, or whose
+// pitch is not a multiple of 4 floats, into a 16-byte aligned buffer with a row pitch that is a multiple of 4
 // floats: what TMA needs.  One thread per four consecutive destination floats (one 16-byte store); the four source
 // floats are separate 4-byte loads, coalesced across the warp.  The padding columns are written as zeros.
 static __global__ void realign_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, long long rows_total,
-                                           int cols, int dst_pitch) {
+                                           int cols, int src_pitch, int dst_pitch) {
   pdl_prologue();
   const int quads = dst_pitch >> 2;
   const long long total = rows_total * quads;
@@ -40,7 +40,7 @@ static __global__ void realign_rows_kernel(const float* __restrict__ src, float*
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
     const long long row = i / quads;
     const int c = static_cast<int>(i - row * quads) << 2;
-    const float* s0 = src + row * cols + c;
+    const float* s0 = src + row * src_pitch + c;
     float4 v;
     v.x = c < cols ? __ldg(s0) : 0.0f;
     v.y = c + 1 < cols ? __ldg(s0 + 1) : 0.0f;

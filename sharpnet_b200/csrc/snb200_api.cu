@@ -765,40 +765,76 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
     const bool fixB = !aligned16(g.B) || (g.ldb & 3) || (g.batch > 1 && (g.strideB & 3));
     const long long a_rows = g.transA ? g.K : g.M, b_rows = g.transB ? g.N : g.K;
     const int a_pitch = (g.lda + 3) & ~3, b_pitch = (g.ldb + 3) & ~3;
-    const long long a_mat = (a_rows * a_pitch + 63) / 64 * 64, b_mat = (b_rows * b_pitch + 63) / 64 * 64;   // 256-byte granules
-    const long long need = (fixA ? a_mat * g.batch : 0) + (fixB ? b_mat * g.batch : 0);
-    // the copies move (reads + writes) 8 bytes per operand float; worth it when the product does far more work
-    const double flops_per_copied_float = 2.0 * g.M * g.N * g.K * g.batch / static_cast<double>(need > 0 ? need : 1);
+    auto granules = [](long long floats) { return (floats + 63) / 64 * 64; };   // 256-byte granules
+    const long long a_mat = granules(a_rows * a_pitch), b_mat = granules(b_rows * b_pitch);
+    const long long budget = static_cast<long long>(h->workspace_floats / 4 * 3);   // a quarter stays for partial sums
+    const long long need_b = fixB ? b_mat * g.batch : 0;
+    // A may go through in panels of rows of op(A) (one matrix, dense result only) when it does not fit beside B
+    const bool panels_ok = g.batch == 1 && !g.omap.on;
+    int m_panel = g.M;
+    if (fixA && need_b + a_mat * g.batch > budget && panels_ok) {
+      const long long per_row = g.transA ? granules(static_cast<long long>(g.K) * 256) / 256 : a_pitch;   // floats per row of op(A)
+      const long long rows_fit = (budget - need_b) / (per_row > 0 ? per_row : 1);
+      m_panel = static_cast<int>(rows_fit / 256 * 256);
+    }
+    const long long a_panel_rows = g.transA ? g.K : m_panel;
+    const int a_panel_pitch = g.transA ? ((m_panel + 3) & ~3) : a_pitch;
+    const long long need_a = fixA ? granules(a_panel_rows * a_panel_pitch) * g.batch : 0;
+    const long long need = need_a + need_b;
+    // the copies move 8 bytes per operand float; worth it when the product does far more work than that
+    const double copied = static_cast<double>((fixA ? a_mat : 0) + (fixB ? b_mat : 0)) * g.batch;
+    const double flops_per_copied_float = 2.0 * g.M * g.N * g.K * g.batch / (copied > 0 ? copied : 1.0);
     // one copy launch per matrix: worth it for a few large matrices, not for a batch of many small ones
-    if (need > 0 && need <= static_cast<long long>(h->workspace_floats / 2) && flops_per_copied_float >= 256.0 && g.batch <= 16) {
-      GemmProblem t = g;
+    if (need > 0 && m_panel >= 256 - (g.M < 256 ? 256 : 0) && m_panel > 0 && need <= budget &&
+        flops_per_copied_float >= 256.0 && g.batch <= 16) {
       float* ws = h->workspace;
-      auto copy = [&](const float* src, float* dst, long long rows, int cols, int pitch) {
+      auto copy = [&](const float* src, float* dst, long long rows, int cols, int src_pitch, int pitch) {
         const long long quads = rows * (pitch >> 2);
         long long blocks = (quads + 255) / 256;
         if (blocks > 16LL * h->sm_count) blocks = 16LL * h->sm_count;
-        launch_pdl(h, realign_rows_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), src, dst, rows, cols, pitch);
+        launch_pdl(h, realign_rows_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), src, dst, rows, cols, src_pitch, pitch);
         h->launches += 1;
       };
-      if (fixA) {
-        for (int b = 0; b < g.batch; ++b) copy(g.A + b * g.strideA, ws + b * a_mat, a_rows, g.lda, a_pitch);
-        t.A = ws; t.lda = a_pitch; t.strideA = a_mat;
-        ws += a_mat * g.batch;
-      }
+      GemmProblem t = g;
+      float* b_copy = nullptr;
       if (fixB) {
-        for (int b = 0; b < g.batch; ++b) copy(g.B + b * g.strideB, ws + b * b_mat, b_rows, g.ldb, b_pitch);
-        t.B = ws; t.ldb = b_pitch; t.strideB = b_mat;
-        ws += b_mat * g.batch;
+        b_copy = ws;
+        for (int b = 0; b < g.batch; ++b) copy(g.B + b * g.strideB, ws + b * b_mat, b_rows, g.ldb, g.ldb, b_pitch);
+        t.B = b_copy; t.ldb = b_pitch; t.strideB = b_mat;
+        ws += need_b;
       }
-      int st = check_launch(h, "realign_rows_kernel launch");
-      if (st) return st;
-      // the product sees the rest of the workspace
+      float* a_copy = ws;
+      if (fixA) ws += need_a;
+      // the products see the rest of the workspace
       float* ws0 = h->workspace;
       const size_t wf0 = h->workspace_floats;
       h->workspace_floats -= static_cast<size_t>(ws - ws0);
       h->workspace = ws;
       h->realigning = 1;
-      st = run_gemm_untimed(h, t);
+      int st = 0;
+      for (int m0 = 0; m0 < g.M && !st; m0 += m_panel) {
+        const int mp = g.M - m0 < m_panel ? g.M - m0 : m_panel;
+        if (fixA) {
+          if (!g.transA) {          // rows m0 .. m0 + mp of A
+            const long long mat = granules(static_cast<long long>(mp) * a_pitch);
+            for (int b = 0; b < g.batch; ++b)
+              copy(g.A + b * g.strideA + static_cast<long long>(m0) * g.lda, a_copy + b * mat, mp, g.lda, g.lda, a_pitch);
+            t.A = a_copy; t.lda = a_pitch; t.strideA = mat;
+          } else {                  // columns m0 .. m0 + mp of the stored [K x M] matrix
+            const int pitch = (mp + 3) & ~3;
+            const long long mat = granules(static_cast<long long>(g.K) * pitch);
+            for (int b = 0; b < g.batch; ++b) copy(g.A + b * g.strideA + m0, a_copy + b * mat, g.K, mp, g.lda, pitch);
+            t.A = a_copy; t.lda = pitch; t.strideA = mat;
+          }
+        } else {
+          t.A = g.transA ? g.A + m0 : g.A + static_cast<long long>(m0) * g.lda;   // an aligned A walks in place
+        }
+        t.M = mp;
+        t.C = g.C + static_cast<long long>(m0) * g.ldc;
+        t.Z = g.Z ? g.Z + static_cast<long long>(m0) * g.ldc : nullptr;
+        st = check_launch(h, "realign_rows_kernel launch");
+        if (!st) st = run_gemm_untimed(h, t);
+      }
       h->realigning = 0;
       h->workspace = ws0;
       h->workspace_floats = wf0;

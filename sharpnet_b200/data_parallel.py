@@ -141,10 +141,13 @@ class GradientAllReduce:
     One process per GPU: rank 0 creates the NCCL id and ``broadcast_bytes`` (any callable that
     ships 128 bytes from rank 0 to everyone, e.g. built on torch.distributed) distributes it."""
 
-    # CTAs the collective may use, and therefore the SMs the product queued right behind a reduction leaves free
-    # for it: a persistent GEMM grid counts on every SM it was launched for, so a collective that has to squeeze
-    # in displaces some of its CTAs for as long as it runs and the GEMM ends that much later -- the overlap is lost.
-    COLLECTIVE_CTAS = 16
+    # Optional: CTAs the collective may use (NCCL_MAX_CTAS), and the SMs the product queued right behind a reduction
+    # leaves free for it.  A persistent GEMM grid counts on every SM it was launched for, so a collective that has
+    # to squeeze in displaces some of its CTAs for as long as it runs and the GEMM ends that much later.  Off by
+    # default (0): measured at 2 and 4 GPUs, capping NCCL at 16 CTAs lengthened the exposed tail of the last
+    # reduction by more than the reservation saved (13.82 against 13.67 ms per step at 4 GPUs).
+    # SNB200_COLLECTIVE_CTAS=<n> turns it on.
+    COLLECTIVE_CTAS = 0
 
     def __init__(self, device_id, world_size, rank, broadcast_bytes):
         import ctypes
