@@ -129,7 +129,9 @@ int snb200_gemm_timing_end(snb200_handle_t handle, double* total_ms, int* gemm_c
  *         loader warps;
  * key 12: n keeps n SMs out of the persistent tensor-core grids launched from now on (0 = use all): a host that
  *         has just queued a collective on another stream sets it for the next product, so that the collective's
- *         CTAs find free SMs instead of displacing CTAs of a grid that counts on every SM. */
+ *         CTAs find free SMs instead of displacing CTAs of a grid that counts on every SM;
+ * key 13: K cut inside thread-block clusters, summed through distributed shared memory, for problems whose tiles
+ *         leave SMs idle (0 automatic, 1 never, 2 or 4: always, in clusters of that size). */
 int snb200_set_tuning(snb200_handle_t handle, int key, int value);
 
 /* ---- Tensor.Dot -----------------------------------------------------------------------------

@@ -19,7 +19,7 @@ ACT_SOFTMAX = 1000   # snb200_dense_fwd only
 W_OUT_IN, W_IN_OUT = 0, 1
 LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
 (TUNE_FORCE_PATH, TUNE_FORCE_BN, TUNE_REWRITE_HI, TUNE_CHUNK_K, TUNE_PAIR, TUNE_SPLITK, TUNE_VARIANT, TUNE_PDL,
- TUNE_FORCE_SPLITS, TUNE_NO_TS, TUNE_NO_FUSED_ATTN, TUNE_NO_SWLOAD, TUNE_SM_RESERVE) = range(13)
+ TUNE_FORCE_SPLITS, TUNE_NO_TS, TUNE_NO_FUSED_ATTN, TUNE_NO_SWLOAD, TUNE_SM_RESERVE, TUNE_CLUSTER) = range(14)
 
 _c = ctypes
 _H = _c.c_void_p

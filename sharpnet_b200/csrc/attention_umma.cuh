@@ -179,7 +179,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (kb == 0) SNB_STAMP(p.s, i == 0 ? 5 : 24);
             tc_fence_after_sync();
             const uint32_t a_hi = smem_u32(ring + s * T::STAGE_BYTES);
-            const uint64_t da0 = kdesc + (a_hi >> 4), db0 = kdesc + ((a_hi + T::Q_BYTES) >> 4);
+            const uint64_t da0 = kdesc + ((a_hi & 0x3ffffu) >> 4), db0 = kdesc + (((a_hi + T::Q_BYTES) & 0x3ffffu) >> 4);
 #pragma unroll
             for (int ks = 0; ks < BK / kUmmaK; ++ks) {
               const uint64_t da_hi = da0 + ks * 2, db_hi = db0 + ks * 2;          // 32 bytes per K slice
@@ -205,7 +205,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int kb = 0; kb < kb2; ++kb) {
             if (!mbar_wait(&split_bar[s], ph, abortp)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint64_t db0 = vdesc + (smem_u32(ring + s * T::STAGE_BYTES) >> 4);
+            const uint64_t db0 = vdesc + ((smem_u32(ring + s * T::STAGE_BYTES) & 0x3ffffu) >> 4);
 #pragma unroll
             for (int ks = 0; ks < BK / kUmmaK; ++ks) {
               const uint64_t db_hi = db0 + ks * 64;                                // 1024 bytes per K slice

@@ -137,6 +137,12 @@ struct UmmaParams {
   int causal;
   const float* aux;
   OutMap omap;   // placement of C / Z when not dense (see OutMap)
+  // K cut inside a thread-block cluster (the CLUSTER instantiations): CTA r of a cluster of `cluster` computes K
+  // part r of the cluster's tile, and the parts are summed through distributed shared memory (no workspace, no
+  // second kernel).  store_t = 1: the kernel ran the transposed problem and stores tile element (row, col) at
+  // C[col * ldc + row], so C, Z and ldc are those of the caller's matrix and bias runs along the tile's rows.
+  int cluster;
+  int store_t;
   // operands as plain pointers, for the kernels whose loader warps replace TMA
   const float* A;
   const float* B;
@@ -164,7 +170,11 @@ constexpr bool kSlowIssue = false;
 // partial result it produces.
 __device__ __forceinline__ void unit_decode(const UmmaParams& p, int n_tiles, int u, int& tile, int& split,
                                             int& kb_begin, int& kb_end) {
-  if (u < p.whole_tiles) {
+  if (p.cluster > 1) {      // consecutive CTAs (one cluster) share a tile
+    tile = u / p.cluster; split = u - tile * p.cluster;
+    kb_begin = split * p.kb_per_split;
+    kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+  } else if (u < p.whole_tiles) {
     tile = u; split = -1; kb_begin = 0; kb_end = p.k_blocks;
   } else {
     const int tail = n_tiles - p.whole_tiles;
@@ -538,6 +548,51 @@ __device__ __forceinline__ void epilogue_store_unit(const UmmaParams& p, float a
   epilogue_store_rows<NC>(p, t, acc, stage, b, off, row_base, n0, lane);
 }
 
+// Store phase of a kernel that ran the transposed problem (p.store_t): the lane's row of the tile is a column of
+// the caller's matrix, so for every tile column the 32 lanes of a warp write 32 consecutive floats of one row of C.
+// The bias runs along the tile's rows.
+template <int NC>
+__device__ __forceinline__ void epilogue_store_transposed(const UmmaParams& p, float beta, const float (&acc)[NC], int b,
+                                                          int row_base, int n0, int lane) {
+  const int r = row_base + lane;
+  if (r >= p.M) return;
+  const float bv = p.bias ? __ldg(p.bias + r) : 0.0f;
+  const long long base = static_cast<long long>(b) * p.strideC + r;
+#pragma unroll       // fully: acc must stay in registers
+  for (int j = 0; j < NC; ++j) {
+    const int c = n0 + j;
+    if (c >= p.N) break;
+    const long long off = base + static_cast<long long>(c) * p.ldc;
+    float o = p.alpha * acc[j];
+    if (beta != 0.0f) o = fmaf(beta, p.C[off], o);
+    o += bv;
+    if (p.Z) p.Z[off] = o;
+    p.C[off] = act_forward_compact(p.act, o);
+  }
+}
+
+// beta * C of a transposed store, read while the products run (see epilogue_fold_c): acc starts at (beta / alpha) * C.
+template <int NC>
+__device__ __forceinline__ bool epilogue_fold_c_transposed(const UmmaParams& p, float (&acc)[NC], int b, int row_base,
+                                                           int n0, int lane) {
+  if (p.beta == 0.0f || p.alpha == 0.0f) return false;
+  const int r = row_base + lane;
+  const float f = p.beta / p.alpha;
+  const float* cb = p.C + static_cast<long long>(b) * p.strideC + r;
+  // all loads first, then their uses: issued one after the other they would cost a memory latency each, and the
+  // tensor core waits for the accumulator buffers this warp has not drained yet
+  const int rc = r < p.M ? r : 0;     // rows past the edge read a valid address; their values are never stored
+  float c[NC];
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int col = n0 + j < p.N ? n0 + j : p.N - 1;
+    c[j] = *(cb - r + rc + static_cast<long long>(col) * p.ldc);
+  }
+#pragma unroll
+  for (int j = 0; j < NC; ++j) acc[j] = f * c[j];
+  return true;
+}
+
 // 3xTF32 operand split of one landed stage: lo = tf32(x - hi) goes to the second plane, RAW_BYTES
 // after the raw tile, at the same (swizzled) offset.
 template <int RAW_BYTES, int NTHREADS>
@@ -661,7 +716,7 @@ __device__ __forceinline__ void sw_issue_tile(uint8_t* dst, const float* src, lo
 // never waits for them.
 // ROWOP instantiates the epilogue with the row operations of attention (epilogue_row_op); the plain
 // instantiation carries none of their code or registers.
-template <class T, bool ROWOP = false>
+template <class T, bool ROWOP = false, int CLUSTER = 1>
 __global__ void __launch_bounds__(T::THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const UmmaParams p) {
@@ -675,6 +730,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
   __shared__ float row_xch[ROWOP ? 2 * 128 : 1];   // row maximum / sum exchange of the row operations
+  __shared__ uint64_t xchg_bar;            // CLUSTER: the other CTAs' partial sums of the rows this CTA stores are published
+  static_assert(CLUSTER == 1 || CLUSTER == 2 || CLUSTER == 4, "clusters of 2 or 4 CTAs");
+  static_assert(CLUSTER == 1 || (!ROWOP && !T::TS && !T::SWLOAD), "the cluster form is the plain product");
+  static_assert(4 * T::EPI_GROUPS * 32 * T::EPI_COLS * 4 <= T::RING_BYTES, "partial sums are published in the operand ring");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -691,6 +750,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&acc_full_bar[b], 1);
       mbar_init(&acc_empty_bar[b], T::EPI_THREADS / 32);   // one arrival per epilogue warp
     }
+    // every other CTA's warps of the row quarters this CTA owns arrive once
+    mbar_init(&xchg_bar, CLUSTER > 1 ? (CLUSTER - 1) * (4 / CLUSTER) * T::EPI_GROUPS : 1);
     abort_flag = 0;
     fence_mbar_init();
     if (!T::SWLOAD) {
@@ -703,7 +764,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_relinquish();
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if (CLUSTER > 1) cluster_sync_all();   // the barriers of every CTA of the cluster exist before anyone signals them
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_holder;
   volatile int* abortp = &abort_flag;
@@ -794,7 +856,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               // Descriptors differ from slice to slice and from plane to plane only in their start-address field (bits
               // 0-13, in 16-byte units), so they are formed by additions to one descriptor per operand and K block:
               // the issuing lane spends a few instructions per tcgen05.mma instead of rebuilding every descriptor.
-              const uint64_t da0 = desc_a0 + (a_hi >> 4), db0 = desc_b0 + (b_hi >> 4);
+              // (the address field holds bits 4-17 of the CTA-relative address: in a cluster launch shared-memory
+              // addresses carry the CTA's rank in higher bits, which must not spill into the next field)
+              const uint64_t da0 = desc_a0 + ((a_hi & 0x3ffffu) >> 4), db0 = desc_b0 + ((b_hi & 0x3ffffu) >> 4);
 #pragma unroll
               for (int ks = 0; ks < BK / kUmmaK; ++ks) {
                 const uint64_t da_hi = da0 + ks * a_step16, db_hi = db0 + ks * b_step16;
@@ -856,7 +920,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       float acc[NC];
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] = 0.0f;
-      const bool c_folded = epilogue_fold_c<NC>(p, acc, stage, b, split, tm * BM + q * 32, tn * BN + col_base, lane);
+      // CLUSTER: CTA r of the cluster stores the row quarters q with q * CLUSTER / 4 == r, summed over all K parts
+      const int owner = CLUSTER > 1 ? q * CLUSTER / 4 : 0;
+      const bool mine = CLUSTER == 1 || owner == static_cast<int>(cluster_ctarank());
+      const bool c_folded =
+          !mine ? false
+          : (CLUSTER > 1 && p.store_t)
+              ? epilogue_fold_c_transposed<NC>(p, acc, b, tm * BM + q * 32, tn * BN + col_base, lane)
+              : epilogue_fold_c<NC>(p, acc, stage, b, split, tm * BM + q * 32, tn * BN + col_base, lane);
       for (int c = 0; c < n_chunks && ok; ++c, ++chunk_id) {
         const int buf = chunk_id & 1;
         if (!mbar_wait_warp(&acc_full_bar[buf], (acc_ph >> buf) & 1u, abortp)) { ok = false; break; }
@@ -879,6 +950,35 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (ROWOP && T::EPI_GROUPS == 2) ok = row_pair_all(row_xch, q, (warp - 4) >> 2, lane, ok);
       if (!ok) break;
+      if constexpr (CLUSTER > 1) {
+        // The operand ring is free (the last products have retired and this CTA loads nothing more): each warp
+        // owns 32 x NC floats of it, laid out [column quad][lane] so that neither side has bank conflicts.
+        float4* slab = reinterpret_cast<float4*>(ring) + (warp - 4) * (NC / 4) * 32;
+        if (!mine) {
+#pragma unroll
+          for (int j4 = 0; j4 < NC / 4; ++j4)
+            slab[j4 * 32 + lane] = make_float4(acc[4 * j4], acc[4 * j4 + 1], acc[4 * j4 + 2], acc[4 * j4 + 3]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive_release_cluster(map_to_cta(smem_u32(&xchg_bar), owner));
+          continue;   // the owner stores these rows
+        }
+        if (!mbar_wait_acquire_cluster_warp(&xchg_bar, 0, abortp)) { ok = false; break; }
+        const uint32_t rank = cluster_ctarank();
+#pragma unroll
+        for (uint32_t r = 0; r < CLUSTER; ++r) {       // fixed order: the sum does not depend on timing
+          if (r == rank) continue;
+          const uint32_t peer = map_to_cta(smem_u32(slab), r) + lane * 16;
+#pragma unroll
+          for (int j4 = 0; j4 < NC / 4; ++j4) {
+            const float4 v = ld_shared_cluster_v4(peer + j4 * 512);
+            acc[4 * j4] += v.x; acc[4 * j4 + 1] += v.y; acc[4 * j4 + 2] += v.z; acc[4 * j4 + 3] += v.w;
+          }
+        }
+        if (p.store_t) {
+          epilogue_store_transposed<NC>(p, c_folded ? 0.0f : p.beta, acc, b, tm * BM + q * 32, tn * BN + col_base, lane);
+          continue;
+        }
+      }
       float alpha = p.alpha;
       const float* bias = p.bias;
       if (ROWOP) {   // this instantiation is launched for row operations only
@@ -975,6 +1075,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, T::TMEM_COLS);
   }
+  // No CTA leaves while another may still read its shared memory.  Every thread of every CTA gets here: all waits
+  // above are bounded.
+  if (CLUSTER > 1) cluster_sync_all();
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.error_word, 1);
   if (threadIdx.x == 0) SNB_STAMP(p, 12);
 }

@@ -223,6 +223,55 @@ __device__ __forceinline__ bool mbar_wait_cluster_warp(uint64_t* bar, uint32_t p
   return ok;
 }
 
+// Split-K inside a cluster: a CTA publishes partial sums in its own shared memory, signals the owner CTA with a
+// release at cluster scope, and the owner reads them through the shared::cluster window after an acquiring wait.
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded like every other wait; every lane of the warp acquires for itself once lane 0 has seen the phase.
+__device__ __forceinline__ bool mbar_wait_acquire_cluster_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0 && !mbar_try_wait_acquire_cluster(bar, parity)) {
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (!mbar_try_wait_acquire_cluster(bar, parity)) {
+      if ((++spins & 0x3ff) == 0) {
+        if (*abort_flag) { ok = false; break; }
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > SNB_WAIT_TIMEOUT_NS) { *abort_flag = 1; ok = false; break; }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (ok) {
+    uint32_t tries = 0;
+    while (!mbar_try_wait_acquire_cluster(bar, parity)) {   // the phase has completed: this returns at once
+      if (++tries > (1u << 20)) { *abort_flag = 1; ok = false; break; }
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
 // tcgen05 forms for a CTA pair: TMEM is allocated by the same warp of both CTAs together, one thread
 // of the even CTA issues the MMA for both tensor cores, and its commit can signal both CTAs.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_holder, uint32_t ncols) {  // whole warp, both CTAs

@@ -19,7 +19,7 @@
 using namespace snb;
 
 // ------------------------------------------------------------------------------------ handle
-enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_FORCE_SPLITS = 8, TUNE_NO_TS = 9, TUNE_NO_FUSED_ATTN = 10, TUNE_NO_SWLOAD = 11, TUNE_SM_RESERVE = 12, TUNE_COUNT = 13 };
+enum { TUNE_FORCE_PATH = 0, TUNE_FORCE_BN = 1, TUNE_REWRITE_HI = 2, TUNE_CHUNK_K = 3, TUNE_PAIR = 4, TUNE_SPLITK = 5, TUNE_VARIANT = 6, TUNE_PDL = 7, TUNE_FORCE_SPLITS = 8, TUNE_NO_TS = 9, TUNE_NO_FUSED_ATTN = 10, TUNE_NO_SWLOAD = 11, TUNE_SM_RESERVE = 12, TUNE_CLUSTER = 13, TUNE_COUNT = 14 };
 
 struct snb200_context {
   int device;
@@ -178,6 +178,8 @@ extern "C" int snb200_get_math_mode(snb200_handle_t h, int* m) {
 extern "C" int snb200_set_tuning(snb200_handle_t h, int key, int value) {
   if (!h) return SNB200_STATUS_NOT_INITIALIZED;
   if (key < 0 || key >= TUNE_COUNT) return fail(h, SNB200_STATUS_INVALID_VALUE, "unknown tuning key %d", key);
+  if (key == TUNE_CLUSTER && value != 0 && value != 1 && value != 2 && value != 4)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "cluster size %d: 0 (automatic), 1 (never), 2 or 4", value);
   h->tune[key] = value;
   return 0;
 }
@@ -352,6 +354,8 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
 #ifdef SNB_TRACE
   p.trace = reinterpret_cast<unsigned long long*>(h->workspace + (h->workspace_floats - 128));   // last 512 bytes of the workspace
 #endif
+  p.cluster = 1;
+  p.store_t = 0;
   p.whole_tiles = 0;       // set by the launcher: it knows the tile grid of its kernel
   p.partial_tiled = 0;
   p.partial = nullptr;
@@ -369,6 +373,10 @@ struct SplitPlan {
   int tiled; int whole_tiles;
   int tail;         // out: tiles whose partial sums are in the workspace
   int tiles_m;      // out: tile rows of the grid the kernel walked
+  // cluster > 1: instead of all the above, every tile is cut into `cluster` K parts computed by the CTAs of one
+  // thread-block cluster, which sum them through distributed shared memory and store C themselves (store_t: as the
+  // transpose of what the kernel computed)
+  int cluster; int store_t;
 };
 
 template <class T>
@@ -395,7 +403,15 @@ static void apply_split_plan(snb200_handle_t h, const GemmProblem& g, int tile_r
   plan.tail = static_cast<int>(n_tiles) - p.whole_tiles;
 }
 
-template <class T, bool ROWOP = false>
+// K blocks per CTA when a tile's K range is shared by a cluster of `cs` CTAs (whole accumulation chunks of
+// `chunk` blocks each), or 0 when that would leave a CTA without work.
+static long long cluster_kblocks(long long k_blocks, int cs, long long chunk) {
+  long long kbps = (k_blocks + cs - 1) / cs;
+  if (chunk > 1 && chunk < k_blocks) kbps = (kbps + chunk - 1) / chunk * chunk;
+  return kbps * (cs - 1) < k_blocks ? kbps : 0;
+}
+
+template <class T, bool ROWOP = false, int CLUSTER = 1>
 static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& plan) {
   static bool configured[64] = {};
   CUtensorMap tmA, tmB;
@@ -403,12 +419,40 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pla
   int st = fill_umma_args<T>(h, g, T::BN, &tmA, &tmB, &p);
   if (st) return st;
   const long long n_tiles = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
-  apply_split_plan<T>(h, g, T::BM, n_tiles, p, plan);
+  if (CLUSTER > 1) {
+    // one work unit per CTA: CTA r of a cluster takes K part r of the cluster's tile
+    const int kbps = static_cast<int>(cluster_kblocks(p.k_blocks, CLUSTER, p.chunk_kblocks));
+    if (kbps == 0 || n_tiles * CLUSTER > 0x7fffffffLL)
+      return fail(h, SNB200_STATUS_INTERNAL_ERROR, "K = %d is too short for a cluster of %d", g.K, CLUSTER);
+    p.cluster = CLUSTER; p.splits = CLUSTER; p.kb_per_split = kbps; p.whole_tiles = 0;
+    p.store_t = plan.store_t;
+    plan.parts = 0; plan.tail = 0;
+  } else {
+    apply_split_plan<T>(h, g, T::BM, n_tiles, p, plan);
+  }
   plan.tiles_m = p.tiles_m;
   if (!configured[h->device]) {
-    SNB_CUDA(h, cudaFuncSetAttribute(umma_gemm_kernel<T, ROWOP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SNB_CUDA(h, cudaFuncSetAttribute(umma_gemm_kernel<T, ROWOP, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      T::SMEM_BYTES));
     configured[h->device] = true;
+  }
+  if (CLUSTER > 1) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(static_cast<unsigned>(n_tiles * CLUSTER));
+    cfg.blockDim = dim3(T::THREADS);
+    cfg.dynamicSmemBytes = T::SMEM_BYTES;
+    cfg.stream = h->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = h->tune[TUNE_PDL] == 1 ? 1 : 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T, ROWOP, CLUSTER>, tmA, tmB, p);
+    if (e != cudaSuccess) return cuda_fail(h, e, "umma_gemm_kernel (cluster) launch");
+    return check_launch(h, "umma_gemm_kernel (cluster) launch");
   }
   const long long units = p.whole_tiles + (n_tiles - p.whole_tiles) * p.splits;
   const int grid = static_cast<int>(units < usable_sms(h) ? units : usable_sms(h));
@@ -425,7 +469,7 @@ static int launch_umma_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pla
   cfg.stream = h->stream;
   cfg.attrs = attr;
   cfg.numAttrs = h->tune[TUNE_PDL] == 1 ? 0 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T, ROWOP>, tmA, tmB, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T, ROWOP, 1>, tmA, tmB, p);
   if (e != cudaSuccess) return cuda_fail(h, e, "umma_gemm_kernel launch");
   return check_launch(h, "umma_gemm_kernel launch");
 }
@@ -503,8 +547,64 @@ static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int
   }
 }
 
+// How many clusters of `cs` CTAs of the tensor-core kernel (one CTA per SM) the device runs at once: fewer than
+// SMs / cs, because a cluster lives inside one GPC.  0 when the query fails.
+template <int CS>
+static int cluster_capacity_t(snb200_handle_t h) {
+  static int cap[64] = {};
+  static bool known[64] = {};
+  if (!known[h->device]) {
+    using T = UmmaTile<128, 32, true>;
+    int n = 0;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(static_cast<unsigned>(h->sm_count / CS * CS));
+    cfg.blockDim = dim3(T::THREADS);
+    cfg.dynamicSmemBytes = T::SMEM_BYTES;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaFuncSetAttribute(umma_gemm_kernel<T, false, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES) !=
+            cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, umma_gemm_kernel<T, false, CS>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cap[h->device] = n;
+    known[h->device] = true;
+  }
+  return cap[h->device];
+}
+static int cluster_capacity(snb200_handle_t h, int cs) { return cs == 4 ? cluster_capacity_t<4>(h) : cluster_capacity_t<2>(h); }
+
+template <int CS>
+static int launch_umma_cluster(snb200_handle_t h, const GemmProblem& g, bool split, int bn, SplitPlan& plan) {
+  if (split) {
+    switch (bn) {
+      case 256: return launch_umma_t<UmmaTile<256, 32, true>, false, CS>(h, g, plan);
+      case 128: return launch_umma_t<UmmaTile<128, 32, true>, false, CS>(h, g, plan);
+      case 64: return launch_umma_t<UmmaTile<64, 32, true>, false, CS>(h, g, plan);
+      default: return launch_umma_t<UmmaTile<32, 32, true>, false, CS>(h, g, plan);
+    }
+  }
+  switch (bn) {
+    case 256: return launch_umma_t<UmmaTile<256, 32, false>, false, CS>(h, g, plan);
+    case 128: return launch_umma_t<UmmaTile<128, 32, false>, false, CS>(h, g, plan);
+    case 64: return launch_umma_t<UmmaTile<64, 32, false>, false, CS>(h, g, plan);
+    default: return launch_umma_t<UmmaTile<32, 32, false>, false, CS>(h, g, plan);
+  }
+}
+
 static int launch_umma(snb200_handle_t h, const GemmProblem& g, bool split, int bn, SplitPlan& plan) {
   char name[64];
+  if (plan.cluster > 1) {
+    snprintf(name, sizeof(name), "umma_%s_128x%d%s_clusterk%d", split ? "3xtf32" : "tf32", bn,
+             plan.store_t ? "_swapAB" : "", plan.cluster);
+    note_kernel(h, name, 1);
+    return plan.cluster == 4 ? launch_umma_cluster<4>(h, g, split, bn, plan) : launch_umma_cluster<2>(h, g, split, bn, plan);
+  }
   snprintf(name, sizeof(name), "umma_%s_128x%d%s", split ? "3xtf32" : "tf32", bn,
            plan.splits > 0 ? (plan.transposed ? "_swapAB_splitk" : "_splitk") : "");
   note_kernel(h, name, 1);
@@ -542,7 +642,7 @@ static int launch_umma_swload(snb200_handle_t h, const GemmProblem& g, bool spli
   char name[64];
   snprintf(name, sizeof(name), "umma_%s_128x%d_swload", split ? "3xtf32" : "tf32", bn);
   note_kernel(h, name, 1);
-  SplitPlan none = {0, 0, 0, 0, 0, 0, 0, 0};
+  SplitPlan none = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
   if (split) {
     if (bn == 128) return launch_umma_t<UmmaTile<128, 32, true, 0, false, true>>(h, g, none);
     if (bn == 64) return launch_umma_t<UmmaTile<64, 32, true, 0, false, true>>(h, g, none);
@@ -591,7 +691,7 @@ static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
 // instruction, so a narrow tile (which re-reads its 128 rows of A for few columns) costs almost as much per K
 // block as a tile twice as wide -- narrow tiles only pay when they fill a wave that wide tiles cannot -- and a
 // pair, where each SM holds half of B, runs a 256-wide tile 1.45x faster than one CTA does in 3xTF32 mode.
-struct TileChoice { int pair; int bn; int splits; int whole_tiles; };   // splits > 1: cut K of the tail tiles
+struct TileChoice { int pair; int bn; int splits; int whole_tiles; int cluster; };   // splits > 1: cut K of the tail tiles; cluster > 1: of every tile, inside a cluster
 struct TileCost { double kblock_us, fixed_us; };
 static TileCost tile_cost(bool split3x, int pair, int bn, const GemmProblem& g) {
   const int i = bn == 256 ? 0 : bn == 128 ? 1 : bn == 64 ? 2 : 3;
@@ -612,7 +712,7 @@ static TileCost tile_cost(bool split3x, int pair, int bn, const GemmProblem& g) 
   return pair ? paired_nt[i] : single_nt[i];
 }
 static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, bool split, bool hybrid) {
-  TileChoice best = {0, 256, 1, 0};
+  TileChoice best = {0, 256, 1, 0, 1};
   const bool allow_splitk = h->tune[TUNE_SPLITK] == 0;
   double best_cost = 1e300;
   const int pair_mode = h->tune[TUNE_PAIR];   // 0 automatic, 1 always, 2 never
@@ -635,6 +735,31 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
       const TileCost tc = tile_cost(split, pair, bn, g);
       // TF32 + bf16 cross terms: two instruction times per K slice instead of three, on the pair kernel's wide tiles
       const double c = tc.kblock_us * ((hybrid && pair && bn >= 128) ? 0.7 : 1.0), fixed = tc.fixed_us;
+      // One wave of tiles that leaves SMs idle: clusters of 2 or 4 CTAs share a tile's K range and sum their parts
+      // through distributed shared memory.  No workspace pass, and every CTA stores only its share of the rows.
+      const int cluster_mode = h->tune[TUNE_CLUSTER];   // 0 automatic, 1 never, 2 / 4 forced
+      if (!pair && cluster_mode != 1 && allow_splitk && g.row_op == ROW_NONE && forced_splits <= 1) {
+        static const double store_us[4] = {4.5, 2.0, 1.3, 0.9};   // the store phase of a whole tile (nothing overlaps it)
+        for (int cs = 2; cs <= 4; cs *= 2) {
+          if (cluster_mode > 1 && cs != cluster_mode) continue;
+          // left to itself: pairs of CTAs, all resident at once (measured: clusters of four lose to pairs on wider
+          // tiles or to the workspace plans wherever they fit, and a second wave of clusters loses to everything)
+          if (cluster_mode == 0 && (cs != 2 || kb / cs < 4 ||
+                                    tiles > cluster_capacity(const_cast<snb200_context*>(h), cs) || tiles * cs > slots))
+            continue;
+          const long long kbps = cluster_kblocks(kb, cs, split ? (h->tune[TUNE_CHUNK_K] + 31) / 32 : 0);
+          if (kbps == 0) continue;                                  // every CTA needs a part of K
+          const long long waves = (tiles * cs + slots - 1) / slots;
+          // the exchange: every CTA reads (cs - 1) / cs of a tile from the other CTAs' shared memory, about 20 KB / us
+          const double exchange_us = 0.5 + 128.0 * bn * 4.0 * (cs - 1) / cs / 20.0e3;
+          // + 1.5: where the estimates tie, the workspace plans of the CTA-pair kernel measured faster
+          double cost = waves * (fixed + c * kbps) + exchange_us - store_us[i] * (1.0 - 1.0 / cs) + 1.5;
+          if (cluster_mode > 1) cost -= 1.0e6;                      // forced: beats every other plan
+          if (cost < best_cost * 0.999) {
+            best_cost = cost; best.pair = 0; best.bn = bn; best.splits = 1; best.whole_tiles = 0; best.cluster = cs;
+          }
+        }
+      }
       for (int j = 0; j < 11; ++j) {
         const long long ks = ks_cand[j];
         if (forced_splits > 1) {            // tests: cut the tail tiles this many times whatever it costs
@@ -649,10 +774,10 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
         double cost = fixed + c * (static_cast<double>(whole / slots) * kb + static_cast<double>(tail_waves) * (ks > 1 ? kbps : kb));
         // a cut costs: the reduction kernel (launch + its traffic) and, per wave of cut units, one more
         // pipeline fill and a partial-tile store that nothing overlaps
-        if (ks > 1) cost += 7.0 + static_cast<double>(ks + 1) * tail_floats * 4.0 / 4.0e6 + 2.0 * tail_waves;
+        if (ks > 1) cost += 2.0 + static_cast<double>(ks + 1) * tail_floats * 4.0 / 4.0e6 + 2.0 * tail_waves;
         if (cost < best_cost * 0.999) {
           best_cost = cost; best.pair = pair; best.bn = bn; best.splits = static_cast<int>(ks);
-          best.whole_tiles = static_cast<int>(whole);
+          best.whole_tiles = static_cast<int>(whole); best.cluster = 1;
         }
       }
     }
@@ -855,7 +980,7 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
   const bool hybrid = h->math_mode == SNB200_MATH_TF32_BF16X2 && !g.transA && g.transB;
   if (g.row_op != ROW_NONE) {
     // whole rows in one tile of the single-CTA kernel, K never cut (the caller checked row_op_fits)
-    SplitPlan none = {0, 0, 0, 0, 0, 0, 0, 0};
+    SplitPlan none = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     const int bn = g.N <= 32 ? 32 : g.N <= 64 ? 64 : g.N <= 128 ? 128 : 256;
     char name[64];
     snprintf(name, sizeof(name), "umma_%s_128x%d_%s", split ? "3xtf32" : "tf32", bn,
@@ -893,8 +1018,19 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
     if (s > g.K / 256) s = g.K / 256;
     const size_t per_split = static_cast<size_t>(g.batch) * g.M * g.N;
     if (s * per_split > h->workspace_floats) s = static_cast<long long>(h->workspace_floats / per_split);
+    const int cluster_mode = h->tune[TUNE_CLUSTER];
+    int cs = cluster_mode > 1 ? cluster_mode : (s >= 4 ? 4 : s >= 2 ? 2 : 1);
+    const long long chunk = split ? (h->tune[TUNE_CHUNK_K] + 31) / 32 : 0;
+    while (cs > 1 && (g.K / cs < 128 || cluster_kblocks((g.K + 31) / 32, cs, chunk) == 0 ||
+                      (cluster_mode == 0 && tiles > cluster_capacity(h, cs)))) cs /= 2;
+    // worth it while the cluster keeps about as many CTAs busy as the workspace plan would (s K parts per tile)
+    if (cluster_mode != 1 && cs > 1 && !g.omap.on && (cluster_mode > 1 || 5 * cs >= 4 * s)) {
+      // K parts summed inside clusters; the owners store the transposed tile straight into C
+      SplitPlan plan = {0, 0, 0, 0, 0, 0, 0, 0, cs, 1};
+      return launch_umma(h, t, split, bn, plan);
+    }
     if (s >= 1) {
-      SplitPlan plan = {static_cast<int>(s), static_cast<int>((g.K + s - 1) / s), 1, 0, 0, 0, 0, 0};
+      SplitPlan plan = {static_cast<int>(s), static_cast<int>((g.K + s - 1) / s), 1, 0, 0, 0, 0, 0, 0, 0};
       plan.k_per_split = (plan.k_per_split + 127) / 128 * 128;
       const int st = launch_umma(h, t, split, bn, plan);
       if (st) return st;
@@ -903,8 +1039,10 @@ static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g) {
   }
   const TileChoice c = choose_tile(h, g, split, hybrid);
   // Tiles that would leave most SMs idle in the last wave are cut along K.
-  SplitPlan plan = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (c.splits > 1) {
+  SplitPlan plan = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (c.cluster > 1) {
+    plan.cluster = c.cluster;
+  } else if (c.splits > 1) {
     plan.splits = c.splits;
     plan.k_per_split = (g.K + c.splits - 1) / c.splits;
     plan.tiled = 1;

@@ -7,7 +7,7 @@ import pytest
 from oracle import sharpnet_oracle as orc
 from sharpnet_b200 import (ACT_IDENTITY, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH, MATH_3XTF32, MATH_TF32, W_IN_OUT,
                            W_OUT_IN)
-from sharpnet_b200._capi import TUNE_FORCE_PATH
+from sharpnet_b200._capi import TUNE_CLUSTER, TUNE_FORCE_PATH
 from sharpnet_b200._capi import LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE
 from sharpnet_b200.linear import (DenseBackwardPropagation, DenseForwardPropagation, FusedDenseBackward,
                                   FusedDenseBackwardFromLoss, FusedDenseForward)
@@ -128,11 +128,17 @@ def test_dense_fwd_bwd_tensor_core(wrapper, act, layout, mode, tol):
 
 @pytest.mark.parametrize("act", [ACT_RELU, ACT_SWISH])
 @pytest.mark.parametrize("layout", [W_IN_OUT, W_OUT_IN])
-def test_dense_small_batch_takes_the_split_k_plans(wrapper, act, layout):
+@pytest.mark.parametrize("clusters", [0, 1])
+def test_dense_small_batch_takes_the_split_k_plans(wrapper, act, layout, clusters):
     # inference-sized batches: forward runs with swapped operands, the gradients with K cut in pieces;
-    # bias, activation and the pre-activation output then come from the reduction kernel
-    _dense_case(wrapper, 32, 2048, 512, act, layout, 300 + act, TOL_3XTF32)
-    _dense_case(wrapper, 8, 1024, 260, act, layout, 320 + act, TOL_3XTF32, mult=0.125)
+    # bias, activation and the pre-activation output then come from the CTAs of a cluster that store the
+    # transposed tile, or (clusters switched off) from the reduction kernel
+    wrapper.set_tuning(TUNE_CLUSTER, clusters)
+    try:
+        _dense_case(wrapper, 32, 2048, 512, act, layout, 300 + act, TOL_3XTF32)
+        _dense_case(wrapper, 8, 1024, 260, act, layout, 320 + act, TOL_3XTF32, mult=0.125)
+    finally:
+        wrapper.set_tuning(TUNE_CLUSTER, 0)
 
 
 @pytest.mark.parametrize("act", [ACT_RELU, ACT_SWISH, ACT_TANH])

@@ -5,7 +5,7 @@ import pytest
 
 from oracle import sharpnet_oracle as orc
 from sharpnet_b200 import MATH_3XTF32, MATH_FP32_SIMT, MATH_TF32
-from sharpnet_b200._capi import TUNE_FORCE_BN, TUNE_FORCE_PATH, TUNE_PAIR, SharpNetB200Error
+from sharpnet_b200._capi import TUNE_CLUSTER, TUNE_FORCE_BN, TUNE_FORCE_PATH, TUNE_PAIR, SharpNetB200Error
 from sharpnet_b200.tensor import GPUTensor
 
 from gpu_util import TOL_3XTF32, TOL_TF32, run_dot
@@ -21,11 +21,13 @@ def _reset(wrapper):
     wrapper.set_tuning(TUNE_FORCE_PATH, 0)
     wrapper.set_tuning(TUNE_FORCE_BN, 0)
     wrapper.set_tuning(TUNE_PAIR, 0)
+    wrapper.set_tuning(TUNE_CLUSTER, 0)
     yield
     wrapper.set_math_mode(MATH_3XTF32)
     wrapper.set_tuning(TUNE_FORCE_PATH, 0)
     wrapper.set_tuning(TUNE_FORCE_BN, 0)
     wrapper.set_tuning(TUNE_PAIR, 0)
+    wrapper.set_tuning(TUNE_CLUSTER, 0)
 
 
 def _check(w, M, N, K, tA, tB, alpha, beta, seed, tol, lo=-1.0, hi=1.0, batch=None):
@@ -285,6 +287,7 @@ def test_few_tiles_split_k_and_swapped_operands(wrapper, mode, tol, tA, tB):
     # problems with fewer tiles than SMs: K is cut into partial sums (workspace + reduction kernel), and
     # with few rows the operands are swapped so that N fills the 128-row tile
     wrapper.set_math_mode(mode)
+    wrapper.set_tuning(TUNE_CLUSTER, 1)       # this test: the workspace plans (clusters have their own test below)
     seed = 700
     for (M, N, K) in ((256, 512, 4096), (132, 300, 2052), (512, 128, 8192)):
         seed += 1
@@ -297,6 +300,42 @@ def test_few_tiles_split_k_and_swapped_operands(wrapper, mode, tol, tA, tB):
             tma_ok = (not tA or M % 4 == 0)      # a transposed A is stored [K x M]: its pitch M must be a 16-byte multiple
             assert ("swapAB" in wrapper.last_kernel()) == tma_ok, wrapper.last_kernel()
     _check(wrapper, 8, 512, 1024, tA, tB, 1.0, 0.0, 777, tol, batch=6)       # batched, swapped
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
+@pytest.mark.parametrize("tA,tB", [(False, False), (False, True), (True, False), (True, True)])
+def test_k_cut_inside_clusters(wrapper, mode, tol, tA, tB):
+    # K parts computed by the CTAs of a thread-block cluster and summed through distributed shared memory: every
+    # tile width, clusters of 2 and 4, ragged edges, beta = 1 (read by the CTA that stores the rows), a batch, a
+    # grid of more clusters than the GPU holds at once, and the swapped-operand form that stores the transpose
+    wrapper.set_math_mode(mode)
+    seed = 900
+    for cs in (2, 4):
+        wrapper.set_tuning(TUNE_CLUSTER, cs)
+        for bn in (32, 64, 128, 256):
+            wrapper.set_tuning(TUNE_FORCE_BN, bn)
+            seed += 1
+            _check(wrapper, 260, 300, 2052, tA, tB, 0.5, 1.0, seed, tol)
+            assert wrapper.last_kernel() == "umma_%s_128x%d_clusterk%d" % (
+                "3xtf32" if mode == MATH_3XTF32 else "tf32", bn, cs), wrapper.last_kernel()
+        wrapper.set_tuning(TUNE_FORCE_BN, 128)
+        _check(wrapper, 1024, 1024, 1024, tA, tB, 1.0, 0.0, seed + 50, tol)
+        _check(wrapper, 132, 200, 1280, tA, tB, 1.0, 1.0, seed + 51, tol, batch=5)
+        _check(wrapper, 2048, 2304, 512, tA, tB, 1.0, 0.0, seed + 52, tol)      # 288 tiles: several waves of clusters
+        assert "clusterk%d" % cs in wrapper.last_kernel(), wrapper.last_kernel()
+        wrapper.set_tuning(TUNE_FORCE_BN, 0)
+        for (M, N, K) in ((32, 4096, 4096), (5, 1000, 2052), (64, 260, 2048)):
+            for beta in (0.0, 1.0):
+                seed += 1
+                _check(wrapper, M, N, K, tA, tB, 0.5, beta, seed, tol)
+                if not tA or M % 4 == 0:
+                    assert "swapAB_clusterk%d" % cs in wrapper.last_kernel(), wrapper.last_kernel()
+        _check(wrapper, 8, 512, 1024, tA, tB, 1.0, 1.0, seed + 60, tol, batch=6)
+    # left to itself the library takes clusters where one wave of tiles leaves SMs idle
+    wrapper.set_tuning(TUNE_CLUSTER, 0)
+    _check(wrapper, 1024, 1024, 1024, tA, tB, 1.0, 0.0, 990, tol)
+    _check(wrapper, 32, 4096, 4096, tA, tB, 1.0, 1.0, 991, tol)
+    assert "swapAB_clusterk4" in wrapper.last_kernel(), wrapper.last_kernel()
 
 
 @pytest.mark.parametrize("mode,tol", [(MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32)])
