@@ -748,6 +748,15 @@ def run_ours(args):
             os.environ.setdefault("NCCL_MAX_CTAS", str(ctas))
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    if world > 1 and os.environ.get("SNB200_NO_NUMA_BIND", "0") != "1":
+        # one process per GPU: keep each replica's staging buffers and host thread on its GPU's NUMA node (at N = 1
+        # the process keeps every core: the CPU baseline legs use them)
+        from sharpnet_b200.data_parallel import bind_host_to_device_node, device_pci_bus_id
+        try:
+            bound = bind_host_to_device_node(device_pci_bus_id(local))
+        except Exception:          # a torch without the PCI fields: stay unbound
+            bound = None
+        print(f"rank {rank}: host bound to {len(bound) if bound else 0} CPUs of the GPU's NUMA node", file=sys.stderr)
     peaks = _peaks()
     w = GPUWrapper.FromDeviceId(local)
     w.set_math_mode(MATH_3XTF32)

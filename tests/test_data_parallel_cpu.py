@@ -168,3 +168,26 @@ def test_reservation_is_made_only_where_the_collective_is_long_against_the_produ
         r.world, r.COLLECTIVE_CTAS = world, 16
         assert r._worth_reserving(stack, 1) is expected
         assert r._worth_reserving(stack, 2) is expected   # the 16 MB reduction of the output layer scales the same way
+
+
+def test_host_binds_to_the_numa_node_of_its_gpu(tmp_path):
+    # a fake sysfs: the GPU at 0000:1b:00.0 hangs off node 1 (CPUs 8-15,24-27); the process may use CPUs 0-11 and 24
+    from sharpnet_b200.data_parallel import bind_host_to_device_node, _parse_cpulist
+    dev = tmp_path / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("8-15,24-27\n")
+    assert _parse_cpulist("0-3,7,9-10") == {0, 1, 2, 3, 7, 9, 10}
+    calls = []
+    allowed = set(range(12)) | {24}
+    got = bind_host_to_device_node("0000:1B:00.0", str(tmp_path), calls.append, lambda: allowed)
+    assert got == {8, 9, 10, 11, 24} and calls == [got]
+    # unknown node, missing device, or no CPU in common: nothing is changed
+    (dev / "numa_node").write_text("-1\n")
+    assert bind_host_to_device_node("0000:1b:00.0", str(tmp_path), calls.append, lambda: allowed) is None
+    assert bind_host_to_device_node("0000:99:00.0", str(tmp_path), calls.append, lambda: allowed) is None
+    (dev / "numa_node").write_text("1\n")
+    assert bind_host_to_device_node("0000:1b:00.0", str(tmp_path), calls.append, lambda: {0, 1}) is None
+    assert len(calls) == 1
