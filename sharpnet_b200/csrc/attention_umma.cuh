@@ -19,8 +19,17 @@
 // unit u, and the loads of later units overlap everything.  No scores buffer, no second launch, and the
 // probabilities never pass through shared memory.
 //
+// The same kernel body, instantiated with GRAD, is the middle of the backward pass:
+//
+//   dScores = softmax'(scaling * dy V^T; weights),  dQ = dScores K
+//
+// product 1 takes dy and V in the places of Q and K, the epilogue warps apply the softmax Jacobian
+// y * (g - sum_j g_j y_j) with the forward pass's probabilities read from `weights` (coalesced, through the warp's
+// shared-memory tile) instead of the softmax, dScores is stored where the forward kernel stores the weights (the
+// dK product reads it) and handed to product 2 through tensor memory, and K takes the place of V.
+//
 // Reference: ScaledDotProductAttentionLayer.ScaledDotProductAttentionForwardPropagation
-// (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-91).
+// (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-91) and its BackwardPropagation (:93-132).
 #pragma once
 #include "gemm_umma.cuh"
 
@@ -72,10 +81,9 @@ struct AttnParams {
   int* error_word;
 };
 
-template <class T>
-__global__ void __launch_bounds__(T::THREADS, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+template <class T, bool GRAD>
+__device__ __forceinline__ void attn_core(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                                          const AttnParams& p) {
   constexpr int TKN = T::TKN, EN = T::EN, BK = T::BK, STAGES = T::STAGES, G = T::G, NC = T::NC;
   extern __shared__ uint8_t smem_dyn[];
   __shared__ uint64_t full_bar[STAGES], split_bar[STAGES], empty_bar[STAGES];
@@ -246,9 +254,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // unrolled over the whole row, this code is several thousand instructions that every warp runs once per unit,
       // and the warps then wait for instruction fetches more than for anything else (measured: 16 % of the
       // instruction-cache requests missed, "no instruction" the top stall reason).  TMEM reads are cheap.
+      const float alpha = p.s.alpha;
+      if constexpr (GRAD) {
+        // softmax Jacobian: dS = y * (g - sum_j g_j y_j), g = alpha * S, y = the forward pass's probabilities
+        // (0 in masked columns, so the mask needs no second application: Prod/GPU/GpuTensor.cs:445-490)
+        const float* yrow = p.s.aux + static_cast<long long>(b) * p.s.strideC + static_cast<long long>(row_base) * p.s.ldc;
+        const int rows_valid = p.s.M - row_base;
+        float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+        for (int g = 0; g < NC / 32; ++g) {
+          float v[32], y[32];
+          tmem_ld_32x32(s_col + g * 32, v);
+          const int c0 = col_base + g * 32;
+          epilogue_load_block(yrow + c0, p.s.ldc, rows_valid, p.s.N - c0, stage, lane, y);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) d4[j & 3] = fmaf(alpha * v[j], y[j], d4[j & 3]);
+        }
+        float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+        if (G == 2) {
+          const float other = row_pair_exchange(row_xch, q, grp, lane, dot);
+          dot = grp == 0 ? dot + other : other + dot;   // same order in both warps
+        }
+#pragma unroll 1
+        for (int g = 0; g < NC / 32; ++g) {
+          float v[32], y[32];
+          uint32_t lo[32];
+          tmem_ld_32x32(s_col + g * 32, v);
+          const int c0 = col_base + g * 32;
+          epilogue_load_block(yrow + c0, p.s.ldc, rows_valid, p.s.N - c0, stage, lane, y);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = y[j] * (alpha * v[j] - dot);
+            lo[j] = to_tf32_rna(v[j] - __uint_as_float(__float_as_uint(v[j]) & 0xffffe000u));
+          }
+          tmem_st_32x32(s_col + g * 32, reinterpret_cast<const uint32_t*>(v));
+          tmem_st_32x32(tmem_base + lane_base + T::COL_PLO + col_base + g * 32, lo);
+        }
+      } else {
       const int row = row_base + lane;
       const int limit = p.s.causal ? row : 0x7fffffff;          // columns > limit are masked
-      const float alpha = p.s.alpha;
       // pass 1: row maximum of mask(alpha * S)
       float mx = -3.402823466e38f;
 #pragma unroll 1
@@ -313,6 +359,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_st_32x32(s_col + g * 32, reinterpret_cast<const uint32_t*>(v));
         tmem_st_32x32(tmem_base + lane_base + T::COL_PLO + col_base + g * 32, lo);
       }
+      }   // !GRAD
       if (warp == 4 && lane == 0 && it == 0) SNB_STAMP(p.s, 15);
       tmem_st_wait();
       tc_fence_before_sync();
@@ -385,6 +432,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.error_word, 1);
   if (threadIdx.x == 0) SNB_STAMP(p.s, 12);
+}
+
+template <class T>
+__global__ void __launch_bounds__(T::THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  attn_core<T, false>(tmQ, tmK, tmV, p);
+}
+
+// dScores and dQ of the backward pass: tmQ describes dy, tmK describes V, tmV describes K (see the header comment).
+template <class T>
+__global__ void __launch_bounds__(T::THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  attn_core<T, true>(tmQ, tmK, tmV, p);
 }
 
 }  // namespace snb

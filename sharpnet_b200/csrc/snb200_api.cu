@@ -1502,9 +1502,10 @@ static bool row_op_fits(const snb200_context* h, const GemmProblem& g, int max_c
 // The attention core as one kernel (attn_fwd_kernel): score rows of up to 128 columns, embeddings of up to 128, the
 // 3xTF32 mode, operands TMA can load.  Returns -1 when the case does not qualify (the caller then runs the products
 // one by one).
-template <class T>
+template <class T, bool GRAD = false>
 static int launch_attn_fwd_t(snb200_handle_t h, const AttnParams& ap, const float* Q, const float* K, const float* V) {
   static bool configured[64] = {};
+  auto kernel = GRAD ? attn_bwd_kernel<T> : attn_fwd_kernel<T>;
   CUtensorMap tmQ, tmK, tmV;
   const uint64_t B = ap.batch, Tq = ap.q_steps, Tk = ap.v_steps, E = ap.embedding_dim;
   bool ok = encode_3d(&tmQ, Q, E, Tq, B, E, Tq * E, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B) &&
@@ -1512,7 +1513,7 @@ static int launch_attn_fwd_t(snb200_handle_t h, const AttnParams& ap, const floa
             encode_3d(&tmV, V, E, Tk, B, E, Tk * E, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (!ok) return fail(h, SNB200_STATUS_INTERNAL_ERROR, "cuTensorMapEncodeTiled rejected an attention operand");
   if (!configured[h->device]) {
-    SNB_CUDA(h, cudaFuncSetAttribute(attn_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    SNB_CUDA(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     configured[h->device] = true;
   }
   const long long units = static_cast<long long>(ap.batch) * ap.tiles_q;
@@ -1527,9 +1528,9 @@ static int launch_attn_fwd_t(snb200_handle_t h, const AttnParams& ap, const floa
   cfg.stream = h->stream;
   cfg.attrs = attr;
   cfg.numAttrs = h->tune[TUNE_PDL] == 1 ? 0 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_fwd_kernel<T>, tmQ, tmK, tmV, ap);
-  if (e != cudaSuccess) return cuda_fail(h, e, "attn_fwd_kernel launch");
-  return check_launch(h, "attn_fwd_kernel launch");
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmQ, tmK, tmV, ap);
+  if (e != cudaSuccess) return cuda_fail(h, e, "attention kernel launch");
+  return check_launch(h, "attention kernel launch");
 }
 
 static int try_fused_attention_fwd(snb200_handle_t h, int batch, int Tq, int Tk, int E, float scaling, int is_causal,
@@ -1566,6 +1567,50 @@ static int try_fused_attention_fwd(snb200_handle_t h, int batch, int Tq, int Tk,
   snprintf(name, sizeof(name), "attention_fwd_3xtf32_%dx%d", tkn, en);
   note_kernel(h, name, 1);
 #define SNB_ATTN_CASE(TK, EE) if (tkn == TK && en == EE) return launch_attn_fwd_t<AttnTile<TK, EE>>(h, ap, Q, K, V)
+  SNB_ATTN_CASE(32, 32); SNB_ATTN_CASE(32, 64); SNB_ATTN_CASE(32, 128);
+  SNB_ATTN_CASE(64, 32); SNB_ATTN_CASE(64, 64); SNB_ATTN_CASE(64, 128);
+  SNB_ATTN_CASE(128, 32); SNB_ATTN_CASE(128, 64); SNB_ATTN_CASE(128, 128);
+#undef SNB_ATTN_CASE
+  return -1;
+}
+
+// The middle of the backward pass in one launch of the same kernel body: dScores = softmax'(scaling dy V^T; weights)
+// stored to `scores_grad` (the dK product reads it) and dQ = dScores K.  Same conditions as the forward kernel, plus
+// probability rows that are 16-byte aligned.  Returns -1 when the case does not qualify.
+static int try_fused_attention_bwd(snb200_handle_t h, int batch, int Tq, int Tk, int E, float scaling, const float* dy,
+                                   const float* V, const float* K, const float* weights, float* scores_grad, float* dQ,
+                                   const OutMap* dq_map) {
+  if (h->tune[TUNE_NO_FUSED_ATTN] == 1 || h->tune[TUNE_FORCE_PATH] == 2) return -1;
+  if (h->math_mode != SNB200_MATH_3XTF32 && h->math_mode != SNB200_MATH_TF32_BF16X2) return -1;
+  if (Tk > 128 || E > 128 || Tk < 8 || Tq < 16 || (E & 3) || (Tk & 3)) return -1;
+  if (!aligned16(dy) || !aligned16(K) || !aligned16(V) || !aligned16(weights) || !aligned16(scores_grad)) return -1;
+  if (static_cast<double>(batch) * Tq * Tk * E < 64.0 * 64 * 64) return -1;
+  if (static_cast<long long>(batch) * ((Tq + 127) / 128) > 0x7fffffffLL) return -1;
+  AttnParams ap;
+  memset(&ap, 0, sizeof(ap));
+  ap.batch = batch; ap.q_steps = Tq; ap.v_steps = Tk; ap.embedding_dim = E;
+  ap.tiles_q = (Tq + 127) / 128;
+  ap.error_word = h->error_word;
+  UmmaParams& s = ap.s;
+  s.M = Tq; s.N = Tk; s.K = E; s.batch = batch;
+  s.ldc = Tk; s.strideC = static_cast<long long>(Tq) * Tk;
+  s.C = scores_grad; s.aux = weights; s.alpha = scaling; s.beta = 0.0f; s.act = ACT_IDENTITY;
+  s.row_op = ROW_SOFTMAX_GRAD;
+  s.vec_ok = 1;
+  UmmaParams& o = ap.o;
+  o.M = Tq; o.N = E; o.K = Tk; o.batch = batch;
+  o.ldc = E; o.strideC = static_cast<long long>(Tq) * E;
+  o.C = dQ; o.alpha = 1.0f; o.beta = 0.0f; o.act = ACT_IDENTITY;
+  o.vec_ok = aligned16(dQ);
+  if (dq_map) { o.omap = *dq_map; if (!omap_vec(*dq_map)) o.vec_ok = 0; }
+#ifdef SNB_TRACE
+  s.trace = reinterpret_cast<unsigned long long*>(h->workspace + (h->workspace_floats - 128));
+#endif
+  const int tkn = Tk <= 32 ? 32 : Tk <= 64 ? 64 : 128, en = E <= 32 ? 32 : E <= 64 ? 64 : 128;
+  char name[64];
+  snprintf(name, sizeof(name), "attention_bwd_3xtf32_%dx%d", tkn, en);
+  note_kernel(h, name, 1);
+#define SNB_ATTN_CASE(TK, EE) if (tkn == TK && en == EE) return launch_attn_fwd_t<AttnTile<TK, EE>, true>(h, ap, dy, V, K)
   SNB_ATTN_CASE(32, 32); SNB_ATTN_CASE(32, 64); SNB_ATTN_CASE(32, 128);
   SNB_ATTN_CASE(64, 32); SNB_ATTN_CASE(64, 64); SNB_ATTN_CASE(64, 128);
   SNB_ATTN_CASE(128, 32); SNB_ATTN_CASE(128, 64); SNB_ATTN_CASE(128, 128);
@@ -1654,6 +1699,15 @@ static int sdpa_bwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps,
   if (dkv_map) g.omap = *dkv_map;
   st = run_gemm(h, g);
   if (st) return st;
+  // dScores and dQ in one kernel where a score row fits one tile                       (:119-123)
+  st = try_fused_attention_bwd(h, batch, Tq, Tk, E, scaling, dy, V, K, weights, scores_grad_scratch, dQ, dq_map);
+  if (st > 0) return st;
+  if (st == 0) {
+    // dK = dScores^T * Q                                                               (:124)
+    bmm_problem(&g, batch, Tk, E, Tq, 1, 0, scores_grad_scratch, Tk, sW, Q, E, sQ, dK, 1.0f);
+    if (dkv_map) g.omap = *dkv_map;
+    return run_gemm(h, g);
+  }
   // gradient w.r.t. the weights, scaled: scaling * dy * V^T    (:119)
   bmm_problem(&g, batch, Tq, Tk, E, 0, 1, dy, E, sQ, V, E, sK, scores_grad_scratch, scaling);
   g.aux = weights;

@@ -78,7 +78,8 @@ def test_gpu_attention_matches_reference_goldens(wrapper, golden):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("causal", [False, True])
-@pytest.mark.parametrize("shape", [(3, 12, 12, 7), (2, 5, 9, 4), (8, 128, 128, 64), (4, 96, 200, 32), (2, 64, 1500, 16)])
+@pytest.mark.parametrize("shape", [(3, 12, 12, 7), (2, 5, 9, 4), (8, 128, 128, 64), (4, 96, 200, 32), (2, 64, 1500, 16),
+                                   (5, 100, 72, 24), (3, 300, 128, 128), (6, 40, 32, 64), (2, 130, 60, 36)])
 def test_gpu_attention_forward_backward_against_oracle(wrapper, shape, causal):
     from sharpnet_b200.attention import (ScaledDotProductAttentionBackwardPropagation,
                                          ScaledDotProductAttentionForwardPropagation)
@@ -89,8 +90,14 @@ def test_gpu_attention_forward_backward_against_oracle(wrapper, shape, causal):
     dy = rng.uniform(-1.5, 1.5, (B, Tq, E)).astype(np.float32)
     Qg, Kg, Vg, DY = (GPUTensor(a.shape, a, wrapper) for a in (Q, K, V, dy))
     y = GPUTensor((B, Tq, E), None, wrapper)
+    # a score row that fits one tile (up to 128 keys, head width up to 128 and a multiple of 4, 16 queries or more):
+    # one kernel for the forward pass, three for the backward pass (dV; dScores + dQ; dK)
+    fused = Tk <= 128 and E <= 128 and E % 4 == 0 and Tk % 4 == 0 and Tq >= 16
+    n0 = wrapper.launch_count()
     W = ScaledDotProductAttentionForwardPropagation(Qg, Kg, Vg, y, True, None, True, causal)
     wrapper.check_device_status()
+    if fused:
+        assert wrapper.launch_count() - n0 == 1 and wrapper.last_kernel().startswith("attention_fwd")
     w64, y64 = orc.sdpa_forward(Q, K, V, True, causal, f64=True)
     w = W.ContentAsFloatArray()
     # the scores carry the 1e-5 * sqrt(E) GEMM bound (times |q||k| <= 2.25, over sqrt(E)); softmax has slope <= 1/4
@@ -105,8 +112,22 @@ def test_gpu_attention_forward_backward_against_oracle(wrapper, shape, causal):
         assert np.abs(w - wm).max() <= 1e-5 * 2.25 + 1e-6
         assert np.abs(y.ContentAsFloatArray() - ym).max() <= 1e-5 * np.sqrt(Tk) * 1.5 + 1e-5
     dQ, dK, dV = (GPUTensor(s, None, wrapper) for s in ((B, Tq, E), (B, Tk, E), (B, Tk, E)))
+    n0 = wrapper.launch_count()
     ScaledDotProductAttentionBackwardPropagation(dQ, dK, dV, Qg, Kg, Vg, DY, W, True)
     wrapper.check_device_status()
+    if fused:      # one launch fewer than the four separate products, and the same gradients
+        from sharpnet_b200._capi import TUNE_NO_FUSED_ATTN
+        n_fused = wrapper.launch_count() - n0
+        dQ2, dK2, dV2 = (GPUTensor(s, None, wrapper) for s in ((B, Tq, E), (B, Tk, E), (B, Tk, E)))
+        wrapper.set_tuning(TUNE_NO_FUSED_ATTN, 1)
+        try:
+            n0 = wrapper.launch_count()
+            ScaledDotProductAttentionBackwardPropagation(dQ2, dK2, dV2, Qg, Kg, Vg, DY, W, True)
+            assert wrapper.launch_count() - n0 == n_fused + 1
+        finally:
+            wrapper.set_tuning(TUNE_NO_FUSED_ATTN, 0)
+        for a, b2 in ((dQ, dQ2), (dK, dK2), (dV, dV2)):
+            assert np.abs(a.ContentAsFloatArray() - b2.ContentAsFloatArray()).max() <= 2e-5
     dQ64, dK64, dV64 = orc.sdpa_backward(Q, K, V, dy, w, True)
     assert np.abs(dV.ContentAsFloatArray() - dV64).max() <= 1e-5 * np.sqrt(Tq) * 1.5 + 1e-5
     assert np.abs(dQ.ContentAsFloatArray() - dQ64).max() <= 1e-4
