@@ -143,6 +143,11 @@ struct UmmaParams {
   // C[col * ldc + row], so C, Z and ldc are those of the caller's matrix and bias runs along the tile's rows.
   int cluster;
   int store_t;
+  // Two products of the same shape in one launch (the GROUPED instantiation): matrices [0, group_batch) of the
+  // batch are problem 1 (tmA, tmB, C), matrices [group_batch, batch) problem 2 (tmA2, tmB2), whose results land
+  // c_shift floats away from where C + b * strideC (or the mapped placement of matrix b) would put them.
+  int group_batch;
+  long long c_shift;
   // operands as plain pointers, for the kernels whose loader warps replace TMA
   const float* A;
   const float* B;
@@ -524,10 +529,10 @@ template <int NC>
 __device__ __forceinline__ void epilogue_store_unit(const UmmaParams& p, float alpha, float beta, const float* bias,
                                                     const float (&acc)[NC], float* stage,
                                                     int b, int n_tiles, int tile, int split, int tile_row0, int tile_col0,
-                                                    int bn, int row_base, int n0, int lane) {
+                                                    int bn, int row_base, int n0, int lane, long long c_shift = 0) {
   // one call of the store phase (its code is long: a second copy costs instruction-cache misses); the
   // partial-sum case redirects it to the workspace
-  StoreTarget t = {p.C, p.Z, bias, alpha, beta, p.act, p.ldc, p.vec_ok, p.omap.on};
+  StoreTarget t = {p.C + c_shift, p.Z, bias, alpha, beta, p.act, p.ldc, p.vec_ok, p.omap.on};
   long long off = static_cast<long long>(b) * p.strideC;
   if (split >= 0 && p.partial != nullptr) {
     t.C = p.partial;
@@ -716,10 +721,10 @@ __device__ __forceinline__ void sw_issue_tile(uint8_t* dst, const float* src, lo
 // never waits for them.
 // ROWOP instantiates the epilogue with the row operations of attention (epilogue_row_op); the plain
 // instantiation carries none of their code or registers.
-template <class T, bool ROWOP = false, int CLUSTER = 1>
-__global__ void __launch_bounds__(T::THREADS, 1)
-umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const UmmaParams p) {
+template <class T, bool ROWOP, int CLUSTER, bool GROUPED>
+__device__ __forceinline__ void umma_gemm_core(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2,
+                                               const CUtensorMap& tmB2, const UmmaParams& p) {
+  static_assert(!GROUPED || (!ROWOP && CLUSTER == 1 && !T::SWLOAD && !T::TS), "the grouped form is the plain product");
   constexpr int BM = T::BM, BN = T::BN, BK = T::BK, STAGES = T::STAGES;
   extern __shared__ uint8_t smem_dyn[];
   __shared__ uint64_t full_bar[STAGES];    // TMA bytes landed
@@ -757,6 +762,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (!T::SWLOAD) {
       prefetch_tmap(&tmA);
       prefetch_tmap(&tmB);
+      if (GROUPED) {
+        prefetch_tmap(&tmA2);
+        prefetch_tmap(&tmB2);
+      }
     }
   }
   if (warp == 1) {
@@ -791,6 +800,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         unit_decode(p, n_tiles, t, tile, split, kb_begin, kb_end);
         tile_coords(tile, p.tiles_m, p.tiles_n, b, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        const bool second = GROUPED && b >= p.group_batch;
+        const CUtensorMap* mapA = second ? &tmA2 : &tmA;
+        const CUtensorMap* mapB = second ? &tmB2 : &tmB;
+        if (second) b -= p.group_batch;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) { ok = false; break; }
           uint8_t* a_dst = ring + s * T::STAGE_BYTES;
@@ -799,18 +812,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int k0 = kb * BK;
           if (t == blockIdx.x && kb == kb_begin) SNB_STAMP(p, 3);
           if (!p.a_mn) {
-            tma_load_3d(a_dst, &tmA, &full_bar[s], k0, m0, b);
+            tma_load_3d(a_dst, mapA, &full_bar[s], k0, m0, b);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 32; ++j)
-              tma_load_3d(a_dst + j * T::MNMAJ_CHUNK_BYTES, &tmA, &full_bar[s], m0 + 32 * j, k0, b);
+              tma_load_3d(a_dst + j * T::MNMAJ_CHUNK_BYTES, mapA, &full_bar[s], m0 + 32 * j, k0, b);
           }
           if (!p.b_mn) {
-            tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, b);
+            tma_load_3d(b_dst, mapB, &full_bar[s], k0, n0, b);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 32; ++j)
-              tma_load_3d(b_dst + j * T::MNMAJ_CHUNK_BYTES, &tmB, &full_bar[s], n0 + 32 * j, k0, b);
+              tma_load_3d(b_dst + j * T::MNMAJ_CHUNK_BYTES, mapB, &full_bar[s], n0 + 32 * j, k0, b);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -988,7 +1001,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         bias = nullptr;
       }
       epilogue_store_unit<NC>(p, alpha, c_folded ? 0.0f : p.beta, bias, acc, stage, b, n_tiles, tile, split, tm * BM, tn * BN,
-                              BN, tm * BM + q * 32, tn * BN + col_base, lane);
+                              BN, tm * BM + q * 32, tn * BN + col_base, lane,
+                              (GROUPED && b >= p.group_batch) ? p.c_shift : 0);
       if (warp == 4 && lane == 0) SNB_STAMP(p, t == blockIdx.x ? 9 : 10);
     }
   } else if (T::SPLIT && threadIdx.x < T::LOAD_THREAD0) {
@@ -1080,6 +1094,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (CLUSTER > 1) cluster_sync_all();
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.error_word, 1);
   if (threadIdx.x == 0) SNB_STAMP(p, 12);
+}
+
+template <class T, bool ROWOP = false, int CLUSTER = 1>
+__global__ void __launch_bounds__(T::THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const UmmaParams p) {
+  umma_gemm_core<T, ROWOP, CLUSTER, false>(tmA, tmB, tmA, tmB, p);
+}
+
+// Two products of one shape in one grid (see UmmaParams::group_batch): the second product's operands come through
+// their own tensor maps.  Whole tiles only, no row operation, beta = 0.
+template <class T>
+__global__ void __launch_bounds__(T::THREADS, 1)
+umma_gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                         const UmmaParams p) {
+  umma_gemm_core<T, false, 1, true>(tmA, tmB, tmA2, tmB2, p);
 }
 
 // Second pass of a split-K (or swapped-operand) GEMM: sums the `splits` raw partial results and applies

@@ -356,6 +356,8 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
 #endif
   p.cluster = 1;
   p.store_t = 0;
+  p.group_batch = 0;
+  p.c_shift = 0;
   p.whole_tiles = 0;       // set by the launcher: it knows the tile grid of its kernel
   p.partial_tiled = 0;
   p.partial = nullptr;
@@ -827,6 +829,97 @@ static int launch_reduce(snb200_handle_t h, const GemmProblem& g, int parts, int
 }
 
 static int run_gemm_untimed(snb200_handle_t h, const GemmProblem& g);
+static int run_gemm(snb200_handle_t h, const GemmProblem& g);
+
+// Two strided-batched products of one shape (same dimensions, transposes, pitches and strides; beta = 0, no bias, no
+// activation) as ONE launch of the single-CTA tensor-core kernel: the grid walks 2 x batch matrices and takes the
+// second half's operands from their own tensor maps.  Used where two small products follow each other and each
+// would be mostly launch (the dV and dK products of the attention backward pass).  Falls back to two calls when the
+// pair does not qualify.
+template <class T>
+static int launch_umma_grouped_t(snb200_handle_t h, const GemmProblem& g1, const GemmProblem& g2, long long c_shift) {
+  static bool configured[64] = {};
+  CUtensorMap tmA, tmB, tmA2, tmB2;
+  UmmaParams p, p2;
+  int st = fill_umma_args<T>(h, g1, T::BN, &tmA, &tmB, &p);
+  if (!st) st = fill_umma_args<T>(h, g2, T::BN, &tmA2, &tmB2, &p2);
+  if (st) return st;
+  p.group_batch = g1.batch;
+  p.batch = 2 * g1.batch;
+  p.c_shift = c_shift;
+  p.vec_ok = p.vec_ok && p2.vec_ok && !(c_shift & 3);
+  const long long n_tiles = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
+  p.whole_tiles = static_cast<int>(n_tiles);
+  if (!configured[h->device]) {
+    SNB_CUDA(h, cudaFuncSetAttribute(umma_gemm_grouped_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    configured[h->device] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(n_tiles < usable_sms(h) ? n_tiles : usable_sms(h)));
+  cfg.blockDim = dim3(T::THREADS);
+  cfg.dynamicSmemBytes = T::SMEM_BYTES;
+  cfg.stream = h->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = h->tune[TUNE_PDL] == 1 ? 0 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_grouped_kernel<T>, tmA, tmB, tmA2, tmB2, p);
+  if (e != cudaSuccess) return cuda_fail(h, e, "umma_gemm_grouped_kernel launch");
+  return check_launch(h, "umma_gemm_grouped_kernel launch");
+}
+
+static int run_gemm_pair(snb200_handle_t h, const GemmProblem& g1, const GemmProblem& g2) {
+  const bool same = g1.M == g2.M && g1.N == g2.N && g1.K == g2.K && g1.batch == g2.batch && g1.transA == g2.transA &&
+                    g1.transB == g2.transB && g1.lda == g2.lda && g1.ldb == g2.ldb && g1.ldc == g2.ldc &&
+                    g1.strideA == g2.strideA && g1.strideB == g2.strideB && g1.strideC == g2.strideC &&
+                    g1.alpha == g2.alpha && memcmp(&g1.omap, &g2.omap, sizeof(OutMap)) == 0;
+  const bool plain = g1.beta == 0.0f && g2.beta == 0.0f && !g1.bias && !g2.bias && !g1.Z && !g2.Z &&
+                     g1.act == ACT_IDENTITY && g2.act == ACT_IDENTITY && g1.row_op == ROW_NONE && g2.row_op == ROW_NONE;
+  const bool tensor = h->math_mode != SNB200_MATH_FP32_SIMT && h->tune[TUNE_FORCE_PATH] != 2 &&
+                      h->tune[TUNE_NO_FUSED_ATTN] == 0 && tma_eligible(g1) && tma_eligible(g2);
+  // few K blocks per tile: launch-bound products that no K cut would help
+  const long long tiles = static_cast<long long>(g1.batch) * ((g1.M + 127) / 128) * ((g1.N + 127) / 128);
+  const bool small = g1.N <= 128 && g1.M >= 16 && g1.N >= 8 && g1.K <= 512 && 2 * tiles <= 0x3fffffffLL &&
+                     static_cast<double>(g1.M) * g1.N * g1.K * g1.batch >= 64.0 * 64 * 64;
+  long long c_shift = 0;
+  bool placed = ((reinterpret_cast<uintptr_t>(g1.C) | reinterpret_cast<uintptr_t>(g2.C)) & 3u) == 0;
+  if (same && placed) {
+    // where matrix b of the doubled batch would land from g1.C, against where matrix b - batch of g2 must land
+    const long long base = g1.omap.on ? (g1.batch % g1.omap.H == 0 ? static_cast<long long>(g1.batch / g1.omap.H) * g1.omap.s_io : -1)
+                                      : static_cast<long long>(g1.batch) * g1.strideC;
+    if (g1.omap.on && base < 0) placed = false;
+    c_shift = (reinterpret_cast<intptr_t>(g2.C) - reinterpret_cast<intptr_t>(g1.C)) / 4 - base;
+  }
+  if (!(same && plain && tensor && small && placed)) {
+    const int st = run_gemm(h, g1);
+    return st ? st : run_gemm(h, g2);
+  }
+  const bool timed = h->time_gemms && h->gemm_events_used + 2 <= 2 * kMaxTimedGemms;
+  if (timed) SNB_CUDA(h, cudaEventRecord(h->gemm_events[h->gemm_events_used], h->stream));
+  const bool split = h->math_mode == SNB200_MATH_3XTF32 || h->math_mode == SNB200_MATH_TF32_BF16X2;
+  const int bn = g1.N <= 32 ? 32 : g1.N <= 64 ? 64 : 128;
+  char name[64];
+  snprintf(name, sizeof(name), "umma_%s_128x%d_grouped", split ? "3xtf32" : "tf32", bn);
+  note_kernel(h, name, 1);
+  int st;
+  if (split) {
+    st = bn == 32 ? launch_umma_grouped_t<UmmaTile<32, 32, true>>(h, g1, g2, c_shift)
+       : bn == 64 ? launch_umma_grouped_t<UmmaTile<64, 32, true>>(h, g1, g2, c_shift)
+                  : launch_umma_grouped_t<UmmaTile<128, 32, true>>(h, g1, g2, c_shift);
+  } else {
+    st = bn == 32 ? launch_umma_grouped_t<UmmaTile<32, 32, false>>(h, g1, g2, c_shift)
+       : bn == 64 ? launch_umma_grouped_t<UmmaTile<64, 32, false>>(h, g1, g2, c_shift)
+                  : launch_umma_grouped_t<UmmaTile<128, 32, false>>(h, g1, g2, c_shift);
+  }
+  if (timed) {
+    SNB_CUDA(h, cudaEventRecord(h->gemm_events[h->gemm_events_used + 1], h->stream));
+    h->gemm_events_used += 2;
+  }
+  return st;
+}
+
 static int run_gemm(snb200_handle_t h, const GemmProblem& g) {
   const bool timed = h->time_gemms && h->gemm_events_used + 2 <= 2 * kMaxTimedGemms;
   if (timed) SNB_CUDA(h, cudaEventRecord(h->gemm_events[h->gemm_events_used], h->stream));
@@ -1694,20 +1787,22 @@ static int sdpa_bwd_impl(snb200_handle_t h, int batch, int q_steps, int v_steps,
   const long long sW = static_cast<long long>(Tq) * Tk;
   const float scaling = use_scale ? 1.0f / sqrtf(static_cast<float>(E)) : 1.0f;
   GemmProblem g;
+  // dScores and dQ in one kernel where a score row fits one tile                       (:119-123)
+  st = try_fused_attention_bwd(h, batch, Tq, Tk, E, scaling, dy, V, K, weights, scores_grad_scratch, dQ, dq_map);
+  if (st > 0) return st;
+  if (st == 0) {
+    // dV = weights^T * dy and dK = dScores^T * Q: two products of one shape, one launch where they qualify  (:113,124)
+    GemmProblem gk;
+    bmm_problem(&g, batch, Tk, E, Tq, 1, 0, weights, Tk, sW, dy, E, sQ, dV, 1.0f);
+    bmm_problem(&gk, batch, Tk, E, Tq, 1, 0, scores_grad_scratch, Tk, sW, Q, E, sQ, dK, 1.0f);
+    if (dkv_map) { g.omap = *dkv_map; gk.omap = *dkv_map; }
+    return run_gemm_pair(h, g, gk);
+  }
   // dV = weights^T * dy                               (ScaledDotProductAttentionLayer.cs:113)
   bmm_problem(&g, batch, Tk, E, Tq, 1, 0, weights, Tk, sW, dy, E, sQ, dV, 1.0f);
   if (dkv_map) g.omap = *dkv_map;
   st = run_gemm(h, g);
   if (st) return st;
-  // dScores and dQ in one kernel where a score row fits one tile                       (:119-123)
-  st = try_fused_attention_bwd(h, batch, Tq, Tk, E, scaling, dy, V, K, weights, scores_grad_scratch, dQ, dq_map);
-  if (st > 0) return st;
-  if (st == 0) {
-    // dK = dScores^T * Q                                                               (:124)
-    bmm_problem(&g, batch, Tk, E, Tq, 1, 0, scores_grad_scratch, Tk, sW, Q, E, sQ, dK, 1.0f);
-    if (dkv_map) g.omap = *dkv_map;
-    return run_gemm(h, g);
-  }
   // gradient w.r.t. the weights, scaled: scaling * dy * V^T    (:119)
   bmm_problem(&g, batch, Tq, Tk, E, 0, 1, dy, E, sQ, V, E, sK, scores_grad_scratch, scaling);
   g.aux = weights;
