@@ -376,6 +376,10 @@ int snb200_stager_destroy(snb200_stager_t stager);
 int snb200_stager_issue(snb200_stager_t stager, int slot, int n_copies, void* const* device_dst,
                         const void* const* host_src, const long long* bytes);
 int snb200_stager_acquire(snb200_stager_t stager, int slot);
+/* The same for ONE copy of the slot's last issue (the first 16 copies of an issue have an event of their own): the
+ * handle's stream waits only for copies 0 .. part, so that work on the first rows of a mini-batch staged as several
+ * row panels starts while the later panels are still on their way. */
+int snb200_stager_acquire_part(snb200_stager_t stager, int slot, int part);
 int snb200_stager_release(snb200_stager_t stager, int slot);
 /* Page-locks / unlocks caller-owned host memory so that the copies above run asynchronously at full speed: what
  * HostPinnedMemory does for a managed array (Prod/CPU/HostPinnedMemory.cs:17-21; there the GC pin, here the CUDA

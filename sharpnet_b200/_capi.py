@@ -93,6 +93,7 @@ SIGNATURES = {
     "snb200_stager_destroy": (_I, [_P]),
     "snb200_stager_issue": (_I, [_P, _I, _I, _c.POINTER(_P), _c.POINTER(_P), _c.POINTER(_L)]),
     "snb200_stager_acquire": (_I, [_P, _I]),
+    "snb200_stager_acquire_part": (_I, [_P, _I, _I]),
     "snb200_stager_release": (_I, [_P, _I]),
     "snb200_host_pin": (_I, [_P, _L]),
     "snb200_host_unpin": (_I, [_P]),

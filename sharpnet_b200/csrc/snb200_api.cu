@@ -1937,7 +1937,10 @@ struct snb200_stager {
   cudaEvent_t* consumed;
   unsigned char* has_copied;
   unsigned char* has_consumed;
+  cudaEvent_t* part_copied;   // [slots][kStagerParts]: behind each of the first copies of an issue
+  int* n_parts;               // copies of the slot's last issue that have an event of their own
 };
+constexpr int kStagerParts = 16;
 
 extern "C" int snb200_stager_create(snb200_handle_t h, int slots, snb200_stager_t* out) {
   int st = enter(h);
@@ -1951,11 +1954,15 @@ extern "C" int snb200_stager_create(snb200_handle_t h, int slots, snb200_stager_
   s->consumed = static_cast<cudaEvent_t*>(calloc(slots, sizeof(cudaEvent_t)));
   s->has_copied = static_cast<unsigned char*>(calloc(slots, 1));
   s->has_consumed = static_cast<unsigned char*>(calloc(slots, 1));
-  bool ok = s->copied && s->consumed && s->has_copied && s->has_consumed &&
+  s->part_copied = static_cast<cudaEvent_t*>(calloc(static_cast<size_t>(slots) * kStagerParts, sizeof(cudaEvent_t)));
+  s->n_parts = static_cast<int*>(calloc(slots, sizeof(int)));
+  bool ok = s->copied && s->consumed && s->has_copied && s->has_consumed && s->part_copied && s->n_parts &&
             cudaStreamCreateWithFlags(&s->copy_stream, cudaStreamNonBlocking) == cudaSuccess;
   for (int i = 0; ok && i < slots; ++i)
     ok = cudaEventCreateWithFlags(&s->copied[i], cudaEventDisableTiming) == cudaSuccess &&
          cudaEventCreateWithFlags(&s->consumed[i], cudaEventDisableTiming) == cudaSuccess;
+  for (int i = 0; ok && i < slots * kStagerParts; ++i)
+    ok = cudaEventCreateWithFlags(&s->part_copied[i], cudaEventDisableTiming) == cudaSuccess;
   if (!ok) {
     snb200_stager_destroy(s);
     return fail(h, SNB200_STATUS_ALLOC_FAILED, "could not create the copy stream or its events");
@@ -1972,6 +1979,9 @@ extern "C" int snb200_stager_destroy(snb200_stager_t s) {
     if (s->copied && s->copied[i]) cudaEventDestroy(s->copied[i]);
     if (s->consumed && s->consumed[i]) cudaEventDestroy(s->consumed[i]);
   }
+  for (int i = 0; s->part_copied && i < s->slots * kStagerParts; ++i)
+    if (s->part_copied[i]) cudaEventDestroy(s->part_copied[i]);
+  free(s->part_copied); free(s->n_parts);
   free(s->copied); free(s->consumed); free(s->has_copied); free(s->has_consumed);
   free(s);
   return 0;
@@ -1991,12 +2001,28 @@ extern "C" int snb200_stager_issue(snb200_stager_t s, int slot, int n_copies, vo
       return fail(h, SNB200_STATUS_INVALID_VALUE, "bad copy %d", i);
   // the slot may still be read by the step it was staged for
   if (s->has_consumed[slot]) SNB_CUDA(h, cudaStreamWaitEvent(s->copy_stream, s->consumed[slot], 0));
-  for (int i = 0; i < n_copies; ++i)
+  for (int i = 0; i < n_copies; ++i) {
     if (bytes[i] > 0)
       SNB_CUDA(h, cudaMemcpyAsync(device_dst[i], host_src[i], static_cast<size_t>(bytes[i]), cudaMemcpyHostToDevice,
                                   s->copy_stream));
+    if (i < kStagerParts) SNB_CUDA(h, cudaEventRecord(s->part_copied[slot * kStagerParts + i], s->copy_stream));
+  }
+  s->n_parts[slot] = n_copies < kStagerParts ? n_copies : kStagerParts;
   SNB_CUDA(h, cudaEventRecord(s->copied[slot], s->copy_stream));
   s->has_copied[slot] = 1;
+  return 0;
+}
+
+extern "C" int snb200_stager_acquire_part(snb200_stager_t s, int slot, int part) {
+  if (!s) return SNB200_STATUS_NOT_INITIALIZED;
+  snb200_handle_t h = s->h;
+  int st = enter(h);
+  if (st) return st;
+  if (slot < 0 || slot >= s->slots) return fail(h, SNB200_STATUS_INVALID_VALUE, "slot %d of %d", slot, s->slots);
+  if (!s->has_copied[slot]) return fail(h, SNB200_STATUS_INVALID_VALUE, "nothing was staged into slot %d", slot);
+  if (part < 0 || part >= s->n_parts[slot])
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "copy %d of the %d with their own event in slot %d", part, s->n_parts[slot], slot);
+  SNB_CUDA(h, cudaStreamWaitEvent(h->stream, s->part_copied[slot * kStagerParts + part], 0));
   return 0;
 }
 

@@ -64,14 +64,30 @@ class DenseStack:
         self.dx = [None] + [GPUTensor((local_batch, dims[i]), None, wrapper) for i in range(1, n)]
         self.dy = GPUTensor((local_batch, dims[-1]), None, wrapper)
         self.reserve_pending = False
+        # set by HostStaging when the input arrives as row panels: the first layer then runs panel by panel, each
+        # product waiting only for its own rows, and the upstream gradient is waited for where the backward pass starts
+        self.input_panels = None        # [(row0, row1), ...]
+        self.before_panel = None        # callable(k)
+        self.before_backward = None     # callable()
 
     def forward(self):
+        import ctypes
         lib, h = self.w.lib, self.w.handle
         src = self.x
         for i, W in enumerate(self.W):
-            st = lib.snb200_dense_fwd(h, self.layout, self.batch, self.dims[i], self.dims[i + 1], src.Pointer,
-                                      W.Pointer, self.b[i].Pointer, self.acts[i], None, self.y[i].Pointer)
-            check(h, st)
+            if i == 0 and self.input_panels:
+                K, N = self.dims[0], self.dims[1]
+                for k, (r0, r1) in enumerate(self.input_panels):
+                    if self.before_panel is not None:
+                        self.before_panel(k)
+                    st = lib.snb200_dense_fwd(h, self.layout, r1 - r0, K, N,
+                                              ctypes.c_void_p(src.Pointer.value + 4 * r0 * K), W.Pointer, self.b[0].Pointer,
+                                              self.acts[0], None, ctypes.c_void_p(self.y[0].Pointer.value + 4 * r0 * N))
+                    check(h, st)
+            else:
+                st = lib.snb200_dense_fwd(h, self.layout, self.batch, self.dims[i], self.dims[i + 1], src.Pointer,
+                                          W.Pointer, self.b[i].Pointer, self.acts[i], None, self.y[i].Pointer)
+                check(h, st)
             src = self.y[i]
 
     def _bwd(self, i, grad, act, dz, dx, dW, db):
@@ -100,6 +116,8 @@ class DenseStack:
         instead of in its turn (it depends only on that layer's dz and input, which stay in place), so that the
         reduction nothing is left to hide behind is the smallest one.  The arithmetic is the same in any order."""
         n = len(self.W)
+        if self.before_backward is not None:
+            self.before_backward()
         deferred = None
         if defer_smallest and n > 1:
             smallest = min(range(n), key=lambda i: self.W[i].Count)
@@ -273,7 +291,11 @@ class HostStaging:
     i+1 runs on the stager's stream while step i computes; the compute stream only waits for the copy it
     is about to consume, and a buffer is not overwritten before the step that read it has finished."""
 
-    def __init__(self, stack, x_host, dy_host, slots=2):
+    def __init__(self, stack, x_host, dy_host, slots=2, panels=1):
+        """``panels`` > 1 stages x as that many row panels (up to 15), each with an event of its own, and lets the
+        stack's first layer start on a panel as soon as it has landed; the upstream gradient, copied last, is
+        waited for where the backward pass starts.  Only the very first step of a loop gains (its copy has nothing
+        to hide behind); every later copy overlaps the step before it either way."""
         import ctypes
         self.stack = stack
         self.x_host, self.dy_host = x_host, dy_host
@@ -283,22 +305,47 @@ class HostStaging:
                                                 for _ in range(slots - 1)]
         self.handle = ctypes.c_void_p()
         check(w.handle, w.lib.snb200_stager_create(w.handle, slots, ctypes.byref(self.handle)))
-        self._src = (ctypes.c_void_p * 2)(x_host.data_ptr(), dy_host.data_ptr())
-        self._bytes = (ctypes.c_longlong * 2)(x_host.numel() * 4, dy_host.numel() * 4)
-        self._dst = [(ctypes.c_void_p * 2)(bx.Pointer, bdy.Pointer) for bx, bdy in self.buffers]
+        rows, width = stack.batch, stack.dims[0]
+        panels = max(1, min(int(panels), 15, rows // 256 if rows >= 256 else 1))
+        per = -(-rows // panels)
+        per = -(-per // 128) * 128 if panels > 1 else per          # whole tile rows per panel
+        self.panels = [(r, min(rows, r + per)) for r in range(0, rows, per)]
+        n = len(self.panels) + 1
+        self._n = n
+        self._src = (ctypes.c_void_p * n)(*[x_host.data_ptr() + 4 * r0 * width for r0, _ in self.panels], dy_host.data_ptr())
+        self._bytes = (ctypes.c_longlong * n)(*[4 * (r1 - r0) * width for r0, r1 in self.panels], dy_host.numel() * 4)
+        self._dst = [(ctypes.c_void_p * n)(*[bx.Pointer.value + 4 * r0 * width for r0, _ in self.panels], bdy.Pointer.value)
+                     for bx, bdy in self.buffers]
+        self._slot = 0
 
     def issue(self, i):
         """Queues the copy of step ``i``'s inputs into buffer ``i % slots``."""
         w = self.stack.w
         b = i % self.slots
-        check(w.handle, w.lib.snb200_stager_issue(self.handle, b, 2, self._dst[b], self._src, self._bytes))
+        check(w.handle, w.lib.snb200_stager_issue(self.handle, b, self._n, self._dst[b], self._src, self._bytes))
+
+    def _wait_panel(self, k):
+        w = self.stack.w
+        check(w.handle, w.lib.snb200_stager_acquire_part(self.handle, self._slot, k))
+
+    def wait(self):
+        """Makes the compute stream wait for everything staged into the bound buffer."""
+        w = self.stack.w
+        check(w.handle, w.lib.snb200_stager_acquire(self.handle, self._slot))
 
     def bind(self, i):
-        """Points the stack at buffer ``i % slots`` and makes the compute stream wait for its copy."""
+        """Points the stack at buffer ``i % slots`` and makes the compute stream wait for its copy: for all of it
+        here, or (row panels) panel by panel inside the stack's first layer and before its backward pass."""
         w = self.stack.w
         b = i % self.slots
-        check(w.handle, w.lib.snb200_stager_acquire(self.handle, b))
+        self._slot = b
         self.stack.x, self.stack.dy = self.buffers[b]
+        if len(self.panels) > 1:
+            self.stack.input_panels = self.panels
+            self.stack.before_panel = self._wait_panel
+            self.stack.before_backward = self.wait
+        else:
+            check(w.handle, w.lib.snb200_stager_acquire(self.handle, b))
 
     def release(self, i):
         """Call after step ``i`` has been queued: marks when its buffer may be overwritten."""
@@ -310,6 +357,7 @@ class HostStaging:
             self.stack.w.lib.snb200_stager_destroy(self.handle)
             self.handle = None
         self.stack.x, self.stack.dy = self.buffers[0]
+        self.stack.input_panels = self.stack.before_panel = self.stack.before_backward = None
 
 
 class SgdUpdate:

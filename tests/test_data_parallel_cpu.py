@@ -120,6 +120,7 @@ def _fake_stack(dims, acts):
     s.dx = [None] + [_FakeTensor(8 * dims[i], f"dx{i}") for i in range(1, n)]
     s.dy = _FakeTensor(8 * dims[-1], "dy")
     s.reserve_pending = False
+    s.input_panels = s.before_panel = s.before_backward = None
     return s
 
 

@@ -254,16 +254,20 @@ def test_stager_orders_copies_and_steps(wrapper):
     assert lib.snb200_host_pin(None, 16) == 7
 
 
-def test_host_staging_class_feeds_the_stack(wrapper):
+@pytest.mark.parametrize("batch,panels", [(256, 1), (1024, 4), (900, 3)])
+def test_host_staging_class_feeds_the_stack(wrapper, batch, panels):
+    # whole mini-batches, and x staged as row panels that the first layer consumes one by one (the ragged case:
+    # 900 rows in panels of 384, 384 and 132)
     from sharpnet_b200 import ACT_IDENTITY, ACT_RELU
     from sharpnet_b200.data_parallel import DenseStack, HostStaging, training_step
     import torch
-    batch, dims = 256, (128, 96, 32)
+    dims = (128, 96, 32)
     x, dy, Ws, bs = _problem(batch, dims, 300)
     stack = DenseStack(wrapper, batch, dims, (ACT_RELU, ACT_IDENTITY), Ws)
     _load(stack, np.zeros_like(x), np.zeros_like(dy), bs)
     xh, dyh = torch.from_numpy(x).pin_memory(), torch.from_numpy(dy).pin_memory()
-    staging = HostStaging(stack, xh, dyh)
+    staging = HostStaging(stack, xh, dyh, panels=panels)
+    assert len(staging.panels) == panels and staging.panels[-1][1] == batch
     staging.issue(0)
     for i in range(3):
         staging.bind(i)
