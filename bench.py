@@ -857,7 +857,7 @@ def run_ours(args):
     from sharpnet_b200.data_parallel import HostStaging
     # x travels as four row panels: the first layer starts on a panel as soon as it has landed, which shortens the one
     # copy of the loop that nothing overlaps (the first) to a quarter
-    staging = HostStaging(stack, x_host, dy_host, panels=4)
+    staging = HostStaging(stack, x_host, dy_host, panels=int(os.environ.get("SNB200_STAGE_PANELS", "4")))
 
     def e2e_loop(n):
         staging.issue(0)
