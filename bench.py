@@ -857,7 +857,10 @@ def run_ours(args):
     from sharpnet_b200.data_parallel import HostStaging
     # x travels as four row panels: the first layer starts on a panel as soon as it has landed, which shortens the one
     # copy of the loop that nothing overlaps (the first) to a quarter
-    staging = HostStaging(stack, x_host, dy_host, panels=int(os.environ.get("SNB200_STAGE_PANELS", "4")))
+    # (panels of at least 16384 rows: below that the first layer's products get too small to run at full rate, measured
+    # at 4 GPUs -- 4096-row panels cost 0.4 ms per step)
+    panels = int(os.environ.get("SNB200_STAGE_PANELS", str(min(4, max(1, rows // 16384)))))
+    staging = HostStaging(stack, x_host, dy_host, panels=panels)
 
     def e2e_loop(n):
         staging.issue(0)
@@ -918,8 +921,8 @@ def run_ours(args):
                     "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms,
                     "pipeline_fill_ms": fill_ms,
                     "note": "pipeline_fill_ms = one step's input copy on its own.  The timed loop starts with step 0's copy, "
-                            "which nothing of the region runs before; x travels as 4 row panels and the first layer starts "
-                            "on each as it lands, so about a quarter of it is exposed, once per run of `steps` steps; "
+                            f"which nothing of the region runs before; x travels as {panels} row panel(s) and the first layer "
+                            "starts on each as it lands, so that fraction of it is exposed, once per run of `steps` steps; "
                             "every later copy runs behind the step before it"},
             "gpu_launches": launches * world,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak3, "unit": "TFLOP/s",
