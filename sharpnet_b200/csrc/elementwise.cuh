@@ -134,6 +134,39 @@ static __global__ void transpose_second_third_kernel(long long total_vec, int B,
   }
 }
 
+// The same permutation through a shared-memory tile, for large tensors with short D-runs: a block takes TB
+// consecutive b x TC consecutive c of one a, reads them in source order (runs of TC * D floats) and writes them in
+// destination order (runs of TB * D floats), so that both sides of the copy move kilobytes at a time instead of one
+// D-run (256 bytes for 64-wide heads) per 4 KB of address space.  D is a multiple of 4; TB * TC * D <= 8192 floats.
+static __global__ void __launch_bounds__(256)
+transpose_second_third_tiled_kernel(int A, int B, int C, int Dv, int TB, int TC, const float4* __restrict__ src,
+                                    float4* __restrict__ dst) {
+  pdl_prologue();
+  __shared__ float4 tile[2048];
+  const int tiles_b = (B + TB - 1) / TB, tiles_c = (C + TC - 1) / TC;
+  const long long n_tiles = static_cast<long long>(A) * tiles_b * tiles_c;
+  const int per_tile = TB * TC * Dv;
+  for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int tc = static_cast<int>(t % tiles_c);
+    const long long r = t / tiles_c;
+    const int tb = static_cast<int>(r % tiles_b);
+    const long long a = r / tiles_b;
+    const int b0 = tb * TB, c0 = tc * TC;
+    for (int i = threadIdx.x; i < per_tile; i += 256) {          // (bi, ci, dv), dv fastest: source order
+      const int dv = i % Dv, ci = (i / Dv) % TC, bi = i / (Dv * TC);
+      if (b0 + bi < B && c0 + ci < C)
+        tile[(ci * TB + bi) * Dv + dv] = src[((a * B + b0 + bi) * C + c0 + ci) * Dv + dv];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < per_tile; i += 256) {          // (ci, bi, dv), dv fastest: destination order
+      const int dv = i % Dv, bi = (i / Dv) % TB, ci = i / (Dv * TB);
+      if (b0 + bi < B && c0 + ci < C)
+        dst[((a * C + c0 + ci) * B + b0 + bi) * Dv + dv] = tile[i];
+    }
+    __syncthreads();
+  }
+}
+
 // Column sums of g[M x N] over a slab of rows, optionally fused with the activation gradient:
 //   g = dy                        (FUSE_ACT = false:  db = sum_m dy,  CpuTensor.cs:3343-3362)
 //   g = act'(z, y) * dy -> dz     (FUSE_ACT = true:   ActivationBackward + bias gradient in one pass)
@@ -287,6 +320,62 @@ softmax_fwd_kernel(long long rows, int cols, int causal_rows, const float* x, fl
       }
     } else {
       for (int c = lane; c < cols; c += 32) yr[c] = expf(((c > limit) ? -1e12f : xr[c]) - mx) / sum;
+    }
+  }
+}
+
+// The same for short rows (up to 32 * PER_LANE columns), R rows per warp at a time: with one 512-byte row in flight
+// per warp the kernel is bound by memory latency (0.69 of the HBM rate at 128 columns); R independent rows give every
+// lane R * PER_LANE loads in flight.  Per row the arithmetic and its order are those of the kernel above.
+template <int PER_LANE, int R>
+static __global__ void __launch_bounds__(256)
+softmax_fwd_rows_kernel(long long rows, int cols, int causal_rows, const float* x, float* y) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r0 = warp * R; r0 < rows; r0 += n_warps * R) {
+    float v[R][PER_LANE];
+    float mx[R], sum[R];
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const long long r = r0 + q;
+      const bool live = r < rows;
+      const float* xr = x + (live ? r : r0) * cols;
+      const int limit = causal_rows > 0 ? static_cast<int>((live ? r : r0) % causal_rows) : cols;
+      mx[q] = -3.402823466e38f;
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        v[q][i] = (c < cols) ? ((c > limit) ? -1e12f : xr[c]) : -3.402823466e38f;
+        mx[q] = fmaxf(mx[q], v[q][i]);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], o));
+      sum[q] = 0.0f;
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        v[q][i] = (c < cols) ? expf(v[q][i] - mx[q]) : 0.0f;
+        sum[q] += v[q][i];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum[q] += __shfl_xor_sync(0xffffffffu, sum[q], o);
+    }
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const long long r = r0 + q;
+      if (r < rows) {
+        float* yr = y + r * cols;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+          const int c = lane + 32 * i;
+          if (c < cols) yr[c] = v[q][i] / sum[q];
+        }
+      }
     }
   }
 }
