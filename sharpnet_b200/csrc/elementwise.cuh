@@ -134,39 +134,6 @@ static __global__ void transpose_second_third_kernel(long long total_vec, int B,
   }
 }
 
-// The same permutation through a shared-memory tile, for large tensors with short D-runs: a block takes TB
-// consecutive b x TC consecutive c of one a, reads them in source order (runs of TC * D floats) and writes them in
-// destination order (runs of TB * D floats), so that both sides of the copy move kilobytes at a time instead of one
-// D-run (256 bytes for 64-wide heads) per 4 KB of address space.  D is a multiple of 4; TB * TC * D <= 8192 floats.
-static __global__ void __launch_bounds__(256)
-transpose_second_third_tiled_kernel(int A, int B, int C, int Dv, int TB, int TC, const float4* __restrict__ src,
-                                    float4* __restrict__ dst) {
-  pdl_prologue();
-  __shared__ float4 tile[2048];
-  const int tiles_b = (B + TB - 1) / TB, tiles_c = (C + TC - 1) / TC;
-  const long long n_tiles = static_cast<long long>(A) * tiles_b * tiles_c;
-  const int per_tile = TB * TC * Dv;
-  for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-    const int tc = static_cast<int>(t % tiles_c);
-    const long long r = t / tiles_c;
-    const int tb = static_cast<int>(r % tiles_b);
-    const long long a = r / tiles_b;
-    const int b0 = tb * TB, c0 = tc * TC;
-    for (int i = threadIdx.x; i < per_tile; i += 256) {          // (bi, ci, dv), dv fastest: source order
-      const int dv = i % Dv, ci = (i / Dv) % TC, bi = i / (Dv * TC);
-      if (b0 + bi < B && c0 + ci < C)
-        tile[(ci * TB + bi) * Dv + dv] = src[((a * B + b0 + bi) * C + c0 + ci) * Dv + dv];
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < per_tile; i += 256) {          // (ci, bi, dv), dv fastest: destination order
-      const int dv = i % Dv, bi = (i / Dv) % TB, ci = i / (Dv * TB);
-      if (b0 + bi < B && c0 + ci < C)
-        dst[((a * C + c0 + ci) * B + b0 + bi) * Dv + dv] = tile[i];
-    }
-    __syncthreads();
-  }
-}
-
 // Column sums of g[M x N] over a slab of rows, optionally fused with the activation gradient:
 //   g = dy                        (FUSE_ACT = false:  db = sum_m dy,  CpuTensor.cs:3343-3362)
 //   g = act'(z, y) * dy -> dz     (FUSE_ACT = true:   ActivationBackward + bias gradient in one pass)

@@ -1484,19 +1484,7 @@ extern "C" int snb200_transpose_second_third(snb200_handle_t h, int A, int B, in
   if (total == 0) return 0;
   if (!src || !dst) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (src == dst) return fail(h, SNB200_STATUS_INVALID_VALUE, "the permutation is not done in place");
-  if (D % 4 == 0 && aligned16(src) && aligned16(dst) && D <= 512 && total >= (4LL << 20) && B >= 8 && C >= 4) {
-    // large tensors with short runs: through a 32 KB shared-memory tile
-    const int Dv = D / 4;
-    int TC = C < 16 ? C : 16;
-    while (TC > 1 && TC * Dv > 1024) TC >>= 1;
-    int TB = 2048 / (TC * Dv);
-    if (TB > B) TB = B;
-    if (TB > 64) TB = 64;
-    const long long tiles = static_cast<long long>(A) * ((B + TB - 1) / TB) * ((C + TC - 1) / TC);
-    const long long cap = 8LL * h->sm_count;
-    launch_pdl(h, transpose_second_third_tiled_kernel, dim3(static_cast<unsigned>(tiles < cap ? tiles : cap)), dim3(256), A, B, C,
-               Dv, TB, TC, reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(dst));
-  } else if (D % 4 == 0 && aligned16(src) && aligned16(dst))
+  if (D % 4 == 0 && aligned16(src) && aligned16(dst))
     launch_pdl(h, transpose_second_third_kernel<4>, dim3(ew_grid(h, total / 4, 256)), dim3(256), total / 4, B, C, D / 4, src, dst);
   else
     launch_pdl(h, transpose_second_third_kernel<1>, dim3(ew_grid(h, total, 256)), dim3(256), total, B, C, D, src, dst);

@@ -79,7 +79,8 @@ def test_gpu_attention_matches_reference_goldens(wrapper, golden):
 @pytest.mark.gpu
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("shape", [(3, 12, 12, 7), (2, 5, 9, 4), (8, 128, 128, 64), (4, 96, 200, 32), (2, 64, 1500, 16),
-                                   (5, 100, 72, 24), (3, 300, 128, 128), (6, 40, 32, 64), (2, 130, 60, 36)])
+                                   (5, 100, 72, 24), (3, 300, 128, 128), (6, 40, 32, 64), (2, 130, 60, 36),
+                                   (80, 128, 128, 6)])
 def test_gpu_attention_forward_backward_against_oracle(wrapper, shape, causal):
     from sharpnet_b200.attention import (ScaledDotProductAttentionBackwardPropagation,
                                          ScaledDotProductAttentionForwardPropagation)
@@ -138,7 +139,8 @@ def test_gpu_attention_forward_backward_against_oracle(wrapper, shape, causal):
 @pytest.mark.gpu
 def test_gpu_softmax_alone(wrapper):
     from sharpnet_b200.tensor import GPUTensor
-    for shape in ((1, 1), (5, 3), (2, 3, 130), (7, 1024), (3, 1025), (2, 5000)):
+    # (the last three: enough short rows for the kernel that takes several rows per warp, 4 and 2 at a time)
+    for shape in ((1, 1), (5, 3), (2, 3, 130), (7, 1024), (3, 1025), (2, 5000), (20001, 100), (3, 4001, 32), (12001, 200)):
         x = orc.uniform(shape, -4, 4, 5)
         dy = orc.uniform(shape, -1.5, 1.5, 6)
         X, DY = GPUTensor(shape, x, wrapper), GPUTensor(shape, dy, wrapper)
