@@ -260,33 +260,37 @@ __device__ __forceinline__ void attn_core(const CUtensorMap& tmQ, const CUtensor
         // (0 in masked columns, so the mask needs no second application: Prod/GPU/GpuTensor.cs:445-490)
         const float* yrow = p.s.aux + static_cast<long long>(b) * p.s.strideC + static_cast<long long>(row_base) * p.s.ldc;
         const int rows_valid = p.s.M - row_base;
+        // The lane's NC probabilities stay in registers between the two passes (both loops unrolled: NC / 32 is 1 or
+        // 2 with two warps per row, and a rolled loop would index the array dynamically).
         float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 1
-        for (int g = 0; g < NC / 32; ++g) {
-          float v[32], y[32];
-          tmem_ld_32x32(s_col + g * 32, v);
-          const int c0 = col_base + g * 32;
-          epilogue_load_block(yrow + c0, p.s.ldc, rows_valid, p.s.N - c0, stage, lane, y);
-          tmem_ld_wait();
+        float ykeep[NC];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) d4[j & 3] = fmaf(alpha * v[j], y[j], d4[j & 3]);
-        }
-        float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-        if (G == 2) {
-          const float other = row_pair_exchange(row_xch, q, grp, lane, dot);
-          dot = grp == 0 ? dot + other : other + dot;   // same order in both warps
-        }
-#pragma unroll 1
         for (int g = 0; g < NC / 32; ++g) {
           float v[32], y[32];
-          uint32_t lo[32];
           tmem_ld_32x32(s_col + g * 32, v);
           const int c0 = col_base + g * 32;
           epilogue_load_block(yrow + c0, p.s.ldc, rows_valid, p.s.N - c0, stage, lane, y);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            v[j] = y[j] * (alpha * v[j] - dot);
+            d4[j & 3] = fmaf(alpha * v[j], y[j], d4[j & 3]);
+            ykeep[g * 32 + j] = y[j];
+          }
+        }
+        float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+        if (G == 2) {
+          const float other = row_pair_exchange(row_xch, q, grp, lane, dot);
+          dot = grp == 0 ? dot + other : other + dot;   // same order in both warps
+        }
+#pragma unroll
+        for (int g = 0; g < NC / 32; ++g) {
+          float v[32];
+          uint32_t lo[32];
+          tmem_ld_32x32(s_col + g * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = ykeep[g * 32 + j] * (alpha * v[j] - dot);
             lo[j] = to_tf32_rna(v[j] - __uint_as_float(__float_as_uint(v[j]) & 0xffffe000u));
           }
           tmem_st_32x32(s_col + g * 32, reinterpret_cast<const uint32_t*>(v));
