@@ -228,6 +228,12 @@ def run_reference(args):
         return
     import torch
     from sharpnet_b200.data_parallel import mlp_step_flops
+    # every host thread this process may use: torchrun presets OMP_NUM_THREADS=1 for its children, which would time
+    # MKL on one core (the other ranks have left, the cores are free)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     step = cpu_step_sample(CPU_SAMPLE_ROWS)
     for _ in range(args.warmup):
         step()
