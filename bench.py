@@ -770,6 +770,8 @@ def run_ours(args):
     rows = r1 - r0
     weights = [orc.glorot_uniform((DIMS[i + 1], DIMS[i]), 14 + i) for i in range(3)]
     stack = DenseStack(w, rows, DIMS, MLP_ACTS, weights)
+    # the first layer's weight gradient in row panels, each reduced while the next is computed (N > 1 only)
+    stack.dw_row_panels = int(os.environ.get("SNB200_DW_PANELS", "1")) if world > 1 else 1
     # synthetic inputs of the named shape, generated on the host and pinned for the e2e leg
     g = torch.Generator().manual_seed(17 + rank)
     x_host = torch.randn(rows, DIMS[0], generator=g).pin_memory()

@@ -185,6 +185,14 @@ int snb200_dense_fwd(snb200_handle_t handle, int w_layout, int M, int K, int N, 
 int snb200_dense_bwd(snb200_handle_t handle, int w_layout, int M, int K, int N, const float* x, const float* W,
                      const float* dy, int act, const float* y, const float* z, float dW_multiplier,
                      float* dz_scratch, float* dx, float* dW, float* db);
+/* Rows [row0, row0 + rows) of the same weight gradient (in the layout of W: rows are output features for
+ * SNB200_W_OUT_IN, input features for SNB200_W_IN_OUT) from the layer's input x [M x K] and dz [M x N], the
+ * gradient with respect to the pre-activation that snb200_dense_bwd leaves in dz_scratch (dy itself for an identity
+ * layer): the product of Linear.cs:158 restricted to a panel of its result.  For hosts that sum gradients across
+ * replicas (Prod/Networks/NetworkMultiGPUSupport.cs:161-173): the reduction of one panel runs while the next is
+ * computed.  row0 must be a multiple of 4 for the tensor-core path. */
+int snb200_dense_bwd_weight_rows(snb200_handle_t handle, int w_layout, int M, int K, int N, const float* x,
+                                 const float* dz, float dW_multiplier, int row0, int rows, float* dW);
 
 /* ---- loss gradient, alone and fused into the last Dense layer's backward ------------------------
  * dy = scale * (yPredicted - yExpected), [rows x cols].  Replaces

@@ -63,6 +63,7 @@ SIGNATURES = {
     "snb200_batched_gemm": (_I, [_H, _I, _I, _I, _I, _L, _I, _I, _L, _L, _I, _F, _P, _P, _F, _P]),
     "snb200_dense_fwd": (_I, [_H, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P]),
     "snb200_dense_bwd": (_I, [_H, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P]),
+    "snb200_dense_bwd_weight_rows": (_I, [_H, _I, _I, _I, _I, _P, _P, _F, _I, _I, _P]),
     "snb200_loss_gradient": (_I, [_H, _I, _I, _I, _P, _P, _P]),
     "snb200_dense_bwd_from_loss": (_I, [_H, _I, _I, _I, _I, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P]),
     "snb200_bias_add": (_I, [_H, _I, _I, _P, _P]),

@@ -1322,6 +1322,35 @@ static int dense_bwd_gemms(snb200_handle_t h, int w_layout, int M, int K, int N,
   return 0;
 }
 
+// Rows [row0, row0 + rows) of the weight gradient, in the layout of W, from the layer's input and dz: the product
+// dense_bwd_gemms runs for dW, restricted to a panel of its result.  A host that sums gradients across replicas
+// cuts the last large weight gradient of a backward pass into panels and starts the reduction of each panel while
+// the next one is computed, so that only the last panel's reduction has nothing to hide behind.
+extern "C" int snb200_dense_bwd_weight_rows(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x,
+                                            const float* dz, float dW_multiplier, int row0, int rows, float* dW) {
+  int st = enter(h);
+  if (st) return st;
+  if (M < 0 || K < 0 || N < 0 || row0 < 0 || rows < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative dimension");
+  if (w_layout != SNB200_W_OUT_IN && w_layout != SNB200_W_IN_OUT)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "unknown weight layout %d", w_layout);
+  const int w_rows = w_layout == SNB200_W_OUT_IN ? N : K, w_cols = w_layout == SNB200_W_OUT_IN ? K : N;
+  if (row0 + static_cast<long long>(rows) > w_rows)
+    return fail(h, SNB200_STATUS_INVALID_VALUE, "rows %d .. %lld of a weight matrix of %d rows", row0,
+                row0 + static_cast<long long>(rows), w_rows);
+  if (rows == 0 || w_cols == 0) return 0;
+  st = check_ptrs(h, x, dz, dW);
+  if (st) return st;
+  GemmProblem g;
+  memset(&g, 0, sizeof(g));
+  g.batch = 1; g.act = ACT_IDENTITY; g.beta = 0.0f;
+  g.M = rows; g.N = w_cols; g.K = M;
+  g.transA = 1; g.transB = 0;
+  if (w_layout == SNB200_W_OUT_IN) { g.A = dz + row0; g.lda = N; g.B = x; g.ldb = K; }    // dz[:, row0 ..]^T * x
+  else                             { g.A = x + row0; g.lda = K; g.B = dz; g.ldb = N; }    // x[:, row0 ..]^T * dz
+  g.C = dW + static_cast<long long>(row0) * w_cols; g.ldc = w_cols; g.alpha = dW_multiplier;
+  return run_gemm(h, g);
+}
+
 extern "C" int snb200_loss_gradient(snb200_handle_t h, int loss, int rows, int cols, const float* yExpected,
                                     const float* yPredicted, float* dy) {
   int st = enter(h);

@@ -67,6 +67,9 @@ class DenseStack:
         # set by HostStaging when the input arrives as row panels: the first layer then runs panel by panel, each
         # product waiting only for its own rows, and the upstream gradient is waited for where the backward pass starts
         self.input_panels = None        # [(row0, row1), ...]
+        # > 1: the weight-gradient product of the first layer -- the last large gradient of a backward pass -- is
+        # cut into that many row panels, and `after_gradient_rows` (the reduction of one panel) runs behind each
+        self.dw_row_panels = 1
         self.before_panel = None        # callable(k)
         self.before_backward = None     # callable()
 
@@ -104,7 +107,21 @@ class DenseStack:
             self.w.set_tuning(_capi.TUNE_SM_RESERVE, 0)
             self.reserve_pending = False
 
-    def backward(self, after_gradients=None, after_layer=None, defer_smallest=False):
+    def _bwd_weight_panels(self, dz, after_gradient_rows):
+        """dW of layer 0 as ``dw_row_panels`` products over row panels of the result, each followed by its hook."""
+        lib, h = self.w.lib, self.w.handle
+        rows_total = self.W[0].Shape[0]
+        per = -(-rows_total // self.dw_row_panels)
+        per = -(-per // 256) * 256                      # whole tile rows of the CTA-pair kernel
+        r0 = 0
+        while r0 < rows_total:
+            rows = min(per, rows_total - r0)
+            check(h, lib.snb200_dense_bwd_weight_rows(h, self.layout, self.batch, self.dims[0], self.dims[1], self.x.Pointer,
+                                                      dz.Pointer, 1.0, r0, rows, self.dW[0].Pointer))
+            after_gradient_rows(0, r0, rows, r0 + rows >= rows_total)
+            r0 += rows
+
+    def backward(self, after_gradients=None, after_layer=None, defer_smallest=False, after_gradient_rows=None):
         """Backward through every layer, last to first.
 
         Per layer the two products are queued as two calls: first the activation gradient with the bias
@@ -132,6 +149,9 @@ class DenseStack:
             dx = None if i == 0 else self.dx[i]
             if i == deferred:
                 self._bwd(i, grad, act, self.dz[i], None, None, self.db[i])     # dz and db now, dW at the end
+            elif i == 0 and self.dw_row_panels > 1 and after_gradient_rows is not None:
+                self._bwd(i, grad, act, self.dz[i], None, None, self.db[i])     # dz and db, then dW panel by panel
+                self._bwd_weight_panels(dz, after_gradient_rows)
             else:
                 self._bwd(i, grad, act, self.dz[i], None, self.dW[i], self.db[i])
                 if after_gradients is not None:
@@ -207,6 +227,19 @@ class GradientAllReduce:
         if self.COLLECTIVE_CTAS > 0 and self._worth_reserving(stack, i):
             stack.w.set_tuning(_capi.TUNE_SM_RESERVE, self.COLLECTIVE_CTAS)
             stack.reserve_pending = True
+
+    def reduce_rows(self, stack, i, row0, rows, last, compute_stream):
+        """The same for rows [row0, row0 + rows) of layer ``i``'s weight gradient; the bias gradient travels with the
+        last panel."""
+        import ctypes
+        ev = self.torch.cuda.Event()
+        ev.record(compute_stream)
+        self.stream.wait_event(ev)
+        lib, h = self.comm_wrapper.lib, self.comm_wrapper.handle
+        width = stack.dW[i].Count // stack.dW[i].Shape[0]
+        bufs = (ctypes.c_void_p * 2)(stack.dW[i].Pointer.value + 4 * row0 * width, stack.db[i].Pointer)
+        counts = (ctypes.c_longlong * 2)(rows * width, stack.db[i].Count)
+        check(h, lib.snb200_allreduce_sum_group(h, 2 if last else 1, bufs, counts))
 
     def _worth_reserving(self, stack, i):
         """Rough durations: the all-reduce of layer ``i`` at ~350 GB/s of bus bandwidth against the product queued
@@ -392,7 +425,8 @@ def training_step(stack, reducer=None, compute_stream=None, update=None, defer_s
         return
     stack.backward(after_gradients=lambda i: reducer.reduce_layer(stack, i, compute_stream),
                    after_layer=None if update is None else (lambda i: reducer.update_layer(stack, i, compute_stream, update)),
-                   defer_smallest=defer_smallest)
+                   defer_smallest=defer_smallest,
+                   after_gradient_rows=lambda i, r0, n, last: reducer.reduce_rows(stack, i, r0, n, last, compute_stream))
     reducer.join(compute_stream)
 
 

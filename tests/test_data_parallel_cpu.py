@@ -96,6 +96,10 @@ class _FakeLib:
         self.calls.append(("bwd", dW, dx, db, act))
         return 0
 
+    def snb200_dense_bwd_weight_rows(self, h, layout, M, K, N, x, dz, mult, row0, rows, dW):
+        self.calls.append(("dw_rows", dW, None, None, (row0, rows)))
+        return 0
+
 
 class _FakeWrapper:
     def __init__(self):
@@ -121,6 +125,9 @@ def _fake_stack(dims, acts):
     s.dy = _FakeTensor(8 * dims[-1], "dy")
     s.reserve_pending = False
     s.input_panels = s.before_panel = s.before_backward = None
+    s.dw_row_panels = 1
+    for t, i in zip(s.W, range(n)):
+        t.Shape = [dims[i + 1], dims[i]]
     return s
 
 
@@ -143,6 +150,26 @@ def test_backward_queues_gradients_before_dx_and_the_smallest_gradient_last():
     stack2.backward(after_gradients=order.append)
     assert order == [1, 0]
     assert [(c[1], c[2]) for c in stack2.w.lib.calls] == [("dW1", None), (None, "dx1"), ("dW0", None)]
+
+
+def test_last_large_weight_gradient_goes_out_in_row_panels():
+    # layer 0's dW as two row panels, each followed by its reduction; the smallest layer's dW still comes last
+    stack = _fake_stack((4096, 4096, 4096, 1000), (1, 1, 5))
+    stack.dw_row_panels = 2
+    events = []
+    stack.backward(after_gradients=lambda i: events.append(("grads", i, len(stack.w.lib.calls))),
+                   defer_smallest=True,
+                   after_gradient_rows=lambda i, r0, n, last: events.append(("rows", i, r0, n, last, len(stack.w.lib.calls))))
+    calls = stack.w.lib.calls
+    assert [c[0] for c in calls] == ["bwd", "bwd", "bwd", "bwd", "bwd", "dw_rows", "dw_rows", "bwd"]
+    assert calls[4][1] is None and calls[4][3] == "db0"              # dz and db of layer 0 without its dW
+    assert [c[4] for c in calls[5:7]] == [(0, 2048), (2048, 2048)] and calls[7][1] == "dW2"
+    assert events == [("grads", 1, 3), ("rows", 0, 0, 2048, False, 6), ("rows", 0, 2048, 2048, True, 7), ("grads", 2, 8)]
+    # without a row hook the layer runs as one product
+    stack = _fake_stack((64, 32, 16), (1, 5))
+    stack.dw_row_panels = 2
+    stack.backward(after_gradients=lambda i: None)
+    assert [c[0] for c in stack.w.lib.calls] == ["bwd", "bwd", "bwd"]
 
 
 def test_sm_reservation_covers_exactly_one_product_after_each_reduction():

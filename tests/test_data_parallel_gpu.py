@@ -74,9 +74,10 @@ def _check_gradients(stack, grads, gmax, a, batch):
         assert e <= TOL, (i, "db", e)
 
 
-@pytest.mark.parametrize("batch,dims,defer", [(384, (256, 192, 128, 40), False), (384, (256, 192, 128, 40), True),
-                                              (4096, (4096, 4096, 4096, 1000), True)])
-def test_training_step_and_update_on_one_gpu(wrapper, batch, dims, defer):
+@pytest.mark.parametrize("batch,dims,defer,dw_panels", [(384, (256, 192, 128, 40), False, 1), (384, (256, 192, 128, 40), True, 1),
+                                                        (4096, (4096, 4096, 4096, 1000), True, 1),
+                                                        (384, (256, 600, 128, 40), True, 2), (4096, (4096, 4096, 4096, 1000), True, 4)])
+def test_training_step_and_update_on_one_gpu(wrapper, batch, dims, defer, dw_panels):
     """DenseStack + training_step + SgdUpdate against the oracle: activations, every dW / db, and the weights after
     the update; the second shape is benchmark config 5's network on 4096 of its 65536 rows."""
     from sharpnet_b200 import ACT_IDENTITY, ACT_RELU, MATH_3XTF32
@@ -88,7 +89,18 @@ def test_training_step_and_update_on_one_gpu(wrapper, batch, dims, defer):
     _load(stack, x, dy, bs)
     oacts = (orc.ACT_RELU, orc.ACT_RELU, orc.ACT_IDENTITY)
     a = _oracle_forward(x, Ws, bs, oacts)
-    if defer:
+    if defer and dw_panels > 1:
+        # layer 0's weight gradient as row panels (snb200_dense_bwd_weight_rows), a hook behind each
+        stack.forward()
+        stack.dw_row_panels = dw_panels
+        order = []
+        stack.backward(after_gradients=order.append, defer_smallest=True,
+                       after_gradient_rows=lambda i, r0, n, last: order.append((i, r0, n, last)))
+        rows = dims[1]
+        per = -(-(-(-rows // dw_panels)) // 256) * 256
+        want = [(0, r0, min(per, rows - r0), r0 + per >= rows) for r0 in range(0, rows, per)]
+        assert order == [1] + want + [2], order
+    elif defer:
         stack.forward()
         order = []
         stack.backward(after_gradients=order.append, defer_smallest=True)
