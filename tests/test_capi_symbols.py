@@ -27,6 +27,15 @@ def test_binding_table_matches_header(built_library):
     assert lib.snb200_get_version() >= 100
 
 
+def test_reference_side_binding_names_every_entry_point():
+    # the P/Invoke class a SharpNet maintainer would add declares every symbol of the header
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    missing = [n for n in _declared_symbols() if ("extern cublasStatus_t " + n + "(") not in text
+               and ("extern int " + n + "(") not in text and ("extern long " + n + "(") not in text
+               and ("extern IntPtr " + n + "(") not in text]
+    assert not missing, missing
+
+
 def test_create_fails_loudly_without_a_device(built_library):
     import torch
     if torch.cuda.is_available():
