@@ -484,3 +484,31 @@ def test_config_5_square_16384_on_row_samples(wrapper, mode, tol):
         assert e64 <= tol and emkl <= tol, (r0, e64, emkl)
     del A, B, C
     torch.cuda.empty_cache()
+
+
+def test_seeded_sweep_over_shapes_and_plans(wrapper):
+    """A seeded draw of shapes, transposes, alpha / beta, batches, math modes and forced kernel plans (tile width,
+    CTA pair on or off, K cut inside clusters of 2 or 4 or never): whatever kernel the library ends up with, the
+    result stays within the mode's bound of the float64 product."""
+    rng = np.random.default_rng(2026)
+    kernels = set()
+    try:
+        for it in range(160):
+            mode, tol = ((MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32))[it % 5 == 4]
+            M = int(rng.choice([1, 5, 17, 32, 33, 64, 100, 128, 129, 200, 256, 300, 513, 700]))
+            N = int(rng.choice([8, 12, 32, 40, 64, 100, 128, 132, 256, 260, 512, 640]))
+            K = int(rng.choice([64, 100, 128, 256, 300, 512, 516, 1000, 1024, 2052, 3000]))
+            tA, tB = bool(rng.integers(2)), bool(rng.integers(2))
+            beta, alpha = float(rng.choice([0.0, 1.0, -0.5])), float(rng.choice([1.0, 0.5]))
+            batch = None if rng.integers(4) else int(rng.choice([2, 5]))
+            wrapper.set_math_mode(mode)
+            wrapper.set_tuning(TUNE_CLUSTER, int(rng.choice([0, 0, 2, 4, 1])))
+            wrapper.set_tuning(TUNE_FORCE_BN, int(rng.choice([0, 0, 32, 64, 128, 256])))
+            wrapper.set_tuning(TUNE_PAIR, int(rng.choice([0, 0, 2])))
+            _check(wrapper, M, N, K, tA, tB, alpha, beta, 1000 + it, tol, batch=batch)
+            kernels.add(wrapper.last_kernel().split("_p")[0])
+    finally:
+        wrapper.set_tuning(TUNE_CLUSTER, 0)
+    # the draw reaches every family of plans
+    for family in ("clusterk2", "clusterk4", "swapAB", "splitk", "swload", "realigned", "umma2_", "simt"):
+        assert any(family in k for k in kernels), (family, sorted(kernels))
