@@ -137,6 +137,49 @@ def test_gpu_attention_forward_backward_against_oracle(wrapper, shape, causal):
 
 
 @pytest.mark.gpu
+def test_gpu_attention_seeded_sweep(wrapper):
+    """A seeded draw of batch, query / key lengths, head widths, scaling and masking: every tile shape of the fused
+    kernels (and the paths beside them) against the float64 oracle, forward and backward."""
+    from sharpnet_b200.attention import (ScaledDotProductAttentionBackwardPropagation,
+                                         ScaledDotProductAttentionForwardPropagation)
+    from sharpnet_b200.tensor import GPUTensor
+    rng = np.random.default_rng(7)
+    kernels = set()
+    for it in range(90):
+        B = int(rng.choice([1, 2, 3, 7, 12]))
+        Tq = int(rng.choice([16, 17, 40, 64, 100, 128, 129, 200, 300]))
+        Tk = int(rng.choice([8, 12, 32, 36, 60, 64, 72, 100, 128, 132, 200]))
+        E = int(rng.choice([4, 8, 20, 32, 36, 64, 68, 100, 128, 132]))
+        causal = False
+        if rng.integers(3) == 0 and Tq <= 128:
+            Tk, causal = Tq, bool(rng.integers(2))
+        use_scale = bool(rng.integers(2))
+        g = np.random.default_rng(100 + it)
+        Q, K, V = (g.uniform(-1.5, 1.5, s).astype(np.float32) for s in ((B, Tq, E), (B, Tk, E), (B, Tk, E)))
+        dy = g.uniform(-1.5, 1.5, (B, Tq, E)).astype(np.float32)
+        Qg, Kg, Vg, DY = (GPUTensor(a.shape, a, wrapper) for a in (Q, K, V, dy))
+        y = GPUTensor((B, Tq, E), None, wrapper)
+        W = ScaledDotProductAttentionForwardPropagation(Qg, Kg, Vg, y, True, None, use_scale, causal)
+        kernels.add(wrapper.last_kernel())
+        wrapper.check_device_status()
+        w64, y64 = orc.sdpa_forward(Q, K, V, use_scale, causal, f64=True)
+        wt = W.ContentAsFloatArray()
+        slack = 4.0 * (1.0 if use_scale else np.sqrt(E))     # unscaled scores are sqrt(E) times larger
+        case = (it, B, Tq, Tk, E, causal, use_scale)
+        assert np.abs(wt - w64).max() <= (1e-5 * 2.25 + 1e-6) * slack, case
+        assert np.abs(y.ContentAsFloatArray() - y64).max() <= (1e-5 * np.sqrt(Tk) * 1.5 + 1e-5) * slack, case
+        dQ, dK, dV = (GPUTensor(s, None, wrapper) for s in ((B, Tq, E), (B, Tk, E), (B, Tk, E)))
+        ScaledDotProductAttentionBackwardPropagation(dQ, dK, dV, Qg, Kg, Vg, DY, W, use_scale)
+        kernels.add(wrapper.last_kernel())
+        wrapper.check_device_status()
+        dQ64, dK64, dV64 = orc.sdpa_backward(Q, K, V, dy, wt, use_scale)
+        assert np.abs(dV.ContentAsFloatArray() - dV64).max() <= 1e-5 * np.sqrt(Tq) * 1.5 + 1e-5, case
+        assert np.abs(dQ.ContentAsFloatArray() - dQ64).max() <= 5e-5 * slack, case
+        assert np.abs(dK.ContentAsFloatArray() - dK64).max() <= 5e-5 * slack, case
+    assert sum(k.startswith("attention_fwd") for k in kernels) >= 6 and any(k.endswith("_grouped") for k in kernels), kernels
+
+
+@pytest.mark.gpu
 def test_gpu_softmax_alone(wrapper):
     from sharpnet_b200.tensor import GPUTensor
     # (the last three: enough short rows for the kernel that takes several rows per warp, 4 and 2 at a time)
