@@ -364,3 +364,24 @@ def test_dense_backward_rejects_softmax(wrapper):
     t = GPUTensor((4, 4), None, wrapper)
     with pytest.raises(SharpNetB200Error):
         FusedDenseBackward(t, t, None, t, t, t, ACT_SOFTMAX, y=t)
+
+
+def test_dense_seeded_sweep(wrapper):
+    """A seeded draw of batch sizes (down to single rows, which run with swapped operands), widths, activations, weight
+    layouts, bias on / off, dx on / off, math modes and K cuts inside clusters: forward and backward against the
+    oracle, whatever kernels the shapes end up on."""
+    rng = np.random.default_rng(11)
+    try:
+        for it in range(90):
+            M = int(rng.choice([1, 8, 17, 32, 64, 100, 300, 512, 1024]))
+            K = int(rng.choice([64, 260, 1024, 2048, 516]))
+            N = int(rng.choice([8, 40, 128, 260, 512, 1000]))
+            act, layout = int(rng.choice(ACTS)), int(rng.choice([W_IN_OUT, W_OUT_IN]))
+            bias, need_dx = bool(rng.integers(4)), bool(rng.integers(4))
+            wrapper.set_tuning(TUNE_CLUSTER, int(rng.choice([0, 0, 1, 2, 4])))
+            mode, tol = ((MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32))[it % 6 == 5]
+            wrapper.set_math_mode(mode)
+            _dense_case(wrapper, M, K, N, act, layout, 5000 + it, tol, with_bias=bias, need_dx=need_dx,
+                        mult=float(rng.choice([1.0, 0.25])))
+    finally:
+        wrapper.set_tuning(TUNE_CLUSTER, 0)
