@@ -56,8 +56,12 @@ enum {
   SNB200_ACT_SIGMOID = 0,
   SNB200_ACT_RELU = 1,
   SNB200_ACT_TANH = 2,
+  /* x >= 0 ? x : alpha * (exp(x) - 1), alpha from snb200_set_activation_parameter (the layer's activationParameter) */
+  SNB200_ACT_ELU = 4,
   SNB200_ACT_IDENTITY = 5,
   SNB200_ACT_SWISH = 6,
+  /* x >= 0 ? x : alpha * x, alpha from snb200_set_activation_parameter */
+  SNB200_ACT_LEAKY_RELU = 1002,
   /* snb200_dense_fwd only: y = softmax over every row of x * op(W) + bias, a Linear layer followed by an
    * ActivationLayer with CUDNN_ACTIVATION_SOFTMAX (Prod/GPU/GpuTensor.cs:411-413 -> cudnnSoftmaxForward): the output
    * layer of every classification network.  Its gradient enters through snb200_dense_bwd_from_loss. */
@@ -85,6 +89,10 @@ int snb200_destroy(snb200_handle_t handle);
  * all cuBLAS/cuDNN work: it never calls cublasSetStream). */
 int snb200_set_stream(snb200_handle_t handle, void* cuda_stream);
 int snb200_set_math_mode(snb200_handle_t handle, int math_mode);
+/* The coefficient of the parametric activations (ELU, LeakyRelu) for every call on this handle that follows: what
+ * ActivationLayer hands to ActivationForward / ActivationBackward as activationParameter
+ * (Prod/Layers/ActivationLayer.cs:21,36,66; Prod/CPU/CpuTensorActivationFunctions.cs:210-231).  0 by default. */
+int snb200_set_activation_parameter(snb200_handle_t handle, float alpha);
 int snb200_get_math_mode(snb200_handle_t handle, int* math_mode);
 /* Text of the last error recorded on this handle (never NULL; empty when none). */
 const char* snb200_last_error_string(snb200_handle_t handle);

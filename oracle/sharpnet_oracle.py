@@ -25,6 +25,7 @@ import torch
 
 # cudnnActivationMode_t values (Prod/GPU/CudnnWrapper.cs:267-281)
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
+ACT_ELU, ACT_LEAKY_RELU = 4, 1002   # CUDNN_ACTIVATION_ELU / _LEAKY_RELU (Prod/GPU/CudnnWrapper.cs:273,277): take an alpha
 ACT_SOFTMAX = 1000          # CUDNN_ACTIVATION_SOFTMAX (Prod/GPU/CudnnWrapper.cs:276): softmax over every row
 W_OUT_IN, W_IN_OUT = 0, 1
 LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
@@ -118,11 +119,16 @@ def update_adding_alpha_x(y, alpha, x):
     return y
 
 
-def activation_forward(act, x):
+def activation_forward(act, x, alpha=0.0):
     """Element-wise activations with the precision SharpNet's CPU code uses
     (Prod/CPU/CpuTensorActivationFunctions.cs): Swish and Sigmoid go through double
-    (:152-156, Prod/Utils.cs:888-891), Tanh is MathF.Tanh (:184-189), Relu is max(0, x) (:198-201)."""
+    (:152-156, Prod/Utils.cs:888-891), Tanh is MathF.Tanh (:184-189), Relu is max(0, x) (:198-201),
+    LeakyRelu is x or (float)alpha * x (:210-213), Elu is x or (float)(alpha * (exp(x) - 1)) through double (:223-226)."""
     x = np.asarray(x, dtype=np.float32)
+    if act == ACT_LEAKY_RELU:
+        return np.where(x >= 0, x, np.float32(alpha) * x).astype(np.float32)
+    if act == ACT_ELU:
+        return np.where(x >= 0, x, (float(alpha) * (np.exp(x.astype(np.float64)) - 1.0)).astype(np.float32)).astype(np.float32)
     if act == ACT_RELU:
         return np.maximum(x, np.float32(0))
     if act == ACT_SWISH:
@@ -140,12 +146,16 @@ def activation_forward(act, x):
     raise ValueError(f"activation {act} is not on the path")
 
 
-def activation_backward(act, dy, x, y):
+def activation_backward(act, dy, x, y, alpha=0.0):
     """dx from dy, the activation input x and output y, all in fp32
     (Prod/CPU/CpuTensorActivationFunctions.cs:158-167 Swish, :190-194 Tanh, :202-206 Relu,
-    :240-244 Sigmoid)."""
+    :240-244 Sigmoid, :214-219 LeakyRelu from y, :227-231 Elu from x and y)."""
     dy = np.asarray(dy, dtype=np.float32)
     one = np.float32(1)
+    if act == ACT_LEAKY_RELU:
+        return np.where(np.asarray(y) >= 0, dy, np.float32(alpha) * dy).astype(np.float32)
+    if act == ACT_ELU:
+        return np.where(np.asarray(x) >= 0, dy, dy * (np.asarray(y, dtype=np.float32) + np.float32(alpha))).astype(np.float32)
     if act == ACT_RELU:
         return np.where(y > 0, dy, np.float32(0)).astype(np.float32)
     if act == ACT_SWISH:
@@ -333,7 +343,7 @@ def update_adam_optimizer(W, learning_rate, beta1, beta2, epsilon, weight_decay,
 # --------------------------------------------------------------------------------------------
 # Dense layer
 # --------------------------------------------------------------------------------------------
-def dense_forward(x, W, bias, act=ACT_IDENTITY, w_layout=W_OUT_IN, f64=False):
+def dense_forward(x, W, bias, act=ACT_IDENTITY, w_layout=W_OUT_IN, f64=False, alpha=0.0):
     """Returns (z, y): z = x * op(W) + bias, y = act(z).
 
     OUT_IN follows Linear.DenseForwardPropagation (Prod/Layers/Linear.cs:125-132: Dot(x, false,
@@ -347,16 +357,16 @@ def dense_forward(x, W, bias, act=ACT_IDENTITY, w_layout=W_OUT_IN, f64=False):
         z = dot_f64(x.ravel(), M, K, False, W.ravel(), W.shape[0], W.shape[1], tB, np.zeros(M * N), 1.0, 0.0)
         if bias is not None:
             z = z + np.asarray(bias, dtype=np.float64).reshape(1, -1)
-        return z, _act_f64(act, z)
+        return z, _act_f64(act, z, alpha)
     z = np.zeros((M, N), dtype=np.float32)
     dot_mkl(x.ravel(), M, K, False, W.ravel(), W.shape[0], W.shape[1], tB, z.reshape(-1), 1.0, 0.0)
     if bias is not None:
         broadcast_add_vector_to_output(bias, z)
-    return z, activation_forward(act, z)
+    return z, activation_forward(act, z, alpha)
 
 
 def dense_backward(x, W, dy, act=ACT_IDENTITY, y=None, z=None, multiplier=1.0, w_layout=W_OUT_IN, need_dx=True,
-                   f64=False):
+                   f64=False, alpha=0.0):
     """Returns (dz, dW, db, dx).
 
     dz = ActivationBackward(dy, z, y) (Prod/Layers/ActivationLayer.cs:39-69), then
@@ -366,7 +376,7 @@ def dense_backward(x, W, dy, act=ACT_IDENTITY, y=None, z=None, multiplier=1.0, w
     M, K = x.shape
     N = dy.shape[1]
     if f64:
-        dz = _act_bwd_f64(act, dy, z, y)
+        dz = _act_bwd_f64(act, dy, z, y, alpha)
         xd, Wd = x.astype(np.float64), W.astype(np.float64)
         if w_layout == W_OUT_IN:
             dW = multiplier * (dz.T @ xd)
@@ -375,7 +385,7 @@ def dense_backward(x, W, dy, act=ACT_IDENTITY, y=None, z=None, multiplier=1.0, w
             dW = multiplier * (xd.T @ dz)
             dx = dz @ Wd.T if need_dx else None
         return dz, dW, dz.sum(axis=0), dx
-    dz = activation_backward(act, dy, z, y)
+    dz = activation_backward(act, dy, z, y, alpha)
     if w_layout == W_OUT_IN:
         dW = np.zeros((N, K), dtype=np.float32)
         dot_mkl(dz.ravel(), M, N, True, x.ravel(), M, K, False, dW.reshape(-1), multiplier, 0.0)
@@ -393,7 +403,11 @@ def dense_backward(x, W, dy, act=ACT_IDENTITY, y=None, z=None, multiplier=1.0, w
     return dz, dW, db, dx
 
 
-def _act_f64(act, z):
+def _act_f64(act, z, alpha=0.0):
+    if act == ACT_LEAKY_RELU:
+        return np.where(z >= 0, z, alpha * z)
+    if act == ACT_ELU:
+        return np.where(z >= 0, z, alpha * (np.exp(np.minimum(z, 0.0)) - 1.0))
     if act == ACT_RELU:
         return np.maximum(z, 0.0)
     if act == ACT_SWISH:
@@ -408,8 +422,12 @@ def _act_f64(act, z):
     return z.copy()
 
 
-def _act_bwd_f64(act, dy, z, y):
+def _act_bwd_f64(act, dy, z, y, alpha=0.0):
     dy = np.asarray(dy, dtype=np.float64)
+    if act == ACT_LEAKY_RELU:
+        return np.where(np.asarray(y) >= 0, dy, alpha * dy)
+    if act == ACT_ELU:
+        return np.where(np.asarray(z) >= 0, dy, dy * (np.asarray(y, dtype=np.float64) + alpha))
     if act == ACT_RELU:
         return np.where(np.asarray(y) > 0, dy, 0.0)
     if act == ACT_SWISH:

@@ -22,7 +22,9 @@ __device__ __forceinline__ void pdl_prologue() {
 }
 
 // Values of cudnnActivationMode_t (Prod/GPU/CudnnWrapper.cs:267-281).
-enum Act : int { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_IDENTITY = 5, ACT_SWISH = 6 };
+// ELU and LEAKY_RELU take a coefficient (the layer's activationParameter); it travels beside the code as act_alpha.
+enum Act : int { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_ELU = 4, ACT_IDENTITY = 5, ACT_SWISH = 6, ACT_LEAKY_RELU = 1002 };
+__host__ __device__ __forceinline__ bool act_needs_input(int act) { return act == ACT_SWISH || act == ACT_ELU; }   // ActivationLayer.cs:73
 // Internal selector of the fused column-sum pass: dz = scale * (yPredicted - yExpected), the gradient of
 // the BinaryCrossentropy / CategoricalCrossentropy / Mse losses (Prod/Data/Tensor.cs:1379-1395,
 // Prod/CPU/CpuTensor.cs:2458-2475).
@@ -59,6 +61,7 @@ struct GemmProblem {
   const float* bias;      // [N] or nullptr: added to every row
   float* Z;               // optional copy of the value before the activation (pitch ldc, stride strideC)
   int act;                // Act
+  float act_alpha;        // coefficient of ACT_ELU / ACT_LEAKY_RELU
   // Row operation applied to alpha * op(A) * op(B) before it is stored, for products whose whole row lies in one
   // tile (N <= 128): the two softmax passes of scaled dot-product attention.
   int row_op;             // RowOp
@@ -68,10 +71,12 @@ struct GemmProblem {
 };
 enum RowOp : int { ROW_NONE = 0, ROW_SOFTMAX = 1, ROW_SOFTMAX_GRAD = 2 };
 
-__device__ __forceinline__ float act_forward(int act, float v) {
+__device__ __forceinline__ float act_forward(int act, float v, float a = 0.0f) {
   // Formulas of Prod/CPU/CpuTensorActivationFunctions.cs:152-244 and Prod/Utils.cs:888-891.
   switch (act) {
     case ACT_RELU: return fmaxf(v, 0.0f);
+    case ACT_LEAKY_RELU: return v >= 0.0f ? v : a * v;                 // :210-213
+    case ACT_ELU: return v >= 0.0f ? v : a * expm1f(v);                // :223-226 (alpha * (exp(x) - 1), in double there)
     case ACT_SWISH: return v / (1.0f + expf(-v));
     case ACT_TANH: return tanhf(v);
     case ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
@@ -81,18 +86,20 @@ __device__ __forceinline__ float act_forward(int act, float v) {
 
 // For fully unrolled epilogues: Identity and Relu inline, the transcendental activations through one
 // out-of-line copy, so that the unrolled code stays small enough for the instruction cache.
-static __device__ __noinline__ float act_forward_call(int act, float v) { return act_forward(act, v); }
-__device__ __forceinline__ float act_forward_compact(int act, float v) {
+static __device__ __noinline__ float act_forward_call(int act, float v, float a) { return act_forward(act, v, a); }
+__device__ __forceinline__ float act_forward_compact(int act, float v, float a = 0.0f) {
   if (act == ACT_IDENTITY) return v;
   if (act == ACT_RELU) return fmaxf(v, 0.0f);
-  return act_forward_call(act, v);
+  return act_forward_call(act, v, a);
 }
 
 // Gradient with respect to the pre-activation, from the upstream gradient dy, the activation
-// output y and (SWISH only) the pre-activation x.
-__device__ __forceinline__ float act_backward(int act, float dy, float x, float y) {
+// output y and (SWISH and ELU only) the pre-activation x.
+__device__ __forceinline__ float act_backward(int act, float dy, float x, float y, float a = 0.0f) {
   switch (act) {
     case ACT_RELU: return y > 0.0f ? dy : 0.0f;                       // CpuTensorActivationFunctions.cs:202-206
+    case ACT_LEAKY_RELU: return y >= 0.0f ? dy : a * dy;              // :214-219
+    case ACT_ELU: return x >= 0.0f ? dy : dy * (y + a);               // :227-231
     case ACT_SWISH: {                                                  // :158-167
       float s = (fabsf(x) < 0.0001f) ? 0.5f : y / x;
       return dy * (s + x * s * (1.0f - s));

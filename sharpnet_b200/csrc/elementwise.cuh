@@ -59,7 +59,8 @@ __device__ __forceinline__ void lane_set(float4& v, int i, float x) { if (i == 0
 __device__ __forceinline__ void lane_set(float& v, int, float x) { v = x; }
 
 template <int VEC>
-static __global__ void activation_fwd_kernel(int act, long long n, const float* __restrict__ x, float* __restrict__ y) {
+static __global__ void activation_fwd_kernel(int act, float act_alpha, long long n, const float* __restrict__ x,
+                                             float* __restrict__ y) {
   pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -69,31 +70,31 @@ static __global__ void activation_fwd_kernel(int act, long long n, const float* 
     const P xv = reinterpret_cast<const P*>(x)[i];
     P yv;
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) lane_set(yv, k, act_forward(act, lane_get(xv, k)));
+    for (int k = 0; k < VEC; ++k) lane_set(yv, k, act_forward(act, lane_get(xv, k), act_alpha));
     reinterpret_cast<P*>(y)[i] = yv;
   }
-  for (long long i = nv * VEC + tid; i < n; i += stride) y[i] = act_forward(act, x[i]);
+  for (long long i = nv * VEC + tid; i < n; i += stride) y[i] = act_forward(act, x[i], act_alpha);
 }
 template <int VEC>
-static __global__ void activation_bwd_kernel(int act, long long n, const float* __restrict__ dy, const float* __restrict__ x,
+static __global__ void activation_bwd_kernel(int act, float act_alpha, long long n, const float* __restrict__ dy, const float* __restrict__ x,
                                              const float* __restrict__ y, float* __restrict__ dx) {
   pdl_prologue();
   typedef typename Pack<VEC>::type P;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const long long nv = n / VEC;
-  const bool need_x = (act == ACT_SWISH), need_y = (act != ACT_IDENTITY);
+  const bool need_x = act_needs_input(act), need_y = (act != ACT_IDENTITY);
   for (long long i = tid; i < nv; i += stride) {
     const P g = reinterpret_cast<const P*>(dy)[i];
     P xv = P(), yv = P(), o;
     if (need_x) xv = reinterpret_cast<const P*>(x)[i];
     if (need_y) yv = reinterpret_cast<const P*>(y)[i];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) lane_set(o, k, act_backward(act, lane_get(g, k), lane_get(xv, k), lane_get(yv, k)));
+    for (int k = 0; k < VEC; ++k) lane_set(o, k, act_backward(act, lane_get(g, k), lane_get(xv, k), lane_get(yv, k), act_alpha));
     reinterpret_cast<P*>(dx)[i] = o;
   }
   for (long long i = nv * VEC + tid; i < n; i += stride)
-    dx[i] = act_backward(act, dy[i], need_x ? x[i] : 0.0f, need_y ? y[i] : 0.0f);
+    dx[i] = act_backward(act, dy[i], need_x ? x[i] : 0.0f, need_y ? y[i] : 0.0f, act_alpha);
 }
 // y += alpha * x                                    (Prod/CPU/CpuTensor.cs:1032-1038)
 template <int VEC>
@@ -145,7 +146,7 @@ template <int VEC, bool FUSE_ACT>
 __global__ void __launch_bounds__(256)
 colsum_slab_kernel(int M, int N, int rows_per_slab, int act, const float* __restrict__ dy,
                    const float* __restrict__ y, const float* __restrict__ z, float* __restrict__ dz,
-                   float* __restrict__ out, float scale = 1.0f) {
+                   float* __restrict__ out, float scale = 1.0f, float act_alpha = 0.0f) {
   pdl_prologue();
   __shared__ float red[8][32 * VEC];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -169,18 +170,18 @@ colsum_slab_kernel(int M, int N, int rows_per_slab, int act, const float* __rest
         if (VEC == 4) {
           const float4 t = *reinterpret_cast<const float4*>(y + off);
           yv[0] = t.x; yv[1] = t.y; yv[2] = t.z; yv[3] = t.w;
-          if (act == ACT_SWISH) {
+          if (act_needs_input(act)) {
             const float4 u = *reinterpret_cast<const float4*>(z + off);
             zv[0] = u.x; zv[1] = u.y; zv[2] = u.z; zv[3] = u.w;
           }
         } else {
           yv[0] = y[off];
-          if (act == ACT_SWISH) zv[0] = z[off];
+          if (act_needs_input(act)) zv[0] = z[off];
         }
 #pragma unroll
         for (int v = 0; v < VEC; ++v)
           g[v] = (act == ACT_LOSS_DIFF) ? scale * (g[v] - yv[v])      // dy = yPredicted, y = yExpected
-                                        : act_backward(act, g[v], act == ACT_SWISH ? zv[v] : 0.0f, yv[v]);
+                                        : act_backward(act, g[v], act_needs_input(act) ? zv[v] : 0.0f, yv[v], act_alpha);
         if (VEC == 4) {
           *reinterpret_cast<float4*>(dz + off) = make_float4(g[0], g[1], g[2], g[3]);
         } else {

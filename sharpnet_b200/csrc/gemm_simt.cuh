@@ -22,6 +22,7 @@ struct SimtParams {
   const float* bias;
   float alpha, beta;
   int act;
+  float act_alpha;
   int tiles_m, tiles_n;
   OutMap omap;
 };
@@ -109,7 +110,7 @@ simt_gemm_kernel(const SimtParams p) {
       if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
       if (p.bias) o += __ldg(p.bias + col);
       if (p.Z) p.Z[off] = o;
-      p.C[off] = act_forward_compact(p.act, o);
+      p.C[off] = act_forward_compact(p.act, o, p.act_alpha);
     }
   }
 }
@@ -231,7 +232,7 @@ simt_gemm_big_kernel(const SimtParams p) {
       if (p.beta != 0.0f) o = fmaf(p.beta, p.C[off], o);
       if (p.bias) o += __ldg(p.bias + col);
       if (p.Z) p.Z[off] = o;
-      p.C[off] = act_forward_compact(p.act, o);
+      p.C[off] = act_forward_compact(p.act, o, p.act_alpha);
     }
   }
 }

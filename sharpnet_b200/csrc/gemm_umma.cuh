@@ -117,6 +117,7 @@ struct UmmaParams {
   const float* bias;
   float alpha, beta;
   int act;
+  float act_alpha;  // coefficient of ELU / LeakyRelu
   int rewrite_hi;   // 3xTF32: store the rounded hi plane back over the raw tile
   int vec_ok;       // C (and Z, bias) rows are 16-byte aligned
   int* error_word;  // set to 1 when a pipeline wait timed out
@@ -235,6 +236,7 @@ struct StoreTarget {
   const float* bias;
   float alpha, beta;
   int act, ldc, vec_ok, mapped;
+  float act_alpha;
 };
 
 template <bool HEAVY, bool MAPPED>
@@ -274,10 +276,10 @@ __device__ __forceinline__ void epilogue_store_block_vec(const UmmaParams& p, co
       o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
       if (t.Z) *reinterpret_cast<float4*>(t.Z + off) = o;
       if (HEAVY) {
-        o.x = act_forward(t.act, o.x);
-        o.y = act_forward(t.act, o.y);
-        o.z = act_forward(t.act, o.z);
-        o.w = act_forward(t.act, o.w);
+        o.x = act_forward(t.act, o.x, t.act_alpha);
+        o.y = act_forward(t.act, o.y, t.act_alpha);
+        o.z = act_forward(t.act, o.z, t.act_alpha);
+        o.w = act_forward(t.act, o.w, t.act_alpha);
       } else {
         o.x = relu ? fmaxf(o.x, 0.0f) : o.x;
         o.y = relu ? fmaxf(o.y, 0.0f) : o.y;
@@ -366,7 +368,7 @@ __device__ __forceinline__ void epilogue_store_rows(const UmmaParams& p, const S
           if (t.beta != 0.0f) o = fmaf(t.beta, t.C[off], o);
           o += bv;
           if (t.Z) t.Z[off] = o;
-          t.C[off] = act_forward(t.act, o);
+          t.C[off] = act_forward(t.act, o, t.act_alpha);
         }
       }
     }
@@ -532,7 +534,7 @@ __device__ __forceinline__ void epilogue_store_unit(const UmmaParams& p, float a
                                                     int bn, int row_base, int n0, int lane, long long c_shift = 0) {
   // one call of the store phase (its code is long: a second copy costs instruction-cache misses); the
   // partial-sum case redirects it to the workspace
-  StoreTarget t = {p.C + c_shift, p.Z, bias, alpha, beta, p.act, p.ldc, p.vec_ok, p.omap.on};
+  StoreTarget t = {p.C + c_shift, p.Z, bias, alpha, beta, p.act, p.ldc, p.vec_ok, p.omap.on, p.act_alpha};
   long long off = static_cast<long long>(b) * p.strideC;
   if (split >= 0 && p.partial != nullptr) {
     t.C = p.partial;
@@ -572,7 +574,7 @@ __device__ __forceinline__ void epilogue_store_transposed(const UmmaParams& p, f
     if (beta != 0.0f) o = fmaf(beta, p.C[off], o);
     o += bv;
     if (p.Z) p.Z[off] = o;
-    p.C[off] = act_forward_compact(p.act, o);
+    p.C[off] = act_forward_compact(p.act, o, p.act_alpha);
   }
 }
 
@@ -1128,6 +1130,7 @@ struct SplitKReduceParams {
   long long strideC;
   float alpha, beta;
   int act;
+  float act_alpha;
   OutMap omap;
 };
 static __global__ void splitk_reduce_kernel(const SplitKReduceParams p) {
@@ -1148,7 +1151,7 @@ static __global__ void splitk_reduce_kernel(const SplitKReduceParams p) {
     if (p.beta != 0.0f) v = fmaf(p.beta, p.C[off], v);
     if (p.bias) v += __ldg(p.bias + n);
     if (p.Z) p.Z[off] = v;
-    p.C[off] = act_forward(p.act, v);
+    p.C[off] = act_forward(p.act, v, p.act_alpha);
   }
 }
 
@@ -1180,7 +1183,7 @@ static __global__ void __launch_bounds__(256) splitk_reduce_transposed_kernel(co
       if (p.beta != 0.0f) v = fmaf(p.beta, p.C[off], v);
       if (p.bias) v += __ldg(p.bias + n);
       if (p.Z) p.Z[off] = v;
-      p.C[off] = act_forward(p.act, v);
+      p.C[off] = act_forward(p.act, v, p.act_alpha);
     }
   }
 }
@@ -1202,6 +1205,7 @@ struct TailReduceParams {
   long long strideC;
   float alpha, beta;
   int act;
+  float act_alpha;
   int vec_ok;
   OutMap omap;
 };
@@ -1240,7 +1244,7 @@ static __global__ void __launch_bounds__(256) tail_reduce_kernel(const TailReduc
       }
       if (p.Z) *reinterpret_cast<float4*>(p.Z + off) = make_float4(o[0], o[1], o[2], o[3]);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = act_forward(p.act, o[e]);
+      for (int e = 0; e < 4; ++e) o[e] = act_forward(p.act, o[e], p.act_alpha);
       *reinterpret_cast<float4*>(p.C + off) = make_float4(o[0], o[1], o[2], o[3]);
     } else {
       // a mapped result whose inner run d is not a multiple of 4: the four columns may lie in different runs
@@ -1250,7 +1254,7 @@ static __global__ void __launch_bounds__(256) tail_reduce_kernel(const TailReduc
         if (p.beta != 0.0f) v = fmaf(p.beta, p.C[oe], v);
         if (p.bias) v += __ldg(p.bias + col + e);
         if (p.Z) p.Z[oe] = v;
-        p.C[oe] = act_forward(p.act, v);
+        p.C[oe] = act_forward(p.act, v, p.act_alpha);
       }
     }
   }

@@ -27,6 +27,7 @@ struct snb200_context {
   cudaStream_t stream;
   int math_mode;
   int tune[TUNE_COUNT];
+  float act_alpha;          // coefficient of ELU / LeakyRelu for the calls that follow (snb200_set_activation_parameter)
   float* workspace;            // partial sums of the column reductions
   size_t workspace_floats;
   int* error_word;             // device word set by a kernel whose pipeline wait timed out
@@ -181,6 +182,11 @@ extern "C" int snb200_set_tuning(snb200_handle_t h, int key, int value) {
   if (key == TUNE_CLUSTER && value != 0 && value != 1 && value != 2 && value != 4)
     return fail(h, SNB200_STATUS_INVALID_VALUE, "cluster size %d: 0 (automatic), 1 (never), 2 or 4", value);
   h->tune[key] = value;
+  return 0;
+}
+extern "C" int snb200_set_activation_parameter(snb200_handle_t h, float alpha) {
+  if (!h) return SNB200_STATUS_NOT_INITIALIZED;
+  h->act_alpha = alpha;
   return 0;
 }
 extern "C" const char* snb200_last_error_string(snb200_handle_t h) { return h ? h->last_error : "null handle"; }
@@ -339,7 +345,7 @@ static int fill_umma_args(snb200_handle_t h, const GemmProblem& g, int bn_box, C
   p.b_mn = g.transB ? 0 : 1;
   p.ldc = g.ldc; p.strideC = g.strideC;
   p.C = g.C; p.Z = g.Z; p.bias = g.bias;
-  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act;
+  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act; p.act_alpha = g.act_alpha;
   p.rewrite_hi = h->tune[TUNE_REWRITE_HI];
   p.vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (g.batch == 1 || g.strideC % 4 == 0) &&
              (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias));
@@ -665,7 +671,7 @@ static int launch_simt(snb200_handle_t h, const GemmProblem& g) {
   p.strideA = g.strideA; p.strideB = g.strideB; p.strideC = g.strideC;
   p.ldc = g.ldc;
   p.A = g.A; p.B = g.B; p.C = g.C; p.Z = g.Z; p.bias = g.bias;
-  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act;
+  p.alpha = g.alpha; p.beta = g.beta; p.act = g.act; p.act_alpha = g.act_alpha;
   p.omap = g.omap;
   // 128 x 128 tiles once they fill most of the SMs; 64 x 64 tiles for everything smaller
   const long long big_tiles = static_cast<long long>((g.M + kSimtBigBM - 1) / kSimtBigBM) *
@@ -797,7 +803,7 @@ static int launch_tail_reduce(snb200_handle_t h, const GemmProblem& g, const Spl
   r.partial = h->workspace;
   r.tile_elems = static_cast<long long>(tile_rows) * bn;
   r.C = g.C; r.Z = g.Z; r.bias = g.bias; r.ldc = g.ldc; r.strideC = g.strideC;
-  r.alpha = g.alpha; r.beta = g.beta; r.act = g.act;
+  r.alpha = g.alpha; r.beta = g.beta; r.act = g.act; r.act_alpha = g.act_alpha;
   r.omap = g.omap;
   r.vec_ok = aligned16(g.C) && (g.ldc % 4 == 0) && (g.batch == 1 || g.strideC % 4 == 0) &&
              (!g.Z || aligned16(g.Z)) && (!g.bias || aligned16(g.bias)) && omap_vec(g.omap);
@@ -813,7 +819,7 @@ static int launch_reduce(snb200_handle_t h, const GemmProblem& g, int parts, int
   r.partial = h->workspace;
   r.partial_stride = static_cast<long long>(g.batch) * g.M * g.N;
   r.C = g.C; r.Z = g.Z; r.bias = g.bias; r.ldc = g.ldc; r.strideC = g.strideC;
-  r.alpha = g.alpha; r.beta = g.beta; r.act = g.act;
+  r.alpha = g.alpha; r.beta = g.beta; r.act = g.act; r.act_alpha = g.act_alpha;
   r.omap = g.omap;
   const long long total = r.partial_stride;
   long long blocks = (total + 255) / 256;
@@ -1192,7 +1198,8 @@ extern "C" int snb200_gemm(snb200_handle_t h, int transA, int transB, int aH, in
 
 // ------------------------------------------------------------------------------------ Dense
 static bool act_supported(int act) {
-  return act == ACT_SIGMOID || act == ACT_RELU || act == ACT_TANH || act == ACT_IDENTITY || act == ACT_SWISH;
+  return act == ACT_SIGMOID || act == ACT_RELU || act == ACT_TANH || act == ACT_IDENTITY || act == ACT_SWISH ||
+         act == ACT_ELU || act == ACT_LEAKY_RELU;
 }
 
 static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
@@ -1226,7 +1233,7 @@ static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, 
   g.ldc = N; g.batch = 1;
   g.A = x; g.B = W; g.C = y;
   g.alpha = 1.0f; g.beta = 0.0f;
-  g.bias = bias; g.Z = z; g.act = act;
+  g.bias = bias; g.Z = z; g.act = act; g.act_alpha = h->act_alpha;
   if (y_map) g.omap = *y_map;
   if (!softmax) return run_gemm(h, g);
   if (y_map) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "a softmax result is stored densely");
@@ -1259,9 +1266,9 @@ static int launch_colsum(snb200_handle_t h, int M, int N, int act, const float* 
   float* out = db ? (slabs == 1 ? db : h->workspace) : nullptr;
   dim3 grid(col_blocks, slabs);
   if (vec)
-    launch_pdl(h, colsum_slab_kernel<4, FUSE>, grid, dim3(256), M, N, rows_per_slab, act, dy, y, z, dz, out, scale);
+    launch_pdl(h, colsum_slab_kernel<4, FUSE>, grid, dim3(256), M, N, rows_per_slab, act, dy, y, z, dz, out, scale, h->act_alpha);
   else
-    launch_pdl(h, colsum_slab_kernel<1, FUSE>, grid, dim3(256), M, N, rows_per_slab, act, dy, y, z, dz, out, scale);
+    launch_pdl(h, colsum_slab_kernel<1, FUSE>, grid, dim3(256), M, N, rows_per_slab, act, dy, y, z, dz, out, scale, h->act_alpha);
   int launches = 1;
   if (db && slabs > 1) {
     launch_pdl(h, colsum_finish_kernel, dim3((N + 255) / 256), dim3(256), N, slabs, h->workspace, db);
@@ -1413,7 +1420,7 @@ static int dense_bwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, 
   const float* dz = dy;
   if (act != ACT_IDENTITY) {
     if (!y) return fail(h, SNB200_STATUS_INVALID_VALUE, "activation output y is required for this activation");
-    if (act == ACT_SWISH && !z) return fail(h, SNB200_STATUS_INVALID_VALUE, "pre-activation z is required for SWISH");
+    if (act_needs_input(act) && !z) return fail(h, SNB200_STATUS_INVALID_VALUE, "pre-activation z is required for SWISH and ELU");
     if (!dz_scratch) return fail(h, SNB200_STATUS_INVALID_VALUE, "dz_scratch is required for this activation");
     if (M > 0 && N > 0) {
       st = launch_colsum<true>(h, M, N, act, dy, y, z, dz_scratch, db);   // dz and db in one pass over dy
@@ -1466,9 +1473,9 @@ extern "C" int snb200_activation_fwd(snb200_handle_t h, int act, long long count
   if (count == 0) return 0;
   if (!x || !y) return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (aligned16(x) && aligned16(y))
-    launch_pdl(h, activation_fwd_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), act, count, x, y);
+    launch_pdl(h, activation_fwd_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), act, h->act_alpha, count, x, y);
   else
-    launch_pdl(h, activation_fwd_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), act, count, x, y);
+    launch_pdl(h, activation_fwd_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), act, h->act_alpha, count, x, y);
   note_kernel(h, "activation_fwd", 1);
   return check_launch(h, "activation_fwd launch");
 }
@@ -1480,12 +1487,12 @@ extern "C" int snb200_activation_bwd(snb200_handle_t h, int act, long long count
   if (count < 0) return fail(h, SNB200_STATUS_INVALID_VALUE, "negative count");
   if (!act_supported(act)) return fail(h, SNB200_STATUS_NOT_SUPPORTED, "activation %d is not implemented", act);
   if (count == 0) return 0;
-  if (!dy || !dx || (act != ACT_IDENTITY && !y) || (act == ACT_SWISH && !x))
+  if (!dy || !dx || (act != ACT_IDENTITY && !y) || (act_needs_input(act) && !x))
     return fail(h, SNB200_STATUS_INVALID_VALUE, "null pointer");
   if (aligned16(dy) && aligned16(dx) && (!x || aligned16(x)) && (!y || aligned16(y)))
-    launch_pdl(h, activation_bwd_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), act, count, dy, x, y, dx);
+    launch_pdl(h, activation_bwd_kernel<4>, dim3(ew_grid(h, count / 4 + 1, 256)), dim3(256), act, h->act_alpha, count, dy, x, y, dx);
   else
-    launch_pdl(h, activation_bwd_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), act, count, dy, x, y, dx);
+    launch_pdl(h, activation_bwd_kernel<1>, dim3(ew_grid(h, count, 256)), dim3(256), act, h->act_alpha, count, dy, x, y, dx);
   note_kernel(h, "activation_bwd", 1);
   return check_launch(h, "activation_bwd launch");
 }

@@ -39,13 +39,16 @@ def DenseBackwardPropagation(dx, weightGradients, biasGradients_1D, x, dy, weigh
 
 
 def FusedDenseForward(y, x, weights, biasIfAny_1D, activation=ACT_IDENTITY, z=None, w_layout=W_OUT_IN,
-                      flattenInputTensorOnLastDimension=False):
-    """y = act(x * op(W) + bias) in one kernel; ``z`` optionally receives the pre-activation."""
+                      flattenInputTensorOnLastDimension=False, activationParameter=None):
+    """y = act(x * op(W) + bias) in one kernel; ``z`` optionally receives the pre-activation;
+    ``activationParameter`` is the coefficient of ELU / LeakyRelu."""
     x2 = x.As2DTensor(flattenInputTensorOnLastDimension)
     y2 = y.As2DTensor(flattenInputTensorOnLastDimension)
     M, K = x2.Shape
     N = y2.Shape[1]
     w = y.wrapper
+    if activationParameter is not None:
+        w.set_activation_parameter(activationParameter)
     st = w.lib.snb200_dense_fwd(w.handle, w_layout, M, K, N, x2.Pointer, weights.Pointer,
                                 None if biasIfAny_1D is None else biasIfAny_1D.Pointer, int(activation),
                                 None if z is None else z.Pointer, y2.Pointer)
@@ -53,13 +56,16 @@ def FusedDenseForward(y, x, weights, biasIfAny_1D, activation=ACT_IDENTITY, z=No
 
 
 def FusedDenseBackward(dx, weightGradients, biasGradients_1D, x, dy, weights, activation=ACT_IDENTITY, y=None, z=None,
-                       multiplier=1.0, dz_scratch=None, w_layout=W_OUT_IN, flattenInputTensorOnLastDimension=False):
+                       multiplier=1.0, dz_scratch=None, w_layout=W_OUT_IN, flattenInputTensorOnLastDimension=False,
+                       activationParameter=None):
     """ActivationLayer backward + Dense backward through one ``snb200_dense_bwd`` call."""
     x2 = x.As2DTensor(flattenInputTensorOnLastDimension)
     dy2 = dy.As2DTensor(flattenInputTensorOnLastDimension)
     M, K = x2.Shape
     N = dy2.Shape[1]
     w = dy.wrapper
+    if activationParameter is not None:
+        w.set_activation_parameter(activationParameter)
     p = lambda t: None if t is None else t.Pointer  # noqa: E731
     st = w.lib.snb200_dense_bwd(w.handle, w_layout, M, K, N, x2.Pointer, weights.Pointer, dy2.Pointer, int(activation),
                                 p(y), p(z), float(multiplier), p(dz_scratch), p(dx), weightGradients.Pointer,

@@ -45,6 +45,10 @@ class GPUWrapper:
     def set_math_mode(self, mode):
         check(self.handle, self.lib.snb200_set_math_mode(self.handle, mode))
 
+    def set_activation_parameter(self, alpha):
+        """Coefficient of the ELU / LeakyRelu calls that follow (the layer's activationParameter)."""
+        check(self.handle, self.lib.snb200_set_activation_parameter(self.handle, float(alpha)))
+
     def get_math_mode(self):
         m = ctypes.c_int()
         check(self.handle, self.lib.snb200_get_math_mode(self.handle, ctypes.byref(m)))
@@ -204,13 +208,18 @@ class GPUTensor:
                                                biasGradient_1D.Pointer))
 
     def ActivationForward(self, activationType, activationParameter, y):
-        """y = act(this)   (Prod/Data/Tensor.cs:618, Prod/GPU/GpuTensor.cs:397-443)."""
+        """y = act(this)   (Prod/Data/Tensor.cs:618, Prod/GPU/GpuTensor.cs:397-443).  ``activationParameter``: the
+        coefficient of ELU / LeakyRelu (a number here, a one-element tensor in SharpNet)."""
         w = self.wrapper
+        if activationParameter is not None:
+            w.set_activation_parameter(activationParameter)
         check(w.handle, w.lib.snb200_activation_fwd(w.handle, int(activationType), self.Count, self.Pointer, y.Pointer))
 
     def ActivationBackward(self, activationType, activationParameter, dy, x, y):
         """this = dx = act'(x, y) * dy   (Prod/Data/Tensor.cs:628, Prod/GPU/GpuTensor.cs:445-490)."""
         w = self.wrapper
+        if activationParameter is not None:
+            w.set_activation_parameter(activationParameter)
         check(w.handle, w.lib.snb200_activation_bwd(
             w.handle, int(activationType), self.Count, dy.Pointer, None if x is None else x.Pointer,
             None if y is None else y.Pointer, self.Pointer))

@@ -10,6 +10,9 @@ Sources (paths inside the reference):
   Tests/NonReg/TestNetworkPropagation.cs:24-34   inputs X_1_1_4_4, X_2_1_4_4 and weights W_N_1_4_4
   Tests/NonReg/TestNetworkPropagation.cs:80-132  Linear + Sigmoid predictions before training and after 10 epochs of
                                                  VanillaSGD ([in,out] weights)
+  Tests/NonReg/TestNetworkPropagation.cs:135-160,216-244,330-358,725-770,1161-1192
+                                                 Linear networks with Softmax, ReLU, LeakyRelu, weight decay and Mse loss:
+                                                 predictions before training and after 10 epochs
   Tests/NonReg/TestNetworkPropagation.cs:500-575 attention block: predictions before training, plain and causal
   Tests/NonReg/TestNetworkPropagation.cs:580-623 MultiHeadAttention (3 heads x 5, [in,out] weights): predictions before
                                                  training and after 10 epochs of SGD with momentum, plain and causal
@@ -102,6 +105,35 @@ def main(ref):
     blk = _between(tnp, "public void TestSigmoidActivation_NCHW_1_1_1_1", "const int num_epochs")
     out["sigmoid_1_1_1_1_w"] = _nth_numpy_literal(blk, 0)
     out["sigmoid_1_1_1_1_pred"] = _numbers(re.search(r'TestPredict\(network, X, "(.*?)"\)', blk).group(1))
+
+    # ---- more Dense networks of the same file, each with predictions (and losses where the test states them)
+    #      before training and after 10 epochs on the one batch of 2 rows -----------------------------------------
+    out["Y_2_3"] = _const(tnp, "Y_2_3")
+    out["X_2_3_4_5"] = _const(tnp, "X_2_3_4_5")
+
+    def network_case(name, end):
+        blk = _between(tnp, "public void " + name, end)
+        weights = [_numbers(c) for c in re.findall(r'FromNumpyArray\("(\[\[.*?\]\])"\)', blk)
+                   if len(_numbers(c)) > 6]                      # weight literals (predictions have 6 numbers)
+        preds = [_numbers(c) for c in re.findall(r'TestPredict\(network, X,\s*"(.*?)"', blk)]
+        losses = [float(v) for v in re.findall(r"TestLossAccuracy\(network, X, Y, ([0-9.]+),", blk)]
+        hidden = [float(v) for v in re.findall(r"TestLossAccuracy\(network, X, Y, null\s*/\*\s*([0-9.]+)\s*\*/", blk)]
+        return {"weights": weights, "pred_before": preds[0], "pred_after": preds[1],
+                "loss_before": (losses or hidden or [None])[0], "loss_after": (losses or hidden or [None, None])[1]}
+    # :135-160 Linear(3) + Softmax, CategoricalCrossentropy, VanillaSGD lr 0.1
+    out["softmax_2_1_4_4"] = network_case("TestSoftmaxActivation_NCHW_2_1_4_4", "public static CpuTensor<float> FromNumpyArray")
+    # :216-244 Linear(3) + ReLU + Linear(3) + Sigmoid, BinaryCrossentropy, VanillaSGD lr 0.1
+    out["relu_2_1_4_4"] = network_case("TestReluActivation_NCHW_2_1_4_4", "public void TestEmbedding(")
+    # :330-358 Linear(3) + LeakyRelu(0.1) + Linear(3) + Sigmoid, BinaryCrossentropy, SGD lr 0.1 momentum 0.9
+    out["leaky_relu_2_1_4_4"] = network_case("TestLeakyReluActivation_NCHW_2_1_4_4", "public void TestConvolutionWithReluActivation")
+    # :725-770 Linear(3) + Softmax with weight decay: VanillaSGD lr 0.12, weight_decay 0.05; SGD lr 0.12 momentum 0.9,
+    # weight_decay 0.5 (the losses there are commented out in the reference: they include the regularisation term)
+    out["weight_decay_vanilla_2_1_4_4"] = network_case("Test_weight_decay_LinearLayer_SGDVanilla_NCHW_2_1_4_4",
+                                                       "public void Test_weight_decay_LinearLayer_SGDMomentum")
+    out["weight_decay_momentum_2_1_4_4"] = network_case("Test_weight_decay_LinearLayer_SGDMomentum_NCHW_2_1_4_4",
+                                                        "public void TestConcatenate_NCHW_1_1_1_1")
+    # :1161-1192 Linear(3, on the last dimension) + ReLU + Linear(3), Mse, SGD lr 0.1 momentum 0.9; tolerance 1e-3
+    out["mse_2_3_4_5"] = network_case("Test_MseLoss", "private const string X_RNN_4_2_1")
 
     # ---- attention goldens: Conv1D(k=1) Q/K/V projections -> ScaledDotProductAttention -> Flatten -> Linear -> Softmax
     out["X_3_4_5"] = _const(tnp, "X_3_4_5")

@@ -5,8 +5,8 @@ import numpy as np
 import pytest
 
 from oracle import sharpnet_oracle as orc
-from sharpnet_b200 import (ACT_IDENTITY, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH, MATH_3XTF32, MATH_TF32, W_IN_OUT,
-                           W_OUT_IN)
+from sharpnet_b200 import (ACT_ELU, ACT_IDENTITY, ACT_LEAKY_RELU, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH, MATH_3XTF32,
+                           MATH_TF32, W_IN_OUT, W_OUT_IN)
 from sharpnet_b200._capi import TUNE_CLUSTER, TUNE_FORCE_PATH
 from sharpnet_b200._capi import LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE
 from sharpnet_b200.linear import (DenseBackwardPropagation, DenseForwardPropagation, FusedDenseBackward,
@@ -16,7 +16,8 @@ from sharpnet_b200.tensor import GPUTensor
 from gpu_util import TOL_3XTF32, TOL_TF32
 
 pytestmark = pytest.mark.gpu
-ACTS = [ACT_IDENTITY, ACT_RELU, ACT_SWISH, ACT_TANH, ACT_SIGMOID]
+ACTS = [ACT_IDENTITY, ACT_RELU, ACT_SWISH, ACT_TANH, ACT_SIGMOID, ACT_ELU, ACT_LEAKY_RELU]
+ALPHA = {ACT_ELU: 0.7, ACT_LEAKY_RELU: 0.3}      # the coefficient the parametric activations are tested with
 
 
 @pytest.fixture(autouse=True)
@@ -79,10 +80,11 @@ def _dense_case(wrapper, M, K, N, act, layout, seed, tol, with_bias=True, need_d
     X, W, DY = _t(wrapper, x), _t(wrapper, Wl), _t(wrapper, dy)
     B = _t(wrapper, b) if with_bias else None
     Y, Z = GPUTensor((M, N), None, wrapper), GPUTensor((M, N), None, wrapper)
-    FusedDenseForward(Y, X, W, B, act, z=Z, w_layout=layout)
+    alpha = ALPHA.get(act, 0.0)
+    FusedDenseForward(Y, X, W, B, act, z=Z, w_layout=layout, activationParameter=alpha)
     wrapper.check_device_status()
-    z64, y64 = orc.dense_forward(x, Wl, b, act, layout, f64=True)
-    zm, ym = orc.dense_forward(x, Wl, b, act, layout)
+    z64, y64 = orc.dense_forward(x, Wl, b, act, layout, f64=True, alpha=alpha)
+    zm, ym = orc.dense_forward(x, Wl, b, act, layout, alpha=alpha)
     y, z = Y.ContentAsFloatArray(), Z.ContentAsFloatArray()
     for got, r64, rm in ((z, z64, zm), (y, y64, ym)):
         assert orc.scaled_error(got, r64, K, 4.0, wmax) <= tol
@@ -94,8 +96,8 @@ def _dense_case(wrapper, M, K, N, act, layout, seed, tol, with_bias=True, need_d
     DB = GPUTensor((N,), None, wrapper) if with_bias else None
     FusedDenseBackward(DX, DW, DB, X, DY, W, act, y=Y, z=Z, multiplier=mult, dz_scratch=DZ, w_layout=layout)
     wrapper.check_device_status()
-    dz64, dW64, db64, dx64 = orc.dense_backward(x, Wl, dy, act, y, z, mult, layout, need_dx, f64=True)
-    dzm, dWm, dbm, dxm = orc.dense_backward(x, Wl, dy, act, y, z, mult, layout, need_dx)
+    dz64, dW64, db64, dx64 = orc.dense_backward(x, Wl, dy, act, y, z, mult, layout, need_dx, f64=True, alpha=alpha)
+    dzm, dWm, dbm, dxm = orc.dense_backward(x, Wl, dy, act, y, z, mult, layout, need_dx, alpha=alpha)
     if act != ACT_IDENTITY:
         np.testing.assert_allclose(DZ.ContentAsFloatArray(), dzm, rtol=2e-6, atol=1e-6)
     gmax = 4.0 * 1.2  # |dz| <= |dy| * max|act'| (1.1 for Swish)
@@ -208,12 +210,13 @@ def test_activations_and_axpy(wrapper):
         X, DY = _t(wrapper, x), _t(wrapper, dy)
         for act in ACTS:
             Y, DX = GPUTensor(shape, None, wrapper), GPUTensor(shape, None, wrapper)
-            X.ActivationForward(act, None, Y)
+            alpha = ALPHA.get(act)
+            X.ActivationForward(act, alpha, Y)
             y = Y.ContentAsFloatArray()
-            np.testing.assert_allclose(y, orc.activation_forward(act, x), rtol=1e-6, atol=1e-7)
-            DX.ActivationBackward(act, None, DY, X, Y)
-            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y), rtol=2e-6,
-                                       atol=1e-6)
+            np.testing.assert_allclose(y, orc.activation_forward(act, x, alpha or 0.0), rtol=1e-6, atol=1e-7)
+            DX.ActivationBackward(act, alpha, DY, X, Y)
+            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, alpha or 0.0),
+                                       rtol=2e-6, atol=1e-6)
         Yv = _t(wrapper, dy)
         Yv.Update_Adding_Alpha_X(0.25, X)
         np.testing.assert_allclose(Yv.ContentAsFloatArray(), orc.update_adding_alpha_x(dy.copy(), 0.25, x), rtol=0,
@@ -224,7 +227,7 @@ def test_dense_argument_errors(wrapper):
     lib, h = wrapper.lib, wrapper.handle
     T = GPUTensor((4, 4), None, wrapper)
     assert lib.snb200_dense_fwd(h, 2, 4, 4, 4, T.Pointer, T.Pointer, None, ACT_RELU, None, T.Pointer) == 7
-    assert lib.snb200_dense_fwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, None, 4, None, T.Pointer) == 15   # ELU not fused
+    assert lib.snb200_dense_fwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, None, 3, None, T.Pointer) == 15   # CLIPPED_RELU is not built
     # Swish backward without the pre-activation
     assert lib.snb200_dense_bwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, T.Pointer, ACT_SWISH, T.Pointer, None, 1.0,
                                 T.Pointer, None, T.Pointer, None) == 7
@@ -385,3 +388,82 @@ def test_dense_seeded_sweep(wrapper):
                         mult=float(rng.choice([1.0, 0.25])))
     finally:
         wrapper.set_tuning(TUNE_CLUSTER, 0)
+
+
+def _golden_mlp_on_device(wrapper, g, acts, loss, lr, momentum=0.0, weight_decay=0.0, alphas=None, x=None,
+                          first_on_last_dim=False, epochs=10):
+    """The reference's small Dense networks (Tests/NonReg/TestNetworkPropagation.cs) trained for 10 epochs entirely
+    through the C ABI: fused forward, loss gradient fused into the output layer's backward, hidden layers through
+    snb200_dense_bwd, weight decay as dW += 2 * batch * wd * W (Update_Adding_Alpha_X), SGD with or without momentum.
+    TensorFlow compatibility mode (dW multiplier 1, [in, out] weights).  Returns predictions before and after."""
+    from sharpnet_b200._capi import LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE  # noqa: F401
+    from sharpnet_b200 import ACT_SOFTMAX
+    from sharpnet_b200.optimizers import Sgd, VanillaSgd
+    n = len(acts)
+    alphas = alphas or [None] * n
+    batch = x.shape[0]
+    y_true = _t(wrapper, np.asarray([[1, 0, 0], [0, 0, 1]], np.float32))
+    shapes, fan_in = [], (x.shape[-1] if first_on_last_dim else x[0].size)
+    for i in range(n):
+        shapes.append((fan_in, 3))
+        fan_in = (x[0].size // x.shape[-1]) * 3 if (i == 0 and first_on_last_dim) else 3
+    Ws = [_t(wrapper, np.asarray(g["weights"][i], np.float32).reshape(shapes[i])) for i in range(n)]
+    bs = [GPUTensor((3,), None, wrapper) for _ in range(n)]
+    dWs = [GPUTensor(shapes[i], None, wrapper) for i in range(n)]
+    dbs = [GPUTensor((3,), None, wrapper) for _ in range(n)]
+    opts = [Sgd(wrapper, momentum, False, shapes[i], (3,)) if momentum else VanillaSgd() for i in range(n)]
+    rows = [x.size // shapes[0][0] if first_on_last_dim else batch] + [batch] * (n - 1)
+    ins = [_t(wrapper, x.reshape(rows[0], shapes[0][0]))]
+    zs = [GPUTensor((rows[i], 3), None, wrapper) for i in range(n)]
+    ys = [GPUTensor((rows[i], 3), None, wrapper) for i in range(n)]
+    dzs = [GPUTensor((rows[i], 3), None, wrapper) for i in range(n)]
+    dxs = [None] + [GPUTensor((rows[i], shapes[i][0]), None, wrapper) for i in range(1, n)]
+
+    def forward():
+        h = ins[0]
+        for i in range(n):
+            if i > 0:
+                h = GPUTensor((rows[i], shapes[i][0]), None, wrapper, storage=ys[i - 1].storage)   # Flatten: a view
+            FusedDenseForward(ys[i], h, Ws[i], bs[i], acts[i], z=None if acts[i] == ACT_SOFTMAX else zs[i],
+                              w_layout=W_IN_OUT, activationParameter=alphas[i])
+            ins[i:i + 1] = [h]
+        return ys[-1].ContentAsFloatArray().reshape(batch, -1).copy()
+    before = forward()
+    for _ in range(epochs):
+        forward()
+        last = n - 1
+        FusedDenseBackwardFromLoss(dxs[last], dWs[last], dbs[last], ins[last], y_true, ys[last], Ws[last], loss, 1.0,
+                                   dzs[last], W_IN_OUT)
+        for i in reversed(range(n - 1)):
+            dy = GPUTensor((rows[i], 3), None, wrapper, storage=dxs[i + 1].storage)
+            FusedDenseBackward(dxs[i], dWs[i], dbs[i], ins[i], dy, Ws[i], acts[i], y=ys[i], z=zs[i], multiplier=1.0,
+                               dz_scratch=dzs[i], w_layout=W_IN_OUT, activationParameter=alphas[i])
+        for i in range(n):
+            if weight_decay:
+                dWs[i].Update_Adding_Alpha_X(2 * batch * weight_decay, Ws[i])
+            opts[i].UpdateWeights(lr, lr, batch, Ws[i], dWs[i], bs[i], dbs[i])
+        wrapper.check_device_status()
+    return before, forward()
+
+
+def test_golden_softmax_relu_leaky_relu_weight_decay_and_mse_networks(wrapper, golden):
+    # Tests/NonReg/TestNetworkPropagation.cs:135-160, 216-244, 330-358, 725-770 at 1e-6 and :1161-1192 at 1e-3:
+    # predictions before training and after 10 epochs, nothing on the host between the steps
+    from sharpnet_b200 import ACT_SOFTMAX
+    from sharpnet_b200._capi import LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE
+    x = np.asarray(golden["X_2_1_4_4"], np.float32).reshape(2, 16)
+    cases = (
+        ("softmax_2_1_4_4", (ACT_SOFTMAX,), LOSS_CATEGORICAL_CROSSENTROPY, dict(lr=0.1), x, 1e-6),
+        ("relu_2_1_4_4", (ACT_RELU, ACT_SIGMOID), LOSS_BINARY_CROSSENTROPY, dict(lr=0.1), x, 1e-6),
+        ("leaky_relu_2_1_4_4", (ACT_LEAKY_RELU, ACT_SIGMOID), LOSS_BINARY_CROSSENTROPY,
+         dict(lr=0.1, momentum=0.9, alphas=[0.1, None]), x, 1e-6),
+        ("weight_decay_vanilla_2_1_4_4", (ACT_SOFTMAX,), LOSS_CATEGORICAL_CROSSENTROPY, dict(lr=0.12, weight_decay=0.05), x, 1e-6),
+        ("weight_decay_momentum_2_1_4_4", (ACT_SOFTMAX,), LOSS_CATEGORICAL_CROSSENTROPY,
+         dict(lr=0.12, momentum=0.9, weight_decay=0.5), x, 1e-6),
+        ("mse_2_3_4_5", (ACT_RELU, ACT_IDENTITY), LOSS_MSE, dict(lr=0.1, momentum=0.9, first_on_last_dim=True),
+         np.asarray(golden["X_2_3_4_5"], np.float32).reshape(2, 3, 4, 5), 1e-3),
+    )
+    for key, acts, loss, kw, xin, tol in cases:
+        before, after = _golden_mlp_on_device(wrapper, golden[key], acts, loss, x=xin, **kw)
+        np.testing.assert_allclose(before.ravel(), golden[key]["pred_before"], rtol=0, atol=tol, err_msg=key)
+        np.testing.assert_allclose(after.ravel(), golden[key]["pred_after"], rtol=0, atol=tol, err_msg=key)

@@ -160,3 +160,101 @@ def test_optimizer_updates_against_closed_forms():
     orc.update_adam_optimizer(W, 0.001, 0.9, 0.999, 1e-8, 0.0, dW, m, s, 1)
     # first Adam step moves every weight by lr * sign(dW) (bias-corrected moments cancel)
     np.testing.assert_allclose(W0 - W, 0.001 * np.sign(dW), rtol=0, atol=1e-6)
+
+
+# ---- the other Dense networks of Tests/NonReg/TestNetworkPropagation.cs, before and after 10 epochs -------------
+def _mlp_forward(x, Ws, bs, acts, alphas, first_on_last_dim):
+    """Forward of a stack of Linear layers with [in, out] weights; returns the per-layer (input, z, y).  The first
+    layer may act on the last dimension (flattenInputTensorOnLastDimension), later layers flatten per row."""
+    cache, h = [], x
+    for i, (W, b, act, alpha) in enumerate(zip(Ws, bs, acts, alphas)):
+        h2 = h.reshape(-1, W.shape[0]) if (i == 0 and first_on_last_dim) else h.reshape(x.shape[0], -1)
+        out_act = orc.ACT_IDENTITY if act in (orc.ACT_SIGMOID, orc.ACT_SOFTMAX) and i == len(Ws) - 1 else act
+        z, y = orc.dense_forward(h2, W, b, act, orc.W_IN_OUT, alpha=alpha)
+        cache.append((h2, z, y, out_act))
+        h = y
+    return cache
+
+
+def _train_mlp(g, acts, loss, lr, momentum=0.0, weight_decay=0.0, alphas=None, x=None, first_on_last_dim=False,
+               epochs=10):
+    """TensorFlow compatibility mode as the reference's tests set it: dW multiplier 1 (Prod/Layers/Linear.cs:150-155),
+    learning rate / batch size (Prod/Optimizers/Optimizer.cs:26-29), the output layer's Sigmoid / Softmax folded into
+    the loss gradient (Prod/Layers/ActivationLayer.cs:59-62), weight decay as dW += 2 * batch * wd * W (Linear.cs:167-176),
+    biases from zero.  Returns predictions before and after training."""
+    n = len(acts)
+    Ws = [np.asarray(w, np.float32) for w in g["weights"][:n]]
+    y_true = np.asarray([[1, 0, 0], [0, 0, 1]], np.float32)
+    alphas = alphas or [0.0] * n
+    widths = []
+    fan_in = (x.shape[-1] if first_on_last_dim else x[0].size)
+    for i, w in enumerate(Ws):
+        out = 3
+        Ws[i] = w.reshape(fan_in, out)
+        widths.append(out)
+        fan_in = (x[0].size // x.shape[-1]) * out if (i == 0 and first_on_last_dim) else out
+    bs = [np.zeros(w.shape[1], np.float32) for w in Ws]
+    vW = [np.zeros_like(w) for w in Ws] if momentum else [None] * n
+    vb = [np.zeros_like(b) for b in bs] if momentum else [None] * n
+    batch = x.shape[0]
+    predict = lambda: _mlp_forward(x, Ws, bs, acts, alphas, first_on_last_dim)[-1][2].reshape(batch, -1)  # noqa: E731
+    before = predict()
+    for _ in range(epochs):
+        cache = _mlp_forward(x, Ws, bs, acts, alphas, first_on_last_dim)
+        grad = orc.loss_gradient(loss, y_true, cache[-1][2].reshape(batch, -1))
+        for i in reversed(range(n)):
+            h2, z, y, act = cache[i]
+            dz, dW, db, dx = orc.dense_backward(h2, Ws[i], grad.reshape(z.shape), act, y, z, 1.0, orc.W_IN_OUT,
+                                                need_dx=i > 0, alpha=alphas[i])
+            if weight_decay:
+                orc.update_adding_alpha_x(dW, 2 * batch * np.float32(weight_decay), Ws[i])
+            grad = dx
+            orc.update_sgd_optimizer(Ws[i], lr / batch, momentum, False, dW, vW[i])
+            orc.update_sgd_optimizer(bs[i], lr / batch, momentum, False, db, vb[i])
+    return before, predict()
+
+
+def _x_2_1_4_4(golden):
+    return np.asarray(golden["X_2_1_4_4"], np.float32).reshape(2, 16)
+
+
+def test_softmax_relu_and_leaky_relu_networks_before_and_after_training(golden):
+    x = _x_2_1_4_4(golden)
+    y_true = np.asarray(golden["Y_2_3"], np.float32).reshape(2, 3)
+    cases = (
+        # :135-160 Linear + Softmax, CategoricalCrossentropy, VanillaSGD 0.1
+        ("softmax_2_1_4_4", (orc.ACT_SOFTMAX,), orc.LOSS_CATEGORICAL_CROSSENTROPY, dict(lr=0.1), 1e-6),
+        # :216-244 Linear + ReLU + Linear + Sigmoid, BinaryCrossentropy, VanillaSGD 0.1
+        ("relu_2_1_4_4", (orc.ACT_RELU, orc.ACT_SIGMOID), orc.LOSS_BINARY_CROSSENTROPY, dict(lr=0.1), 1e-6),
+        # :330-358 Linear + LeakyRelu(0.1) + Linear + Sigmoid, BinaryCrossentropy, SGD 0.1 with momentum 0.9
+        ("leaky_relu_2_1_4_4", (orc.ACT_LEAKY_RELU, orc.ACT_SIGMOID), orc.LOSS_BINARY_CROSSENTROPY,
+         dict(lr=0.1, momentum=0.9, alphas=[0.1, 0.0]), 1e-6),
+        # :725-747 Linear + Softmax with weight decay 0.05, VanillaSGD 0.12
+        ("weight_decay_vanilla_2_1_4_4", (orc.ACT_SOFTMAX,), orc.LOSS_CATEGORICAL_CROSSENTROPY,
+         dict(lr=0.12, weight_decay=0.05), 1e-6),
+        # :749-770 the same with SGD 0.12, momentum 0.9, weight decay 0.5
+        ("weight_decay_momentum_2_1_4_4", (orc.ACT_SOFTMAX,), orc.LOSS_CATEGORICAL_CROSSENTROPY,
+         dict(lr=0.12, momentum=0.9, weight_decay=0.5), 1e-6),
+    )
+    for key, acts, loss, kw, tol in cases:
+        g = golden[key]
+        before, after = _train_mlp(g, acts, loss, x=x, **kw)
+        np.testing.assert_allclose(before.ravel(), g["pred_before"], rtol=0, atol=tol, err_msg=key)
+        np.testing.assert_allclose(after.ravel(), g["pred_after"], rtol=0, atol=tol, err_msg=key)
+        if loss == orc.LOSS_BINARY_CROSSENTROPY:
+            assert abs(orc.binary_crossentropy(y_true, before) - g["loss_before"]) < 1e-5, key
+            assert abs(orc.binary_crossentropy(y_true, after) - g["loss_after"]) < 1e-5, key
+        elif not kw.get("weight_decay"):
+            cce = lambda p: float(-(y_true * np.log(p.astype(np.float64))).sum(1).mean())  # noqa: E731
+            assert abs(cce(before) - g["loss_before"]) < 1e-5 and abs(cce(after) - g["loss_after"]) < 1e-5, key
+
+
+def test_mse_network_on_the_last_dimension_before_and_after_training(golden):
+    # :1161-1192 Linear(5 -> 3 on the last dimension) + ReLU + Linear(36 -> 3), Mse, SGD 0.1 with momentum 0.9; the
+    # reference states these predictions to 1e-3
+    x = np.asarray(golden["X_2_3_4_5"], np.float32).reshape(2, 3, 4, 5)
+    g = golden["mse_2_3_4_5"]
+    before, after = _train_mlp(g, (orc.ACT_RELU, orc.ACT_IDENTITY), orc.LOSS_MSE, lr=0.1, momentum=0.9, x=x,
+                               first_on_last_dim=True)
+    np.testing.assert_allclose(before.ravel(), g["pred_before"], rtol=0, atol=1e-3)
+    np.testing.assert_allclose(after.ravel(), g["pred_after"], rtol=0, atol=1e-3)
