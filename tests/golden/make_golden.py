@@ -21,6 +21,8 @@ Sources (paths inside the reference):
                                                  and after 10 epochs of SGD with momentum in batches of 2
   Tests/NonReg/ParallelRunWithPyTorch.cs:102-138 Linear(5->3, last-dim flatten)+ReLU+Flatten+Linear(36->3), Mse
   Tests/NonReg/ParallelRunWithPyTorch.cs:179-214 Linear(16->3)+ReLU+Linear(3->3)+Sigmoid, BCE ([out,in] weights)
+  Tests/NonReg/ParallelRunWithPyTorch.cs:813-850 Linear(16->3)+LeakyRelu(0.1)+Linear(3->3)+Softmax, 10 rows in batches of 2
+  (for the three PyTorch-layout networks also the loss after 10 epochs of SGD with momentum / weight decay / Nesterov)
 """
 import json
 import os
@@ -184,6 +186,16 @@ def main(ref):
     out["pt_relu_w1"] = _nth_numpy_literal(blk, 0)        # [3, 16]
     out["pt_relu_w2"] = _nth_numpy_literal(blk, 1)        # [3, 3]
     out["pt_relu_loss_before"] = _numbers(re.search(r"Assert.AreEqual\(([0-9.]+), loss_before", blk).group(1))[0]
+    out["pt_relu_loss_after"] = _numbers(re.search(r"Assert.AreEqual\(([0-9.]+), loss_after", blk).group(1))[0]
+    blk = _between(pt, "public void TestParallelRunWithPyTorch_Mse()", "public void TestParallelRunWithPyTorch_Mse_AdamW")
+    out["pt_mse_loss_after"] = _numbers(re.search(r"Assert.AreEqual\(([0-9.]+), loss_after", blk).group(1))[0]
+    # :813-850 Flatten + Linear(16->3) + LeakyRelu(0.1) + Linear(3->3) + Softmax on 10 rows in batches of 2,
+    # CategoricalCrossentropy, SGD lr 0.1 momentum 0.66 weight_decay 0.17 Nesterov, PyTorch compatibility mode
+    blk = _between(pt, "public void TestLeakyReluActivation_NCHW_10_1_4_4()", "public void TestMultiply_NCHW_2_3_4_5_different_dimension")
+    out["pt_leaky_w1"] = _nth_numpy_literal(blk, 0)       # [3, 16]
+    out["pt_leaky_w2"] = _nth_numpy_literal(blk, 1)       # [3, 3]
+    out["pt_leaky_loss_before"] = _numbers(re.search(r"Assert.AreEqual\(([0-9.]+), loss_before", blk).group(1))[0]
+    out["pt_leaky_loss_after"] = _numbers(re.search(r"Assert.AreEqual\(([0-9.]+), loss_after", blk).group(1))[0]
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json")
     with open(dst, "w") as f:

@@ -467,3 +467,81 @@ def test_golden_softmax_relu_leaky_relu_weight_decay_and_mse_networks(wrapper, g
         before, after = _golden_mlp_on_device(wrapper, golden[key], acts, loss, x=xin, **kw)
         np.testing.assert_allclose(before.ravel(), golden[key]["pred_before"], rtol=0, atol=tol, err_msg=key)
         np.testing.assert_allclose(after.ravel(), golden[key]["pred_after"], rtol=0, atol=tol, err_msg=key)
+
+
+def _pytorch_mlp_on_device(wrapper, x, t, w1, w2, act1, alpha1, out_act, loss, lr, momentum, weight_decay, nesterov,
+                           batch_size, first_on_last_dim=False, epochs=10):
+    """Two Linear layers with [out, in] weights in the reference's PyTorch compatibility mode (weight decay
+    dW += batch * wd * W and db += batch * wd * b, Prod/Layers/Linear.cs:167-181), trained in mini-batches entirely
+    through the C ABI.  Returns the predictions on all of x after training."""
+    from sharpnet_b200 import ACT_SOFTMAX
+    from sharpnet_b200.optimizers import Sgd
+    rows = x.shape[0]
+    X, T = _t(wrapper, x), _t(wrapper, t)
+    Ws, bs = [_t(wrapper, w1), _t(wrapper, w2)], [GPUTensor((w1.shape[0],), None, wrapper), GPUTensor((w2.shape[0],), None, wrapper)]
+    dWs = [GPUTensor(w1.shape, None, wrapper), GPUTensor(w2.shape, None, wrapper)]
+    dbs = [GPUTensor((w1.shape[0],), None, wrapper), GPUTensor((w2.shape[0],), None, wrapper)]
+    opts = [Sgd(wrapper, momentum, nesterov, w.shape, (w.shape[0],)) for w in (w1, w2)]
+    per_row_in = x[0].size
+    inner = per_row_in // w1.shape[1] if first_on_last_dim else 1      # rows of the first product per sample
+    h_per_row = inner * w1.shape[0]
+    view = lambda t_, r0, n, width: GPUTensor((n, width), None, wrapper, storage=t_.storage[r0 * width:(r0 + n) * width])  # noqa: E731
+
+    def forward(r0, n, bufs):
+        h0 = GPUTensor((n * inner, w1.shape[1]), None, wrapper, storage=X.storage[r0 * per_row_in:(r0 + n) * per_row_in])
+        z1, y1, p = bufs
+        FusedDenseForward(y1, h0, Ws[0], bs[0], act1, z=z1, w_layout=W_OUT_IN, activationParameter=alpha1)
+        h1 = GPUTensor((n, h_per_row), None, wrapper, storage=y1.storage)
+        FusedDenseForward(p, h1, Ws[1], bs[1], out_act, z=None, w_layout=W_OUT_IN)
+        return h0, h1
+    for _ in range(epochs):
+        for r0 in range(0, rows, batch_size):
+            n = min(batch_size, rows - r0)
+            z1, y1 = GPUTensor((n * inner, w1.shape[0]), None, wrapper), GPUTensor((n * inner, w1.shape[0]), None, wrapper)
+            p, dz2, dz1 = GPUTensor((n, w2.shape[0]), None, wrapper), GPUTensor((n, w2.shape[0]), None, wrapper), GPUTensor(
+                (n * inner, w1.shape[0]), None, wrapper)
+            dx = GPUTensor((n, h_per_row), None, wrapper)
+            h0, h1 = forward(r0, n, (z1, y1, p))
+            FusedDenseBackwardFromLoss(dx, dWs[1], dbs[1], h1, view(T, r0, n, t.shape[1]), p, Ws[1], loss, 1.0, dz2, W_OUT_IN)
+            dy1 = GPUTensor((n * inner, w1.shape[0]), None, wrapper, storage=dx.storage)
+            FusedDenseBackward(None, dWs[0], dbs[0], h0, dy1, Ws[0], act1, y=y1, z=z1, multiplier=1.0, dz_scratch=dz1,
+                               w_layout=W_OUT_IN, activationParameter=alpha1)
+            for i in range(2):
+                if weight_decay:
+                    dWs[i].Update_Adding_Alpha_X(n * weight_decay, Ws[i])
+                    dbs[i].Update_Adding_Alpha_X(n * weight_decay, bs[i])
+                opts[i].UpdateWeights(lr, lr, n, Ws[i], dWs[i], bs[i], dbs[i])
+            wrapper.check_device_status()
+    z1, y1 = GPUTensor((rows * inner, w1.shape[0]), None, wrapper), GPUTensor((rows * inner, w1.shape[0]), None, wrapper)
+    p = GPUTensor((rows, w2.shape[0]), None, wrapper)
+    forward(0, rows, (z1, y1, p))
+    return p.ContentAsFloatArray()
+
+
+def test_golden_pytorch_layout_networks_after_training(wrapper, golden):
+    # Tests/NonReg/ParallelRunWithPyTorch.cs:179-214, :102-138 and :813-850: the loss after 10 epochs (1e-6) with SGD
+    # momentum, weight decay on weights and biases, Nesterov and mini-batches, all through the C ABI
+    from sharpnet_b200 import ACT_SOFTMAX
+    from sharpnet_b200._capi import LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE
+    x, t = orc.numpy_array_for_tests(2, 1, 4, 4), orc.y_numpy_array_for_tests(2, 3)
+    w1 = np.asarray(golden["pt_relu_w1"], np.float32).reshape(3, 16)
+    w2 = np.asarray(golden["pt_relu_w2"], np.float32).reshape(3, 3)
+    p = _pytorch_mlp_on_device(wrapper, x, t, w1, w2, ACT_RELU, None, ACT_SIGMOID, LOSS_BINARY_CROSSENTROPY, 0.1, 0.9, 0.03,
+                               False, 2)
+    assert abs(orc.binary_crossentropy(t, p) - golden["pt_relu_loss_after"]) < 1e-6
+    x = orc.numpy_array_for_tests(2, 3, 4, 5)
+    w1 = np.asarray(golden["pt_mse_w1"], np.float32).reshape(3, 5)
+    w2 = np.asarray(golden["pt_mse_w2"], np.float32).reshape(3, 36)
+    p = _pytorch_mlp_on_device(wrapper, x, t, w1, w2, ACT_RELU, None, ACT_IDENTITY, LOSS_MSE, 0.1, 0.9, 0.0, False, 2,
+                               first_on_last_dim=True)
+    assert abs(orc.mse(t, p) - golden["pt_mse_loss_after"]) < 1e-6
+    x, t = orc.numpy_array_for_tests(10, 1, 4, 4), orc.y_numpy_array_for_tests(10, 3)
+    w1 = np.asarray(golden["pt_leaky_w1"], np.float32).reshape(3, 16)
+    w2 = np.asarray(golden["pt_leaky_w2"], np.float32).reshape(3, 3)
+    cce = lambda p_: float(-(t * np.log(p_.astype(np.float64))).sum(1).mean())  # noqa: E731
+    p = _pytorch_mlp_on_device(wrapper, x, t, w1, w2, ACT_LEAKY_RELU, 0.1, ACT_SOFTMAX, LOSS_CATEGORICAL_CROSSENTROPY, 0.1,
+                               0.66, 0.17, True, 2, epochs=0)
+    assert abs(cce(p) - golden["pt_leaky_loss_before"]) < 1e-6
+    p = _pytorch_mlp_on_device(wrapper, x, t, w1, w2, ACT_LEAKY_RELU, 0.1, ACT_SOFTMAX, LOSS_CATEGORICAL_CROSSENTROPY, 0.1,
+                               0.66, 0.17, True, 2)
+    assert abs(cce(p) - golden["pt_leaky_loss_after"]) < 1e-6

@@ -258,3 +258,63 @@ def test_mse_network_on_the_last_dimension_before_and_after_training(golden):
                                first_on_last_dim=True)
     np.testing.assert_allclose(before.ravel(), g["pred_before"], rtol=0, atol=1e-3)
     np.testing.assert_allclose(after.ravel(), g["pred_after"], rtol=0, atol=1e-3)
+
+
+# ---- PyTorch compatibility mode: [out, in] weights, weight decay dW += batch * wd * W and likewise for the bias
+#      (Prod/Layers/Linear.cs:167-181), after 10 epochs (Tests/NonReg/ParallelRunWithPyTorch.cs) ------------------
+def _train_pytorch_mlp(x, y_true, W1, W2, act1, alpha1, out_act, loss, lr, momentum, weight_decay, nesterov,
+                       batch_size, first_on_last_dim=False, epochs=10):
+    Ws, bs = [W1.copy(), W2.copy()], [np.zeros(W1.shape[0], np.float32), np.zeros(W2.shape[0], np.float32)]
+    vW, vb = [np.zeros_like(w) for w in Ws], [np.zeros_like(b) for b in bs]
+
+    def forward(xb):
+        h0 = xb.reshape(-1, W1.shape[1]) if first_on_last_dim else xb.reshape(xb.shape[0], -1)
+        z1, y1 = orc.dense_forward(h0, Ws[0], bs[0], act1, orc.W_OUT_IN, alpha=alpha1)
+        h1 = y1.reshape(xb.shape[0], -1)
+        z2, y2 = orc.dense_forward(h1, Ws[1], bs[1], out_act, orc.W_OUT_IN)
+        return h0, z1, y1, h1, y2
+    for _ in range(epochs):
+        for r0 in range(0, x.shape[0], batch_size):
+            xb, tb = x[r0:r0 + batch_size], y_true[r0:r0 + batch_size]
+            n = xb.shape[0]
+            h0, z1, y1, h1, p = forward(xb)
+            dy = orc.loss_gradient(loss, tb, p)
+            _, dW2, db2, dx = orc.dense_backward(h1, Ws[1], dy, orc.ACT_IDENTITY, None, None, 1.0, orc.W_OUT_IN)
+            _, dW1, db1, _ = orc.dense_backward(h0, Ws[0], dx.reshape(z1.shape), act1, y1, z1, 1.0, orc.W_OUT_IN,
+                                                need_dx=False, alpha=alpha1)
+            for W, b, dW, db, v, u in ((Ws[0], bs[0], dW1, db1, vW[0], vb[0]), (Ws[1], bs[1], dW2, db2, vW[1], vb[1])):
+                if weight_decay:
+                    orc.update_adding_alpha_x(dW, n * np.float32(weight_decay), W)
+                    orc.update_adding_alpha_x(db, n * np.float32(weight_decay), b)
+                orc.update_sgd_optimizer(W, lr / n, momentum, nesterov, dW, v)
+                orc.update_sgd_optimizer(b, lr / n, momentum, nesterov, db, u)
+    return lambda xb: forward(xb)[-1]
+
+
+def test_pytorch_layout_networks_after_training(golden):
+    cce = lambda t, p: float(-(t * np.log(p.astype(np.float64))).sum(1).mean())  # noqa: E731
+    # :179-214 Linear(16->3) + ReLU + Linear(3->3) + Sigmoid, BCE, SGD 0.1 momentum 0.9 weight decay 0.03
+    x, t = orc.numpy_array_for_tests(2, 1, 4, 4), orc.y_numpy_array_for_tests(2, 3)
+    w1 = np.asarray(golden["pt_relu_w1"], np.float32).reshape(3, 16)
+    w2 = np.asarray(golden["pt_relu_w2"], np.float32).reshape(3, 3)
+    predict = _train_pytorch_mlp(x, t, w1, w2, orc.ACT_RELU, 0.0, orc.ACT_SIGMOID, orc.LOSS_BINARY_CROSSENTROPY, 0.1, 0.9,
+                                 0.03, False, 2)
+    assert abs(orc.binary_crossentropy(t, predict(x)) - golden["pt_relu_loss_after"]) < 1e-6
+    # :102-138 Linear(5->3 on the last dimension) + ReLU + Flatten + Linear(36->3), Mse, SGD 0.1 momentum 0.9
+    x = orc.numpy_array_for_tests(2, 3, 4, 5)
+    w1 = np.asarray(golden["pt_mse_w1"], np.float32).reshape(3, 5)
+    w2 = np.asarray(golden["pt_mse_w2"], np.float32).reshape(3, 36)
+    predict = _train_pytorch_mlp(x, t, w1, w2, orc.ACT_RELU, 0.0, orc.ACT_IDENTITY, orc.LOSS_MSE, 0.1, 0.9, 0.0, False, 2,
+                                 first_on_last_dim=True)
+    assert abs(orc.mse(t, predict(x)) - golden["pt_mse_loss_after"]) < 1e-6
+    # :813-850 Linear(16->3) + LeakyRelu(0.1) + Linear(3->3) + Softmax on 10 rows in batches of 2,
+    # CategoricalCrossentropy, SGD 0.1 momentum 0.66 weight decay 0.17 with Nesterov
+    x, t = orc.numpy_array_for_tests(10, 1, 4, 4), orc.y_numpy_array_for_tests(10, 3)
+    w1 = np.asarray(golden["pt_leaky_w1"], np.float32).reshape(3, 16)
+    w2 = np.asarray(golden["pt_leaky_w2"], np.float32).reshape(3, 3)
+    before = _train_pytorch_mlp(x, t, w1, w2, orc.ACT_LEAKY_RELU, 0.1, orc.ACT_SOFTMAX, orc.LOSS_CATEGORICAL_CROSSENTROPY,
+                                0.1, 0.66, 0.17, True, 2, epochs=0)
+    assert abs(cce(t, before(x)) - golden["pt_leaky_loss_before"]) < 1e-6
+    predict = _train_pytorch_mlp(x, t, w1, w2, orc.ACT_LEAKY_RELU, 0.1, orc.ACT_SOFTMAX, orc.LOSS_CATEGORICAL_CROSSENTROPY,
+                                 0.1, 0.66, 0.17, True, 2)
+    assert abs(cce(t, predict(x)) - golden["pt_leaky_loss_after"]) < 1e-6
