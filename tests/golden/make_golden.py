@@ -16,6 +16,9 @@ Sources (paths inside the reference):
   Tests/NonReg/TestNetworkPropagation.cs:500-575 attention block: predictions before training, plain and causal
   Tests/NonReg/TestNetworkPropagation.cs:580-623 MultiHeadAttention (3 heads x 5, [in,out] weights): predictions before
                                                  training and after 10 epochs of SGD with momentum, plain and causal
+  Tests/NonReg/ParallelRunWithPyTorch.cs:963-1010 ScaledDotProductAttention without scaling ([out,in] weights), plain and
+                                                 causal: CategoricalCrossentropy loss before training and after 10 epochs
+                                                 of SGD with momentum and weight decay in batches of 2
   Tests/NonReg/ParallelRunWithPyTorch.cs:1013-1129 MultiHeadAttention (3 heads x 2, [out,in] weights), with and without
                                                  bias, plain and causal: CategoricalCrossentropy loss before training
                                                  and after 10 epochs of SGD with momentum in batches of 2
@@ -178,6 +181,16 @@ def main(ref):
             "cases": [{"causal": c[0] == "true", "loss_before": float(c[1]), "loss_after": float(c[2])}
                       for c in re.findall(r"\[TestCase\((\w+), ([0-9.]+), ([0-9.]+)\)", head)],
         }
+    # :963-1010 Conv1D(k=1) Q/K/V ([2 out, 4 in, 1]) -> ScaledDotProductAttention(no scaling, plain / causal) -> Flatten ->
+    # Linear(10 -> 3, [out, in]) -> Softmax on X = numpy_array_for_tests(6, 4, 5): CategoricalCrossentropy before training
+    # and after 10 epochs of SGD (lr 0.1, momentum 0.9, weight decay 0.07) in batches of 2
+    i = pt.index("public void Test_DotProductAttention(")
+    blk = pt[i:pt.index("Train(model, X, Y)", i)]
+    head = pt[pt.rindex("[TestCase(false", 0, i):i]
+    lits = [_numbers(c) for c in re.findall(r'FromNumpyArray\("(\[\[.*?\]\])"\)\.CopyTo', blk)]
+    out["sdpa_pt"] = {"conv_q": lits[0], "conv_k": lits[1], "conv_v": lits[2], "w_linear": lits[3],
+                      "cases": [{"causal": c[0] == "true", "loss_before": float(c[1]), "loss_after": float(c[2])}
+                                for c in re.findall(r"\[TestCase\((\w+), ([0-9.]+), ([0-9.]+)\)", head)]}
     blk = _between(pt, "public void TestParallelRunWithPyTorch_Mse()", "public void TestParallelRunWithPyTorch_Mse_AdamW")
     out["pt_mse_w1"] = _nth_numpy_literal(blk, 0)         # [3, 5]  = [out, in]
     out["pt_mse_w2"] = _nth_numpy_literal(blk, 1)         # [3, 36]

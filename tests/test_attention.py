@@ -481,6 +481,121 @@ class _MhaNet:
         return [slice(s, s + self.batch) for s in range(0, self.B, self.batch)]
 
 
+class _SdpaPtNet:
+    """Tests/NonReg/ParallelRunWithPyTorch.cs:963-1010: X [6, 4 channels, 5] -> three Conv1D(kernel 1, 2 filters,
+    [out, in, 1], with bias) -> ScaledDotProductAttention(no scaling) on Q, K, V [n, 2 steps, 5] -> Flatten ->
+    Linear(10 -> 3, [out, in]) -> Softmax; CategoricalCrossentropy; SGD lr 0.1, momentum 0.9, weight decay 0.07 in the
+    PyTorch compatibility mode (every gradient, biases included, gets + batch * wd * parameter:
+    Prod/Layers/Linear.cs:167-181, ConvolutionLayer.cs:210-220); batches of 2."""
+    lr, momentum, wd, batch = 0.1, 0.9, 0.07, 2
+
+    def __init__(self, golden, case):
+        g = golden["sdpa_pt"]
+        self.causal = case["causal"]
+        self.conv_w = [np.asarray(g[k], np.float64).reshape(2, 4) for k in ("conv_q", "conv_k", "conv_v")]
+        self.conv_b = [np.zeros(2) for _ in range(3)]
+        self.lin_w, self.lin_b = np.asarray(g["w_linear"], np.float64).reshape(3, 10), np.zeros(3)
+        self.X = orc.numpy_array_for_tests(6, 4, 5).astype(np.float64)
+        self.Y = orc.y_numpy_array_for_tests(6, 3).astype(np.float64)
+
+    def params(self):
+        return self.conv_w + self.conv_b + [self.lin_w, self.lin_b]
+
+    def conv_forward(self, Xb):
+        return [np.stack([w @ x + b[:, None] for x in Xb]) for w, b in zip(self.conv_w, self.conv_b)]   # [n, 2, 5] each
+
+    def conv_gradients(self, Xb, dQKV):
+        return ([sum(d[i] @ Xb[i].T for i in range(len(Xb))) for d in dQKV], [d.sum((0, 2)) for d in dQKV])
+
+    def batches(self):
+        return [slice(s, s + self.batch) for s in range(0, 6, self.batch)]
+
+    def loss(self, p):
+        return float(-(self.Y * np.log(p)).sum(1).mean())
+
+    def step(self, grads, vel, n):
+        params = self.params()
+        for p, g in zip(params, grads):
+            g += n * self.wd * p
+        _sgd_momentum(params, grads, vel, self.lr / n, self.momentum)
+
+
+def _sdpa_pt_train_with_oracle(net, epochs=10):
+    vel = [np.zeros_like(p) for p in net.params()]
+
+    def forward(Xb):
+        Q, K, V = net.conv_forward(Xb)
+        w, y = orc.sdpa_forward(Q, K, V, False, net.causal, f64=True)
+        flat = y.reshape(len(Xb), -1)
+        return (Q, K, V), w, flat, _softmax64(flat @ net.lin_w.T + net.lin_b)
+    for _ in range(epochs):
+        for sl in net.batches():
+            Xb, Yb = net.X[sl], net.Y[sl]
+            (Q, K, V), w, flat, p = forward(Xb)
+            dz = p - Yb
+            dflat = dz @ net.lin_w
+            dQ, dK, dV = orc.sdpa_backward(Q, K, V, dflat.reshape(len(Xb), 2, 5), w, False)
+            d_conv_w, d_conv_b = net.conv_gradients(Xb, (dQ, dK, dV))
+            net.step(d_conv_w + d_conv_b + [dz.T @ flat, dz.sum(0)], vel, len(Xb))
+    return forward(net.X)[3]
+
+
+def test_oracle_attention_training_matches_reference_goldens_pytorch_layout(golden):
+    for case in golden["sdpa_pt"]["cases"]:
+        net = _SdpaPtNet(golden, case)
+        assert abs(net.loss(_sdpa_pt_train_with_oracle(net, 0)) - case["loss_before"]) <= 1e-6
+        assert abs(net.loss(_sdpa_pt_train_with_oracle(net)) - case["loss_after"]) <= 1e-6
+
+
+@pytest.mark.gpu
+def test_gpu_attention_training_matches_reference_goldens_pytorch_layout(wrapper, golden):
+    # the same replay with the attention core (snb200_sdpa_fwd / _bwd), the output Dense layer, the loss gradient, the
+    # weight decay and the momentum updates on the device
+    from sharpnet_b200._capi import ACT_SOFTMAX, LOSS_CATEGORICAL_CROSSENTROPY
+    from sharpnet_b200.attention import (ScaledDotProductAttentionBackwardPropagation,
+                                         ScaledDotProductAttentionForwardPropagation)
+    from sharpnet_b200.linear import FusedDenseBackwardFromLoss, FusedDenseForward
+    from sharpnet_b200.tensor import GPUTensor
+    T = lambda a: GPUTensor(np.shape(a), np.asarray(a, np.float32), wrapper)  # noqa: E731
+    for case in golden["sdpa_pt"]["cases"]:
+        net = _SdpaPtNet(golden, case)
+        lin_w, lin_b = T(net.lin_w), T(net.lin_b)
+        d_lin_w, d_lin_b = GPUTensor((3, 10), None, wrapper), GPUTensor((3,), None, wrapper)
+        v_w, v_b = GPUTensor((3, 10), None, wrapper), GPUTensor((3,), None, wrapper)
+        conv_params = net.conv_w + net.conv_b
+        conv_vel = [np.zeros_like(p) for p in conv_params]
+
+        def forward(Xb):
+            n = len(Xb)
+            Q, K, V = (T(a) for a in net.conv_forward(Xb))
+            y = GPUTensor((n, 2, 5), None, wrapper)
+            W = ScaledDotProductAttentionForwardPropagation(Q, K, V, y, True, None, False, net.causal)
+            p = GPUTensor((n, 3), None, wrapper)
+            FusedDenseForward(p, y.Reshape(n, 10), lin_w, lin_b, ACT_SOFTMAX, None, W_OUT_IN)
+            return (Q, K, V), W, y, p
+        assert abs(net.loss(forward(net.X)[3].ContentAsFloatArray().astype(np.float64)) - case["loss_before"]) <= 1e-6
+        for _ in range(10):
+            for sl in net.batches():
+                Xb, n = net.X[sl], net.batch
+                (Q, K, V), W, y, p = forward(Xb)
+                dflat, dz = GPUTensor((n, 10), None, wrapper), GPUTensor((n, 3), None, wrapper)
+                FusedDenseBackwardFromLoss(dflat, d_lin_w, d_lin_b, y.Reshape(n, 10), T(net.Y[sl]), p, lin_w,
+                                           LOSS_CATEGORICAL_CROSSENTROPY, 1.0, dz, W_OUT_IN)
+                dQ, dK, dV = (GPUTensor((n, 2, 5), None, wrapper) for _ in range(3))
+                ScaledDotProductAttentionBackwardPropagation(dQ, dK, dV, Q, K, V, dflat.Reshape(n, 2, 5), W, False)
+                d_conv_w, d_conv_b = net.conv_gradients(Xb, [t.ContentAsFloatArray().astype(np.float64) for t in (dQ, dK, dV)])
+                grads = d_conv_w + d_conv_b
+                for prm, g in zip(conv_params, grads):
+                    g += n * net.wd * prm
+                _sgd_momentum(conv_params, grads, conv_vel, net.lr / n, net.momentum)
+                d_lin_w.Update_Adding_Alpha_X(n * net.wd, lin_w)
+                d_lin_b.Update_Adding_Alpha_X(n * net.wd, lin_b)
+                lin_w.UpdateSGDOptimizer(net.lr / n, net.momentum, False, d_lin_w, v_w)
+                lin_b.UpdateSGDOptimizer(net.lr / n, net.momentum, False, d_lin_b, v_b)
+        wrapper.check_device_status()
+        assert abs(net.loss(forward(net.X)[3].ContentAsFloatArray().astype(np.float64)) - case["loss_after"]) <= 1e-6
+
+
 def _sgd_momentum(params, grads, velocities, lr, momentum):
     for p, g, v in zip(params, grads, velocities):
         v[...] = momentum * v - lr * g            # Prod/Optimizers/Sgd.cs:43-52, Prod/CPU/CpuTensor.cs:470-489
