@@ -217,6 +217,15 @@ def test_activations_and_axpy(wrapper):
             DX.ActivationBackward(act, alpha, DY, X, Y)
             np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, alpha or 0.0),
                                        rtol=2e-6, atol=1e-6)
+        # the coefficients the reference's own CPU-versus-GPU cases use (Tests/TestParallelRunCpuVersusGpu.cs:761-763,811-813)
+        for act, alpha in ((ACT_LEAKY_RELU, 0.1), (ACT_LEAKY_RELU, 0.3), (ACT_ELU, 0.0), (ACT_ELU, 1.0)):
+            Y, DX = GPUTensor(shape, None, wrapper), GPUTensor(shape, None, wrapper)
+            X.ActivationForward(act, alpha, Y)
+            y = Y.ContentAsFloatArray()
+            np.testing.assert_allclose(y, orc.activation_forward(act, x, alpha), rtol=1e-6, atol=1e-7)
+            DX.ActivationBackward(act, alpha, DY, X, Y)
+            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, alpha), rtol=2e-6,
+                                       atol=1e-6)
         Yv = _t(wrapper, dy)
         Yv.Update_Adding_Alpha_X(0.25, X)
         np.testing.assert_allclose(Yv.ContentAsFloatArray(), orc.update_adding_alpha_x(dy.copy(), 0.25, x), rtol=0,
