@@ -62,6 +62,8 @@ enum {
   SNB200_ACT_SWISH = 6,
   /* x >= 0 ? x : alpha * x, alpha from snb200_set_activation_parameter */
   SNB200_ACT_LEAKY_RELU = 1002,
+  /* x <= 0 ? -100 : log(x); its gradient dy / x needs the input (Prod/CPU/CpuTensorActivationFunctions.cs:170-180) */
+  SNB200_ACT_LN = 1004,
   /* snb200_dense_fwd only: y = softmax over every row of x * op(W) + bias, a Linear layer followed by an
    * ActivationLayer with CUDNN_ACTIVATION_SOFTMAX (Prod/GPU/GpuTensor.cs:411-413 -> cudnnSoftmaxForward): the output
    * layer of every classification network.  Its gradient enters through snb200_dense_bwd_from_loss. */

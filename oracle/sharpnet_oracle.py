@@ -26,6 +26,7 @@ import torch
 # cudnnActivationMode_t values (Prod/GPU/CudnnWrapper.cs:267-281)
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
 ACT_ELU, ACT_LEAKY_RELU = 4, 1002   # CUDNN_ACTIVATION_ELU / _LEAKY_RELU (Prod/GPU/CudnnWrapper.cs:273,277): take an alpha
+ACT_LN = 1004                       # CUDNN_ACTIVATION_LN (:279)
 ACT_SOFTMAX = 1000          # CUDNN_ACTIVATION_SOFTMAX (Prod/GPU/CudnnWrapper.cs:276): softmax over every row
 W_OUT_IN, W_IN_OUT = 0, 1
 LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
@@ -125,6 +126,9 @@ def activation_forward(act, x, alpha=0.0):
     (:152-156, Prod/Utils.cs:888-891), Tanh is MathF.Tanh (:184-189), Relu is max(0, x) (:198-201),
     LeakyRelu is x or (float)alpha * x (:210-213), Elu is x or (float)(alpha * (exp(x) - 1)) through double (:223-226)."""
     x = np.asarray(x, dtype=np.float32)
+    if act == ACT_LN:                                    # x <= 0 ? -100 : MathF.Log(x)  (:170-174)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            return np.where(x <= 0, np.float32(-100), np.log(x)).astype(np.float32)
     if act == ACT_LEAKY_RELU:
         return np.where(x >= 0, x, np.float32(alpha) * x).astype(np.float32)
     if act == ACT_ELU:
@@ -152,6 +156,8 @@ def activation_backward(act, dy, x, y, alpha=0.0):
     :240-244 Sigmoid, :214-219 LeakyRelu from y, :227-231 Elu from x and y)."""
     dy = np.asarray(dy, dtype=np.float32)
     one = np.float32(1)
+    if act == ACT_LN:                                    # dy / x  (:176-180)
+        return (dy / np.asarray(x, dtype=np.float32)).astype(np.float32)
     if act == ACT_LEAKY_RELU:
         return np.where(np.asarray(y) >= 0, dy, np.float32(alpha) * dy).astype(np.float32)
     if act == ACT_ELU:

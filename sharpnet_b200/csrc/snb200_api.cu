@@ -1199,7 +1199,7 @@ extern "C" int snb200_gemm(snb200_handle_t h, int transA, int transB, int aH, in
 // ------------------------------------------------------------------------------------ Dense
 static bool act_supported(int act) {
   return act == ACT_SIGMOID || act == ACT_RELU || act == ACT_TANH || act == ACT_IDENTITY || act == ACT_SWISH ||
-         act == ACT_ELU || act == ACT_LEAKY_RELU;
+         act == ACT_ELU || act == ACT_LEAKY_RELU || act == ACT_LN;
 }
 
 static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,
@@ -1420,7 +1420,7 @@ static int dense_bwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, 
   const float* dz = dy;
   if (act != ACT_IDENTITY) {
     if (!y) return fail(h, SNB200_STATUS_INVALID_VALUE, "activation output y is required for this activation");
-    if (act_needs_input(act) && !z) return fail(h, SNB200_STATUS_INVALID_VALUE, "pre-activation z is required for SWISH and ELU");
+    if (act_needs_input(act) && !z) return fail(h, SNB200_STATUS_INVALID_VALUE, "pre-activation z is required for SWISH, ELU and LN");
     if (!dz_scratch) return fail(h, SNB200_STATUS_INVALID_VALUE, "dz_scratch is required for this activation");
     if (M > 0 && N > 0) {
       st = launch_colsum<true>(h, M, N, act, dy, y, z, dz_scratch, db);   // dz and db in one pass over dy

@@ -7,7 +7,7 @@ import pytest
 from oracle import sharpnet_oracle as orc
 from sharpnet_b200 import (ACT_ELU, ACT_IDENTITY, ACT_LEAKY_RELU, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH, MATH_3XTF32,
                            MATH_TF32, W_IN_OUT, W_OUT_IN)
-from sharpnet_b200._capi import TUNE_CLUSTER, TUNE_FORCE_PATH
+from sharpnet_b200._capi import ACT_LN, TUNE_CLUSTER, TUNE_FORCE_PATH
 from sharpnet_b200._capi import LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE
 from sharpnet_b200.linear import (DenseBackwardPropagation, DenseForwardPropagation, FusedDenseBackward,
                                   FusedDenseBackwardFromLoss, FusedDenseForward)
@@ -218,13 +218,13 @@ def test_activations_and_axpy(wrapper):
             np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, alpha or 0.0),
                                        rtol=2e-6, atol=1e-6)
         # the coefficients the reference's own CPU-versus-GPU cases use (Tests/TestParallelRunCpuVersusGpu.cs:761-763,811-813)
-        for act, alpha in ((ACT_LEAKY_RELU, 0.1), (ACT_LEAKY_RELU, 0.3), (ACT_ELU, 0.0), (ACT_ELU, 1.0)):
+        for act, alpha in ((ACT_LEAKY_RELU, 0.1), (ACT_LEAKY_RELU, 0.3), (ACT_ELU, 0.0), (ACT_ELU, 1.0), (ACT_LN, None)):
             Y, DX = GPUTensor(shape, None, wrapper), GPUTensor(shape, None, wrapper)
             X.ActivationForward(act, alpha, Y)
             y = Y.ContentAsFloatArray()
-            np.testing.assert_allclose(y, orc.activation_forward(act, x, alpha), rtol=1e-6, atol=1e-7)
+            np.testing.assert_allclose(y, orc.activation_forward(act, x, alpha or 0.0), rtol=1e-6, atol=1e-7)
             DX.ActivationBackward(act, alpha, DY, X, Y)
-            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, alpha), rtol=2e-6,
+            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, alpha or 0.0), rtol=2e-6,
                                        atol=1e-6)
         Yv = _t(wrapper, dy)
         Yv.Update_Adding_Alpha_X(0.25, X)
