@@ -56,7 +56,11 @@ enum {
   SNB200_ACT_SIGMOID = 0,
   SNB200_ACT_RELU = 1,
   SNB200_ACT_TANH = 2,
-  /* x >= 0 ? x : alpha * (exp(x) - 1), alpha from snb200_set_activation_parameter (the layer's activationParameter) */
+  /* min(max(x, 0), 1): the reference creates its cuDNN descriptors with coefficient 1.0 (Prod/GPU/GPUWrapper.cs:183) */
+  SNB200_ACT_CLIPPED_RELU = 3,
+  /* x >= 0 ? x : alpha * (exp(x) - 1), alpha from snb200_set_activation_parameter.  The reference itself always runs
+   * ELU with alpha 1 (Prod/CPU/CpuTensor.cs:954,1000; the cuDNN descriptor of Prod/GPU/GPUWrapper.cs:183): a binding
+   * sets 1.0 before an ELU call. */
   SNB200_ACT_ELU = 4,
   SNB200_ACT_IDENTITY = 5,
   SNB200_ACT_SWISH = 6,

@@ -27,6 +27,8 @@ import torch
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
 ACT_ELU, ACT_LEAKY_RELU = 4, 1002   # CUDNN_ACTIVATION_ELU / _LEAKY_RELU (Prod/GPU/CudnnWrapper.cs:273,277): take an alpha
 ACT_LN = 1004                       # CUDNN_ACTIVATION_LN (:279)
+ACT_CLIPPED_RELU = 3                # CUDNN_ACTIVATION_CLIPPED_RELU (:272); the reference has no CPU code for it:
+                                    # cuDNN's definition min(max(x, 0), coef) with the coef 1.0 of Prod/GPU/GPUWrapper.cs:183
 ACT_SOFTMAX = 1000          # CUDNN_ACTIVATION_SOFTMAX (Prod/GPU/CudnnWrapper.cs:276): softmax over every row
 W_OUT_IN, W_IN_OUT = 0, 1
 LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2
@@ -135,6 +137,8 @@ def activation_forward(act, x, alpha=0.0):
         return np.where(x >= 0, x, (float(alpha) * (np.exp(x.astype(np.float64)) - 1.0)).astype(np.float32)).astype(np.float32)
     if act == ACT_RELU:
         return np.maximum(x, np.float32(0))
+    if act == ACT_CLIPPED_RELU:
+        return np.minimum(np.maximum(x, np.float32(0)), np.float32(1))
     if act == ACT_SWISH:
         xd = x.astype(np.float64)
         return (xd / (1.0 + np.exp(-xd))).astype(np.float32)
@@ -164,6 +168,9 @@ def activation_backward(act, dy, x, y, alpha=0.0):
         return np.where(np.asarray(x) >= 0, dy, dy * (np.asarray(y, dtype=np.float32) + np.float32(alpha))).astype(np.float32)
     if act == ACT_RELU:
         return np.where(y > 0, dy, np.float32(0)).astype(np.float32)
+    if act == ACT_CLIPPED_RELU:
+        y = np.asarray(y)
+        return np.where((y > 0) & (y < 1), dy, np.float32(0)).astype(np.float32)
     if act == ACT_SWISH:
         x = np.asarray(x, dtype=np.float32)
         with np.errstate(divide="ignore", invalid="ignore"):
@@ -416,6 +423,11 @@ def _act_f64(act, z, alpha=0.0):
         return np.where(z >= 0, z, alpha * (np.exp(np.minimum(z, 0.0)) - 1.0))
     if act == ACT_RELU:
         return np.maximum(z, 0.0)
+    if act == ACT_CLIPPED_RELU:
+        return np.minimum(np.maximum(z, 0.0), 1.0)
+    if act == ACT_LN:
+        with np.errstate(divide="ignore", invalid="ignore"):
+            return np.where(z <= 0, -100.0, np.log(z))
     if act == ACT_SWISH:
         return z / (1.0 + np.exp(-z))
     if act == ACT_SIGMOID:
@@ -436,6 +448,10 @@ def _act_bwd_f64(act, dy, z, y, alpha=0.0):
         return np.where(np.asarray(z) >= 0, dy, dy * (np.asarray(y, dtype=np.float64) + alpha))
     if act == ACT_RELU:
         return np.where(np.asarray(y) > 0, dy, 0.0)
+    if act == ACT_CLIPPED_RELU:
+        return np.where((np.asarray(y) > 0) & (np.asarray(y) < 1), dy, 0.0)
+    if act == ACT_LN:
+        return dy / np.asarray(z, dtype=np.float64)
     if act == ACT_SWISH:
         zd = np.asarray(z, dtype=np.float64)
         s = 1.0 / (1.0 + np.exp(-zd))

@@ -17,6 +17,7 @@ MATH_3XTF32, MATH_TF32, MATH_FP32_SIMT, MATH_TF32_BF16X2 = 0, 1, 2, 3
 ACT_SIGMOID, ACT_RELU, ACT_TANH, ACT_IDENTITY, ACT_SWISH = 0, 1, 2, 5, 6
 ACT_ELU, ACT_LEAKY_RELU = 4, 1002   # take a coefficient: snb200_set_activation_parameter
 ACT_LN = 1004
+ACT_CLIPPED_RELU = 3                # ceiling 1.0, as the reference's cuDNN descriptors have it
 ACT_SOFTMAX = 1000   # snb200_dense_fwd only
 W_OUT_IN, W_IN_OUT = 0, 1
 LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE = 0, 1, 2

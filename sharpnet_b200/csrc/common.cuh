@@ -23,7 +23,10 @@ __device__ __forceinline__ void pdl_prologue() {
 
 // Values of cudnnActivationMode_t (Prod/GPU/CudnnWrapper.cs:267-281).
 // ELU and LEAKY_RELU take a coefficient (the layer's activationParameter); it travels beside the code as act_alpha.
-enum Act : int { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_ELU = 4, ACT_IDENTITY = 5, ACT_SWISH = 6, ACT_LEAKY_RELU = 1002, ACT_LN = 1004 };
+enum Act : int { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_CLIPPED_RELU = 3, ACT_ELU = 4, ACT_IDENTITY = 5, ACT_SWISH = 6, ACT_LEAKY_RELU = 1002, ACT_LN = 1004 };
+// The reference builds every cuDNN activation descriptor with coefficient 1.0 (Prod/GPU/GPUWrapper.cs:183):
+// its ClippedRelu is min(max(x, 0), 1).
+#define SNB_CLIPPED_RELU_CEILING 1.0f
 __host__ __device__ __forceinline__ bool act_needs_input(int act) { return act == ACT_SWISH || act == ACT_ELU || act == ACT_LN; }   // ActivationLayer.cs:73
 // Internal selector of the fused column-sum pass: dz = scale * (yPredicted - yExpected), the gradient of
 // the BinaryCrossentropy / CategoricalCrossentropy / Mse losses (Prod/Data/Tensor.cs:1379-1395,
@@ -75,6 +78,7 @@ __device__ __forceinline__ float act_forward(int act, float v, float a = 0.0f) {
   // Formulas of Prod/CPU/CpuTensorActivationFunctions.cs:152-244 and Prod/Utils.cs:888-891.
   switch (act) {
     case ACT_RELU: return fmaxf(v, 0.0f);
+    case ACT_CLIPPED_RELU: return fminf(fmaxf(v, 0.0f), SNB_CLIPPED_RELU_CEILING);
     case ACT_LEAKY_RELU: return v >= 0.0f ? v : a * v;                 // :210-213
     case ACT_LN: return v <= 0.0f ? -100.0f : logf(v);                   // :170-174
     case ACT_ELU: return v >= 0.0f ? v : a * expm1f(v);                // :223-226 (alpha * (exp(x) - 1), in double there)
@@ -99,6 +103,7 @@ __device__ __forceinline__ float act_forward_compact(int act, float v, float a =
 __device__ __forceinline__ float act_backward(int act, float dy, float x, float y, float a = 0.0f) {
   switch (act) {
     case ACT_RELU: return y > 0.0f ? dy : 0.0f;                       // CpuTensorActivationFunctions.cs:202-206
+    case ACT_CLIPPED_RELU: return (y > 0.0f && y < SNB_CLIPPED_RELU_CEILING) ? dy : 0.0f;   // open interval: flat at both clips
     case ACT_LEAKY_RELU: return y >= 0.0f ? dy : a * dy;              // :214-219
     case ACT_ELU: return x >= 0.0f ? dy : dy * (y + a);               // :227-231
     case ACT_LN: return dy / x;                                       // :176-180

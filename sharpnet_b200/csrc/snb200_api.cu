@@ -1199,7 +1199,7 @@ extern "C" int snb200_gemm(snb200_handle_t h, int transA, int transB, int aH, in
 // ------------------------------------------------------------------------------------ Dense
 static bool act_supported(int act) {
   return act == ACT_SIGMOID || act == ACT_RELU || act == ACT_TANH || act == ACT_IDENTITY || act == ACT_SWISH ||
-         act == ACT_ELU || act == ACT_LEAKY_RELU || act == ACT_LN;
+         act == ACT_ELU || act == ACT_LEAKY_RELU || act == ACT_LN || act == ACT_CLIPPED_RELU;
 }
 
 static int dense_fwd_impl(snb200_handle_t h, int w_layout, int M, int K, int N, const float* x, const float* W,

@@ -91,6 +91,11 @@ class GPUWrapper:
             GPUWrapper._cache.pop(self.device_id, None)
 
 
+def _reference_coefficient(activationType, activationParameter):
+    """The coefficient SharpNet itself would run this activation with: 1 for ELU, the layer's parameter otherwise."""
+    return 1.0 if int(activationType) == _capi.ACT_ELU else activationParameter
+
+
 def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
@@ -209,8 +214,11 @@ class GPUTensor:
 
     def ActivationForward(self, activationType, activationParameter, y):
         """y = act(this)   (Prod/Data/Tensor.cs:618, Prod/GPU/GpuTensor.cs:397-443).  ``activationParameter``: the
-        coefficient of ELU / LeakyRelu (a number here, a one-element tensor in SharpNet)."""
+        coefficient of LeakyRelu (a number here, a one-element tensor in SharpNet).  ELU runs with coefficient 1
+        whatever the parameter says, as in SharpNet (Prod/CPU/CpuTensor.cs:954; the cuDNN descriptor of
+        Prod/GPU/GPUWrapper.cs:183)."""
         w = self.wrapper
+        activationParameter = _reference_coefficient(activationType, activationParameter)
         if activationParameter is not None:
             w.set_activation_parameter(activationParameter)
         check(w.handle, w.lib.snb200_activation_fwd(w.handle, int(activationType), self.Count, self.Pointer, y.Pointer))
@@ -218,6 +226,7 @@ class GPUTensor:
     def ActivationBackward(self, activationType, activationParameter, dy, x, y):
         """this = dx = act'(x, y) * dy   (Prod/Data/Tensor.cs:628, Prod/GPU/GpuTensor.cs:445-490)."""
         w = self.wrapper
+        activationParameter = _reference_coefficient(activationType, activationParameter)   # ELU: 1 (CpuTensor.cs:1000)
         if activationParameter is not None:
             w.set_activation_parameter(activationParameter)
         check(w.handle, w.lib.snb200_activation_bwd(

@@ -7,7 +7,7 @@ import pytest
 from oracle import sharpnet_oracle as orc
 from sharpnet_b200 import (ACT_ELU, ACT_IDENTITY, ACT_LEAKY_RELU, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH, MATH_3XTF32,
                            MATH_TF32, W_IN_OUT, W_OUT_IN)
-from sharpnet_b200._capi import ACT_LN, TUNE_CLUSTER, TUNE_FORCE_PATH
+from sharpnet_b200._capi import ACT_CLIPPED_RELU, ACT_LN, TUNE_CLUSTER, TUNE_FORCE_PATH
 from sharpnet_b200._capi import LOSS_BINARY_CROSSENTROPY, LOSS_CATEGORICAL_CROSSENTROPY, LOSS_MSE
 from sharpnet_b200.linear import (DenseBackwardPropagation, DenseForwardPropagation, FusedDenseBackward,
                                   FusedDenseBackwardFromLoss, FusedDenseForward)
@@ -16,7 +16,7 @@ from sharpnet_b200.tensor import GPUTensor
 from gpu_util import TOL_3XTF32, TOL_TF32
 
 pytestmark = pytest.mark.gpu
-ACTS = [ACT_IDENTITY, ACT_RELU, ACT_SWISH, ACT_TANH, ACT_SIGMOID, ACT_ELU, ACT_LEAKY_RELU]
+ACTS = [ACT_IDENTITY, ACT_RELU, ACT_SWISH, ACT_TANH, ACT_SIGMOID, ACT_ELU, ACT_LEAKY_RELU, ACT_CLIPPED_RELU]
 ALPHA = {ACT_ELU: 0.7, ACT_LEAKY_RELU: 0.3}      # the coefficient the parametric activations are tested with
 
 
@@ -211,21 +211,33 @@ def test_activations_and_axpy(wrapper):
         for act in ACTS:
             Y, DX = GPUTensor(shape, None, wrapper), GPUTensor(shape, None, wrapper)
             alpha = ALPHA.get(act)
+            ref_alpha = 1.0 if act == ACT_ELU else alpha or 0.0   # Elu runs with 1 whatever the parameter (CpuTensor.cs:954)
             X.ActivationForward(act, alpha, Y)
             y = Y.ContentAsFloatArray()
-            np.testing.assert_allclose(y, orc.activation_forward(act, x, alpha or 0.0), rtol=1e-6, atol=1e-7)
+            np.testing.assert_allclose(y, orc.activation_forward(act, x, ref_alpha), rtol=1e-6, atol=1e-7)
             DX.ActivationBackward(act, alpha, DY, X, Y)
-            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, alpha or 0.0),
+            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, ref_alpha),
                                        rtol=2e-6, atol=1e-6)
         # the coefficients the reference's own CPU-versus-GPU cases use (Tests/TestParallelRunCpuVersusGpu.cs:761-763,811-813)
         for act, alpha in ((ACT_LEAKY_RELU, 0.1), (ACT_LEAKY_RELU, 0.3), (ACT_ELU, 0.0), (ACT_ELU, 1.0), (ACT_LN, None)):
             Y, DX = GPUTensor(shape, None, wrapper), GPUTensor(shape, None, wrapper)
+            ref_alpha = 1.0 if act == ACT_ELU else alpha or 0.0
             X.ActivationForward(act, alpha, Y)
             y = Y.ContentAsFloatArray()
-            np.testing.assert_allclose(y, orc.activation_forward(act, x, alpha or 0.0), rtol=1e-6, atol=1e-7)
+            np.testing.assert_allclose(y, orc.activation_forward(act, x, ref_alpha), rtol=1e-6, atol=1e-7)
             DX.ActivationBackward(act, alpha, DY, X, Y)
-            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, alpha or 0.0), rtol=2e-6,
+            np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, ref_alpha), rtol=2e-6,
                                        atol=1e-6)
+            # the C entry points themselves take any coefficient
+            for coefficient in ((0.7, 0.25) if act in (ACT_ELU, ACT_LEAKY_RELU) else ()):
+                wrapper.set_activation_parameter(coefficient)
+                lib, h = wrapper.lib, wrapper.handle
+                assert lib.snb200_activation_fwd(h, act, X.Count, X.Pointer, Y.Pointer) == 0
+                y = Y.ContentAsFloatArray()
+                np.testing.assert_allclose(y, orc.activation_forward(act, x, coefficient), rtol=1e-6, atol=1e-7)
+                assert lib.snb200_activation_bwd(h, act, X.Count, DY.Pointer, X.Pointer, Y.Pointer, DX.Pointer) == 0
+                np.testing.assert_allclose(DX.ContentAsFloatArray(), orc.activation_backward(act, dy, x, y, coefficient),
+                                           rtol=2e-6, atol=1e-6)
         Yv = _t(wrapper, dy)
         Yv.Update_Adding_Alpha_X(0.25, X)
         np.testing.assert_allclose(Yv.ContentAsFloatArray(), orc.update_adding_alpha_x(dy.copy(), 0.25, x), rtol=0,
@@ -236,7 +248,7 @@ def test_dense_argument_errors(wrapper):
     lib, h = wrapper.lib, wrapper.handle
     T = GPUTensor((4, 4), None, wrapper)
     assert lib.snb200_dense_fwd(h, 2, 4, 4, 4, T.Pointer, T.Pointer, None, ACT_RELU, None, T.Pointer) == 7
-    assert lib.snb200_dense_fwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, None, 3, None, T.Pointer) == 15   # CLIPPED_RELU is not built
+    assert lib.snb200_dense_fwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, None, 7, None, T.Pointer) == 15   # not an activation of the reference
     # Swish backward without the pre-activation
     assert lib.snb200_dense_bwd(h, 0, 4, 4, 4, T.Pointer, T.Pointer, T.Pointer, ACT_SWISH, T.Pointer, None, 1.0,
                                 T.Pointer, None, T.Pointer, None) == 7
