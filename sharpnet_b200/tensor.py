@@ -88,7 +88,8 @@ class GPUWrapper:
         if self.handle is not None:
             self.lib.snb200_destroy(self.handle)
             self.handle = None
-            GPUWrapper._cache.pop(self.device_id, None)
+            if GPUWrapper._cache.get(self.device_id) is self:
+                del GPUWrapper._cache[self.device_id]
 
 
 def _reference_coefficient(activationType, activationParameter):

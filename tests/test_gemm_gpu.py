@@ -512,3 +512,52 @@ def test_seeded_sweep_over_shapes_and_plans(wrapper):
     # the draw reaches every family of plans
     for family in ("clusterk2", "clusterk4", "swapAB", "splitk", "swload", "realigned", "umma2_", "simt"):
         assert any(family in k for k in kernels), (family, sorted(kernels))
+
+
+def test_two_handles_on_two_host_threads(built_library):
+    """Handles are independent of one another: each owns its workspace, its tensor-map cache, its error word and its
+    stream, and SharpNet drives every device from a thread of its own (Prod/GPU/GPUWrapper.cs:782-832,
+    Prod/Networks/Network.cs:71-83).  Two host threads drive one handle each on the same GPU at the same time,
+    through products that take the workspace, clusters, swapped operands and the FMA kernel; small integer operands
+    make every result exact, so one wrong tile or one torn workspace shows."""
+    import threading
+    import torch
+    from sharpnet_b200.tensor import GPUWrapper
+    shapes = [(1024, 1024, 1024), (256, 4096, 2048), (32, 4096, 4096), (2048, 1536, 768), (9, 5, 21), (300, 136, 200)]
+    rng = np.random.default_rng(5)
+    cases = []
+    for M, N, K in shapes:
+        a = rng.integers(-2, 3, (M, K)).astype(np.float32)
+        b = rng.integers(-2, 3, (K, N)).astype(np.float32)
+        cases.append((a, b, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)))
+    errors = []
+
+    def drive(tid):
+        w = GPUWrapper(0)      # a handle of this thread's own, not the cached one
+        try:
+            stream = torch.cuda.Stream(device=0)
+            w.set_stream(stream)
+            with torch.cuda.stream(stream):
+                tensors = [(GPUTensor(a.shape, a, w), GPUTensor(b.shape, b, w), GPUTensor(c.shape, None, w), c)
+                           for a, b, c in cases]
+                for it in range(6):
+                    order = range(len(tensors)) if tid == 0 else reversed(range(len(tensors)))
+                    for i in order:
+                        A, B, C, _ = tensors[i]
+                        C.Dot(A, False, B, False, 1.0, 0.0)
+                    for i, (_, _, C, want) in enumerate(tensors):
+                        if not np.array_equal(C.ContentAsFloatArray(), want):
+                            errors.append((tid, it, shapes[i]))
+                    w.check_device_status()
+        except Exception as e:   # noqa: BLE001 -- reported by the assertion below
+            errors.append((tid, repr(e)))
+        finally:
+            torch.cuda.synchronize()
+            w.Dispose()
+
+    threads = [threading.Thread(target=drive, args=(t,)) for t in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
