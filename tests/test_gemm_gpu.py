@@ -561,3 +561,47 @@ def test_two_handles_on_two_host_threads(built_library):
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+def test_tensors_beyond_four_gigabytes(wrapper):
+    """SharpNet's tensors hold up to 2^31 - 1 floats (Prod/Data/Tensor.cs:189), 8.6 GB: element offsets beyond 2^30
+    and byte offsets beyond 2^32 are inside the contract.  A 1 114 112 x 1024 tensor (4.56 GB) as the result of a
+    product, as the transposed operand of a weight-gradient product whose K is its 1.1 M rows, as the input of a bias
+    gradient and of an activation pass; small integers, so every result is exact."""
+    import torch
+    from sharpnet_b200 import ACT_RELU
+    dev = wrapper.device
+    block, reps, N, k = 65536, 17, 1024, 32
+    M = block * reps
+    rng = np.random.default_rng(21)
+    a_block = rng.integers(-1, 2, (block, N)).astype(np.float32)          # the big tensor is this block 17 times over
+    big = torch.from_numpy(a_block).to(dev).repeat(reps, 1).contiguous()
+    assert big.numel() * 4 > 2 ** 32
+    BIG = GPUTensor((M, N), wrapper=wrapper, storage=big.view(-1))
+    try:
+        # dW = big^T * dy, K = M                                       (Prod/Layers/Linear.cs:158)
+        dy = rng.integers(-1, 2, (M, k)).astype(np.float32)
+        DY, DW = GPUTensor(dy.shape, dy, wrapper), GPUTensor((N, k), None, wrapper)
+        DW.Dot(BIG, True, DY, False, 1.0, 0.0)
+        want = sum(a_block.T @ dy[r * block:(r + 1) * block] for r in range(reps))
+        np.testing.assert_array_equal(DW.ContentAsFloatArray(), want)
+        # db = column sums of big                                      (Prod/GPU/GpuTensor.cs:686-701)
+        DB = GPUTensor((N,), None, wrapper)
+        BIG.Compute_BiasGradient_from_dy(DB)
+        np.testing.assert_array_equal(DB.ContentAsFloatArray(), reps * a_block.sum(0, dtype=np.float64).astype(np.float32))
+        # y = relu(big), a second 4.56 GB tensor, then overwritten as the result of a product with K = 32
+        out = torch.empty_like(big)
+        OUT = GPUTensor((M, N), wrapper=wrapper, storage=out.view(-1))
+        BIG.ActivationForward(ACT_RELU, None, OUT)
+        assert torch.equal(out, torch.clamp_min(big, 0))
+        x = rng.integers(-2, 3, (M, k)).astype(np.float32)
+        wgt = rng.integers(-2, 3, (k, N)).astype(np.float32)
+        X, W = GPUTensor(x.shape, x, wrapper), GPUTensor(wgt.shape, wgt, wrapper)
+        OUT.Dot(X, False, W, False, 1.0, 0.0)
+        wrapper.check_device_status()
+        for r0 in (0, 2 ** 20 - 64, M - 128):        # the start, across byte offset 2^32, the end
+            np.testing.assert_array_equal(out[r0:r0 + 128].cpu().numpy(), x[r0:r0 + 128] @ wgt)
+        assert torch.equal(out.sum(1, dtype=torch.float64).cpu(), torch.from_numpy((x @ wgt.sum(1)).astype(np.float64)))
+    finally:
+        del big, BIG
+        torch.cuda.empty_cache()
