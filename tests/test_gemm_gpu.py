@@ -605,3 +605,35 @@ def test_tensors_beyond_four_gigabytes(wrapper):
     finally:
         del big, BIG
         torch.cuda.empty_cache()
+
+
+def test_create_and_destroy_release_what_they_took(built_library):
+    """A handle owns its workspace, its error word and its timing events and nothing else (SharpNet creates one
+    wrapper per device and disposes it with the process, Prod/GPU/GPUWrapper.cs:99-160,737-777): creating a handle,
+    working through it and destroying it, over and over, leaves the device's free memory where it was."""
+    import torch
+    from sharpnet_b200.tensor import GPUWrapper
+    a = np.arange(64 * 48, dtype=np.float32).reshape(64, 48) % 5 - 2
+    b = np.arange(48 * 40, dtype=np.float32).reshape(48, 40) % 3 - 1
+
+    def cycle():
+        w = GPUWrapper(0)
+        try:
+            A, B, C = GPUTensor(a.shape, a, w), GPUTensor(b.shape, b, w), GPUTensor((64, 40), None, w)
+            w.gemm_timing_begin()
+            C.Dot(A, False, B, False, 1.0, 0.0)
+            w.gemm_timing_end()
+            np.testing.assert_array_equal(C.ContentAsFloatArray(), a @ b)
+        finally:
+            w.Dispose()
+
+    cycle()                                   # first use: module load, function attributes
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(0)
+    for _ in range(20):
+        cycle()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_before - free_after < (8 << 20), (free_before, free_after)   # a leaked 128 MB workspace would show
+    lib = GPUWrapper.FromDeviceId(0).lib
+    assert lib.snb200_destroy(None) == 1      # CUBLAS_STATUS_NOT_INITIALIZED's number: no handle
