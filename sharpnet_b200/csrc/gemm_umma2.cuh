@@ -40,7 +40,7 @@ struct Umma2Tile {
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;   // a power of two
   static constexpr int EPI_GROUPS = (BN >= 64) ? 2 : 1;
   static constexpr int EPI_THREADS = 128 * EPI_GROUPS;
   static constexpr int EPI_COLS = BN / EPI_GROUPS;
@@ -60,7 +60,7 @@ struct Umma2Tile {
   static constexpr int MNMAJ_SBO = 512;
   static constexpr int MNMAJ_LAYOUT = 1;
   static_assert(BK == 32 || BK == 16, "BK must be 16 or 32");
-  static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
+  static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "BN must be 64, 128, 192 or 256");
   static_assert(STAGES >= 2, "need at least two stages");
 };
 

@@ -530,7 +530,7 @@ static int launch_umma2_t(snb200_handle_t h, const GemmProblem& g, SplitPlan& pl
 
 static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int bn, SplitPlan& plan, bool hybrid) {
   char name[64];
-  hybrid = hybrid && split && bn >= 128;
+  hybrid = hybrid && split && (bn == 128 || bn == 256);
   snprintf(name, sizeof(name), "umma2_%s_256x%d%s", hybrid ? "tf32bf16x2" : split ? "3xtf32" : "tf32", bn,
            plan.splits > 0 ? "_splitk" : "");
   note_kernel(h, name, 1);
@@ -544,12 +544,14 @@ static int launch_umma2(snb200_handle_t h, const GemmProblem& g, bool split, int
       case 256:
         if (h->tune[TUNE_VARIANT] == 1) return launch_umma2_t<Umma2Tile<256, 16, true>>(h, g, plan);
         return launch_umma2_t<Umma2Tile<256, 32, true>>(h, g, plan);
+      case 192: return launch_umma2_t<Umma2Tile<192, 32, true>>(h, g, plan);
       case 128: return launch_umma2_t<Umma2Tile<128, 32, true>>(h, g, plan);
       default: return launch_umma2_t<Umma2Tile<64, 32, true>>(h, g, plan);
     }
   }
   switch (bn) {
     case 256: return launch_umma2_t<Umma2Tile<256, 32, false>>(h, g, plan);
+    case 192: return launch_umma2_t<Umma2Tile<192, 32, false>>(h, g, plan);
     case 128: return launch_umma2_t<Umma2Tile<128, 32, false>>(h, g, plan);
     default: return launch_umma2_t<Umma2Tile<64, 32, false>>(h, g, plan);
   }
@@ -703,6 +705,11 @@ struct TileChoice { int pair; int bn; int splits; int whole_tiles; int cluster; 
 struct TileCost { double kblock_us, fixed_us; };
 static TileCost tile_cost(bool split3x, int pair, int bn, const GemmProblem& g) {
   const int i = bn == 256 ? 0 : bn == 128 ? 1 : bn == 64 ? 2 : 3;
+  if (bn == 192) {   // CTA pairs only: between the 256- and the 128-wide tile
+    if (split3x) return {0.91, 11.4};
+    if (g.transA) return {0.515, 8.3};
+    return g.transB ? TileCost{0.369, 9.1} : TileCost{0.402, 8.9};
+  }
   if (split3x) {   // the hi/lo split and three products per block hide the operand layout
     static const TileCost single[4] = {{1.46, 13.3}, {0.90, 8.5}, {0.81, 6.7}, {0.69, 5.7}};
     static const TileCost paired[4] = {{1.00, 13.3}, {0.82, 9.4}, {0.72, 7.6}, {0.72, 7.6}};
@@ -726,15 +733,16 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
   const int pair_mode = h->tune[TUNE_PAIR];   // 0 automatic, 1 always, 2 never
   const int forced_bn = h->tune[TUNE_FORCE_BN];
   const int forced_splits = allow_splitk ? h->tune[TUNE_FORCE_SPLITS] : 0;
-  const int cand[4] = {256, 128, 64, 32};
+  const int cand[5] = {256, 192, 128, 64, 32};
   const int ks_cand[11] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 16};
   const long long kb = (g.K + 31) / 32;
   for (int pair = 0; pair < 2; ++pair) {
     if (pair == 0 && pair_mode == 1) continue;
     if (pair == 1 && (pair_mode == 2 || (pair_mode == 0 && g.M <= 128))) continue;
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 5; ++i) {
       const int bn = cand[i];
       if (pair && bn < 64) continue;
+      if (!pair && bn == 192) continue;
       if (forced_bn && bn != forced_bn) continue;
       const int rows = pair ? 256 : 128;
       const long long tiles = static_cast<long long>(g.batch) * ((g.M + rows - 1) / rows) * ((g.N + bn - 1) / bn);
@@ -742,12 +750,12 @@ static TileChoice choose_tile(const snb200_context* h, const GemmProblem& g, boo
       const long long whole = tiles / slots * slots, tail = tiles - whole;
       const TileCost tc = tile_cost(split, pair, bn, g);
       // TF32 + bf16 cross terms: two instruction times per K slice instead of three, on the pair kernel's wide tiles
-      const double c = tc.kblock_us * ((hybrid && pair && bn >= 128) ? 0.7 : 1.0), fixed = tc.fixed_us;
+      const double c = tc.kblock_us * ((hybrid && pair && (bn == 128 || bn == 256)) ? 0.7 : 1.0), fixed = tc.fixed_us;
       // One wave of tiles that leaves SMs idle: clusters of 2 or 4 CTAs share a tile's K range and sum their parts
       // through distributed shared memory.  No workspace pass, and every CTA stores only its share of the rows.
       const int cluster_mode = h->tune[TUNE_CLUSTER];   // 0 automatic, 1 never, 2 / 4 forced
       if (!pair && cluster_mode != 1 && allow_splitk && g.row_op == ROW_NONE && forced_splits <= 1) {
-        static const double store_us[4] = {4.5, 2.0, 1.3, 0.9};   // the store phase of a whole tile (nothing overlaps it)
+        static const double store_us[5] = {4.5, 0.0, 2.0, 1.3, 0.9};   // the store phase of a whole tile (nothing overlaps it)
         for (int cs = 2; cs <= 4; cs *= 2) {
           if (cluster_mode > 1 && cs != cluster_mode) continue;
           // left to itself: pairs of CTAs, all resident at once (measured: clusters of four lose to pairs on wider
@@ -798,7 +806,7 @@ static int launch_tail_reduce(snb200_handle_t h, const GemmProblem& g, const Spl
   TailReduceParams r;
   r.M = g.M; r.N = g.N;
   r.tiles_m = plan.tiles_m; r.tiles_n = (g.N + bn - 1) / bn;
-  r.tile_rows = tile_rows; r.bn = bn; r.rows_per_block = 1024 / bn;
+  r.tile_rows = tile_rows; r.bn = bn; r.rows_per_block = bn == 192 ? 4 : 1024 / bn;   // divides the tile's rows
   r.whole_tiles = plan.whole_tiles; r.tail = plan.tail; r.splits = plan.parts;
   r.partial = h->workspace;
   r.tile_elems = static_cast<long long>(tile_rows) * bn;

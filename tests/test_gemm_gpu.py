@@ -120,7 +120,7 @@ def test_tensor_core_ragged_shapes(wrapper, mode, tol, tA, tB, pair):
     wrapper.set_tuning(TUNE_FORCE_PATH, 1)
     wrapper.set_tuning(TUNE_PAIR, pair)
     seed = 500
-    for bn in ((32, 64, 128, 256) if pair == 2 else (64, 128, 256)):
+    for bn in ((32, 64, 128, 256) if pair == 2 else (64, 128, 192, 256)):
         wrapper.set_tuning(TUNE_FORCE_BN, bn)
         for (M, N, K) in ((128, 256, 64), (132, 260, 36), (200, 328, 100), (4, 8, 4), (260, 516, 20), (96, 40, 520)):
             seed += 1
@@ -250,7 +250,8 @@ def test_config_2_four_transposes_beta_one(wrapper, mode, tol):
     for tA in (False, True):
         for tB in (False, True):
             _check(wrapper, 2048, 1536, 768, tA, tB, 1, 1, seed, tol)
-            assert wrapper.last_kernel().startswith("umma")
+            # 8 x 8 tiles of 256 x 192 fill 64 of the 74 SM pairs where 8 x 6 tiles of 256 x 256 fill 48
+            assert wrapper.last_kernel().startswith("umma2") and "256x192" in wrapper.last_kernel(), wrapper.last_kernel()
             _check(wrapper, 32, 4096, 4096, tA, tB, 1, 1, 5, tol)
             seed += 1
 
@@ -355,6 +356,13 @@ def test_partly_filled_last_wave_is_cut_along_k(wrapper, mode, tol, tA, tB):
         if mode == MATH_3XTF32:               # 81 (171) tiles on 74 (148) slots: the model must cut the 7 (23) left over
             assert "splitk" in wrapper.last_kernel(), wrapper.last_kernel()
         _check(wrapper, 772, 1000, 1536, tA, tB, 1.0, 1.0, 815 + pair, tol, batch=7)
+    # the 192-wide pair tile with its tail cut: 10 x 8 = 80 tiles on 74 pairs, the 6 left over cut along K
+    wrapper.set_tuning(TUNE_FORCE_BN, 192)
+    wrapper.set_tuning(TUNE_PAIR, 1)
+    _check(wrapper, 2308, 1530, 1028, tA, tB, 1.0, 1.0, 819, tol)
+    assert wrapper.last_kernel().startswith("umma2") and "256x192" in wrapper.last_kernel(), wrapper.last_kernel()
+    if mode == MATH_3XTF32:
+        assert "splitk" in wrapper.last_kernel(), wrapper.last_kernel()
 
 
 def test_long_k_keeps_fp32_accuracy(wrapper):
@@ -496,21 +504,21 @@ def test_seeded_sweep_over_shapes_and_plans(wrapper):
         for it in range(160):
             mode, tol = ((MATH_3XTF32, TOL_3XTF32), (MATH_TF32, TOL_TF32))[it % 5 == 4]
             M = int(rng.choice([1, 5, 17, 32, 33, 64, 100, 128, 129, 200, 256, 300, 513, 700]))
-            N = int(rng.choice([8, 12, 32, 40, 64, 100, 128, 132, 256, 260, 512, 640]))
+            N = int(rng.choice([8, 12, 32, 40, 64, 100, 128, 132, 256, 260, 384, 512, 640]))
             K = int(rng.choice([64, 100, 128, 256, 300, 512, 516, 1000, 1024, 2052, 3000]))
             tA, tB = bool(rng.integers(2)), bool(rng.integers(2))
             beta, alpha = float(rng.choice([0.0, 1.0, -0.5])), float(rng.choice([1.0, 0.5]))
             batch = None if rng.integers(4) else int(rng.choice([2, 5]))
             wrapper.set_math_mode(mode)
             wrapper.set_tuning(TUNE_CLUSTER, int(rng.choice([0, 0, 2, 4, 1])))
-            wrapper.set_tuning(TUNE_FORCE_BN, int(rng.choice([0, 0, 32, 64, 128, 256])))
+            wrapper.set_tuning(TUNE_FORCE_BN, int(rng.choice([0, 0, 32, 64, 128, 192, 256])))
             wrapper.set_tuning(TUNE_PAIR, int(rng.choice([0, 0, 2])))
             _check(wrapper, M, N, K, tA, tB, alpha, beta, 1000 + it, tol, batch=batch)
             kernels.add(wrapper.last_kernel().split("_p")[0])
     finally:
         wrapper.set_tuning(TUNE_CLUSTER, 0)
     # the draw reaches every family of plans
-    for family in ("clusterk2", "clusterk4", "swapAB", "splitk", "swload", "realigned", "umma2_", "simt"):
+    for family in ("clusterk2", "clusterk4", "swapAB", "splitk", "swload", "realigned", "umma2_", "256x192", "simt"):
         assert any(family in k for k in kernels), (family, sorted(kernels))
 
 
