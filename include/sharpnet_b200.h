@@ -128,7 +128,7 @@ int snb200_gemm_timing_end(snb200_handle_t handle, double* total_ms, int* gemm_c
  *        swapped-operand plans for problems with few tiles (0 automatic, 1 never); key 6: 1 selects the
  *        16-wide K blocks in 3xTF32 mode instead of the default 32-wide ones (A/B measurements).
  * key 0: path (0 automatic, 1 tensor cores whenever the operands allow TMA, 2 SIMT fp32);
- * key 1: tile width of the tensor-core kernel (0 automatic, else 32, 64, 128 or 256);
+ * key 1: tile width of the tensor-core kernel (0 automatic, else 32, 64, 128, 256, or 192 on the CTA-pair kernel);
  * key 2: 3xTF32 writes the rounded hi plane back to shared memory (1) or lets the
  *        tensor core truncate the raw fp32 words itself (0, default);
  * key 7: 1 launches the tensor-core kernels without programmatic dependent launch (by default their set-up
