@@ -16,8 +16,9 @@
 namespace SharpNet {
 
 enum class cudnnActivationMode_t : int {   // Prod/GPU/CudnnWrapper.cs:267-281
-  CUDNN_ACTIVATION_SIGMOID = 0, CUDNN_ACTIVATION_RELU = 1, CUDNN_ACTIVATION_TANH = 2,
-  CUDNN_ACTIVATION_IDENTITY = 5, CUDNN_ACTIVATION_SWISH = 6
+  CUDNN_ACTIVATION_SIGMOID = 0, CUDNN_ACTIVATION_RELU = 1, CUDNN_ACTIVATION_TANH = 2, CUDNN_ACTIVATION_CLIPPED_RELU = 3,
+  CUDNN_ACTIVATION_ELU = 4, CUDNN_ACTIVATION_IDENTITY = 5, CUDNN_ACTIVATION_SWISH = 6, CUDNN_ACTIVATION_LEAKY_RELU = 1002,
+  CUDNN_ACTIVATION_LN = 1004
 };
 
 // One per device: owns the library handle (the role of Prod/GPU/GPUWrapper.cs:99-160).
@@ -36,6 +37,12 @@ class GPUWrapper {
   }
   snb200_handle_t Handle() const { return handle_; }
   void SetMathMode(int mode) { CheckStatus(snb200_set_math_mode(handle_, mode)); }
+  // The coefficient SharpNet runs the activation with: the layer's activationParameter for LeakyRelu, 1 for Elu
+  // whatever the parameter says (Prod/CPU/CpuTensor.cs:954,1000; the cuDNN descriptor of Prod/GPU/GPUWrapper.cs:183).
+  void SetActivationCoefficient(cudnnActivationMode_t activationType, const float* activationParameterOrNull) {
+    if (activationType == cudnnActivationMode_t::CUDNN_ACTIVATION_ELU) CheckStatus(snb200_set_activation_parameter(handle_, 1.0f));
+    else if (activationParameterOrNull) CheckStatus(snb200_set_activation_parameter(handle_, *activationParameterOrNull));
+  }
   const int DeviceId;
  private:
   snb200_handle_t handle_ = nullptr;
@@ -100,15 +107,22 @@ class GPUTensor {
   void Compute_BiasGradient_from_dy(GPUTensor& biasGradient_1D) const {
     wrapper_->CheckStatus(snb200_bias_grad(wrapper_->Handle(), Shape[0], MultDim0(), ptr_, biasGradient_1D.ptr_));
   }
-  // y = act(this)                                         (Tensor.cs:618, GpuTensor.cs:397-443)
-  void ActivationForward(cudnnActivationMode_t activationType, GPUTensor& y) const {
+  // y = act(this); activationParameter is the host value of SharpNet's one-element tensor (LeakyRelu's slope)
+  //                                                       (Tensor.cs:618, GpuTensor.cs:397-443)
+  void ActivationForward(cudnnActivationMode_t activationType, const float* activationParameterOrNull, GPUTensor& y) const {
+    wrapper_->SetActivationCoefficient(activationType, activationParameterOrNull);
     wrapper_->CheckStatus(snb200_activation_fwd(wrapper_->Handle(), static_cast<int>(activationType), Count(), ptr_, y.ptr_));
   }
+  void ActivationForward(cudnnActivationMode_t activationType, GPUTensor& y) const { ActivationForward(activationType, nullptr, y); }
   // this = dx = act'(x, y) * dy                           (Tensor.cs:628, GpuTensor.cs:445-490)
-  void ActivationBackward(cudnnActivationMode_t activationType, const GPUTensor& dy, const GPUTensor* x,
-                          const GPUTensor* y) {
+  void ActivationBackward(cudnnActivationMode_t activationType, const float* activationParameterOrNull, const GPUTensor& dy,
+                          const GPUTensor* x, const GPUTensor* y) {
+    wrapper_->SetActivationCoefficient(activationType, activationParameterOrNull);
     wrapper_->CheckStatus(snb200_activation_bwd(wrapper_->Handle(), static_cast<int>(activationType), Count(), dy.ptr_,
                                                 x ? x->ptr_ : nullptr, y ? y->ptr_ : nullptr, ptr_));
+  }
+  void ActivationBackward(cudnnActivationMode_t activationType, const GPUTensor& dy, const GPUTensor* x, const GPUTensor* y) {
+    ActivationBackward(activationType, nullptr, dy, x, y);
   }
   // this += alpha * x                                     (Tensor.cs:555, GpuTensor.cs:1359-1362)
   void Update_Adding_Alpha_X(float alpha, const GPUTensor& x) {

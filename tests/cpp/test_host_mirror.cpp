@@ -131,6 +131,39 @@ int main() {
       EXPECT(std::fabs(dbv[n] - s) < 1e-3, "db[%d]", n);
     }
   }
+  {  // parametric activations: LeakyRelu with the layer's slope, Elu with SharpNet's fixed coefficient of 1
+     // (Prod/CPU/CpuTensorActivationFunctions.cs:210-231, Prod/CPU/CpuTensor.cs:954,1000), Ln (:170-180)
+    const int n = 1000;
+    auto x = uniform(n, -1.5f, 1.5f, 70), dy = uniform(n, -1.5f, 1.5f, 71);
+    GPUTensor X({n}, x.data(), gpu), DY({n}, dy.data(), gpu), Y({n}, nullptr, gpu), DX({n}, nullptr, gpu);
+    const float slope = 0.3f, ignored = 0.0f;
+    X.ActivationForward(cudnnActivationMode_t::CUDNN_ACTIVATION_LEAKY_RELU, &slope, Y);
+    DX.ActivationBackward(cudnnActivationMode_t::CUDNN_ACTIVATION_LEAKY_RELU, &slope, DY, &X, &Y);
+    auto y = Y.ContentAsFloatArray(), dx = DX.ContentAsFloatArray();
+    for (int i = 0; i < n; ++i) {
+      EXPECT(y[i] == (x[i] >= 0 ? x[i] : slope * x[i]), "LeakyRelu forward at %d", i);
+      EXPECT(dx[i] == (y[i] >= 0 ? dy[i] : slope * dy[i]), "LeakyRelu backward at %d", i);
+    }
+    X.ActivationForward(cudnnActivationMode_t::CUDNN_ACTIVATION_ELU, &ignored, Y);
+    DX.ActivationBackward(cudnnActivationMode_t::CUDNN_ACTIVATION_ELU, &ignored, DY, &X, &Y);
+    y = Y.ContentAsFloatArray(); dx = DX.ContentAsFloatArray();
+    for (int i = 0; i < n; ++i) {
+      const double want = x[i] >= 0 ? x[i] : std::exp(static_cast<double>(x[i])) - 1.0;
+      EXPECT(std::fabs(y[i] - want) <= 1e-6 * std::fabs(want) + 1e-7, "Elu forward at %d", i);
+      EXPECT(std::fabs(dx[i] - (x[i] >= 0 ? dy[i] : dy[i] * (y[i] + 1.0f))) <= 1e-6, "Elu backward at %d", i);
+    }
+    X.ActivationForward(cudnnActivationMode_t::CUDNN_ACTIVATION_LN, Y);
+    DX.ActivationBackward(cudnnActivationMode_t::CUDNN_ACTIVATION_LN, DY, &X, &Y);
+    y = Y.ContentAsFloatArray(); dx = DX.ContentAsFloatArray();
+    for (int i = 0; i < n; ++i) {
+      const double want = x[i] <= 0 ? -100.0 : std::log(static_cast<double>(x[i]));
+      EXPECT(std::fabs(y[i] - want) <= 1e-6 * std::fabs(want) + 1e-7, "Ln forward at %d", i);
+      EXPECT(std::fabs(dx[i] - dy[i] / x[i]) <= 2e-6 * std::fabs(dy[i] / x[i]), "Ln backward at %d", i);
+    }
+    X.ActivationForward(cudnnActivationMode_t::CUDNN_ACTIVATION_CLIPPED_RELU, Y);
+    y = Y.ContentAsFloatArray();
+    for (int i = 0; i < n; ++i) EXPECT(y[i] == std::fmin(std::fmax(x[i], 0.0f), 1.0f), "ClippedRelu forward at %d", i);
+  }
   {  // errors surface as exceptions, like GPUWrapper.CheckStatus
     GPUTensor A({4, 3}, nullptr, gpu), B({5, 4}, nullptr, gpu), C({4, 4}, nullptr, gpu);
     bool thrown = false;
