@@ -9,6 +9,7 @@
 #include <numeric>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/sharpnet_b200.h"
@@ -17,8 +18,8 @@ namespace SharpNet {
 
 enum class cudnnActivationMode_t : int {   // Prod/GPU/CudnnWrapper.cs:267-281
   CUDNN_ACTIVATION_SIGMOID = 0, CUDNN_ACTIVATION_RELU = 1, CUDNN_ACTIVATION_TANH = 2, CUDNN_ACTIVATION_CLIPPED_RELU = 3,
-  CUDNN_ACTIVATION_ELU = 4, CUDNN_ACTIVATION_IDENTITY = 5, CUDNN_ACTIVATION_SWISH = 6, CUDNN_ACTIVATION_LEAKY_RELU = 1002,
-  CUDNN_ACTIVATION_LN = 1004
+  CUDNN_ACTIVATION_ELU = 4, CUDNN_ACTIVATION_IDENTITY = 5, CUDNN_ACTIVATION_SWISH = 6, CUDNN_ACTIVATION_SOFTMAX = 1000,
+  CUDNN_ACTIVATION_LEAKY_RELU = 1002, CUDNN_ACTIVATION_LN = 1004, CUDNN_ACTIVATION_SOFTMAX_LAST_DIMENSION = 1005
 };
 
 // One per device: owns the library handle (the role of Prod/GPU/GPUWrapper.cs:99-160).
@@ -110,6 +111,13 @@ class GPUTensor {
   // y = act(this); activationParameter is the host value of SharpNet's one-element tensor (LeakyRelu's slope)
   //                                                       (Tensor.cs:618, GpuTensor.cs:397-443)
   void ActivationForward(cudnnActivationMode_t activationType, const float* activationParameterOrNull, GPUTensor& y) const {
+    if (activationType == cudnnActivationMode_t::CUDNN_ACTIVATION_SOFTMAX ||
+        activationType == cudnnActivationMode_t::CUDNN_ACTIVATION_SOFTMAX_LAST_DIMENSION) {
+      // over the columns of the 2-D view (GpuTensor.cs:407-413), or over the last dimension
+      const int cols = activationType == cudnnActivationMode_t::CUDNN_ACTIVATION_SOFTMAX ? MultDim0() : Shape.back();
+      wrapper_->CheckStatus(snb200_softmax_fwd(wrapper_->Handle(), Count() / cols, cols, ptr_, y.ptr_));
+      return;
+    }
     wrapper_->SetActivationCoefficient(activationType, activationParameterOrNull);
     wrapper_->CheckStatus(snb200_activation_fwd(wrapper_->Handle(), static_cast<int>(activationType), Count(), ptr_, y.ptr_));
   }
@@ -117,6 +125,12 @@ class GPUTensor {
   // this = dx = act'(x, y) * dy                           (Tensor.cs:628, GpuTensor.cs:445-490)
   void ActivationBackward(cudnnActivationMode_t activationType, const float* activationParameterOrNull, const GPUTensor& dy,
                           const GPUTensor* x, const GPUTensor* y) {
+    if (activationType == cudnnActivationMode_t::CUDNN_ACTIVATION_SOFTMAX ||
+        activationType == cudnnActivationMode_t::CUDNN_ACTIVATION_SOFTMAX_LAST_DIMENSION) {
+      const int cols = activationType == cudnnActivationMode_t::CUDNN_ACTIVATION_SOFTMAX ? MultDim0() : Shape.back();
+      wrapper_->CheckStatus(snb200_softmax_bwd(wrapper_->Handle(), Count() / cols, cols, dy.ptr_, y->ptr_, ptr_));   // GpuTensor.cs:461-468
+      return;
+    }
     wrapper_->SetActivationCoefficient(activationType, activationParameterOrNull);
     wrapper_->CheckStatus(snb200_activation_bwd(wrapper_->Handle(), static_cast<int>(activationType), Count(), dy.ptr_,
                                                 x ? x->ptr_ : nullptr, y ? y->ptr_ : nullptr, ptr_));
@@ -127,6 +141,26 @@ class GPUTensor {
   // this += alpha * x                                     (Tensor.cs:555, GpuTensor.cs:1359-1362)
   void Update_Adding_Alpha_X(float alpha, const GPUTensor& x) {
     wrapper_->CheckStatus(snb200_axpy(wrapper_->Handle(), Count(), alpha, x.ptr_, ptr_));
+  }
+  // target[a, c, b, :] = this[a, b, c, :]                (GpuTensor.cs:672-684)
+  void TransposeSecondAndThirdDimension(GPUTensor& target) const {
+    const int A = Shape[0], B = Shape[1], C = Shape[2];
+    const int D = static_cast<int>(Count() / (static_cast<long long>(A) * B * C));
+    wrapper_->CheckStatus(snb200_transpose_second_third(wrapper_->Handle(), A, B, C, D, ptr_, target.ptr_));
+    target.Shape = Shape;
+    std::swap(target.Shape[1], target.Shape[2]);
+  }
+  // this = W: SGD with momentum; velocity null = the VanillaSgd update   (Tensor.cs:714, GpuTensor.cs:1147-1161)
+  void UpdateSGDOptimizer(double learningRate, double momentum, bool nesterov, const GPUTensor& dW, GPUTensor* velocity) {
+    wrapper_->CheckStatus(snb200_sgd_update(wrapper_->Handle(), Count(), static_cast<float>(learningRate),
+                                            static_cast<float>(momentum), nesterov, dW.ptr_, ptr_,
+                                            velocity ? velocity->ptr_ : nullptr));
+  }
+  // this = W: Adam / AdamW                                (Tensor.cs:712, GpuTensor.cs:1136-1145)
+  void UpdateAdamOptimizer(double learningRate, double beta1, double beta2, double epsilon, double weight_decay,
+                           const GPUTensor& dW, GPUTensor& adam_vW, GPUTensor& adam_sW, int timeStep) {
+    wrapper_->CheckStatus(snb200_adam_update(wrapper_->Handle(), Count(), learningRate, beta1, beta2, epsilon, weight_decay,
+                                             timeStep, dW.ptr_, ptr_, adam_vW.ptr_, adam_sW.ptr_));
   }
   GPUWrapper& Wrapper() const { return *wrapper_; }
 
@@ -175,6 +209,28 @@ struct Linear {
                                    weights.Pointer(), dy.Pointer(), static_cast<int>(act), y ? y->Pointer() : nullptr,
                                    z ? z->Pointer() : nullptr, multiplier, dzScratch ? dzScratch->Pointer() : nullptr,
                                    dx ? dx->Pointer() : nullptr, dW.Pointer(), db ? db->Pointer() : nullptr));
+  }
+};
+
+// Static methods of the attention layer (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-129); Q [batch, q, E],
+// K and V [batch, v, E].  weights_buffer keeps the probabilities for the backward pass, scores_grad_scratch
+// [batch, q, v] is what the reference takes from its memory pool there.
+struct ScaledDotProductAttentionLayer {
+  static void ScaledDotProductAttentionForwardPropagation(const GPUTensor& Q, const GPUTensor& K, const GPUTensor& V,
+                                                          GPUTensor& y, GPUTensor& weights_buffer, bool use_scale,
+                                                          bool is_causal) {
+    GPUWrapper& w = y.Wrapper();
+    w.CheckStatus(snb200_sdpa_fwd(w.Handle(), Q.Shape[0], Q.Shape[1], V.Shape[1], Q.Shape[2], use_scale, is_causal,
+                                  Q.Pointer(), K.Pointer(), V.Pointer(), weights_buffer.Pointer(), y.Pointer()));
+  }
+  static void ScaledDotProductAttentionBackwardPropagation(GPUTensor& dQ, GPUTensor& dK, GPUTensor& dV, const GPUTensor& Q,
+                                                           const GPUTensor& K, const GPUTensor& V, const GPUTensor& dy,
+                                                           const GPUTensor& weights_buffer, GPUTensor& scores_grad_scratch,
+                                                           bool use_scale) {
+    GPUWrapper& w = dQ.Wrapper();
+    w.CheckStatus(snb200_sdpa_bwd(w.Handle(), Q.Shape[0], Q.Shape[1], V.Shape[1], Q.Shape[2], use_scale, Q.Pointer(),
+                                  K.Pointer(), V.Pointer(), dy.Pointer(), weights_buffer.Pointer(),
+                                  scores_grad_scratch.Pointer(), dQ.Pointer(), dK.Pointer(), dV.Pointer()));
   }
 };
 

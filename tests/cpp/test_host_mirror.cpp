@@ -164,6 +164,64 @@ int main() {
     y = Y.ContentAsFloatArray();
     for (int i = 0; i < n; ++i) EXPECT(y[i] == std::fmin(std::fmax(x[i], 0.0f), 1.0f), "ClippedRelu forward at %d", i);
   }
+  {  // attention: the layer's static methods against the same arithmetic spelled out with the tensor calls
+     // (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-129), and the optimizer updates against host loops
+    const int nb = 6, L = 40, E = 32;
+    auto q = uniform(nb * L * E, -1, 1, 80), k = uniform(nb * L * E, -1, 1, 81), v = uniform(nb * L * E, -1, 1, 82), dy = uniform(nb * L * E, -1, 1, 83);
+    GPUTensor Q({nb, L, E}, q.data(), gpu), K({nb, L, E}, k.data(), gpu), V({nb, L, E}, v.data(), gpu), DY({nb, L, E}, dy.data(), gpu);
+    GPUTensor y({nb, L, E}, nullptr, gpu), wts({nb, L, L}, nullptr, gpu), scores({nb, L, L}, nullptr, gpu), p({nb, L, L}, nullptr, gpu), y2({nb, L, E}, nullptr, gpu);
+    ScaledDotProductAttentionLayer::ScaledDotProductAttentionForwardPropagation(Q, K, V, y, wts, true, false);
+    scores.BatchMatrixMultiplication(Q, false, K, true, 1.0f / std::sqrt(static_cast<float>(E)), 0.0f);
+    scores.ActivationForward(cudnnActivationMode_t::CUDNN_ACTIVATION_SOFTMAX_LAST_DIMENSION, p);
+    y2.BatchMatrixMultiplication(p, false, V, false, 1.0f, 0.0f);
+    auto w1 = wts.ContentAsFloatArray(), w2 = p.ContentAsFloatArray(), o1 = y.ContentAsFloatArray(), o2 = y2.ContentAsFloatArray();
+    for (size_t i = 0; i < w1.size(); ++i) EXPECT(std::fabs(w1[i] - w2[i]) < 2e-6, "attention weights at %zu", i);
+    for (size_t i = 0; i < o1.size(); ++i) EXPECT(std::fabs(o1[i] - o2[i]) < 2e-5, "attention output at %zu", i);
+    for (int r = 0; r < nb * L; ++r) {
+      double sum = 0;
+      for (int c = 0; c < L; ++c) sum += w1[r * L + c];
+      EXPECT(std::fabs(sum - 1.0) < 1e-5, "probabilities of row %d sum to %f", r, sum);
+    }
+    GPUTensor dQ({nb, L, E}, nullptr, gpu), dK({nb, L, E}, nullptr, gpu), dV({nb, L, E}, nullptr, gpu), scratch({nb, L, L}, nullptr, gpu);
+    ScaledDotProductAttentionLayer::ScaledDotProductAttentionBackwardPropagation(dQ, dK, dV, Q, K, V, DY, wts, scratch, true);
+    GPUTensor dV2({nb, L, E}, nullptr, gpu), dW({nb, L, L}, nullptr, gpu), dS({nb, L, L}, nullptr, gpu), dQ2({nb, L, E}, nullptr, gpu), dK2({nb, L, E}, nullptr, gpu);
+    dV2.BatchMatrixMultiplication(wts, true, DY, false, 1.0f, 0.0f);                                   // :113
+    dW.BatchMatrixMultiplication(DY, false, V, true, 1.0f / std::sqrt(static_cast<float>(E)), 0.0f);   // :119
+    dS.ActivationBackward(cudnnActivationMode_t::CUDNN_ACTIVATION_SOFTMAX_LAST_DIMENSION, dW, nullptr, &wts);   // :121
+    dQ2.BatchMatrixMultiplication(dS, false, K, false, 1.0f, 0.0f);                                    // :123
+    dK2.BatchMatrixMultiplication(dS, true, Q, false, 1.0f, 0.0f);                                     // :124
+    auto a = dQ.ContentAsFloatArray(), b = dQ2.ContentAsFloatArray();
+    for (size_t i = 0; i < a.size(); ++i) EXPECT(std::fabs(a[i] - b[i]) < 2e-5, "dQ at %zu", i);
+    a = dK.ContentAsFloatArray(); b = dK2.ContentAsFloatArray();
+    for (size_t i = 0; i < a.size(); ++i) EXPECT(std::fabs(a[i] - b[i]) < 2e-5, "dK at %zu", i);
+    a = dV.ContentAsFloatArray(); b = dV2.ContentAsFloatArray();
+    for (size_t i = 0; i < a.size(); ++i) EXPECT(std::fabs(a[i] - b[i]) < 2e-5, "dV at %zu", i);
+    // head split: [b, t, h, d] -> [b, h, t, d]
+    GPUTensor heads({2, 5, 3, 8}, q.data(), gpu), split({2, 3, 5, 8}, nullptr, gpu);
+    heads.TransposeSecondAndThirdDimension(split);
+    auto sp = split.ContentAsFloatArray();
+    for (int bb = 0; bb < 2; ++bb) for (int t = 0; t < 5; ++t) for (int h = 0; h < 3; ++h) for (int d = 0; d < 8; ++d)
+      EXPECT(sp[((bb * 3 + h) * 5 + t) * 8 + d] == q[((bb * 5 + t) * 3 + h) * 8 + d], "transposition at %d %d %d %d", bb, t, h, d);
+    EXPECT(split.Shape[1] == 3 && split.Shape[2] == 5, "transposed shape");
+    // SGD with momentum, then Adam, one step each against the formulas of Prod/CPU/CpuTensor.cs:470-489,1755-1769
+    const int n = 777;
+    auto w0 = uniform(n, -1, 1, 90), g = uniform(n, -1, 1, 91), vel0 = uniform(n, -0.1f, 0.1f, 92);
+    GPUTensor W({n}, w0.data(), gpu), G({n}, g.data(), gpu), Vel({n}, vel0.data(), gpu);
+    W.UpdateSGDOptimizer(0.1, 0.9, false, G, &Vel);
+    auto wn = W.ContentAsFloatArray(), vn = Vel.ContentAsFloatArray();
+    for (int i = 0; i < n; ++i) {
+      const float vel = 0.9f * vel0[i] - 0.1f * g[i];
+      EXPECT(std::fabs(vn[i] - vel) < 1e-6 && std::fabs(wn[i] - (w0[i] + vel)) < 1e-6, "SGD at %d", i);
+    }
+    GPUTensor W2({n}, w0.data(), gpu), M1({n}, nullptr, gpu), M2({n}, nullptr, gpu);
+    W2.UpdateAdamOptimizer(0.01, 0.9, 0.999, 1e-8, 0.0, G, M1, M2, 1);
+    wn = W2.ContentAsFloatArray();
+    for (int i = 0; i < n; ++i) {
+      const double m = 0.1 * g[i], s2 = 0.001 * g[i] * g[i];
+      const double step = 0.01 * std::sqrt(1 - 0.999) / (1 - 0.9) * m / (std::sqrt(s2) + 1e-8);
+      EXPECT(std::fabs(wn[i] - (w0[i] - step)) < 2e-6, "Adam at %d: %f against %f", i, wn[i], w0[i] - step);
+    }
+  }
   {  // errors surface as exceptions, like GPUWrapper.CheckStatus
     GPUTensor A({4, 3}, nullptr, gpu), B({5, 4}, nullptr, gpu), C({4, 4}, nullptr, gpu);
     bool thrown = false;
