@@ -6,6 +6,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <memory>
 #include <numeric>
 #include <stdexcept>
 #include <string>
@@ -232,6 +233,72 @@ struct ScaledDotProductAttentionLayer {
                                   K.Pointer(), V.Pointer(), dy.Pointer(), weights_buffer.Pointer(),
                                   scores_grad_scratch.Pointer(), dQ.Pointer(), dK.Pointer(), dV.Pointer()));
   }
+};
+
+// The multi-head attention layer (Prod/Layers/MultiheadAttention.cs:178-295) over snb200_mha_fwd / snb200_mha_bwd:
+// the parameters (weights [out, in], biases or null) belong to the caller, the state the layer keeps between its
+// two passes (:73-81) and the backward scratch are allocated on first use for the shapes of the call.
+class MultiheadAttention {
+ public:
+  struct Parameters {
+    const GPUTensor *w_Q, *w_K, *w_V, *out_proj_weight;
+    const GPUTensor *w_Q_bias, *w_K_bias, *w_V_bias, *out_proj_bias;   // null: no bias
+  };
+  struct Gradients {
+    GPUTensor *w_Q, *w_K, *w_V, *out_proj_weight;
+    GPUTensor *w_Q_bias, *w_K_bias, *w_V_bias, *out_proj_bias;         // null where the layer has no bias
+  };
+  MultiheadAttention(int num_heads, int key_dim, int value_dim, bool is_causal, GPUWrapper& wrapper)
+      : num_heads_(num_heads), key_dim_(key_dim), value_dim_(value_dim), is_causal_(is_causal), wrapper_(&wrapper) {}
+
+  void ForwardPropagation(const GPUTensor& Q, const GPUTensor& K, const GPUTensor& V, const Parameters& p, GPUTensor& y) {
+    const snb200_mha_desc d = Desc(Q, V);
+    const int BH = d.batch * num_heads_;
+    Q_heads_T.reset(new GPUTensor({BH, d.q_steps, key_dim_}, nullptr, *wrapper_));
+    K_heads_T.reset(new GPUTensor({BH, d.v_steps, key_dim_}, nullptr, *wrapper_));
+    V_heads_T.reset(new GPUTensor({BH, d.v_steps, value_dim_}, nullptr, *wrapper_));
+    attention_heads_T.reset(new GPUTensor({d.batch, d.q_steps, num_heads_ * value_dim_}, nullptr, *wrapper_));
+    weights_buffer.reset(new GPUTensor({BH, d.q_steps, d.v_steps}, nullptr, *wrapper_));
+    const snb200_mha_weights w = Weights(p);
+    const snb200_mha_state st = State();
+    wrapper_->CheckStatus(snb200_mha_fwd(wrapper_->Handle(), &d, &w, Q.Pointer(), K.Pointer(), V.Pointer(), &st, nullptr,
+                                         y.Pointer()));
+  }
+  // dW_multiplier: the factor of the weight gradients (Linear.cs:152-158)
+  void BackwardPropagation(const GPUTensor& Q, const GPUTensor& K, const GPUTensor& V, const GPUTensor& dy,
+                           const Parameters& p, float dW_multiplier, const Gradients& g, GPUTensor& dQ, GPUTensor& dK,
+                           GPUTensor& dV) {
+    const snb200_mha_desc d = Desc(Q, V);
+    const long long need = snb200_mha_scratch_floats(&d, 1);
+    if (!scratch_ || scratch_->Count() < need) scratch_.reset(new GPUTensor({static_cast<int>(need)}, nullptr, *wrapper_));
+    const snb200_mha_weights w = Weights(p);
+    const snb200_mha_state st = State();
+    auto ptr = [](GPUTensor* t) { return t ? t->Pointer() : nullptr; };
+    const snb200_mha_gradients gr = {ptr(g.w_Q), ptr(g.w_K), ptr(g.w_V), ptr(g.out_proj_weight),
+                                     ptr(g.w_Q_bias), ptr(g.w_K_bias), ptr(g.w_V_bias), ptr(g.out_proj_bias)};
+    wrapper_->CheckStatus(snb200_mha_bwd(wrapper_->Handle(), &d, &w, Q.Pointer(), K.Pointer(), V.Pointer(), dy.Pointer(), &st,
+                                         dW_multiplier, scratch_->Pointer(), &gr, dQ.Pointer(), dK.Pointer(), dV.Pointer()));
+  }
+  // what the layer keeps between the passes (MultiheadAttention.cs:73-81)
+  std::unique_ptr<GPUTensor> Q_heads_T, K_heads_T, V_heads_T, attention_heads_T, weights_buffer;
+
+ private:
+  snb200_mha_desc Desc(const GPUTensor& Q, const GPUTensor& V) const {
+    return {SNB200_W_OUT_IN, Q.Shape[0], Q.Shape[1], V.Shape[1], Q.Shape[2], num_heads_, key_dim_, value_dim_, is_causal_};
+  }
+  static snb200_mha_weights Weights(const Parameters& p) {
+    auto ptr = [](const GPUTensor* t) -> const float* { return t ? t->Pointer() : nullptr; };
+    return {ptr(p.w_Q), ptr(p.w_K), ptr(p.w_V), ptr(p.out_proj_weight), ptr(p.w_Q_bias), ptr(p.w_K_bias), ptr(p.w_V_bias),
+            ptr(p.out_proj_bias)};
+  }
+  snb200_mha_state State() const {
+    return {Q_heads_T->Pointer(), K_heads_T->Pointer(), V_heads_T->Pointer(), attention_heads_T->Pointer(),
+            weights_buffer->Pointer()};
+  }
+  int num_heads_, key_dim_, value_dim_;
+  bool is_causal_;
+  GPUWrapper* wrapper_;
+  std::unique_ptr<GPUTensor> scratch_;
 };
 
 }  // namespace SharpNet

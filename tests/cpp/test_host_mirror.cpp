@@ -222,6 +222,67 @@ int main() {
       EXPECT(std::fabs(wn[i] - (w0[i] - step)) < 2e-6, "Adam at %d: %f against %f", i, wn[i], w0[i] - step);
     }
   }
+  {  // multi-head attention as one call each way against the layer's own sequence of tensor calls
+     // (Prod/Layers/MultiheadAttention.cs:178-295): projections on the last dimension, head split, attention per
+     // head, head merge, output projection -- and the reverse
+    const int B = 3, T = 24, H = 4, d = 8, E = H * d;
+    auto q = uniform(B * T * E, -1, 1, 100), k = uniform(B * T * E, -1, 1, 101), v = uniform(B * T * E, -1, 1, 102), g = uniform(B * T * E, -1, 1, 103);
+    auto wq = uniform(E * E, -0.3f, 0.3f, 104), wk = uniform(E * E, -0.3f, 0.3f, 105), wv = uniform(E * E, -0.3f, 0.3f, 106), wo = uniform(E * E, -0.3f, 0.3f, 107);
+    auto bq = uniform(E, -0.2f, 0.2f, 108), bk = uniform(E, -0.2f, 0.2f, 109), bv = uniform(E, -0.2f, 0.2f, 110), bo = uniform(E, -0.2f, 0.2f, 111);
+    GPUTensor Q({B, T, E}, q.data(), gpu), K({B, T, E}, k.data(), gpu), V({B, T, E}, v.data(), gpu), DY({B, T, E}, g.data(), gpu);
+    GPUTensor Wq({E, E}, wq.data(), gpu), Wk({E, E}, wk.data(), gpu), Wv({E, E}, wv.data(), gpu), Wo({E, E}, wo.data(), gpu);
+    GPUTensor Bq({E}, bq.data(), gpu), Bk({E}, bk.data(), gpu), Bv({E}, bv.data(), gpu), Bo({E}, bo.data(), gpu);
+    MultiheadAttention mha(H, d, d, true, gpu);
+    const MultiheadAttention::Parameters params = {&Wq, &Wk, &Wv, &Wo, &Bq, &Bk, &Bv, &Bo};
+    GPUTensor y({B, T, E}, nullptr, gpu);
+    mha.ForwardPropagation(Q, K, V, params, y);
+    // the same with the layer's tensor calls
+    auto project = [&](const GPUTensor& x, const GPUTensor& W, const GPUTensor& bias, GPUTensor& heads_T) {
+      GPUTensor p({B, T, E}, nullptr, gpu);
+      Linear::DenseForwardPropagation(p, x, W, &bias, true);
+      GPUTensor split({B, H, T, d}, nullptr, gpu);
+      p.Reshape({B, T, H, d}).TransposeSecondAndThirdDimension(split);
+      cudaMemcpy(heads_T.Pointer(), split.Pointer(), sizeof(float) * B * T * E, cudaMemcpyDeviceToDevice);
+    };
+    GPUTensor QhT({B * H, T, d}, nullptr, gpu), KhT({B * H, T, d}, nullptr, gpu), VhT({B * H, T, d}, nullptr, gpu);
+    project(Q, Wq, Bq, QhT); project(K, Wk, Bk, KhT); project(V, Wv, Bv, VhT);
+    GPUTensor att({B * H, T, d}, nullptr, gpu), wts({B * H, T, T}, nullptr, gpu), attT({B, T, H, d}, nullptr, gpu), y2({B, T, E}, nullptr, gpu);
+    ScaledDotProductAttentionLayer::ScaledDotProductAttentionForwardPropagation(QhT, KhT, VhT, att, wts, true, true);
+    att.Reshape({B, H, T, d}).TransposeSecondAndThirdDimension(attT);
+    GPUTensor attT3 = attT.Reshape({B, T, E});
+    Linear::DenseForwardPropagation(y2, attT3, Wo, &Bo, true);
+    auto a = y.ContentAsFloatArray(), b2 = y2.ContentAsFloatArray();
+    for (size_t i = 0; i < a.size(); ++i) EXPECT(std::fabs(a[i] - b2[i]) < 3e-5, "multi-head attention output at %zu: %f against %f", i, a[i], b2[i]);
+    // backward
+    GPUTensor dWq({E, E}, nullptr, gpu), dWk({E, E}, nullptr, gpu), dWv({E, E}, nullptr, gpu), dWo({E, E}, nullptr, gpu);
+    GPUTensor dBq({E}, nullptr, gpu), dBk({E}, nullptr, gpu), dBv({E}, nullptr, gpu), dBo({E}, nullptr, gpu);
+    GPUTensor dQ({B, T, E}, nullptr, gpu), dK({B, T, E}, nullptr, gpu), dV({B, T, E}, nullptr, gpu);
+    const MultiheadAttention::Gradients grads = {&dWq, &dWk, &dWv, &dWo, &dBq, &dBk, &dBv, &dBo};
+    mha.BackwardPropagation(Q, K, V, DY, params, 1.0f, grads, dQ, dK, dV);
+    GPUTensor dAttT({B, T, E}, nullptr, gpu), dWo2({E, E}, nullptr, gpu), dBo2({E}, nullptr, gpu);
+    Linear::DenseBackwardPropagation(&dAttT, dWo2, &dBo2, attT3, DY, Wo, 1.0f, false, true);
+    GPUTensor dAtt({B, H, T, d}, nullptr, gpu);
+    dAttT.Reshape({B, T, H, d}).TransposeSecondAndThirdDimension(dAtt);
+    GPUTensor dAtt3 = dAtt.Reshape({B * H, T, d});
+    GPUTensor dQh({B * H, T, d}, nullptr, gpu), dKh({B * H, T, d}, nullptr, gpu), dVh({B * H, T, d}, nullptr, gpu), scratch({B * H, T, T}, nullptr, gpu);
+    ScaledDotProductAttentionLayer::ScaledDotProductAttentionBackwardPropagation(dQh, dKh, dVh, QhT, KhT, VhT, dAtt3, wts, scratch, true);
+    auto unproject = [&](const GPUTensor& dheads, const GPUTensor& x, const GPUTensor& W, GPUTensor& dx, GPUTensor& dW, GPUTensor& db) {
+      GPUTensor merged({B, T, H, d}, nullptr, gpu);
+      dheads.Reshape({B, H, T, d}).TransposeSecondAndThirdDimension(merged);
+      GPUTensor merged3 = merged.Reshape({B, T, E});
+      Linear::DenseBackwardPropagation(&dx, dW, &db, x, merged3, W, 1.0f, false, true);
+    };
+    GPUTensor dQ2({B, T, E}, nullptr, gpu), dK2({B, T, E}, nullptr, gpu), dV2({B, T, E}, nullptr, gpu);
+    GPUTensor dWq2({E, E}, nullptr, gpu), dWk2({E, E}, nullptr, gpu), dWv2({E, E}, nullptr, gpu), dBq2({E}, nullptr, gpu), dBk2({E}, nullptr, gpu), dBv2({E}, nullptr, gpu);
+    unproject(dQh, Q, Wq, dQ2, dWq2, dBq2); unproject(dKh, K, Wk, dK2, dWk2, dBk2); unproject(dVh, V, Wv, dV2, dWv2, dBv2);
+    auto close = [&](const GPUTensor& x1, const GPUTensor& x2, double tol, const char* what) {
+      auto u = x1.ContentAsFloatArray(), w2 = x2.ContentAsFloatArray();
+      for (size_t i = 0; i < u.size(); ++i) EXPECT(std::fabs(u[i] - w2[i]) < tol, "%s at %zu: %f against %f", what, i, u[i], w2[i]);
+    };
+    close(dQ, dQ2, 5e-5, "dQ"); close(dK, dK2, 5e-5, "dK"); close(dV, dV2, 5e-5, "dV");
+    close(dWq, dWq2, 2e-4, "dW_Q"); close(dWk, dWk2, 2e-4, "dW_K"); close(dWv, dWv2, 2e-4, "dW_V"); close(dWo, dWo2, 2e-4, "dW_O");
+    close(dBq, dBq2, 2e-4, "db_Q"); close(dBo, dBo2, 2e-4, "db_O");
+  }
   {  // errors surface as exceptions, like GPUWrapper.CheckStatus
     GPUTensor A({4, 3}, nullptr, gpu), B({5, 4}, nullptr, gpu), C({4, 4}, nullptr, gpu);
     bool thrown = false;
