@@ -23,6 +23,11 @@ enum class cudnnActivationMode_t : int {   // Prod/GPU/CudnnWrapper.cs:267-281
   CUDNN_ACTIVATION_LEAKY_RELU = 1002, CUDNN_ACTIVATION_LN = 1004, CUDNN_ACTIVATION_SOFTMAX_LAST_DIMENSION = 1005
 };
 
+enum class EvaluationMetricEnum : int {   // the losses whose gradient the library produces (Prod/Data/Tensor.cs:1182-1217)
+  BinaryCrossentropy = SNB200_LOSS_BINARY_CROSSENTROPY, CategoricalCrossentropy = SNB200_LOSS_CATEGORICAL_CROSSENTROPY,
+  Mse = SNB200_LOSS_MSE
+};
+
 // One per device: owns the library handle (the role of Prod/GPU/GPUWrapper.cs:99-160).
 class GPUWrapper {
  public:
@@ -163,6 +168,11 @@ class GPUTensor {
     wrapper_->CheckStatus(snb200_adam_update(wrapper_->Handle(), Count(), learningRate, beta1, beta2, epsilon, weight_decay,
                                              timeStep, dW.ptr_, ptr_, adam_vW.ptr_, adam_sW.ptr_));
   }
+  // this = dyPredicted = scale * (yPredicted - yExpected)   (Tensor.cs:1182-1217)
+  void ComputeGradientForEvaluationMetric(const GPUTensor& yExpected, const GPUTensor& yPredicted, EvaluationMetricEnum loss) {
+    wrapper_->CheckStatus(snb200_loss_gradient(wrapper_->Handle(), static_cast<int>(loss), Shape[0], MultDim0(),
+                                               yExpected.ptr_, yPredicted.ptr_, ptr_));
+  }
   GPUWrapper& Wrapper() const { return *wrapper_; }
 
  private:
@@ -211,6 +221,53 @@ struct Linear {
                                    z ? z->Pointer() : nullptr, multiplier, dzScratch ? dzScratch->Pointer() : nullptr,
                                    dx ? dx->Pointer() : nullptr, dW.Pointer(), db ? db->Pointer() : nullptr));
   }
+};
+
+// Page-locks a caller-owned host array for as long as the object lives, as HostPinnedMemory does for a managed
+// array (Prod/CPU/HostPinnedMemory.cs:17-21): what the asynchronous host-to-device copies below need.
+class HostPinnedMemory {
+ public:
+  HostPinnedMemory(void* hostPointer, long long bytes) : ptr_(hostPointer) {
+    const int st = snb200_host_pin(hostPointer, bytes);
+    if (st != 0) throw std::runtime_error("snb200_host_pin failed with status " + std::to_string(st));
+  }
+  ~HostPinnedMemory() { snb200_host_unpin(ptr_); }
+  HostPinnedMemory(const HostPinnedMemory&) = delete;
+  HostPinnedMemory& operator=(const HostPinnedMemory&) = delete;
+  void* Pointer() const { return ptr_; }
+ private:
+  void* ptr_;
+};
+
+// The mini-batch copies of Network.cs:1211-1258 (x_miniBatch_cpu.CopyTo(x_miniBatch)) on a copy stream of their
+// own, `slots`-fold buffered: Issue(slot, ...) queues the copies of a step's inputs, Acquire(slot) makes the
+// wrapper's stream wait for them, Release(slot) marks where the slot's last reader ends.
+class MiniBatchStager {
+ public:
+  MiniBatchStager(GPUWrapper& wrapper, int slots) : wrapper_(&wrapper) {
+    wrapper_->CheckStatus(snb200_stager_create(wrapper_->Handle(), slots, &stager_));
+  }
+  ~MiniBatchStager() { if (stager_) snb200_stager_destroy(stager_); }
+  MiniBatchStager(const MiniBatchStager&) = delete;
+  MiniBatchStager& operator=(const MiniBatchStager&) = delete;
+  // copies[i]: (device tensor of the slot, pinned host source holding at least its Count() floats)
+  void Issue(int slot, const std::vector<std::pair<GPUTensor*, const float*>>& copies) {
+    std::vector<void*> dst;
+    std::vector<const void*> src;
+    std::vector<long long> bytes;
+    for (const auto& c : copies) {
+      dst.push_back(c.first->Pointer());
+      src.push_back(c.second);
+      bytes.push_back(static_cast<long long>(sizeof(float)) * c.first->Count());
+    }
+    wrapper_->CheckStatus(snb200_stager_issue(stager_, slot, static_cast<int>(copies.size()), dst.data(), src.data(), bytes.data()));
+  }
+  void Acquire(int slot) { wrapper_->CheckStatus(snb200_stager_acquire(stager_, slot)); }
+  void AcquirePart(int slot, int part) { wrapper_->CheckStatus(snb200_stager_acquire_part(stager_, slot, part)); }
+  void Release(int slot) { wrapper_->CheckStatus(snb200_stager_release(stager_, slot)); }
+ private:
+  GPUWrapper* wrapper_;
+  snb200_stager_t stager_ = nullptr;
 };
 
 // Static methods of the attention layer (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-129); Q [batch, q, E],

@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <memory>
 #include <random>
 
 #include "../../sharpnet_b200/host/sharpnet_tensor.hpp"
@@ -282,6 +283,45 @@ int main() {
     close(dQ, dQ2, 5e-5, "dQ"); close(dK, dK2, 5e-5, "dK"); close(dV, dV2, 5e-5, "dV");
     close(dWq, dWq2, 2e-4, "dW_Q"); close(dWk, dWk2, 2e-4, "dW_K"); close(dWv, dWv2, 2e-4, "dW_V"); close(dWo, dWo2, 2e-4, "dW_O");
     close(dBq, dBq2, 2e-4, "db_Q"); close(dBo, dBo2, 2e-4, "db_O");
+  }
+  {  // loss gradients (Prod/Data/Tensor.cs:1182-1217) and the mini-batch staging of Network.cs:1211-1258:
+     // three steps, double buffered, each step's input copied from pinned host memory while the step before runs
+    const int rows = 50, cols = 7;
+    auto t = uniform(rows * cols, 0, 1, 120), pr = uniform(rows * cols, 0, 1, 121);
+    GPUTensor Tt({rows, cols}, t.data(), gpu), P({rows, cols}, pr.data(), gpu), D({rows, cols}, nullptr, gpu);
+    D.ComputeGradientForEvaluationMetric(Tt, P, EvaluationMetricEnum::CategoricalCrossentropy);
+    auto dv = D.ContentAsFloatArray();
+    for (int i = 0; i < rows * cols; ++i) EXPECT(dv[i] == pr[i] - t[i], "categorical cross-entropy gradient at %d", i);
+    D.ComputeGradientForEvaluationMetric(Tt, P, EvaluationMetricEnum::Mse);
+    dv = D.ContentAsFloatArray();
+    for (int i = 0; i < rows * cols; ++i) EXPECT(std::fabs(dv[i] - 2.0f * (pr[i] - t[i]) / cols) < 1e-7, "Mse gradient at %d", i);
+    D.ComputeGradientForEvaluationMetric(Tt, P, EvaluationMetricEnum::BinaryCrossentropy);
+    dv = D.ContentAsFloatArray();
+    for (int i = 0; i < rows * cols; ++i) EXPECT(std::fabs(dv[i] - (pr[i] - t[i]) / cols) < 1e-7, "binary cross-entropy gradient at %d", i);
+
+    const int M = 512, Kd = 64, N = 32, steps = 3;
+    std::vector<std::vector<float>> batches;
+    for (int i = 0; i < steps; ++i) batches.push_back(uniform(M * Kd, -1, 1, 130 + i));
+    std::vector<std::unique_ptr<HostPinnedMemory>> pins;
+    for (auto& bt : batches) pins.emplace_back(new HostPinnedMemory(bt.data(), static_cast<long long>(sizeof(float)) * bt.size()));
+    auto wv = uniform(Kd * N, -1, 1, 140);
+    GPUTensor Wm({Kd, N}, wv.data(), gpu);
+    GPUTensor x0({M, Kd}, nullptr, gpu), x1({M, Kd}, nullptr, gpu);
+    GPUTensor* slot_x[2] = {&x0, &x1};
+    std::vector<std::unique_ptr<GPUTensor>> outs;
+    for (int i = 0; i < steps; ++i) outs.emplace_back(new GPUTensor({M, N}, nullptr, gpu));
+    MiniBatchStager stager(gpu, 2);
+    stager.Issue(0, {{slot_x[0], batches[0].data()}});
+    for (int i = 0; i < steps; ++i) {
+      if (i + 1 < steps) stager.Issue((i + 1) % 2, {{slot_x[(i + 1) % 2], batches[i + 1].data()}});
+      stager.Acquire(i % 2);
+      outs[i]->Dot(*slot_x[i % 2], false, Wm, false, 1.0f, 0.0f);
+      stager.Release(i % 2);
+    }
+    std::vector<float> zeros(M * N, 0.0f);
+    for (int i = 0; i < steps; ++i)
+      EXPECT(max_abs_diff(outs[i]->ContentAsFloatArray(), ref_gemm(batches[i], M, Kd, false, wv, Kd, N, false, zeros, 1.0, 0.0)) / 8.0 < 1e-5,
+             "staged step %d", i);
   }
   {  // errors surface as exceptions, like GPUWrapper.CheckStatus
     GPUTensor A({4, 3}, nullptr, gpu), B({5, 4}, nullptr, gpu), C({4, 4}, nullptr, gpu);
