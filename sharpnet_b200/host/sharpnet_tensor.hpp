@@ -223,6 +223,35 @@ struct Linear {
   }
 };
 
+// The gradient sum of data-parallel training (Prod/Networks/NetworkMultiGPUSupport.cs:161-173) for SharpNet's
+// one-thread-per-GPU model (Prod/Networks/Network.cs:71-83): one communicator over the wrappers of one process.
+// AllReduceSum leaves the sum over all replicas in every replica's buffer; each wrapper's call is made from the
+// thread that drives that wrapper.
+class GradientCommunicator {
+ public:
+  explicit GradientCommunicator(const std::vector<GPUWrapper*>& wrappers) : wrappers_(wrappers) {
+    std::vector<snb200_handle_t> handles;
+    for (GPUWrapper* w : wrappers_) handles.push_back(w->Handle());
+    wrappers_[0]->CheckStatus(snb200_comm_init_all(handles.data(), static_cast<int>(handles.size())));
+  }
+  ~GradientCommunicator() { for (GPUWrapper* w : wrappers_) snb200_comm_destroy(w->Handle()); }
+  GradientCommunicator(const GradientCommunicator&) = delete;
+  GradientCommunicator& operator=(const GradientCommunicator&) = delete;
+  static void AllReduceSum(GPUTensor& gradients) {
+    GPUWrapper& w = gradients.Wrapper();
+    w.CheckStatus(snb200_allreduce_sum(w.Handle(), gradients.Pointer(), gradients.Count()));
+  }
+  // a layer's dW and db as one collective launch
+  static void AllReduceSum(GPUTensor& weightGradients, GPUTensor& biasGradients) {
+    GPUWrapper& w = weightGradients.Wrapper();
+    float* bufs[2] = {weightGradients.Pointer(), biasGradients.Pointer()};
+    const long long counts[2] = {weightGradients.Count(), biasGradients.Count()};
+    w.CheckStatus(snb200_allreduce_sum_group(w.Handle(), 2, bufs, counts));
+  }
+ private:
+  std::vector<GPUWrapper*> wrappers_;
+};
+
 // Page-locks a caller-owned host array for as long as the object lives, as HostPinnedMemory does for a managed
 // array (Prod/CPU/HostPinnedMemory.cs:17-21): what the asynchronous host-to-device copies below need.
 class HostPinnedMemory {

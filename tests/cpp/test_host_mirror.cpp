@@ -8,6 +8,7 @@
 #include <cstdlib>
 #include <memory>
 #include <random>
+#include <string>
 
 #include "../../sharpnet_b200/host/sharpnet_tensor.hpp"
 
@@ -322,6 +323,24 @@ int main() {
     for (int i = 0; i < steps; ++i)
       EXPECT(max_abs_diff(outs[i]->ContentAsFloatArray(), ref_gemm(batches[i], M, Kd, false, wv, Kd, N, false, zeros, 1.0, 0.0)) / 8.0 < 1e-5,
              "staged step %d", i);
+  }
+  {  // the gradient sum over the replicas of one process; with the one GPU this program drives the sum is the
+     // buffer itself (the two-GPU form runs in the Python suite, one thread per GPU)
+    auto gw = uniform(1000, -1, 1, 150), gb = uniform(10, -1, 1, 151);
+    GPUTensor GW({100, 10}, gw.data(), gpu), GB({10}, gb.data(), gpu);
+    std::unique_ptr<GradientCommunicator> comm;
+    try {
+      comm.reset(new GradientCommunicator({&gpu}));
+    } catch (const std::runtime_error& e) {   // status 15: no NCCL library on this machine, the one accepted reason
+      EXPECT(std::string(e.what()).find("status 15") != std::string::npos, "communicator: %s", e.what());
+    }
+    if (comm) {
+      GradientCommunicator::AllReduceSum(GW);
+      GradientCommunicator::AllReduceSum(GW, GB);
+      auto r = GW.ContentAsFloatArray(), rb = GB.ContentAsFloatArray();
+      for (size_t i = 0; i < r.size(); ++i) EXPECT(r[i] == gw[i], "all-reduce over one replica at %zu", i);
+      for (size_t i = 0; i < rb.size(); ++i) EXPECT(rb[i] == gb[i], "grouped all-reduce over one replica at %zu", i);
+    }
   }
   {  // errors surface as exceptions, like GPUWrapper.CheckStatus
     GPUTensor A({4, 3}, nullptr, gpu), B({5, 4}, nullptr, gpu), C({4, 4}, nullptr, gpu);
