@@ -50,3 +50,22 @@ def test_create_fails_loudly_without_a_device(built_library):
     from sharpnet_b200.tensor import GPUWrapper
     with pytest.raises(RuntimeError):
         GPUWrapper(0)
+
+
+def test_activation_codes_agree_everywhere():
+    """The activation selector has one numbering -- cudnnActivationMode_t of the reference
+    (Prod/GPU/CudnnWrapper.cs:267-281) -- in the C header, the ctypes binding, the oracle and the C++ mirror."""
+    import re
+    from oracle import sharpnet_oracle as orc
+    from sharpnet_b200 import _capi
+    header = open(os.path.join(ROOT, "include", "sharpnet_b200.h")).read()
+    mirror = open(os.path.join(ROOT, "sharpnet_b200", "host", "sharpnet_tensor.hpp")).read()
+    expected = {"SIGMOID": 0, "RELU": 1, "TANH": 2, "CLIPPED_RELU": 3, "ELU": 4, "IDENTITY": 5, "SWISH": 6, "SOFTMAX": 1000,
+                "LEAKY_RELU": 1002, "LN": 1004}
+    for name, value in expected.items():
+        m = re.search(r"SNB200_ACT_%s\s*=\s*(\d+)" % name, header)
+        assert m and int(m.group(1)) == value, name
+        assert getattr(_capi, "ACT_" + name) == value, name
+        assert getattr(orc, "ACT_" + name) == value, name
+        m = re.search(r"CUDNN_ACTIVATION_%s\s*=\s*(\d+)" % name, mirror)
+        assert m and int(m.group(1)) == value, name
