@@ -210,6 +210,15 @@ def softmax_gradient_last_dimension(dy, y, f64=False):
     return (p * (g - (g * p).sum(axis=-1, keepdims=True))).astype(t)
 
 
+def set_all_elements_above_main_diagonal(x, value):
+    """In place: x[..., row, col] = value for col > row, on one matrix or a batch of matrices
+    (Tensor.SetAllElementsAboveMainDiagonal, Prod/CPU/CpuTensor.cs:3037-3052): the causal mask of attention."""
+    assert x.ndim in (2, 3)
+    rows, cols = np.triu_indices(x.shape[-2], 1, x.shape[-1])
+    x[..., rows, cols] = value
+    return x
+
+
 def sdpa_forward(Q, K, V, use_scale, is_causal, f64=False):
     """Returns (weights, y) of ScaledDotProductAttentionLayer.ScaledDotProductAttentionForwardPropagation
     (Prod/Layers/ScaledDotProductAttentionLayer.cs:46-91): scores = scaling * Q K^T per batch element,
@@ -224,9 +233,7 @@ def sdpa_forward(Q, K, V, use_scale, is_causal, f64=False):
         s = np.zeros((B, Tq, Tk), dtype=np.float32)
         batch_matrix_multiplication(Q, False, K, True, s, np.float32(scaling), 0.0)
     if is_causal:
-        s = s.copy()
-        rows, cols = np.triu_indices(Tq, 1, Tk)
-        s[:, rows, cols] = -1e12
+        s = set_all_elements_above_main_diagonal(s.copy(), -1e12)
     if f64:
         e = np.exp(s - s.max(-1, keepdims=True))
         w = e / e.sum(-1, keepdims=True)

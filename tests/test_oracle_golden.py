@@ -318,3 +318,32 @@ def test_pytorch_layout_networks_after_training(golden):
     predict = _train_pytorch_mlp(x, t, w1, w2, orc.ACT_LEAKY_RELU, 0.1, orc.ACT_SOFTMAX, orc.LOSS_CATEGORICAL_CROSSENTROPY,
                                  0.1, 0.66, 0.17, True, 2)
     assert abs(cce(t, predict(x)) - golden["pt_leaky_loss_after"]) < 1e-6
+
+
+def test_transposition_and_causal_mask_goldens_of_the_reference():
+    """Tests/CPU/TestCpuTensor.cs:104-112 (TransposeSecondAndThirdDimension of arange(2*3*4*5), expected values as
+    written there) and :162-196 (SetAllElementsAboveMainDiagonal with -666 on 1x1, 1x6, 6x1, 2x3, 3x2 and 3x3)."""
+    x = np.arange(2 * 3 * 4 * 5, dtype=np.float32).reshape(2, 3, 4, 5)
+    expected = np.array(
+        [[[[0, 1, 2, 3, 4], [20, 21, 22, 23, 24], [40, 41, 42, 43, 44]], [[5, 6, 7, 8, 9], [25, 26, 27, 28, 29], [45, 46, 47, 48, 49]],
+          [[10, 11, 12, 13, 14], [30, 31, 32, 33, 34], [50, 51, 52, 53, 54]], [[15, 16, 17, 18, 19], [35, 36, 37, 38, 39], [55, 56, 57, 58, 59]]],
+         [[[60, 61, 62, 63, 64], [80, 81, 82, 83, 84], [100, 101, 102, 103, 104]], [[65, 66, 67, 68, 69], [85, 86, 87, 88, 89], [105, 106, 107, 108, 109]],
+          [[70, 71, 72, 73, 74], [90, 91, 92, 93, 94], [110, 111, 112, 113, 114]], [[75, 76, 77, 78, 79], [95, 96, 97, 98, 99], [115, 116, 117, 118, 119]]]],
+        dtype=np.float32)
+    np.testing.assert_array_equal(orc.transpose_second_third(x), expected)
+    v = -666.0
+    data = [0.5, 1, 2, 3, 4, 5]
+    cases = [((1, 1), [1.0], [1.0]),
+             ((1, 6), data, [0.5, v, v, v, v, v]),
+             ((6, 1), data, data),
+             ((2, 3), data, [0.5, v, v, 3, 4, v]),
+             ((3, 2), data, [0.5, v, 2, 3, 4, 5]),
+             ((3, 3), [0.5, 1, 2, 3, 4, 5, 6, 7, 8], [0.5, v, v, 3, 4, v, 6, 7, 8])]
+    for shape, src, want in cases:
+        got = orc.set_all_elements_above_main_diagonal(np.asarray(src, np.float32).reshape(shape), v)
+        np.testing.assert_array_equal(got.ravel(), np.asarray(want, np.float32))
+    # a batch of matrices is masked matrix by matrix (Prod/CPU/CpuTensor.cs:3040-3043)
+    batch = np.arange(2 * 3 * 3, dtype=np.float32).reshape(2, 3, 3)
+    got = orc.set_all_elements_above_main_diagonal(batch.copy(), v)
+    for b in range(2):
+        np.testing.assert_array_equal(got[b], orc.set_all_elements_above_main_diagonal(batch[b].copy(), v))
